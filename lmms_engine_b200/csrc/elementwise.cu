@@ -1,0 +1,853 @@
+// Bandwidth-bound kernels of the training step, written for sm_100a:
+// RMSNorm / LayerNorm (+ residual add) forward and backward, rotary embedding
+// (plain, multimodal-sectioned, multimodal-interleaved, vision 2-D all reduce to a
+// per-token cos/sin table plus one apply kernel), SwiGLU, flat-buffer AdamW, Muon
+// momentum / scale / update, EMA, gradient norm + clip, index gather/scatter for packed
+// sequences, and the cross-entropy passes that follow the logits GEMM.
+//
+// All kernels use 16-byte vector accesses, grid-stride loops sized to the SM count and
+// fp32 arithmetic on bf16 storage.  Reference behaviour: Liger RMSNorm / RoPE / SwiGLU
+// (src/lmms_engine/models/qwen2/monkey_patch.py:47-118), torch.optim.AdamW
+// (src/lmms_engine/train/fsdp2/fsdp2_trainer.py:202-209), the Muon update
+// (src/lmms_engine/utils/muon_utils.py:159-183, 273-275), EMA
+// (src/lmms_engine/utils/ema_utils.py:97-101) and foreach grad clipping
+// (src/lmms_engine/utils/fsdp2_utils.py:250-289).
+#include "common.cuh"
+
+namespace b200 {
+
+typedef __nv_bfloat16 bf16;
+
+struct alignas(16) bf16x8 {
+  uint32_t w[4];
+};
+
+__device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
+  bf16x8 u = *reinterpret_cast<const bf16x8*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = unpack_bf16x2(u.w[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) {
+  bf16x8 u;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) u.w[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<bf16x8*>(p) = u;
+}
+
+template <int kThreads>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < kThreads / 32) ? red[lane] : 0.f;
+  t = warp_sum(t);
+  __syncthreads();
+  return t;
+}
+
+// ------------------------------------------------------------------ RMSNorm / LayerNorm forward
+// One CTA per row (H >= 1024) keeps the row in registers: H <= kThreads * 8 * kVecPerThread.
+// y = (x [+ res]) * rstd * (w + w_offset);  optional res_out = x + res;  LayerNorm when `ln`.
+template <int kThreads, int kVec>
+__global__ void __launch_bounds__(kThreads) norm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res,
+                                                            const bf16* __restrict__ w, const bf16* __restrict__ b,
+                                                            bf16* __restrict__ y, bf16* __restrict__ res_out,
+                                                            float* __restrict__ rstd_out, float* __restrict__ mean_out,
+                                                            int rows, int H, float eps, float w_offset, int ln) {
+  __shared__ float red[32];
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const size_t base = static_cast<size_t>(row) * H;
+    float v[kVec][8];
+    float s = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) {
+      const int c = (i * kThreads + threadIdx.x) * 8;
+      if (c < H) {
+        load8(x + base + c, v[i]);
+        if (res != nullptr) {
+          float r[8];
+          load8(res + base + c, r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] += r[j];
+          // round the sum to bf16 so that the normalised row matches the stored residual stream
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] = __bfloat162float(__float2bfloat16(v[i][j]));
+          if (res_out != nullptr) store8(res_out + base + c, v[i]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          s += v[i][j];
+          s2 += v[i][j] * v[i][j];
+        }
+      }
+    }
+    float mean = 0.f;
+    if (ln) {
+      mean = block_sum<kThreads>(s, red) / H;
+      float var = 0.f;
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) {
+        const int c = (i * kThreads + threadIdx.x) * 8;
+        if (c < H) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float d = v[i][j] - mean;
+            var += d * d;
+          }
+        }
+      }
+      s2 = block_sum<kThreads>(var, red);
+    } else {
+      s2 = block_sum<kThreads>(s2, red);
+    }
+    const float rstd = rsqrtf(s2 / H + eps);
+    if (threadIdx.x == 0) {
+      rstd_out[row] = rstd;
+      if (ln && mean_out != nullptr) mean_out[row] = mean;
+    }
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) {
+      const int c = (i * kThreads + threadIdx.x) * 8;
+      if (c < H) {
+        float wv[8], o[8];
+        load8(w + c, wv);
+        float bv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (b != nullptr) load8(b + c, bv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * (wv[j] + w_offset) + bv[j];
+        store8(y + base + c, o);
+      }
+    }
+  }
+}
+
+// One warp per row for short rows (per-head QK-norm: H = 64..512, multiple of 8).
+__global__ void __launch_bounds__(256) norm_fwd_warp_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                                            bf16* __restrict__ y, float* __restrict__ rstd_out, int rows,
+                                                            int H, float eps, float w_offset) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  for (int row = blockIdx.x * wpb + (threadIdx.x >> 5); row < rows; row += gridDim.x * wpb) {
+    const size_t base = static_cast<size_t>(row) * H;
+    float v[2][8];
+    float s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      if (c < H) {
+        load8(x + base + c, v[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s2 += v[i][j] * v[i][j];
+      }
+    }
+    s2 = warp_sum(s2);
+    const float rstd = rsqrtf(s2 / H + eps);
+    if (lane == 0) rstd_out[row] = rstd;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      if (c < H) {
+        float wv[8], o[8];
+        load8(w + c, wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = v[i][j] * rstd * (wv[j] + w_offset);
+        store8(y + base + c, o);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ RMSNorm / LayerNorm backward
+// dx = rstd * (g - xhat * mean(g * xhat) [- mean(g) for LN]) [+ dres_in], g = dy * (w + off)
+// Partial dw (and db) are accumulated per CTA in registers over its rows and written to
+// dw_part[blockIdx.x, H]; a second kernel reduces the partials.
+template <int kThreads, int kVec>
+__global__ void __launch_bounds__(kThreads)
+norm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
+                const float* __restrict__ rstd_in, const float* __restrict__ mean_in, const bf16* __restrict__ dres_in,
+                bf16* __restrict__ dx, float* __restrict__ dw_part, float* __restrict__ db_part, int rows, int H,
+                float w_offset, int ln) {
+  __shared__ float red[32];
+  float dw[kVec][8], db[kVec][8];
+#pragma unroll
+  for (int i = 0; i < kVec; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw[i][j] = 0.f, db[i][j] = 0.f;
+
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const size_t base = static_cast<size_t>(row) * H;
+    const float rstd = rstd_in[row];
+    const float mean = (ln && mean_in != nullptr) ? mean_in[row] : 0.f;
+    float g[kVec][8], xh[kVec][8];
+    float dot = 0.f, gsum = 0.f;
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) {
+      const int c = (i * kThreads + threadIdx.x) * 8;
+      if (c < H) {
+        float dyv[8], xv[8], wv[8];
+        load8(dy + base + c, dyv);
+        load8(x + base + c, xv);
+        load8(w + c, wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = (xv[j] - mean) * rstd;
+          g[i][j] = dyv[j] * (wv[j] + w_offset);
+          dw[i][j] += dyv[j] * xh[i][j];
+          db[i][j] += dyv[j];
+          dot += g[i][j] * xh[i][j];
+          gsum += g[i][j];
+        }
+      }
+    }
+    dot = block_sum<kThreads>(dot, red) / H;
+    if (ln) gsum = block_sum<kThreads>(gsum, red) / H;
+    else gsum = 0.f;
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) {
+      const int c = (i * kThreads + threadIdx.x) * 8;
+      if (c < H) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - xh[i][j] * dot - gsum);
+        if (dres_in != nullptr) {
+          float r[8];
+          load8(dres_in + base + c, r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += r[j];
+        }
+        store8(dx + base + c, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kVec; ++i) {
+    const int c = (i * kThreads + threadIdx.x) * 8;
+    if (c < H) {
+      float* o = dw_part + static_cast<size_t>(blockIdx.x) * H + c;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = dw[i][j];
+      if (db_part != nullptr) {
+        float* ob = db_part + static_cast<size_t>(blockIdx.x) * H + c;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ob[j] = db[i][j];
+      }
+    }
+  }
+}
+
+__global__ void norm_bwd_warp_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                     const bf16* __restrict__ w, const float* __restrict__ rstd_in,
+                                     bf16* __restrict__ dx, float* __restrict__ dw_part, int rows, int H,
+                                     float w_offset) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  const int gw = blockIdx.x * wpb + (threadIdx.x >> 5);
+  float dw[2][8];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw[i][j] = 0.f;
+  for (int row = gw; row < rows; row += gridDim.x * wpb) {
+    const size_t base = static_cast<size_t>(row) * H;
+    const float rstd = rstd_in[row];
+    float g[2][8], xh[2][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      if (c < H) {
+        float dyv[8], xv[8], wv[8];
+        load8(dy + base + c, dyv);
+        load8(x + base + c, xv);
+        load8(w + c, wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = xv[j] * rstd;
+          g[i][j] = dyv[j] * (wv[j] + w_offset);
+          dw[i][j] += dyv[j] * xh[i][j];
+          dot += g[i][j] * xh[i][j];
+        }
+      }
+    }
+    dot = warp_sum(dot) / H;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      if (c < H) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - xh[i][j] * dot);
+        store8(dx + base + c, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int c = (i * 32 + lane) * 8;
+    if (c < H) {
+      float* o = dw_part + static_cast<size_t>(gw) * H + c;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = dw[i][j];
+    }
+  }
+}
+
+// out[c] = sum_p part[p, c]  (fp32 -> fp32, optionally accumulating into out)
+__global__ void colsum_kernel(const float* __restrict__ part, float* __restrict__ out, int parts, int H,
+                              int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  float s = 0.f;
+  for (int p = 0; p < parts; ++p) s += part[static_cast<size_t>(p) * H + c];
+  out[c] = accumulate ? out[c] + s : s;
+}
+
+// ------------------------------------------------------------------ rotary embedding
+// cos/sin tables [T, D] (fp32) from up to three position streams.
+// mode 0: plain (pos[0]);  mode 1: sectioned M-RoPE (frequency i uses stream by section
+// boundaries s0, s0+s1);   mode 2: interleaved M-RoPE (Qwen3-VL: frequency i uses stream
+// i % 3 while i < 3*section[i % 3] for streams 1, 2; stream 0 otherwise).
+__global__ void rope_table_kernel(const int64_t* __restrict__ pos, const float* __restrict__ inv_freq,
+                                  float* __restrict__ cos_out, float* __restrict__ sin_out, int T, int half,
+                                  int mode, int s0, int s1, int s2, float scaling) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= T * half) return;
+  const int t = idx / half, i = idx - t * half;
+  int stream = 0;
+  if (mode == 1) {
+    stream = (i < s0) ? 0 : (i < s0 + s1 ? 1 : 2);
+  } else if (mode == 2) {
+    const int m = i % 3;
+    if (m == 1 && i < 3 * s1) stream = 1;
+    else if (m == 2 && i < 3 * s2) stream = 2;
+    else stream = 0;
+  }
+  const float ang = static_cast<float>(pos[static_cast<size_t>(stream) * T + t]) * inv_freq[i];
+  float sn, cs;
+  sincosf(ang, &sn, &cs);
+  cs *= scaling;
+  sn *= scaling;
+  const size_t o = static_cast<size_t>(t) * 2 * half;
+  cos_out[o + i] = cs;
+  cos_out[o + half + i] = cs;
+  sin_out[o + i] = sn;
+  sin_out[o + half + i] = sn;
+}
+
+// x: [T, Hn, D] (row stride ldx elements between tokens), rotate-half convention:
+// y[:half] = x1*c1 - x2*s1 ; y[half:] = x2*c2 + x1*s2.  `conj` applies the transpose
+// (backward).  rot_dim <= D: dims beyond rot_dim are copied.
+__global__ void rope_apply_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, const float* __restrict__ cosb,
+                                  const float* __restrict__ sinb, int T, int Hn, int D, int rot_dim, long ldx,
+                                  long ldy, int conj) {
+  const int half = rot_dim / 2;
+  const int per_head = half / 8;  // vectors of 8 pairs
+  const long total = static_cast<long>(T) * Hn * per_head;
+  for (long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long>(gridDim.x) * blockDim.x) {
+    const int v = idx % per_head;
+    const long th = idx / per_head;
+    const int h = th % Hn;
+    const long t = th / Hn;
+    const bf16* xp = x + t * ldx + static_cast<long>(h) * D;
+    bf16* yp = y + t * ldy + static_cast<long>(h) * D;
+    float x1[8], x2[8], o1[8], o2[8];
+    load8(xp + v * 8, x1);
+    load8(xp + half + v * 8, x2);
+    const float* c = cosb + t * rot_dim;
+    const float* s = sinb + t * rot_dim;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float c1 = c[v * 8 + j], c2 = c[half + v * 8 + j];
+      const float s1 = s[v * 8 + j], s2 = s[half + v * 8 + j];
+      if (!conj) {
+        o1[j] = x1[j] * c1 - x2[j] * s1;
+        o2[j] = x2[j] * c2 + x1[j] * s2;
+      } else {
+        o1[j] = x1[j] * c1 + x2[j] * s2;
+        o2[j] = x2[j] * c2 - x1[j] * s1;
+      }
+    }
+    store8(yp + v * 8, o1);
+    store8(yp + half + v * 8, o2);
+  }
+}
+
+// ------------------------------------------------------------------ SwiGLU
+__global__ void swiglu_fwd_kernel(const bf16* __restrict__ g, const bf16* __restrict__ u, bf16* __restrict__ h,
+                                  long n8) {
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    float gv[8], uv[8], o[8];
+    load8(g + i * 8, gv);
+    load8(u + i * 8, uv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = gv[j] / (1.f + __expf(-gv[j])) * uv[j];
+    store8(h + i * 8, o);
+  }
+}
+// dg, du may alias g, u (in place).
+__global__ void swiglu_bwd_kernel(const bf16* __restrict__ dh, const bf16* g, const bf16* u, bf16* dg, bf16* du,
+                                  long n8) {
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    float dv[8], gv[8], uv[8], og[8], ou[8];
+    load8(dh + i * 8, dv);
+    load8(g + i * 8, gv);
+    load8(u + i * 8, uv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sig = 1.f / (1.f + __expf(-gv[j]));
+      const float silu = gv[j] * sig;
+      ou[j] = dv[j] * silu;
+      og[j] = dv[j] * uv[j] * (sig + silu * (1.f - sig));
+    }
+    store8(dg + i * 8, og);
+    store8(du + i * 8, ou);
+  }
+}
+
+// ------------------------------------------------------------------ optimizers on flat buffers
+// AdamW with fp32 master weights and moments; gradient bf16 or fp32.  `gscale` (device
+// scalar, may be null) multiplies the gradient (clip coefficient); `skip` (device int,
+// may be null) suppresses the whole update when non-zero (non-finite gradient norm).
+template <typename GT>
+__global__ void adamw_kernel(float* __restrict__ p32, bf16* __restrict__ p16, float* __restrict__ m,
+                             float* __restrict__ v, const GT* __restrict__ g, long n, float lr, float beta1,
+                             float beta2, float eps, float wd, float bc1, float bc2, const float* gscale,
+                             const int* skip) {
+  if (skip != nullptr && *skip) return;
+  const float gs = gscale != nullptr ? *gscale : 1.f;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const float gi = static_cast<float>(g[i]) * gs;
+    float pi = p32[i];
+    const float mi = beta1 * m[i] + (1.f - beta1) * gi;
+    const float vi = beta2 * v[i] + (1.f - beta2) * gi * gi;
+    m[i] = mi;
+    v[i] = vi;
+    pi *= (1.f - lr * wd);
+    pi -= lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
+    p32[i] = pi;
+    if (p16 != nullptr) p16[i] = __float2bfloat16(pi);
+  }
+}
+
+// Muon step 1: momentum and the Newton-Schulz input.
+//   mom = beta*mom + (1-beta)*g ; u = nesterov ? g + beta*(mom - g) : mom ; out = bf16(u)
+// plus the sum of squares of u into sumsq[0] (one atomic per CTA) for the Frobenius norm.
+template <typename GT>
+__global__ void muon_momentum_kernel(float* __restrict__ mom, const GT* __restrict__ g, bf16* __restrict__ out,
+                                     float* __restrict__ sumsq, long n, float beta, int nesterov,
+                                     const float* gscale) {
+  __shared__ float red[32];
+  const float gs = gscale != nullptr ? *gscale : 1.f;
+  float acc = 0.f;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const float gi = static_cast<float>(g[i]) * gs;
+    const float mi = beta * mom[i] + (1.f - beta) * gi;
+    mom[i] = mi;
+    const float u = nesterov ? gi + beta * (mi - gi) : mi;
+    out[i] = __float2bfloat16(u);
+    acc += u * u;
+  }
+  acc = block_sum<256>(acc, red);
+  if (threadIdx.x == 0) atomicAdd(sumsq, acc);
+}
+// x *= 1 / (sqrt(sumsq) + eps)   (bf16 in place)
+__global__ void scale_by_norm_kernel(bf16* __restrict__ x, const float* __restrict__ sumsq, long n, float eps) {
+  const float s = 1.f / (sqrtf(*sumsq) + eps);
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long>(gridDim.x) * blockDim.x)
+    x[i] = __float2bfloat16(__bfloat162float(x[i]) * s);
+}
+// Muon step 3: p = p*(1 - lr*wd) - lr*scale*o ; bf16 copy refreshed.
+__global__ void muon_update_kernel(float* __restrict__ p32, bf16* __restrict__ p16, const bf16* __restrict__ o,
+                                   long n, float lr, float wd, float scale, const int* skip) {
+  if (skip != nullptr && *skip) return;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    float pi = p32[i] * (1.f - lr * wd) - lr * scale * __bfloat162float(o[i]);
+    p32[i] = pi;
+    if (p16 != nullptr) p16[i] = __float2bfloat16(pi);
+  }
+}
+
+// ema = decay*ema + (1-decay)*p
+template <typename PT>
+__global__ void ema_kernel(float* __restrict__ ema, const PT* __restrict__ p, long n, float decay) {
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long>(gridDim.x) * blockDim.x)
+    ema[i] = decay * ema[i] + (1.f - decay) * static_cast<float>(p[i]);
+}
+
+// Deterministic two-stage sum of squares: part[blockIdx.x] then a single-CTA finish.
+template <typename GT>
+__global__ void sumsq_part_kernel(const GT* __restrict__ g, float* __restrict__ part, long n) {
+  __shared__ float red[32];
+  float acc = 0.f;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const float gi = static_cast<float>(g[i]);
+    acc += gi * gi;
+  }
+  acc = block_sum<256>(acc, red);
+  if (threadIdx.x == 0) part[blockIdx.x] = acc;
+}
+// out[0] (+)= sum(part)
+__global__ void sumsq_finish_kernel(const float* __restrict__ part, float* __restrict__ out, int parts,
+                                    int accumulate) {
+  __shared__ float red[32];
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < parts; i += blockDim.x) acc += part[i];
+  acc = block_sum<256>(acc, red);
+  if (threadIdx.x == 0) out[0] = accumulate ? out[0] + acc : acc;
+}
+// From the global sum of squares: norm, clip coefficient min(1, max_norm/(norm+1e-6)),
+// and a skip flag when the norm is not finite.  No host round trip.
+__global__ void clip_coef_kernel(const float* __restrict__ sumsq, float* __restrict__ norm_out,
+                                 float* __restrict__ coef_out, int* __restrict__ skip_out, float max_norm) {
+  const float norm = sqrtf(*sumsq);
+  *norm_out = norm;
+  const bool finite = isfinite(norm);
+  *skip_out = finite ? 0 : 1;
+  float c = 1.f;
+  if (max_norm > 0.f && finite) c = fminf(1.f, max_norm / (norm + 1e-6f));
+  *coef_out = c;
+}
+template <typename GT>
+__global__ void scale_kernel(GT* __restrict__ g, long n, const float* __restrict__ coef) {
+  const float c = *coef;
+  if (c == 1.f) return;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long>(gridDim.x) * blockDim.x)
+    g[i] = static_cast<GT>(static_cast<float>(g[i]) * c);
+}
+
+// ------------------------------------------------------------------ packed-sequence index kernels
+// out[i, :] = src[idx[i], :]  (idx < 0 writes zeros) and the scatter inverse (optionally adding).
+__global__ void gather_rows_kernel(const bf16* __restrict__ src, const int64_t* __restrict__ idx,
+                                   bf16* __restrict__ out, long n_out, int H) {
+  const int vec = H / 8;
+  const long total = n_out * vec;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long r = i / vec;
+    const int c = (i - r * vec) * 8;
+    const int64_t s = idx[r];
+    bf16x8 v;
+    v.w[0] = v.w[1] = v.w[2] = v.w[3] = 0u;
+    if (s >= 0) v = *reinterpret_cast<const bf16x8*>(src + s * H + c);
+    *reinterpret_cast<bf16x8*>(out + r * H + c) = v;
+  }
+}
+__global__ void scatter_rows_kernel(const bf16* __restrict__ src, const int64_t* __restrict__ idx,
+                                    bf16* __restrict__ out, long n_src, int H, int add) {
+  const int vec = H / 8;
+  const long total = n_src * vec;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long r = i / vec;
+    const int c = (i - r * vec) * 8;
+    const int64_t d = idx[r];
+    if (d < 0) continue;
+    float v[8];
+    load8(src + r * H + c, v);
+    if (add) {
+      float o[8];
+      load8(out + d * H + c, o);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] += o[j];
+    }
+    store8(out + d * H + c, v);
+  }
+}
+
+// ------------------------------------------------------------------ cross-entropy passes
+// After the logits GEMM with the statistics epilogue: combine the per-tile partials into
+// lse, pick the target logit, emit per-row loss (0 for ignored rows).
+__global__ void ce_finalize_kernel(const float2* __restrict__ stats, const bf16* __restrict__ logits,
+                                   const int64_t* __restrict__ labels, float* __restrict__ lse_out,
+                                   float* __restrict__ loss_out, int rows, int n_tiles, long ld, int V,
+                                   int ignore_index) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  for (int row = blockIdx.x * wpb + (threadIdx.x >> 5); row < rows; row += gridDim.x * wpb) {
+    float mx = -INFINITY;
+    for (int i = lane; i < n_tiles; i += 32) mx = fmaxf(mx, stats[static_cast<size_t>(row) * n_tiles + i].x);
+    mx = warp_max(mx);
+    float s = 0.f;
+    for (int i = lane; i < n_tiles; i += 32) {
+      const float2 st = stats[static_cast<size_t>(row) * n_tiles + i];
+      if (st.x > -INFINITY) s += st.y * __expf(st.x - mx);
+    }
+    s = warp_sum(s);
+    if (lane == 0) {
+      const float lse = mx + logf(s);
+      lse_out[row] = lse;
+      const int64_t y = labels[row];
+      float l = 0.f;
+      if (y != ignore_index && y >= 0 && y < V) l = lse - __bfloat162float(logits[static_cast<size_t>(row) * ld + y]);
+      loss_out[row] = l;
+    }
+  }
+}
+// In place: logits[r, c] <- gscale[0]*row_w * (exp(logits - lse) - [c == label]); ignored rows -> 0.
+__global__ void ce_dlogits_kernel(bf16* __restrict__ logits, const float* __restrict__ lse,
+                                  const int64_t* __restrict__ labels, const float* __restrict__ gscale, int rows,
+                                  long ld, int V, int ignore_index) {
+  const int vec = V / 8;
+  const float gs = *gscale;
+  for (int row = blockIdx.y; row < rows; row += gridDim.y) {
+    const int64_t y = labels[row];
+    const bool ign = (y == ignore_index);
+    const float l = lse[row];
+    bf16* base = logits + static_cast<size_t>(row) * ld;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < vec; i += gridDim.x * blockDim.x) {
+      float v[8];
+      if (ign) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = 0.f;
+      } else {
+        load8(base + i * 8, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float pr = __expf(v[j] - l);
+          if (i * 8 + j == y) pr -= 1.f;
+          v[j] = pr * gs;
+        }
+      }
+      store8(base + i * 8, v);
+    }
+  }
+}
+
+static int g_sms = 0;
+static int num_sms() {
+  if (g_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return g_sms;
+}
+static int grid_for(long work_items, int threads, int per_sm = 8) {
+  long blocks = (work_items + threads - 1) / threads;
+  long cap = static_cast<long>(num_sms()) * per_sm;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return static_cast<int>(blocks);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+#define CHECK_LAUNCH() (cudaGetLastError() == cudaSuccess ? 0 : -4)
+
+extern "C" {
+
+int b200_num_partials() { return num_sms() * 2; }
+
+// rows x H bf16.  ln = 0: RMSNorm, 1: LayerNorm (b may be null).  res/res_out may be null.
+int b200_norm_fwd(const void* x, const void* res, const void* w, const void* b, void* y, void* res_out, void* rstd,
+                  void* mean, int rows, int H, float eps, float w_offset, int ln, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (H % 8) return -10;
+  if (H <= 512 && !ln && res == nullptr) {
+    int blocks = grid_for(static_cast<long>(rows) * 32, 256, 8);
+    norm_fwd_warp_kernel<<<blocks, 256, 0, st>>>((const bf16*)x, (const bf16*)w, (bf16*)y, (float*)rstd, rows, H, eps,
+                                                 w_offset);
+    return CHECK_LAUNCH();
+  }
+  int blocks = rows < num_sms() * 8 ? rows : num_sms() * 8;
+#define NORM_FWD(T, V)                                                                                              \
+  norm_fwd_kernel<T, V><<<blocks, T, 0, st>>>((const bf16*)x, (const bf16*)res, (const bf16*)w, (const bf16*)b,     \
+                                              (bf16*)y, (bf16*)res_out, (float*)rstd, (float*)mean, rows, H, eps, \
+                                              w_offset, ln)
+  if (H <= 1024) NORM_FWD(128, 1);
+  else if (H <= 2048) NORM_FWD(256, 1);
+  else if (H <= 4096) NORM_FWD(256, 2);
+  else if (H <= 8192) NORM_FWD(512, 2);
+  else if (H <= 16384) NORM_FWD(512, 4);
+  else return -11;
+#undef NORM_FWD
+  return CHECK_LAUNCH();
+}
+
+// dw_part / db_part: fp32 [b200_num_partials(), H] scratch.  dw/db fp32 [H] (accumulate flag).
+int b200_norm_bwd(const void* dy, const void* x, const void* w, const void* rstd, const void* mean,
+                  const void* dres_in, void* dx, void* dw_part, void* db_part, void* dw, void* db, int rows, int H,
+                  float w_offset, int ln, int accumulate, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (H % 8) return -10;
+  int parts;
+  if (H <= 512 && !ln && dres_in == nullptr) {
+    int blocks = num_sms() * 2 / 8;
+    if (blocks < 1) blocks = 1;
+    parts = blocks * 8;
+    norm_bwd_warp_kernel<<<blocks, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)rstd,
+                                                 (bf16*)dx, (float*)dw_part, rows, H, w_offset);
+  } else {
+    parts = num_sms() * 2;
+    if (parts > rows) parts = rows;
+#define NORM_BWD(T, V)                                                                                            \
+  norm_bwd_kernel<T, V><<<parts, T, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)rstd, \
+                                             (const float*)mean, (const bf16*)dres_in, (bf16*)dx, (float*)dw_part, \
+                                             (float*)db_part, rows, H, w_offset, ln)
+    if (H <= 1024) NORM_BWD(128, 1);
+    else if (H <= 2048) NORM_BWD(256, 1);
+    else if (H <= 4096) NORM_BWD(256, 2);
+    else if (H <= 8192) NORM_BWD(512, 2);
+    else if (H <= 16384) NORM_BWD(512, 4);
+    else return -11;
+#undef NORM_BWD
+  }
+  if (cudaGetLastError() != cudaSuccess) return -4;
+  colsum_kernel<<<(H + 255) / 256, 256, 0, st>>>((const float*)dw_part, (float*)dw, parts, H, accumulate);
+  if (db != nullptr && db_part != nullptr)
+    colsum_kernel<<<(H + 255) / 256, 256, 0, st>>>((const float*)db_part, (float*)db, parts, H, accumulate);
+  return CHECK_LAUNCH();
+}
+
+int b200_rope_table(const void* pos, const void* inv_freq, void* cos_out, void* sin_out, int T, int half, int mode,
+                    int s0, int s1, int s2, float scaling, cudaStream_t st) {
+  long n = static_cast<long>(T) * half;
+  if (n <= 0) return 0;
+  rope_table_kernel<<<(n + 255) / 256, 256, 0, st>>>((const int64_t*)pos, (const float*)inv_freq, (float*)cos_out,
+                                                     (float*)sin_out, T, half, mode, s0, s1, s2, scaling);
+  return CHECK_LAUNCH();
+}
+
+int b200_rope_apply(const void* x, void* y, const void* cosb, const void* sinb, int T, int Hn, int D, int rot_dim,
+                    long ldx, long ldy, int conj, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (rot_dim % 16 || D % 8 || ldx % 8 || ldy % 8) return -10;
+  long total = static_cast<long>(T) * Hn * (rot_dim / 16);
+  rope_apply_kernel<<<grid_for(total, 256), 256, 0, st>>>((const bf16*)x, (bf16*)y, (const float*)cosb,
+                                                          (const float*)sinb, T, Hn, D, rot_dim, ldx, ldy, conj);
+  return CHECK_LAUNCH();
+}
+
+int b200_swiglu_fwd(const void* g, const void* u, void* h, long n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (n % 8) return -10;
+  swiglu_fwd_kernel<<<grid_for(n / 8, 256), 256, 0, st>>>((const bf16*)g, (const bf16*)u, (bf16*)h, n / 8);
+  return CHECK_LAUNCH();
+}
+int b200_swiglu_bwd(const void* dh, const void* g, const void* u, void* dg, void* du, long n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (n % 8) return -10;
+  swiglu_bwd_kernel<<<grid_for(n / 8, 256), 256, 0, st>>>((const bf16*)dh, (const bf16*)g, (const bf16*)u, (bf16*)dg,
+                                                          (bf16*)du, n / 8);
+  return CHECK_LAUNCH();
+}
+
+int b200_adamw(void* p32, void* p16, void* m, void* v, const void* g, int g_is_fp32, long n, float lr, float beta1,
+               float beta2, float eps, float wd, float bc1, float bc2, const void* gscale, const void* skip,
+               cudaStream_t st) {
+  if (n <= 0) return 0;
+  int blocks = grid_for(n, 256);
+  if (g_is_fp32)
+    adamw_kernel<float><<<blocks, 256, 0, st>>>((float*)p32, (bf16*)p16, (float*)m, (float*)v, (const float*)g, n, lr,
+                                                beta1, beta2, eps, wd, bc1, bc2, (const float*)gscale,
+                                                (const int*)skip);
+  else
+    adamw_kernel<bf16><<<blocks, 256, 0, st>>>((float*)p32, (bf16*)p16, (float*)m, (float*)v, (const bf16*)g, n, lr,
+                                               beta1, beta2, eps, wd, bc1, bc2, (const float*)gscale, (const int*)skip);
+  return CHECK_LAUNCH();
+}
+
+int b200_muon_momentum(void* mom, const void* g, int g_is_fp32, void* out, void* sumsq, long n, float beta,
+                       int nesterov, const void* gscale, float eps, cudaStream_t st) {
+  if (n <= 0) return 0;
+  cudaMemsetAsync(sumsq, 0, sizeof(float), st);
+  int blocks = grid_for(n, 256, 4);
+  if (g_is_fp32)
+    muon_momentum_kernel<float><<<blocks, 256, 0, st>>>((float*)mom, (const float*)g, (bf16*)out, (float*)sumsq, n,
+                                                        beta, nesterov, (const float*)gscale);
+  else
+    muon_momentum_kernel<bf16><<<blocks, 256, 0, st>>>((float*)mom, (const bf16*)g, (bf16*)out, (float*)sumsq, n, beta,
+                                                       nesterov, (const float*)gscale);
+  scale_by_norm_kernel<<<blocks, 256, 0, st>>>((bf16*)out, (const float*)sumsq, n, eps);
+  return CHECK_LAUNCH();
+}
+
+int b200_muon_update(void* p32, void* p16, const void* o, long n, float lr, float wd, float scale, const void* skip,
+                     cudaStream_t st) {
+  if (n <= 0) return 0;
+  muon_update_kernel<<<grid_for(n, 256), 256, 0, st>>>((float*)p32, (bf16*)p16, (const bf16*)o, n, lr, wd, scale,
+                                                       (const int*)skip);
+  return CHECK_LAUNCH();
+}
+
+int b200_ema(void* ema, const void* p, int p_is_fp32, long n, float decay, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (p_is_fp32) ema_kernel<float><<<grid_for(n, 256), 256, 0, st>>>((float*)ema, (const float*)p, n, decay);
+  else ema_kernel<bf16><<<grid_for(n, 256), 256, 0, st>>>((float*)ema, (const bf16*)p, n, decay);
+  return CHECK_LAUNCH();
+}
+
+// part: fp32 scratch of b200_num_partials() floats.  out[0] (+)= sum g^2.
+int b200_sumsq(const void* g, int g_is_fp32, long n, void* part, void* out, int accumulate, cudaStream_t st) {
+  int blocks = grid_for(n > 0 ? n : 1, 256, 2);
+  if (g_is_fp32) sumsq_part_kernel<float><<<blocks, 256, 0, st>>>((const float*)g, (float*)part, n);
+  else sumsq_part_kernel<bf16><<<blocks, 256, 0, st>>>((const bf16*)g, (float*)part, n);
+  sumsq_finish_kernel<<<1, 256, 0, st>>>((const float*)part, (float*)out, blocks, accumulate);
+  return CHECK_LAUNCH();
+}
+int b200_clip_coef(const void* sumsq, void* norm_out, void* coef_out, void* skip_out, float max_norm,
+                   cudaStream_t st) {
+  clip_coef_kernel<<<1, 1, 0, st>>>((const float*)sumsq, (float*)norm_out, (float*)coef_out, (int*)skip_out,
+                                    max_norm);
+  return CHECK_LAUNCH();
+}
+int b200_scale(void* g, int g_is_fp32, long n, const void* coef, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (g_is_fp32) scale_kernel<float><<<grid_for(n, 256), 256, 0, st>>>((float*)g, n, (const float*)coef);
+  else scale_kernel<bf16><<<grid_for(n, 256), 256, 0, st>>>((bf16*)g, n, (const float*)coef);
+  return CHECK_LAUNCH();
+}
+
+int b200_gather_rows(const void* src, const void* idx, void* out, long n_out, int H, cudaStream_t st) {
+  if (n_out <= 0) return 0;
+  if (H % 8) return -10;
+  gather_rows_kernel<<<grid_for(n_out * (H / 8), 256), 256, 0, st>>>((const bf16*)src, (const int64_t*)idx, (bf16*)out,
+                                                                     n_out, H);
+  return CHECK_LAUNCH();
+}
+int b200_scatter_rows(const void* src, const void* idx, void* out, long n_src, int H, int add, cudaStream_t st) {
+  if (n_src <= 0) return 0;
+  if (H % 8) return -10;
+  scatter_rows_kernel<<<grid_for(n_src * (H / 8), 256), 256, 0, st>>>((const bf16*)src, (const int64_t*)idx,
+                                                                      (bf16*)out, n_src, H, add);
+  return CHECK_LAUNCH();
+}
+
+int b200_ce_finalize(const void* stats, const void* logits, const void* labels, void* lse, void* loss, int rows,
+                     int n_tiles, long ld, int V, int ignore_index, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  ce_finalize_kernel<<<grid_for(static_cast<long>(rows) * 32, 256), 256, 0, st>>>(
+      (const float2*)stats, (const bf16*)logits, (const int64_t*)labels, (float*)lse, (float*)loss, rows, n_tiles, ld,
+      V, ignore_index);
+  return CHECK_LAUNCH();
+}
+int b200_ce_dlogits(void* logits, const void* lse, const void* labels, const void* gscale, int rows, long ld, int V,
+                    int ignore_index, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (V % 8) return -10;
+  int bx = (V / 8 + 255) / 256;
+  if (bx > 16) bx = 16;
+  int by = rows < 65535 ? rows : 65535;
+  ce_dlogits_kernel<<<dim3(bx, by), 256, 0, st>>>((bf16*)logits, (const float*)lse, (const int64_t*)labels,
+                                                  (const float*)gscale, rows, ld, V, ignore_index);
+  return CHECK_LAUNCH();
+}
+
+}  // extern "C"

@@ -1,0 +1,109 @@
+"""Per-kernel timings against the library baselines and the measured roofline.
+
+``python -m lmms_engine_b200.ops.microbench [--json OUT]`` times each native kernel at
+the shapes of the Qwen2.5-7B training step with CUDA events (3 warm-ups, L2 flushed
+between iterations) and prints achieved TFLOP/s or GB/s next to cuBLAS / torch.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+
+def _flush_l2(buf):
+    buf.zero_()
+
+
+def timeit(fn, iters=10, warmup=3, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush is not None:
+            _flush_l2(flush)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--json", default=None)
+    ap.add_argument("--quick", action="store_true")
+    args = ap.parse_args()
+    from . import gemm, _cuda
+
+    dev = torch.device("cuda")
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    rows = []
+
+    def rnd(*s):
+        return torch.randn(*s, device=dev, dtype=torch.bfloat16) * 0.05
+
+    T = 16384
+    shapes = [
+        ("qkv_fwd nt", T, 4608, 3584, "nt"),
+        ("gate_up_fwd nt", T, 18944, 3584, "nt"),
+        ("down_fwd nt", T, 3584, 18944, "nt"),
+        ("down_dx nn", T, 18944, 3584, "nn"),
+        ("gate_dw tn", 18944, 3584, T, "tn"),
+        ("lm_head nt", 8192, 152064, 3584, "nt"),
+    ]
+    if args.quick:
+        shapes = shapes[:2]
+    for name, M, N, K, kind in shapes:
+        if kind == "nt":
+            a, b = rnd(M, K), rnd(N, K)
+            mine = lambda: gemm.gemm(a, b)
+            lib = lambda: torch.matmul(a, b.t())
+        elif kind == "nn":
+            a, b = rnd(M, K), rnd(K, N)
+            mine = lambda: gemm.gemm(a, b, b_mn_major=True)
+            lib = lambda: torch.matmul(a, b)
+        else:
+            a, b = rnd(K, M), rnd(K, N)
+            mine = lambda: gemm.gemm(a, b, a_mn_major=True, b_mn_major=True)
+            lib = lambda: torch.matmul(a.t(), b)
+        t1 = timeit(mine, flush=flush)
+        t2 = timeit(lib, flush=flush)
+        fl = 2.0 * M * N * K
+        rows.append({"op": name, "M": M, "N": N, "K": K, "ms": t1, "tflops": fl / t1 / 1e9, "lib_ms": t2,
+                     "lib_tflops": fl / t2 / 1e9})
+        print(rows[-1], flush=True)
+        del a, b
+    # fused SwiGLU GEMM vs cuBLAS x2 + elementwise
+    x, wg, wu = rnd(T, 3584), rnd(18944, 3584), rnd(18944, 3584)
+    t1 = timeit(lambda: gemm.gemm_swiglu(x, wg, wu, True), flush=flush)
+    def lib_sw():
+        g = torch.matmul(x, wg.t()); u = torch.matmul(x, wu.t())
+        return torch.nn.functional.silu(g) * u
+    t2 = timeit(lib_sw, flush=flush)
+    fl = 4.0 * T * 18944 * 3584
+    rows.append({"op": "gate_up_swiglu fused", "ms": t1, "tflops": fl / t1 / 1e9, "lib_ms": t2, "lib_tflops": fl / t2 / 1e9})
+    print(rows[-1], flush=True)
+    # symmetric X X^T (Muon)
+    for M, K in ((3584, 18944), (3584, 3584)):
+        xx = rnd(M, K)
+        t1 = timeit(lambda: gemm.gemm(xx, xx, symmetric=True), flush=flush)
+        t2 = timeit(lambda: torch.matmul(xx, xx.t()), flush=flush)
+        fl = 2.0 * M * M * K
+        rows.append({"op": f"xxt symm {M}x{K}", "ms": t1, "tflops_full_equiv": fl / t1 / 1e9, "lib_ms": t2, "lib_tflops": fl / t2 / 1e9})
+        print(rows[-1], flush=True)
+    _cuda.check_status()
+    if args.json:
+        os.makedirs(os.path.dirname(args.json) or ".", exist_ok=True)
+        with open(args.json, "w") as f:
+            json.dump(rows, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()
