@@ -425,9 +425,18 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// The driver entry points used below need the primary context to be current on the calling
+// thread.  Autograd runs backward on its own threads, where no runtime call may have bound
+// it yet; cudaSetDevice on the current device does.
+static void bind_context() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaSetDevice(dev);
+}
+
 // 2-D bf16 tensor map over a row-major [rows, cols] matrix with row stride `ld` elements.
 static int make_map(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
                     uint32_t box_rows, bool swizzle128) {
+  bind_context();
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return -1;
   cuuint64_t dims[2] = {cols, rows};
@@ -437,7 +446,14 @@ static int make_map(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t col
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -2;
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr,
+            "[b200 gemm] cuTensorMapEncodeTiled failed (%d): ptr=%p rows=%llu cols=%llu ld=%llu box=(%u,%u) swizzle=%d\n",
+            static_cast<int>(r), ptr, static_cast<unsigned long long>(rows), static_cast<unsigned long long>(cols),
+            static_cast<unsigned long long>(ld), box_cols, box_rows, static_cast<int>(swizzle128));
+    return -2;
+  }
+  return 0;
 }
 
 static int g_num_sms = 0;

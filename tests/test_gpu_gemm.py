@@ -28,7 +28,7 @@ def test_gemm_nt(M, N, K):
     _cuda.check_status()
 
 
-@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("M,N,K", SHAPES[:-1] + [(80, 40, 24)])
 def test_gemm_nn_b_mn_major(M, N, K):
     from lmms_engine_b200.ops import gemm, _cuda
 
@@ -38,7 +38,7 @@ def test_gemm_nn_b_mn_major(M, N, K):
     _cuda.check_status()
 
 
-@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("M,N,K", SHAPES[:-1] + [(80, 40, 24)])
 def test_gemm_tn_both_mn_major(M, N, K):
     from lmms_engine_b200.ops import gemm, _cuda
 
