@@ -1,0 +1,125 @@
+"""Synthetic packed-token datasets (no files, no tokenizer): documents with lengths uniform
+in ``[min_len, max_len]`` and token ids uniform in ``[0, vocab)``, packed online into rows of
+``packing_length`` tokens.  Used by the plumbing tests and by ``bench.py``; the reference's
+tests download a real dataset instead (cicd/run_traincicd.sh:51-62)."""
+from __future__ import annotations
+
+from typing import Any, Dict, Iterator, List, Optional
+
+import numpy as np
+import torch
+from torch.utils.data import IterableDataset
+
+from ..mapping_func import register_dataset
+from .collator.packed_collator import PackedCollator
+from .packing import build_online_packer
+
+
+@register_dataset("synthetic_packed")
+class SyntheticPackedDataset(IterableDataset):
+    """Yields packs: ``List[{"input_ids": LongTensor, "labels": LongTensor}]``.
+
+    ``extra_kwargs`` of the dataset config: ``vocab_size`` (4096), ``min_len`` (32),
+    ``max_len`` (512), ``num_documents`` (per rank, default unlimited), ``fill_exact``
+    (truncate the last document of a pack so that every pack has exactly
+    ``packing_length`` tokens).
+    """
+
+    def __init__(self, config):
+        self.config = config
+        kw = dict(config.extra_kwargs or {})
+        self.vocab = int(kw.get("vocab_size", 4096))
+        self.min_len = int(kw.get("min_len", 32))
+        self.max_len = int(kw.get("max_len", 512))
+        self.num_documents = kw.get("num_documents")
+        self.fill_exact = bool(kw.get("fill_exact", False))
+        self.pattern = kw.get("pattern", "uniform")  # "uniform" | "periodic" (learnable)
+        self.interleave_ranks = int(kw.get("interleave_ranks", 0) or 0)
+        self.packing_length = int(config.packing_length or 1024)
+        self.strategy = config.packing_strategy or "first_fit"
+        self.packing_kwargs = dict(kw.get("packing_kwargs", {}) or {})
+        self.seed = int(config.data_seed or 0)
+        self.dp_rank, self.dp_size = 0, 1
+        self.cur_idx = 0  # documents consumed (resume point)
+        self.processor = None
+
+    # -- reference dataset API -----------------------------------------------------------
+    def build(self):
+        try:
+            from ..parallel import process_group_manager as pgm
+
+            m = pgm.process_group_manager
+            if m is not None:
+                self.dp_rank, self.dp_size = m.dp_rank, m.dp_size
+        except Exception:
+            pass
+        return self
+
+    def get_collator(self):
+        return PackedCollator()
+
+    def state_dict(self) -> Dict[str, Any]:
+        return {"cur_idx": self.cur_idx}
+
+    def load_state_dict(self, sd: Dict[str, Any]) -> None:
+        self.cur_idx = int(sd.get("cur_idx", 0))
+
+    def _document(self, idx: int) -> Dict[str, torch.Tensor]:
+        # every document is a pure function of (seed, rank, index): resumable and reproducible
+        rng = np.random.default_rng([self.seed, self.dp_rank, idx])
+        n = int(rng.integers(self.min_len, self.max_len + 1))
+        if self.pattern == "periodic":
+            # a short random motif repeated: learnable, so tests can watch the loss fall
+            period = int(rng.integers(2, 6))
+            motif = rng.integers(0, min(self.vocab, 64), size=period, dtype=np.int64)
+            ids = torch.from_numpy(np.resize(motif, n))
+        else:
+            ids = torch.from_numpy(rng.integers(0, self.vocab, size=n, dtype=np.int64))
+        return {"input_ids": ids, "labels": ids.clone()}
+
+    def __iter__(self) -> Iterator[List[Dict[str, torch.Tensor]]]:
+        if self.interleave_ranks > 1:
+            # one process replaying the streams of several data-parallel ranks in turn
+            subs = []
+            for r in range(self.interleave_ranks):
+                d = SyntheticPackedDataset(self.config)
+                d.interleave_ranks = 0
+                d.dp_rank = r
+                subs.append(iter(d))
+            while True:
+                for it in subs:
+                    yield next(it)
+        packer = None if self.fill_exact else build_online_packer(self.strategy, self.packing_length, **self.packing_kwargs)
+        idx = self.cur_idx
+        buf: List[Dict[str, torch.Tensor]] = []
+        used = 0
+        while self.num_documents is None or idx < int(self.num_documents):
+            doc = self._document(idx)
+            idx += 1
+            n = doc["input_ids"].numel()
+            if self.fill_exact:
+                room = self.packing_length - used
+                if n >= room:
+                    buf.append({k: v[:room] for k, v in doc.items()})
+                    self.cur_idx = idx
+                    yield buf
+                    buf, used = [], 0
+                else:
+                    buf.append(doc)
+                    used += n
+                continue
+            if n > self.packing_length:
+                self.cur_idx = idx
+                yield [{k: v[: self.packing_length] for k, v in doc.items()}]
+                continue
+            for pack in packer.add(doc, n):
+                # next-fit emits the open pack because THIS document did not fit, so the
+                # stream resumes exactly at this document; multi-bucket packers are approximate
+                self.cur_idx = idx - 1 if self.strategy == "first_fit" else idx
+                yield pack
+        if packer is not None:
+            for pack in packer.flush():
+                self.cur_idx = idx
+                yield pack
+        elif buf:
+            yield buf

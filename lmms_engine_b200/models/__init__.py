@@ -1,0 +1,9 @@
+"""Native model families and their registration."""
+from ..mapping_func import register_model
+from .config import ModelConfig
+from .decoder_lm import DecoderConfig, DecoderLM
+
+for _mt in ("qwen2", "qwen2_5", "qwen3", "llama"):
+    register_model(_mt, DecoderConfig, DecoderLM, "causal_lm")
+
+__all__ = ["ModelConfig", "DecoderConfig", "DecoderLM"]

@@ -1,0 +1,330 @@
+"""Owner-sharded data parallelism: the engine's native ZeRO runtime for B200.
+
+A B200 has 180 GB of HBM, so for models up to a few tens of billions of parameters the
+bf16 working copy of the weights fits on every GPU.  This runtime therefore keeps the bf16
+parameters REPLICATED (no all-gather before forward, no re-gather in backward, nothing
+on the critical path of the step) and shards what is actually large: fp32 master weights,
+optimizer moments and the optimizer's compute.  One step is
+
+    forward/backward      gradients accumulate in a flat bf16 buffer, no communication
+    reduce-to-owner       every rank receives the mean gradient of the ranges it owns
+    norm / clip           sum of squares over owned ranges, one scalar all-reduce
+    owner update          AdamW on an even slice of the elementwise region; Muon on WHOLE
+                          matrices, spread over ranks by Newton-Schulz cost (LPT)
+    publish               owners write the new bf16 values into every replica
+
+Whole-matrix ownership is what Muon needs (Newton-Schulz works on full matrices): the
+reference gathers FSDP shards to ``index % world`` owners and scatters them back with
+NCCL gather/scatter per parameter (src/lmms_engine/utils/muon_utils.py:206-275); here the
+ownership is the sharding itself.  The collective steps go through a ``Comm`` object: the
+default uses torch.distributed (NCCL or gloo); on NVLink systems the peer-memory
+implementation in ``parallel/peer_comm.py`` fuses reduce+momentum and update+publish into
+single kernels that read and write peer memory directly.
+
+For models too large to replicate, the trainer falls back to stock FSDP2
+(``sharding_runtime: torch_fsdp2``), as the reference does everywhere
+(src/lmms_engine/utils/fsdp2_utils.py:24-111).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..ops import muon as muon_ops
+from ..ops import optim as optim_ops
+
+ALIGN = 64  # elements; keeps every parameter 128-byte aligned for TMA and vector access
+
+
+def _round_up(x: int, a: int) -> int:
+    return (x + a - 1) // a * a
+
+
+@dataclass
+class Segment:
+    name: str
+    shape: Tuple[int, ...]
+    numel: int
+    kind: str  # "muon" | "adam"
+    decay: bool
+    owner: int  # muon: owning rank; adam: -1 (evenly sliced)
+    offset: int = 0  # into the flat buffers
+
+
+def lpt_assign(costs: Sequence[float], n: int) -> List[int]:
+    """Longest-processing-time assignment: heaviest item first onto the least loaded rank."""
+    order = sorted(range(len(costs)), key=lambda i: (-costs[i], i))
+    load = [0.0] * n
+    owner = [0] * len(costs)
+    for i in order:
+        r = min(range(n), key=lambda k: (load[k], k))
+        owner[i] = r
+        load[r] += costs[i]
+    return owner
+
+
+class TorchComm:
+    """Collective steps of the runtime on torch.distributed (NCCL / gloo)."""
+
+    def __init__(self, group):
+        self.group = group
+        self.n = dist.get_world_size(group) if group is not None else 1
+        self.rank = dist.get_rank(group) if group is not None else 0
+
+    def global_rank(self, r: int) -> int:
+        return dist.get_global_rank(self.group, r) if self.group is not None else r
+
+    def allocate(self, numel: int, dtype, device) -> torch.Tensor:
+        return torch.zeros(numel, dtype=dtype, device=device)
+
+    def reduce_to_owner(self, grad_flat: torch.Tensor, ranges: List[List[Tuple[int, int]]]) -> None:
+        """Sum ``grad_flat[lo:hi]`` of all ranks into rank r for every (lo, hi) in ranges[r]."""
+        if self.n == 1:
+            return
+        works = []
+        for r in range(self.n):
+            for lo, hi in ranges[r]:
+                if hi > lo:
+                    works.append(dist.reduce(grad_flat[lo:hi], dst=self.global_rank(r), group=self.group, async_op=True))
+        for w in works:
+            w.wait()
+
+    def publish(self, param_flat: torch.Tensor, ranges: List[List[Tuple[int, int]]]) -> None:
+        if self.n == 1:
+            return
+        works = []
+        for r in range(self.n):
+            for lo, hi in ranges[r]:
+                if hi > lo:
+                    works.append(dist.broadcast(param_flat[lo:hi], src=self.global_rank(r), group=self.group, async_op=True))
+        for w in works:
+            w.wait()
+
+    def all_reduce_sum(self, t: torch.Tensor) -> None:
+        if self.n > 1:
+            dist.all_reduce(t, group=self.group)
+
+    def barrier(self) -> None:
+        if self.n > 1:
+            dist.barrier(group=self.group)
+
+
+class OwnerShardedRuntime:
+    """Flat replicated parameters + owner-sharded optimizer (AdamW and Muon)."""
+
+    def __init__(
+        self,
+        model: torch.nn.Module,
+        group=None,
+        *,
+        lr: float,
+        weight_decay: float = 0.0,
+        betas: Tuple[float, float] = (0.9, 0.999),
+        eps: float = 1e-8,
+        max_grad_norm: float = 1.0,
+        use_muon: bool = False,
+        muon_momentum: float = 0.95,
+        muon_nesterov: bool = True,
+        muon_ns_steps: int = 5,
+        muon_rms_scale: bool = True,
+        param_dtype: torch.dtype = torch.bfloat16,
+        grad_dtype: Optional[torch.dtype] = None,
+        device: Optional[torch.device] = None,
+        comm: Optional[Any] = None,
+        no_decay_patterns: Sequence[str] = ("bias", "norm"),
+    ):
+        self.model = model
+        self.comm = comm if comm is not None else TorchComm(group)
+        self.n, self.rank = self.comm.n, self.comm.rank
+        self.lr, self.weight_decay, self.betas, self.eps = lr, weight_decay, betas, eps
+        self.max_grad_norm = max_grad_norm
+        self.muon = dict(momentum=muon_momentum, nesterov=muon_nesterov, ns_steps=muon_ns_steps, rms_scale=muon_rms_scale)
+        self.param_dtype = param_dtype
+        self.grad_dtype = grad_dtype or param_dtype
+        self.step_count = 0
+        self._ns_work: Dict[Any, torch.Tensor] = {}
+
+        params: List[Tuple[str, torch.nn.Parameter]] = []
+        seen = set()
+        for name, p in model.named_parameters():
+            if id(p) in seen or not p.requires_grad:
+                continue
+            seen.add(id(p))
+            params.append((name, p))
+        self.device = device or params[0][1].device
+
+        muon_idx = [i for i, (nm, p) in enumerate(params) if use_muon and muon_ops.is_muon_param(nm, p)]
+        owners = lpt_assign([muon_ops.ns_flops(tuple(params[i][1].shape), muon_ns_steps) for i in muon_idx], self.n)
+        owner_of = dict(zip(muon_idx, owners))
+
+        # ---- flat layout: [rank0 matrices | rank1 matrices | ... | adam decay | adam no-decay]
+        segs: List[Segment] = []
+        self.muon_ranges: List[Tuple[int, int]] = []
+        off = 0
+        for r in range(self.n):
+            lo = off
+            for i in muon_idx:
+                if owner_of[i] != r:
+                    continue
+                nm, p = params[i]
+                segs.append(Segment(nm, tuple(p.shape), p.numel(), "muon", True, r, off))
+                off = _round_up(off + p.numel(), ALIGN)
+            self.muon_ranges.append((lo, off))
+        adam_lo = off
+        for want_decay in (True, False):
+            for i, (nm, p) in enumerate(params):
+                if i in owner_of:
+                    continue
+                decay = p.ndim >= 2 and not any(pat in nm for pat in no_decay_patterns)
+                if decay != want_decay:
+                    continue
+                segs.append(Segment(nm, tuple(p.shape), p.numel(), "adam", decay, -1, off))
+                off = _round_up(off + p.numel(), ALIGN)
+            if want_decay:
+                self.adam_decay_end = off
+        adam_hi = off
+        chunk = _round_up(max(1, math.ceil((adam_hi - adam_lo) / self.n)), ALIGN)
+        total = adam_lo + chunk * self.n
+        self.adam_ranges = [(adam_lo + r * chunk, adam_lo + (r + 1) * chunk) for r in range(self.n)]
+        self.total = total
+        self.segments = segs
+        self.by_name = {s.name: s for s in segs}
+
+        # ---- flat buffers and parameter views -------------------------------------------------
+        self.P = self.comm.allocate(total, param_dtype, self.device)
+        self.G = self.comm.allocate(total, self.grad_dtype, self.device)
+        name_to_param = dict(params)
+        with torch.no_grad():
+            for s in segs:
+                p = name_to_param[s.name]
+                view = self.P[s.offset : s.offset + s.numel].view(s.shape)
+                view.copy_(p.data)
+                p.data = view
+                p.grad = self.G[s.offset : s.offset + s.numel].view(s.shape)
+        self.params = name_to_param
+
+        # ---- owned state ------------------------------------------------------------------------
+        my_mu, my_ad = self.muon_ranges[self.rank], self.adam_ranges[self.rank]
+        self.own_ranges = [my_mu, my_ad]
+        f32 = dict(dtype=torch.float32, device=self.device)
+        self.needs_master = param_dtype != torch.float32
+        self.mu_master = self.P[my_mu[0] : my_mu[1]].float() if self.needs_master else self.P[my_mu[0] : my_mu[1]]
+        self.mu_mom = torch.zeros(my_mu[1] - my_mu[0], **f32)
+        self.ad_master = self.P[my_ad[0] : my_ad[1]].float() if self.needs_master else self.P[my_ad[0] : my_ad[1]]
+        self.ad_m = torch.zeros(my_ad[1] - my_ad[0], **f32)
+        self.ad_v = torch.zeros(my_ad[1] - my_ad[0], **f32)
+        self._sumsq = torch.zeros(1, **f32)
+        self._norm = torch.zeros(1, **f32)
+        self._coef = torch.ones(1, **f32)
+        self._skip = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._ns_in = None
+        self.my_matrices = [s for s in segs if s.kind == "muon" and s.owner == self.rank]
+
+    # ------------------------------------------------------------------------------------
+    @property
+    def all_ranges(self) -> List[List[Tuple[int, int]]]:
+        return [[self.muon_ranges[r], self.adam_ranges[r]] for r in range(self.n)]
+
+    def zero_grad(self) -> None:
+        self.G.zero_()
+
+    def rebind_grads(self) -> None:
+        """Point every ``p.grad`` at its slice of the flat buffer again (after an external ``zero_grad(set_to_none)``)."""
+        for s in self.segments:
+            self.params[s.name].grad = self.G[s.offset : s.offset + s.numel].view(s.shape)
+
+    @torch.no_grad()
+    def step(self, lr_factor: float = 1.0) -> torch.Tensor:
+        """Reduce, clip, update and publish.  Returns the global gradient norm (device scalar)."""
+        comm = self.comm
+        self.step_count += 1
+        comm.reduce_to_owner(self.G, self.all_ranges)
+        # gradient of the MEAN loss over ranks; folded into the clip coefficient below
+        inv_n = 1.0 / self.n
+        first = True
+        for lo, hi in self.own_ranges:
+            if hi > lo:
+                optim_ops.sumsq_(self.G[lo:hi], self._sumsq, accumulate=not first)
+                first = False
+        if first:
+            self._sumsq.zero_()
+        comm.all_reduce_sum(self._sumsq)
+        if inv_n != 1.0:
+            self._sumsq.mul_(inv_n * inv_n)
+        optim_ops.clip_coef(self._sumsq, self._norm, self._coef, self._skip, float(self.max_grad_norm or 0.0))
+        gscale = self._coef * inv_n if inv_n != 1.0 else self._coef
+        lr = self.lr * lr_factor
+        self._adam_update(lr, gscale)
+        self._muon_update(lr, gscale)
+        comm.publish(self.P, self.all_ranges)
+        self.G.zero_()
+        return self._norm
+
+    def _adam_update(self, lr: float, gscale: torch.Tensor) -> None:
+        lo, hi = self.adam_ranges[self.rank]
+        if hi <= lo:
+            return
+        split = min(max(self.adam_decay_end, lo), hi)
+        for a, b, wd in ((lo, split, self.weight_decay), (split, hi, 0.0)):
+            if b <= a:
+                continue
+            s = slice(a - lo, b - lo)
+            optim_ops.adamw_step(
+                self.ad_master[s], self.P[a:b] if self.needs_master else None, self.ad_m[s], self.ad_v[s], self.G[a:b],
+                lr=lr, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps, wd=wd, step=self.step_count,
+                gscale=gscale, skip=self._skip,
+            )
+
+    def _muon_update(self, lr: float, gscale: torch.Tensor) -> None:
+        lo, _ = self.muon_ranges[self.rank]
+        cfg = self.muon
+        for s in self.my_matrices:
+            a, b = s.offset, s.offset + s.numel
+            mom = self.mu_mom[a - lo : b - lo]
+            x = torch.empty(s.shape, dtype=torch.bfloat16 if self.P.is_cuda else torch.float32, device=self.device)
+            optim_ops.muon_momentum(mom, self.G[a:b], x.view(-1), self._sumsq, beta=cfg["momentum"],
+                                    nesterov=cfg["nesterov"], gscale=gscale)
+            o = muon_ops.newton_schulz(x, cfg["ns_steps"], self._ns_work)
+            optim_ops.muon_update(
+                self.mu_master[a - lo : b - lo], self.P[a:b] if self.needs_master else None, o.reshape(-1),
+                lr=lr, wd=self.weight_decay, scale=muon_ops.muon_scale(s.shape, cfg["rms_scale"]), skip=self._skip,
+            )
+
+    # ---- checkpoint ------------------------------------------------------------------------
+    def state_dict(self) -> Dict[str, Any]:
+        return {
+            "step": self.step_count,
+            "world_size": self.n,
+            "rank": self.rank,
+            "muon_range": self.muon_ranges[self.rank],
+            "adam_range": self.adam_ranges[self.rank],
+            "mu_master": self.mu_master.detach().cpu() if self.needs_master else None,
+            "mu_mom": self.mu_mom.cpu(),
+            "ad_master": self.ad_master.detach().cpu() if self.needs_master else None,
+            "ad_m": self.ad_m.cpu(),
+            "ad_v": self.ad_v.cpu(),
+            "segments": [(s.name, s.shape, s.kind, s.owner, s.offset) for s in self.segments],
+        }
+
+    def load_state_dict(self, sd: Dict[str, Any]) -> None:
+        if sd["world_size"] != self.n or sd["rank"] != self.rank:
+            raise ValueError("optimizer shard belongs to a different world size / rank")
+        self.step_count = int(sd["step"])
+        self.mu_mom.copy_(sd["mu_mom"])
+        self.ad_m.copy_(sd["ad_m"])
+        self.ad_v.copy_(sd["ad_v"])
+        if self.needs_master:
+            self.mu_master.copy_(sd["mu_master"])
+            self.ad_master.copy_(sd["ad_master"])
+
+    def refresh_master_from_params(self) -> None:
+        """Re-derive fp32 masters from the (just loaded) parameter values."""
+        if not self.needs_master:
+            return
+        my_mu, my_ad = self.own_ranges
+        self.mu_master.copy_(self.P[my_mu[0] : my_mu[1]])
+        self.ad_master.copy_(self.P[my_ad[0] : my_ad[1]])
