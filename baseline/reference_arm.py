@@ -1,0 +1,24 @@
+"""Reference arm of ``bench.py``: runs the UNMODIFIED reference package installed under
+``baseline/_ref`` through its own ``create_train_task`` / ``fsdp2_trainer`` code path on the
+same model, data shapes and metric, or reports why it cannot."""
+from __future__ import annotations
+
+import json
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def unavailable(reason: str) -> None:
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": reason}), flush=True)
+
+
+def run(args) -> None:
+    ref = os.path.join(HERE, "_ref", "lmms_engine")
+    if not os.path.isdir(ref):
+        unavailable("reference package is not installed under baseline/_ref")
+        return
+    from . import reference_run
+
+    reference_run.main(args)

@@ -1,0 +1,69 @@
+"""Stand-ins for third-party packages that the reference imports at module import time but
+that are absent from this offline image (hydra, omegaconf, accelerate, peft, deepspeed,
+decord, librosa, soundfile, jsonlines, qwen_vl_utils, av).  None of them sits on the timed
+training path of the reference's fsdp2 trainer; the few functions that ARE called
+(``accelerate.utils.send_to_device``, ``init_empty_weights``) are implemented for real.
+Any other attribute resolves to an inert placeholder so that ``from pkg import Name`` works.
+The reference's own source is used unmodified."""
+import sys
+import types
+
+
+class _Placeholder:
+    def __init__(self, *a, **k):
+        pass
+
+    def __call__(self, *a, **k):
+        if len(a) == 1 and callable(a[0]) and not k:
+            return a[0]  # used as a decorator
+        return _Placeholder()
+
+    def __getattr__(self, name):
+        if name.startswith("__"):
+            raise AttributeError(name)
+        return _Placeholder()
+
+    def __iter__(self):
+        return iter(())
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+    def __mro_entries__(self, bases):
+        return (object,)
+
+
+class PermissiveModule(types.ModuleType):
+    def __getattr__(self, name):
+        if name.startswith("__"):
+            raise AttributeError(name)
+        full = self.__name__ + "." + name
+        if full in sys.modules:
+            return sys.modules[full]
+        cls = type(name, (_Placeholder,), {})
+        setattr(self, name, cls)
+        return cls
+
+
+def install(name, submodules=(), attrs=None):
+    from importlib.machinery import ModuleSpec
+
+    mod = PermissiveModule(name)
+    mod.__path__ = []  # behaves as a package
+    mod.__version__ = "0.0.0-shim"
+    mod.__spec__ = ModuleSpec(name, None, is_package=True)
+    sys.modules[name] = mod
+    for sub in submodules:
+        m = PermissiveModule(name + "." + sub)
+        m.__path__ = []
+        m.__spec__ = ModuleSpec(name + "." + sub, None, is_package=True)
+        sys.modules[name + "." + sub] = m
+        parent = sys.modules[(name + "." + sub).rsplit(".", 1)[0]]
+        setattr(parent, sub.rsplit(".", 1)[-1], m)
+    for k, v in (attrs or {}).items():
+        target, _, attr = k.rpartition(".")
+        setattr(sys.modules[name + ("." + target if target else "")], attr, v)
+    return mod

@@ -57,15 +57,29 @@ def _resolve(model_type: str, general_type: Optional[str]):
     return None
 
 
-def create_model_from_config(model_type: str, config: Dict[str, Any], model_general_type: Optional[str] = None, **kw):
-    """Random-init model from a config dict (``model_config.load_from_config``)."""
+def create_model_from_config(model_type: str, config: Dict[str, Any], model_general_type: Optional[str] = None,
+                             device=None, dtype=None, **kw):
+    """Random-init model from a config dict (``model_config.load_from_config``).  With
+    ``device`` / ``dtype`` the parameters are created (and initialised) directly there, so a
+    multi-billion-parameter model never takes a detour through fp32 host memory."""
+    import torch
+
     from . import models  # noqa: F401  (populates the registry)
 
     hit = _resolve(model_type, model_general_type)
     if hit is not None:
         cfg_cls, model_cls = hit
         cfg = cfg_cls.from_dict({"model_type": model_type, **(config or {})})
-        return model_cls(cfg)
+        if device is None and dtype is None:
+            return model_cls(cfg)
+        old = torch.get_default_dtype()
+        try:
+            if dtype is not None:
+                torch.set_default_dtype(dtype)
+            with torch.device(device if device is not None else "cpu"):
+                return model_cls(cfg)
+        finally:
+            torch.set_default_dtype(old)
     return _hf_fallback_from_config(model_type, config, model_general_type, **kw)
 
 

@@ -104,6 +104,10 @@ class TorchComm:
         for w in works:
             w.wait()
 
+    def broadcast_all(self, flat: torch.Tensor, src: int = 0) -> None:
+        if self.n > 1:
+            dist.broadcast(flat, src=self.global_rank(src), group=self.group)
+
     def all_reduce_sum(self, t: torch.Tensor) -> None:
         if self.n > 1:
             dist.all_reduce(t, group=self.group)
@@ -206,6 +210,8 @@ class OwnerShardedRuntime:
                 p.data = view
                 p.grad = self.G[s.offset : s.offset + s.numel].view(s.shape)
         self.params = name_to_param
+        # replicas must start identical whatever each rank's initialisation did
+        self.comm.broadcast_all(self.P, 0)
 
         # ---- owned state ------------------------------------------------------------------------
         my_mu, my_ad = self.muon_ranges[self.rank], self.adam_ranges[self.rank]

@@ -72,7 +72,13 @@ class TrainRunner:
             model_type = cfg.pop("model_type")
             conf = dict(cfg.pop("config", {}) or {})
             conf.update(mc.overwrite_config or {})
-            model = create_model_from_config(model_type, conf, mc.model_general_type)
+            args = self.config.trainer_args
+            device = dtype = None
+            if torch.cuda.is_available() and not args.use_cpu:
+                # build straight on the GPU in the compute dtype
+                device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+                dtype = torch.bfloat16 if args.bf16 else (torch.float16 if args.fp16 else None)
+            model = create_model_from_config(model_type, conf, mc.model_general_type, device=device, dtype=dtype)
         else:
             raise ValueError("model_config needs load_from_pretrained_path or load_from_config")
         if mc.load_from_pretrained_path and mc.overwrite_config:
