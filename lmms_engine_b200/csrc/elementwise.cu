@@ -851,3 +851,70 @@ int b200_ce_dlogits(void* logits, const void* lse, const void* labels, const voi
 }
 
 }  // extern "C"
+
+// ====================================================================================
+// Allocation-free RMSNorm backward (see no_alloc.h for who needs it and for its limits).
+// ====================================================================================
+#include "no_alloc.h"
+
+#include <mutex>
+
+namespace b200 {
+
+// Scratch for the per-CTA partial sums of dw.  File scope, device memory, part of the
+// library image: no allocation at run time.  In host code this name is only a handle for
+// cudaGetSymbolAddress, never a pointer a kernel could use.
+static __device__ __align__(256) float g_noalloc_dw_part[B200_NOALLOC_MAX_PARTS * B200_NOALLOC_MAX_H];
+
+constexpr int kNoAllocMaxDevices = 64;
+static float* g_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};
+static std::mutex g_noalloc_mutex;
+
+// Device address of the scratch array on the current device, resolved once per device.
+static float* noalloc_scratch_for_current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_dw_part) != cudaSuccess || p == nullptr) return nullptr;
+    g_noalloc_ptr[dev] = static_cast<float*>(p);
+  }
+  return g_noalloc_ptr[dev];
+}
+
+}  // namespace b200
+
+extern "C" int b200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const void* rstd, void* dx,
+                                        void* dw, int rows, int H, float w_offset, cudaStream_t st) {
+  using namespace b200;
+  if (rows <= 0) return 0;
+  if (H % 8) return -10;
+  if (H > B200_NOALLOC_MAX_H) return B200_NOALLOC_ERR_TOO_LARGE;
+  float* part = noalloc_scratch_for_current_device();
+  if (part == nullptr) return B200_NOALLOC_ERR_SETUP;
+  int parts;
+  if (H <= 512) {
+    int blocks = num_sms() * 2 / 8;
+    if (blocks < 1) blocks = 1;
+    parts = blocks * 8;
+    if (parts > B200_NOALLOC_MAX_PARTS) return B200_NOALLOC_ERR_TOO_LARGE;
+    norm_bwd_warp_kernel<<<blocks, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)rstd,
+                                                 (bf16*)dx, part, rows, H, w_offset);
+  } else {
+    parts = num_sms() * 2;
+    if (parts > rows) parts = rows;
+    if (parts > B200_NOALLOC_MAX_PARTS) parts = B200_NOALLOC_MAX_PARTS;
+#define NOALLOC_BWD(T, V)                                                                                          \
+  norm_bwd_kernel<T, V><<<parts, T, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)rstd, \
+                                             nullptr, nullptr, (bf16*)dx, part, nullptr, rows, H, w_offset, 0)
+    if (H <= 1024) NOALLOC_BWD(128, 1);
+    else if (H <= 2048) NOALLOC_BWD(256, 1);
+    else NOALLOC_BWD(256, 2);
+#undef NOALLOC_BWD
+  }
+  if (cudaGetLastError() != cudaSuccess) return -4;
+  // every partial row that is summed here was written by the launch above
+  colsum_kernel<<<(H + 255) / 256, 256, 0, st>>>(part, (float*)dw, parts, H, 0);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
