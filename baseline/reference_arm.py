@@ -19,6 +19,12 @@ def run(args) -> None:
     if not os.path.isdir(ref):
         unavailable("reference package is not installed under baseline/_ref")
         return
-    from . import reference_run
+    try:
+        from . import reference_run
 
-    reference_run.main(args)
+        reference_run.main(args)
+    except BaseException as e:  # the arm must always answer with one JSON line and exit 0
+        import traceback
+
+        traceback.print_exc()
+        unavailable(f"reference run failed: {type(e).__name__}: {str(e)[:300]}")

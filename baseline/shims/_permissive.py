@@ -53,7 +53,7 @@ def install(name, submodules=(), attrs=None):
 
     mod = PermissiveModule(name)
     mod.__path__ = []  # behaves as a package
-    mod.__version__ = "0.0.0-shim"
+    mod.__version__ = "0.0.0"
     mod.__spec__ = ModuleSpec(name, None, is_package=True)
     sys.modules[name] = mod
     for sub in submodules:

@@ -41,6 +41,7 @@ def install_all():
             getattr(_iu, fn)()
         except Exception:
             pass
+    _patch_hf_device_setup()
     if _missing("hydra"):
         def main(*a, **k):
             def deco(fn):
@@ -58,3 +59,33 @@ def install_all():
                        ("torchdiffeq", ()), ("bitsandbytes", ()), ("lmms_eval", ())):
         if _missing(name):
             P.install(name, submodules=subs)
+
+
+def _patch_hf_device_setup():
+    """``transformers.TrainingArguments`` resolves its device through accelerate's
+    ``PartialState``.  Without accelerate the same answer is computed directly: the local
+    CUDA device of this rank (or the CPU)."""
+    import functools
+    import os
+
+    import torch
+    import transformers.training_args as ta
+    from transformers.utils import import_utils as iu
+
+    if iu.is_accelerate_available():
+        return
+
+    def _setup_devices(self):
+        if self.use_cpu or not torch.cuda.is_available():
+            self._n_gpu = 0
+            self.distributed_state = None
+            return torch.device("cpu")
+        dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        torch.cuda.set_device(dev)
+        self._n_gpu = 1
+        self.distributed_state = None
+        return dev
+
+    prop = functools.cached_property(_setup_devices)
+    prop.__set_name__(ta.TrainingArguments, "_setup_devices")
+    ta.TrainingArguments._setup_devices = prop

@@ -228,6 +228,8 @@ def main():
     ap.add_argument("--runtime", default="native", choices=["native", "torch_fsdp2", "auto"])
     ap.add_argument("--linear-backend", default=None, choices=[None, "tcgen05", "cublas"])
     ap.add_argument("--checkpointing", type=int, default=0)
+    ap.add_argument("--ref-checkpointing", type=int, default=1,
+                    help="reference arm: gradient checkpointing as in its examples/qwen2_5_llm config")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -1,0 +1,39 @@
+"""Multi-GPU checks (skipped with fewer than two visible GPUs): the peer-memory runtime
+under torchrun, one rank per GPU."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HELPERS = os.path.join(os.path.dirname(__file__), "helpers")
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _torchrun(script, nproc, timeout=600):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HELPERS, script)]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    return res.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_runtime_two_gpus():
+    out = _torchrun("peer_two_gpu.py", 2)
+    assert "peer runtime ok" in out
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four GPUs")
+def test_peer_runtime_four_gpus():
+    out = _torchrun("peer_two_gpu.py", 4)
+    assert "peer runtime ok" in out
