@@ -51,6 +51,7 @@ enum Epilogue : int { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_STATS = 2, EPI_SYMM = 3
 struct GemmParams {
   int M, N, K;
   int a_mn_major, b_mn_major;
+  int a_mn3d, b_mn3d;          // MN-major operand fetched with ONE 3-D TMA box (all 64-wide chunks at once)
   float alpha, beta;
   const __nv_bfloat16* bias;   // [N] or null (PLAIN)
   const __nv_bfloat16* cin;    // [M, ldcin] or null (PLAIN / SYMM)
@@ -152,6 +153,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int k0 = kb * BK;
           if (!p.a_mn_major) {
             tma_load_2d(sa, &tmA, &full_bar[s], k0, m0);
+          } else if (p.a_mn3d) {
+            tma_load_3d(sa, &tmA, &full_bar[s], 0, k0, m0 / 64);
           } else {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * 8192, &tmA, &full_bar[s], m0 + c * 64, k0);
@@ -162,6 +165,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tma_load_2d(sb + 128 * 128, &tmB2, &full_bar[s], k0, n0);
           } else if (!p.b_mn_major) {
             tma_load_2d(sb, &tmB, &full_bar[s], k0, n0);
+          } else if (p.b_mn3d) {
+            tma_load_3d(sb, &tmB, &full_bar[s], 0, k0, n0 / 64);
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * 8192, &tmB, &full_bar[s], n0 + c * 64, k0);
@@ -456,6 +461,29 @@ static int make_map(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t col
   return 0;
 }
 
+// MN-major operand stored row-major [K, R] (R % 64 == 0) seen as {64, K, R/64}: one box
+// {64, BK, chunks} lands in shared memory chunk-major, which is exactly the layout the
+// MN-major UMMA descriptor walks (64-wide chunks BK*128 bytes apart).
+static int make_map_mn3d(CUtensorMap* m, const void* ptr, uint64_t k_rows, uint64_t r_cols, uint64_t ld,
+                         uint32_t chunks) {
+  bind_context();
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[3] = {64, k_rows, r_cols / 64};
+  cuuint64_t strides[2] = {ld * 2, 128};
+  cuuint32_t box[3] = {64, static_cast<cuuint32_t>(BK), chunks};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr, "[b200 gemm] 3-D map failed (%d): k=%llu r=%llu ld=%llu\n", static_cast<int>(r),
+            (unsigned long long)k_rows, (unsigned long long)r_cols, (unsigned long long)ld);
+    return -2;
+  }
+  return 0;
+}
+
 static int g_num_sms = 0;
 
 template <int EPI>
@@ -498,15 +526,21 @@ int b200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, i
   if ((lda | ldb | ldc) & 7) return -10;
   CUtensorMap tA, tB, tC;
   int rc = 0;
+  int a3d = a_mn_major && (M % 64 == 0) && (lda >= M);
+  int b3d = b_mn_major && (N % 64 == 0) && (ldb >= N);
+  // the one-box fetch is an optimisation: if the driver rejects the 3-D view, use 2-D boxes
+  if (a3d && make_map_mn3d(&tA, A, K, M, lda, BM / 64) != 0) a3d = 0;
+  if (b3d && make_map_mn3d(&tB, B, K, N, ldb, BN / 64) != 0) b3d = 0;
   if (!a_mn_major) rc |= make_map(&tA, A, M, K, lda, BK, BM, true);
-  else rc |= make_map(&tA, A, K, M, lda, 64, BK, true);
+  else if (!a3d) rc |= make_map(&tA, A, K, M, lda, 64, BK, true);
   if (!b_mn_major) rc |= make_map(&tB, B, N, K, ldb, BK, BN, true);
-  else rc |= make_map(&tB, B, K, N, ldb, 64, BK, true);
+  else if (!b3d) rc |= make_map(&tB, B, K, N, ldb, 64, BK, true);
   rc |= make_map(&tC, C, M, N, ldc, 64, 32, true);
   if (rc != 0) return rc;
   GemmParams p{};
   p.M = M; p.N = N; p.K = K;
   p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
+  p.a_mn3d = a3d; p.b_mn3d = b3d;
   p.alpha = alpha; p.beta = beta;
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.cin = static_cast<const __nv_bfloat16*>(cin);
