@@ -62,6 +62,12 @@ struct GemmParams {
   int store_gu;                // SWIGLU: also store gate / up pre-activations
   __nv_bfloat16* cmirror;      // SYMM: base of C for the transposed stores
   int ldc;
+  // grouped (mixture-of-experts) modes; all tables live in device memory
+  const int* tile_expert;      // grouped-M: expert of every 128-row tile of A / C (-1: unused tile)
+  int up_row_offset;           // grouped SWIGLU: row of the first "up" weight inside an expert's [2I, K] block
+  const int* expert_start;     // grouped-K: row range [start[e], start[e+1]) of expert e in A and B
+  int group_k;                 // 1: C[e] = A[rows_e]^T B[rows_e] (both operands MN-major)
+  int n_experts;
   int* status;
 };
 
@@ -126,8 +132,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   // SYMM skips tiles that lie entirely below the diagonal.
   auto tile_active = [&](int mb, int nb) -> bool {
+    if (p.tile_expert != nullptr && p.tile_expert[mb] < 0) return false;
     if (EPI != EPI_SYMM) return true;
     return (nb + 1) * BN > mb * BM;
+  };
+  // grouped-K: tile t = (expert, m-block, n-block); K runs over the expert's own rows
+  const int tiles_per_expert = tiles_m * tiles_n;
+  const int total_tiles = p.group_k ? n_tiles * p.n_experts : n_tiles;
+  auto decode = [&](int t, int& e, int& mb, int& nb, int& kb_lo, int& kb_n) {
+    if (p.group_k) {
+      e = t / tiles_per_expert;
+      tile_coords(t - e * tiles_per_expert, tiles_m, tiles_n, mb, nb);
+      const int r0 = p.expert_start[e], r1 = p.expert_start[e + 1];
+      kb_lo = r0 / BK;
+      kb_n = (r1 - r0) / BK;
+    } else {
+      tile_coords(t, tiles_m, tiles_n, mb, nb);
+      e = p.tile_expert != nullptr ? p.tile_expert[mb] : 0;
+      kb_lo = 0;
+      kb_n = n_kb;
+    }
   };
 
   if (warp == 0) {
@@ -137,20 +161,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tma_prefetch_desc(&tmB);
       uint32_t it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-        int mb, nb;
-        tile_coords(t, tiles_m, tiles_n, mb, nb);
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int ex, mb, nb, kb_lo, kb_n;
+        decode(t, ex, mb, nb, kb_lo, kb_n);
         if (!tile_active(mb, nb)) continue;
         const int m0 = mb * BM;
         const int n0 = (EPI == EPI_SWIGLU) ? nb * (BN / 2) : nb * BN;
-        for (int kb = 0; kb < n_kb; ++kb, ++it) {
+        const bool grouped_b = p.tile_expert != nullptr;  // B is a 3-D map indexed by expert
+        for (int kb = 0; kb < kb_n; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_word)) { ok = false; break; }
           uint8_t* sa = smem + s * kStageBytes;
           uint8_t* sb = sa + kATileBytes;
           mbar_expect_tx(&full_bar[s], kStageBytes);
-          const int k0 = kb * BK;
+          const int k0 = (kb_lo + kb) * BK;
           if (!p.a_mn_major) {
             tma_load_2d(sa, &tmA, &full_bar[s], k0, m0);
           } else if (p.a_mn3d) {
@@ -159,10 +184,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * 8192, &tmA, &full_bar[s], m0 + c * 64, k0);
           }
-          if (EPI == EPI_SWIGLU) {
+          if (EPI == EPI_SWIGLU && grouped_b) {
+            tma_load_3d(sb, &tmB, &full_bar[s], k0, n0, ex);
+            tma_load_3d(sb + 128 * 128, &tmB, &full_bar[s], k0, p.up_row_offset + n0, ex);
+          } else if (EPI == EPI_SWIGLU) {
             // gate rows then up rows, 128 each (K-major only)
             tma_load_2d(sb, &tmB, &full_bar[s], k0, n0);
             tma_load_2d(sb + 128 * 128, &tmB2, &full_bar[s], k0, n0);
+          } else if (grouped_b && !p.b_mn_major) {
+            tma_load_3d(sb, &tmB, &full_bar[s], k0, n0, ex);
+          } else if (grouped_b) {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_3d(sb + c * 8192, &tmB, &full_bar[s], n0 + c * 64, k0, ex);
           } else if (!p.b_mn_major) {
             tma_load_2d(sb, &tmB, &full_bar[s], k0, n0);
           } else if (p.b_mn3d) {
@@ -180,16 +213,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t idesc = umma_idesc_bf16_major(BM, BN, p.a_mn_major, p.b_mn_major);
       uint32_t it = 0, tl = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-        int mb, nb;
-        tile_coords(t, tiles_m, tiles_n, mb, nb);
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int ex, mb, nb, kb_lo, kb_n;
+        decode(t, ex, mb, nb, kb_lo, kb_n);
         if (!tile_active(mb, nb)) continue;
         const int acc = tl & 1;
         const uint32_t acc_ph = (tl >> 1) & 1;
         if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_word)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < n_kb; ++kb, ++it) {
+        for (int kb = 0; kb < kb_n; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           if (!mbar_wait(&full_bar[s], ph, abort_word)) { ok = false; break; }
@@ -226,10 +259,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t tl = 0;
     int buf = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-      int mb, nb;
-      tile_coords(t, tiles_m, tiles_n, mb, nb);
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int ex, mb, nb, kb_lo, kb_n;
+      decode(t, ex, mb, nb, kb_lo, kb_n);
       if (!tile_active(mb, nb)) continue;
+      const bool empty_k = (kb_n == 0);  // grouped-K expert without rows: the product is zero
       const int acc = tl & 1;
       const uint32_t acc_ph = (tl >> 1) & 1;
       if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_word)) { ok = false; break; }
@@ -255,7 +289,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const int col0 = n0 + c64 * 64 + h * 32;
             float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+            for (int j = 0; j < 32; ++j) v[j] = empty_k ? 0.f : __uint_as_float(r[j]) * p.alpha;
             if (EPI == EPI_PLAIN && p.bias != nullptr) {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
@@ -332,7 +366,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&tmC, slab, n0 + c64 * 64, m0 + q * 32);
+            if (p.group_k) tma_store_3d(&tmC, slab, n0 + c64 * 64, m0 + q * 32, ex);
+            else tma_store_2d(&tmC, slab, n0 + c64 * 64, m0 + q * 32);
             tma_store_commit();
           }
           buf ^= 1;
@@ -484,6 +519,27 @@ static int make_map_mn3d(CUtensorMap* m, const void* ptr, uint64_t k_rows, uint6
   return 0;
 }
 
+// [E, R, C] bf16, contiguous: 3-D map (c, r, e) with box (box_c, box_r, 1)
+static int make_map_e3(CUtensorMap* m, const void* ptr, uint64_t E, uint64_t R, uint64_t C, uint32_t box_c,
+                       uint32_t box_r) {
+  bind_context();
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[3] = {C, R, E};
+  cuuint64_t strides[2] = {C * 2, R * C * 2};
+  cuuint32_t box[3] = {box_c, box_r, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr, "[b200 gemm] expert map failed (%d): E=%llu R=%llu C=%llu\n", static_cast<int>(r),
+            (unsigned long long)E, (unsigned long long)R, (unsigned long long)C);
+    return -2;
+  }
+  return 0;
+}
+
 static int g_num_sms = 0;
 
 template <int EPI>
@@ -503,7 +559,7 @@ static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMa
   }
   int ctas = g_num_sms;
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
-  int tiles = p.n_tiles_m * p.n_tiles_n;
+  int tiles = p.n_tiles_m * p.n_tiles_n * (p.group_k ? p.n_experts : 1);
   if (tiles < ctas) ctas = tiles;
   if (ctas <= 0) return 0;
   gemm_bf16_kernel<EPI><<<ctas, kThreads, kSmemBytes, stream>>>(tA, tB, tB2, tC, tC2, tC3, p);
@@ -602,6 +658,81 @@ int b200_gemm_stats_bf16(const void* X, const void* W, void* logits, void* stats
   p.n_tiles_n = (N + BN - 1) / BN;
   p.status = status;
   return launch<EPI_STATS>(tA, tB, tB, tC, tC, tC, p, 0, stream);
+}
+
+// ---- grouped (mixture-of-experts) products ------------------------------------------------
+// A rows are grouped by expert in 128-row tiles (tile_expert[i] = expert of tile i, -1 for
+// unused tiles); W is [E, N, K] (K-major) or [E, K, N] (w_mn_major).  C[rows, N] = A W[e]^T.
+int b200_gemm_grouped_bf16(const void* A, const void* W, void* C, const void* tile_expert, int rows, int N, int K,
+                           int E, int lda, int ldc, int w_mn_major, int* status, cudaStream_t stream) {
+  if (rows <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda | ldc) & 7) return -10;
+  CUtensorMap tA, tB, tC;
+  int rc = make_map(&tA, A, rows, K, lda, BK, BM, true);
+  if (!w_mn_major) rc |= make_map_e3(&tB, W, E, N, K, BK, BN);
+  else rc |= make_map_e3(&tB, W, E, K, N, 64, BK);
+  rc |= make_map(&tC, C, rows, N, ldc, 64, 32, true);
+  if (rc != 0) return rc;
+  GemmParams p{};
+  p.M = rows; p.N = N; p.K = K;
+  p.b_mn_major = w_mn_major;
+  p.alpha = 1.f;
+  p.n_tiles_m = (rows + BM - 1) / BM;
+  p.n_tiles_n = (N + BN - 1) / BN;
+  p.tile_expert = static_cast<const int*>(tile_expert);
+  p.n_experts = E;
+  p.status = status;
+  return launch<EPI_PLAIN>(tA, tB, tB, tC, tC, tC, p, 0, stream);
+}
+
+// Grouped gate/up projection with SwiGLU: W is [E, 2I, K] with gate rows first.
+// H[rows, I] = silu(g) * u; GU[rows, 2I] = [g | u] (kept for backward).
+int b200_gemm_grouped_swiglu_bf16(const void* A, const void* W, void* H, void* GU, const void* tile_expert, int rows,
+                                  int I, int K, int E, int lda, int* status, cudaStream_t stream) {
+  if (rows <= 0 || I <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (I & 7)) return -10;
+  CUtensorMap tA, tB, tC, tC2, tC3;
+  int rc = make_map(&tA, A, rows, K, lda, BK, BM, true);
+  rc |= make_map_e3(&tB, W, E, 2 * I, K, BK, 128);
+  rc |= make_map(&tC, H, rows, I, I, 64, 32, true);
+  rc |= make_map(&tC2, GU, rows, I, 2 * I, 64, 32, true);
+  rc |= make_map(&tC3, static_cast<const __nv_bfloat16*>(GU) + I, rows, I, 2 * I, 64, 32, true);
+  if (rc != 0) return rc;
+  GemmParams p{};
+  p.M = rows; p.N = I; p.K = K;
+  p.alpha = 1.f;
+  p.n_tiles_m = (rows + BM - 1) / BM;
+  p.n_tiles_n = (I + 127) / 128;
+  p.store_gu = 1;
+  p.tile_expert = static_cast<const int*>(tile_expert);
+  p.up_row_offset = I;
+  p.n_experts = E;
+  p.status = status;
+  return launch<EPI_SWIGLU>(tA, tB, tB, tC, tC2, tC3, p, 0, stream);
+}
+
+// Per-expert weight gradient: dW[e] [M, N] = A[rows_e, M]^T B[rows_e, N], rows_e =
+// [expert_start[e], expert_start[e+1]) (multiples of 128; padding rows must be zero in A or B).
+int b200_gemm_grouped_wgrad_bf16(const void* A, const void* B, void* dW, const void* expert_start, int rows, int M,
+                                 int N, int E, int lda, int ldb, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || E <= 0) return 0;
+  if ((lda | ldb) & 7) return -10;
+  CUtensorMap tA, tB, tC;
+  int rc = make_map(&tA, A, rows, M, lda, 64, BK, true);
+  rc |= make_map(&tB, B, rows, N, ldb, 64, BK, true);
+  rc |= make_map_e3(&tC, dW, E, M, N, 64, 32);
+  if (rc != 0) return rc;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = rows;
+  p.a_mn_major = 1; p.b_mn_major = 1;
+  p.alpha = 1.f;
+  p.n_tiles_m = (M + BM - 1) / BM;
+  p.n_tiles_n = (N + BN - 1) / BN;
+  p.expert_start = static_cast<const int*>(expert_start);
+  p.group_k = 1;
+  p.n_experts = E;
+  p.status = status;
+  return launch<EPI_PLAIN>(tA, tB, tB, tC, tC, tC, p, 0, stream);
 }
 
 int b200_gemm_tile_n() { return BN; }

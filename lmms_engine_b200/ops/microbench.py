@@ -39,6 +39,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
     ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--only", default=None, help="substring filter on the op name (GEMM shapes only)")
+    ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args()
     from . import gemm, _cuda
 
@@ -60,6 +62,8 @@ def main():
     ]
     if args.quick:
         shapes = shapes[:2]
+    if args.only:
+        shapes = [s_ for s_ in shapes if args.only in s_[0]]
     for name, M, N, K, kind in shapes:
         if kind == "nt":
             a, b = rnd(M, K), rnd(N, K)
@@ -73,13 +77,16 @@ def main():
             a, b = rnd(K, M), rnd(K, N)
             mine = lambda: gemm.gemm(a, b, a_mn_major=True, b_mn_major=True)
             lib = lambda: torch.matmul(a.t(), b)
-        t1 = timeit(mine, flush=flush)
-        t2 = timeit(lib, flush=flush)
+        t1 = timeit(mine, iters=args.iters, flush=flush)
+        t2 = timeit(lib, iters=args.iters, flush=flush)
         fl = 2.0 * M * N * K
         rows.append({"op": name, "M": M, "N": N, "K": K, "ms": t1, "tflops": fl / t1 / 1e9, "lib_ms": t2,
                      "lib_tflops": fl / t2 / 1e9})
         print(rows[-1], flush=True)
         del a, b
+    if args.only:
+        _cuda.check_status()
+        return
     # fused SwiGLU GEMM vs cuBLAS x2 + elementwise
     x, wg, wu = rnd(T, 3584), rnd(18944, 3584), rnd(18944, 3584)
     t1 = timeit(lambda: gemm.gemm_swiglu(x, wg, wu, True), flush=flush)
