@@ -6,4 +6,9 @@ from .decoder_lm import DecoderConfig, DecoderLM
 for _mt in ("qwen2", "qwen2_5", "qwen3", "llama"):
     register_model(_mt, DecoderConfig, DecoderLM, "causal_lm")
 
-__all__ = ["ModelConfig", "DecoderConfig", "DecoderLM"]
+from .moe_lm import MoEConfig, MoEDecoderLM
+
+for _mt in ("qwen3_moe", "qwen2_moe", "qwen3_5_moe_text"):
+    register_model(_mt, MoEConfig, MoEDecoderLM, "causal_lm")
+
+__all__ = ["ModelConfig", "DecoderConfig", "DecoderLM", "MoEConfig", "MoEDecoderLM"]
