@@ -1,0 +1,51 @@
+"""Parallelism plumbing on CPU/gloo ranks: expert parallel, Ulysses, tensor parallel and the
+rank-layout arithmetic, each against the unsharded computation."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+
+HELPERS = os.path.join(os.path.dirname(__file__), "helpers")
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def torchrun(script, nproc, *args, timeout=600):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HELPERS, script), *args]
+    env = dict(os.environ, OMP_NUM_THREADS="2", CUDA_VISIBLE_DEVICES="")
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    return res.stdout
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_matches_unsharded(world):
+    assert "expert parallel ok" in torchrun("ep_run.py", world)
+
+
+def test_rank_layout_arithmetic():
+    from lmms_engine_b200.parallel.process_group_manager import RankLayout
+
+    lay = RankLayout(world_size=8, tp=2, cp=2, pp=1, dp=2)
+    assert lay.coords(5) == (1, 0, 0, 1)
+    assert lay.group_ranks(5, "tp") == [4, 5]
+    assert lay.group_ranks(5, "cp") == [5, 7]
+    assert lay.group_ranks(5, "dp") == [1, 5]
+    assert lay.group_ranks(0, "dp_cp") == [0, 2, 4, 6]
+    ep = RankLayout(world_size=8, dp=8, ep=4)
+    assert (ep.dp_shard_mod_ep, ep.dp_shard_in_ep) == (2, 4)
+    assert ep.group_ranks(5, "ep") == [4, 5, 6, 7]
+    with pytest.raises(ValueError):
+        RankLayout(world_size=8, dp=8, hsdp_shard=1)
+    with pytest.raises(ValueError):
+        RankLayout(world_size=8, dp=4, pp=2)
+    with pytest.raises(ValueError):
+        RankLayout(world_size=8, dp=8, ep=3)
