@@ -30,9 +30,17 @@ from ..ops import gemm as gemm_ops
 from ..ops import norm as norm_ops
 from ..ops import rope as rope_ops
 from ..ops import swiglu as swiglu_ops
+from ..parallel import tp_ops
 from ..parallel.sequence_parallel import ulysses as sp
 
 IGNORE_INDEX = -100
+
+
+def _w(p):
+    """Plain local tensor of a parameter (tensor-parallel parameters are DTensors on the tp mesh)."""
+    if p is None:
+        return None
+    return p.to_local() if hasattr(p, "to_local") else p
 
 
 @dataclass
@@ -130,12 +138,17 @@ class Attention(nn.Module):
         self.window = (window, -1) if window else (-1, -1)
 
     def forward(self, x: torch.Tensor, ctx: "PackedContext") -> torch.Tensor:
-        T = x.shape[0]
         D = self.head_dim
+        if ctx.tp_size > 1:
+            # sequence-parallel tensor parallelism: gather the token shards, project onto this
+            # rank's heads; the row-parallel output projection below reduce-scatters back
+            x = tp_ops.all_gather_tokens(x, ctx.tp_group)
+        T = x.shape[0]
         # one GEMM for q, k, v: the three weights are concatenated on the fly (tens of MB,
         # microseconds) so the projection runs as a single [T, (Hq+2Hkv)D] product
-        w = torch.cat([self.q_proj.weight, self.k_proj.weight, self.v_proj.weight], 0)
-        b = torch.cat([self.q_proj.bias, self.k_proj.bias, self.v_proj.bias], 0) if self.q_proj.bias is not None else None
+        w = torch.cat([_w(self.q_proj.weight), _w(self.k_proj.weight), _w(self.v_proj.weight)], 0)
+        b = (torch.cat([_w(self.q_proj.bias), _w(self.k_proj.bias), _w(self.v_proj.bias)], 0)
+             if self.q_proj.bias is not None else None)
         qkv = gemm_ops.linear(x, w, b)
         nq, nkv = self.n_q * D, self.n_kv * D
         q = qkv[:, :nq].view(T, self.n_q, D)
@@ -155,7 +168,10 @@ class Attention(nn.Module):
         )
         if ctx.sp_size > 1:
             o = sp.head_to_seq(o, ctx.sp_group, self.n_q, self.n_kv)
-        return gemm_ops.linear(o.reshape(o.shape[0], -1), self.o_proj.weight, None)
+        out = gemm_ops.linear(o.reshape(o.shape[0], -1), _w(self.o_proj.weight), None)
+        if ctx.tp_size > 1:
+            out = tp_ops.reduce_scatter_tokens(out, ctx.tp_group)
+        return out
 
 
 class SwiGLUMLP(nn.Module):
@@ -165,8 +181,15 @@ class SwiGLUMLP(nn.Module):
         self.up_proj = nn.Linear(hidden, inter, bias=False)
         self.down_proj = nn.Linear(inter, hidden, bias=False)
 
+        self.tp_group = None
+
     def forward(self, x):
-        return swiglu_ops.swiglu_mlp(x, self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight)
+        if self.tp_group is not None:
+            x = tp_ops.all_gather_tokens(x, self.tp_group)
+        y = swiglu_ops.swiglu_mlp(x, _w(self.gate_proj.weight), _w(self.up_proj.weight), _w(self.down_proj.weight))
+        if self.tp_group is not None:
+            y = tp_ops.reduce_scatter_tokens(y, self.tp_group)
+        return y
 
 
 class DecoderLayer(nn.Module):
@@ -208,6 +231,8 @@ class PackedContext:
     causal: bool = True
     sp_group: Any = None
     sp_size: int = 1
+    tp_group: Any = None
+    tp_size: int = 1
     aux: List[Any] = field(default_factory=list)
     deepstack: Optional[List[torch.Tensor]] = None  # per-layer additive visual features
     deepstack_index: Optional[torch.Tensor] = None
@@ -291,6 +316,7 @@ class DecoderLM(nn.Module):
         if cfg.tie_word_embeddings:
             self.lm_head.weight = self.model.embed_tokens.weight
         self.sp_group = None  # set by the trainer when Ulysses is on
+        self.tp_group = None  # set by the tensor-parallel plan
         self.causal = True
         self.loss_reduction = "mean"
         self.apply(self._init_weights)
@@ -359,44 +385,49 @@ class DecoderLM(nn.Module):
             max_seqlen = T_full  # an upper bound is enough: the kernels schedule from cu_seqlens
         shifted = shift_labels_per_document(labels, cu) if labels is not None else None
         cos, sin = self.model.rope_tables(pos)
-        sp_group = self.sp_group
-        sp_size = sp.group_size(sp_group)
-        ctx = PackedContext(cu, int(max_seqlen), cos, sin, self.causal, sp_group, sp_size,
+        sp_group, tp_group = self.sp_group, self.tp_group
+        sp_size, tp_size = sp.group_size(sp_group), sp.group_size(tp_group)
+        if sp_size > 1 and tp_size > 1:
+            raise NotImplementedError("Ulysses and tensor parallelism cannot be combined in one model")
+        # sg: the group over which the token stream is split between blocks (Ulysses ranks, or
+        # tensor-parallel ranks in the sequence-parallel regions)
+        sg, sg_size = (tp_group, tp_size) if tp_size > 1 else (sp_group, sp_size)
+        ctx = PackedContext(cu, int(max_seqlen), cos, sin, self.causal, sp_group, sp_size, tp_group, tp_size,
                             deepstack=deepstack, deepstack_index=deepstack_index)
         if inputs_embeds is None:
-            if sp_size > 1:
-                ids = sp.slice_for_rank(sp.pad_to_multiple(ids, sp_size, 0), sp_group)
+            if sg_size > 1:
+                ids = sp.slice_for_rank(sp.pad_to_multiple(ids, sg_size, 0), sg)
             inputs_embeds = self.model.embed_tokens(ids)
-        elif sp_size > 1:
-            inputs_embeds = sp.slice_for_rank(sp.pad_to_multiple(inputs_embeds, sp_size, 0), sp_group)
-        if sp_size > 1:
+        elif sg_size > 1:
+            inputs_embeds = sp.slice_for_rank(sp.pad_to_multiple(inputs_embeds, sg_size, 0), sg)
+        if sg_size > 1:
             # padded tail tokens form a trailing pseudo-document
-            pad = (-T_full) % sp_size
+            pad = (-T_full) % sg_size
             if pad:
                 ctx.cu_seqlens = torch.cat([cu, cu[-1:] + pad]).to(torch.int32)
-                ctx.cos = sp.pad_to_multiple(cos, sp_size, 0)
-                ctx.sin = sp.pad_to_multiple(sin, sp_size, 0)
+                ctx.cos = sp.pad_to_multiple(cos, sg_size, 0)
+                ctx.sin = sp.pad_to_multiple(sin, sg_size, 0)
             if shifted is not None:
-                shifted = sp.slice_for_rank(sp.pad_to_multiple(shifted, sp_size, IGNORE_INDEX), sp_group)
+                shifted = sp.slice_for_rank(sp.pad_to_multiple(shifted, sg_size, IGNORE_INDEX), sg)
         hidden = self.model(inputs_embeds, ctx)
         out: Dict[str, Any] = {"aux": ctx.aux}
         if return_logits:
             out["logits"] = F.linear(hidden, self.lm_head.weight)
         if shifted is not None:
-            out["loss"] = self.compute_loss(hidden, shifted, sp_group, sp_size)
+            out["loss"] = self.compute_loss(hidden, shifted, sg, sg_size, averaged_by_fsdp=tp_size <= 1)
             n_valid = (shifted != IGNORE_INDEX).sum()
             out["num_tokens"] = n_valid
         out["hidden_states"] = hidden if labels is None else None
         return out
 
-    def compute_loss(self, hidden, shifted, sp_group, sp_size):
-        w = self.lm_head.weight
+    def compute_loss(self, hidden, shifted, sp_group, sp_size, averaged_by_fsdp=True):
+        w = _w(self.lm_head.weight)
         if sp_size > 1:
             # per-token losses on the local slice, then the SP-wide token-weighted mean;
             # the gather's backward scales by the group size because FSDP averages over
             # the flattened dp x cp mesh (see sequence_parallel.ulysses.gather_loss)
             per_tok = ce_ops.fused_linear_cross_entropy(hidden, w, shifted, "none")
-            return sp.reduce_loss(per_tok, shifted != IGNORE_INDEX, sp_group)
+            return sp.reduce_loss(per_tok, shifted != IGNORE_INDEX, sp_group, averaged_by_fsdp)
         return ce_ops.fused_linear_cross_entropy(hidden, w, shifted, self.loss_reduction)
 
 

@@ -208,21 +208,22 @@ class _SPLossReduce(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, local_sum, local_count, group):
+    def forward(ctx, local_sum, local_count, group, averaged):
         buf = torch.stack([local_sum.detach().float(), local_count.float()])
         dist.all_reduce(buf, group=group)
         total = buf[1].clamp(min=1.0)
-        ctx.scale = dist.get_world_size(group) / total
+        # `averaged`: the data-parallel reduction will divide by this group's size as well
+        ctx.scale = (dist.get_world_size(group) if averaged else 1.0) / total
         return buf[0] / total
 
     @staticmethod
     def backward(ctx, g):
-        return g * ctx.scale, None, None
+        return g * ctx.scale, None, None, None
 
 
-def reduce_loss(per_token: torch.Tensor, valid: torch.Tensor, group) -> torch.Tensor:
+def reduce_loss(per_token: torch.Tensor, valid: torch.Tensor, group, averaged_by_fsdp: bool = True) -> torch.Tensor:
     local_sum = (per_token * valid.to(per_token.dtype)).sum()
-    return _SPLossReduce.apply(local_sum, valid.sum(), group)
+    return _SPLossReduce.apply(local_sum, valid.sum(), group, averaged_by_fsdp)
 
 
 def calculate_seq_len_per_rank(cu_seqlens, sp_size: int, rank: int):

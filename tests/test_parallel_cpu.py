@@ -49,3 +49,13 @@ def test_rank_layout_arithmetic():
         RankLayout(world_size=8, dp=4, pp=2)
     with pytest.raises(ValueError):
         RankLayout(world_size=8, dp=8, ep=3)
+
+
+def test_tensor_parallel_matches_unsharded():
+    assert "tp ok" in torchrun("tp_run.py", 2, "tp")
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_ulysses_matches_unsharded(world):
+    # 4 query heads / 1 KV head over 4 ranks also exercises KV-head replication
+    assert "ulysses ok" in torchrun("tp_run.py", world, "ulysses")
