@@ -11,4 +11,9 @@ from .moe_lm import MoEConfig, MoEDecoderLM
 for _mt in ("qwen3_moe", "qwen2_moe", "qwen3_5_moe_text"):
     register_model(_mt, MoEConfig, MoEDecoderLM, "causal_lm")
 
-__all__ = ["ModelConfig", "DecoderConfig", "DecoderLM", "MoEConfig", "MoEDecoderLM"]
+from .vl import VLConfig, VLModel
+
+for _mt in ("qwen2_5_vl", "qwen2_vl", "qwen3_vl", "qwen3_vl_moe"):
+    register_model(_mt, VLConfig, VLModel, "image_text_to_text")
+
+__all__ = ["ModelConfig", "DecoderConfig", "DecoderLM", "MoEConfig", "MoEDecoderLM", "VLConfig", "VLModel"]

@@ -1,0 +1,110 @@
+"""Parity of the native vision towers and the multimodal rotary index builder with the
+upstream ``transformers`` implementations (fp32, CPU, random weights copied by name)."""
+import os
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+transformers = pytest.importorskip("transformers")
+
+
+def _copy(src, dst):
+    sd = {k: v for k, v in src.state_dict().items()}
+    missing, unexpected = dst.load_state_dict(sd, strict=False)
+    assert not missing and not unexpected, (missing[:5], unexpected[:5])
+
+
+def test_qwen2_5_vl_tower_matches_hf():
+    from transformers.models.qwen2_5_vl.configuration_qwen2_5_vl import Qwen2_5_VLVisionConfig
+    from transformers.models.qwen2_5_vl.modeling_qwen2_5_vl import Qwen2_5_VisionTransformerPretrainedModel
+
+    from lmms_engine_b200.models.vision import Qwen25VisionTower, VisionConfig
+
+    kw = dict(depth=4, hidden_size=64, intermediate_size=96, num_heads=4, patch_size=14, out_hidden_size=48,
+              window_size=56, fullatt_block_indexes=[1, 3], spatial_merge_size=2, temporal_patch_size=2, in_channels=3)
+    torch.manual_seed(0)
+    hf = Qwen2_5_VisionTransformerPretrainedModel._from_config(Qwen2_5_VLVisionConfig(**kw), attn_implementation="eager").float().eval()
+    mine = Qwen25VisionTower(VisionConfig.from_dict(kw)).float().eval()
+    _copy(hf, mine)
+    grid = torch.tensor([[1, 6, 10], [2, 4, 4], [1, 8, 8]])
+    P = int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum())
+    pix = torch.randn(P, 3 * 2 * 14 * 14)
+    with torch.no_grad():
+        ref = hf(pix, grid_thw=grid)
+        ref = ref.pooler_output if hasattr(ref, "pooler_output") else ref
+        out = mine(pix, grid)
+    assert out.shape == ref.shape
+    assert torch.allclose(out, ref, atol=2e-4, rtol=1e-3), (out - ref).abs().max()
+
+
+def test_qwen3_vl_tower_matches_hf():
+    from transformers.models.qwen3_vl.configuration_qwen3_vl import Qwen3VLVisionConfig
+    from transformers.models.qwen3_vl.modeling_qwen3_vl import Qwen3VLVisionModel
+
+    from lmms_engine_b200.models.vision import Qwen3VisionTower, VisionConfig
+
+    kw = dict(depth=4, hidden_size=64, intermediate_size=96, num_heads=4, patch_size=16, out_hidden_size=48,
+              spatial_merge_size=2, temporal_patch_size=2, in_channels=3, num_position_embeddings=64,
+              deepstack_visual_indexes=[0, 2], hidden_act="gelu_pytorch_tanh")
+    torch.manual_seed(0)
+    hf = Qwen3VLVisionModel._from_config(Qwen3VLVisionConfig(**kw), attn_implementation="eager").float().eval()
+    mine = Qwen3VisionTower(VisionConfig.from_dict(kw)).float().eval()
+    _copy(hf, mine)
+    grid = torch.tensor([[1, 6, 10], [2, 4, 4]])
+    P = int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum())
+    pix = torch.randn(P, 3 * 2 * 16 * 16)
+    with torch.no_grad():
+        ref = hf(pix, grid_thw=grid)
+        if isinstance(ref, tuple):
+            ref_main, ref_deep = ref[0], ref[1]
+        else:
+            ref_main, ref_deep = ref.pooler_output, ref.deepstack_features
+        out, deep = mine(pix, grid)
+    assert torch.allclose(out, ref_main, atol=2e-4, rtol=1e-3), (out - ref_main).abs().max()
+    for a, b in zip(deep, ref_deep):
+        assert torch.allclose(a, b, atol=2e-4, rtol=1e-3)
+
+
+def _slow_mrope(ids, vision_ids, grids, seconds, merge, tps):
+    """Token-by-token oracle of the documented rule (text advances all streams; a vision run
+    takes temporal / row / column indices offset by the running position; text resumes at max+1)."""
+    pos, cur, g, i = [], 0, 0, 0
+    ids = list(ids)
+    while i < len(ids):
+        if ids[i] not in vision_ids:
+            pos.append((cur, cur, cur))
+            cur += 1
+            i += 1
+            continue
+        t, h, w = grids[g]
+        gh, gw = h // merge, w // merge
+        block = []
+        for f in range(t):
+            for r in range(gh):
+                for c in range(gw):
+                    block.append((int(f * seconds[g] * tps) + cur, r + cur, c + cur))
+        pos += block
+        cur = max(max(p) for p in block) + 1
+        i += len(block)
+        g += 1
+    return torch.tensor(pos).t()
+
+
+def test_mrope_positions_match_slow_oracle():
+    from lmms_engine_b200.models import mrope
+
+    img, vid = [1, 4, 6], [3, 4, 4]
+    doc1 = [1, 2, 252] + [250] * 6 + [5, 6, 252] + [251] * 12 + [7, 8, 9]
+    doc2 = [3, 252] + [250] * 4 + [4]
+    ids = torch.tensor(doc1 + doc2)
+    cu = torch.tensor([0, len(doc1), len(doc1) + len(doc2)], dtype=torch.int32)
+    grids, secs = [img, vid, [1, 4, 4]], [0.0, 1.5, 0.0]
+    mine = mrope.build_mrope_positions(ids, cu, (250, 251), grids, secs, 2, 2.0)
+    ref = torch.cat([_slow_mrope(doc1, (250, 251), grids[:2], secs[:2], 2, 2.0),
+                     _slow_mrope(doc2, (250, 251), grids[2:], secs[2:], 2, 2.0)], 1)
+    assert torch.equal(mine, ref)
+    # temporal index of the third video frame: floor(2 * 1.5 s * 2 tokens/s) = 6 past the run start
+    start = 3 + 6 + 3  # tokens before the video run in doc1
+    assert mine[0, start + 2 * 4] - mine[0, start] == 6
