@@ -271,6 +271,10 @@ class FSDP2SFTTrainer:
             else:
                 from ...utils.fsdp2_utils import fsdp2_clip_grad_norm_
 
+                if self.pgm is not None and self.pgm.enable_tp:
+                    from ...parallel import tp_ops
+
+                    tp_ops.sync_replicated_grads(self.model, self.pgm.tp_group)
                 grad_norm = fsdp2_clip_grad_norm_(self.model.parameters(), args.max_grad_norm)
                 for g in self.optimizer.param_groups:
                     g["lr"] = g["initial_lr"] * self.lr_factor

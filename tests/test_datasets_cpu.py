@@ -1,0 +1,157 @@
+"""Data plane on CPU: packers, processors, map-style and iterable datasets, collators."""
+import json
+import os
+import random
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+@pytest.mark.parametrize("name", ["first_fit", "best_fit", "balanced", "true_first_fit"])
+def test_online_packers_lose_nothing_and_respect_budget(name):
+    from lmms_engine_b200.datasets.packing import build_online_packer
+
+    rng = random.Random(1)
+    packer = build_online_packer(name, 2048)
+    lens = [rng.randint(1, 2048) for _ in range(2000)]
+    seen = []
+    for i, n in enumerate(lens):
+        for pack in packer.add((i, n), n):
+            assert sum(x[1] for x in pack) <= 2048
+            seen += [x[0] for x in pack]
+    for pack in packer.flush():
+        assert sum(x[1] for x in pack) <= 2048
+        seen += [x[0] for x in pack]
+    assert sorted(seen) == list(range(2000))
+
+
+def test_first_fit_is_next_fit_like_the_reference():
+    from lmms_engine_b200.datasets.packing import FirstFitPacking, pack_by_first_fit, pack_by_window
+
+    p = FirstFitPacking(10)
+    out = []
+    for i, n in enumerate([6, 3, 4, 5, 5, 1]):
+        out += list(p.add(i, n))
+    out += list(p.flush())
+    assert out == [[0, 1], [2, 3], [4, 5]]  # the open pack is never revisited
+    assert pack_by_first_fit([6, 3, 4, 5, 5, 1], 10) == [[0, 1], [2, 3], [4, 5]]
+    groups = pack_by_window([6, 3, 4, 5, 5, 1], 10, 6)
+    assert sorted(i for g in groups for i in g) == list(range(6))
+    assert all(sum([6, 3, 4, 5, 5, 1][i] for i in g) <= 10 for g in groups)
+
+
+def test_best_fit_packs_tighter_than_next_fit():
+    from lmms_engine_b200.datasets.packing import build_online_packer
+
+    rng = random.Random(3)
+    lens = [rng.randint(100, 1500) for _ in range(3000)]
+
+    def n_packs(name):
+        p = build_online_packer(name, 4096)
+        k = 0
+        for i, n in enumerate(lens):
+            k += len(list(p.add(i, n)))
+        return k + len(list(p.flush()))
+
+    assert n_packs("best_fit") <= n_packs("first_fit")
+    assert n_packs("balanced") <= n_packs("first_fit")
+
+
+def _write_records(path, n=40):
+    recs = []
+    for i in range(n):
+        recs.append({"id": i, "messages": [
+            {"role": "user", "content": [{"type": "text", "text": "question " * (1 + i % 7)}]},
+            {"role": "assistant", "content": [{"type": "text", "text": f"answer {i}"}]}]})
+    with open(path, "w") as f:
+        for r in recs:
+            f.write(json.dumps(r) + "\n")
+    return recs
+
+
+def test_labels_supervise_assistant_only(tmp_path):
+    from lmms_engine_b200.datasets.config import ProcessorConfig
+    from lmms_engine_b200.datasets.processor import ChatProcessor
+
+    p = ChatProcessor(ProcessorConfig(processor_name="byte", processor_type="qwen2")).build()
+    out = p.process([{"role": "user", "content": [{"type": "text", "text": "hi"}]},
+                     {"role": "assistant", "content": [{"type": "text", "text": "hello"}]}])
+    sup = out["input_ids"][out["labels"] != -100]
+    assert p.tokenizer.decode(sup) == "hello<|im_end|>\n"
+    assert (out["labels"][out["labels"] != -100] == sup).all()
+
+
+def test_iterable_dataset_packs_shards_and_resumes(tmp_path):
+    from lmms_engine_b200.datasets.config import DatasetConfig
+    from lmms_engine_b200.datasets import registry  # noqa: F401
+    from lmms_engine_b200.mapping_func import DATASET_MAPPING
+
+    path = tmp_path / "d.jsonl"
+    _write_records(path)
+    cfg = DatasetConfig(dataset_type="vision_iterable", dataset_format="jsonl", dataset_path=str(path),
+                        processor_config={"processor_name": "byte", "processor_type": "qwen2"}, packing=True,
+                        packing_strategy="first_fit", packing_length=512, shuffle=True, data_seed=3)
+    ds = DATASET_MAPPING["vision_iterable"](cfg).build()
+    packs = list(ds)
+    assert sum(len(p) for p in packs) == 40
+    assert all(sum(s["input_ids"].numel() for s in p) <= 512 for p in packs)
+    # resume after two packs reproduces the tail exactly
+    ds2 = DATASET_MAPPING["vision_iterable"](cfg).build()
+    it = iter(ds2)
+    next(it); next(it)
+    state = ds2.state_dict()
+    ds3 = DATASET_MAPPING["vision_iterable"](cfg).build()
+    ds3.load_state_dict(state)
+    tail = list(ds3)
+    assert [[s["input_ids"].tolist() for s in p] for p in tail] == [[s["input_ids"].tolist() for s in p] for p in packs[2:]]
+    batch = ds.get_collator()([packs[0]])
+    assert batch["input_ids"].dim() == 1 and batch["cu_seqlens"][-1] == batch["input_ids"].numel()
+    assert batch["position_ids"][batch["cu_seqlens"][1]] == 0
+
+
+def test_map_dataset_offline_packing_and_padded_collator(tmp_path):
+    from lmms_engine_b200.datasets.config import DatasetConfig
+    from lmms_engine_b200.datasets import registry  # noqa: F401
+    from lmms_engine_b200.mapping_func import DATASET_MAPPING
+
+    path = tmp_path / "d.jsonl"
+    _write_records(path)
+    cfg = DatasetConfig(dataset_type="vision", dataset_format="jsonl", dataset_path=str(path),
+                        processor_config={"processor_name": "byte", "processor_type": "qwen2"}, packing=True,
+                        packing_strategy="window_8", packing_length=64, extra_kwargs={"collator_type": "vision"})
+    ds = DATASET_MAPPING["vision"](cfg).build()
+    assert sorted(i for g in ds.groups for i in g) == list(range(40))
+    assert len(ds.modality_length) == len(ds) and all(n < 0 for n in ds.modality_length)
+    batch = ds.get_collator()([ds[0]])
+    assert batch["input_ids"].dim() == 2 and batch["attention_mask"].shape == batch["input_ids"].shape
+    assert (batch["labels"][batch["attention_mask"] == 0] == -100).all()
+
+
+def test_vl_processor_counts_and_patch_order():
+    from lmms_engine_b200.datasets.config import ProcessorConfig
+    from lmms_engine_b200.datasets.processor import QwenVLProcessor
+    from lmms_engine_b200.datasets.processor import vision_process as vp
+
+    assert vp.smart_resize(100, 150, 28) == (112, 140)
+    h, w = vp.smart_resize(4000, 3000, 28, max_pixels=1280 * 28 * 28)
+    assert h % 28 == 0 and w % 28 == 0 and h * w <= 1280 * 28 * 28
+    p = QwenVLProcessor(ProcessorConfig(processor_name="byte", processor_type="qwen2_5_vl")).build()
+    img = (np.random.rand(100, 150, 3) * 255).astype(np.uint8)
+    out = p.process([{"role": "user", "content": [{"type": "image", "image": "x"}, {"type": "text", "text": "?"}]},
+                     {"role": "assistant", "content": [{"type": "text", "text": "ok"}]}], images=[img])
+    t, gh, gw = out["image_grid_thw"][0].tolist()
+    assert (out["input_ids"] == p.image_token_id).sum().item() == t * gh * gw // 4
+    assert out["pixel_values"].shape == (t * gh * gw, 3 * 2 * 14 * 14)
+    assert out["position_ids"].shape == (3, out["input_ids"].numel())
+    # first patch row = top-left 14x14 patch, channel-major, both temporal copies
+    arr = np.asarray(__import__("PIL.Image", fromlist=["Image"]).fromarray(img).resize((140, 112), 3)).astype(np.float32) / 255
+    ref = ((arr[:14, :14] - np.array(vp.CLIP_MEAN)) / np.array(vp.CLIP_STD)).transpose(2, 0, 1)
+    got = out["pixel_values"][0].view(3, 2, 14, 14)
+    assert torch.allclose(got[:, 0], torch.from_numpy(ref).float(), atol=1e-5)
+    # second row of the stream is the patch to the right inside the same 2x2 block
+    ref2 = ((arr[:14, 14:28] - np.array(vp.CLIP_MEAN)) / np.array(vp.CLIP_STD)).transpose(2, 0, 1)
+    assert torch.allclose(out["pixel_values"][1].view(3, 2, 14, 14)[:, 0], torch.from_numpy(ref2).float(), atol=1e-5)
