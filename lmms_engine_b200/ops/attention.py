@@ -9,6 +9,7 @@ runs a per-document fp32 reference (also the oracle of the GPU tests).
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -17,6 +18,11 @@ from . import _cuda
 
 _cuda.register("b200_attn_fwd", "attention_sm100", "ppppppp" + "iiiiii" + "llll" + "fii" + "ps")
 _cuda.register("b200_attn_bwd", "attention_sm100", "ppppppppppppp" + "iiiiii" + "llllllll" + "fii" + "ps")
+_cuda.register("b200_attn_bwd_v2", "attention_bwd_sm100", "pppppppppppp" + "iiiiii" + "llllllll" + "fii" + "ps")
+
+# "split": dK/dV and dQ in two reduction-free kernels (default); "fused": the single-kernel
+# variant that reduces dQ across key blocks with fp32 red.global
+BACKWARD_IMPL = os.environ.get("LMMS_B200_ATTN_BWD", "split")
 
 
 def varlen_attn_ref(q, k, v, cu_q, cu_k, causal=True, softmax_scale=None, window_left: int = -1):
@@ -83,8 +89,18 @@ class _VarlenAttnFn(torch.autograd.Function):
         dk = torch.empty((Tk, Hkv, D), dtype=q.dtype, device=q.device)
         dv = torch.empty((Tk, Hkv, D), dtype=q.dtype, device=q.device)
         delta = torch.empty((Hq, Tq), dtype=torch.float32, device=q.device)
-        dq_acc = torch.empty((Tq, Hq, D), dtype=torch.float32, device=q.device)
         st = _cuda.status_word(q.device)
+        if BACKWARD_IMPL == "split":
+            # two reduction-free kernels (dK/dV per key block, dQ per query block)
+            _cuda.call(
+                "b200_attn_bwd_v2", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(),
+                lse.data_ptr(), delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), cu_q.data_ptr(),
+                cu_k.data_ptr(), cu_q.numel() - 1, Tq, Tk, Hq, Hkv, D, q.stride(0), k.stride(0), v.stride(0),
+                o.stride(0), do.stride(0), dq.stride(0), dk.stride(0), dv.stride(0), float(scale), int(causal),
+                int(window_left), st.data_ptr(), _cuda.stream(),
+            )
+            return dq, dk, dv, None, None, None, None, None
+        dq_acc = torch.empty((Tq, Hq, D), dtype=torch.float32, device=q.device)
         _cuda.call(
             "b200_attn_bwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
             delta.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), cu_q.data_ptr(),

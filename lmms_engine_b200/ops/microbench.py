@@ -84,8 +84,50 @@ def main():
                      "lib_tflops": fl / t2 / 1e9})
         print(rows[-1], flush=True)
         del a, b
+    if args.only and args.only != "attn":
+        _cuda.check_status()
+        return
+    if args.only in (None, "attn"):
+        from . import attention
+
+        for lens in ([8192, 8192], [4096] * 4, [1024] * 16):
+            Tq = sum(lens)
+            cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+            q = rnd(Tq, 28, 128).requires_grad_(); k = rnd(Tq, 4, 128).requires_grad_(); v = rnd(Tq, 4, 128).requires_grad_()
+            fwd = lambda: attention.varlen_attn(q, k, v, cu, cu, causal=True)
+            t_f = timeit(fwd, iters=args.iters, flush=flush)
+            o = fwd(); do = torch.randn_like(o)
+            res = {"op": f"attn causal 28q/4kv d128 docs {len(lens)}x{lens[0]}", "fwd_ms": t_f}
+            fl = sum(4.0 * l * l * 128 * 28 / 2 for l in lens)
+            res["fwd_tflops"] = fl / t_f / 1e9
+            for impl in ("split", "fused"):
+                attention.BACKWARD_IMPL = impl
+                def bwd():
+                    o2 = attention.varlen_attn(q, k, v, cu, cu, causal=True)
+                    o2.backward(do)
+                t_fb = timeit(bwd, iters=args.iters, flush=flush)
+                res[f"bwd_{impl}_ms"] = t_fb - t_f
+                res[f"bwd_{impl}_tflops"] = 2.5 * fl / max(t_fb - t_f, 1e-6) / 1e9
+            attention.BACKWARD_IMPL = "split"
+            try:
+                from flash_attn import flash_attn_varlen_func
+                mx = max(lens)
+                lib_f = lambda: flash_attn_varlen_func(q, k, v, cu, cu, mx, mx, causal=True)
+                t_lf = timeit(lib_f, iters=args.iters, flush=flush)
+                def lib_b():
+                    flash_attn_varlen_func(q, k, v, cu, cu, mx, mx, causal=True).backward(do)
+                t_lfb = timeit(lib_b, iters=args.iters, flush=flush)
+                res.update({"lib_fwd_ms": t_lf, "lib_bwd_ms": t_lfb - t_lf})
+            except Exception as e:
+                res["lib"] = f"unavailable: {type(e).__name__}"
+            rows.append(res)
+            print(res, flush=True)
     if args.only:
         _cuda.check_status()
+        if args.json:
+            os.makedirs(os.path.dirname(args.json) or ".", exist_ok=True)
+            with open(args.json, "w") as f:
+                json.dump(rows, f, indent=1)
         return
     # fused SwiGLU GEMM vs cuBLAS x2 + elementwise
     x, wg, wu = rnd(T, 3584), rnd(18944, 3584), rnd(18944, 3584)
