@@ -35,6 +35,9 @@ class SyntheticPackedDataset(IterableDataset):
         self.fill_exact = bool(kw.get("fill_exact", False))
         self.pattern = kw.get("pattern", "uniform")  # "uniform" | "periodic" (learnable)
         self.interleave_ranks = int(kw.get("interleave_ranks", 0) or 0)
+        self.prompt_len = int(kw.get("prompt_len", 0) or 0)
+        self.collator_type = kw.get("collator_type", "packed")
+        self.mask_token_id = int(kw.get("mask_token_id", self.vocab - 1))
         self.packing_length = int(config.packing_length or 1024)
         self.strategy = config.packing_strategy or "first_fit"
         self.packing_kwargs = dict(kw.get("packing_kwargs", {}) or {})
@@ -56,6 +59,10 @@ class SyntheticPackedDataset(IterableDataset):
         return self
 
     def get_collator(self):
+        if self.collator_type == "dllm":
+            from .collator.text_dllm_collator import TextDllmCollator
+
+            return TextDllmCollator(self.mask_token_id, seed=self.seed)
         return PackedCollator()
 
     def state_dict(self) -> Dict[str, Any]:
@@ -75,7 +82,10 @@ class SyntheticPackedDataset(IterableDataset):
             ids = torch.from_numpy(np.resize(motif, n))
         else:
             ids = torch.from_numpy(rng.integers(0, self.vocab, size=n, dtype=np.int64))
-        return {"input_ids": ids, "labels": ids.clone()}
+        labels = ids.clone()
+        if self.prompt_len:
+            labels[: self.prompt_len] = -100  # an unsupervised prompt prefix (RL / SFT style records)
+        return {"input_ids": ids, "labels": labels}
 
     def __iter__(self) -> Iterator[List[Dict[str, torch.Tensor]]]:
         if self.interleave_ranks > 1:
@@ -123,3 +133,63 @@ class SyntheticPackedDataset(IterableDataset):
                 yield pack
         elif buf:
             yield buf
+
+
+class StackCollator:
+    """Stacks same-shaped tensors of a list of samples on a new leading dimension."""
+
+    def __call__(self, batch):
+        out = {}
+        for k in batch[0]:
+            vals = [b[k] for b in batch]
+            out[k] = torch.stack(vals) if torch.is_tensor(vals[0]) else vals
+        return out
+
+
+@register_dataset("synthetic_tensors")
+class SyntheticTensorDataset(IterableDataset):
+    """Random tensors by spec, for the image / video / latent trainers:
+    ``extra_kwargs.spec = {name: {shape: [...], kind: randn|randint|rand, high: int}}``."""
+
+    def __init__(self, config):
+        self.config = config
+        self.spec = dict((config.extra_kwargs or {}).get("spec", {}))
+        self.seed = int(config.data_seed or 0)
+        self.cur_idx = 0
+        self.processor = None
+        self.dp_rank = 0
+
+    def build(self):
+        try:
+            from ..parallel import process_group_manager as pgm
+
+            if pgm.process_group_manager is not None:
+                self.dp_rank = pgm.process_group_manager.dp_rank
+        except Exception:
+            pass
+        return self
+
+    def get_collator(self):
+        return StackCollator()
+
+    def state_dict(self):
+        return {"cur_idx": self.cur_idx}
+
+    def load_state_dict(self, sd):
+        self.cur_idx = int(sd.get("cur_idx", 0))
+
+    def __iter__(self):
+        while True:
+            g = torch.Generator().manual_seed(hash((self.seed, self.dp_rank, self.cur_idx)) % (2 ** 31))
+            self.cur_idx += 1
+            item = {}
+            for name, sp in self.spec.items():
+                shape = tuple(sp.get("shape", ()))
+                kind = sp.get("kind", "randn")
+                if kind == "randint":
+                    item[name] = torch.randint(0, int(sp.get("high", 2)), shape, generator=g)
+                elif kind == "rand":
+                    item[name] = torch.rand(shape, generator=g)
+                else:
+                    item[name] = torch.randn(shape, generator=g)
+            yield item

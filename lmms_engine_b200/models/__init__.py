@@ -16,4 +16,16 @@ from .vl import VLConfig, VLModel
 for _mt in ("qwen2_5_vl", "qwen2_vl", "qwen3_vl", "qwen3_vl_moe"):
     register_model(_mt, VLConfig, VLModel, "image_text_to_text")
 
-__all__ = ["ModelConfig", "DecoderConfig", "DecoderLM", "MoEConfig", "MoEDecoderLM", "VLConfig", "VLModel"]
+from .bagel import Bagel, BagelConfig
+from .diffusion import RaeAutoencoder, RaeConfig, SiT, SiTConfig, WanConfig, WanDiT
+from .dllm import DiffusionLM, DLLMConfig
+
+for _mt in ("qwen3_dllm", "dream_dllm", "llada_dllm"):
+    register_model(_mt, DLLMConfig, DiffusionLM, "masked_lm")
+register_model("sit", SiTConfig, SiT, "general")
+register_model("wanvideo", WanConfig, WanDiT, "general")
+register_model("rae_siglip", RaeConfig, RaeAutoencoder, "general")
+register_model("bagel", BagelConfig, Bagel, "general")
+
+__all__ = ["ModelConfig", "DecoderConfig", "DecoderLM", "MoEConfig", "MoEDecoderLM", "VLConfig", "VLModel", "DLLMConfig",
+           "DiffusionLM", "SiT", "SiTConfig", "WanDiT", "WanConfig", "RaeAutoencoder", "RaeConfig", "Bagel", "BagelConfig"]

@@ -318,6 +318,7 @@ class DecoderLM(nn.Module):
         self.sp_group = None  # set by the trainer when Ulysses is on
         self.tp_group = None  # set by the tensor-parallel plan
         self.causal = True
+        self.shift_labels = True
         self.loss_reduction = "mean"
         self.apply(self._init_weights)
 
@@ -383,7 +384,12 @@ class DecoderLM(nn.Module):
         T_full = pos.shape[-1]
         if max_seqlen is None:
             max_seqlen = T_full  # an upper bound is enough: the kernels schedule from cu_seqlens
-        shifted = shift_labels_per_document(labels, cu) if labels is not None else None
+        if labels is None:
+            shifted = None
+        elif self.shift_labels:
+            shifted = shift_labels_per_document(labels, cu)
+        else:  # targets already aligned with their positions (masked-token objectives)
+            shifted = labels
         cos, sin = self.model.rope_tables(pos)
         sp_group, tp_group = self.sp_group, self.tp_group
         sp_size, tp_size = sp.group_size(sp_group), sp.group_size(tp_group)

@@ -295,7 +295,10 @@ class FSDP2SFTTrainer:
             return (cu[1:] - cu[:-1]).tolist()
         if "attention_mask" in batch:
             return batch["attention_mask"].sum(-1).tolist()
-        return [int(batch["input_ids"].numel())]
+        if "input_ids" in batch:
+            return [int(batch["input_ids"].numel())]
+        first = next((v for v in batch.values() if torch.is_tensor(v)), None)
+        return [int(first.shape[0])] if first is not None else [0]
 
     def calculate_training_metrics(self, seqlens: List[int], step_seconds: float) -> Dict[str, Any]:
         ntok = float(sum(seqlens))
@@ -323,6 +326,10 @@ class FSDP2SFTTrainer:
             "train/tokens_per_second": total / max(step_seconds, 1e-9),
             "train/tokens_per_gpu": total / max(step_seconds, 1e-9) / self.world_size,
         }
+
+    def extra_metrics(self) -> Dict[str, Any]:
+        """Trainer-specific values merged into every logged step."""
+        return {}
 
     # ------------------------------------------------------------------ checkpoints
     def _full_model_state(self) -> Dict[str, torch.Tensor]:
@@ -542,6 +549,7 @@ class FSDP2SFTTrainer:
                                "train/grad_norm": float(grad_norm) if grad_norm is not None else 0.0}
                     if self.enable_perf_metrics:
                         metrics.update(self.calculate_training_metrics(seqlens_acc, step_s))
+                    metrics.update(self.extra_metrics())
                     metrics["train/step_time"] = step_s
                     metrics["train/epoch"] = epoch + (micro / ga) / spe if spe else 0.0
                     ev_prof.stop("training_metrics")

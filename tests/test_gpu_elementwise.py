@@ -255,3 +255,19 @@ def test_fused_linear_cross_entropy(reduction):
     for a, b in ((h.grad, hr.grad), (w.grad, wr.grad)):
         err = (a.float() - b).abs().max() / (b.abs().max() + 1e-9)
         assert err < 3e-2, err
+
+
+def test_plucker_rays_match_reference_formulation():
+    from lmms_engine_b200.ops import camera
+
+    B, V, H, W = 2, 5, 48, 84
+    K = torch.tensor([400.0, 420.0, W / 2, H / 2], device="cuda").repeat(B, V, 1) * (1 + 0.1 * torch.rand(B, V, 4, device="cuda"))
+    rot = torch.linalg.qr(torch.randn(B, V, 3, 3, device="cuda")).Q
+    c2w = torch.eye(4, device="cuda").repeat(B, V, 1, 1)
+    c2w[..., :3, :3] = rot
+    c2w[..., :3, 3] = torch.randn(B, V, 3, device="cuda")
+    out = camera.plucker_rays(K, c2w, H, W)
+    ref = camera.plucker_rays_ref(K.cpu(), c2w.cpu(), H, W)
+    assert torch.allclose(out.cpu(), ref, atol=1e-4, rtol=1e-4)
+    cf = camera.plucker_rays(K, c2w, H, W, channels_first=True)
+    assert torch.equal(cf, out.permute(0, 1, 4, 2, 3))
