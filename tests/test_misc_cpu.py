@@ -1,0 +1,150 @@
+"""Small host-side components: LPT planner, eval backend with a fake client, CUDA-event
+profiler with fake events, schedulers, FLOPs counter, override grammar, merger consolidation."""
+import json
+import os
+import sys
+import time
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def test_lpt_planner_balances_and_prefers_home():
+    from lmms_engine_b200.parallel.vit_parallel import lpt_balance, plan_frame_exchange
+
+    owner, load = lpt_balance([100, 100, 100, 100], [0, 0, 0, 0], 2)
+    assert sorted(load) == [200, 200]
+    owner2, _ = lpt_balance([10, 10, 10, 10], [0, 1, 2, 3], 4)
+    assert owner2 == [0, 1, 2, 3]  # already balanced: nothing moves
+    frames = [[1024] * 6, [1024], [], [256, 256]]
+    own, send, load = plan_frame_exchange(frames)
+    assert sum(load) == sum(sum(f) for f in frames) and max(load) - min(load) <= 1024
+    assert plan_frame_exchange(frames) == (own, send, load)  # deterministic
+
+
+def test_eval_backend_with_fake_server():
+    from lmms_engine_b200.eval.backends import EvalServerBackend
+
+    class FakeClient:
+        def __init__(self):
+            self.n = 0
+            self.payloads = []
+
+        def submit(self, payload):
+            self.payloads.append(payload)
+            self.n += 1
+            return f"job{self.n}"
+
+        def status(self, job):
+            if job == "job1":
+                return {"status": "completed", "result": {"results": {"mmmu_val": {"acc,none": 0.41, "acc_stderr,none": 0.01}}}}
+            return {"status": "failed", "error": "boom"}
+
+    fake = FakeClient()
+    be = EvalServerBackend({"server_url": "http://x", "poll_interval": 0.05, "tasks": ["mmmu_val"], "checkpoint_key": "pretrained",
+                            "model_args": {"tensor_parallel_size": 1}}, client=fake)
+    be.submit("/ckpt/checkpoint-10", 10)
+    be.submit("/ckpt/checkpoint-20", 20)
+    assert fake.payloads[0]["model_args"]["pretrained"] == "/ckpt/checkpoint-10"
+    deadline = time.time() + 5
+    results = []
+    while time.time() < deadline and be.pending():
+        time.sleep(0.05)
+    results = list(be.poll_results())
+    be.close()
+    assert results == [(10, {"eval/mmmu_val_acc": 0.41})]  # the failed job is dropped, not raised
+
+
+def test_cuda_event_profiler_with_fake_events(tmp_path, monkeypatch):
+    from lmms_engine_b200.utils import profiler as prof
+
+    class FakeEvent:
+        clock = 0.0
+
+        def __init__(self, enable_timing=True):
+            self.t = None
+
+        def record(self):
+            FakeEvent.clock += 1.5
+            self.t = FakeEvent.clock
+
+        def query(self):
+            return True
+
+        def synchronize(self):
+            pass
+
+        def elapsed_time(self, other):
+            return other.t - self.t
+
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: True)
+    monkeypatch.setattr(torch.cuda, "Event", FakeEvent)
+    p = prof.CudaEventProfiler(True, str(tmp_path), {"start_step": 1, "end_step": 6, "stride": 2, "ranks": [0]}, rank=0)
+    for step in range(8):
+        p.set_step(step)
+        p.start("training_step")
+        p.stop("training_step")
+        p.flush()
+    p.close()
+    lines = [json.loads(l) for l in open(tmp_path / "cuda_event_profiler" / "cuda_events_rank_0.jsonl")]
+    assert [l["step"] for l in lines] == [1, 3, 5] and all(l["ms"] == 1.5 for l in lines)
+    off = prof.CudaEventProfiler(True, str(tmp_path), {"ranks": [1]}, rank=0)
+    assert not off.enable
+
+
+def test_schedules():
+    from lmms_engine_b200.utils.schedulers import lr_factor
+
+    assert lr_factor("cosine", 0, 10, 100) == 0.0 and lr_factor("cosine", 10, 10, 100) == 1.0
+    assert abs(lr_factor("cosine", 100, 10, 100, min_lr_ratio=0.1) - 0.1) < 1e-9
+    assert lr_factor("wsd", 50, 10, 100, stable_ratio=0.9) == 1.0
+    assert lr_factor("wsd", 100, 10, 100, stable_ratio=0.9, min_lr_ratio=0.2) == pytest.approx(0.2)
+    assert lr_factor("constant", 0, 10, 100) == pytest.approx(0.01) and lr_factor("constant", 10, 10, 100) == 1.0
+
+
+def test_flops_formula_matches_reference_definition():
+    from lmms_engine_b200.models.utils import FlopsCounter
+
+    cfg = dict(hidden_size=3584, intermediate_size=18944, num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4,
+               head_dim=128, vocab_size=152064)
+    fc = FlopsCounter(cfg)
+    dense = 28 * (3584 * 18944 * 3 + 3584 * (3584 + 512 + 512 + 3584)) + 2 * 152064 * 3584
+    assert fc.dense_params() == dense
+    seq = [4096, 8192, 4096]
+    assert fc.flops_per_step(seq) == 6.0 * dense * 16384 + 12.0 * sum(s * s for s in seq) * 128 * 28 * 28
+
+
+def test_override_grammar(tmp_path):
+    from lmms_engine_b200.launch import cli
+
+    y = tmp_path / "c.yaml"
+    y.write_text("trainer_type: hf_trainer\ntrainer_args:\n  output_dir: /tmp/x\n  max_steps: 5\n")
+    cfg = cli.build_config([f"config_yaml={y}", "hydra.output_subdir=null", "hydra/job_logging=disabled"])
+    assert cfg["trainer_type"] == "hf_trainer" and cfg["trainer_args"] == {"output_dir": "/tmp/x", "max_steps": 5}
+    cfg = cli.build_config(["trainer_args.learning_rate=3e-4", "+trainer_args.custom=[1,2]", "~trainer_args.run_name",
+                            "dataset_config.packing=true"])
+    assert cfg["trainer_args"]["learning_rate"] == pytest.approx(3e-4) and cfg["trainer_args"]["custom"] == [1, 2]
+    assert "run_name" not in cfg["trainer_args"] and cfg["dataset_config"]["packing"] is True
+    d = tmp_path / "conf"
+    d.mkdir()
+    (d / "mine.yaml").write_text("trainer_type: sit_trainer\n")
+    assert cli.build_config(["--config-path", str(d), "--config-name", "mine"])["trainer_type"] == "sit_trainer"
+
+
+def test_consolidate_multi_axis_and_uneven():
+    from lmms_engine_b200.merger.consolidate import fold_axis
+
+    full = torch.arange(7 * 4.0).view(7, 4)
+    # uneven Shard(0) over 4 ranks: chunks of 2,2,2,1
+    pieces = list(torch.chunk(full, 4, 0))
+    assert torch.equal(fold_axis(pieces, ("S", 0)), full)
+    # 2-D mesh (2 x 2): outer Shard(0), inner Shard(1)
+    outer = torch.chunk(full, 2, 0)
+    grid = [list(torch.chunk(o, 2, 1)) for o in outer]
+    rows = [fold_axis(g, ("S", 1)) for g in grid]
+    assert torch.equal(fold_axis(rows, ("S", 0)), full)
+    # replicate axis takes one copy; zero-size shard on an axis is skipped
+    assert torch.equal(fold_axis([full, full], ("R",)), full)
+    assert torch.equal(fold_axis([full, full.new_empty((0, 4))], ("S", 0)), full)
