@@ -74,20 +74,48 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait.  `abort_word` lives in shared memory and is raised by whichever
 // role first runs out of budget; everybody else sees it within 64 polls.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word,
+                                          long long limit = kWaitCycleLimit) {
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = clock64();
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 63u) == 0u) {
       if (*abort_word) return false;
-      if (clock64() - t0 > kWaitCycleLimit) {
+      if (clock64() - t0 > limit) {
         *abort_word = 1;
         return false;
       }
     }
   }
 }
+
+// ---------------------------------------------------------------- cross-GPU flags (peer-mapped memory)
+// Counters only grow; a waiter compares with wrap-around arithmetic.  Bounded like every wait here.
+__device__ __forceinline__ bool flag_wait_ge(const uint32_t* flag, uint32_t target, long long limit,
+                                             volatile int* abort_word) {
+  const long long t0 = clock64();
+  for (uint32_t i = 1;; ++i) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (static_cast<int>(v - target) >= 0) return true;
+    if ((i & 15u) == 0u) {
+      if (*abort_word) return false;
+      if (clock64() - t0 > limit) {
+        *abort_word = 1;
+        return false;
+      }
+    }
+    __nanosleep(64);
+  }
+}
+__device__ __forceinline__ void flag_add_release(uint32_t* flag, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(flag), "r"(v) : "memory");
+}
+__device__ __forceinline__ void bar_sync_named(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 // ---------------------------------------------------------------- TMA (never multicast)
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {

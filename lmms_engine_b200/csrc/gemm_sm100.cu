@@ -71,6 +71,56 @@ struct GemmParams {
   int* status;
 };
 
+// Collective work fused into one GEMM launch over peer-mapped buffers (plain peer stores and
+// system-scope flags; no multicast).  Three independent parts, each optional:
+//  push    : before its tiles, every CTA copies a slice of a local block into every rank's buffer
+//            (all-gather of rows, or the sequence<->head all-to-all) and raises arrive_in there;
+//  wait    : the TMA producer waits for arrive_in of the rank whose rows (mode 1) or k-range
+//            (mode 2) a tile reads, so tiles of blocks that have already landed run first;
+//  scatter : the epilogue stores each tile into the destination rank's buffer instead of C:
+//            mode 1 = row blocks into per-source slots that the destination sums at the end of
+//            the same kernel (reduce-scatter), mode 2 = 64-column chunks routed by a table
+//            (all-to-all by heads).  arrive_out counts finished source CTAs.
+// Flag block of a buffer on every rank: u32 [3][kMaxRanks] = arrive_in | arrive_out | done.
+constexpr int kMaxRanks = 8;
+constexpr int kMaxPushSeg = 3;
+struct CommParams {
+  int rank, world;
+  long long wait_cycles;
+  // push
+  int push, push_rows, push_nseg;
+  // the block is made of up to three column segments, each with its own source matrix; the rows for
+  // destination r start at row r * push_block_rows of every source (0: the same rows go to all ranks)
+  const __nv_bfloat16* seg_src[kMaxPushSeg];
+  long long seg_src_ld[kMaxPushSeg];
+  long long push_block_rows;
+  long long push_dst_ld, push_dst_off;     // element offset of this rank's block inside a destination buffer
+  int seg_dst_col[kMaxPushSeg], seg_cols[kMaxPushSeg];
+  __nv_bfloat16* push_dst[kMaxRanks];
+  uint32_t* pflags[kMaxRanks];
+  uint32_t in_target;
+  // handshake of a shared gather buffer: a CTA that starts raises done on every rank (whatever read
+  // this rank's buffer earlier in the stream has finished) and writes to rank r only once all CTAs
+  // of r have started too
+  int push_done_wait;
+  uint32_t push_done_target;
+  // wait
+  int wait_mode, rows_per_src, k_per_src, m_rot, k_rot;
+  const int* kb_src;                       // mode 2: source rank of every 64-wide k-block (null: k / k_per_src)
+  // scatter
+  int scatter;
+  long long sc_ld, sc_slot_stride;
+  const int* chunk_dst;
+  const int* chunk_col;
+  const int* chunk_ndst;
+  int sc_row_off;
+  __nv_bfloat16* sc_dst[kMaxRanks];
+  uint32_t* sflags[kMaxRanks];
+  uint32_t out_target, sc_done_target;
+  __nv_bfloat16* reduce_out;
+  long long reduce_ld;
+};
+
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
 // Map a linear tile index to (m_block, n_block).  Sixteen m-blocks share each sweep
@@ -86,12 +136,15 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   nb = r / gsz;
 }
 
-template <int EPI>
+template <int EPI, int COMM>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmC,
                  const __grid_constant__ CUtensorMap tmC2, const __grid_constant__ CUtensorMap tmC3,
-                 const GemmParams p) {
+                 const GemmParams p, const __grid_constant__ CommParams cp) {
+  // a fused collective may have to wait for a rank that was launched later: its waits use the
+  // caller's limit, every other launch keeps the short default
+  const long long wait_limit = COMM ? cp.wait_cycles : kWaitCycleLimit;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_smem = smem + kStages * kStageBytes;
@@ -148,6 +201,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       kb_n = (r1 - r0) / BK;
     } else {
       tile_coords(t, tiles_m, tiles_n, mb, nb);
+      if (COMM) {
+        // start with the row blocks whose data is local (gather) or whose destination is the
+        // farthest in the ring (reduce-scatter), so that transfers overlap the remaining tiles
+        mb += cp.m_rot;
+        if (mb >= tiles_m) mb -= tiles_m;
+      }
       e = p.tile_expert != nullptr ? p.tile_expert[mb] : 0;
       kb_lo = 0;
       kb_n = n_kb;
@@ -161,6 +220,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tma_prefetch_desc(&tmB);
       uint32_t it = 0;
       bool ok = true;
+      uint32_t landed = 0;  // COMM: sources whose block is known to have arrived
+      auto source_ready = [&](int src) -> bool {
+        if ((landed >> src) & 1u) return true;
+        if (!flag_wait_ge(cp.pflags[cp.rank] + src, cp.in_target, wait_limit, abort_word)) return false;
+        fence_proxy_async_all();  // the block was written by generic stores, TMA reads it next
+        landed |= 1u << src;
+        return true;
+      };
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         int ex, mb, nb, kb_lo, kb_n;
         decode(t, ex, mb, nb, kb_lo, kb_n);
@@ -168,14 +235,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int m0 = mb * BM;
         const int n0 = (EPI == EPI_SWIGLU) ? nb * (BN / 2) : nb * BN;
         const bool grouped_b = p.tile_expert != nullptr;  // B is a 3-D map indexed by expert
+        if (COMM && cp.wait_mode == 1 && !source_ready(m0 / cp.rows_per_src)) { ok = false; break; }
         for (int kb = 0; kb < kb_n; ++kb, ++it) {
+          int kbr = kb_lo + kb;
+          if (COMM) {
+            kbr += cp.k_rot;  // begin with the k-range that this rank contributed itself
+            if (kbr >= n_kb) kbr -= n_kb;
+            if (cp.wait_mode == 2 && !source_ready(cp.kb_src != nullptr ? cp.kb_src[kbr] : kbr * BK / cp.k_per_src)) { ok = false; break; }
+          }
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_word)) { ok = false; break; }
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_word, wait_limit)) { ok = false; break; }
           uint8_t* sa = smem + s * kStageBytes;
           uint8_t* sb = sa + kATileBytes;
           mbar_expect_tx(&full_bar[s], kStageBytes);
-          const int k0 = (kb_lo + kb) * BK;
+          const int k0 = kbr * BK;
           if (!p.a_mn_major) {
             tma_load_2d(sa, &tmA, &full_bar[s], k0, m0);
           } else if (p.a_mn3d) {
@@ -219,13 +293,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!tile_active(mb, nb)) continue;
         const int acc = tl & 1;
         const uint32_t acc_ph = (tl >> 1) & 1;
-        if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_word)) { ok = false; break; }
+        if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_word, wait_limit)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < kb_n; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
-          if (!mbar_wait(&full_bar[s], ph, abort_word)) { ok = false; break; }
+          if (!mbar_wait(&full_bar[s], ph, abort_word, wait_limit)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * kStageBytes);
           const uint32_t sb = sa + kATileBytes;
@@ -252,6 +326,59 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         ++tl;
       }
     }
+  } else if (COMM && warp < 4) {
+    // ------------------------------------------------------------ push (warps 2, 3)
+    if (cp.push) {
+      const int ct = (warp - 2) * 32 + lane;
+      bool okp = true;
+      if (cp.push_done_wait && warp == 2 && lane < cp.world) {
+        __threadfence_system();
+        flag_add_release(cp.pflags[lane] + 2 * kMaxRanks + cp.rank, 1u);
+      }
+      for (int d = 0; d < cp.world; ++d) {
+        // own copy first, then the ranks in the order in which they will need this block
+        const int r = (cp.rank - d + cp.world) % cp.world;
+        if (okp && cp.push_done_wait) {
+          int w = 1;
+          if (lane == 0) w = flag_wait_ge(cp.pflags[cp.rank] + 2 * kMaxRanks + r, cp.push_done_target, wait_limit, abort_word);
+          okp = __shfl_sync(0xffffffffu, w, 0) != 0;
+        }
+        if (okp) {
+          __nv_bfloat16* dst = cp.push_dst[r] + cp.push_dst_off;
+          for (int sg = 0; sg < cp.push_nseg; ++sg) {
+            const long long sld = cp.seg_src_ld[sg];
+            const int vpr = cp.seg_cols[sg] >> 3;  // 16-byte vectors per row
+            const long long total = static_cast<long long>(cp.push_rows) * vpr;
+            const long long per = (total + gridDim.x - 1) / gridDim.x;
+            const long long v_hi = min(total, per * (blockIdx.x + 1));
+            const __nv_bfloat16* s0 = cp.seg_src[sg] + r * cp.push_block_rows * sld;
+            __nv_bfloat16* d0 = dst + cp.seg_dst_col[sg];
+            for (long long v = per * blockIdx.x + ct; v < v_hi; v += 64 * 4) {
+              uint4 val[4];
+              long long dof[4];
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const long long vv = v + u * 64;
+                if (vv < v_hi) {
+                  const long long row = vv / vpr;
+                  const int c = static_cast<int>(vv - row * vpr) * 8;
+                  val[u] = *reinterpret_cast<const uint4*>(s0 + row * sld + c);
+                  dof[u] = row * cp.push_dst_ld + c;
+                }
+              }
+#pragma unroll
+              for (int u = 0; u < 4; ++u)
+                if (v + u * 64 < v_hi) *reinterpret_cast<uint4*>(d0 + dof[u]) = val[u];
+            }
+          }
+        }
+        bar_sync_named(1, 64);
+        if (warp == 2 && lane == 0 && okp) {
+          __threadfence_system();
+          flag_add_release(cp.pflags[r] + cp.rank, 1u);
+        }
+      }
+    }
   } else if (warp >= 4) {
     // ------------------------------------------------------------ epilogue (warps 4..7)
     const int q = warp - 4;  // TMEM lane quadrant == warp % 4
@@ -259,6 +386,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t tl = 0;
     int buf = 0;
     bool ok = true;
+    uint32_t sc_open = 0;  // COMM scatter: destinations known to have drained their slots
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       int ex, mb, nb, kb_lo, kb_n;
       decode(t, ex, mb, nb, kb_lo, kb_n);
@@ -266,7 +394,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const bool empty_k = (kb_n == 0);  // grouped-K expert without rows: the product is zero
       const int acc = tl & 1;
       const uint32_t acc_ph = (tl >> 1) & 1;
-      if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_word)) { ok = false; break; }
+      if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_word, wait_limit)) { ok = false; break; }
       tc_fence_after();
       const int m0 = mb * BM;
       const int row = m0 + q * 32 + lane;  // global row owned by this thread
@@ -363,15 +491,59 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               }
             }
           }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            if (p.group_k) tma_store_3d(&tmC, slab, n0 + c64 * 64, m0 + q * 32, ex);
-            else tma_store_2d(&tmC, slab, n0 + c64 * 64, m0 + q * 32);
-            tma_store_commit();
+          if (COMM && cp.scatter) {
+            // peer stores straight from the staged slab: 8 lanes cover one 128-byte row segment
+            __syncwarp();
+            const int r0 = m0 + q * 32;
+            const int ccol = n0 + c64 * 64;
+            int dst_lo, ndst, col_base;
+            long long row_base, slot_off;
+            if (cp.scatter == 1) {
+              dst_lo = r0 / cp.rows_per_src;
+              ndst = 1;
+              col_base = ccol;
+              row_base = r0 - static_cast<long long>(dst_lo) * cp.rows_per_src;
+              slot_off = cp.rank * cp.sc_slot_stride;
+              if (!((sc_open >> dst_lo) & 1u)) {
+                int w = 1;
+                if (lane == 0) w = flag_wait_ge(cp.sflags[cp.rank] + 2 * kMaxRanks + dst_lo, cp.sc_done_target, wait_limit, abort_word);
+                if (__shfl_sync(0xffffffffu, w, 0) == 0) { ok = false; break; }
+                sc_open |= 1u << dst_lo;
+              }
+            } else {
+              const int chunk = ccol >> 6;
+              const bool live = ccol < p.N;  // the last tile may hang over the end of the table
+              dst_lo = live ? cp.chunk_dst[chunk] : 0;
+              ndst = live ? cp.chunk_ndst[chunk] : 0;
+              col_base = live ? cp.chunk_col[chunk] : 0;
+              row_base = cp.sc_row_off + r0;
+              slot_off = 0;
+            }
+            for (int dd = 0; dd < ndst; ++dd) {
+              __nv_bfloat16* dbase = cp.sc_dst[dst_lo + dd] + slot_off + col_base;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int rr = i * 4 + (lane >> 3);
+                const int ch = lane & 7;
+                if (r0 + rr < p.M && ccol + ch * 8 < p.N) {
+                  const uint4 val = *reinterpret_cast<const uint4*>(slab + rr * 128 + ((ch ^ (rr & 7)) * 16));
+                  *reinterpret_cast<uint4*>(dbase + (row_base + rr) * cp.sc_ld + ch * 8) = val;
+                }
+              }
+            }
+            __syncwarp();
+          } else {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (p.group_k) tma_store_3d(&tmC, slab, n0 + c64 * 64, m0 + q * 32, ex);
+              else tma_store_2d(&tmC, slab, n0 + c64 * 64, m0 + q * 32);
+              tma_store_commit();
+            }
           }
           buf ^= 1;
         }
+        if (!ok) break;
         if (EPI == EPI_STATS && row < p.M) p.stats[static_cast<size_t>(row) * tiles_n + nb] = make_float2(run_max, run_sum);
       } else {  // EPI_SWIGLU: accumulator cols [0,128) = gate, [128,256) = up
         const int n0 = nb * (BN / 2);
@@ -430,11 +602,54 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       ++tl;
     }
     if (lane == 0) tma_store_wait_all<0>();
+    if (COMM && cp.scatter) {
+      // every tile of this CTA has been stored: tell all destinations
+      bar_sync_named(2, kEpiWarps * 32);
+      if (warp == 4 && lane < cp.world && !*abort_word) {
+        __threadfence_system();
+        flag_add_release(cp.sflags[lane] + kMaxRanks + cp.rank, 1u);
+      }
+    }
   }
 
   // ------------------------------------------------------------ teardown
   tc_fence_before();
   __syncthreads();
+  if (COMM) {
+    // wait for what the other ranks sent here, then finish the reduction on the local slots
+    if (static_cast<int>(threadIdx.x) < cp.world) {
+      if (cp.scatter) flag_wait_ge(cp.sflags[cp.rank] + kMaxRanks + threadIdx.x, cp.out_target, wait_limit, abort_word);
+      if (cp.push && cp.wait_mode == 0) flag_wait_ge(cp.pflags[cp.rank] + threadIdx.x, cp.in_target, wait_limit, abort_word);
+    }
+    __syncthreads();
+    if (cp.scatter == 1 && !*abort_word) {
+      const int vpr = p.N >> 3;
+      const long long total = static_cast<long long>(cp.rows_per_src) * vpr;
+      const long long per = (total + gridDim.x - 1) / gridDim.x;
+      const long long v_hi = min(total, per * (blockIdx.x + 1));
+      const __nv_bfloat16* slots = cp.sc_dst[cp.rank];
+      for (long long v = per * blockIdx.x + threadIdx.x; v < v_hi; v += kThreads) {
+        const long long row = v / vpr;
+        const int c = static_cast<int>(v - row * vpr) * 8;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int sr = 0; sr < cp.world; ++sr) {
+          const uint4 u = __ldcg(reinterpret_cast<const uint4*>(slots + sr * cp.sc_slot_stride + row * cp.sc_ld + c));
+          const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+          acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+          acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+        }
+        *reinterpret_cast<uint4*>(cp.reduce_out + row * cp.reduce_ld + c) =
+            make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                       pack_bf16x2(acc[6], acc[7]));
+      }
+    }
+    __syncthreads();
+    // this rank no longer reads its gather buffer / its slots: writers of the next call may proceed
+    if (static_cast<int>(threadIdx.x) < cp.world && !*abort_word) {
+      __threadfence_system();
+      if (cp.scatter == 1) flag_add_release(cp.sflags[threadIdx.x] + 2 * kMaxRanks + cp.rank, 1u);
+    }
+  }
   if (*abort_word) {
     // give copies still in flight time to land before shared memory is released
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
@@ -542,13 +757,13 @@ static int make_map_e3(CUtensorMap* m, const void* ptr, uint64_t E, uint64_t R, 
 
 static int g_num_sms = 0;
 
-template <int EPI>
+template <int EPI, int COMM = 0>
 static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const CUtensorMap& tC,
                   const CUtensorMap& tC2, const CUtensorMap& tC3, const GemmParams& p, int max_ctas,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, const CommParams* comm = nullptr, int* launched = nullptr) {
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<EPI, COMM>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return -3;
     attr_set = true;
   }
@@ -562,7 +777,16 @@ static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMa
   int tiles = p.n_tiles_m * p.n_tiles_n * (p.group_k ? p.n_experts : 1);
   if (tiles < ctas) ctas = tiles;
   if (ctas <= 0) return 0;
-  gemm_bf16_kernel<EPI><<<ctas, kThreads, kSmemBytes, stream>>>(tA, tB, tB2, tC, tC2, tC3, p);
+  CommParams cp{};
+  if (comm != nullptr) {
+    // arrival counters grow by one per CTA and call on every rank (all ranks launch the same grid)
+    cp = *comm;
+    cp.in_target += static_cast<uint32_t>(ctas);
+    cp.out_target += static_cast<uint32_t>(ctas);
+    cp.push_done_target += static_cast<uint32_t>(ctas);
+  }
+  if (launched != nullptr) *launched = ctas;
+  gemm_bf16_kernel<EPI, COMM><<<ctas, kThreads, kSmemBytes, stream>>>(tA, tB, tB2, tC, tC2, tC3, p, cp);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -612,6 +836,98 @@ int b200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, i
     return launch<EPI_SYMM>(tA, tB, tB, tC, tC, tC, p, max_ctas, stream);
   }
   return launch<EPI_PLAIN>(tA, tB, tB, tC, tC, tC, p, max_ctas, stream);
+}
+
+// GEMM with fused collective parts (see CommParams).  `ca` is a flat int64 record:
+//  [0] rank [1] world [2] wait limit in ms
+//  [3] push [4] k-block source table [6] rows between destination blocks [7] push_dst_ld [8] push_dst_off
+//  [9] push_rows [10] segments [11..13] source matrix [14..16] destination column [17..19] columns and
+//  [73..75] source row stride of each segment
+//  [20] arrive_in counter before this call [21] start handshake on the gather buffer [22] done counter before
+//  this call [24..31] destination buffer of every rank [32..39] flag block of every rank
+//  [40] wait mode [41] rows per source [42] k per source [43] m rotation (blocks) [44] k rotation (blocks)
+//  [45] scatter mode [46] sc_ld [47] slot stride [48] chunk_dst [49] chunk_col [50] chunk_ndst [51] row offset
+//  [52] arrive_out counter before this call [53] done counter to wait for [54] reduce_out [55] reduce_ld
+//  [56..63] scatter buffer of every rank [64..71] its flag block on every rank [72] max CTAs
+// A is K-major; B is [N,K] or, with b_mn_major, [K,N].  With a scatter mode C is not written and may be
+// null.  Returns the number of CTAs launched (every flag counter of this call grows by that much on
+// every rank) or a negative error code.
+int b200_gemm_comm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                        int b_mn_major, float alpha, const void* bias, const long long* ca, int* status,
+                        cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return -10;
+  if ((lda | ldb) & 7) return -10;
+  CommParams cp{};
+  cp.rank = static_cast<int>(ca[0]);
+  cp.world = static_cast<int>(ca[1]);
+  if (cp.world < 1 || cp.world > kMaxRanks || cp.rank < 0 || cp.rank >= cp.world) return -12;
+  cp.wait_cycles = ca[2] * 1900000LL;
+  cp.push = static_cast<int>(ca[3]);
+  cp.kb_src = reinterpret_cast<const int*>(ca[4]);
+  cp.push_block_rows = ca[6]; cp.push_dst_ld = ca[7]; cp.push_dst_off = ca[8];
+  cp.push_rows = static_cast<int>(ca[9]);
+  cp.push_nseg = static_cast<int>(ca[10]);
+  if (cp.push && (cp.push_nseg < 1 || cp.push_nseg > kMaxPushSeg)) return -12;
+  for (int i = 0; i < kMaxPushSeg; ++i) {
+    cp.seg_src[i] = reinterpret_cast<const __nv_bfloat16*>(ca[11 + i]);
+    cp.seg_dst_col[i] = static_cast<int>(ca[14 + i]);
+    cp.seg_cols[i] = static_cast<int>(ca[17 + i]);
+    cp.seg_src_ld[i] = ca[73 + i];
+    if (cp.push && i < cp.push_nseg &&
+        (((cp.seg_dst_col[i] | cp.seg_cols[i] | cp.seg_src_ld[i]) & 7) || (ca[11 + i] & 15))) return -10;
+  }
+  if (cp.push && ((cp.push_dst_ld | cp.push_dst_off) & 7)) return -10;
+  cp.in_target = static_cast<uint32_t>(ca[20]);
+  cp.push_done_wait = static_cast<int>(ca[21]);
+  cp.push_done_target = static_cast<uint32_t>(ca[22]);
+  for (int r = 0; r < kMaxRanks; ++r) {
+    cp.push_dst[r] = reinterpret_cast<__nv_bfloat16*>(ca[24 + r]);
+    cp.pflags[r] = reinterpret_cast<uint32_t*>(ca[32 + r]);
+    cp.sc_dst[r] = reinterpret_cast<__nv_bfloat16*>(ca[56 + r]);
+    cp.sflags[r] = reinterpret_cast<uint32_t*>(ca[64 + r]);
+  }
+  cp.wait_mode = static_cast<int>(ca[40]);
+  cp.rows_per_src = static_cast<int>(ca[41]);
+  cp.k_per_src = static_cast<int>(ca[42]);
+  cp.m_rot = static_cast<int>(ca[43]);
+  cp.k_rot = static_cast<int>(ca[44]);
+  cp.scatter = static_cast<int>(ca[45]);
+  cp.sc_ld = ca[46]; cp.sc_slot_stride = ca[47];
+  cp.chunk_dst = reinterpret_cast<const int*>(ca[48]);
+  cp.chunk_col = reinterpret_cast<const int*>(ca[49]);
+  cp.chunk_ndst = reinterpret_cast<const int*>(ca[50]);
+  cp.sc_row_off = static_cast<int>(ca[51]);
+  cp.out_target = static_cast<uint32_t>(ca[52]);
+  cp.sc_done_target = static_cast<uint32_t>(ca[53]);
+  cp.reduce_out = reinterpret_cast<__nv_bfloat16*>(ca[54]);
+  cp.reduce_ld = ca[55];
+  const int max_ctas = static_cast<int>(ca[72]);
+  const int tiles_m = (M + BM - 1) / BM, n_kb = (K + BK - 1) / BK;
+  // row blocks / k-ranges of one source must be whole tiles, or a tile would mix sources
+  if ((cp.wait_mode == 1 || cp.scatter == 1) && (cp.rows_per_src % BM != 0 || cp.rows_per_src * cp.world != M)) return -13;
+  if (cp.wait_mode == 2 && cp.kb_src == nullptr && (cp.k_per_src % BK != 0 || cp.k_per_src * cp.world != K)) return -13;
+  if (cp.m_rot < 0 || cp.m_rot >= tiles_m || cp.k_rot < 0 || cp.k_rot >= n_kb) return -13;
+  if (cp.scatter && ((cp.sc_ld | cp.sc_slot_stride | cp.reduce_ld) & 7 || (N & 7))) return -10;
+  if (cp.scatter == 0 && (C == nullptr || (ldc & 7))) return -10;
+  CUtensorMap tA, tB, tC;
+  int rc = make_map(&tA, A, M, K, lda, BK, BM, true);
+  if (!b_mn_major) rc |= make_map(&tB, B, N, K, ldb, BK, BN, true);
+  else rc |= make_map(&tB, B, K, N, ldb, 64, BK, true);
+  // the C map is unused by a scattering epilogue; describe A so that the encode still succeeds
+  if (cp.scatter) rc |= make_map(&tC, A, M, K, lda, 64, 32, true);
+  else rc |= make_map(&tC, C, M, N, ldc, 64, 32, true);
+  if (rc != 0) return rc;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.b_mn_major = b_mn_major;
+  p.alpha = alpha;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.n_tiles_m = tiles_m;
+  p.n_tiles_n = (N + BN - 1) / BN;
+  p.status = status;
+  int launched = 0;
+  rc = launch<EPI_PLAIN, 1>(tA, tB, tB, tC, tC, tC, p, max_ctas, stream, &cp, &launched);
+  return rc != 0 ? rc : launched;
 }
 
 // H = silu(X Wg^T) * (X Wu^T); optionally also writes G and U.  X [M,K], Wg/Wu [I,K].

@@ -30,7 +30,7 @@ from ..ops import gemm as gemm_ops
 from ..ops import norm as norm_ops
 from ..ops import rope as rope_ops
 from ..ops import swiglu as swiglu_ops
-from ..parallel import tp_ops
+from ..parallel import fused_ops, tp_ops
 from ..parallel.sequence_parallel import ulysses as sp
 
 IGNORE_INDEX = -100
@@ -139,25 +139,35 @@ class Attention(nn.Module):
 
     def forward(self, x: torch.Tensor, ctx: "PackedContext") -> torch.Tensor:
         D = self.head_dim
-        if ctx.tp_size > 1:
-            # sequence-parallel tensor parallelism: gather the token shards, project onto this
-            # rank's heads; the row-parallel output projection below reduce-scatters back
-            x = tp_ops.all_gather_tokens(x, ctx.tp_group)
-        T = x.shape[0]
         # one GEMM for q, k, v: the three weights are concatenated on the fly (tens of MB,
         # microseconds) so the projection runs as a single [T, (Hq+2Hkv)D] product
         w = torch.cat([_w(self.q_proj.weight), _w(self.k_proj.weight), _w(self.v_proj.weight)], 0)
         b = (torch.cat([_w(self.q_proj.bias), _w(self.k_proj.bias), _w(self.v_proj.bias)], 0)
              if self.q_proj.bias is not None else None)
-        qkv = gemm_ops.linear(x, w, b)
         nq, nkv = self.n_q * D, self.n_kv * D
-        q = qkv[:, :nq].view(T, self.n_q, D)
-        k = qkv[:, nq : nq + nkv].view(T, self.n_kv, D)
-        v = qkv[:, nq + nkv :].view(T, self.n_kv, D)
-        if self.cfg.qk_norm:
-            q = self.q_norm(q.reshape(-1, D)).view(T, self.n_q, D)
-            k = self.k_norm(k.reshape(-1, D)).view(T, self.n_kv, D)
-        if ctx.sp_size > 1:
+        # fused collectives: the projection kernels move the data between the ranks themselves
+        fc_tp = fused_ops.context_for(ctx.tp_group) if (ctx.tp_size > 1 and x.is_cuda and fused_ops.tp_supported(x.shape[0])) else None
+        fc_sp = (fused_ops.context_for(ctx.sp_group)
+                 if (ctx.sp_size > 1 and x.is_cuda and fused_ops.ulysses_supported(self.n_q, self.n_kv, D, ctx.sp_size)) else None)
+        if fc_sp is not None:
+            q, k, v = fused_ops.ulysses_qkv(x, w, b, fc_sp, self.n_q, self.n_kv, D, self.layer_idx)
+        else:
+            if fc_tp is not None:
+                qkv = fused_ops.column_linear(x, w, b, fc_tp)
+            else:
+                if ctx.tp_size > 1:
+                    # sequence-parallel tensor parallelism: gather the token shards, project onto this
+                    # rank's heads; the row-parallel output projection below reduce-scatters back
+                    x = tp_ops.all_gather_tokens(x, ctx.tp_group)
+                qkv = gemm_ops.linear(x, w, b)
+            T = qkv.shape[0]
+            q = qkv[:, :nq].view(T, self.n_q, D)
+            k = qkv[:, nq : nq + nkv].view(T, self.n_kv, D)
+            v = qkv[:, nq + nkv :].view(T, self.n_kv, D)
+        if self.cfg.qk_norm:  # per head, so it commutes with the head exchange
+            q = self.q_norm(q.reshape(-1, D)).view(q.shape)
+            k = self.k_norm(k.reshape(-1, D)).view(k.shape)
+        if ctx.sp_size > 1 and fc_sp is None:
             # Ulysses: trade the sequence split for a head split around attention
             q, k, v = sp.seq_to_head_qkv(q, k, v, ctx.sp_group)
         q = rope_ops.rope_apply(q, ctx.cos, ctx.sin)
@@ -166,8 +176,12 @@ class Attention(nn.Module):
             q, k, v, ctx.cu_seqlens, ctx.cu_seqlens, ctx.max_seqlen, ctx.max_seqlen, causal=ctx.causal,
             softmax_scale=1.0 / math.sqrt(D), window_size=self.window,
         )
+        if fc_sp is not None:
+            return fused_ops.ulysses_out(o, _w(self.o_proj.weight), fc_sp, self.n_q, D, self.layer_idx)
         if ctx.sp_size > 1:
             o = sp.head_to_seq(o, ctx.sp_group, self.n_q, self.n_kv)
+        if fc_tp is not None:
+            return fused_ops.row_linear(o.reshape(o.shape[0], -1), _w(self.o_proj.weight), fc_tp)
         out = gemm_ops.linear(o.reshape(o.shape[0], -1), _w(self.o_proj.weight), None)
         if ctx.tp_size > 1:
             out = tp_ops.reduce_scatter_tokens(out, ctx.tp_group)
@@ -184,6 +198,14 @@ class SwiGLUMLP(nn.Module):
         self.tp_group = None
 
     def forward(self, x):
+        if self.tp_group is not None and x.is_cuda and fused_ops.tp_supported(x.shape[0]):
+            fc = fused_ops.context_for(self.tp_group)
+            if fc is not None:
+                # all-gather -> [gate; up] GEMM, GEMM -> reduce-scatter: two kernels carry both collectives
+                wg, wu = _w(self.gate_proj.weight), _w(self.up_proj.weight)
+                gu = fused_ops.column_linear(x, torch.cat([wg, wu], 0), None, fc)
+                h = swiglu_ops.swiglu(gu[:, : wg.shape[0]], gu[:, wg.shape[0] :])
+                return fused_ops.row_linear(h, _w(self.down_proj.weight), fc)
         if self.tp_group is not None:
             x = tp_ops.all_gather_tokens(x, self.tp_group)
         y = swiglu_ops.swiglu_mlp(x, _w(self.gate_proj.weight), _w(self.up_proj.weight), _w(self.down_proj.weight))

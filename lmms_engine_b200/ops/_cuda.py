@@ -98,6 +98,14 @@ def call(name: str, *args) -> None:
         raise RuntimeError(f"{name} failed with code {rc}")
 
 
+def call_raw(name: str, *args) -> int:
+    """Like ``call`` for launchers whose return value carries information (negative = error)."""
+    global launch_count
+    rc = fn(name)(*args)
+    launch_count += 1
+    return rc
+
+
 def require_bf16_cuda(*ts: torch.Tensor) -> None:
     for t in ts:
         if t is None:

@@ -37,3 +37,21 @@ def test_peer_runtime_two_gpus():
 def test_peer_runtime_four_gpus():
     out = _torchrun("peer_two_gpu.py", 4)
     assert "peer runtime ok" in out
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_comm_gemms_two_gpus():
+    out = _torchrun("fused_comm_run.py", 2)
+    assert "fused comm ok" in out
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four GPUs")
+def test_fused_comm_gemms_four_gpus():
+    out = _torchrun("fused_comm_run.py", 4)
+    assert "fused comm ok" in out
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_projections_in_decoder_two_gpus():
+    out = _torchrun("fused_model_run.py", 2)
+    assert "fused model ok" in out
