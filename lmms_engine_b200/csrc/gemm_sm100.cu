@@ -78,9 +78,11 @@ struct GemmParams {
 //  wait    : the TMA producer waits for arrive_in of the rank whose rows (mode 1) or k-range
 //            (mode 2) a tile reads, so tiles of blocks that have already landed run first;
 //  scatter : the epilogue stores each tile into the destination rank's buffer instead of C:
-//            mode 1 = row blocks into per-source slots that the destination sums at the end of
-//            the same kernel (reduce-scatter), mode 2 = 64-column chunks routed by a table
-//            (all-to-all by heads).  arrive_out counts finished source CTAs.
+//            mode 1 = row blocks into per-source slots of the rank that owns the rows; every rank
+//            computes its own row blocks last and their epilogue adds the slots that have landed
+//            by then (reduce-scatter without a separate pass), mode 2 = 64-column chunks routed
+//            by a table (all-to-all by heads).  arrive_out counts stored tiles (mode 1, one per
+//            epilogue warp) or finished source CTAs (mode 2).
 // Flag block of a buffer on every rank: u32 [3][kMaxRanks] = arrive_in | arrive_out | done.
 constexpr int kMaxRanks = 8;
 constexpr int kMaxPushSeg = 3;
@@ -106,6 +108,7 @@ struct CommParams {
   uint32_t push_done_target;
   // wait
   int wait_mode, rows_per_src, k_per_src, m_rot, k_rot;
+  int own_direct;                          // mode 1: tiles of this rank's own rows read the source matrix (map tmB2)
   const int* kb_src;                       // mode 2: source rank of every 64-wide k-block (null: k / k_per_src)
   // scatter
   int scatter;
@@ -117,10 +120,22 @@ struct CommParams {
   __nv_bfloat16* sc_dst[kMaxRanks];
   uint32_t* sflags[kMaxRanks];
   uint32_t out_target, sc_done_target;
+  int out_inc_tiles;                       // mode 1: arrive_out grows by 4 (epilogue warps) per tile sent to a rank
+  // optional timeline of CTA 0 in globaltimer nanoseconds: [0] start [1] handshake passed [2] first
+  // remote block pushed and flagged [3] all blocks pushed [4] producer saw its last source [5] end
+  unsigned long long* trace;
   __nv_bfloat16* reduce_out;
   long long reduce_ld;
 };
 
+// Signalling convention of the fused collectives: the data stores of a warp / of the pushing warps
+// are ordered before the signalling thread by __syncwarp / a named barrier, and the signal itself is
+// a release at system scope (flag_add_release), which is cumulative over that order.
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
 // Map a linear tile index to (m_block, n_block).  Sixteen m-blocks share each sweep
@@ -145,6 +160,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // a fused collective may have to wait for a rank that was launched later: its waits use the
   // caller's limit, every other launch keeps the short default
   const long long wait_limit = COMM ? cp.wait_cycles : kWaitCycleLimit;
+  const bool tracing = COMM && cp.trace != nullptr && blockIdx.x == 0;
+  if (tracing && threadIdx.x == 0) cp.trace[0] = global_ns();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_smem = smem + kStages * kStageBytes;
@@ -213,6 +230,64 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   };
 
+  // Copy this rank's block into every rank's buffer (COMM push).  Runs on warps 2..7 (192 threads):
+  // the epilogue warps have nothing to drain before the first accumulator completes.  Every thread
+  // executes every iteration, so the named barrier below always gets its full count.
+  constexpr int kPushThreads = 192;
+  auto push_blocks = [&](const int ct) {
+    const int pw = ct >> 5;
+    bool okp = true;
+    if (cp.push_done_wait && pw == 0 && lane < cp.world) {
+      flag_add_release(cp.pflags[lane] + 2 * kMaxRanks + cp.rank, 1u);
+    }
+    for (int d = 0; d < cp.world; ++d) {
+      // the ranks in the order in which they will need this block; the local copy comes last when
+      // this rank's own tiles read the source directly, first otherwise
+      const int r = cp.own_direct ? (cp.rank - 1 - d + 2 * cp.world) % cp.world : (cp.rank - d + cp.world) % cp.world;
+      if (okp && cp.push_done_wait) {
+        int w = 1;
+        if (lane == 0) w = flag_wait_ge(cp.pflags[cp.rank] + 2 * kMaxRanks + r, cp.push_done_target, wait_limit, abort_word);
+        okp = __shfl_sync(0xffffffffu, w, 0) != 0;
+        if (tracing && ct == 0 && d == 0) cp.trace[1] = global_ns();
+      }
+      if (okp) {
+        __nv_bfloat16* dst = cp.push_dst[r] + cp.push_dst_off;
+        for (int sg = 0; sg < cp.push_nseg; ++sg) {
+          const long long sld = cp.seg_src_ld[sg];
+          const int vpr = cp.seg_cols[sg] >> 3;  // 16-byte vectors per row
+          const long long total = static_cast<long long>(cp.push_rows) * vpr;
+          const long long per = (total + gridDim.x - 1) / gridDim.x;
+          const long long v_hi = min(total, per * (blockIdx.x + 1));
+          const __nv_bfloat16* s0 = cp.seg_src[sg] + r * cp.push_block_rows * sld;
+          __nv_bfloat16* d0 = dst + cp.seg_dst_col[sg];
+          for (long long v = per * blockIdx.x + ct; v < v_hi; v += kPushThreads * 8) {
+            uint4 val[8];
+            long long dof[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const long long vv = v + u * kPushThreads;
+              if (vv < v_hi) {
+                const long long row = vv / vpr;
+                const int c = static_cast<int>(vv - row * vpr) * 8;
+                val[u] = *reinterpret_cast<const uint4*>(s0 + row * sld + c);
+                dof[u] = row * cp.push_dst_ld + c;
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              if (v + u * kPushThreads < v_hi) *reinterpret_cast<uint4*>(d0 + dof[u]) = val[u];
+          }
+        }
+      }
+      bar_sync_named(1, kPushThreads);
+      if (ct == 0 && okp) {
+        flag_add_release(cp.pflags[r] + cp.rank, 1u);
+        if (tracing && d == 0) cp.trace[2] = global_ns();
+        if (tracing && d == cp.world - 1) cp.trace[3] = global_ns();
+      }
+    }
+  };
+
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -226,6 +301,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!flag_wait_ge(cp.pflags[cp.rank] + src, cp.in_target, wait_limit, abort_word)) return false;
         fence_proxy_async_all();  // the block was written by generic stores, TMA reads it next
         landed |= 1u << src;
+        if (tracing) cp.trace[4] = global_ns();
         return true;
       };
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -235,13 +311,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int m0 = mb * BM;
         const int n0 = (EPI == EPI_SWIGLU) ? nb * (BN / 2) : nb * BN;
         const bool grouped_b = p.tile_expert != nullptr;  // B is a 3-D map indexed by expert
-        if (COMM && cp.wait_mode == 1 && !source_ready(m0 / cp.rows_per_src)) { ok = false; break; }
+        bool own_rows = false;
+        if (COMM && cp.wait_mode == 1) {
+          const int src = m0 / cp.rows_per_src;
+          own_rows = cp.own_direct && src == cp.rank;
+          if (!own_rows && !source_ready(src)) { ok = false; break; }
+        }
         for (int kb = 0; kb < kb_n; ++kb, ++it) {
           int kbr = kb_lo + kb;
           if (COMM) {
             kbr += cp.k_rot;  // begin with the k-range that this rank contributed itself
             if (kbr >= n_kb) kbr -= n_kb;
-            if (cp.wait_mode == 2 && !source_ready(cp.kb_src != nullptr ? cp.kb_src[kbr] : kbr * BK / cp.k_per_src)) { ok = false; break; }
+            if (cp.wait_mode == 2) {
+              const int src = cp.kb_src != nullptr ? cp.kb_src[kbr] : kbr * BK / cp.k_per_src;
+              own_rows = cp.own_direct && src == cp.rank;
+              if (!own_rows && !source_ready(src)) { ok = false; break; }
+            }
           }
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
@@ -250,7 +335,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* sb = sa + kATileBytes;
           mbar_expect_tx(&full_bar[s], kStageBytes);
           const int k0 = kbr * BK;
-          if (!p.a_mn_major) {
+          if (COMM && own_rows) {
+            // this rank's own block straight from the matrix that is being pushed
+            if (cp.wait_mode == 1) tma_load_2d(sa, &tmB2, &full_bar[s], k0, m0 - cp.rank * cp.rows_per_src);
+            else tma_load_2d(sa, &tmB2, &full_bar[s], k0 - cp.rank * cp.k_per_src, m0 + cp.rank * static_cast<int>(cp.push_block_rows));
+          } else if (!p.a_mn_major) {
             tma_load_2d(sa, &tmA, &full_bar[s], k0, m0);
           } else if (p.a_mn3d) {
             tma_load_3d(sa, &tmA, &full_bar[s], 0, k0, m0 / 64);
@@ -327,58 +416,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
   } else if (COMM && warp < 4) {
-    // ------------------------------------------------------------ push (warps 2, 3)
-    if (cp.push) {
-      const int ct = (warp - 2) * 32 + lane;
-      bool okp = true;
-      if (cp.push_done_wait && warp == 2 && lane < cp.world) {
-        __threadfence_system();
-        flag_add_release(cp.pflags[lane] + 2 * kMaxRanks + cp.rank, 1u);
-      }
-      for (int d = 0; d < cp.world; ++d) {
-        // own copy first, then the ranks in the order in which they will need this block
-        const int r = (cp.rank - d + cp.world) % cp.world;
-        if (okp && cp.push_done_wait) {
-          int w = 1;
-          if (lane == 0) w = flag_wait_ge(cp.pflags[cp.rank] + 2 * kMaxRanks + r, cp.push_done_target, wait_limit, abort_word);
-          okp = __shfl_sync(0xffffffffu, w, 0) != 0;
-        }
-        if (okp) {
-          __nv_bfloat16* dst = cp.push_dst[r] + cp.push_dst_off;
-          for (int sg = 0; sg < cp.push_nseg; ++sg) {
-            const long long sld = cp.seg_src_ld[sg];
-            const int vpr = cp.seg_cols[sg] >> 3;  // 16-byte vectors per row
-            const long long total = static_cast<long long>(cp.push_rows) * vpr;
-            const long long per = (total + gridDim.x - 1) / gridDim.x;
-            const long long v_hi = min(total, per * (blockIdx.x + 1));
-            const __nv_bfloat16* s0 = cp.seg_src[sg] + r * cp.push_block_rows * sld;
-            __nv_bfloat16* d0 = dst + cp.seg_dst_col[sg];
-            for (long long v = per * blockIdx.x + ct; v < v_hi; v += 64 * 4) {
-              uint4 val[4];
-              long long dof[4];
-#pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const long long vv = v + u * 64;
-                if (vv < v_hi) {
-                  const long long row = vv / vpr;
-                  const int c = static_cast<int>(vv - row * vpr) * 8;
-                  val[u] = *reinterpret_cast<const uint4*>(s0 + row * sld + c);
-                  dof[u] = row * cp.push_dst_ld + c;
-                }
-              }
-#pragma unroll
-              for (int u = 0; u < 4; ++u)
-                if (v + u * 64 < v_hi) *reinterpret_cast<uint4*>(d0 + dof[u]) = val[u];
-            }
-          }
-        }
-        bar_sync_named(1, 64);
-        if (warp == 2 && lane == 0 && okp) {
-          __threadfence_system();
-          flag_add_release(cp.pflags[r] + cp.rank, 1u);
-        }
-      }
-    }
+    // ------------------------------------------------------------ push (warps 2, 3; the epilogue warps help)
+    if (cp.push) push_blocks((warp - 2) * 32 + lane);
   } else if (warp >= 4) {
     // ------------------------------------------------------------ epilogue (warps 4..7)
     const int q = warp - 4;  // TMEM lane quadrant == warp % 4
@@ -387,6 +426,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int buf = 0;
     bool ok = true;
     uint32_t sc_open = 0;  // COMM scatter: destinations known to have drained their slots
+    bool own_ready = false;
+    if (COMM && cp.push) push_blocks(64 + q * 32 + lane);
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       int ex, mb, nb, kb_lo, kb_n;
       decode(t, ex, mb, nb, kb_lo, kb_n);
@@ -400,6 +441,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int row = m0 + q * 32 + lane;  // global row owned by this thread
       const uint32_t t_acc = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
 
+      const bool rs_tile = COMM && cp.scatter == 1;
+      const int rs_dst = rs_tile ? m0 / cp.rows_per_src : 0;
+      const bool own_tile = rs_tile && rs_dst == cp.rank;
+      if (own_tile && !own_ready) {
+        // partial products of the other ranks for my rows: they were computed before those ranks' own rows
+        int w = 1;
+        if (lane < cp.world && lane != cp.rank)
+          w = flag_wait_ge(cp.sflags[cp.rank] + kMaxRanks + lane, cp.out_target, wait_limit, abort_word);
+        if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+        own_ready = true;
+      }
       if (EPI == EPI_PLAIN || EPI == EPI_STATS || EPI == EPI_SYMM) {
         const int n0 = nb * BN;
         float run_max = -INFINITY, run_sum = 0.f;
@@ -441,6 +493,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
                   if (col0 + j < p.N) v[j] += p.beta * __bfloat162float(crow[j]);
+              }
+            }
+            if (COMM && own_tile) {
+              const long long lrow = row - static_cast<long long>(cp.rank) * cp.rows_per_src;
+              for (int sr = 1; sr < cp.world; ++sr) {
+                int src = cp.rank + sr;
+                if (src >= cp.world) src -= cp.world;
+                const __nv_bfloat16* srow = cp.sc_dst[cp.rank] + src * cp.sc_slot_stride + lrow * cp.sc_ld + col0;
+#pragma unroll
+                for (int j4 = 0; j4 < 4; ++j4) {
+                  if (col0 + j4 * 8 < p.N) {
+                    const uint4 u = __ldcg(reinterpret_cast<const uint4*>(srow + j4 * 8));
+                    const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z),
+                                 f3 = unpack_bf16x2(u.w);
+                    v[j4 * 8 + 0] += f0.x; v[j4 * 8 + 1] += f0.y; v[j4 * 8 + 2] += f1.x; v[j4 * 8 + 3] += f1.y;
+                    v[j4 * 8 + 4] += f2.x; v[j4 * 8 + 5] += f2.y; v[j4 * 8 + 6] += f3.x; v[j4 * 8 + 7] += f3.y;
+                  }
+                }
               }
             }
             uint32_t pk[16];
@@ -497,14 +567,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const int r0 = m0 + q * 32;
             const int ccol = n0 + c64 * 64;
             int dst_lo, ndst, col_base;
-            long long row_base, slot_off;
+            long long row_base, slot_off, dld = cp.sc_ld;
+            __nv_bfloat16* own_out = nullptr;
             if (cp.scatter == 1) {
-              dst_lo = r0 / cp.rows_per_src;
+              dst_lo = rs_dst;
               ndst = 1;
               col_base = ccol;
               row_base = r0 - static_cast<long long>(dst_lo) * cp.rows_per_src;
               slot_off = cp.rank * cp.sc_slot_stride;
-              if (!((sc_open >> dst_lo) & 1u)) {
+              if (own_tile) {  // already summed: this is the result
+                own_out = cp.reduce_out;
+                dld = cp.reduce_ld;
+              } else if (!((sc_open >> dst_lo) & 1u)) {
                 int w = 1;
                 if (lane == 0) w = flag_wait_ge(cp.sflags[cp.rank] + 2 * kMaxRanks + dst_lo, cp.sc_done_target, wait_limit, abort_word);
                 if (__shfl_sync(0xffffffffu, w, 0) == 0) { ok = false; break; }
@@ -520,14 +594,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               slot_off = 0;
             }
             for (int dd = 0; dd < ndst; ++dd) {
-              __nv_bfloat16* dbase = cp.sc_dst[dst_lo + dd] + slot_off + col_base;
+              __nv_bfloat16* dbase = own_out != nullptr ? own_out + col_base : cp.sc_dst[dst_lo + dd] + slot_off + col_base;
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 const int rr = i * 4 + (lane >> 3);
                 const int ch = lane & 7;
                 if (r0 + rr < p.M && ccol + ch * 8 < p.N) {
                   const uint4 val = *reinterpret_cast<const uint4*>(slab + rr * 128 + ((ch ^ (rr & 7)) * 16));
-                  *reinterpret_cast<uint4*>(dbase + (row_base + rr) * cp.sc_ld + ch * 8) = val;
+                  *reinterpret_cast<uint4*>(dbase + (row_base + rr) * dld + ch * 8) = val;
                 }
               }
             }
@@ -544,6 +618,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           buf ^= 1;
         }
         if (!ok) break;
+        if (rs_tile && !own_tile) {
+          // this warp's part of the tile is on its way: count it on the destination
+          __syncwarp();
+          if (lane == 0) {
+            flag_add_release(cp.sflags[rs_dst] + kMaxRanks + cp.rank, 1u);
+          }
+        }
         if (EPI == EPI_STATS && row < p.M) p.stats[static_cast<size_t>(row) * tiles_n + nb] = make_float2(run_max, run_sum);
       } else {  // EPI_SWIGLU: accumulator cols [0,128) = gate, [128,256) = up
         const int n0 = nb * (BN / 2);
@@ -602,11 +683,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       ++tl;
     }
     if (lane == 0) tma_store_wait_all<0>();
-    if (COMM && cp.scatter) {
+    if (COMM && cp.scatter == 2) {
       // every tile of this CTA has been stored: tell all destinations
       bar_sync_named(2, kEpiWarps * 32);
       if (warp == 4 && lane < cp.world && !*abort_word) {
-        __threadfence_system();
         flag_add_release(cp.sflags[lane] + kMaxRanks + cp.rank, 1u);
       }
     }
@@ -616,34 +696,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (COMM) {
-    // wait for what the other ranks sent here, then finish the reduction on the local slots
+    // wait for what the other ranks sent here
     if (static_cast<int>(threadIdx.x) < cp.world) {
-      if (cp.scatter) flag_wait_ge(cp.sflags[cp.rank] + kMaxRanks + threadIdx.x, cp.out_target, wait_limit, abort_word);
+      // (mode 1 counts only what other ranks sent: this rank's own rows never pass through a slot)
+      if (cp.scatter == 2 || (cp.scatter == 1 && static_cast<int>(threadIdx.x) != cp.rank))
+        flag_wait_ge(cp.sflags[cp.rank] + kMaxRanks + threadIdx.x, cp.out_target, wait_limit, abort_word);
       if (cp.push && cp.wait_mode == 0) flag_wait_ge(cp.pflags[cp.rank] + threadIdx.x, cp.in_target, wait_limit, abort_word);
     }
     __syncthreads();
-    if (cp.scatter == 1 && !*abort_word) {
-      const int vpr = p.N >> 3;
-      const long long total = static_cast<long long>(cp.rows_per_src) * vpr;
-      const long long per = (total + gridDim.x - 1) / gridDim.x;
-      const long long v_hi = min(total, per * (blockIdx.x + 1));
-      const __nv_bfloat16* slots = cp.sc_dst[cp.rank];
-      for (long long v = per * blockIdx.x + threadIdx.x; v < v_hi; v += kThreads) {
-        const long long row = v / vpr;
-        const int c = static_cast<int>(v - row * vpr) * 8;
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int sr = 0; sr < cp.world; ++sr) {
-          const uint4 u = __ldcg(reinterpret_cast<const uint4*>(slots + sr * cp.sc_slot_stride + row * cp.sc_ld + c));
-          const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
-          acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
-          acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
-        }
-        *reinterpret_cast<uint4*>(cp.reduce_out + row * cp.reduce_ld + c) =
-            make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
-                       pack_bf16x2(acc[6], acc[7]));
-      }
-    }
     __syncthreads();
+    if (tracing && threadIdx.x == 0) cp.trace[5] = global_ns();
     // this rank no longer reads its gather buffer / its slots: writers of the next call may proceed
     if (static_cast<int>(threadIdx.x) < cp.world && !*abort_word) {
       __threadfence_system();
@@ -782,7 +844,7 @@ static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMa
     // arrival counters grow by one per CTA and call on every rank (all ranks launch the same grid)
     cp = *comm;
     cp.in_target += static_cast<uint32_t>(ctas);
-    cp.out_target += static_cast<uint32_t>(ctas);
+    cp.out_target += static_cast<uint32_t>(cp.scatter == 1 ? cp.out_inc_tiles : ctas);
     cp.push_done_target += static_cast<uint32_t>(ctas);
   }
   if (launched != nullptr) *launched = ctas;
@@ -849,6 +911,8 @@ int b200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, i
 //  [45] scatter mode [46] sc_ld [47] slot stride [48] chunk_dst [49] chunk_col [50] chunk_ndst [51] row offset
 //  [52] arrive_out counter before this call [53] done counter to wait for [54] reduce_out [55] reduce_ld
 //  [56..63] scatter buffer of every rank [64..71] its flag block on every rank [72] max CTAs
+//  [76] tiles of this rank's own rows read the pushed matrix itself (all-gather mode)
+//  [77] optional device buffer of six u64 for CTA 0's timeline (see CommParams::trace)
 // A is K-major; B is [N,K] or, with b_mn_major, [K,N].  With a scatter mode C is not written and may be
 // null.  Returns the number of CTAs launched (every flag counter of this call grows by that much on
 // every rank) or a negative error code.
@@ -902,6 +966,9 @@ int b200_gemm_comm_bf16(const void* A, const void* B, void* C, int M, int N, int
   cp.reduce_out = reinterpret_cast<__nv_bfloat16*>(ca[54]);
   cp.reduce_ld = ca[55];
   const int max_ctas = static_cast<int>(ca[72]);
+  cp.own_direct = static_cast<int>(ca[76]);
+  cp.trace = reinterpret_cast<unsigned long long*>(ca[77]);
+  cp.out_inc_tiles = 4 * (cp.rows_per_src > 0 ? cp.rows_per_src / BM : 0) * ((N + BN - 1) / BN);
   const int tiles_m = (M + BM - 1) / BM, n_kb = (K + BK - 1) / BK;
   // row blocks / k-ranges of one source must be whole tiles, or a tile would mix sources
   if ((cp.wait_mode == 1 || cp.scatter == 1) && (cp.rows_per_src % BM != 0 || cp.rows_per_src * cp.world != M)) return -13;
@@ -909,10 +976,25 @@ int b200_gemm_comm_bf16(const void* A, const void* B, void* C, int M, int N, int
   if (cp.m_rot < 0 || cp.m_rot >= tiles_m || cp.k_rot < 0 || cp.k_rot >= n_kb) return -13;
   if (cp.scatter && ((cp.sc_ld | cp.sc_slot_stride | cp.reduce_ld) & 7 || (N & 7))) return -10;
   if (cp.scatter == 0 && (C == nullptr || (ldc & 7))) return -10;
-  CUtensorMap tA, tB, tC;
+  CUtensorMap tA, tB, tC, tOwn;
   int rc = make_map(&tA, A, M, K, lda, BK, BM, true);
   if (!b_mn_major) rc |= make_map(&tB, B, N, K, ldb, BK, BN, true);
   else rc |= make_map(&tB, B, K, N, ldb, 64, BK, true);
+  if (cp.own_direct) {
+    // tiles of this rank's own rows read the matrix that is being pushed, not its copy
+    if (!(cp.push && cp.push_nseg == 1 && (cp.wait_mode == 1 || cp.wait_mode == 2))) return -13;
+    if (cp.wait_mode == 1) {
+      if (cp.seg_cols[0] != K) return -13;
+      rc |= make_map(&tOwn, cp.seg_src[0], cp.push_rows, K, cp.seg_src_ld[0], BK, BM, true);
+    } else {
+      // source [world * rows, k_per_src]: rows of block r feed rank r; this rank reads its own block
+      if (cp.kb_src != nullptr || cp.seg_cols[0] != cp.k_per_src) return -13;
+      rc |= make_map(&tOwn, cp.seg_src[0], static_cast<uint64_t>(cp.push_block_rows) * cp.world, cp.k_per_src,
+                     cp.seg_src_ld[0], BK, BM, true);
+    }
+  } else {
+    tOwn = tB;
+  }
   // the C map is unused by a scattering epilogue; describe A so that the encode still succeeds
   if (cp.scatter) rc |= make_map(&tC, A, M, K, lda, 64, 32, true);
   else rc |= make_map(&tC, C, M, N, ldc, 64, 32, true);
@@ -926,7 +1008,7 @@ int b200_gemm_comm_bf16(const void* A, const void* B, void* C, int M, int N, int
   p.n_tiles_n = (N + BN - 1) / BN;
   p.status = status;
   int launched = 0;
-  rc = launch<EPI_PLAIN, 1>(tA, tB, tB, tC, tC, tC, p, max_ctas, stream, &cp, &launched);
+  rc = launch<EPI_PLAIN, 1>(tA, tB, tOwn, tC, tC, tC, p, max_ctas, stream, &cp, &launched);
   return rc != 0 ? rc : launched;
 }
 

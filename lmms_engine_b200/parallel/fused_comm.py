@@ -169,12 +169,23 @@ class FusedComm:
         self.group, self.world, self.rank, self.device = group, self.pool.world, self.pool.rank, device
         self.wait_ms = wait_ms
         self._buffers: Dict[Tuple, CommBuffer] = {}
+        self._turn: Dict = {}
         self.max_ctas = 0
         self.launches = 0
+        self.trace: Optional[torch.Tensor] = None  # set to an int64[6] device tensor to record a launch timeline
 
-    def buffer(self, key, rows: int, cols: int) -> CommBuffer:
+    def buffer(self, key, rows: int, cols: int, rotate: bool = False) -> CommBuffer:
         """The named buffer, shaped for this call.  It is re-created (rows rounded up to 1024) only
-        when a call needs more room than any earlier one, identically on every rank."""
+        when a call needs more room than any earlier one, identically on every rank.
+
+        ``rotate`` alternates between two buffers of that name.  A gather buffer that the next call
+        with the same name overwrites needs it: a rank can start call n+2 only after call n+1, in
+        which it waited for every other rank's block, and a rank sends its block of call n+1 only
+        after everything it queued behind call n (the readers of that buffer) has finished; so the
+        buffer of call n is free on every rank when call n+2 writes it, without a handshake."""
+        if rotate:
+            turn = self._turn[key] = self._turn.get(key, 0) ^ 1
+            key = (key, "turn", turn)
         b = self._buffers.get(key)
         if b is None or b.capacity < rows * cols:
             b = self._buffers[key] = CommBuffer(self.pool, ((rows + 1023) // 1024 * 1024) * cols)
@@ -182,7 +193,7 @@ class FusedComm:
 
     # ------------------------------------------------------------------ launch
     def _launch(self, a, b, c, M, N, K, b_mn, alpha, bias, *, push=None, wait_mode=0, rows_per_src=0, k_per_src=0,
-                kb_src=None, m_rot=0, k_rot=0, scatter=None):
+                kb_src=None, m_rot=0, k_rot=0, scatter=None, own_direct=False):
         ca = (ctypes.c_longlong * 80)()
         ca[0], ca[1], ca[2] = self.rank, self.world, self.wait_ms
         if push is not None:
@@ -199,7 +210,7 @@ class FusedComm:
                     raise TypeError("pushed blocks must be 2-D bf16 CUDA matrices with unit inner stride")
                 ca[11 + i], ca[14 + i], ca[17 + i], ca[73 + i] = src.data_ptr(), dcol, cols, src.stride(0)
             ca[20] = buf.n_in
-            ca[21] = 1 if push.get("handshake", True) else 0
+            ca[21] = 1 if push.get("handshake", False) else 0
             ca[22] = buf.n_done
             for r in range(self.world):
                 ca[24 + r], ca[32 + r] = buf.ptrs[r], buf.flag_ptrs[r]
@@ -223,6 +234,9 @@ class FusedComm:
             for r in range(self.world):
                 ca[56 + r], ca[64 + r] = sb.ptrs[r], sb.flag_ptrs[r]
         ca[72] = self.max_ctas
+        ca[76] = 1 if own_direct else 0
+        if self.trace is not None:  # CTA 0's timeline of this launch, six globaltimer stamps
+            ca[77] = self.trace.data_ptr()
         st = _cuda.status_word(self.device)
         ctas = _cuda.call_raw(
             "b200_gemm_comm_bf16", a.data_ptr(), b.data_ptr(), c.data_ptr() if c is not None else 0, M, N, K,
@@ -236,9 +250,12 @@ class FusedComm:
             if ca[21]:
                 push["buf"].n_done += ctas
         if scatter is not None:
-            scatter["buf"].n_out += ctas
             if scatter["mode"] == 1:
+                # one count per epilogue warp and tile that a rank sends to another
+                scatter["buf"].n_out += 4 * (rows_per_src // 128) * ((N + 255) // 256)
                 scatter["buf"].n_done += ctas
+            else:
+                scatter["buf"].n_out += ctas
         self.launches += 1
         return ctas
 
@@ -254,11 +271,11 @@ class FusedComm:
         N, Kw = self._bshape(w, b_mn)
         if K != Kw or Ms % 128:
             raise ValueError("ag_gemm needs matching K and a multiple of 128 rows per rank")
-        buf = self.buffer(key, Ms * self.world, K)
+        buf = self.buffer(key, Ms * self.world, K, rotate=True)
         y = torch.empty((Ms * self.world, N), dtype=torch.bfloat16, device=x.device)
         push = dict(buf=buf, block_rows=0, dst_off=self.rank * Ms * buf.t.stride(0), rows=Ms, segs=[(x, 0, K)])
         self._launch(buf.t, w, y, Ms * self.world, N, K, b_mn, 1.0, bias, push=push, wait_mode=1, rows_per_src=Ms,
-                     m_rot=self.rank * (Ms // 128))
+                     m_rot=self.rank * (Ms // 128), own_direct=True)
         return y, buf.t
 
     # ------------------------------------------------------------------ GEMM -> reduce-scatter rows
@@ -277,7 +294,7 @@ class FusedComm:
         push, gathered = None, None
         if regather is not None:
             xl, gkey = regather
-            gb = self.buffer(gkey, xl.shape[0] * self.world, xl.shape[1])
+            gb = self.buffer(gkey, xl.shape[0] * self.world, xl.shape[1], rotate=True)
             push = dict(buf=gb, block_rows=0, dst_off=self.rank * xl.shape[0] * gb.t.stride(0), rows=xl.shape[0],
                         segs=[(xl, 0, xl.shape[1])])
             gathered = gb.t
@@ -301,7 +318,7 @@ class FusedComm:
 
     # ------------------------------------------------------------------ all-to-all by heads -> GEMM
     def a2a_gemm(self, parts: Sequence[Tuple[torch.Tensor, int]], w: torch.Tensor, cols_total: int, kb_src=None,
-                 b_mn: bool = False, bias=None, key="o", k_rot: int = 0):
+                 b_mn: bool = False, bias=None, key="o", k_rot: int = 0, rotate: bool = True):
         """``parts`` = ``[(src [world*Tl, c_i], dst_col_i), ...]``: rows ``[r*Tl, (r+1)*Tl)`` of every
         source go to rank r at columns ``dst_col_i``; then ``y = gathered[Tl, cols_total] @ op(w)^T``.
         Returns ``(y, gathered)``; ``gathered`` is the shared buffer of ``key``."""
@@ -310,13 +327,15 @@ class FusedComm:
         N, Kw = self._bshape(w, b_mn)
         if Kw != cols_total:
             raise ValueError("weight does not match the gathered width")
-        buf = self.buffer(key, Tl, cols_total)
+        buf = self.buffer(key, Tl, cols_total, rotate=rotate)
         y = torch.empty((Tl, N), dtype=torch.bfloat16, device=w.device)
         segs = [(src, dcol, src.shape[1]) for src, dcol in parts]
         push = dict(buf=buf, block_rows=Tl, dst_off=0, rows=Tl, segs=segs)
         kps = cols_total // self.world
+        # a single source whose block sits at my rank's column range can be read in place
+        direct = len(parts) == 1 and kb_src is None and parts[0][1] == self.rank * kps and parts[0][0].shape[1] == kps
         self._launch(buf.t, w, y, Tl, N, cols_total, b_mn, 1.0, bias, push=push, wait_mode=2, k_per_src=kps,
-                     kb_src=kb_src, k_rot=k_rot)
+                     kb_src=kb_src, k_rot=k_rot, own_direct=direct)
         return y, buf.t
 
 

@@ -167,7 +167,7 @@ class _UlyssesOut(torch.autograd.Function):
         hq = n_q // fc.world
         o2 = _c2(o, T)
         # the gathered attention output stays in this layer's own buffer until its backward pass
-        y, g = fc.a2a_gemm([(o2, fc.rank * hq * D)], w, n_q * D, key=("o", layer), k_rot=fc.rank * hq * D // 64)
+        y, g = fc.a2a_gemm([(o2, fc.rank * hq * D)], w, n_q * D, key=("o", layer), k_rot=fc.rank * hq * D // 64, rotate=False)
         ctx.fc, ctx.meta = fc, (n_q, D, T)
         ctx.save_for_backward(g, w)
         return y

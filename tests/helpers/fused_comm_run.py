@@ -14,12 +14,22 @@ import torch
 import torch.distributed as dist
 
 
+_BLOCK = None
+
+
 def timed(fn, iters=10, warm=3):
+    """Device time per call.  A few milliseconds of unrelated GEMMs are queued first so that the
+    host has enqueued every timed launch before the first one starts (no launch gaps in the span)."""
+    global _BLOCK
+    if _BLOCK is None:
+        _BLOCK = torch.randn(8192, 8192, device="cuda", dtype=torch.bfloat16)
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
     dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(6):
+        torch.mm(_BLOCK, _BLOCK)
     e0.record()
     for _ in range(iters):
         fn()
@@ -40,7 +50,7 @@ def main():
     from lmms_engine_b200.parallel.fused_comm import FusedComm, out_head_route, qkv_head_route, qkv_kb_sources
 
     big = os.environ.get("FUSED_COMM_TIME") == "1"
-    fc = FusedComm(None, dev, wait_ms=20000, chunk_bytes=(1 << 30) if big else (64 << 20))
+    fc = FusedComm(dist.group.WORLD, dev, wait_ms=20000, chunk_bytes=(1 << 30) if big else (64 << 20))
     g = torch.Generator(device="cuda")
     rnd = lambda seed, *shape, scale=1.0: (torch.randn(*shape, device=dev, generator=g.manual_seed(seed)) * scale).to(torch.bfloat16)
     close = lambda a, b, tol=3e-2: (a.float() - b.float()).abs().max().item() <= tol * max(1.0, b.float().abs().max().item())
@@ -55,7 +65,13 @@ def main():
     xg = torch.empty(Ms * world, H, dtype=torch.bfloat16, device=dev)
     dist.all_gather_into_tensor(xg, x)
     torch.cuda.synchronize()
-    assert torch.equal(gathered, xg), "gathered rows differ"
+    if not torch.equal(gathered, xg):
+        for r in range(world):
+            blk, ref = gathered[r * Ms:(r + 1) * Ms], xg[r * Ms:(r + 1) * Ms]
+            bad = (blk != ref)
+            print(f"[rank {rank}] block {r}: {int(bad.sum())} of {bad.numel()} differ, zeros in block {int((blk == 0).sum())}, "
+                  f"bad rows {bad.any(1).nonzero().flatten()[:8].tolist()} flags {fc._buffers['ag'].flags.tolist()}", flush=True)
+        raise AssertionError("gathered rows differ")
     assert close(y, xg.float() @ w_up.float().t()), "ag_gemm"
     # ---- GEMM -> reduce-scatter (row-parallel down projection) -----------------------------------
     h = rnd(30 + rank, Ms * world, F, scale=0.5)
@@ -152,11 +168,43 @@ def main():
             ("a2a_gemm_o", lambda: fc.a2a_gemm([(ao, rank * hq_l * D)], wo, nq * D, key="o", k_rot=rank * hq_l * D // 64), base_o,
              2.0 * Tl * nq * D * Hm, (world - 1) / world * Tl * nq * D * 2),
         ]
+        solo = FusedComm(None, dev, wait_ms=20000, chunk_bytes=1 << 30)  # same kernels, no peers
+        only = {
+            "ag_gemm": (lambda: gemm(xg, w_up), lambda: solo.ag_gemm(xg, w_up)),
+            "gemm_rs": (lambda: gemm(h, w_dn), lambda: solo.gemm_rs(h, w_dn)),
+            "gemm_a2a_qkv": (lambda: gemm(xs, wqkv, bias=bqkv), None),
+            "a2a_gemm_o": (lambda: gemm(ao_seq, wo), None),
+        }
         for name, fused, base, flops, nv_bytes in cases:
             tf, tb = timed(fused), timed(base)
+            tg = timed(only[name][0])
+            ts = timed(only[name][1]) if only[name][1] is not None else None
             report.append({"op": name, "world": world, "fused_ms": round(tf, 4), "gemm_plus_nccl_ms": round(tb, 4),
+                           "gemm_only_ms": round(tg, 4), "fused_single_rank_ms": None if ts is None else round(ts, 4),
                            "speedup": round(tb / tf, 3), "tflops_fused": round(flops / tf / 1e9, 1),
                            "nvlink_out_bytes_per_rank": int(nv_bytes)})
+        # timeline of one launch of each pushing kernel (CTA 0, nanoseconds from its start)
+        fc.trace = torch.zeros(6, dtype=torch.int64, device=dev)
+        for name, fused in (("ag_gemm", cases[0][1]), ("a2a_gemm_o", cases[3][1])):
+            for _ in range(3):
+                fused()
+            torch.cuda.synchronize()
+            dist.barrier()
+            fused()
+            torch.cuda.synchronize()
+            tr = fc.trace.tolist()
+            print(f"[rank {rank}] {name} timeline us: handshake {(tr[1]-tr[0])/1e3:.1f} first_push {(tr[2]-tr[0])/1e3:.1f} "
+                  f"all_push {(tr[3]-tr[0])/1e3:.1f} last_source_seen {(tr[4]-tr[0])/1e3:.1f} end {(tr[5]-tr[0])/1e3:.1f}", flush=True)
+        fc.trace = None
+        # the exchange by itself: a one-tile-wide GEMM behind the same push (rate = pushed bytes / time)
+        w_thin = rnd(99, 256, H, scale=0.03)
+        for rows in (512, 2048, 8192):
+            xr = rnd(200 + rank, rows, H)
+            t_push = timed(lambda: fc.ag_gemm(xr, w_thin, key="thin"))
+            t_ref = timed(lambda: gemm(xg[: rows * world] if rows * world <= xg.shape[0] else torch.cat([xg] * (rows * world // xg.shape[0])), w_thin))
+            report.append({"op": "push_only_ag", "rows_per_rank": rows, "bytes_to_each_peer": rows * H * 2, "fused_ms": round(t_push, 4),
+                           "thin_gemm_only_ms": round(t_ref, 4),
+                           "peer_store_gbs": round(rows * H * 2 * (world - 1) / max(t_push - t_ref, 1e-6) / 1e6, 1)})
         _cuda.check_status()
         if rank == 0:
             for r in report:

@@ -98,12 +98,16 @@ def test_unset_flag_times_out_with_status():
 
     fc = _ctx()
     fc.wait_ms = 50
-    x, w = _rand(128, 64), _rand(64, 64)
-    buf = fc.buffer("ag", 128, 64)
-    buf.n_in += 1000  # pretend that earlier calls had raised the counter: this call's target is unreachable
-    fc.ag_gemm(x, w)
+    x, w = _rand(256, 64), _rand(64, 64)
+    y = fc.gemm_rs(x, w, key="stuck")
+    torch.cuda.synchronize()
+    _cuda.check_status()
+    fc._buffers["stuck"].n_out += 1000  # as if earlier calls had counted more tiles: this rank would wait for
+    fc.world, fc.rank = 2, 0             # a second rank's partial products, which nothing ever sends
+    fc._buffers["stuck"].ptrs.append(fc._buffers["stuck"].ptrs[0])
+    fc._buffers["stuck"].flag_ptrs.append(fc._buffers["stuck"].flag_ptrs[0])
+    fc.gemm_rs(x, w, key="stuck")
     torch.cuda.synchronize()
     with pytest.raises(RuntimeError, match="status"):
         _cuda.check_status()
-    ok = torch.ones(4, device="cuda").sum().item()  # the context still works
-    assert ok == 4.0
+    assert torch.ones(4, device="cuda").sum().item() == 4.0  # the context still works
