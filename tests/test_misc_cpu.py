@@ -148,3 +148,62 @@ def test_consolidate_multi_axis_and_uneven():
     # replicate axis takes one copy; zero-size shard on an axis is skipped
     assert torch.equal(fold_axis([full, full], ("R",)), full)
     assert torch.equal(fold_axis([full, full.new_empty((0, 4))], ("S", 0)), full)
+
+
+def test_example_configs_parse_into_config_objects():
+    """Every shipped example YAML must be accepted by the CLI config builder and the config classes."""
+    import glob
+
+    from lmms_engine_b200.datasets.config import DatasetConfig
+    from lmms_engine_b200.launch import cli
+    from lmms_engine_b200.models.config import ModelConfig
+    from lmms_engine_b200.train.config import TrainingArguments
+    from lmms_engine_b200.train.registry import TRAINER_REGISTER
+    import lmms_engine_b200.train  # noqa: F401  (registers the trainers)
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    files = sorted(glob.glob(os.path.join(root, "examples", "*", "*.yaml")))
+    files = [f for f in files if os.sep + "data" + os.sep not in f]
+    assert len(files) >= 5
+    known = set(TrainingArguments.field_names())
+    for f in files:
+        cfg = cli.build_config([f"config_yaml={f}"])
+        DatasetConfig(**cfg["dataset_config"])
+        ModelConfig(**cfg["model_config"])
+        assert cfg["trainer_type"] in TRAINER_REGISTER, (f, cfg["trainer_type"])
+        unknown = set(cfg["trainer_args"]) - known
+        assert not unknown, (f, unknown)
+        TrainingArguments(**cfg["trainer_args"])
+
+
+def test_tools_and_legacy_merge(tmp_path):
+    from lmms_engine_b200.merger import legacy
+    from lmms_engine_b200.tools import check_data, create_json_dataset, generate_default_yaml
+
+    out = tmp_path / "d.yaml"
+    generate_default_yaml.main(["--output", str(out)])
+    import yaml
+
+    cfg = yaml.safe_load(open(out))
+    assert cfg["trainer_type"] == "fsdp2_trainer" and "learning_rate" in cfg["trainer_args"]
+    # qa records -> messages -> check
+    src = tmp_path / "qa.jsonl"
+    src.write_text(json.dumps({"question": "what is this", "answer": "a cat", "image": "cat.png"}) + "\n")
+    create_json_dataset.main(["--input", str(src), "--output", str(tmp_path / "m.jsonl")])
+    rows = [json.loads(l) for l in open(tmp_path / "m.jsonl")]
+    rep = check_data.check(rows, str(tmp_path))
+    assert rep["rows"] == 1 and rep["media"] == {"image_url": 1} and rep["missing"] == [(0, "cat.png")]
+    assert rep["tokens_total"] >= 2000
+    # two "checkpoints" of dim-0 sharded tensors -> merged and averaged
+    for step, val in ((10, 1.0), (20, 3.0)):
+        d = tmp_path / "run" / f"checkpoint-{step}" / "pytorch_model_fsdp_0"
+        d.mkdir(parents=True)
+        for r in range(2):
+            torch.save({"w": torch.full((2, 3), val + r), "b": torch.full((1,), val)}, d / f"model_world_size_2_rank_{r}.pt")
+    one = legacy.merge_fsdp2_dir(str(tmp_path / "run" / "checkpoint-10"))
+    assert one["w"].shape == (4, 3) and one["w"][3, 0] == 2.0
+    out_dir = legacy.main(["--input_dir", str(tmp_path / "run"), "--merge", "--dtype", "float32"])
+    from lmms_engine_b200.models import hf_io
+
+    merged = hf_io.read_state_dict(str(out_dir))
+    assert torch.allclose(merged["w"][:2], torch.full((2, 3), 2.0)) and torch.allclose(merged["w"][2:], torch.full((2, 3), 3.0))
