@@ -102,6 +102,10 @@ class VLModel(nn.Module):
         self.visual = (Qwen3VisionTower if cfg.is_qwen3 else Qwen25VisionTower)(cfg.vision_config)
         self.language_model = (MoEDecoderLM if isinstance(cfg.text_config, MoEConfig) else DecoderLM)(cfg.text_config)
 
+    # ViT frame balancing over the flattened dp x cp ranks (set by the trainer / monkey_patch_kwargs)
+    vit_frame_parallel = False
+    vit_group = None
+
     # the trainer toggles these on whatever model it gets
     @property
     def sp_group(self):
@@ -125,9 +129,22 @@ class VLModel(nn.Module):
         deep_all, index_all = None, None
         for pix, grid, tok in ((pixel_values, image_grid_thw, cfg.image_token_id),
                                (pixel_values_videos, video_grid_thw, cfg.video_token_id)):
-            if pix is None or pix.numel() == 0:
+            balanced = self.vit_frame_parallel and self.vit_group is not None
+            if (pix is None or pix.numel() == 0) and not balanced:
                 continue
-            out = self.visual(pix.to(emb.dtype), grid)
+            if balanced:
+                # every rank takes part in the exchange, also one whose batch has no frames of this kind
+                from ..parallel.vit_parallel import balanced_vit_forward
+
+                vc = cfg.vision_config
+                if pix is None:
+                    pix = emb.new_zeros((0, vc.in_channels * vc.temporal_patch_size * vc.patch_size ** 2))
+                    grid = torch.zeros((0, 3), dtype=torch.long, device=emb.device)
+                out = balanced_vit_forward(self.visual, pix.to(emb.dtype), grid, self.vit_group)
+                if pix.shape[0] == 0:
+                    continue
+            else:
+                out = self.visual(pix.to(emb.dtype), grid)
             feats, deep = out if isinstance(out, tuple) else (out, None)
             mask = ids == tok
             # the k-th placeholder takes the k-th feature row: prefix count, no host round trip

@@ -38,17 +38,22 @@ def balanced_vit_forward(tower, patches: torch.Tensor, grid_thw: torch.Tensor, g
     got = _AllToAllRows.apply(patches.index_select(0, idx), send_p, recv_p, group)
     recv_frames = [shapes[s][i] for s in range(n) for i in sorted(range(len(gathered[s])), key=lambda j: (owner[s][j], j))
                    if owner[s][i] == me]
-    out = tower(got, recv_frames) if recv_frames else None
-    feats, deep = (out if isinstance(out, tuple) else (out, None)) if out is not None else (patches.new_zeros((0, 1)), None)
     unit = tower.cfg.spatial_merge_size ** 2
+    n_deep = len(getattr(tower, "deepstack_merger_list", []) or [])
+    if recv_frames:
+        out = tower(got, torch.tensor(recv_frames, dtype=torch.long, device=patches.device))
+        feats, deep = out if isinstance(out, tuple) else (out, None)
+    else:
+        # nothing assigned to this rank: still contribute (empty) rows so that the exchange and the
+        # autograd graph have the same shape everywhere
+        width = tower.cfg.out_hidden_size
+        feats = got.new_zeros((0, width)) + 0.0 * sum(p.sum() for p in tower.parameters() if p.requires_grad).to(got.dtype)
+        deep = [feats for _ in range(n_deep)] if n_deep else None
     back_send = [c // unit for c in recv_p]
     back_recv = [c // unit for c in send_p]
 
     def go_home(t):
-        if t is None or t.numel() == 0 and sum(back_recv) == 0:
-            return t
         home = _AllToAllRows.apply(t, back_send, back_recv, group)
-        inv = torch.empty_like(idx[::unit]) if False else None
         # undo the by-destination ordering at merged-token granularity
         m_starts = [0]
         for i in order:

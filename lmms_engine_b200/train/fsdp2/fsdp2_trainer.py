@@ -122,6 +122,8 @@ class FSDP2SFTTrainer:
             self.model.gradient_checkpointing_enable()
         if self.sp_size > 1 and self.pgm is not None:
             self.model.sp_group = self.pgm.cp_group
+        if getattr(self.model, "vit_frame_parallel", False) and self.pgm is not None and self.world_size > 1:
+            self.model.vit_group = self.pgm.dp_cp_group
         if self.runtime_kind == "native":
             self.model.to(device=self.device, dtype=dtype)
             return

@@ -59,3 +59,7 @@ def test_tensor_parallel_matches_unsharded():
 def test_ulysses_matches_unsharded(world):
     # 4 query heads / 1 KV head over 4 ranks also exercises KV-head replication
     assert "ulysses ok" in torchrun("tp_run.py", world, "ulysses")
+
+
+def test_vit_frame_parallel_matches_local_tower():
+    assert "vit frame parallel ok" in torchrun("vit_fp_run.py", 3)
