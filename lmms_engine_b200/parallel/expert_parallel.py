@@ -113,6 +113,25 @@ class ExpertParallel:
         return moe_ops.combine(back, w, perm)
 
 
+_PEER_DISPATCHERS = {}
+
+
+def make_dispatcher(group, num_experts: int, device):
+    """One dispatcher per (group, expert count): over peer memory when the group's ranks can map each
+    other's memory (``csrc/ep_comm.cu``), NCCL / gloo all-to-all otherwise."""
+    from . import fused_ops
+
+    key = (id(group), num_experts)
+    if key not in _PEER_DISPATCHERS:
+        ep = None
+        if torch.device(device).type == "cuda" and fused_ops.peer_memory_ok(group):
+            from .peer_expert_parallel import PeerExpertParallel
+
+            ep = PeerExpertParallel(group, num_experts, torch.device("cuda", torch.cuda.current_device()))
+        _PEER_DISPATCHERS[key] = ep if ep is not None else ExpertParallel(group, num_experts)
+    return _PEER_DISPATCHERS[key]
+
+
 def _local_tensor(p):
     """Expert parameters may be DTensors sharded over the ep mesh: compute on the local shard."""
     if hasattr(p, "to_local"):
@@ -134,4 +153,4 @@ def apply_expert_parallel(model: nn.Module, ep_mesh, ep_group) -> None:
         for name in ("gate_up_proj", "down_proj"):
             p = getattr(ex, name)
             setattr(ex, name, nn.Parameter(distribute_tensor(p.data, ep_mesh, [Shard(0)]), requires_grad=p.requires_grad))
-        block.ep = ExpertParallel(ep_group, ex.num_experts)
+        block.ep = make_dispatcher(ep_group, ex.num_experts, p.device)

@@ -28,12 +28,9 @@ from .fused_comm import FusedComm, HeadRoute, out_head_route, qkv_head_route, qk
 _CONTEXTS: Dict[int, Optional[FusedComm]] = {}
 
 
-def context_for(group) -> Optional[FusedComm]:
-    """The group's fused-collective context, created on first use (collectively), or None."""
-    key = id(group)
-    if key in _CONTEXTS:
-        return _CONTEXTS[key]
-    fc = None
+def peer_memory_ok(group) -> bool:
+    """Can the ranks of ``group`` map each other's memory?  CUDA, NCCL, at most eight ranks, one host,
+    and not disabled with ``LMMS_B200_FUSED_COMM=0``.  Collective on first use per group."""
     ok = (
         os.environ.get("LMMS_B200_FUSED_COMM", "1") != "0"
         and torch.cuda.is_available()
@@ -45,6 +42,16 @@ def context_for(group) -> Optional[FusedComm]:
         hosts = [None] * dist.get_world_size(group)
         dist.all_gather_object(hosts, socket.gethostname(), group=group)
         ok = len(set(hosts)) == 1
+    return ok
+
+
+def context_for(group) -> Optional[FusedComm]:
+    """The group's fused-collective context, created on first use (collectively), or None."""
+    key = id(group)
+    if key in _CONTEXTS:
+        return _CONTEXTS[key]
+    fc = None
+    ok = peer_memory_ok(group)
     if ok:
         fc = FusedComm(group, torch.device("cuda", torch.cuda.current_device()))
         fc._routes = {}

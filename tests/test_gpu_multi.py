@@ -55,3 +55,9 @@ def test_fused_comm_gemms_four_gpus():
 def test_fused_projections_in_decoder_two_gpus():
     out = _torchrun("fused_model_run.py", 2)
     assert "fused model ok" in out
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_expert_parallel_two_gpus():
+    out = _torchrun("peer_ep_run.py", 2)
+    assert "peer expert parallel ok" in out
