@@ -109,6 +109,14 @@ struct CommParams {
   // wait
   int wait_mode, rows_per_src, k_per_src, m_rot, k_rot;
   int own_direct;                          // mode 1: tiles of this rank's own rows read the source matrix (map tmB2)
+  // > 0: the last push_ctas CTAs of the grid only push (all eight warps) and the others only compute,
+  // so the copy neither delays an epilogue nor shares an SM with a main loop; 0: warps 2..7 of every
+  // CTA push before their tiles (right when no tile can finish before the blocks have landed)
+  int push_ctas;
+  // 1: the four epilogue warps join warps 2 and 3 in the copy before their first tile (right when no
+  // tile can finish before the blocks have landed); 0: only warps 2 and 3 copy, next to the tiles
+  int push_wide;
+  int in_inc;                              // > 0: arrive_in grows by this much per call (the copy is made outside the kernel)
   const int* kb_src;                       // mode 2: source rank of every 64-wide k-block (null: k / k_per_src)
   // scatter
   int scatter;
@@ -160,7 +168,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // a fused collective may have to wait for a rank that was launched later: its waits use the
   // caller's limit, every other launch keeps the short default
   const long long wait_limit = COMM ? cp.wait_cycles : kWaitCycleLimit;
-  const bool tracing = COMM && cp.trace != nullptr && blockIdx.x == 0;
+  const int n_gemm_ctas = COMM ? static_cast<int>(gridDim.x) - cp.push_ctas : static_cast<int>(gridDim.x);
+  const bool push_cta = COMM && static_cast<int>(blockIdx.x) >= n_gemm_ctas;
+  const bool tracing = COMM && cp.trace != nullptr && blockIdx.x == (cp.push_ctas > 0 ? n_gemm_ctas : 0);
   if (tracing && threadIdx.x == 0) cp.trace[0] = global_ns();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -191,7 +201,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     *abort_word = 0;
     fence_barrier_init();
   }
-  if (warp == 2) {
+  if (warp == 2 && !push_cta) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -233,7 +243,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // Copy this rank's block into every rank's buffer (COMM push).  Runs on warps 2..7 (192 threads):
   // the epilogue warps have nothing to drain before the first accumulator completes.  Every thread
   // executes every iteration, so the named barrier below always gets its full count.
-  constexpr int kPushThreads = 192;
+  // In a dedicated push CTA all 256 threads run it instead.
+  const int push_threads = push_cta ? kThreads : (cp.push_wide ? 192 : 64);
+  const int push_slices = cp.push_ctas > 0 ? cp.push_ctas : static_cast<int>(gridDim.x);
+  const int push_slice = cp.push_ctas > 0 ? static_cast<int>(blockIdx.x) - n_gemm_ctas : static_cast<int>(blockIdx.x);
   auto push_blocks = [&](const int ct) {
     const int pw = ct >> 5;
     bool okp = true;
@@ -256,16 +269,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const long long sld = cp.seg_src_ld[sg];
           const int vpr = cp.seg_cols[sg] >> 3;  // 16-byte vectors per row
           const long long total = static_cast<long long>(cp.push_rows) * vpr;
-          const long long per = (total + gridDim.x - 1) / gridDim.x;
-          const long long v_hi = min(total, per * (blockIdx.x + 1));
+          const long long per = (total + push_slices - 1) / push_slices;
+          const long long v_hi = min(total, per * (push_slice + 1));
           const __nv_bfloat16* s0 = cp.seg_src[sg] + r * cp.push_block_rows * sld;
           __nv_bfloat16* d0 = dst + cp.seg_dst_col[sg];
-          for (long long v = per * blockIdx.x + ct; v < v_hi; v += kPushThreads * 8) {
+          for (long long v = per * push_slice + ct; v < v_hi; v += push_threads * 8) {
             uint4 val[8];
             long long dof[8];
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-              const long long vv = v + u * kPushThreads;
+              const long long vv = v + u * push_threads;
               if (vv < v_hi) {
                 const long long row = vv / vpr;
                 const int c = static_cast<int>(vv - row * vpr) * 8;
@@ -275,11 +288,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
 #pragma unroll
             for (int u = 0; u < 8; ++u)
-              if (v + u * kPushThreads < v_hi) *reinterpret_cast<uint4*>(d0 + dof[u]) = val[u];
+              if (v + u * push_threads < v_hi) *reinterpret_cast<uint4*>(d0 + dof[u]) = val[u];
           }
         }
       }
-      bar_sync_named(1, kPushThreads);
+      bar_sync_named(1, push_threads);
       if (ct == 0 && okp) {
         flag_add_release(cp.pflags[r] + cp.rank, 1u);
         if (tracing && d == 0) cp.trace[2] = global_ns();
@@ -288,7 +301,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   };
 
-  if (warp == 0) {
+  if (push_cta) {
+    // ------------------------------------------------------------ dedicated push CTA
+    push_blocks(threadIdx.x);
+  } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tmA);
@@ -304,7 +320,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (tracing) cp.trace[4] = global_ns();
         return true;
       };
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = blockIdx.x; t < total_tiles && ok; t += n_gemm_ctas) {
         int ex, mb, nb, kb_lo, kb_n;
         decode(t, ex, mb, nb, kb_lo, kb_n);
         if (!tile_active(mb, nb)) continue;
@@ -376,7 +392,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t idesc = umma_idesc_bf16_major(BM, BN, p.a_mn_major, p.b_mn_major);
       uint32_t it = 0, tl = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = blockIdx.x; t < total_tiles && ok; t += n_gemm_ctas) {
         int ex, mb, nb, kb_lo, kb_n;
         decode(t, ex, mb, nb, kb_lo, kb_n);
         if (!tile_active(mb, nb)) continue;
@@ -417,7 +433,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (COMM && warp < 4) {
     // ------------------------------------------------------------ push (warps 2, 3; the epilogue warps help)
-    if (cp.push) push_blocks((warp - 2) * 32 + lane);
+    if (cp.push && cp.push_ctas == 0) push_blocks((warp - 2) * 32 + lane);
   } else if (warp >= 4) {
     // ------------------------------------------------------------ epilogue (warps 4..7)
     const int q = warp - 4;  // TMEM lane quadrant == warp % 4
@@ -427,8 +443,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     bool ok = true;
     uint32_t sc_open = 0;  // COMM scatter: destinations known to have drained their slots
     bool own_ready = false;
-    if (COMM && cp.push) push_blocks(64 + q * 32 + lane);
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+    if (COMM && cp.push && cp.push_ctas == 0 && cp.push_wide) push_blocks(64 + q * 32 + lane);
+    for (int t = blockIdx.x; t < total_tiles && ok; t += n_gemm_ctas) {
       int ex, mb, nb, kb_lo, kb_n;
       decode(t, ex, mb, nb, kb_lo, kb_n);
       if (!tile_active(mb, nb)) continue;
@@ -718,7 +734,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (threadIdx.x == 0 && p.status != nullptr) atomicExch(p.status, kStatusBarrierTimeout);
   }
   __syncthreads();
-  if (warp == 2) {
+  if (warp == 2 && !push_cta) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -841,10 +857,16 @@ static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMa
   if (ctas <= 0) return 0;
   CommParams cp{};
   if (comm != nullptr) {
-    // arrival counters grow by one per CTA and call on every rank (all ranks launch the same grid)
+    // arrival counters grow by one per (pushing) CTA and call on every rank (all ranks launch the same grid)
     cp = *comm;
-    cp.in_target += static_cast<uint32_t>(ctas);
-    cp.out_target += static_cast<uint32_t>(cp.scatter == 1 ? cp.out_inc_tiles : ctas);
+    if (cp.push_ctas > 0) {
+      // dedicated push CTAs ride on top of the compute CTAs
+      if (cp.push_ctas > g_num_sms / 2) cp.push_ctas = g_num_sms / 2;
+      if (ctas > g_num_sms - cp.push_ctas) ctas = g_num_sms - cp.push_ctas;
+      ctas += cp.push_ctas;
+    }
+    cp.in_target += static_cast<uint32_t>(cp.in_inc > 0 ? cp.in_inc : (cp.push_ctas > 0 ? cp.push_ctas : ctas));
+    cp.out_target += static_cast<uint32_t>(cp.scatter == 1 ? cp.out_inc_tiles : ctas - cp.push_ctas);
     cp.push_done_target += static_cast<uint32_t>(ctas);
   }
   if (launched != nullptr) *launched = ctas;
@@ -913,6 +935,10 @@ int b200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, i
 //  [56..63] scatter buffer of every rank [64..71] its flag block on every rank [72] max CTAs
 //  [76] tiles of this rank's own rows read the pushed matrix itself (all-gather mode)
 //  [77] optional device buffer of six u64 for CTA 0's timeline (see CommParams::trace)
+//  [80] > 0: the blocks are copied outside the kernel (copy engines) and arrive_in grows by this per call;
+//       the segment fields then only describe this rank's own block for [76]
+//  [79] epilogue warps join the copy (1) or only warps 2 and 3 copy next to the tiles (0)
+//  [78] number of dedicated push CTAs (all-gather and re-gather pushes; 0 = push from warps 2..7 of every CTA)
 // A is K-major; B is [N,K] or, with b_mn_major, [K,N].  With a scatter mode C is not written and may be
 // null.  Returns the number of CTAs launched (every flag counter of this call grows by that much on
 // every rank) or a negative error code.
@@ -968,6 +994,10 @@ int b200_gemm_comm_bf16(const void* A, const void* B, void* C, int M, int N, int
   const int max_ctas = static_cast<int>(ca[72]);
   cp.own_direct = static_cast<int>(ca[76]);
   cp.trace = reinterpret_cast<unsigned long long*>(ca[77]);
+  cp.push_ctas = cp.push && cp.wait_mode != 2 ? static_cast<int>(ca[78]) : 0;
+  if (cp.push_ctas < 0) cp.push_ctas = 0;
+  cp.push_wide = static_cast<int>(ca[79]);
+  cp.in_inc = static_cast<int>(ca[80]);
   cp.out_inc_tiles = 4 * (cp.rows_per_src > 0 ? cp.rows_per_src / BM : 0) * ((N + BN - 1) / BN);
   const int tiles_m = (M + BM - 1) / BM, n_kb = (K + BK - 1) / BK;
   // row blocks / k-ranges of one source must be whole tiles, or a tile would mix sources
@@ -982,7 +1012,7 @@ int b200_gemm_comm_bf16(const void* A, const void* B, void* C, int M, int N, int
   else rc |= make_map(&tB, B, K, N, ldb, 64, BK, true);
   if (cp.own_direct) {
     // tiles of this rank's own rows read the matrix that is being pushed, not its copy
-    if (!(cp.push && cp.push_nseg == 1 && (cp.wait_mode == 1 || cp.wait_mode == 2))) return -13;
+    if (!(cp.push_nseg == 1 && (cp.wait_mode == 1 || cp.wait_mode == 2))) return -13;
     if (cp.wait_mode == 1) {
       if (cp.seg_cols[0] != K) return -13;
       rc |= make_map(&tOwn, cp.seg_src[0], cp.push_rows, K, cp.seg_src_ld[0], BK, BM, true);

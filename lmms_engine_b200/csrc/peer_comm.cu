@@ -82,6 +82,16 @@ __global__ void peer_barrier_kernel(PeerPtrs pads, int n, int self, unsigned int
   }
 }
 
+// flags[i] += 1 with release semantics at system scope, one lane per flag: publishes what earlier
+// operations of the stream (copy-engine transfers included) wrote into the peers' memory
+__global__ void peer_signal_kernel(PeerPtrs flags, int n) {
+  const int t = threadIdx.x;
+  if (t < n) {
+    __threadfence_system();
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(static_cast<unsigned int*>(flags.p[t])), "r"(1u) : "memory");
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -122,6 +132,29 @@ int b200_peer_barrier(const void* const* pad_ptrs, int n, int self, unsigned int
   for (int i = 0; i < n; ++i) pp.p[i] = const_cast<void*>(pad_ptrs[i]);
   const long long limit = static_cast<long long>(timeout_ms) * 1900000LL;
   peer_barrier_kernel<<<1, 32, 0, st>>>(pp, n, self, epoch, status, limit);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// One device-to-device copy on the stream (copy engines; the destination may be a peer-mapped address).
+int b200_peer_memcpy(void* dst, const void* src, long n_bytes, cudaStream_t st) {
+  if (n_bytes <= 0) return 0;
+  return cudaMemcpyAsync(dst, src, static_cast<size_t>(n_bytes), cudaMemcpyDeviceToDevice, st) == cudaSuccess ? 0 : -4;
+}
+
+// Pitched device-to-device copy (a column block of a matrix) on the stream.
+int b200_peer_memcpy2d(void* dst, long dpitch, const void* src, long spitch, long width_bytes, long height, cudaStream_t st) {
+  if (width_bytes <= 0 || height <= 0) return 0;
+  return cudaMemcpy2DAsync(dst, static_cast<size_t>(dpitch), src, static_cast<size_t>(spitch), static_cast<size_t>(width_bytes),
+                           static_cast<size_t>(height), cudaMemcpyDeviceToDevice, st) == cudaSuccess ? 0 : -4;
+}
+
+// Add one to each of the n flags (peer-mapped addresses), ordered after everything queued on the stream.
+int b200_peer_signal(const void* const* flag_ptrs, int n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (n > kMaxPeers) return -10;
+  PeerPtrs pp{};
+  for (int i = 0; i < n; ++i) pp.p[i] = const_cast<void*>(flag_ptrs[i]);
+  peer_signal_kernel<<<1, 32, 0, st>>>(pp, n);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

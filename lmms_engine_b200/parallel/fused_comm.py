@@ -32,6 +32,9 @@ import torch.distributed as dist
 from ..ops import _cuda
 
 _cuda.register("b200_gemm_comm_bf16", "gemm_sm100", "pppiiiiiiifppps")
+_cuda.register("b200_peer_memcpy", "peer_comm", "ppls")
+_cuda.register("b200_peer_signal", "peer_comm", "pis")
+_cuda.register("b200_peer_memcpy2d", "peer_comm", "plpllls")
 
 MAX_RANKS = 8
 _FLAG_WORDS = 3 * MAX_RANKS
@@ -172,6 +175,13 @@ class FusedComm:
         self._turn: Dict = {}
         self.max_ctas = 0
         self.launches = 0
+        self.push_ctas: Optional[int] = None  # None: chosen per call from the copy volume; 0: push from every CTA
+        self.ag_engine: Optional[str] = None  # force "sm" or "ce" for the all-gather copy
+        self.a2a_engine: Optional[str] = None  # likewise for the column-block exchange of a2a_gemm
+        # GEMM -> reduce-scatter with the scattering epilogue beat GEMM + NCCL on 2 and 4 ranks (1.22x, 1.11x)
+        # and lost on 8 (0.86x: peer stores from the epilogue warps reach ~230 GB/s there)
+        self.rs_fused_max_world = 4
+        self._side: Optional[torch.cuda.Stream] = None
         self.trace: Optional[torch.Tensor] = None  # set to an int64[6] device tensor to record a launch timeline
 
     def buffer(self, key, rows: int, cols: int, rotate: bool = False) -> CommBuffer:
@@ -193,12 +203,13 @@ class FusedComm:
 
     # ------------------------------------------------------------------ launch
     def _launch(self, a, b, c, M, N, K, b_mn, alpha, bias, *, push=None, wait_mode=0, rows_per_src=0, k_per_src=0,
-                kb_src=None, m_rot=0, k_rot=0, scatter=None, own_direct=False):
-        ca = (ctypes.c_longlong * 80)()
+                kb_src=None, m_rot=0, k_rot=0, scatter=None, own_direct=False, push_ctas=0):
+        ca = (ctypes.c_longlong * 96)()
         ca[0], ca[1], ca[2] = self.rank, self.world, self.wait_ms
         if push is not None:
             buf: CommBuffer = push["buf"]
-            ca[3] = 1
+            ca[3] = 0 if push.get("external") else 1
+            ca[80] = 1 if push.get("external") else 0
             ca[6] = push["block_rows"]
             ca[7] = buf.t.stride(0)
             ca[8] = push["dst_off"]
@@ -235,6 +246,11 @@ class FusedComm:
                 ca[56 + r], ca[64 + r] = sb.ptrs[r], sb.flag_ptrs[r]
         ca[72] = self.max_ctas
         ca[76] = 1 if own_direct else 0
+        push_ctas = min(int(push_ctas), 64) if (push is not None and wait_mode != 2 and not push.get("external")) else 0
+        ca[78] = push_ctas
+        # peer stores are limited per SM, so the copy is spread over all CTAs; the epilogue warps join it
+        # only where no tile can complete before the blocks have landed (every tile needs every source)
+        ca[79] = 1 if wait_mode == 2 else 0
         if self.trace is not None:  # CTA 0's timeline of this launch, six globaltimer stamps
             ca[77] = self.trace.data_ptr()
         st = _cuda.status_word(self.device)
@@ -245,37 +261,72 @@ class FusedComm:
         )
         if ctas <= 0:
             raise RuntimeError(f"b200_gemm_comm_bf16 refused the launch (code {ctas}) for M={M} N={N} K={K}")
-        if push is not None:
-            push["buf"].n_in += ctas
+        if push is not None and push.get("external"):
+            push["buf"].n_in += 1
+        elif push is not None:
+            push["buf"].n_in += push_ctas if push_ctas > 0 else ctas
             if ca[21]:
-                push["buf"].n_done += ctas
+                push["buf"].n_done += push_ctas if push_ctas > 0 else ctas
         if scatter is not None:
             if scatter["mode"] == 1:
                 # one count per epilogue warp and tile that a rank sends to another
                 scatter["buf"].n_out += 4 * (rows_per_src // 128) * ((N + 255) // 256)
                 scatter["buf"].n_done += ctas
             else:
-                scatter["buf"].n_out += ctas
+                scatter["buf"].n_out += ctas - push_ctas
         self.launches += 1
         return ctas
+
+    def _push_ctas(self, push_bytes: float, flops: float) -> int:
+        """Dedicated copy CTAs are off by default: measured peer-store throughput is a few GB/s per SM
+        whatever the thread count, so a copy confined to a few SMs is slower than one spread over all."""
+        return 0
 
     @staticmethod
     def _bshape(w: torch.Tensor, b_mn: bool) -> Tuple[int, int]:
         return (w.shape[1], w.shape[0]) if b_mn else (w.shape[0], w.shape[1])  # (N, K)
 
     # ------------------------------------------------------------------ all-gather rows -> GEMM
-    def ag_gemm(self, x: torch.Tensor, w: torch.Tensor, bias=None, b_mn: bool = False, key="ag"):
+    def ag_gemm(self, x: torch.Tensor, w: torch.Tensor, bias=None, b_mn: bool = False, key="ag", engine: Optional[str] = None):
         """``y = concat_r(x_r) @ op(w)^T (+ bias)``; returns ``(y, gathered)`` where ``gathered`` is the
-        shared gather buffer (valid until the next call with the same key)."""
+        shared gather buffer (valid until the second next call with the same key).
+
+        ``engine="ce"``: the copy engines move this rank's rows into the peers' buffers on a side
+        stream (one device-to-device copy and one flag per peer) while the kernel computes the rows
+        it already has and waits, tile by tile, for the flags.  ``engine="sm"``: two warps of every
+        CTA store the rows themselves.  Default: ``ce`` for more than two ranks - stores issued next
+        to a running main loop reach only about 150 GB/s, which hides one peer's block but not more."""
         Ms, K = x.shape
         N, Kw = self._bshape(w, b_mn)
         if K != Kw or Ms % 128:
             raise ValueError("ag_gemm needs matching K and a multiple of 128 rows per rank")
+        if engine is None:
+            engine = self.ag_engine or ("ce" if self.world > 2 else "sm")
         buf = self.buffer(key, Ms * self.world, K, rotate=True)
         y = torch.empty((Ms * self.world, N), dtype=torch.bfloat16, device=x.device)
         push = dict(buf=buf, block_rows=0, dst_off=self.rank * Ms * buf.t.stride(0), rows=Ms, segs=[(x, 0, K)])
+        if engine == "ce" and self.world > 1:
+            x = x if x.is_contiguous() else x.contiguous()
+            push["segs"] = [(x, 0, K)]
+            push["external"] = True
+            main = torch.cuda.current_stream()
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=self.device)
+            ready = torch.cuda.Event()
+            ready.record(main)
+            self._side.wait_event(ready)
+            nbytes, off = Ms * K * 2, self.rank * Ms * K * 2
+            for d in range(self.world):
+                r = (self.rank - 1 - d) % self.world  # the order in which the ranks need this block; own copy last
+                _cuda.call("b200_peer_memcpy", buf.ptrs[r] + off, x.data_ptr(), nbytes, self._side.cuda_stream)
+                flag = (ctypes.c_void_p * 1)(buf.flag_ptrs[r] + 4 * self.rank)
+                _cuda.call("b200_peer_signal", ctypes.addressof(flag), 1, self._side.cuda_stream)
+            done = torch.cuda.Event()
+            done.record(self._side)
         self._launch(buf.t, w, y, Ms * self.world, N, K, b_mn, 1.0, bias, push=push, wait_mode=1, rows_per_src=Ms,
                      m_rot=self.rank * (Ms // 128), own_direct=True)
+        if push.get("external"):
+            torch.cuda.current_stream().wait_event(done)  # x and the buffer stay valid for what follows
         return y, buf.t
 
     # ------------------------------------------------------------------ GEMM -> reduce-scatter rows
@@ -298,8 +349,11 @@ class FusedComm:
             push = dict(buf=gb, block_rows=0, dst_off=self.rank * xl.shape[0] * gb.t.stride(0), rows=xl.shape[0],
                         segs=[(xl, 0, xl.shape[1])])
             gathered = gb.t
+        pc = 0
+        if push is not None:
+            pc = self.push_ctas if self.push_ctas is not None else self._push_ctas(push["rows"] * push["segs"][0][2] * 2.0 * self.world, 2.0 * M * N * K)
         self._launch(x, w, None, M, N, K, b_mn, 1.0, None, push=push, rows_per_src=Ms,
-                     m_rot=((self.rank + 1) % self.world) * (Ms // 128), scatter=scatter)
+                     m_rot=((self.rank + 1) % self.world) * (Ms // 128), scatter=scatter, push_ctas=pc)
         return (out, gathered) if regather is not None else out
 
     # ------------------------------------------------------------------ GEMM -> all-to-all by heads
@@ -318,7 +372,7 @@ class FusedComm:
 
     # ------------------------------------------------------------------ all-to-all by heads -> GEMM
     def a2a_gemm(self, parts: Sequence[Tuple[torch.Tensor, int]], w: torch.Tensor, cols_total: int, kb_src=None,
-                 b_mn: bool = False, bias=None, key="o", k_rot: int = 0, rotate: bool = True):
+                 b_mn: bool = False, bias=None, key="o", k_rot: int = 0, rotate: bool = True, engine: Optional[str] = None):
         """``parts`` = ``[(src [world*Tl, c_i], dst_col_i), ...]``: rows ``[r*Tl, (r+1)*Tl)`` of every
         source go to rank r at columns ``dst_col_i``; then ``y = gathered[Tl, cols_total] @ op(w)^T``.
         Returns ``(y, gathered)``; ``gathered`` is the shared buffer of ``key``."""
@@ -334,8 +388,31 @@ class FusedComm:
         kps = cols_total // self.world
         # a single source whose block sits at my rank's column range can be read in place
         direct = len(parts) == 1 and kb_src is None and parts[0][1] == self.rank * kps and parts[0][0].shape[1] == kps
+        engine = engine or self.a2a_engine or ("ce" if self.world > 2 else "sm")
+        if engine == "ce" and self.world > 1:
+            # copy engines move the column blocks (pitched copies) on a side stream; one flag per peer
+            push["external"] = True
+            main = torch.cuda.current_stream()
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=self.device)
+            ready = torch.cuda.Event()
+            ready.record(main)
+            self._side.wait_event(ready)
+            for d in range(self.world):
+                r = (self.rank - 1 - d) % self.world if direct else (self.rank - d) % self.world
+                for src, dcol, cols in segs:
+                    if not _mat_ok(src):
+                        raise TypeError("a2a_gemm sources must be 2-D bf16 CUDA matrices with unit inner stride")
+                    _cuda.call("b200_peer_memcpy2d", buf.ptrs[r] + dcol * 2, cols_total * 2,
+                               src.data_ptr() + r * Tl * src.stride(0) * 2, src.stride(0) * 2, cols * 2, Tl, self._side.cuda_stream)
+                flag = (ctypes.c_void_p * 1)(buf.flag_ptrs[r] + 4 * self.rank)
+                _cuda.call("b200_peer_signal", ctypes.addressof(flag), 1, self._side.cuda_stream)
+            done = torch.cuda.Event()
+            done.record(self._side)
         self._launch(buf.t, w, y, Tl, N, cols_total, b_mn, 1.0, bias, push=push, wait_mode=2, k_per_src=kps,
                      kb_src=kb_src, k_rot=k_rot, own_direct=direct)
+        if push.get("external"):
+            torch.cuda.current_stream().wait_event(done)
         return y, buf.t
 
 

@@ -23,6 +23,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import gemm as gemm_ops
+from . import tp_ops
 from .fused_comm import FusedComm, HeadRoute, out_head_route, qkv_head_route, qkv_kb_sources
 
 _CONTEXTS: Dict[int, Optional[FusedComm]] = {}
@@ -95,7 +96,11 @@ class _ColumnLinear(torch.autograd.Function):
         x, w = ctx.saved_tensors
         fc = ctx.fc
         dy = _c2(dy, dy.shape[0])
-        dx, xg = fc.gemm_rs(dy, w, b_mn=True, key="rs_dx", regather=(x, "regather_x"))
+        if fc.world <= fc.rs_fused_max_world:
+            dx, xg = fc.gemm_rs(dy, w, b_mn=True, key="rs_dx", regather=(x, "regather_x"))
+        else:
+            dx = tp_ops._reduce_scatter(gemm_ops.matmul_nn(dy, w), fc.group)
+            xg = tp_ops._all_gather(x, fc.group)
         dw = gemm_ops.matmul_tn(dy, xg)
         db = dy.sum(0, dtype=torch.float32).to(dy.dtype) if ctx.has_bias else None
         return dx, dw, db, None
@@ -107,7 +112,9 @@ class _RowLinear(torch.autograd.Function):
         ctx.fc = fc
         x = _c2(x, x.shape[0])
         ctx.save_for_backward(x, w)
-        return fc.gemm_rs(x, w, key="rs_y")
+        if fc.world <= fc.rs_fused_max_world:
+            return fc.gemm_rs(x, w, key="rs_y")
+        return tp_ops._reduce_scatter(gemm_ops.matmul_nt(x, w), fc.group)
 
     @staticmethod
     def backward(ctx, dy):

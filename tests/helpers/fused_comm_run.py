@@ -73,6 +73,11 @@ def main():
                   f"bad rows {bad.any(1).nonzero().flatten()[:8].tolist()} flags {fc._buffers['ag'].flags.tolist()}", flush=True)
         raise AssertionError("gathered rows differ")
     assert close(y, xg.float() @ w_up.float().t()), "ag_gemm"
+    # the same product with the copy engines moving the rows (side stream + per-source flags)
+    for _ in range(3):
+        y2, gathered2 = fc.ag_gemm(x, w_up, key="ag_ce", engine="ce")
+    torch.cuda.synchronize()
+    assert torch.equal(gathered2, xg) and close(y2, xg.float() @ w_up.float().t()), "ag_gemm (copy engines)"
     # ---- GEMM -> reduce-scatter (row-parallel down projection) -----------------------------------
     h = rnd(30 + rank, Ms * world, F, scale=0.5)
     w_dn = rnd(40 + rank, H, F, scale=0.03)
@@ -114,11 +119,12 @@ def main():
     # output projection: attention output [T, hq_l*D] per rank -> my tokens, all heads
     ao = rnd(70 + rank, Tl * world, hq_l * D)
     wo = rnd(71, Hm, nq * D, scale=0.03)
-    yo, gath = fc.a2a_gemm([(ao, rank * hq_l * D)], wo, nq * D, key="o", k_rot=rank * hq_l * D // 64)
     ao_seq = ulysses.head_to_seq(ao.view(Tl * world, hq_l, D), dist.group.WORLD).reshape(Tl, nq * D)
-    torch.cuda.synchronize()
-    assert torch.equal(gath, ao_seq), "a2a gather"
-    assert close(yo, ao_seq.float() @ wo.float().t()), "a2a_gemm"
+    for eng in ("sm", "ce", "ce"):
+        yo, gath = fc.a2a_gemm([(ao, rank * hq_l * D)], wo, nq * D, key="o_" + eng, k_rot=rank * hq_l * D // 64, engine=eng)
+        torch.cuda.synchronize()
+        assert torch.equal(gath, ao_seq), "a2a gather " + eng
+        assert close(yo, ao_seq.float() @ wo.float().t()), "a2a_gemm " + eng
     # input gradient of the output projection: GEMM -> heads
     dyo = rnd(80 + rank, Tl, Hm, scale=0.5)
     oroute = out_head_route(nq, D, world, dev)
@@ -131,13 +137,15 @@ def main():
         # input gradient of the QKV projection: three gathered segments, k-blocks waited per source
         dq, dk, dv = rnd(90 + rank, Tl * world, hq_l * D), rnd(91 + rank, Tl * world, hkv_l * D), rnd(92 + rank, Tl * world, hkv_l * D)
         kb = qkv_kb_sources(nq, nkv, D, world, dev)
-        dxs, dqkv = fc.a2a_gemm([(dq, rank * hq_l * D), (dk, nq * D + rank * hkv_l * D), (dv, (nq + nkv) * D + rank * hkv_l * D)],
-                                wqkv, (nq + 2 * nkv) * D, kb_src=kb, b_mn=True, key="dqkv", k_rot=rank * hq_l * D // 64)
         seq = lambda t, hh: ulysses.head_to_seq(t.view(Tl * world, hh, D), dist.group.WORLD).reshape(Tl, -1)
         full = torch.cat([seq(dq, hq_l), seq(dk, hkv_l), seq(dv, hkv_l)], 1)
-        torch.cuda.synchronize()
-        assert torch.equal(dqkv, full), "qkv gradient gather"
-        assert close(dxs, full.float() @ wqkv.float(), 4e-2), "a2a_gemm (three segments)"
+        for eng in ("sm", "ce", "ce"):
+            dxs, dqkv = fc.a2a_gemm([(dq, rank * hq_l * D), (dk, nq * D + rank * hkv_l * D), (dv, (nq + nkv) * D + rank * hkv_l * D)],
+                                    wqkv, (nq + 2 * nkv) * D, kb_src=kb, b_mn=True, key="dqkv_" + eng, k_rot=rank * hq_l * D // 64,
+                                    engine=eng)
+            torch.cuda.synchronize()
+            assert torch.equal(dqkv, full), "qkv gradient gather " + eng
+            assert close(dxs, full.float() @ wqkv.float(), 4e-2), "a2a_gemm (three segments) " + eng
     _cuda.check_status()
 
     if big:
@@ -161,19 +169,24 @@ def main():
             return gemm(s, wo)
 
         cases = [
-            ("ag_gemm", lambda: fc.ag_gemm(x, w_up), base_ag, 2.0 * Ms * world * F * H, (world - 1) * Ms * H * 2),
+            ("ag_gemm", lambda: fc.ag_gemm(x, w_up, engine="sm"), base_ag, 2.0 * Ms * world * F * H, (world - 1) * Ms * H * 2),
+            ("ag_gemm_ce", lambda: fc.ag_gemm(x, w_up, key="ag_ce", engine="ce"), base_ag, 2.0 * Ms * world * F * H, (world - 1) * Ms * H * 2),
             ("gemm_rs", lambda: fc.gemm_rs(h, w_dn), base_rs, 2.0 * Ms * world * F * H, (world - 1) * Ms * H * 2),
             ("gemm_a2a_qkv", lambda: fc.gemm_a2a(xs, wqkv, route, bias=bqkv, key=("qkv", 0)), base_qkv,
              2.0 * Tl * (nq + 2 * nkv) * D * Hm, (world - 1) / world * Tl * (nq + 2 * nkv) * D * 2),
-            ("a2a_gemm_o", lambda: fc.a2a_gemm([(ao, rank * hq_l * D)], wo, nq * D, key="o", k_rot=rank * hq_l * D // 64), base_o,
+            ("a2a_gemm_o", lambda: fc.a2a_gemm([(ao, rank * hq_l * D)], wo, nq * D, key="o_sm", k_rot=rank * hq_l * D // 64, engine="sm"), base_o,
+             2.0 * Tl * nq * D * Hm, (world - 1) / world * Tl * nq * D * 2),
+            ("a2a_gemm_o_ce", lambda: fc.a2a_gemm([(ao, rank * hq_l * D)], wo, nq * D, key="o_ce", k_rot=rank * hq_l * D // 64, engine="ce"), base_o,
              2.0 * Tl * nq * D * Hm, (world - 1) / world * Tl * nq * D * 2),
         ]
         solo = FusedComm(None, dev, wait_ms=20000, chunk_bytes=1 << 30)  # same kernels, no peers
         only = {
             "ag_gemm": (lambda: gemm(xg, w_up), lambda: solo.ag_gemm(xg, w_up)),
+            "ag_gemm_ce": (lambda: gemm(xg, w_up), None),
             "gemm_rs": (lambda: gemm(h, w_dn), lambda: solo.gemm_rs(h, w_dn)),
             "gemm_a2a_qkv": (lambda: gemm(xs, wqkv, bias=bqkv), None),
             "a2a_gemm_o": (lambda: gemm(ao_seq, wo), None),
+            "a2a_gemm_o_ce": (lambda: gemm(ao_seq, wo), None),
         }
         for name, fused, base, flops, nv_bytes in cases:
             tf, tb = timed(fused), timed(base)
@@ -185,7 +198,7 @@ def main():
                            "nvlink_out_bytes_per_rank": int(nv_bytes)})
         # timeline of one launch of each pushing kernel (CTA 0, nanoseconds from its start)
         fc.trace = torch.zeros(6, dtype=torch.int64, device=dev)
-        for name, fused in (("ag_gemm", cases[0][1]), ("a2a_gemm_o", cases[3][1])):
+        for name, fused in (("ag_gemm", cases[0][1]), ("a2a_gemm_o", cases[4][1])):
             for _ in range(3):
                 fused()
             torch.cuda.synchronize()
