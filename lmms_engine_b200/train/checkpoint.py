@@ -44,6 +44,19 @@ def latest_checkpoint(output_dir: str) -> Optional[str]:
     return ck[-1] if ck else None
 
 
+def latest_resumable_checkpoint(output_dir: str) -> Optional[str]:
+    """Newest checkpoint that finished saving.  Directories written by tools that leave no completion
+    marker are accepted only if no checkpoint of the run has one."""
+    from ..utils import failure
+
+    ck = list_checkpoints(output_dir)
+    if not ck:
+        return None
+    if not any(os.path.exists(os.path.join(p, failure.MARKER)) for p in ck):
+        return ck[-1]
+    return failure.latest_valid_checkpoint(output_dir, ck)
+
+
 def rotate_checkpoints(output_dir: str, save_total_limit: Optional[int]) -> None:
     if not save_total_limit or save_total_limit <= 0:
         return

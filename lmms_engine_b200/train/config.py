@@ -81,6 +81,9 @@ class TrainingArguments:
     enable_memory_snapshot: Optional[bool] = False
     memory_snapshot_config: Optional[Dict[str, Any]] = None
     enable_cuda_event_profiler: Optional[bool] = False
+    # > 0: ranks publish a heartbeat in the process group's store between steps and stop with a clear
+    # error when a peer reported a failure or stayed silent for this many seconds
+    heartbeat_timeout: float = 0.0
     cuda_event_profiler_config: Optional[Dict[str, Any]] = None
     ep_degree: Optional[int] = 1
     sp_ulysses_degree: Optional[int] = 1

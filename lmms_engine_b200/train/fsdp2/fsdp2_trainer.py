@@ -39,6 +39,7 @@ from ...parallel.owner_sharded import OwnerShardedRuntime
 from ...utils import schedulers
 from ...utils.compute_tracker import ComputeTracker
 from ...utils.ema_utils import EMAHelper
+from ...utils import failure
 from ...utils.logging_utils import logger
 from ...utils.profiler import CudaEventProfiler, MemorySnapshotProfiler, StepProfiler
 from ...utils.tracking import Tracking
@@ -387,6 +388,11 @@ class FSDP2SFTTrainer:
                     self.processing_class.save_pretrained(out)
                 except Exception as e:
                     logger.warning(f"could not save processor: {e}")
+        ckpt.barrier()  # every rank's files are on disk
+        if r == 0:
+            # the marker makes the checkpoint eligible for resume; a job that dies before this line leaves
+            # a directory that resume skips
+            failure.write_completion_marker(out)
             ckpt.rotate_checkpoints(output_dir or args.output_dir, args.save_total_limit)
         ckpt.barrier()
         return out
@@ -490,6 +496,10 @@ class FSDP2SFTTrainer:
         mem_prof.start()
         ga = max(args.gradient_accumulation_steps, 1)
         cuda = self.device.type == "cuda"
+        heartbeat = None
+        if getattr(args, "heartbeat_timeout", 0) and self.world_size > 1 and dist.is_initialized():
+            store = dist.distributed_c10d._get_default_store()
+            heartbeat = failure.Heartbeat(store, self.rank, self.world_size, float(args.heartbeat_timeout))
         epoch = 0
         micro = 0
         seqlens_acc: List[int] = []
@@ -518,11 +528,22 @@ class FSDP2SFTTrainer:
                 if args.print_batch_input_steps and args.print_batch_input_steps > 0 and self.global_step % args.print_batch_input_steps == 0 and self.rank == 0:
                     logger.info(f"batch keys/shapes: { {k: tuple(v.shape) for k, v in batch.items() if torch.is_tensor(v)} }")
                 do_step = (micro + 1) % ga == 0
+                if heartbeat is not None and micro % ga == 0:
+                    # between steps, on the host: learn of a failed or silent peer before launching
+                    # collectives that it would never join
+                    heartbeat.beat(self.global_step)
+                    heartbeat.check_peers(self.global_step)
                 ev_prof.start("training_step")
                 try:
                     loss, grad_norm = self.training_step(batch, do_step)
                 except torch.OutOfMemoryError:
                     mem_prof.dump_on_oom()
+                    if heartbeat is not None:
+                        heartbeat.report_error(self.global_step, "out of memory")
+                    raise
+                except Exception as e:
+                    if heartbeat is not None:
+                        heartbeat.report_error(self.global_step, f"{type(e).__name__}: {e}")
                     raise
                 ev_prof.stop("training_step")
                 loss_acc = loss if loss_acc is None else loss_acc + loss

@@ -138,7 +138,10 @@ class TrainRunner:
         self.freeze_modules()
         resume = kwargs.get("resume_from_checkpoint") or args.resume_from_checkpoint
         if resume is None or resume is True:
-            latest = ckpt.latest_checkpoint(args.output_dir)
+            latest = ckpt.latest_resumable_checkpoint(args.output_dir)
+            newest = ckpt.latest_checkpoint(args.output_dir)
+            if newest is not None and latest != newest:
+                logger.warning(f"{newest} is incomplete or damaged; resuming from {latest}")
             resume = latest if latest is not None else None
         result = self.trainer.train(resume_from_checkpoint=resume)
         return result

@@ -114,3 +114,50 @@ def test_muon_and_adamw_runtimes_agree(tmp_path, use_muon):
     b = run_tiny(tmp_path / "n2", nproc=2, runtime="native", pattern="periodic", steps=8, extra=extra)
     assert min(a["loss"][-2:]) < a["loss"][0] - 0.15, a["loss"]
     assert min(b["loss"][-2:]) < b["loss"][0] - 0.15, b["loss"]
+
+
+def test_resume_skips_damaged_checkpoint(tmp_path):
+    """A truncated rank file (or a save that never finished) makes resume fall back to the previous checkpoint."""
+    import json
+    import os
+
+    from lmms_engine_b200.train import checkpoint as ckpt
+    from lmms_engine_b200.utils import failure
+
+    out = str(tmp_path / "run")
+    extra = {"save_strategy": "steps", "save_steps": 2, "save_total_limit": 5}
+    run_tiny(out, steps=4, extra=extra)
+    c2, c4 = os.path.join(out, "checkpoint-2"), os.path.join(out, "checkpoint-4")
+    assert failure.checkpoint_is_complete(c2) and failure.checkpoint_is_complete(c4)
+    victim = os.path.join(c4, ckpt.MODEL_DIR, ckpt.rank_file("model", 1, 0))
+    with open(victim, "r+b") as f:
+        f.truncate(os.path.getsize(victim) // 2)
+    assert not failure.checkpoint_is_complete(c4)
+    assert ckpt.latest_resumable_checkpoint(out) == c2
+    os.remove(os.path.join(c2, failure.MARKER))  # as if the job had died while saving checkpoint-2 as well
+    assert ckpt.latest_resumable_checkpoint(out) is None
+    failure.write_completion_marker(c2)
+    res = run_tiny(out, steps=6, extra=extra)  # resumes from checkpoint-2 and overwrites the damaged one
+    assert res["final_step"] == 6 and len(res["loss"]) == 4
+    assert failure.checkpoint_is_complete(os.path.join(out, "checkpoint-6"))
+
+
+def test_rank_failure_is_reported_to_peers(tmp_path):
+    """A rank that raises between collectives: its peer stops on the host with the reason, nobody hangs."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    out = str(tmp_path / "run")
+    os.makedirs(out)
+    helper = os.path.join(os.path.dirname(__file__), "helpers", "failing_rank_run.py")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), helper, out]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    end0 = json.load(open(os.path.join(out, "end_rank0.json")))
+    end1 = json.load(open(os.path.join(out, "end_rank1.json")))
+    assert end1["how"].startswith("raised: injected")
+    assert end0["how"].startswith(("peer_failure", "runtime_error")), end0
+    assert end0["step"] <= 3
