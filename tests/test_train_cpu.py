@@ -9,6 +9,7 @@ import subprocess
 import sys
 
 import pytest
+import torch
 
 HELPER = os.path.join(os.path.dirname(__file__), "helpers", "tiny_run.py")
 
@@ -161,3 +162,21 @@ def test_rank_failure_is_reported_to_peers(tmp_path):
     assert end1["how"].startswith("raised: injected")
     assert end0["how"].startswith(("peer_failure", "runtime_error")), end0
     assert end0["step"] <= 3
+
+
+def test_hsdp_matches_plain_sharding_and_merges(tmp_path):
+    """2 x 2 hybrid sharding (replicate across, shard within) gives the losses of 4-way sharding, and its
+    (Replicate, Shard) checkpoint consolidates to the same weights."""
+    from lmms_engine_b200.merger.fsdp2 import FSDP2Merger
+    from lmms_engine_b200.models import hf_io
+
+    save = {"save_strategy": "steps", "save_steps": 3}
+    plain = run_tiny(tmp_path / "plain", nproc=4, steps=3, runtime="torch_fsdp2", extra=save)
+    hsdp = run_tiny(tmp_path / "hsdp", nproc=4, steps=3, extra={"hsdp_shard_size": 2, **save})
+    for a, b in zip(plain["loss"], hsdp["loss"]):
+        assert abs(a - b) < 2e-4, (plain["loss"], hsdp["loss"])
+    m1 = hf_io.read_state_dict(str(FSDP2Merger(str(tmp_path / "plain" / "checkpoint-3")).merge()))
+    m2 = hf_io.read_state_dict(str(FSDP2Merger(str(tmp_path / "hsdp" / "checkpoint-3")).merge()))
+    assert m1.keys() == m2.keys()
+    for k in m1:
+        assert torch.allclose(m1[k].float(), m2[k].float(), atol=2e-3), k
