@@ -63,6 +63,11 @@ class SyntheticPackedDataset(IterableDataset):
             from .collator.text_dllm_collator import TextDllmCollator
 
             return TextDllmCollator(self.mask_token_id, seed=self.seed)
+        if self.collator_type == "padded":
+            # [n_docs, max_len] with attention_mask: the layout models from the transformers library take
+            from .collator.vision_collator import VisionCollator
+
+            return VisionCollator(pad_token_id=0)
         return PackedCollator()
 
     def state_dict(self) -> Dict[str, Any]:

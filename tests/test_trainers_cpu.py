@@ -87,3 +87,14 @@ def test_grpo_math():
     loss, kl = grpo_token_loss(logp, logp.detach(), logp.detach(), torch.tensor([1.0, -1.0]), torch.ones(2), 0.2, 0.1)
     loss.backward()
     assert torch.allclose(logp.grad, torch.tensor([-0.5, 0.5])) and float(kl) == 0.0
+
+
+def test_transformers_fallback_family_trains(tmp_path):
+    """A model family without a native implementation is built from the transformers library and
+    trained by the same trainer on padded batches."""
+    pytest.importorskip("transformers")
+    cfg = dict(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, max_position_embeddings=256)
+    hist, runner = _run(tmp_path, "fsdp2_trainer", "mistral", cfg, _packed(collator_type="padded"), steps=4)
+    assert type(runner.model).__module__.startswith("transformers")
+    assert hist[-1]["train/loss"] < hist[0]["train/loss"] + 0.5
