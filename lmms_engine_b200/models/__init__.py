@@ -29,3 +29,6 @@ register_model("bagel", BagelConfig, Bagel, "general")
 
 __all__ = ["ModelConfig", "DecoderConfig", "DecoderLM", "MoEConfig", "MoEDecoderLM", "VLConfig", "VLModel", "DLLMConfig",
            "DiffusionLM", "SiT", "SiTConfig", "WanDiT", "WanConfig", "RaeAutoencoder", "RaeConfig", "Bagel", "BagelConfig"]
+from .nanovlm import Nanovlm, NanovlmConfig  # noqa: E402
+
+register_model("nanovlm", NanovlmConfig, Nanovlm, "image_text_to_text")

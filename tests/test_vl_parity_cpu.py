@@ -108,3 +108,37 @@ def test_mrope_positions_match_slow_oracle():
     # temporal index of the third video frame: floor(2 * 1.5 s * 2 tokens/s) = 6 past the run start
     start = 3 + 6 + 3  # tokens before the video run in doc1
     assert mine[0, start + 2 * 4] - mine[0, start] == 6
+
+
+def test_nanovlm_encodes_images_independently_and_trains():
+    """Patches of different images never attend to each other; image features land on the placeholders;
+    padded and packed inputs give the same loss."""
+    from lmms_engine_b200.mapping_func import create_model_from_config
+
+    cfg = dict(text_config=dict(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                                num_key_value_heads=2, head_dim=16),
+               vision_config=dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2, patch_size=4,
+                                  num_patches=16),
+               image_token_id=127, projector_num_layers=2)
+    torch.manual_seed(0)
+    m = create_model_from_config("nanovlm", cfg)
+    shapes = torch.tensor([[4, 4], [2, 3]])
+    pix = torch.randn(22, 48)
+    enc = m.vision_model
+    with torch.no_grad():
+        both, a, b = enc(pix, shapes), enc(pix[:16], shapes[:1]), enc(pix[16:], shapes[1:])
+    assert torch.allclose(both, torch.cat([a, b]), atol=1e-5)
+    ids = torch.randint(0, 120, (60,))
+    ids[5:21] = 127
+    ids[30:36] = 127
+    cu = torch.tensor([0, 25, 60], dtype=torch.int32)
+    out = m(input_ids=ids, labels=ids, cu_seqlens=cu, pixel_values=pix, spatial_shapes=shapes)
+    out["loss"].backward()
+    assert m.vision_model.patch_embedding.weight.grad.abs().sum() > 0
+    # the same two documents as a padded batch
+    padded = torch.zeros(2, 35, dtype=torch.long)
+    mask = torch.zeros(2, 35, dtype=torch.long)
+    padded[0, :25], mask[0, :25] = ids[:25], 1
+    padded[1, :35], mask[1, :35] = ids[25:], 1
+    out2 = m(input_ids=padded, labels=padded, attention_mask=mask, pixel_values=pix, spatial_shapes=shapes)
+    assert abs(float(out["loss"]) - float(out2["loss"])) < 1e-5
