@@ -1,0 +1,159 @@
+"""Datasets and processors of the non-chat trainers and of plain-text pre-training.
+
+* ``fineweb_edu`` (iterable): rows with a ``text`` field, every token supervised, packed online
+  (reference: src/lmms_engine/datasets/iterable/fineweb_edu_dataset.py).
+* ``sit`` (map-style): pre-computed latents + class labels for the SiT trainer
+  (reference: src/lmms_engine/datasets/naive/sit_dataset.py).
+* ``rae`` (map-style): images resized to a fixed square for the autoencoder / discriminator trainer
+  (reference: src/lmms_engine/datasets/naive/rae_dataset.py).
+* processors ``sit``, ``rae_siglip``, ``wanvideo`` (tensor normalisation only) and ``nanovlm`` (ChatML text
+  plus NaFlex patches: an image is resized so that it has at most ``max_num_patches`` patches of
+  ``patch_size`` pixels and is flattened to ``[rows*cols, C*p*p]`` with its ``spatial_shapes`` row).
+"""
+from __future__ import annotations
+
+import math
+import os
+from typing import Any, Dict, List
+
+import numpy as np
+import torch
+from torch.utils.data import Dataset
+
+from ..mapping_func import register_dataset, register_processor
+from .base import DatasetCore
+from .iterable.multimodal_iterable_dataset import MultiModalIterableDataset
+from .processor.chat import ChatProcessor
+from .synthetic import StackCollator
+
+
+# ------------------------------------------------------------------------------- text pre-training
+@register_dataset("fineweb_edu")
+class FinewebEduDataset(MultiModalIterableDataset):
+    """``{"text": ...}`` rows -> ``input_ids`` (+ end-of-text) with every token a target."""
+
+    def process_record(self, record: dict, data_folder: str = "") -> Dict[str, torch.Tensor]:
+        tok = self.processor.tokenizer
+        ids = list(tok.encode(record["text"], add_special_tokens=False))
+        eos = getattr(tok, "eos_token_id", None)
+        if eos is not None:
+            ids.append(int(eos))
+        limit = self.config.max_length or self.config.packing_length
+        if limit:
+            ids = ids[: int(limit)]
+        t = torch.tensor(ids, dtype=torch.long)
+        return {"input_ids": t, "labels": t.clone()}
+
+
+# ------------------------------------------------------------------------------- tensor processors
+class TensorProcessor:
+    """No tokenizer: scales / normalises tensors.  ``extra_kwargs``: ``mean``, ``std``, ``image_size``."""
+
+    def __init__(self, config):
+        self.config = config
+        self.kwargs = dict(getattr(config, "extra_kwargs", {}) or {})
+        self.mean = float(self.kwargs.get("mean", 0.5))
+        self.std = float(self.kwargs.get("std", 0.5))
+        self.image_size = int(self.kwargs.get("image_size", 256))
+
+    def build(self):
+        return self
+
+    @property
+    def processor(self):
+        return self
+
+    def save_pretrained(self, path: str):
+        os.makedirs(path, exist_ok=True)
+
+    def image_to_tensor(self, img) -> torch.Tensor:
+        """PIL image / HWC uint8 array -> ``[3, S, S]`` float, centre-cropped, normalised."""
+        from PIL import Image
+
+        if not isinstance(img, Image.Image):
+            img = Image.fromarray(np.asarray(img).astype(np.uint8))
+        img = img.convert("RGB")
+        w, h = img.size
+        s = min(w, h)
+        img = img.crop(((w - s) // 2, (h - s) // 2, (w - s) // 2 + s, (h - s) // 2 + s)).resize((self.image_size, self.image_size), Image.BICUBIC)
+        x = torch.from_numpy(np.asarray(img).copy()).permute(2, 0, 1).float() / 255.0
+        return (x - self.mean) / self.std
+
+    def process(self, image=None, **kw):
+        return {"pixel_values": self.image_to_tensor(image)} if image is not None else {}
+
+
+for _name in ("sit", "rae_siglip", "wanvideo"):
+    register_processor(_name)(TensorProcessor)
+
+
+@register_processor("nanovlm")
+class NanovlmProcessor(ChatProcessor):
+    """ChatML text with one placeholder per image patch and NaFlex patch rows."""
+
+    def build(self):
+        super().build()
+        self.patch = int(self.kwargs.get("patch_size", 16))
+        self.max_patches = int(self.kwargs.get("max_num_patches", 256))
+        return self
+
+    def patchify(self, img):
+        from PIL import Image
+
+        img = img.convert("RGB") if isinstance(img, Image.Image) else Image.fromarray(np.asarray(img).astype(np.uint8)).convert("RGB")
+        w, h = img.size
+        p = self.patch
+        scale = math.sqrt(self.max_patches * p * p / (w * h))
+        rows = max(1, min(int(h * scale) // p, self.max_patches))
+        cols = max(1, min(int(w * scale) // p, self.max_patches // rows))
+        img = img.resize((cols * p, rows * p), Image.BILINEAR)
+        x = torch.from_numpy(np.asarray(img).copy()).float() / 255.0  # [H, W, C]
+        x = (x - 0.5) / 0.5
+        x = x.view(rows, p, cols, p, 3).permute(0, 2, 4, 1, 3).reshape(rows * cols, 3 * p * p)
+        return x, (rows, cols)
+
+    def process(self, hf_messages=None, images=None, videos=None, audios=None, add_system_prompt: bool = True, **kw):
+        out: Dict[str, torch.Tensor] = {}
+        mm = {"image": [], "video": [], "audio": []}
+        if images:
+            pats, shapes = zip(*(self.patchify(im) for im in images))
+            out["pixel_values"] = torch.cat(pats)
+            out["spatial_shapes"] = torch.tensor(shapes, dtype=torch.long)
+            mm["image"] = [r * c for r, c in shapes]
+        out.update(self.build_ids_and_labels(hf_messages, mm, add_system_prompt))
+        return out
+
+
+# ------------------------------------------------------------------------------- map-style tensor datasets
+class _RecordDataset(DatasetCore, Dataset):
+    def __init__(self, config):
+        super().__init__(config)
+
+    def __len__(self):
+        return len(self.data_list)
+
+    def get_collator(self):
+        return StackCollator()
+
+
+@register_dataset("sit")
+class SitDataset(_RecordDataset):
+    """Rows ``{"latent": path (.pt / .npy) | nested list, "label": int}``."""
+
+    def __getitem__(self, i) -> Dict[str, Any]:
+        rec, folder = self.data_list[i], self.data_folder[i]
+        lat = rec["latent"]
+        if isinstance(lat, str):
+            path = os.path.join(folder or "", lat)
+            lat = torch.load(path, map_location="cpu") if path.endswith(".pt") else torch.from_numpy(np.load(path))
+        return {"latents": torch.as_tensor(lat, dtype=torch.float32), "labels": torch.tensor(int(rec.get("label", 0)))}
+
+
+@register_dataset("rae")
+class RaeDataset(_RecordDataset):
+    """Rows ``{"image": path}`` -> ``pixel_values [3, S, S]``."""
+
+    def __getitem__(self, i) -> Dict[str, Any]:
+        rec, folder = self.data_list[i], self.data_folder[i]
+        img = self.load_image(os.path.join(folder or "", rec["image"]))
+        return {"pixel_values": self.processor.image_to_tensor(img)}

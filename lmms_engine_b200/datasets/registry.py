@@ -3,5 +3,6 @@ from . import synthetic  # noqa: F401
 
 try:
     from . import iterable, naive, processor  # noqa: F401
+    from . import extra  # noqa: F401
 except ImportError:  # pragma: no cover
     pass

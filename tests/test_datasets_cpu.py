@@ -155,3 +155,53 @@ def test_vl_processor_counts_and_patch_order():
     # second row of the stream is the patch to the right inside the same 2x2 block
     ref2 = ((arr[:14, 14:28] - np.array(vp.CLIP_MEAN)) / np.array(vp.CLIP_STD)).transpose(2, 0, 1)
     assert torch.allclose(out["pixel_values"][1].view(3, 2, 14, 14)[:, 0], torch.from_numpy(ref2).float(), atol=1e-5)
+
+
+def test_extra_datasets_and_processors(tmp_path):
+    """fineweb_edu text rows pack with every token supervised; sit / rae rows become tensors; the
+    nanovlm processor emits one placeholder per NaFlex patch."""
+    import json
+
+    import numpy as np
+    from PIL import Image
+
+    from lmms_engine_b200.datasets import registry  # noqa: F401
+    from lmms_engine_b200.datasets.config import DatasetConfig
+    from lmms_engine_b200.mapping_func import DATAPROCESSOR_MAPPING, DATASET_MAPPING
+
+    for name in ("fineweb_edu", "sit", "rae", "vision", "vision_iterable", "qwen3_vl_iterable"):
+        assert name in DATASET_MAPPING, name
+    for name in ("sit", "rae_siglip", "wanvideo", "nanovlm", "pure_text", "qwen2_5_vl", "qwen3_vl"):
+        assert name in DATAPROCESSOR_MAPPING, name
+    txt = tmp_path / "t.jsonl"
+    txt.write_text("\n".join(json.dumps({"text": "hello world " * (5 + i)}) for i in range(12)))
+    ds = DATASET_MAPPING["fineweb_edu"](DatasetConfig(dataset_type="fineweb_edu", dataset_format="jsonl", dataset_path=str(txt),
+                                                      processor_config={"processor_name": "none", "processor_type": "pure_text"},
+                                                      packing=True, packing_length=256, shuffle=False)).build()
+    packs = list(ds)
+    assert packs and all(sum(s["input_ids"].numel() for s in p) <= 256 for p in packs)
+    assert sum(len(p) for p in packs) == 12 and all(torch.equal(s["input_ids"], s["labels"]) for p in packs for s in p)
+    # sit / rae
+    np.save(tmp_path / "lat.npy", np.random.randn(4, 8, 8).astype("float32"))
+    Image.fromarray((np.random.rand(40, 60, 3) * 255).astype("uint8")).save(tmp_path / "im.png")
+    (tmp_path / "sit.json").write_text(json.dumps([{"latent": str(tmp_path / "lat.npy"), "label": 3}] * 2))
+    (tmp_path / "rae.json").write_text(json.dumps([{"image": str(tmp_path / "im.png")}] * 2))
+    sit = DATASET_MAPPING["sit"](DatasetConfig(dataset_type="sit", dataset_format="json", dataset_path=str(tmp_path / "sit.json"),
+                                               processor_config={"processor_name": "none", "processor_type": "sit"})).build()
+    b = sit.get_collator()([sit[0], sit[1]])
+    assert b["latents"].shape == (2, 4, 8, 8) and b["labels"].tolist() == [3, 3]
+    rae = DATASET_MAPPING["rae"](DatasetConfig(dataset_type="rae", dataset_format="json", dataset_path=str(tmp_path / "rae.json"),
+                                               processor_config={"processor_name": "none", "processor_type": "rae_siglip",
+                                                                 "extra_kwargs": {"image_size": 32}})).build()
+    assert rae[0]["pixel_values"].shape == (3, 32, 32) and rae[0]["pixel_values"].abs().max() <= 1.0 + 1e-6
+    # nanovlm processor
+    from lmms_engine_b200.datasets.config import ProcessorConfig
+
+    proc = DATAPROCESSOR_MAPPING["nanovlm"](ProcessorConfig(processor_name="none", processor_type="nanovlm",
+                                                            extra_kwargs={"patch_size": 8, "max_num_patches": 24})).build()
+    msgs = [{"role": "user", "content": [{"type": "image"}, {"type": "text", "text": "what"}]},
+            {"role": "assistant", "content": [{"type": "text", "text": "a picture"}]}]
+    out = proc.process(msgs, images=[Image.open(tmp_path / "im.png")])
+    rows, cols = out["spatial_shapes"][0].tolist()
+    assert rows * cols <= 24 and out["pixel_values"].shape == (rows * cols, 3 * 64)
+    assert int((out["input_ids"] == proc.image_token_id).sum()) == rows * cols
