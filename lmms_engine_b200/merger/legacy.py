@@ -66,10 +66,17 @@ def main(argv=None):
     ap.add_argument("--type", default="fsdp2", choices=["hf", "fsdp2"])
     ap.add_argument("--merge", action="store_true", help="average all checkpoints found (model soup)")
     ap.add_argument("--dtype", default="bfloat16")
+    ap.add_argument("--step", type=int, default=None, help="merge checkpoint-<step> instead of the newest one")
+    ap.add_argument("--state_dict_dirname", default=None, help="sub-directory holding the shards (default: pytorch_model_fsdp_0)")
+    ap.add_argument("--model_name_or_class", default=None, help="accepted for compatibility; the config saved with the checkpoint is used")
     args = ap.parse_args(argv)
     one = merge_dcp_dir if args.type == "hf" else merge_fsdp2_dir
     inp = Path(args.input_dir)
     cands = ckpt.list_checkpoints(str(inp)) if any(inp.glob("checkpoint-*")) else [str(inp)]
+    if args.step is not None:
+        cands = [c for c in cands if c.rstrip("/").endswith(f"checkpoint-{args.step}")] or cands
+    if args.state_dict_dirname:
+        cands = [os.path.join(c, args.state_dict_dirname) if os.path.isdir(os.path.join(c, args.state_dict_dirname)) else c for c in cands]
     if not args.merge:
         cands = cands[-1:]
     states = [one(c) for c in cands]

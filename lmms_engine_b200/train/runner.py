@@ -104,7 +104,14 @@ class TrainRunner:
     def _apply_model_switches(self):
         """Accept ``use_rmpad`` / ``use_liger_kernel`` / ``monkey_patch_kwargs``: they are always
         on in the native models; unknown switches are reported, never silently swallowed."""
+        from ..models.monkey_patch import MONKEY_PATCHER
+
         kw = dict(self.model_config.monkey_patch_kwargs or {})
+        model_type = getattr(getattr(self.model, "config", None), "model_type", None)
+        if model_type is not None:
+            # user-registered patches for this model type (none ship with the native models)
+            MONKEY_PATCHER.apply(self.model, model_type, kw.get("patch_type", ["liger"]),
+                                 **{k: v for k, v in kw.items() if k != "patch_type"})
         known = {"patch_type", "rope", "cross_entropy", "fused_linear_cross_entropy", "rms_norm", "swiglu", "use_rmpad"}
         extra = {k: v for k, v in kw.items() if k not in known}
         for k, v in extra.items():

@@ -207,3 +207,16 @@ def test_tools_and_legacy_merge(tmp_path):
 
     merged = hf_io.read_state_dict(str(out_dir))
     assert torch.allclose(merged["w"][:2], torch.full((2, 3), 2.0)) and torch.allclose(merged["w"][2:], torch.full((2, 3), 3.0))
+
+
+def test_monkey_patcher_registry_runs_user_patches():
+    from lmms_engine_b200.models.monkey_patch import MONKEY_PATCHER
+
+    seen = []
+
+    @MONKEY_PATCHER.register("my_model", "liger")
+    def patch(model, rms_norm=True, **kw):
+        seen.append((model, rms_norm))
+
+    assert MONKEY_PATCHER.apply("m", "my_model", ["liger", "other"], rms_norm=False) == 1
+    assert seen == [("m", False)] and MONKEY_PATCHER.apply("m", "unknown", "liger") == 0
