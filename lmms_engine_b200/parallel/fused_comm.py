@@ -36,6 +36,7 @@ _cuda.register("b200_peer_memcpy", "peer_comm", "ppls")
 _cuda.register("b200_peer_signal", "peer_comm", "pis")
 _cuda.register("b200_peer_memcpy2d", "peer_comm", "plpllls")
 
+_NVTX = os.environ.get("LMMS_B200_NVTX") == "1"
 MAX_RANKS = 8
 _FLAG_WORDS = 3 * MAX_RANKS
 _ALIGN = 256
@@ -254,11 +255,15 @@ class FusedComm:
         if self.trace is not None:  # CTA 0's timeline of this launch, six globaltimer stamps
             ca[77] = self.trace.data_ptr()
         st = _cuda.status_word(self.device)
+        if _NVTX:
+            torch.cuda.nvtx.range_push(f"fused_gemm M{M} N{N} K{K} push{int(push is not None)} wait{wait_mode} scatter{scatter['mode'] if scatter else 0}")
         ctas = _cuda.call_raw(
             "b200_gemm_comm_bf16", a.data_ptr(), b.data_ptr(), c.data_ptr() if c is not None else 0, M, N, K,
             a.stride(0), b.stride(0), c.stride(0) if c is not None else 0, int(b_mn), float(alpha), _cuda.ptr(bias),
             ctypes.addressof(ca), st.data_ptr(), _cuda.stream(),
         )
+        if _NVTX:
+            torch.cuda.nvtx.range_pop()
         if ctas <= 0:
             raise RuntimeError(f"b200_gemm_comm_bf16 refused the launch (code {ctas}) for M={M} N={N} K={K}")
         if push is not None and push.get("external"):
