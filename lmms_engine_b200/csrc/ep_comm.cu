@@ -12,7 +12,9 @@
 //   pull_scalar : the same gather for one fp32 per row (router-weight gradients).
 //
 // Plain ld/st.global on peer addresses and system-scope flags only (no TMA, no multicast); every
-// wait is bounded and raises the status word when it gives up.
+// wait is bounded and raises the status word when it gives up.  Every index that addresses another
+// rank's buffer is checked against the buffer's row capacity (and token indices against the token
+// count): a bad entry is skipped and reported through the status word instead of being dereferenced.
 //
 // The reference moves these rows with all_to_all_single around a python expert loop
 // (src/lmms_engine/parallel/expert_parallel/utils.py:11-77,
@@ -47,7 +49,7 @@ __global__ void ep_push_kernel(const __nv_bfloat16* __restrict__ x, long ldx, co
                                const float* __restrict__ scalar_of_row, const int* __restrict__ dest_rank,
                                const int* __restrict__ dest_row, long n_rows, int H, long ld_dst, EpPeers peers,
                                int world, int rank, uint32_t epoch, unsigned int* block_counter, int* status,
-                               long long limit) {
+                               long long limit, long n_tokens, long cap_rows) {
   const int lane = threadIdx.x & 31;
   const long warp0 = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long n_warps = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
@@ -56,6 +58,10 @@ __global__ void ep_push_kernel(const __nv_bfloat16* __restrict__ x, long ldx, co
     const int r = dest_rank[p];
     if (r < 0) continue;  // row of an unused tile
     const long long tok = token_of_row[p];
+    if (r >= world || dest_row[p] < 0 || dest_row[p] >= cap_rows || tok >= n_tokens) {
+      if (lane == 0 && status != nullptr) atomicExch(status, kStatusOverflow);
+      continue;
+    }
     uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(peers.buf[r]) + static_cast<long>(dest_row[p]) * ld_dst);
     if (tok >= 0) {
       const uint4* src = reinterpret_cast<const uint4*>(x + tok * ldx);
@@ -106,7 +112,7 @@ __device__ __forceinline__ bool ep_start_handshake(const EpPeers& peers, int wor
 __global__ void ep_pull_kernel(__nv_bfloat16* __restrict__ out, long ldo, const int* __restrict__ row_of,
                                const float* __restrict__ w, const int* __restrict__ dest_rank,
                                const int* __restrict__ dest_row, long T, int k, int H, long ld_src, EpPeers peers,
-                               int world, int rank, uint32_t epoch, int* status, long long limit) {
+                               int world, int rank, uint32_t epoch, int* status, long long limit, long n_rows, long cap_rows) {
   if (!ep_start_handshake(peers, world, rank, epoch, 16, status, limit)) return;
   const int lane = threadIdx.x & 31;
   const long warp0 = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -117,6 +123,10 @@ __global__ void ep_pull_kernel(__nv_bfloat16* __restrict__ out, long ldo, const 
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       for (int i = 0; i < k; ++i) {
         const int p = row_of[t * k + i];
+        if (p < 0 || p >= n_rows || dest_rank[p] < 0 || dest_rank[p] >= world || dest_row[p] < 0 || dest_row[p] >= cap_rows) {
+          if (status != nullptr) atomicExch(status, kStatusOverflow);
+          continue;
+        }
         const float wi = w != nullptr ? w[t * k + i] : 1.f;
         const uint4 u = *(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(peers.buf[dest_rank[p]]) +
                                                          static_cast<long>(dest_row[p]) * ld_src) + v);
@@ -133,10 +143,16 @@ __global__ void ep_pull_kernel(__nv_bfloat16* __restrict__ out, long ldo, const 
 
 __global__ void ep_pull_scalar_kernel(float* __restrict__ out, const int* __restrict__ row_of,
                                       const int* __restrict__ dest_rank, const int* __restrict__ dest_row, long n,
-                                      EpPeers peers, int world, int rank, uint32_t epoch, int* status, long long limit) {
+                                      EpPeers peers, int world, int rank, uint32_t epoch, int* status, long long limit,
+                                      long n_rows, long cap_rows) {
   if (!ep_start_handshake(peers, world, rank, epoch, 32, status, limit)) return;
   for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<long>(gridDim.x) * blockDim.x) {
     const int p = row_of[i];
+    if (p < 0 || p >= n_rows || dest_rank[p] < 0 || dest_rank[p] >= world || dest_row[p] < 0 || dest_row[p] >= cap_rows) {
+      if (status != nullptr) atomicExch(status, kStatusOverflow);
+      out[i] = 0.f;
+      continue;
+    }
     out[i] = peers.scalar[dest_rank[p]][dest_row[p]];
   }
 }
@@ -161,7 +177,7 @@ extern "C" {
 int b200_ep_push(const void* x, long ldx, const void* token_of_row, const void* scalar_of_row, const void* dest_rank,
                  const void* dest_row, long n_rows, int H, long ld_dst, const void* const* peer_bufs,
                  const void* const* peer_scalars, const void* const* peer_flags, int world, int rank, unsigned int epoch,
-                 void* block_counter, int* status, int timeout_ms, cudaStream_t st) {
+                 void* block_counter, int* status, int timeout_ms, long n_tokens, long cap_rows, cudaStream_t st) {
   if ((H & 7) || (ldx & 7) || (ld_dst & 7)) return -10;
   EpPeers pp{};
   if (fill_peers(pp, peer_bufs, scalar_of_row != nullptr ? peer_scalars : nullptr, peer_flags, world) != 0) return -10;
@@ -172,13 +188,13 @@ int b200_ep_push(const void* x, long ldx, const void* token_of_row, const void* 
       static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const long long*>(token_of_row),
       static_cast<const float*>(scalar_of_row), static_cast<const int*>(dest_rank), static_cast<const int*>(dest_row), n_rows,
       H, ld_dst, pp, world, rank, epoch, static_cast<unsigned int*>(block_counter), status,
-      static_cast<long long>(timeout_ms) * 1900000LL);
+      static_cast<long long>(timeout_ms) * 1900000LL, n_tokens, cap_rows);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
 int b200_ep_pull(void* out, long ldo, const void* row_of, const void* w, const void* dest_rank, const void* dest_row, long T,
                  int k, int H, long ld_src, const void* const* peer_bufs, const void* const* peer_flags, int world, int rank,
-                 unsigned int epoch, int* status, int timeout_ms, cudaStream_t st) {
+                 unsigned int epoch, int* status, int timeout_ms, long n_rows, long cap_rows, cudaStream_t st) {
   if (T <= 0) T = 0;
   if ((H & 7) || (ldo & 7) || (ld_src & 7)) return -10;
   EpPeers pp{};
@@ -189,13 +205,14 @@ int b200_ep_pull(void* out, long ldo, const void* row_of, const void* w, const v
   ep_pull_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(
       static_cast<__nv_bfloat16*>(out), ldo, static_cast<const int*>(row_of), static_cast<const float*>(w),
       static_cast<const int*>(dest_rank), static_cast<const int*>(dest_row), T, k, H, ld_src, pp, world, rank, epoch, status,
-      static_cast<long long>(timeout_ms) * 1900000LL);
+      static_cast<long long>(timeout_ms) * 1900000LL, n_rows, cap_rows);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
 int b200_ep_pull_scalar(void* out, const void* row_of, const void* dest_rank, const void* dest_row, long n,
                         const void* const* peer_bufs, const void* const* peer_scalars, const void* const* peer_flags,
-                        int world, int rank, unsigned int epoch, int* status, int timeout_ms, cudaStream_t st) {
+                        int world, int rank, unsigned int epoch, int* status, int timeout_ms, long n_rows, long cap_rows,
+                        cudaStream_t st) {
   EpPeers pp{};
   if (fill_peers(pp, peer_bufs, peer_scalars, peer_flags, world) != 0) return -10;
   long blocks = (n + 255) / 256;
@@ -203,7 +220,8 @@ int b200_ep_pull_scalar(void* out, const void* row_of, const void* dest_rank, co
   if (blocks < 1) blocks = 1;
   ep_pull_scalar_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(
       static_cast<float*>(out), static_cast<const int*>(row_of), static_cast<const int*>(dest_rank),
-      static_cast<const int*>(dest_row), n, pp, world, rank, epoch, status, static_cast<long long>(timeout_ms) * 1900000LL);
+      static_cast<const int*>(dest_row), n, pp, world, rank, epoch, status, static_cast<long long>(timeout_ms) * 1900000LL,
+      n_rows, cap_rows);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

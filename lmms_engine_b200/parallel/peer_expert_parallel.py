@@ -33,9 +33,9 @@ from .fused_comm import SymmPool
 
 TILE = moe_ops.TILE
 
-_cuda.register("b200_ep_push", "ep_comm", "plpppplilpppiiippis")
-_cuda.register("b200_ep_pull", "ep_comm", "plppppliilppiiipis")
-_cuda.register("b200_ep_pull_scalar", "ep_comm", "pppplpppiiipis")
+_cuda.register("b200_ep_push", "ep_comm", "plpppplilpppiiippills")
+_cuda.register("b200_ep_pull", "ep_comm", "plppppliilppiiipills")
+_cuda.register("b200_ep_pull_scalar", "ep_comm", "pppplpppiiipills")
 
 
 def _ptrs(v: List[int]):
@@ -120,7 +120,8 @@ class PeerExpertParallel(ExpertParallel):
         _cuda.call("b200_ep_push", x.data_ptr(), x.stride(0), perm.token_of_row.data_ptr(), _cuda.ptr(scalar),
                    dest_rank.data_ptr(), dest_row.data_ptr(), dest_rank.numel(), x.shape[1], xs.t.stride(0),
                    ctypes.addressof(xs.c_ptrs), ctypes.addressof(xs.c_sptrs), ctypes.addressof(self.c_flags), self.ep,
-                   self.rank, self.push_epoch, self.counter.data_ptr(), st.data_ptr(), self.WAIT_MS, _cuda.stream())
+                   self.rank, self.push_epoch, self.counter.data_ptr(), st.data_ptr(), self.WAIT_MS, x.shape[0], xs.cap,
+                   _cuda.stream())
         self.launches += 1
 
     def pull(self, stage: _Stage, row_of, w, dest_rank, dest_row, T: int, k: int, dtype):
@@ -130,7 +131,7 @@ class PeerExpertParallel(ExpertParallel):
         _cuda.call("b200_ep_pull", out.data_ptr(), out.stride(0), row_of.data_ptr(), _cuda.ptr(w), dest_rank.data_ptr(),
                    dest_row.data_ptr(), T, k, stage.H, stage.t.stride(0), ctypes.addressof(stage.c_ptrs),
                    ctypes.addressof(self.c_flags), self.ep, self.rank, self.pull_epoch, st.data_ptr(), self.WAIT_MS,
-                   _cuda.stream())
+                   dest_rank.numel(), stage.cap, _cuda.stream())
         self.launches += 1
         return out
 
@@ -141,7 +142,7 @@ class PeerExpertParallel(ExpertParallel):
         _cuda.call("b200_ep_pull_scalar", out.data_ptr(), row_of.data_ptr(), dest_rank.data_ptr(), dest_row.data_ptr(),
                    row_of.numel(), ctypes.addressof(stage.c_ptrs), ctypes.addressof(stage.c_sptrs),
                    ctypes.addressof(self.c_flags), self.ep, self.rank, self.scalar_epoch, st.data_ptr(), self.WAIT_MS,
-                   _cuda.stream())
+                   dest_rank.numel(), stage.cap, _cuda.stream())
         self.launches += 1
         return out
 

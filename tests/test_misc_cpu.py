@@ -220,3 +220,38 @@ def test_monkey_patcher_registry_runs_user_patches():
 
     assert MONKEY_PATCHER.apply("m", "my_model", ["liger", "other"], rms_norm=False) == 1
     assert seen == [("m", False)] and MONKEY_PATCHER.apply("m", "unknown", "liger") == 0
+
+
+def test_head_routing_tables_match_the_ulysses_layout():
+    """Routing tables of the fused QKV projection against the reference layout: scattering the columns of
+    ``[q | k | v]`` by the tables must equal what the NCCL all-to-all path builds."""
+    from lmms_engine_b200.parallel.fused_comm import out_head_route, qkv_head_route, qkv_kb_sources
+
+    nq, nkv, D, world = 8, 4, 128, 4
+    r = qkv_head_route(nq, nkv, D, world, "cpu")
+    hq, hkv = nq // world, nkv // world
+    assert r.cols_local == (hq + 2 * hkv) * D and not r.kv_replicated
+    n_chunks = (nq + 2 * nkv) * D // 64
+    assert r.chunk_dst.numel() == n_chunks
+    # emulate the scatter on column ids: value = global column index
+    cols = torch.arange((nq + 2 * nkv) * D)
+    got = {d: torch.full((r.cols_local,), -1, dtype=torch.long) for d in range(world)}
+    for c in range(n_chunks):
+        for dd in range(int(r.chunk_ndst[c])):
+            d = int(r.chunk_dst[c]) + dd
+            got[d][int(r.chunk_col[c]):int(r.chunk_col[c]) + 64] = cols[c * 64:(c + 1) * 64]
+    for d in range(world):
+        q = cols[: nq * D].view(nq, D)[d * hq:(d + 1) * hq].reshape(-1)
+        k = cols[nq * D:(nq + nkv) * D].view(nkv, D)[d * hkv:(d + 1) * hkv].reshape(-1)
+        v = cols[(nq + nkv) * D:].view(nkv, D)[d * hkv:(d + 1) * hkv].reshape(-1)
+        assert torch.equal(got[d], torch.cat([q, k, v]))
+    # k-block sources follow the owner of every head
+    kb = qkv_kb_sources(nq, nkv, D, world, "cpu")
+    assert kb.tolist()[: nq * D // 64] == [h // hq for h in range(nq) for _ in range(D // 64)]
+    # replicated kv heads: each kv head goes to world / n_kv consecutive ranks
+    rr = qkv_head_route(8, 2, 64, 4, "cpu")
+    assert rr.kv_replicated and rr.chunk_ndst.tolist() == [1] * 8 + [2] * 4 and rr.chunk_dst.tolist()[8:] == [0, 2, 0, 2]
+    o = out_head_route(nq, D, world, "cpu")
+    assert o.cols_local == hq * D and o.chunk_dst.tolist() == [h // hq for h in range(nq) for _ in range(2)]
+    with pytest.raises(ValueError):
+        qkv_head_route(28, 4, 128, 8, "cpu")
