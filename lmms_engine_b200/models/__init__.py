@@ -32,3 +32,6 @@ __all__ = ["ModelConfig", "DecoderConfig", "DecoderLM", "MoEConfig", "MoEDecoder
 from .nanovlm import Nanovlm, NanovlmConfig  # noqa: E402
 
 register_model("nanovlm", NanovlmConfig, Nanovlm, "image_text_to_text")
+from .audio import Qwen2AudioConfig, Qwen2AudioModel  # noqa: E402
+
+register_model("qwen2_audio", Qwen2AudioConfig, Qwen2AudioModel, "general")

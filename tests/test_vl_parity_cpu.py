@@ -142,3 +142,46 @@ def test_nanovlm_encodes_images_independently_and_trains():
     padded[1, :35], mask[1, :35] = ids[25:], 1
     out2 = m(input_ids=padded, labels=padded, attention_mask=mask, pixel_values=pix, spatial_shapes=shapes)
     assert abs(float(out["loss"]) - float(out2["loss"])) < 1e-5
+
+
+def test_audio_encoder_matches_upstream_and_feeds_the_decoder():
+    """Native Whisper-style encoder on valid frames only == upstream Qwen2AudioEncoder with its key mask;
+    pooled features land on the audio placeholders of the packed stream."""
+    pytest.importorskip("transformers")
+    from transformers.models.qwen2_audio.configuration_qwen2_audio import Qwen2AudioEncoderConfig
+    from transformers.models.qwen2_audio.modeling_qwen2_audio import Qwen2AudioEncoder
+
+    from lmms_engine_b200.mapping_func import create_model_from_config
+    from lmms_engine_b200.models.audio import AudioEncoder
+
+    enc = dict(num_mel_bins=16, d_model=32, encoder_layers=2, encoder_attention_heads=4, encoder_ffn_dim=64, max_source_positions=20)
+    torch.manual_seed(0)
+    hf = Qwen2AudioEncoder(Qwen2AudioEncoderConfig(**enc)).eval()
+    cfg = dict(text_config=dict(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                                num_key_value_heads=2, head_dim=16), audio_config=enc, audio_token_index=127)
+    model = create_model_from_config("qwen2_audio", cfg)
+    model.audio_tower.load_state_dict(hf.state_dict(), strict=True)
+    x = torch.randn(2, 16, 40)
+    lens = torch.tensor([40, 27])
+    mask = (torch.arange(40)[None] < lens[:, None]).long()
+    frames, out_len = AudioEncoder.output_lengths(lens)
+    key_ok = torch.arange(20)[None] < frames[:, None]
+    am = torch.zeros(2, 1, 20, 20).masked_fill(~key_ok[:, None, None, :], float("-inf"))
+    with torch.no_grad():
+        ref = hf(x, attention_mask=am).last_hidden_state
+        got, ol = model.audio_tower(x, mask)
+    assert ol.tolist() == out_len.tolist() == [10, 7]
+    off = 0
+    for i, m in enumerate(ol.tolist()):
+        assert torch.allclose(got[off:off + m], ref[i, :m], atol=1e-5)
+        off += m
+    ids = torch.randint(0, 120, (50,))
+    ids[3:13] = 127
+    ids[30:37] = 127
+    cu = torch.tensor([0, 20, 50], dtype=torch.int32)
+    out = model(input_ids=ids, labels=ids, cu_seqlens=cu, input_features=x, feature_attention_mask=mask)
+    out["loss"].backward()
+    assert model.audio_tower.conv1.weight.grad.abs().sum() > 0 and model.multi_modal_projector.linear.weight.grad.abs().sum() > 0
+    # the collator's names for the same tensors are accepted as well
+    out2 = model(input_ids=ids, labels=ids, cu_seqlens=cu, audio_values=x, audio_attention_mask=mask)
+    assert abs(float(out["loss"]) - float(out2["loss"])) < 1e-6
