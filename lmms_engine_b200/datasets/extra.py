@@ -124,6 +124,34 @@ class NanovlmProcessor(ChatProcessor):
         return out
 
 
+@register_processor("qwen2_audio")
+class Qwen2AudioProcessor(ChatProcessor):
+    """ChatML text with ``<|AUDIO|>`` placeholders: one per pooled encoder frame of every audio clip."""
+
+    def build(self):
+        super().build()
+        self.n_mels = int(self.kwargs.get("num_mel_bins", 128))
+        self.n_frames = int(self.kwargs.get("max_frames", 3000))
+        return self
+
+    def process(self, hf_messages=None, images=None, videos=None, audios=None, add_system_prompt: bool = True, **kw):
+        from .processor.audio_process import log_mel_spectrogram
+
+        out: Dict[str, torch.Tensor] = {}
+        mm = {"image": [], "video": [], "audio": []}
+        if audios:
+            feats, masks = [], []
+            for wav in audios:
+                f, m, valid = log_mel_spectrogram(wav, self.n_mels, self.n_frames)
+                feats.append(f), masks.append(m)
+                frames = (valid - 1) // 2 + 1  # after the stride-2 convolution
+                mm["audio"].append(max((frames - 2) // 2 + 1, 1))  # after the average pooling by 2
+            out["audio_values"] = torch.stack(feats)
+            out["audio_attention_mask"] = torch.stack(masks)
+        out.update(self.build_ids_and_labels(hf_messages, mm, add_system_prompt))
+        return out
+
+
 # ------------------------------------------------------------------------------- map-style tensor datasets
 class _RecordDataset(DatasetCore, Dataset):
     def __init__(self, config):

@@ -205,3 +205,30 @@ def test_extra_datasets_and_processors(tmp_path):
     rows, cols = out["spatial_shapes"][0].tolist()
     assert rows * cols <= 24 and out["pixel_values"].shape == (rows * cols, 3 * 64)
     assert int((out["input_ids"] == proc.image_token_id).sum()) == rows * cols
+
+
+def test_log_mel_matches_whisper_extractor_and_audio_processor_counts():
+    import numpy as np
+
+    from lmms_engine_b200.datasets import registry  # noqa: F401
+    from lmms_engine_b200.datasets.config import ProcessorConfig
+    from lmms_engine_b200.datasets.processor.audio_process import log_mel_spectrogram
+    from lmms_engine_b200.mapping_func import DATAPROCESSOR_MAPPING
+
+    wav = (np.sin(2 * np.pi * 440 * np.arange(16000 * 2) / 16000) * 0.5).astype("float32")
+    feats, mask, valid = log_mel_spectrogram(wav, 128, 3000)
+    assert feats.shape == (128, 3000) and valid == 200 and int(mask.sum()) == 200
+    try:
+        from transformers import WhisperFeatureExtractor
+
+        ref = WhisperFeatureExtractor(feature_size=128)(wav, sampling_rate=16000, return_tensors="pt")["input_features"][0]
+        assert (ref - feats).abs().max() < 1e-4
+    except ImportError:
+        pass
+    proc = DATAPROCESSOR_MAPPING["qwen2_audio"](ProcessorConfig(processor_name="none", processor_type="qwen2_audio")).build()
+    msgs = [{"role": "user", "content": [{"type": "audio"}, {"type": "text", "text": "what is this"}]},
+            {"role": "assistant", "content": [{"type": "text", "text": "a tone"}]}]
+    out = proc.process(msgs, audios=[wav])
+    assert out["audio_values"].shape == (1, 128, 3000)
+    assert int((out["input_ids"] == proc.audio_token_id).sum()) == 50  # 200 mel frames -> 100 -> 50 pooled rows
+    assert (out["labels"][out["input_ids"] == proc.audio_token_id] == -100).all()
