@@ -34,9 +34,10 @@ def newton_schulz_ref(G: torch.Tensor, steps: int = 5, eps: float = 1e-7, prenor
     return (X.t() if tall else X).to(G.dtype)
 
 
-def newton_schulz(X: torch.Tensor, steps: int = 5, work: Optional[dict] = None) -> torch.Tensor:
+def newton_schulz(X: torch.Tensor, steps: int = 5, work: Optional[dict] = None, max_ctas: int = 0) -> torch.Tensor:
     """Orthogonalise a Frobenius-normalised bf16 matrix ``X [m, n]``.  Returns a bf16 tensor
-    (one of two ping-pong buffers; ``X`` itself is used as one of them and is overwritten)."""
+    (one of two ping-pong buffers; ``X`` itself is used as one of them and is overwritten).
+    ``max_ctas`` confines every product to that many SMs, so that several chains can share the GPU."""
     native = X.is_cuda and X.dtype == torch.bfloat16 and X.shape[0] % 8 == 0 and X.shape[1] % 8 == 0 and X.is_contiguous()
     if not native:
         return newton_schulz_ref(X, steps, prenormalized=True)
@@ -57,14 +58,14 @@ def newton_schulz(X: torch.Tensor, steps: int = 5, work: Optional[dict] = None) 
     cur, nxt = X, Y
     for _ in range(steps):
         if tall:
-            _gemm.gemm(cur, cur, a_mn_major=True, b_mn_major=True, symmetric=True, out=A)  # X^T X
+            _gemm.gemm(cur, cur, a_mn_major=True, b_mn_major=True, symmetric=True, out=A, max_ctas=max_ctas)  # X^T X
         else:
-            _gemm.gemm(cur, cur, symmetric=True, out=A)  # X X^T
-        _gemm.gemm(A, A, alpha=c, beta=b, cin=A, symmetric=True, out=B)  # b A + c A^2
+            _gemm.gemm(cur, cur, symmetric=True, out=A, max_ctas=max_ctas)  # X X^T
+        _gemm.gemm(A, A, alpha=c, beta=b, cin=A, symmetric=True, out=B, max_ctas=max_ctas)  # b A + c A^2
         if tall:
-            _gemm.gemm(cur, B, beta=a, cin=cur, out=nxt)  # a X + X B   (B symmetric)
+            _gemm.gemm(cur, B, beta=a, cin=cur, out=nxt, max_ctas=max_ctas)  # a X + X B   (B symmetric)
         else:
-            _gemm.gemm(B, cur, b_mn_major=True, beta=a, cin=cur, out=nxt)  # a X + B X
+            _gemm.gemm(B, cur, b_mn_major=True, beta=a, cin=cur, out=nxt, max_ctas=max_ctas)  # a X + B X
         cur, nxt = nxt, cur
     return cur
 

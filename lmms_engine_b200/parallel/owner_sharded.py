@@ -27,6 +27,9 @@ For models too large to replicate, the trainer falls back to stock FSDP2
 """
 from __future__ import annotations
 
+import contextlib
+import os
+
 import math
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional, Sequence, Tuple
@@ -151,6 +154,7 @@ class OwnerShardedRuntime:
         self.grad_dtype = grad_dtype or param_dtype
         self.step_count = 0
         self._ns_work: Dict[Any, torch.Tensor] = {}
+        self._lanes = None
 
         params: List[Tuple[str, torch.nn.Parameter]] = []
         seen = set()
@@ -286,19 +290,61 @@ class OwnerShardedRuntime:
             )
 
     def _muon_update(self, lr: float, gscale: torch.Tensor) -> None:
+        """Momentum, Newton-Schulz and the update of every matrix this rank owns.
+
+        On CUDA the matrices are dealt round-robin to ``muon_lanes`` streams and every GEMM of a lane
+        is confined to ``SMs / lanes`` CTAs: the symmetric products of one matrix have too few tiles
+        for the whole GPU (210 upper-triangle tiles for a 3584 x 3584 product, 5 for a 512-row KV
+        projection), so running several chains side by side on part of the SMs each removes most of
+        the idle tail of every launch.  The chains are independent; the lanes join before the
+        parameters are published."""
         lo, _ = self.muon_ranges[self.rank]
         cfg = self.muon
-        for s in self.my_matrices:
+        lanes = self._muon_lanes()
+        n_l = len(lanes)
+        main = torch.cuda.current_stream() if n_l > 1 else None
+        if n_l > 1:
+            ready = torch.cuda.Event()
+            ready.record(main)
+            for lane in lanes:
+                lane["stream"].wait_event(ready)
+        for i, s in enumerate(self.my_matrices):
+            lane = lanes[i % n_l]
             a, b = s.offset, s.offset + s.numel
             mom = self.mu_mom[a - lo : b - lo]
-            x = torch.empty(s.shape, dtype=torch.bfloat16 if self.P.is_cuda else torch.float32, device=self.device)
-            optim_ops.muon_momentum(mom, self.G[a:b], x.view(-1), self._sumsq, beta=cfg["momentum"],
-                                    nesterov=cfg["nesterov"], gscale=gscale)
-            o = muon_ops.newton_schulz(x, cfg["ns_steps"], self._ns_work)
-            optim_ops.muon_update(
-                self.mu_master[a - lo : b - lo], self.P[a:b] if self.needs_master else None, o.reshape(-1),
-                lr=lr, wd=self.weight_decay, scale=muon_ops.muon_scale(s.shape, cfg["rms_scale"]), skip=self._skip,
-            )
+            ctx = torch.cuda.stream(lane["stream"]) if n_l > 1 else contextlib.nullcontext()
+            with ctx:
+                x = torch.empty(s.shape, dtype=torch.bfloat16 if self.P.is_cuda else torch.float32, device=self.device)
+                optim_ops.muon_momentum(mom, self.G[a:b], x.view(-1), lane["sumsq"], beta=cfg["momentum"],
+                                        nesterov=cfg["nesterov"], gscale=gscale)
+                o = muon_ops.newton_schulz(x, cfg["ns_steps"], lane["work"], max_ctas=lane["ctas"])
+                optim_ops.muon_update(
+                    self.mu_master[a - lo : b - lo], self.P[a:b] if self.needs_master else None, o.reshape(-1),
+                    lr=lr, wd=self.weight_decay, scale=muon_ops.muon_scale(s.shape, cfg["rms_scale"]), skip=self._skip,
+                )
+                if n_l > 1:
+                    x.record_stream(lane["stream"])
+        if n_l > 1:
+            for lane in lanes:
+                done = torch.cuda.Event()
+                done.record(lane["stream"])
+                main.wait_event(done)
+
+    def _muon_lanes(self):
+        if self._lanes is None:
+            n = 1
+            if self.P.is_cuda:
+                n = max(1, int(os.environ.get("LMMS_B200_MUON_LANES", "4")))
+            sms = torch.cuda.get_device_properties(self.device).multi_processor_count if self.P.is_cuda else 0
+            self._lanes = []
+            for i in range(n):
+                self._lanes.append({
+                    "stream": torch.cuda.Stream(device=self.device) if n > 1 else None,
+                    "sumsq": torch.zeros(1, dtype=torch.float32, device=self.device) if n > 1 else self._sumsq,
+                    "work": {} if n > 1 else self._ns_work,
+                    "ctas": (sms + n - 1) // n if n > 1 else 0,
+                })
+        return self._lanes
 
     # ---- checkpoint ------------------------------------------------------------------------
     def state_dict(self) -> Dict[str, Any]:
