@@ -90,7 +90,7 @@ def build_config(args, out_dir):
         "trainer_type": "fsdp2_trainer",
         "dataset_config": {
             "dataset_type": "synthetic_packed", "dataset_format": "synthetic", "packing": True,
-            "packing_strategy": "first_fit", "packing_length": args.tokens, "data_seed": 1234,
+            "packing_strategy": "first_fit", "packing_length": args.tokens * args.sp, "data_seed": 1234,
             "extra_kwargs": {"vocab_size": model_cfg["vocab_size"], "min_len": 128, "max_len": 8192, "fill_exact": True},
         },
         "model_config": {"load_from_config": {"model_type": "qwen2", "config": model_cfg}},
@@ -98,7 +98,7 @@ def build_config(args, out_dir):
             output_dir=out_dir, max_steps=10**9, learning_rate=2e-4, weight_decay=0.01, per_device_train_batch_size=1,
             bf16=True, logging_steps=10**9, save_strategy="no", lr_scheduler_type="constant", use_muon=not args.adamw,
             max_grad_norm=1.0, sharding_runtime=args.runtime, seed=0, dataloader_pin_memory=True,
-            gradient_checkpointing=bool(args.checkpointing),
+            gradient_checkpointing=bool(args.checkpointing), sp_ulysses_degree=args.sp,
         ),
     }
 
@@ -185,7 +185,7 @@ def run_ours(args):
     ms, ms_e2e = float(t[0]), float(t[1])
     peak_gb = torch.cuda.max_memory_allocated() / 2**30
     if rank == 0:
-        total_tokens = tokens_per_step * world * args.steps
+        total_tokens = tokens_per_step * (world // args.sp) * args.steps  # one packed sequence per sequence-parallel group
         value = total_tokens / (ms / 1e3)
         e2e = total_tokens / (ms_e2e / 1e3)
         seqlens = (host_batches[0]["cu_seqlens"][1:] - host_batches[0]["cu_seqlens"][:-1]).tolist()
@@ -195,8 +195,9 @@ def run_ours(args):
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (uniform random ids, docs U[128,8192] packed to 16384 tokens/GPU), random-init weights",
             "config": {"model": "Qwen2.5-7B-style (28L, h3584, 28q/4kv, d128, ffn18944, vocab152064, qkv bias)",
-                       "global_batch": tokens_per_step * world, "seq_len": tokens_per_step,
-                       "parallelism": f"dp{world} ({tr.runtime_kind} runtime)", "optimizer": "adamw" if args.adamw else "muon+adamw",
+                       "global_batch": tokens_per_step * (world // args.sp), "seq_len": tokens_per_step,
+                       "parallelism": (f"dp{world} ({tr.runtime_kind} runtime)" if args.sp == 1 else
+                                       f"dp{world // args.sp} x ulysses{args.sp} ({tr.runtime_kind} runtime; not the headline layout)"), "optimizer": "adamw" if args.adamw else "muon+adamw",
                        "l2": "inputs and weights larger than L2 every step (15 GB of parameters)",
                        "layers": build_config(args, "x")["model_config"]["load_from_config"]["config"]["num_hidden_layers"],
                        "linear_backend": gemm_ops.LINEAR_BACKEND},
@@ -228,6 +229,7 @@ def main():
     ap.add_argument("--runtime", default="native", choices=["native", "torch_fsdp2", "auto"])
     ap.add_argument("--linear-backend", default=None, choices=[None, "tcgen05", "cublas"])
     ap.add_argument("--checkpointing", type=int, default=0)
+    ap.add_argument("--sp", type=int, default=1, help="Ulysses degree (not the headline layout; sequence = tokens * sp)")
     ap.add_argument("--ref-checkpointing", type=int, default=1,
                     help="reference arm: gradient checkpointing as in its examples/qwen2_5_llm config")
     args = ap.parse_args()
