@@ -127,7 +127,9 @@ def make_dispatcher(group, num_experts: int, device):
         if torch.device(device).type == "cuda" and fused_ops.peer_memory_ok(group):
             from .peer_expert_parallel import PeerExpertParallel
 
-            ep = PeerExpertParallel(group, num_experts, torch.device("cuda", torch.cuda.current_device()))
+            ep = fused_ops.agree_or_none(
+                lambda: PeerExpertParallel(group, num_experts, torch.device("cuda", torch.cuda.current_device())), group,
+                "expert parallelism over peer memory")
         _PEER_DISPATCHERS[key] = ep if ep is not None else ExpertParallel(group, num_experts)
     return _PEER_DISPATCHERS[key]
 

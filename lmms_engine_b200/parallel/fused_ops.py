@@ -52,12 +52,32 @@ def context_for(group) -> Optional[FusedComm]:
     if key in _CONTEXTS:
         return _CONTEXTS[key]
     fc = None
-    ok = peer_memory_ok(group)
-    if ok:
-        fc = FusedComm(group, torch.device("cuda", torch.cuda.current_device()))
-        fc._routes = {}
+    if peer_memory_ok(group):
+        fc = agree_or_none(lambda: FusedComm(group, torch.device("cuda", torch.cuda.current_device())), group,
+                           "fused collectives")
+        if fc is not None:
+            fc._routes = {}
     _CONTEXTS[key] = fc
     return fc
+
+
+def agree_or_none(build, group, what: str):
+    """Run ``build()`` on every rank of ``group``; keep the result only if it succeeded everywhere, so that
+    a machine without peer access falls back to NCCL on all ranks together instead of splitting the group."""
+    obj, err = None, None
+    try:
+        obj = build()
+    except Exception as e:  # symmetric-memory allocation / rendezvous not available
+        err = e
+    flag = torch.tensor([1 if obj is not None else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    if int(flag.item()) == 0:
+        if dist.get_rank(group) == 0:
+            from ..utils.logging_utils import logger
+
+            logger.warning(f"{what}: peer-mapped memory is not usable ({err}); using NCCL collectives")
+        return None
+    return obj
 
 
 def _route(fc: FusedComm, kind: str, n_q: int, n_kv: int, D: int):
