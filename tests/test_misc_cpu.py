@@ -255,3 +255,33 @@ def test_head_routing_tables_match_the_ulysses_layout():
     assert o.cols_local == hq * D and o.chunk_dst.tolist() == [h // hq for h in range(nq) for _ in range(2)]
     with pytest.raises(ValueError):
         qkv_head_route(28, 4, 128, 8, "cpu")
+
+
+def test_ema_filter_compute_tracker_and_formatting(tmp_path, monkeypatch):
+    from lmms_engine_b200.utils.compute_tracker import ComputeTracker
+    from lmms_engine_b200.utils.ema_utils import EMAHelper
+    from lmms_engine_b200.utils.train_utils import TrainUtilities
+
+    model = torch.nn.Sequential(torch.nn.Linear(4, 4), torch.nn.LayerNorm(4))
+    model[1].bias.requires_grad_(False)
+    ema = EMAHelper(model, decay=0.5, param_filter={"mode": "regex", "include": [r"^0[.]"], "exclude": ["bias"]})
+    ema.maybe_init()
+    assert sorted(ema.state_dict()) == ["0.weight"]
+    w0 = model[0].weight.detach().clone()
+    with torch.no_grad():
+        model[0].weight.add_(2.0)
+    ema.update(1)
+    assert torch.allclose(ema.state_dict()["0.weight"].float(), w0 + 1.0, atol=1e-6)  # 0.5 * old + 0.5 * new
+    monkeypatch.setattr(TrainUtilities, "_device_name", staticmethod(lambda: "NVIDIA B200"))
+    assert TrainUtilities.get_device_flops("P") == pytest.approx(2.25) and TrainUtilities.get_device_tdp() == 1000.0
+    ct = ComputeTracker(num_gpus=8)
+    ct.update(flops=1e18, tokens=2_000_000, seconds=3600.0)
+    s = ct.summary()
+    assert s["energy_kwh"] == pytest.approx(8.0) and s["gpu_hours"] == pytest.approx(8.0) and s["total_tokens_human"] == "2.00M"
+    assert s["total_flops_human"] == "1.00 EFLOPs" and s["co2_kg"] == pytest.approx(8.0 * 0.475)
+    ct2 = ComputeTracker(num_gpus=8)
+    ct2.load_state_dict(ct.state_dict())
+    assert ct2.summary()["total_flops"] == 1e18
+    hf = TrainUtilities.convert_open_to_hf([{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "a.png"}},
+                                                                           {"type": "text", "text": "hi"}]}])
+    assert hf[0]["content"][0] == {"type": "image", "image": "a.png"}
