@@ -6,12 +6,17 @@ from __future__ import annotations
 import json
 import os
 
+
+def _emit(obj) -> None:
+    """Result line on the descriptor that ``bench.py`` kept for it (its original stdout)."""
+    os.write(int(os.environ.get("BENCH_JSON_FD", "1")), (json.dumps(obj) + "\n").encode())
+
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 def unavailable(reason: str) -> None:
     if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": reason}), flush=True)
+        _emit({"impl": "reference", "unavailable": reason})
 
 
 def run(args) -> None:

@@ -26,8 +26,15 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
-# stdout carries the one JSON line only: NCCL's own banner / debug output goes to stderr
-os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+
+
+def emit_json(obj) -> None:
+    """Write the result line to the process's ORIGINAL stdout.  ``main`` points file descriptor 1 at stderr
+    for the rest of the run, so banners that libraries print to stdout (NCCL's version line) cannot end up
+    next to the JSON line."""
+    fd = int(os.environ.get("BENCH_JSON_FD", "1"))
+    os.write(fd, (json.dumps(obj) + "\n").encode())
+
 
 MODEL_7B = dict(vocab_size=152064, hidden_size=3584, intermediate_size=18944, num_hidden_layers=28,
                 num_attention_heads=28, num_key_value_heads=4, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6,
@@ -208,7 +215,7 @@ def run_ours(args):
             "gpu_launches": launches, "tokens_per_gpu_per_s": value / world,
             "mfu_ref_formula": flops / (ms / args.steps / 1e3) / 2.25e15, "peak_mem_gb": peak_gb, "last_loss": last,
         }
-        print(json.dumps(out), flush=True)
+        emit_json(out)
     if dist.is_initialized():
         dist.destroy_process_group()
 
@@ -235,6 +242,9 @@ def main():
     ap.add_argument("--ref-checkpointing", type=int, default=1,
                     help="reference arm: gradient checkpointing as in its examples/qwen2_5_llm config")
     args = ap.parse_args()
+    sys.stdout.flush()
+    os.environ["BENCH_JSON_FD"] = str(os.dup(1))
+    os.dup2(2, 1)
     if args.impl == "reference":
         run_reference(args)
     else:
