@@ -68,6 +68,7 @@ struct GemmParams {
   const int* expert_start;     // grouped-K: row range [start[e], start[e+1]) of expert e in A and B
   int group_k;                 // 1: C[e] = A[rows_e]^T B[rows_e] (both operands MN-major)
   int n_experts;
+  int group_m;                 // m-blocks that share one sweep over N (L2 reuse of the B panels)
   int* status;
 };
 
@@ -148,8 +149,7 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)
 
 // Map a linear tile index to (m_block, n_block).  Sixteen m-blocks share each sweep
 // over N so that concurrently resident CTAs reuse the same B panels out of L2.
-__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& mb, int& nb) {
-  constexpr int kGroup = 16;
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& mb, int& nb, int kGroup) {
   int per_group = kGroup * tiles_n;
   int g = t / per_group;
   int first_m = g * kGroup;
@@ -222,12 +222,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   auto decode = [&](int t, int& e, int& mb, int& nb, int& kb_lo, int& kb_n) {
     if (p.group_k) {
       e = t / tiles_per_expert;
-      tile_coords(t - e * tiles_per_expert, tiles_m, tiles_n, mb, nb);
+      tile_coords(t - e * tiles_per_expert, tiles_m, tiles_n, mb, nb, p.group_m);
       const int r0 = p.expert_start[e], r1 = p.expert_start[e + 1];
       kb_lo = r0 / BK;
       kb_n = (r1 - r0) / BK;
     } else {
-      tile_coords(t, tiles_m, tiles_n, mb, nb);
+      tile_coords(t, tiles_m, tiles_n, mb, nb, p.group_m);
       if (COMM) {
         // start with the row blocks whose data is local (gather) or whose destination is the
         // farthest in the ring (reduce-scatter), so that transfers overlap the remaining tiles
@@ -834,6 +834,7 @@ static int make_map_e3(CUtensorMap* m, const void* ptr, uint64_t E, uint64_t R, 
 }
 
 static int g_num_sms = 0;
+static int g_group_m = 16;
 
 template <int EPI, int COMM = 0>
 static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const CUtensorMap& tC,
@@ -870,7 +871,9 @@ static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMa
     cp.push_done_target += static_cast<uint32_t>(ctas);
   }
   if (launched != nullptr) *launched = ctas;
-  gemm_bf16_kernel<EPI, COMM><<<ctas, kThreads, kSmemBytes, stream>>>(tA, tB, tB2, tC, tC2, tC3, p, cp);
+  GemmParams pp = p;
+  if (pp.group_m <= 0) pp.group_m = g_group_m;
+  gemm_bf16_kernel<EPI, COMM><<<ctas, kThreads, kSmemBytes, stream>>>(tA, tB, tB2, tC, tC2, tC3, pp, cp);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -1161,6 +1164,12 @@ int b200_gemm_grouped_wgrad_bf16(const void* A, const void* B, void* dW, const v
   p.n_experts = E;
   p.status = status;
   return launch<EPI_PLAIN>(tA, tB, tB, tC, tC, tC, p, 0, stream);
+}
+
+// Tuning knob: how many m-blocks share a sweep over N (default 16).
+int b200_gemm_set_group_m(int g) {
+  if (g >= 1 && g <= 1024) g_group_m = g;
+  return g_group_m;
 }
 
 int b200_gemm_tile_n() { return BN; }
