@@ -124,6 +124,7 @@ class NanovlmProcessor(ChatProcessor):
         return out
 
 
+@register_processor("aero")
 @register_processor("qwen2_audio")
 class Qwen2AudioProcessor(ChatProcessor):
     """ChatML text with ``<|AUDIO|>`` placeholders: one per pooled encoder frame of every audio clip."""

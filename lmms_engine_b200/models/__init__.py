@@ -35,3 +35,6 @@ register_model("nanovlm", NanovlmConfig, Nanovlm, "image_text_to_text")
 from .audio import Qwen2AudioConfig, Qwen2AudioModel  # noqa: E402
 
 register_model("qwen2_audio", Qwen2AudioConfig, Qwen2AudioModel, "general")
+from .audio import AeroConfig, AeroModel  # noqa: E402
+
+register_model("aero", AeroConfig, AeroModel, "general")

@@ -153,12 +153,13 @@ class _Projector(nn.Module):
 class Qwen2AudioModel(nn.Module):
     config_class = Qwen2AudioConfig
     _no_split_modules = ["DecoderLayer", "AudioEncoderLayer"]
+    projector_name = "multi_modal_projector"  # parameter prefix of the projector in hub checkpoints
 
     def __init__(self, cfg: Qwen2AudioConfig):
         super().__init__()
         self.config = cfg
         self.audio_tower = AudioEncoder(cfg.audio_config)
-        self.multi_modal_projector = _Projector(cfg.audio_config.d_model, cfg.text_config.hidden_size)
+        setattr(self, self.projector_name, _Projector(cfg.audio_config.d_model, cfg.text_config.hidden_size))
         self.language_model = DecoderLM(cfg.text_config)
 
     @property
@@ -187,8 +188,25 @@ class Qwen2AudioModel(nn.Module):
         mask_in = feature_attention_mask if feature_attention_mask is not None else audio_attention_mask
         if feats_in is not None and feats_in.numel() > 0:
             feats, _ = self.audio_tower(feats_in, mask_in)
-            feats = self.multi_modal_projector(feats).to(emb.dtype)
+            feats = getattr(self, self.projector_name)(feats).to(emb.dtype)
             m = ids == self.config.audio_token_index
             src = (torch.cumsum(m, 0) - 1).clamp(min=0, max=max(feats.shape[0] - 1, 0))
             emb = torch.where(m.unsqueeze(-1), feats.index_select(0, src), emb)
         return self.language_model(inputs_embeds=emb, labels=lab, cu_seqlens=cu, position_ids=pos)
+
+
+@dataclass
+class AeroConfig(Qwen2AudioConfig):
+    """``model_type: aero`` with the Qwen2-Audio encoder (reference: src/lmms_engine/models/aero/configuration_aero.py:28-66;
+    its Qwen2.5-Omni encoder option is not built)."""
+
+    model_type: str = "aero"
+    audio_token_index: int = 151648
+
+
+class AeroModel(Qwen2AudioModel):
+    """Audio-LM of the reference (src/lmms_engine/models/aero/modeling_aero.py:230-420): same structure as
+    Qwen2-Audio, projector stored as ``audio_modal_projector``."""
+
+    config_class = AeroConfig
+    projector_name = "audio_modal_projector"
