@@ -45,6 +45,12 @@ class AudioEncoderConfig:
 
 
 @dataclass
+class OmniAudioEncoderConfig(AudioEncoderConfig):
+    n_window: int = 100
+    output_dim: int = 3584
+
+
+@dataclass
 class Qwen2AudioConfig:
     model_type: str = "qwen2_audio"
     text_config: Any = None
@@ -61,12 +67,19 @@ class Qwen2AudioConfig:
         kw["extra"] = {k: v for k, v in d.items() if k not in known}
         cfg = cls(**kw)
         cfg.text_config = text if isinstance(text, DecoderConfig) else DecoderConfig.from_dict({"model_type": "qwen2", **text})
-        cfg.audio_config = audio if isinstance(audio, AudioEncoderConfig) else AudioEncoderConfig.from_dict(audio)
+        if isinstance(audio, AudioEncoderConfig):
+            cfg.audio_config = audio
+        elif audio.get("model_type") == "qwen2_5_omni_audio_encoder":
+            cfg.audio_config = OmniAudioEncoderConfig.from_dict(audio)
+        else:
+            cfg.audio_config = AudioEncoderConfig.from_dict(audio)
         return cfg
 
     def to_dict(self):
         return {"model_type": self.model_type, "text_config": self.text_config.to_dict(),
-                "audio_config": {f.name: getattr(self.audio_config, f.name) for f in fields(self.audio_config)},
+                "audio_config": {"model_type": ("qwen2_5_omni_audio_encoder" if isinstance(self.audio_config, OmniAudioEncoderConfig)
+                                                else "qwen2_audio_encoder"),
+                                 **{f.name: getattr(self.audio_config, f.name) for f in fields(self.audio_config)}},
                 "audio_token_index": self.audio_token_index, **self.extra}
 
     @property
@@ -141,13 +154,73 @@ class AudioEncoder(nn.Module):
         return self.layer_norm(torch.cat(pooled, 0)), out_len
 
 
+class OmniAudioEncoder(nn.Module):
+    """Audio encoder of Qwen2.5-Omni (also an option of ``aero``): the mel stream is cut into chunks of
+    ``2 * n_window`` frames, attention stays inside a chunk (one varlen document per chunk, sinusoidal
+    positions restart per chunk), features are average-pooled by 2 per clip and projected to ``output_dim``.
+    Input: ``input_features [mel_bins, sum(feature_lens)]`` (clips concatenated in time), ``feature_lens``."""
+
+    def __init__(self, c: OmniAudioEncoderConfig):
+        super().__init__()
+        self.cfg = c
+        self.n_window = c.n_window
+        self.conv1 = nn.Conv1d(c.num_mel_bins, c.d_model, kernel_size=3, padding=1)
+        self.conv2 = nn.Conv1d(c.d_model, c.d_model, kernel_size=3, stride=2, padding=1)
+        half = c.d_model // 2
+        inv = torch.exp(-(math.log(10000.0) / (half - 1)) * torch.arange(half).float())
+        t = torch.arange(c.max_source_positions)[:, None] * inv[None, :]
+        self.register_buffer("positional_embedding", torch.cat([torch.sin(t), torch.cos(t)], 1), persistent=False)
+        self.audio_bos_eos_token = nn.Embedding(2, c.output_dim)
+        self.layers = nn.ModuleList([AudioEncoderLayer(c) for _ in range(c.encoder_layers)])
+        self.ln_post = LayerNorm(c.d_model, 1e-5)
+        self.proj = nn.Linear(c.d_model, c.output_dim)
+
+    @staticmethod
+    def output_lengths(feature_lens: torch.Tensor):
+        after_cnn = (feature_lens - 1) // 2 + 1
+        return after_cnn, (after_cnn - 2) // 2 + 1
+
+    def forward(self, input_features: torch.Tensor, feature_lens: torch.Tensor):
+        w2 = self.n_window * 2
+        lens = feature_lens.tolist()
+        chunk_lengths = []
+        for L in lens:
+            n = -(-L // w2)
+            chunk_lengths += [w2] * (n - 1) + [L - (n - 1) * w2]
+        dt = self.conv1.weight.dtype
+        chunks = input_features.to(dt).split(chunk_lengths, dim=1)
+        max_len = max(chunk_lengths)
+        padded = input_features.new_zeros((len(chunks), input_features.shape[0], max_len), dtype=dt)
+        mask = torch.zeros((len(chunks), 1, max_len), dtype=dt, device=input_features.device)
+        for i, (ch, L) in enumerate(zip(chunks, chunk_lengths)):
+            padded[i, :, :L] = ch
+            mask[i, 0, :L] = 1
+        x = F.gelu(self.conv1(padded)) * mask
+        x = F.gelu(self.conv2(x)).transpose(1, 2)
+        x = x + self.positional_embedding[: x.shape[1]].to(x.dtype)
+        after = [(L - 1) // 2 + 1 for L in chunk_lengths]
+        flat = torch.cat([x[i, :n] for i, n in enumerate(after)], 0)
+        cu = torch.cumsum(torch.tensor([0] + after, device=x.device), 0).to(torch.int32)
+        for layer in self.layers:
+            flat = layer(flat, cu)
+        after_cnn, out_len = self.output_lengths(feature_lens)
+        outs, start = [], 0
+        for n, m in zip(after_cnn.tolist(), out_len.tolist()):
+            seg = flat[start:start + 2 * m].view(m, 2, -1).mean(1) if m > 0 else flat[:0]
+            outs.append(seg)
+            start += n
+        h = self.ln_post(torch.cat(outs, 0))
+        return gemm_ops.linear(h, self.proj.weight, self.proj.bias), out_len
+
+
 class _Projector(nn.Module):
-    def __init__(self, d_in: int, d_out: int):
+    def __init__(self, d_in: int, d_out: int, pre_gelu: bool = False):
         super().__init__()
         self.linear = nn.Linear(d_in, d_out, bias=True)
+        self.pre_gelu = pre_gelu
 
     def forward(self, x):
-        return gemm_ops.linear(x, self.linear.weight, self.linear.bias)
+        return gemm_ops.linear(F.gelu(x) if self.pre_gelu else x, self.linear.weight, self.linear.bias)
 
 
 class Qwen2AudioModel(nn.Module):
@@ -158,8 +231,14 @@ class Qwen2AudioModel(nn.Module):
     def __init__(self, cfg: Qwen2AudioConfig):
         super().__init__()
         self.config = cfg
-        self.audio_tower = AudioEncoder(cfg.audio_config)
-        setattr(self, self.projector_name, _Projector(cfg.audio_config.d_model, cfg.text_config.hidden_size))
+        self.omni_encoder = isinstance(cfg.audio_config, OmniAudioEncoderConfig)
+        if self.omni_encoder:
+            self.audio_tower = OmniAudioEncoder(cfg.audio_config)
+            proj = _Projector(cfg.audio_config.output_dim, cfg.text_config.hidden_size, pre_gelu=True)
+        else:
+            self.audio_tower = AudioEncoder(cfg.audio_config)
+            proj = _Projector(cfg.audio_config.d_model, cfg.text_config.hidden_size)
+        setattr(self, self.projector_name, proj)
         self.language_model = DecoderLM(cfg.text_config)
 
     @property
@@ -187,7 +266,13 @@ class Qwen2AudioModel(nn.Module):
         feats_in = input_features if input_features is not None else audio_values
         mask_in = feature_attention_mask if feature_attention_mask is not None else audio_attention_mask
         if feats_in is not None and feats_in.numel() > 0:
-            feats, _ = self.audio_tower(feats_in, mask_in)
+            if self.omni_encoder:
+                # clips concatenated in time, valid frames only
+                lens = mask_in.sum(-1).long()
+                stream = torch.cat([feats_in[i, :, : int(n)] for i, n in enumerate(lens.tolist())], 1)
+                feats, _ = self.audio_tower(stream, lens)
+            else:
+                feats, _ = self.audio_tower(feats_in, mask_in)
             feats = getattr(self, self.projector_name)(feats).to(emb.dtype)
             m = ids == self.config.audio_token_index
             src = (torch.cumsum(m, 0) - 1).clamp(min=0, max=max(feats.shape[0] - 1, 0))
@@ -197,8 +282,8 @@ class Qwen2AudioModel(nn.Module):
 
 @dataclass
 class AeroConfig(Qwen2AudioConfig):
-    """``model_type: aero`` with the Qwen2-Audio encoder (reference: src/lmms_engine/models/aero/configuration_aero.py:28-66;
-    its Qwen2.5-Omni encoder option is not built)."""
+    """``model_type: aero`` (reference: src/lmms_engine/models/aero/configuration_aero.py:28-66); ``audio_config.model_type``
+    selects the Qwen2-Audio encoder (default) or the chunked Qwen2.5-Omni encoder."""
 
     model_type: str = "aero"
     audio_token_index: int = 151648

@@ -185,3 +185,42 @@ def test_audio_encoder_matches_upstream_and_feeds_the_decoder():
     # the collator's names for the same tensors are accepted as well
     out2 = model(input_ids=ids, labels=ids, cu_seqlens=cu, audio_values=x, audio_attention_mask=mask)
     assert abs(float(out["loss"]) - float(out2["loss"])) < 1e-6
+
+
+def test_omni_audio_encoder_matches_upstream():
+    """Chunked audio encoder (attention inside 2*n_window-frame chunks) == upstream Qwen2_5OmniAudioEncoder."""
+    pytest.importorskip("transformers")
+    from transformers.models.qwen2_5_omni.configuration_qwen2_5_omni import Qwen2_5OmniAudioEncoderConfig
+    from transformers.models.qwen2_5_omni.modeling_qwen2_5_omni import Qwen2_5OmniAudioEncoder
+
+    from lmms_engine_b200.mapping_func import create_model_from_config
+    from lmms_engine_b200.models.audio import OmniAudioEncoder, OmniAudioEncoderConfig
+
+    kw = dict(num_mel_bins=16, d_model=32, encoder_layers=2, encoder_attention_heads=4, encoder_ffn_dim=64, max_source_positions=60,
+              n_window=10, output_dim=24)
+    torch.manual_seed(0)
+    hc = Qwen2_5OmniAudioEncoderConfig(**kw)
+    hc._attn_implementation = "eager"
+    hf = Qwen2_5OmniAudioEncoder(hc).eval()
+    mine = OmniAudioEncoder(OmniAudioEncoderConfig(**kw)).eval()
+    mine.load_state_dict(hf.state_dict(), strict=True)
+    lens = torch.tensor([47, 20, 33])
+    x = torch.randn(16, int(lens.sum()))
+    after, out_len = OmniAudioEncoder.output_lengths(lens)
+    with torch.no_grad():
+        ref = hf(x, feature_lens=lens, aftercnn_lens=after).last_hidden_state
+        got, ol = mine(x, lens)
+    assert ol.tolist() == out_len.tolist() and torch.allclose(got, ref, atol=1e-5)
+    # aero with this encoder: padded clips in, features on the placeholders
+    model = create_model_from_config("aero", dict(
+        text_config=dict(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=1, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=16),
+        audio_config=dict(model_type="qwen2_5_omni_audio_encoder", **kw), audio_token_index=127))
+    clips = torch.randn(2, 16, 50)
+    mask = torch.zeros(2, 50, dtype=torch.long)
+    mask[0, :47], mask[1, :20] = 1, 1
+    ids = torch.randint(0, 120, (40,))
+    ids[2:14], ids[20:25] = 127, 127  # 12 + 5 pooled rows
+    out = model(input_ids=ids, labels=ids, cu_seqlens=torch.tensor([0, 40], dtype=torch.int32), audio_values=clips, audio_attention_mask=mask)
+    out["loss"].backward()
+    assert model.audio_tower.proj.weight.grad.abs().sum() > 0
