@@ -153,6 +153,48 @@ class Qwen2AudioProcessor(ChatProcessor):
         return out
 
 
+from .processor.chat import QwenVLProcessor  # noqa: E402
+
+
+@register_processor("Qwen2_5OmniProcessor")
+@register_processor("qwen2_5_omni")
+class OmniProcessor(QwenVLProcessor):
+    """Qwen2.5-VL image / video handling plus log-mel audio clips (one placeholder per pooled encoder row).
+    Temporal positions of videos advance ``position_id_per_seconds`` (25) per second."""
+
+    tokens_per_second = 25.0
+
+    def build(self):
+        super().build()
+        self.n_mels = int(self.kwargs.get("num_mel_bins", 128))
+        self.n_frames = int(self.kwargs.get("max_frames", 3000))
+        self._audio_counts = []
+        return self
+
+    def build_ids_and_labels(self, messages, mm, add_system_prompt=True):
+        mm = dict(mm, audio=list(self._audio_counts))
+        return super().build_ids_and_labels(messages, mm, add_system_prompt)
+
+    def process(self, hf_messages=None, images=None, videos=None, audios=None, add_system_prompt: bool = True, **kw):
+        from .processor.audio_process import log_mel_spectrogram
+
+        audio_out, self._audio_counts = {}, []
+        if audios:
+            feats, masks = [], []
+            for wav in audios:
+                f, m, valid = log_mel_spectrogram(wav, self.n_mels, self.n_frames)
+                feats.append(f), masks.append(m)
+                after = (valid - 1) // 2 + 1
+                self._audio_counts.append(max((after - 2) // 2 + 1, 1))
+            audio_out = {"audio_values": torch.stack(feats), "audio_attention_mask": torch.stack(masks)}
+        try:
+            out = super().process(hf_messages, images=images, videos=videos, audios=None, add_system_prompt=add_system_prompt, **kw)
+        finally:
+            self._audio_counts = []
+        out.update(audio_out)
+        return out
+
+
 # ------------------------------------------------------------------------------- map-style tensor datasets
 class _RecordDataset(DatasetCore, Dataset):
     def __init__(self, config):

@@ -38,3 +38,7 @@ register_model("qwen2_audio", Qwen2AudioConfig, Qwen2AudioModel, "general")
 from .audio import AeroConfig, AeroModel  # noqa: E402
 
 register_model("aero", AeroConfig, AeroModel, "general")
+from .omni import OmniThinker, OmniThinkerConfig  # noqa: E402
+
+for _mt in ("qwen2_5_omni_thinker", "qwen2_5_omni"):
+    register_model(_mt, OmniThinkerConfig, OmniThinker, "general")

@@ -52,6 +52,10 @@ class VLConfig:
         text["model_type"] = text.get("model_type") or ("qwen3_moe" if moe else ("qwen3" if mt.startswith("qwen3") else "qwen2"))
         if text["model_type"].endswith("_text"):
             text["model_type"] = "qwen3_moe" if moe else ("qwen3" if mt.startswith("qwen3") else "qwen2")
+        for key in ("rope_parameters", "rope_scaling"):  # hub configs keep the sections inside the rope dict
+            sect = (text.get(key) or {}).get("mrope_section") if isinstance(text.get(key), dict) else None
+            if sect and "mrope_section" not in text:
+                text["mrope_section"] = list(sect)
         if mt.startswith("qwen3"):
             text.setdefault("mrope_mode", "interleaved")
             text.setdefault("mrope_section", [24, 20, 20])

@@ -224,3 +224,43 @@ def test_omni_audio_encoder_matches_upstream():
     out = model(input_ids=ids, labels=ids, cu_seqlens=torch.tensor([0, 40], dtype=torch.int32), audio_values=clips, audio_attention_mask=mask)
     out["loss"].backward()
     assert model.audio_tower.proj.weight.grad.abs().sum() > 0
+
+
+def test_omni_thinker_matches_upstream_with_text_image_and_audio():
+    """Hub-format weights load (separate q/k/v of the vision blocks are fused) and the loss equals the
+    upstream Qwen2.5-Omni thinker on a sequence with an image and an audio clip."""
+    pytest.importorskip("transformers")
+    from transformers.models.qwen2_5_omni.configuration_qwen2_5_omni import Qwen2_5OmniThinkerConfig
+    from transformers.models.qwen2_5_omni.modeling_qwen2_5_omni import Qwen2_5OmniThinkerForConditionalGeneration
+
+    from lmms_engine_b200.mapping_func import create_model_from_config
+
+    torch.manual_seed(0)
+    text = dict(vocab_size=160, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                rope_scaling={"mrope_section": [2, 3, 3], "rope_type": "default", "type": "default"}, max_position_embeddings=512,
+                rope_theta=10000.0)
+    vis = dict(depth=2, hidden_size=32, intermediate_size=64, num_heads=2, patch_size=4, temporal_patch_size=2, spatial_merge_size=2,
+               out_hidden_size=64, window_size=16, fullatt_block_indexes=[1], in_channels=3)
+    aud = dict(num_mel_bins=16, d_model=32, encoder_layers=1, encoder_attention_heads=4, encoder_ffn_dim=64, max_source_positions=60,
+               n_window=10, output_dim=64)
+    hc = Qwen2_5OmniThinkerConfig(text_config=text, vision_config=vis, audio_config=aud, image_token_index=150, video_token_index=151,
+                                  audio_token_index=152, position_id_per_seconds=25, audio_start_token_id=153, audio_end_token_id=154,
+                                  vision_start_token_id=155, vision_end_token_id=156)
+    for c in (hc, hc.text_config, hc.vision_config, hc.audio_config):
+        c._attn_implementation = "eager"
+    hf = Qwen2_5OmniThinkerForConditionalGeneration(hc).eval().float()
+    mine = create_model_from_config("qwen2_5_omni_thinker", hc.to_dict()).eval()
+    missing, unexpected = mine.load_state_dict(mine.convert_hf_state_dict(hf.state_dict()), strict=False)
+    assert not missing and not unexpected
+    ids = torch.randint(0, 140, (1, 50))
+    ids[0, 2], ids[0, 3:7], ids[0, 7] = 155, 150, 156
+    ids[0, 19], ids[0, 20:32], ids[0, 32] = 153, 152, 154
+    pix, grid = torch.randn(16, 3 * 2 * 4 * 4), torch.tensor([[1, 4, 4]])
+    clips = torch.randn(1, 16, 50)
+    mask = torch.zeros(1, 50, dtype=torch.long)
+    mask[0, :47] = 1
+    kw = dict(input_ids=ids, attention_mask=torch.ones_like(ids), labels=ids, pixel_values=pix, image_grid_thw=grid,
+              input_features=clips, feature_attention_mask=mask)
+    with torch.no_grad():
+        ref, got = hf(**kw).loss, mine(**kw)["loss"]
+    assert abs(float(ref) - float(got)) < 1e-4, (float(ref), float(got))
