@@ -195,6 +195,75 @@ class OmniProcessor(QwenVLProcessor):
         return out
 
 
+@register_processor("llava_video")
+@register_processor("llava_onevision")
+@register_processor("llava")
+class LlavaOnevisionProcessor(ChatProcessor):
+    """Any-resolution tiling of LLaVA-OneVision: an image becomes a resized base view plus the tiles of the
+    best-fitting grid resolution (aspect-preserving resize, centred zero padding); the number of placeholders
+    is what the model's packing of the tile features produces.  Video frames are resized to one tile each."""
+
+    def build(self):
+        super().build()
+        kw = self.kwargs
+        self.tile = int(kw.get("image_size", 384))
+        self.patch = int(kw.get("patch_size", 14))
+        self.max_tiles = int(str(kw.get("vision_aspect_ratio", "anyres_max_9")).replace("anyres_max_", ""))
+        self.pinpoints = kw.get("image_grid_pinpoints") or [[self.tile * i, self.tile * j] for i in range(1, 7) for j in range(1, 7)]
+        self.mean, self.std = float(kw.get("mean", 0.5)), float(kw.get("std", 0.5))
+        return self
+
+    def _to_tensor(self, img):
+        x = torch.from_numpy(np.asarray(img.convert("RGB")).copy()).permute(2, 0, 1).float() / 255.0
+        return (x - self.mean) / self.std
+
+    def tiles_of(self, img):
+        from PIL import Image
+
+        from ..models.llava_ov import select_best_resolution
+
+        img = img if isinstance(img, Image.Image) else Image.fromarray(np.asarray(img).astype(np.uint8))
+        w, h = img.size
+        bh, bw = select_best_resolution((h, w), [tuple(p) for p in self.pinpoints])
+        scale = min(bw / w, bh / h)
+        nw, nh = max(int(math.ceil(w * scale)), 1), max(int(math.ceil(h * scale)), 1)
+        nw, nh = min(nw, bw), min(nh, bh)
+        canvas = Image.new("RGB", (bw, bh), (0, 0, 0))
+        canvas.paste(img.convert("RGB").resize((nw, nh), Image.BICUBIC), ((bw - nw) // 2, (bh - nh) // 2))
+        t = self.tile
+        tiles = [self._to_tensor(img.resize((t, t), Image.BICUBIC))]
+        for i in range(0, bh, t):
+            for j in range(0, bw, t):
+                tiles.append(self._to_tensor(canvas.crop((j, i, j + t, i + t))))
+        return torch.stack(tiles), (h, w)
+
+    def process(self, hf_messages=None, images=None, videos=None, audios=None, add_system_prompt: bool = True, **kw):
+        from PIL import Image
+
+        from ..models.llava_ov import packed_image_tokens
+
+        out: Dict[str, torch.Tensor] = {}
+        mm = {"image": [], "video": [], "audio": []}
+        side = self.tile // self.patch
+        if images:
+            tiles, sizes = zip(*(self.tiles_of(im) for im in images))
+            out["pixel_values"] = torch.cat(tiles)  # tiles of all images, in order
+            out["image_sizes"] = torch.tensor(sizes, dtype=torch.long)
+            mm["image"] = [packed_image_tokens(s, self.pinpoints, self.tile, side, self.max_tiles) for s in sizes]
+        if videos:
+            clips = []
+            for frames in videos:
+                fr = [self._to_tensor(Image.fromarray(np.asarray(f).astype(np.uint8)).resize((self.tile, self.tile), Image.BICUBIC)) for f in frames]
+                clips.append(torch.stack(fr))
+                mm["video"].append(len(fr) * math.ceil(side / 2) ** 2 + 1)
+            if len({c.shape[0] for c in clips}) == 1:
+                out["pixel_values_videos"] = torch.stack(clips)
+            else:
+                raise ValueError("clips of one sample must have the same number of frames")
+        out.update(self.build_ids_and_labels(hf_messages, mm, add_system_prompt))
+        return out
+
+
 # ------------------------------------------------------------------------------- map-style tensor datasets
 class _RecordDataset(DatasetCore, Dataset):
     def __init__(self, config):

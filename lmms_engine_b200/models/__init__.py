@@ -42,3 +42,6 @@ from .omni import OmniThinker, OmniThinkerConfig  # noqa: E402
 
 for _mt in ("qwen2_5_omni_thinker", "qwen2_5_omni"):
     register_model(_mt, OmniThinkerConfig, OmniThinker, "general")
+from .llava_ov import LlavaOnevision, LlavaOnevisionConfig  # noqa: E402
+
+register_model("llava_onevision", LlavaOnevisionConfig, LlavaOnevision, "image_text_to_text")

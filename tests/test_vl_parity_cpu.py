@@ -264,3 +264,59 @@ def test_omni_thinker_matches_upstream_with_text_image_and_audio():
     with torch.no_grad():
         ref, got = hf(**kw).loss, mine(**kw)["loss"]
     assert abs(float(ref) - float(got)) < 1e-4, (float(ref), float(got))
+
+
+def test_llava_onevision_matches_upstream_and_processor_counts():
+    """Any-resolution packing (grid layout, un-padding, newline per row, base view first) and video pooling
+    give the upstream loss on hub-format weights; the processor reserves exactly the rows the model produces."""
+    pytest.importorskip("transformers")
+    import numpy as np
+    from PIL import Image
+    from transformers.models.llava_onevision.configuration_llava_onevision import LlavaOnevisionConfig as HC
+    from transformers.models.llava_onevision.modeling_llava_onevision import LlavaOnevisionForConditionalGeneration
+
+    from lmms_engine_b200.datasets import registry  # noqa: F401
+    from lmms_engine_b200.datasets.config import ProcessorConfig
+    from lmms_engine_b200.mapping_func import DATAPROCESSOR_MAPPING, create_model_from_config
+    from lmms_engine_b200.models.llava_ov import anyres_grid, packed_image_tokens
+
+    torch.manual_seed(0)
+    text = dict(model_type="qwen2", vocab_size=200, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, max_position_embeddings=4096, rope_theta=10000.0)
+    vis = dict(model_type="siglip_vision_model", hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2,
+               image_size=16, patch_size=4, vision_use_head=False)
+    pins = [[16, 16], [16, 32], [32, 16], [32, 32], [16, 48], [48, 16]]
+    hc = HC(text_config=text, vision_config=vis, image_token_index=190, video_token_index=191, image_grid_pinpoints=pins,
+            vision_aspect_ratio="anyres_max_9", tie_word_embeddings=False)
+    for c in (hc, hc.text_config, hc.vision_config):
+        c._attn_implementation = "eager"
+    hf = LlavaOnevisionForConditionalGeneration(hc).eval().float()
+    mine = create_model_from_config("llava_onevision", hc.to_dict()).eval()
+    missing, unexpected = mine.load_state_dict(mine.convert_hf_state_dict(hf.state_dict()), strict=False)
+    assert not missing and not unexpected
+    sizes = [(30, 50), (40, 20)]
+    ntoks = [packed_image_tokens(s, pins, 16, 4) for s in sizes]
+    counts = [1 + anyres_grid(s, pins, 16)[0] * anyres_grid(s, pins, 16)[1] for s in sizes]
+    pix = torch.randn(2, max(counts), 3, 16, 16)
+    ids = torch.randint(0, 180, (1, 20 + sum(ntoks)))
+    ids[0, 3:3 + ntoks[0]] = 190
+    ids[0, 10 + ntoks[0]:10 + ntoks[0] + ntoks[1]] = 190
+    kw = dict(input_ids=ids, attention_mask=torch.ones_like(ids), labels=ids, pixel_values=pix, image_sizes=torch.tensor(sizes))
+    with torch.no_grad():
+        assert abs(float(hf(**kw).loss) - float(mine(**kw)["loss"])) < 1e-4
+    nv = 3 * 4 + 1
+    idv = torch.randint(0, 180, (1, 10 + nv))
+    idv[0, 2:2 + nv] = 191
+    kv = dict(input_ids=idv, attention_mask=torch.ones_like(idv), labels=idv, pixel_values_videos=torch.randn(1, 3, 3, 16, 16))
+    with torch.no_grad():
+        assert abs(float(hf(**kv).loss) - float(mine(**kv)["loss"])) < 1e-4
+    # processor: tiles in order, flattened over images; placeholder count == rows of the packed features
+    proc = DATAPROCESSOR_MAPPING["llava_onevision"](ProcessorConfig(processor_name="none", processor_type="llava_onevision", extra_kwargs={
+        "image_size": 16, "patch_size": 4, "image_grid_pinpoints": pins})).build()
+    img = Image.fromarray((np.random.rand(30, 50, 3) * 255).astype("uint8"))
+    out = proc.process([{"role": "user", "content": [{"type": "image"}, {"type": "text", "text": "what"}]},
+                        {"role": "assistant", "content": [{"type": "text", "text": "a"}]}], images=[img])
+    assert out["pixel_values"].shape == (counts[0], 3, 16, 16) and out["image_sizes"].tolist() == [[30, 50]]
+    assert int((out["input_ids"] == proc.image_token_id).sum()) == ntoks[0]
+    feats = mine.image_features(out["pixel_values"], out["image_sizes"])
+    assert feats.shape[0] == ntoks[0]
