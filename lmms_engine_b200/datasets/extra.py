@@ -195,6 +195,39 @@ class OmniProcessor(QwenVLProcessor):
         return out
 
 
+from .processor.chat import Qwen3VLProcessor  # noqa: E402
+
+
+@register_processor("Qwen3OmniMoeProcessor")
+@register_processor("qwen3_omni_moe")
+class Omni3Processor(Qwen3VLProcessor):
+    """Qwen3-VL image / video handling plus log-mel audio clips; one placeholder per row of the Qwen3-Omni audio
+    encoder (13 rows per 100 mel frames)."""
+
+    build = OmniProcessor.build
+    build_ids_and_labels = OmniProcessor.build_ids_and_labels
+
+    def process(self, hf_messages=None, images=None, videos=None, audios=None, add_system_prompt: bool = True, **kw):
+        from ..models.audio import omni3_output_lengths
+        from .processor.audio_process import log_mel_spectrogram
+
+        audio_out, self._audio_counts = {}, []
+        if audios:
+            feats, masks = [], []
+            for wav in audios:
+                f, m, valid = log_mel_spectrogram(wav, self.n_mels, self.n_frames)
+                feats.append(f), masks.append(m)
+                self._audio_counts.append(max(int(omni3_output_lengths(torch.tensor([valid]))[0]), 1))
+            audio_out = {"audio_values": torch.stack(feats), "audio_attention_mask": torch.stack(masks)}
+        try:
+            out = Qwen3VLProcessor.process(self, hf_messages, images=images, videos=videos, audios=None,
+                                           add_system_prompt=add_system_prompt, **kw)
+        finally:
+            self._audio_counts = []
+        out.update(audio_out)
+        return out
+
+
 @register_processor("llava_video")
 @register_processor("llava_onevision")
 @register_processor("llava")

@@ -45,3 +45,7 @@ for _mt in ("qwen2_5_omni_thinker", "qwen2_5_omni"):
 from .llava_ov import LlavaOnevision, LlavaOnevisionConfig  # noqa: E402
 
 register_model("llava_onevision", LlavaOnevisionConfig, LlavaOnevision, "image_text_to_text")
+from .omni import Omni3Thinker, Omni3ThinkerConfig  # noqa: E402
+
+for _mt in ("qwen3_omni_moe_thinker", "qwen3_omni_moe"):
+    register_model(_mt, Omni3ThinkerConfig, Omni3Thinker, "general")

@@ -88,10 +88,10 @@ class Qwen2AudioConfig:
 
 
 class _SelfAttn(nn.Module):
-    def __init__(self, d: int, heads: int):
+    def __init__(self, d: int, heads: int, k_bias: bool = False):
         super().__init__()
         self.heads, self.head_dim = heads, d // heads
-        self.k_proj = nn.Linear(d, d, bias=False)
+        self.k_proj = nn.Linear(d, d, bias=k_bias)
         self.v_proj = nn.Linear(d, d, bias=True)
         self.q_proj = nn.Linear(d, d, bias=True)
         self.out_proj = nn.Linear(d, d, bias=True)
@@ -99,16 +99,17 @@ class _SelfAttn(nn.Module):
     def forward(self, x, cu):
         P = x.shape[0]
         w = torch.cat([self.q_proj.weight, self.k_proj.weight, self.v_proj.weight], 0)
-        b = torch.cat([self.q_proj.bias, torch.zeros_like(self.q_proj.bias), self.v_proj.bias], 0)
+        kb = self.k_proj.bias if self.k_proj.bias is not None else torch.zeros_like(self.q_proj.bias)
+        b = torch.cat([self.q_proj.bias, kb, self.v_proj.bias], 0)
         qkv = gemm_ops.linear(x, w, b).view(P, 3, self.heads, self.head_dim)
         o = attn_ops.varlen_attn(qkv[:, 0], qkv[:, 1], qkv[:, 2], cu, cu, causal=False, softmax_scale=self.head_dim ** -0.5)
         return gemm_ops.linear(o.reshape(P, -1), self.out_proj.weight, self.out_proj.bias)
 
 
 class AudioEncoderLayer(nn.Module):
-    def __init__(self, c: AudioEncoderConfig):
+    def __init__(self, c: AudioEncoderConfig, k_bias: bool = False):
         super().__init__()
-        self.self_attn = _SelfAttn(c.d_model, c.encoder_attention_heads)
+        self.self_attn = _SelfAttn(c.d_model, c.encoder_attention_heads, k_bias)
         self.self_attn_layer_norm = LayerNorm(c.d_model, 1e-5)
         self.fc1, self.fc2 = nn.Linear(c.d_model, c.encoder_ffn_dim), nn.Linear(c.encoder_ffn_dim, c.d_model)
         self.final_layer_norm = LayerNorm(c.d_model, 1e-5)
@@ -211,6 +212,79 @@ class OmniAudioEncoder(nn.Module):
             start += n
         h = self.ln_post(torch.cat(outs, 0))
         return gemm_ops.linear(h, self.proj.weight, self.proj.bias), out_len
+
+
+@dataclass
+class Omni3AudioEncoderConfig(OmniAudioEncoderConfig):
+    n_window: int = 50
+    n_window_infer: int = 400
+    downsample_hidden_size: int = 480
+    conv_chunksize: int = 500
+
+
+def omni3_output_lengths(input_lengths: torch.Tensor) -> torch.Tensor:
+    """Rows the Qwen3-Omni encoder emits for ``input_lengths`` mel frames (three stride-2 convolutions per
+    100-frame chunk: 13 rows per full chunk)."""
+    leave = input_lengths % 100
+    feat = (leave - 1) // 2 + 1
+    return ((feat - 1) // 2 + 1 - 1) // 2 + 1 + (input_lengths // 100) * 13
+
+
+class Omni3AudioEncoder(nn.Module):
+    """Audio encoder of Qwen3-Omni: chunks of ``2 * n_window`` mel frames go through three stride-2 2-D
+    convolutions (time and frequency) and a linear layer, attention runs inside windows of
+    ``n_window_infer / (2 * n_window)`` chunks (one varlen document per window), then LayerNorm and a
+    two-layer projection to ``output_dim``.  Input as for ``OmniAudioEncoder``."""
+
+    def __init__(self, c: Omni3AudioEncoderConfig):
+        super().__init__()
+        self.cfg = c
+        self.n_window, self.n_window_infer, self.conv_chunksize = c.n_window, c.n_window_infer, c.conv_chunksize
+        half = c.d_model // 2
+        inv = torch.exp(-(math.log(10000.0) / (half - 1)) * torch.arange(half).float())
+        t = torch.arange(c.max_source_positions)[:, None] * inv[None, :]
+        self.register_buffer("positional_embedding", torch.cat([torch.sin(t), torch.cos(t)], 1), persistent=False)
+        self.layers = nn.ModuleList([AudioEncoderLayer(c, k_bias=True) for _ in range(c.encoder_layers)])
+        self.ln_post = LayerNorm(c.d_model, 1e-5)
+        h = c.downsample_hidden_size
+        self.conv2d1 = nn.Conv2d(1, h, 3, 2, padding=1)
+        self.conv2d2 = nn.Conv2d(h, h, 3, 2, padding=1)
+        self.conv2d3 = nn.Conv2d(h, h, 3, 2, padding=1)
+        self.conv_out = nn.Linear(h * ((((c.num_mel_bins + 1) // 2 + 1) // 2 + 1) // 2), c.d_model, bias=False)
+        self.proj1 = nn.Linear(c.d_model, c.d_model)
+        self.proj2 = nn.Linear(c.d_model, c.output_dim)
+
+    def forward(self, input_features: torch.Tensor, feature_lens: torch.Tensor):
+        w2 = self.n_window * 2
+        lens = feature_lens.tolist()
+        chunk_lengths = []
+        for L in lens:
+            n = -(-L // w2)
+            chunk_lengths += [w2] * (n - 1) + [L - (n - 1) * w2]
+        dt = self.conv2d1.weight.dtype
+        chunks = input_features.to(dt).T.split(chunk_lengths, dim=0)
+        padded = nn.utils.rnn.pad_sequence(chunks, batch_first=True).transpose(1, 2).unsqueeze(1)  # [n, 1, mel, t]
+        after = omni3_output_lengths(torch.tensor(chunk_lengths)).tolist()
+        embeds = []
+        for part in padded.split(self.conv_chunksize, dim=0):
+            e = F.gelu(self.conv2d1(part))
+            e = F.gelu(self.conv2d2(e))
+            embeds.append(F.gelu(self.conv2d3(e)))
+        e = torch.cat(embeds, 0)
+        b, c, f, t = e.shape
+        x = gemm_ops.linear(e.permute(0, 3, 1, 2).reshape(b * t, c * f), self.conv_out.weight, None).view(b, t, -1)
+        x = x + self.positional_embedding[:t].to(x.dtype)
+        flat = torch.cat([x[i, :n] for i, n in enumerate(after)], 0)
+        out_len = omni3_output_lengths(feature_lens)
+        window = max(after) * (self.n_window_infer // w2)
+        pieces = [0]
+        for n in out_len.tolist():
+            pieces += [window] * (n // window) + ([n % window] if n % window else [])
+        cu = torch.cumsum(torch.tensor(pieces, device=x.device), 0).to(torch.int32)
+        for layer in self.layers:
+            flat = layer(flat, cu)
+        h = F.gelu(gemm_ops.linear(self.ln_post(flat), self.proj1.weight, self.proj1.bias))
+        return gemm_ops.linear(h, self.proj2.weight, self.proj2.bias), out_len
 
 
 class _Projector(nn.Module):

@@ -15,7 +15,7 @@ from typing import Any, Dict
 
 import torch
 
-from .audio import OmniAudioEncoder, OmniAudioEncoderConfig
+from .audio import Omni3AudioEncoder, Omni3AudioEncoderConfig, OmniAudioEncoder, OmniAudioEncoderConfig
 from .vl import VLConfig, VLModel
 
 
@@ -115,3 +115,67 @@ class OmniThinker(VLModel):
         for (head, kind), parts in qkv.items():
             out[f"{head}.attn.qkv.{kind}"] = torch.cat([parts["q"], parts["k"], parts["v"]], 0)
         return super().convert_hf_state_dict(out)
+
+
+@dataclass
+class Omni3ThinkerConfig(VLConfig):
+    """Qwen3-Omni thinker: mixture-of-experts decoder with interleaved M-RoPE, Qwen3-VL style vision tower
+    with deepstack, Qwen3-Omni audio encoder (``model_type: qwen3_omni_moe_thinker`` / ``qwen3_omni_moe``)."""
+
+    audio_config: Any = None
+    audio_token_id: int = 151675
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "Omni3ThinkerConfig":
+        d = dict(d.get("thinker_config") or d)
+        audio = dict(d.pop("audio_config", None) or {})
+        audio_tok = d.pop("audio_token_id", None)
+        mt = d.get("model_type", "qwen3_omni_moe_thinker")
+        text = dict(d.get("text_config") or {})
+        text["model_type"] = "qwen3_moe"
+        text["tie_word_embeddings"] = bool(d.get("tie_word_embeddings", False))
+        d["text_config"] = text
+        d["model_type"] = "qwen3_vl_moe"
+        base = VLConfig.from_dict(d)
+        cfg = cls(**{f: getattr(base, f) for f in VLConfig.__dataclass_fields__})
+        cfg.model_type = mt
+        audio.setdefault("output_dim", cfg.text_config.hidden_size)
+        cfg.audio_config = Omni3AudioEncoderConfig.from_dict(audio)
+        if audio_tok is not None:
+            cfg.audio_token_id = int(audio_tok)
+        return cfg
+
+    def to_dict(self) -> Dict[str, Any]:
+        d = super().to_dict()
+        d["model_type"] = self.model_type
+        d["architectures"] = ["Qwen3OmniMoeThinkerForConditionalGeneration"]
+        d["audio_config"] = {f: getattr(self.audio_config, f) for f in self.audio_config.__dataclass_fields__}
+        d["audio_token_id"] = self.audio_token_id
+        return d
+
+    @property
+    def is_qwen3(self) -> bool:
+        return True
+
+
+class Omni3Thinker(OmniThinker):
+    config_class = Omni3ThinkerConfig
+
+    def __init__(self, cfg: Omni3ThinkerConfig):
+        base = VLConfig(**{f: getattr(cfg, f) for f in VLConfig.__dataclass_fields__})
+        base.model_type = "qwen3_vl_moe"
+        VLModel.__init__(self, base)
+        self.config = cfg
+        self.audio_tower = Omni3AudioEncoder(cfg.audio_config)
+
+    def convert_hf_state_dict(self, sd):
+        # the hub names of the patch mergers differ from the Qwen3-VL ones that the tower uses
+        ren = {}
+        for k, v in sd.items():
+            k2 = k[len("thinker."):] if k.startswith("thinker.") else k
+            if k2.startswith("visual.merger_list."):
+                k2 = "visual.deepstack_merger_list." + k2[len("visual.merger_list."):]
+            if k2.startswith(("visual.merger.", "visual.deepstack_merger_list.")):
+                k2 = k2.replace(".ln_q.", ".norm.").replace(".mlp.0.", ".linear_fc1.").replace(".mlp.2.", ".linear_fc2.")
+            ren[k2] = v
+        return super().convert_hf_state_dict(ren)

@@ -320,3 +320,51 @@ def test_llava_onevision_matches_upstream_and_processor_counts():
     assert int((out["input_ids"] == proc.image_token_id).sum()) == ntoks[0]
     feats = mine.image_features(out["pixel_values"], out["image_sizes"])
     assert feats.shape[0] == ntoks[0]
+
+
+def test_qwen3_omni_thinker_matches_upstream():
+    """Mixture-of-experts decoder + deepstack vision tower + Qwen3-Omni audio encoder: hub-format weights load
+    (patch-merger names are mapped) and text / image / audio losses equal the upstream thinker."""
+    pytest.importorskip("transformers")
+    from transformers.models.qwen3_omni_moe.configuration_qwen3_omni_moe import Qwen3OmniMoeThinkerConfig
+    from transformers.models.qwen3_omni_moe.modeling_qwen3_omni_moe import Qwen3OmniMoeThinkerForConditionalGeneration
+
+    from lmms_engine_b200.mapping_func import create_model_from_config
+    from lmms_engine_b200.models.audio import omni3_output_lengths
+
+    torch.manual_seed(0)
+    text = dict(vocab_size=160, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, decoder_sparse_step=1, norm_topk_prob=True,
+                mlp_only_layers=[], rope_scaling={"mrope_section": [2, 3, 3], "rope_type": "default", "mrope_interleaved": True},
+                max_position_embeddings=512, rope_theta=10000.0, router_aux_loss_coef=0.0)
+    vis = dict(depth=2, hidden_size=32, intermediate_size=64, num_heads=2, patch_size=4, temporal_patch_size=2, spatial_merge_size=2,
+               out_hidden_size=64, num_position_embeddings=16, deepstack_visual_indexes=[0], in_channels=3)
+    aud = dict(num_mel_bins=16, d_model=32, encoder_layers=1, encoder_attention_heads=4, encoder_ffn_dim=64, max_source_positions=100,
+               n_window=50, n_window_infer=200, output_dim=64, downsample_hidden_size=8, conv_chunksize=3)
+    hc = Qwen3OmniMoeThinkerConfig(text_config=text, vision_config=vis, audio_config=aud, image_token_id=150, video_token_id=151,
+                                   audio_token_id=152, position_id_per_seconds=13, audio_start_token_id=153, vision_start_token_id=155)
+    for c in (hc, hc.text_config, hc.vision_config, hc.audio_config):
+        c._attn_implementation = "eager"
+    hf = Qwen3OmniMoeThinkerForConditionalGeneration(hc).eval().float()
+    mine = create_model_from_config("qwen3_omni_moe_thinker", hc.to_dict()).eval()
+    missing, unexpected = mine.load_state_dict(mine.convert_hf_state_dict(hf.state_dict()), strict=False)
+    assert not missing and not unexpected
+
+    def same(**kw):
+        kw.update(attention_mask=torch.ones_like(kw["input_ids"]), labels=kw["input_ids"])
+        with torch.no_grad():
+            a, b = float(hf(**kw).loss), float(mine(**kw)["loss"])
+        assert abs(a - b) < 1e-4, (a, b)
+
+    t = torch.randint(0, 140, (1, 50))
+    same(input_ids=t)
+    ti = t.clone()
+    ti[0, 2], ti[0, 3:7] = 155, 150
+    same(input_ids=ti, pixel_values=torch.randn(16, 3 * 2 * 4 * 4), image_grid_thw=torch.tensor([[1, 4, 4]]))
+    clips = torch.randn(1, 16, 100)
+    mask = torch.zeros(1, 100, dtype=torch.long)
+    mask[0, :90] = 1  # one attention window: the upstream eager path ignores window boundaries, the flash path and this one do not
+    n = int(omni3_output_lengths(torch.tensor([90]))[0])
+    ta = t.clone()
+    ta[0, 19], ta[0, 20:20 + n] = 153, 152
+    same(input_ids=ta, input_features=clips, feature_attention_mask=mask)
