@@ -49,3 +49,6 @@ from .omni import Omni3Thinker, Omni3ThinkerConfig  # noqa: E402
 
 for _mt in ("qwen3_omni_moe_thinker", "qwen3_omni_moe"):
     register_model(_mt, Omni3ThinkerConfig, Omni3Thinker, "general")
+from .audio import VoxtralRealtimeEncoder, VoxtralRealtimeEncoderConfig  # noqa: E402
+
+register_model("voxtral_realtime_encoder", VoxtralRealtimeEncoderConfig, VoxtralRealtimeEncoder, "general")

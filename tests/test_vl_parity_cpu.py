@@ -368,3 +368,31 @@ def test_qwen3_omni_thinker_matches_upstream():
     ta = t.clone()
     ta[0, 19], ta[0, 20:20 + n] = 153, 152
     same(input_ids=ta, input_features=clips, feature_attention_mask=mask)
+
+
+def test_voxtral_realtime_encoder_matches_upstream():
+    """Causal convolutions + rotary sliding-window attention == upstream VoxtralRealtimeEncoder; a right-padded clip
+    gives the same frames as the clip alone."""
+    pytest.importorskip("transformers")
+    from transformers.models.voxtral_realtime.configuration_voxtral_realtime import VoxtralRealtimeEncoderConfig as HC
+    from transformers.models.voxtral_realtime.modeling_voxtral_realtime import VoxtralRealtimeEncoder as HF
+
+    from lmms_engine_b200.mapping_func import create_model_from_config
+
+    torch.manual_seed(0)
+    hc = HC(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, head_dim=16, num_mel_bins=16, sliding_window=12)
+    hc._attn_implementation = "eager"
+    hf = HF(hc).eval()
+    mine = create_model_from_config("voxtral_realtime_encoder", hc.to_dict()).eval()
+    mine.load_state_dict(hf.state_dict(), strict=True)
+    x = torch.randn(2, 16, 60)
+    with torch.no_grad():
+        ref = hf(input_features=x).last_hidden_state
+        got = mine(x)["last_hidden_state"].view(2, 30, 64)
+    assert torch.allclose(got, ref, atol=1e-4)
+    mask = torch.ones(2, 60, dtype=torch.long)
+    mask[1, 41:] = 0
+    with torch.no_grad():
+        out = mine(x, mask)
+    assert out["frame_lengths"].tolist() == [30, 21]
+    assert torch.allclose(out["last_hidden_state"][30:], ref[1, :21], atol=1e-4)
