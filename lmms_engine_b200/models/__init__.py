@@ -8,7 +8,7 @@ for _mt in ("qwen2", "qwen2_5", "qwen3", "llama"):
 
 from .moe_lm import MoEConfig, MoEDecoderLM
 
-for _mt in ("qwen3_moe", "qwen2_moe", "qwen3_5_moe_text"):
+for _mt in ("qwen3_moe", "qwen2_moe"):
     register_model(_mt, MoEConfig, MoEDecoderLM, "causal_lm")
 
 from .vl import VLConfig, VLModel
@@ -52,3 +52,11 @@ for _mt in ("qwen3_omni_moe_thinker", "qwen3_omni_moe"):
 from .audio import VoxtralRealtimeEncoder, VoxtralRealtimeEncoderConfig  # noqa: E402
 
 register_model("voxtral_realtime_encoder", VoxtralRealtimeEncoderConfig, VoxtralRealtimeEncoder, "general")
+from .qwen3_5 import Qwen35Config, Qwen35LM  # noqa: E402
+
+for _mt in ("qwen3_5_text", "qwen3_5"):
+    register_model(_mt, Qwen35Config, Qwen35LM, "causal_lm")
+from .qwen3_5 import Qwen35MoEConfig, Qwen35MoELM  # noqa: E402
+
+for _mt in ("qwen3_5_moe_text", "qwen3_5_moe"):
+    register_model(_mt, Qwen35MoEConfig, Qwen35MoELM, "causal_lm")

@@ -1,0 +1,321 @@
+"""Qwen3.5 hybrid decoder: three Gated-DeltaNet (linear attention) layers for every gated softmax-attention layer,
+zero-centred RMSNorm, partial rotary embedding (``model_type: qwen3_5_text`` / ``qwen3_5``, text stream).
+The reference patches the ``transformers`` classes and delegates the recurrence to the ``fla`` Triton kernels
+(src/lmms_engine/models/qwen3_5/qwen3_5_ops.py:138-298 linear attention, :445-529 gated attention).
+
+Gated delta rule per head (state ``S [d_k, d_v]``, decay ``exp(g_t) <= 1``, write strength ``beta_t``):
+
+    S_t = exp(g_t) S_{t-1} + beta_t k_t (v_t - (exp(g_t) S_{t-1})^T k_t)^T,    o_t = S_t^T q_t / sqrt(d_k)
+
+It is evaluated chunk-wise (64 tokens): inside a chunk through the inverse of a unit lower-triangular matrix,
+between chunks through the carried state.  Packed documents are processed one by one, so neither the short causal
+convolution nor the state ever crosses a document boundary.  The recurrence runs in fp32 PyTorch; projections,
+norms, the gated attention layers and the loss use the engine's kernels.  Full-attention heads wider than 128
+(the released models use 256) fall back to the reference attention path.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..ops import attention as attn_ops
+from ..ops import gemm as gemm_ops
+from ..ops import norm as norm_ops
+from ..ops import rope as rope_ops
+from .decoder_lm import DecoderBackbone, DecoderConfig, DecoderLM, PackedContext, SwiGLUMLP, _w
+
+
+@dataclass
+class Qwen35Config(DecoderConfig):
+    model_type: str = "qwen3_5_text"
+    partial_rotary_factor: float = 0.25
+    linear_conv_kernel_dim: int = 4
+    linear_key_head_dim: int = 128
+    linear_value_head_dim: int = 128
+    linear_num_key_heads: int = 16
+    linear_num_value_heads: int = 32
+    layer_types: Optional[List[str]] = None
+    full_attention_interval: int = 4
+
+    def __post_init__(self):
+        super().__post_init__()
+        if self.layer_types is None:
+            k = self.full_attention_interval
+            self.layer_types = ["full_attention" if (i + 1) % k == 0 else "linear_attention" for i in range(self.num_hidden_layers)]
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "Qwen35Config":
+        d = dict(d.get("text_config") or d)
+        rope = d.get("rope_parameters") or d.get("rope_scaling") or {}
+        if "partial_rotary_factor" in rope:
+            d.setdefault("partial_rotary_factor", rope["partial_rotary_factor"])
+        d["model_type"] = d.get("model_type", "qwen3_5_text")
+        return super().from_dict(d)
+
+
+class ZRMSNorm(nn.Module):
+    """RMSNorm whose scale is stored as an offset from one (weights initialised to zero)."""
+
+    def __init__(self, dim: int, eps: float = 1e-6):
+        super().__init__()
+        self.weight = nn.Parameter(torch.zeros(dim))
+        self.eps = eps
+
+    def forward(self, x, residual=None):
+        return norm_ops.rmsnorm(x, self.weight, self.eps, 1.0, residual)
+
+
+# ------------------------------------------------------------------------------- gated delta rule
+def _l2norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    return x * torch.rsqrt((x * x).sum(-1, keepdim=True) + eps)
+
+
+def chunk_gated_delta_rule(q, k, v, g, beta, chunk: int = 64):
+    """``q, k [T, H, dk]``, ``v [T, H, dv]``, ``g, beta [T, H]`` of ONE document -> ``o [T, H, dv]`` (fp32 math)."""
+    dt = q.dtype
+    q, k = _l2norm(q.float()), _l2norm(k.float())
+    q, k, v = (x.transpose(0, 1) for x in (q, k, v.float()))  # [H, T, d]
+    g, beta = g.float().transpose(0, 1), beta.float().transpose(0, 1)  # [H, T]
+    H, T, dk = k.shape
+    dv = v.shape[-1]
+    pad = (-T) % chunk
+    if pad:
+        q, k, v = (F.pad(x, (0, 0, 0, pad)) for x in (q, k, v))
+        g, beta = F.pad(g, (0, pad)), F.pad(beta, (0, pad))
+    n = (T + pad) // chunk
+    q = q * dk ** -0.5
+    vb, kb = v * beta[..., None], k * beta[..., None]
+    q, k, v, kb, vb = (x.reshape(H, n, chunk, x.shape[-1]) for x in (q, k, v, kb, vb))
+    g = g.reshape(H, n, chunk).cumsum(-1)
+    decay = (g[..., :, None] - g[..., None, :]).tril().exp().tril()
+    # (I + strictly-lower(kb k^T * decay))^-1 by forward substitution on the unit lower-triangular system
+    a = (kb @ k.transpose(-1, -2)) * decay
+    a = a.masked_fill(torch.triu(torch.ones(chunk, chunk, dtype=torch.bool, device=q.device)), 0)
+    eye = torch.eye(chunk, dtype=a.dtype, device=a.device)
+    inv = torch.linalg.solve_triangular(eye + a, eye.expand_as(a).contiguous(), upper=False)
+    u = inv @ vb                                   # values after the in-chunk corrections
+    w = inv @ (kb * g.exp()[..., None])            # what the carried state contributes to them
+    state = q.new_zeros((H, dk, dv))
+    out = torch.empty_like(u)
+    strict = torch.triu(torch.ones(chunk, chunk, dtype=torch.bool, device=q.device), diagonal=1)
+    for i in range(n):
+        qi, ki = q[:, i], k[:, i]
+        attn = ((qi @ ki.transpose(-1, -2)) * decay[:, i]).masked_fill(strict, 0)
+        v_new = u[:, i] - w[:, i] @ state
+        out[:, i] = (qi * g[:, i, :, None].exp()) @ state + attn @ v_new
+        state = state * g[:, i, -1, None, None].exp() + (ki * (g[:, i, -1, None] - g[:, i]).exp()[..., None]).transpose(-1, -2) @ v_new
+    return out.reshape(H, n * chunk, dv)[:, :T].transpose(0, 1).to(dt)
+
+
+def recurrent_gated_delta_rule(q, k, v, g, beta):
+    """Token-by-token form of the same rule (the oracle of the chunked one)."""
+    q = _l2norm(q.float()) * q.shape[-1] ** -0.5
+    k = _l2norm(k.float())
+    T, H, dk = k.shape
+    state = q.new_zeros((H, dk, v.shape[-1]))
+    out = []
+    for t in range(T):
+        state = state * g[t].float().exp()[:, None, None]
+        delta = (v[t].float() - torch.einsum("hk,hkv->hv", k[t], state)) * beta[t].float()[:, None]
+        state = state + k[t][:, :, None] * delta[:, None, :]
+        out.append(torch.einsum("hk,hkv->hv", q[t], state))
+    return torch.stack(out).to(v.dtype)
+
+
+class GatedDeltaNet(nn.Module):
+    def __init__(self, cfg: Qwen35Config, layer_idx: int):
+        super().__init__()
+        self.hk, self.hv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+        self.dk, self.dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        self.key_dim, self.value_dim = self.hk * self.dk, self.hv * self.dv
+        self.kernel = cfg.linear_conv_kernel_dim
+        conv_dim = 2 * self.key_dim + self.value_dim
+        self.conv1d = nn.Conv1d(conv_dim, conv_dim, self.kernel, groups=conv_dim, padding=self.kernel - 1, bias=False)
+        self.dt_bias = nn.Parameter(torch.ones(self.hv))
+        self.A_log = nn.Parameter(torch.log(torch.empty(self.hv).uniform_(0, 16)))
+        self.norm = nn.Module()
+        self.norm.weight = nn.Parameter(torch.ones(self.dv))
+        self.eps = cfg.rms_norm_eps
+        self.out_proj = nn.Linear(self.value_dim, cfg.hidden_size, bias=False)
+        self.in_proj_qkv = nn.Linear(cfg.hidden_size, conv_dim, bias=False)
+        self.in_proj_z = nn.Linear(cfg.hidden_size, self.value_dim, bias=False)
+        self.in_proj_b = nn.Linear(cfg.hidden_size, self.hv, bias=False)
+        self.in_proj_a = nn.Linear(cfg.hidden_size, self.hv, bias=False)
+
+    def forward(self, x: torch.Tensor, ctx: PackedContext) -> torch.Tensor:
+        T = x.shape[0]
+        w_all = torch.cat([_w(self.in_proj_qkv.weight), _w(self.in_proj_z.weight), _w(self.in_proj_b.weight), _w(self.in_proj_a.weight)], 0)
+        pad = (-w_all.shape[0]) % 8
+        if pad:
+            w_all = F.pad(w_all, (0, 0, 0, pad))
+        proj = gemm_ops.linear(x, w_all, None)
+        c = 2 * self.key_dim + self.value_dim
+        mixed, z = proj[:, :c], proj[:, c:c + self.value_dim]
+        b, a = proj[:, c + self.value_dim:c + self.value_dim + self.hv], proj[:, c + self.value_dim + self.hv:c + self.value_dim + 2 * self.hv]
+        beta = b.sigmoid()
+        g = -self.A_log.float().exp() * F.softplus(a.float() + self.dt_bias)
+        bounds = ctx.cu_seqlens.tolist()
+        outs = []
+        for lo, hi in zip(bounds[:-1], bounds[1:]):
+            if hi <= lo:
+                continue
+            # causal depthwise convolution inside the document, then SiLU
+            seg = F.silu(self.conv1d(mixed[lo:hi].t()[None].to(self.conv1d.weight.dtype))[0, :, : hi - lo]).t()
+            q, k, v = torch.split(seg, [self.key_dim, self.key_dim, self.value_dim], -1)
+            q, k, v = q.reshape(-1, self.hk, self.dk), k.reshape(-1, self.hk, self.dk), v.reshape(-1, self.hv, self.dv)
+            if self.hv // self.hk > 1:
+                q, k = q.repeat_interleave(self.hv // self.hk, 1), k.repeat_interleave(self.hv // self.hk, 1)
+            outs.append(chunk_gated_delta_rule(q, k, v, g[lo:hi], beta[lo:hi]))
+        o = torch.cat(outs, 0) if outs else x.new_zeros((0, self.hv, self.dv))
+        if o.shape[0] < T:  # trailing padding tokens of a sequence-parallel split
+            o = torch.cat([o, o.new_zeros((T - o.shape[0], self.hv, self.dv))], 0)
+        # RMSNorm over the head dim, gated by SiLU(z)
+        o = norm_ops.rmsnorm(o.reshape(-1, self.dv).to(x.dtype), self.norm.weight, self.eps)
+        o = (o.float() * F.silu(z.reshape(-1, self.dv).float())).to(x.dtype).reshape(T, self.value_dim)
+        return gemm_ops.linear(o, _w(self.out_proj.weight), None)
+
+
+class GatedAttention(nn.Module):
+    """Softmax attention whose query projection also emits a per-channel output gate; q/k RMSNorm; partial rotary."""
+
+    def __init__(self, cfg: Qwen35Config, layer_idx: int):
+        super().__init__()
+        self.cfg, self.layer_idx = cfg, layer_idx
+        H, D = cfg.hidden_size, cfg.head_dim
+        self.n_q, self.n_kv, self.head_dim = cfg.num_attention_heads, cfg.num_key_value_heads, D
+        self.q_proj = nn.Linear(H, self.n_q * D * 2, bias=cfg.attention_bias)
+        self.k_proj = nn.Linear(H, self.n_kv * D, bias=cfg.attention_bias)
+        self.v_proj = nn.Linear(H, self.n_kv * D, bias=cfg.attention_bias)
+        self.o_proj = nn.Linear(self.n_q * D, H, bias=cfg.attention_bias)
+        self.q_norm, self.k_norm = ZRMSNorm(D, cfg.rms_norm_eps), ZRMSNorm(D, cfg.rms_norm_eps)
+
+    def forward(self, x, ctx: PackedContext):
+        T, D = x.shape[0], self.head_dim
+        qg = gemm_ops.linear(x, _w(self.q_proj.weight), _w(self.q_proj.bias)).view(T, self.n_q, 2 * D)
+        q, gate = qg[..., :D], qg[..., D:].reshape(T, self.n_q * D)
+        k = gemm_ops.linear(x, _w(self.k_proj.weight), _w(self.k_proj.bias)).view(T, self.n_kv, D)
+        v = gemm_ops.linear(x, _w(self.v_proj.weight), _w(self.v_proj.bias)).view(T, self.n_kv, D)
+        q = self.q_norm(q.reshape(-1, D)).view(T, self.n_q, D)
+        k = self.k_norm(k.reshape(-1, D)).view(T, self.n_kv, D)
+        q, k = rope_ops.rope_apply(q, ctx.cos, ctx.sin), rope_ops.rope_apply(k, ctx.cos, ctx.sin)
+        o = attn_ops.varlen_attn(q, k, v, ctx.cu_seqlens, ctx.cu_seqlens, ctx.max_seqlen, ctx.max_seqlen, causal=ctx.causal,
+                                 softmax_scale=1.0 / math.sqrt(D))
+        o = (o.reshape(T, -1).float() * torch.sigmoid(gate.float())).to(x.dtype)
+        return gemm_ops.linear(o, _w(self.o_proj.weight), _w(self.o_proj.bias))
+
+
+class Qwen35Layer(nn.Module):
+    def __init__(self, cfg: Qwen35Config, layer_idx: int):
+        super().__init__()
+        self.layer_type = cfg.layer_types[layer_idx]
+        if self.layer_type == "linear_attention":
+            self.linear_attn = GatedDeltaNet(cfg, layer_idx)
+        else:
+            self.self_attn = GatedAttention(cfg, layer_idx)
+        self.mlp = SwiGLUMLP(cfg.hidden_size, cfg.intermediate_size)
+        self.input_layernorm = ZRMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
+        self.post_attention_layernorm = ZRMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
+
+    def forward(self, h, residual, ctx: PackedContext):
+        if residual is None:
+            residual, x = h, self.input_layernorm(h)
+        else:
+            x, residual = self.input_layernorm(h, residual)
+        a = self.linear_attn(x, ctx) if self.layer_type == "linear_attention" else self.self_attn(x, ctx)
+        x, residual = self.post_attention_layernorm(a, residual)
+        out = self.mlp(x)
+        if isinstance(out, tuple):  # sparse blocks also return router statistics
+            ctx.aux.append(out[1])
+            out = out[0]
+        return out, residual
+
+
+class Qwen35Backbone(DecoderBackbone):
+    layer_cls = Qwen35Layer
+
+    def __init__(self, cfg: Qwen35Config):
+        super().__init__(cfg)
+        self.norm = ZRMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
+        self.rot_dim = int(cfg.head_dim * cfg.partial_rotary_factor)
+        self.register_buffer("inv_freq", rope_ops.inv_freq(self.rot_dim, cfg.rope_theta), persistent=False)
+
+    def rope_tables(self, position_ids: torch.Tensor):
+        cfg = self.cfg
+        invf = self.inv_freq
+        if invf.dtype != torch.float32 or invf.device != position_ids.device:
+            invf = rope_ops.inv_freq(self.rot_dim, cfg.rope_theta, device=position_ids.device)
+        mode = {"none": rope_ops.MODE_PLAIN, "sectioned": rope_ops.MODE_SECTIONED, "interleaved": rope_ops.MODE_INTERLEAVED}[
+            cfg.mrope_mode if position_ids.dim() == 2 else "none"]
+        sections = tuple(cfg.mrope_section) if (cfg.mrope_section and mode != rope_ops.MODE_PLAIN) else (0, 0, 0)
+        return rope_ops.rope_table(position_ids, invf, mode, sections)
+
+
+class Qwen35LM(DecoderLM):
+    config_class = Qwen35Config
+    backbone_cls = Qwen35Backbone
+    _no_split_modules = ["Qwen35Layer"]
+
+    def _init_weights(self, m):
+        super()._init_weights(m)
+        if isinstance(m, ZRMSNorm):
+            nn.init.zeros_(m.weight)
+
+    def forward(self, *args, **kwargs):
+        if self.sp_group is not None:
+            raise NotImplementedError("sequence parallelism for the linear-attention layers (state hand-off between ranks) is not built")
+        return super().forward(*args, **kwargs)
+
+    def convert_hf_state_dict(self, sd):
+        out = {}
+        for k, v in sd.items():
+            k = k.replace("model.language_model.", "model.")
+            if k.startswith(("model.visual.", "visual.", "mtp.")):
+                continue
+            out[k] = v
+        return out
+
+
+# ------------------------------------------------------------------------------- mixture-of-experts variant
+from .moe_lm import MoEConfig, MoEDecoderLM, SparseMoeBlock  # noqa: E402
+
+
+@dataclass
+class Qwen35MoEConfig(MoEConfig, Qwen35Config):
+    """``qwen3_5_moe_text``: the hybrid layer pattern with sparse MLPs (routed experts + sigmoid-gated shared expert)."""
+
+    model_type: str = "qwen3_5_moe_text"
+
+    @classmethod
+    def from_dict(cls, d):
+        d = dict(d.get("text_config") or d)
+        rope = d.get("rope_parameters") or d.get("rope_scaling") or {}
+        if "partial_rotary_factor" in rope:
+            d.setdefault("partial_rotary_factor", rope["partial_rotary_factor"])
+        return MoEConfig.from_dict.__func__(cls, d)
+
+
+class Qwen35MoELayer(Qwen35Layer):
+    def __init__(self, cfg, layer_idx: int):
+        super().__init__(cfg, layer_idx)
+        if cfg.is_sparse_layer(layer_idx):
+            self.mlp = SparseMoeBlock(cfg)
+
+
+class Qwen35MoEBackbone(Qwen35Backbone):
+    layer_cls = Qwen35MoELayer
+
+
+class Qwen35MoELM(MoEDecoderLM):
+    config_class = Qwen35MoEConfig
+    backbone_cls = Qwen35MoEBackbone
+    _no_split_modules = ["Qwen35MoELayer"]
+
+    def _init_weights(self, m):
+        super()._init_weights(m)
+        if isinstance(m, ZRMSNorm):
+            nn.init.zeros_(m.weight)

@@ -84,3 +84,10 @@ def test_llava_onevision_gpu():
     ids[4:4 + n] = 250
     _compare("llava_onevision", cfg, dict(input_ids=ids, labels=ids, cu_seqlens=torch.tensor([0, 20 + n], dtype=torch.int32),
                                           pixel_values=torch.randn(tiles, 3, 32, 32), image_sizes=torch.tensor([list(size)])))
+
+
+def test_qwen3_5_hybrid_gpu():
+    cfg = dict(TEXT, num_hidden_layers=4, head_dim=64, linear_conv_kernel_dim=4, linear_key_head_dim=32, linear_value_head_dim=32,
+               linear_num_key_heads=2, linear_num_value_heads=4, partial_rotary_factor=0.25)
+    ids = torch.randint(0, 250, (200,))
+    _compare("qwen3_5_text", cfg, dict(input_ids=ids, labels=ids, cu_seqlens=torch.tensor([0, 70, 200], dtype=torch.int32)))

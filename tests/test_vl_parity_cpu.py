@@ -396,3 +396,57 @@ def test_voxtral_realtime_encoder_matches_upstream():
         out = mine(x, mask)
     assert out["frame_lengths"].tolist() == [30, 21]
     assert torch.allclose(out["last_hidden_state"][30:], ref[1, :21], atol=1e-4)
+
+
+def test_gated_delta_rule_chunked_equals_recurrent():
+    from lmms_engine_b200.models.qwen3_5 import chunk_gated_delta_rule, recurrent_gated_delta_rule
+
+    torch.manual_seed(0)
+    for T in (1, 63, 64, 150):
+        q, k, v = torch.randn(T, 3, 16), torch.randn(T, 3, 16), torch.randn(T, 3, 24)
+        g, beta = -torch.rand(T, 3) * 0.5, torch.rand(T, 3)
+        assert torch.allclose(chunk_gated_delta_rule(q, k, v, g, beta), recurrent_gated_delta_rule(q, k, v, g, beta), atol=1e-5)
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_qwen3_5_hybrid_decoder_matches_upstream(moe):
+    """Gated-DeltaNet + gated-attention hybrid (dense and mixture-of-experts) == upstream on hub-format weights;
+    two packed documents == the two documents alone (state and convolution never cross the boundary)."""
+    pytest.importorskip("transformers")
+    from lmms_engine_b200.mapping_func import create_model_from_config
+
+    torch.manual_seed(0)
+    kw = dict(vocab_size=200, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+              linear_conv_kernel_dim=4, linear_key_head_dim=16, linear_value_head_dim=16, linear_num_key_heads=2, linear_num_value_heads=4,
+              max_position_embeddings=512, rope_parameters={"rope_theta": 10000.0, "partial_rotary_factor": 0.25, "rope_type": "default"},
+              tie_word_embeddings=False)
+    if moe:
+        from transformers.models.qwen3_5_moe.configuration_qwen3_5_moe import Qwen3_5MoeTextConfig as HC
+        from transformers.models.qwen3_5_moe.modeling_qwen3_5_moe import Qwen3_5MoeForCausalLM as HF
+
+        kw.update(moe_intermediate_size=32, shared_expert_intermediate_size=48, num_experts=4, num_experts_per_tok=2, router_aux_loss_coef=0.0)
+        name = "qwen3_5_moe_text"
+    else:
+        from transformers.models.qwen3_5.configuration_qwen3_5 import Qwen3_5TextConfig as HC
+        from transformers.models.qwen3_5.modeling_qwen3_5 import Qwen3_5ForCausalLM as HF
+
+        kw.update(intermediate_size=128)
+        name = "qwen3_5_text"
+    hc = HC(**kw)
+    hc._attn_implementation = "eager"
+    hf = HF(hc).eval().float()
+    for n, p in hf.named_parameters():
+        if "norm" in n and "linear_attn" not in n:
+            torch.nn.init.normal_(p, std=0.1)  # zero-centred scales: make them matter
+    mine = create_model_from_config(name, hc.to_dict()).eval()
+    missing, unexpected = mine.load_state_dict(mine.convert_hf_state_dict(hf.state_dict()), strict=False)
+    assert not missing and not unexpected
+    ids = torch.randint(0, 200, (1, 90))
+    with torch.no_grad():
+        ref = float(hf(input_ids=ids, labels=ids).loss)
+        got = float(mine(input_ids=ids, attention_mask=torch.ones_like(ids), labels=ids)["loss"])
+        a, b = ids[0, :50], ids[0, 50:]
+        la, lb = float(hf(input_ids=a[None], labels=a[None]).loss), float(hf(input_ids=b[None], labels=b[None]).loss)
+        packed = float(mine(input_ids=ids[0], labels=ids[0], cu_seqlens=torch.tensor([0, 50, 90], dtype=torch.int32))["loss"])
+    assert abs(ref - got) < 1e-4, (ref, got)
+    assert abs((la * 49 + lb * 39) / 88 - packed) < 1e-4
