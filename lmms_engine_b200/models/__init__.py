@@ -60,3 +60,5 @@ from .qwen3_5 import Qwen35MoEConfig, Qwen35MoELM  # noqa: E402
 
 for _mt in ("qwen3_5_moe_text", "qwen3_5_moe"):
     register_model(_mt, Qwen35MoEConfig, Qwen35MoELM, "causal_lm")
+for _mt in ("qwen3_5", "qwen3_5_moe"):
+    register_model(_mt, VLConfig, VLModel, "image_text_to_text")

@@ -53,7 +53,7 @@ class Qwen35Config(DecoderConfig):
         d = dict(d.get("text_config") or d)
         rope = d.get("rope_parameters") or d.get("rope_scaling") or {}
         if "partial_rotary_factor" in rope:
-            d.setdefault("partial_rotary_factor", rope["partial_rotary_factor"])
+            d["partial_rotary_factor"] = rope["partial_rotary_factor"]  # the rope dict is what the hub model reads
         d["model_type"] = d.get("model_type", "qwen3_5_text")
         return super().from_dict(d)
 
@@ -274,7 +274,7 @@ class Qwen35LM(DecoderLM):
         out = {}
         for k, v in sd.items():
             k = k.replace("model.language_model.", "model.")
-            if k.startswith(("model.visual.", "visual.", "mtp.")):
+            if k.startswith(("model.visual.", "mtp.")):  # text-only use of a multimodal checkpoint; multi-token-prediction head
                 continue
             out[k] = v
         return out
@@ -295,7 +295,7 @@ class Qwen35MoEConfig(MoEConfig, Qwen35Config):
         d = dict(d.get("text_config") or d)
         rope = d.get("rope_parameters") or d.get("rope_scaling") or {}
         if "partial_rotary_factor" in rope:
-            d.setdefault("partial_rotary_factor", rope["partial_rotary_factor"])
+            d["partial_rotary_factor"] = rope["partial_rotary_factor"]  # the rope dict is what the hub model reads
         return MoEConfig.from_dict.__func__(cls, d)
 
 

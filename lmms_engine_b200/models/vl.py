@@ -69,7 +69,15 @@ class VLConfig:
             vis.setdefault("depth", 27)
             vis.setdefault("hidden_size", 1152)
             vis.setdefault("intermediate_size", 4304)
-        tcfg = (MoEConfig if moe else DecoderConfig).from_dict(text)
+        if mt.startswith("qwen3_5"):
+            # hybrid Gated-DeltaNet decoder; its vision tower is the Qwen3-VL one without deepstack taps
+            from .qwen3_5 import Qwen35Config, Qwen35MoEConfig
+
+            text["model_type"] = "qwen3_5_moe_text" if moe else "qwen3_5_text"
+            vis.setdefault("deepstack_visual_indexes", [])
+            tcfg = (Qwen35MoEConfig if moe else Qwen35Config).from_dict(text)
+        else:
+            tcfg = (MoEConfig if moe else DecoderConfig).from_dict(text)
         vis.setdefault("out_hidden_size", tcfg.hidden_size)
         vcfg = VisionConfig.from_dict(vis)
         known = {"image_token_id", "video_token_id", "vision_start_token_id", "vision_end_token_id", "tie_word_embeddings", "architectures"}
@@ -104,7 +112,17 @@ class VLModel(nn.Module):
         super().__init__()
         self.config = cfg
         self.visual = (Qwen3VisionTower if cfg.is_qwen3 else Qwen25VisionTower)(cfg.vision_config)
-        self.language_model = (MoEDecoderLM if isinstance(cfg.text_config, MoEConfig) else DecoderLM)(cfg.text_config)
+        self.language_model = self._decoder_class(cfg.text_config)(cfg.text_config)
+
+    @staticmethod
+    def _decoder_class(text_config):
+        from .qwen3_5 import Qwen35Config, Qwen35LM, Qwen35MoEConfig, Qwen35MoELM
+
+        if isinstance(text_config, Qwen35MoEConfig):
+            return Qwen35MoELM
+        if isinstance(text_config, Qwen35Config):
+            return Qwen35LM
+        return MoEDecoderLM if isinstance(text_config, MoEConfig) else DecoderLM
 
     # ViT frame balancing over the flattened dp x cp ranks (set by the trainer / monkey_patch_kwargs)
     vit_frame_parallel = False

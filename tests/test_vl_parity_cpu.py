@@ -450,3 +450,44 @@ def test_qwen3_5_hybrid_decoder_matches_upstream(moe):
         packed = float(mine(input_ids=ids[0], labels=ids[0], cu_seqlens=torch.tensor([0, 50, 90], dtype=torch.int32))["loss"])
     assert abs(ref - got) < 1e-4, (ref, got)
     assert abs((la * 49 + lb * 39) / 88 - packed) < 1e-4
+
+
+def test_qwen3_5_vision_language_wrapper_matches_upstream():
+    """``qwen3_5`` as an image-text model: Qwen3-VL style tower without deepstack, interleaved M-RoPE on the
+    rotary half of the gated-attention layers, hybrid decoder; loss equal to the hub model's."""
+    from transformers.models.qwen3_5 import modeling_qwen3_5 as m
+    from transformers.models.qwen3_5.configuration_qwen3_5 import Qwen3_5Config
+
+    from lmms_engine_b200.mapping_func import create_model_from_config
+
+    torch.manual_seed(0)
+    text = dict(vocab_size=200, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
+                num_key_value_heads=2, head_dim=32, linear_conv_kernel_dim=4, linear_key_head_dim=16,
+                linear_value_head_dim=16, linear_num_key_heads=2, linear_num_value_heads=4, max_position_embeddings=512,
+                rope_parameters={"rope_theta": 10000.0, "partial_rotary_factor": 0.5, "rope_type": "default",
+                                 "mrope_section": [2, 3, 3], "mrope_interleaved": True})
+    vis = dict(depth=2, hidden_size=32, intermediate_size=64, num_heads=2, patch_size=4, temporal_patch_size=2,
+               spatial_merge_size=2, out_hidden_size=64, num_position_embeddings=16, in_channels=3)
+    hc = Qwen3_5Config(text_config=text, vision_config=vis, image_token_id=190, video_token_id=191,
+                       vision_start_token_id=192, vision_end_token_id=193, tie_word_embeddings=False)
+    for c in (hc, hc.text_config, hc.vision_config):
+        c._attn_implementation = "eager"
+    hf = m.Qwen3_5ForConditionalGeneration(hc).eval().float()
+    mine = create_model_from_config("qwen3_5", hc.to_dict()).eval()
+    assert type(mine).__name__ == "VLModel" and type(mine.language_model).__name__ == "Qwen35LM"
+    missing, unexpected = mine.load_state_dict(mine.convert_hf_state_dict(hf.state_dict()), strict=False)
+    assert not missing and not unexpected, (missing[:4], unexpected[:4])
+    ids = torch.randint(0, 180, (1, 60))
+    ids[0, 2], ids[0, 3:7], ids[0, 7] = 192, 190, 193
+    pix, grid = torch.randn(16, 3 * 2 * 4 * 4), torch.tensor([[1, 4, 4]])
+    mm = (ids == 190).long()
+    ones = torch.ones_like(ids)
+    with torch.no_grad():
+        ref = hf(input_ids=ids, attention_mask=ones, labels=ids, pixel_values=pix, image_grid_thw=grid,
+                 mm_token_type_ids=mm).loss
+        got = mine(input_ids=ids, attention_mask=ones, labels=ids, pixel_values=pix, image_grid_thw=grid)["loss"]
+        t = torch.randint(0, 180, (1, 60))
+        ref_t = hf(input_ids=t, labels=t).loss
+        got_t = mine(input_ids=t, attention_mask=torch.ones_like(t), labels=t)["loss"]
+    assert abs(float(ref) - float(got)) < 2e-5, (float(ref), float(got))
+    assert abs(float(ref_t) - float(got_t)) < 2e-5, (float(ref_t), float(got_t))
