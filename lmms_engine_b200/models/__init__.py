@@ -13,7 +13,7 @@ for _mt in ("qwen3_moe", "qwen2_moe"):
 
 from .vl import VLConfig, VLModel
 
-for _mt in ("qwen2_5_vl", "qwen2_vl", "qwen3_vl", "qwen3_vl_moe"):
+for _mt in ("qwen2_5_vl", "qwen2_vl", "qwen3_vl", "qwen3_vl_moe", "llavaonevision1_5"):
     register_model(_mt, VLConfig, VLModel, "image_text_to_text")
 
 from .bagel import Bagel, BagelConfig

@@ -39,6 +39,11 @@ class VLConfig:
     def is_qwen3(self) -> bool:
         return self.model_type.startswith("qwen3")
 
+    @property
+    def is_rice(self) -> bool:
+        """LLaVA-OneVision-1.5: Rice tower, Qwen3 decoder, plain 1-D rotary positions."""
+        return self.model_type.startswith("llavaonevision1_5")
+
     @classmethod
     def from_dict(cls, d: Dict[str, Any]) -> "VLConfig":
         d = dict(d)
@@ -49,6 +54,18 @@ class VLConfig:
         if not text:
             text = {k: v for k, v in d.items() if k in {f for f in DecoderConfig.__dataclass_fields__}}
         moe = "moe" in mt
+        rice = mt.startswith("llavaonevision1_5")
+        if rice:
+            text["model_type"] = "qwen3"  # q/k RMSNorm on the head dimension, no attention bias
+            text["mrope_section"] = None
+            vis["model_type"] = "rice_vit"
+            vis.setdefault("temporal_patch_size", 1)
+            vis.setdefault("hidden_act", "gelu")
+            vis.setdefault("hidden_size", 1024)
+            vis.setdefault("intermediate_size", 4096)
+            vis.setdefault("depth", 24)
+            if "text_hidden_size" in vis:
+                vis.setdefault("out_hidden_size", vis["text_hidden_size"])
         text["model_type"] = text.get("model_type") or ("qwen3_moe" if moe else ("qwen3" if mt.startswith("qwen3") else "qwen2"))
         if text["model_type"].endswith("_text"):
             text["model_type"] = "qwen3_moe" if moe else ("qwen3" if mt.startswith("qwen3") else "qwen2")
@@ -56,7 +73,9 @@ class VLConfig:
             sect = (text.get(key) or {}).get("mrope_section") if isinstance(text.get(key), dict) else None
             if sect and "mrope_section" not in text:
                 text["mrope_section"] = list(sect)
-        if mt.startswith("qwen3"):
+        if rice:
+            pass
+        elif mt.startswith("qwen3"):
             text.setdefault("mrope_mode", "interleaved")
             text.setdefault("mrope_section", [24, 20, 20])
         else:
@@ -91,6 +110,7 @@ class VLConfig:
              "vision_start_token_id": self.vision_start_token_id, "vision_end_token_id": self.vision_end_token_id,
              "tie_word_embeddings": self.tie_word_embeddings,
              "architectures": self.architectures or [
+                 "LLaVAOneVision1_5_ForConditionalGeneration" if self.is_rice else
                  "Qwen3VLForConditionalGeneration" if self.is_qwen3 else "Qwen2_5_VLForConditionalGeneration"]}
         d.update(self.extra)
         return d
@@ -106,12 +126,17 @@ class VLModel(nn.Module):
     """``visual`` tower + ``language_model`` decoder."""
 
     config_class = VLConfig
-    _no_split_modules = ["DecoderLayer", "MoEDecoderLayer", "VisionBlock"]
+    _no_split_modules = ["DecoderLayer", "MoEDecoderLayer", "VisionBlock", "RiceBlock"]
 
     def __init__(self, cfg: VLConfig):
         super().__init__()
         self.config = cfg
-        self.visual = (Qwen3VisionTower if cfg.is_qwen3 else Qwen25VisionTower)(cfg.vision_config)
+        if cfg.is_rice:
+            from .rice import RiceVisionTower
+
+            self.visual = RiceVisionTower(cfg.vision_config)
+        else:
+            self.visual = (Qwen3VisionTower if cfg.is_qwen3 else Qwen25VisionTower)(cfg.vision_config)
         self.language_model = self._decoder_class(cfg.text_config)(cfg.text_config)
 
     @staticmethod
@@ -189,7 +214,7 @@ class VLModel(nn.Module):
         lm = self.language_model
         had_mrope = position_ids is not None and position_ids.dim() >= 2 and position_ids.shape[-2] == 3
         ids, labels, pos, cu, _ = lm.prepare_packed(input_ids, attention_mask, labels, position_ids if had_mrope else None, cu_seqlens)
-        if not had_mrope:
+        if not had_mrope and not cfg.is_rice:
             grids, secs = [], []
             for g, is_video in ((image_grid_thw, False), (video_grid_thw, True)):
                 if g is None:

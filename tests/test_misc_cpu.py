@@ -174,6 +174,18 @@ def test_example_configs_parse_into_config_objects():
         unknown = set(cfg["trainer_args"]) - known
         assert not unknown, (f, unknown)
         TrainingArguments(**cfg["trainer_args"])
+        # every component an example names is registered, and in-line model configurations parse
+        from lmms_engine_b200 import mapping_func as mf
+        import lmms_engine_b200.datasets.registry  # noqa: F401
+
+        assert cfg["dataset_config"]["dataset_type"] in mf.DATASET_MAPPING, f
+        assert cfg["dataset_config"]["processor_config"]["processor_type"] in mf.DATAPROCESSOR_MAPPING, f
+        inline = cfg["model_config"].get("load_from_config")
+        if inline:
+            config_cls = mf._resolve(inline["model_type"], None)[0]
+            parsed = config_cls.from_dict(dict(inline["config"], model_type=inline["model_type"]))
+            stray = set(getattr(parsed, "extra", None) or {}) - {"model_type"}
+            assert not stray, (f, stray)
 
 
 def test_tools_and_legacy_merge(tmp_path):

@@ -5,6 +5,7 @@ import sys
 
 import pytest
 import torch
+import torch.nn.functional as F
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 transformers = pytest.importorskip("transformers")
@@ -491,3 +492,92 @@ def test_qwen3_5_vision_language_wrapper_matches_upstream():
         got_t = mine(input_ids=t, attention_mask=torch.ones_like(t), labels=t)["loss"]
     assert abs(float(ref) - float(got)) < 2e-5, (float(ref), float(got))
     assert abs(float(ref_t) - float(got_t)) < 2e-5, (float(ref_t), float(got_t))
+
+
+def _rice_reference(sd, patches, grid, heads, merge):
+    """Plain fp32 restatement of the Rice tower for one packed batch: every frame is
+    [class token, patches], attends within itself with 2-D rotary angles (learned for the class token)."""
+    D = sd["pre_layernorm.weight"].numel()
+    hd = D // heads
+    x = patches @ sd["patch_embed.proj.weight"].reshape(D, -1).T
+    invf = 1.0 / (10000.0 ** (torch.arange(0, hd // 2, 2, dtype=torch.float32) / (hd // 2)))
+    outs, at = [], 0
+    for t, h, w in grid:
+        for _ in range(t):
+            n = h * w
+            rows = torch.arange(h).view(h // merge, merge, 1, 1).expand(h // merge, merge, w // merge, merge)
+            cols = torch.arange(w).view(1, 1, w // merge, merge).expand(h // merge, merge, w // merge, merge)
+            rows, cols = rows.permute(0, 2, 1, 3).reshape(-1), cols.permute(0, 2, 1, 3).reshape(-1)
+            ang = torch.cat([rows[:, None] * invf, cols[:, None] * invf], -1)
+            ang = torch.cat([sd["class_pos_emb"], ang], 0)
+            ang = torch.cat([ang, ang], -1)
+            cos, sin = ang.cos()[:, None], ang.sin()[:, None]
+            y = torch.cat([sd["class_embedding"][None], x[at:at + n]], 0)
+            at += n
+            y = F.layer_norm(y, (D,), sd["pre_layernorm.weight"], sd["pre_layernorm.bias"], 1e-5)
+            i = 0
+            while f"blocks.{i}.norm1.weight" in sd:
+                b = f"blocks.{i}."
+                z = F.layer_norm(y, (D,), sd[b + "norm1.weight"], sd[b + "norm1.bias"], 1e-5)
+                q, k, v = (z @ sd[b + "attn.qkv.weight"].T + sd[b + "attn.qkv.bias"]).view(-1, 3, heads, hd).unbind(1)
+                rot = lambda u: u * cos + torch.cat([-u[..., hd // 2:], u[..., :hd // 2]], -1) * sin
+                q, k = rot(q), rot(k)
+                a = torch.softmax(torch.einsum("qhd,khd->hqk", q, k) / hd ** 0.5, -1)
+                o = torch.einsum("hqk,khd->qhd", a, v).reshape(-1, D)
+                y = y + o @ sd[b + "attn.proj.weight"].T + sd[b + "attn.proj.bias"]
+                z = F.layer_norm(y, (D,), sd[b + "norm2.weight"], sd[b + "norm2.bias"], 1e-5)
+                z = F.gelu(z @ sd[b + "mlp.fc1.weight"].T + sd[b + "mlp.fc1.bias"])
+                y = y + z @ sd[b + "mlp.fc2.weight"].T + sd[b + "mlp.fc2.bias"]
+                i += 1
+            outs.append(y[1:])
+    y = torch.cat(outs)
+    y = F.layer_norm(y, (D,), sd["merger.ln_q.weight"], sd["merger.ln_q.bias"], 1e-5).view(-1, D * merge * merge)
+    y = F.gelu(y @ sd["merger.mlp.0.weight"].T + sd["merger.mlp.0.bias"])
+    return y @ sd["merger.mlp.2.weight"].T + sd["merger.mlp.2.bias"]
+
+
+def test_llava_onevision1_5_rice_tower_and_decoder_wiring():
+    """``llavaonevision1_5``: the Rice tower equals a plain restatement (several frames, a video), and the whole
+    model's loss equals the hub Qwen3 decoder fed the same embeddings with plain 1-D positions."""
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+
+    from lmms_engine_b200.mapping_func import create_model_from_config
+
+    torch.manual_seed(0)
+    text = dict(vocab_size=300, hidden_size=48, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=256,
+                tie_word_embeddings=False)
+    vis = dict(depth=2, hidden_size=64, intermediate_size=128, num_heads=4, patch_size=4, spatial_merge_size=2,
+               text_hidden_size=48, hidden_act="gelu", layer_norm_eps=1e-5)
+    model = create_model_from_config("llavaonevision1_5", dict(model_type="llavaonevision1_5", text_config=text,
+                                                               vision_config=vis, image_token_id=290, video_token_id=291)).eval()
+    assert type(model.visual).__name__ == "RiceVisionTower"
+    with torch.no_grad():
+        for p in model.visual.parameters():
+            p.normal_(0, 0.1)
+    grid = torch.tensor([[1, 4, 6], [2, 2, 4]])
+    patches = torch.randn(24 + 16, 3 * 4 * 4)
+    sd = {k: v.detach().float() for k, v in model.visual.state_dict().items()}
+    with torch.no_grad():
+        feats = model.visual(patches, grid)
+    want = _rice_reference(sd, patches, grid.tolist(), heads=4, merge=2)
+    assert feats.shape == (10, 48)
+    assert (feats - want).abs().max() < 2e-5
+    # gradients reach the class token and its learned rotary angle
+    model.visual(patches, grid).square().sum().backward()
+    assert model.visual.class_pos_emb.grad.abs().sum() > 0 and model.visual.class_embedding.grad.abs().sum() > 0
+
+    hf = Qwen3ForCausalLM(Qwen3Config(**text, attn_implementation="eager")).eval().float()
+    hub = {"model.language_model." + k[len("model."):] if k.startswith("model.") else k: v for k, v in hf.state_dict().items()}
+    hub.update({"model.visual." + k: v for k, v in model.visual.state_dict().items()})
+    missing, unexpected = model.load_state_dict(model.convert_hf_state_dict(hub), strict=False)
+    assert not missing and not unexpected, (missing[:4], unexpected[:4])
+    ids = torch.randint(0, 280, (1, 40))
+    ids[0, 3:9], ids[0, 20:24] = 290, 291
+    with torch.no_grad():
+        emb = hf.model.embed_tokens(ids).clone()
+        emb[0, 3:9], emb[0, 20:24] = feats[:6], feats[6:]
+        ref = hf(inputs_embeds=emb, labels=ids).loss
+        got = model(input_ids=ids, attention_mask=torch.ones_like(ids), labels=ids, pixel_values=patches[:24],
+                    image_grid_thw=grid[:1], pixel_values_videos=patches[24:], video_grid_thw=grid[1:])["loss"]
+    assert abs(float(ref) - float(got)) < 2e-5, (float(ref), float(got))
