@@ -151,3 +151,35 @@ class Bagel(DecoderLM):
             kl = ((kl_mean - ref_mean) ** 2).mean(dim=tuple(range(1, kl_mean.dim())), keepdim=True) / (2 * sd ** 2)
             loss = loss + beta * kl.mean()
         return loss
+
+
+def apply_nsa_to_bagel(model: "Bagel", block_size: int = 64, compress_type: str = "weightedpool", kernel_size: int = 32,
+                       kernel_stride: int = 16, topk: int = 16, init_blocks: int = 1, local_blocks: int = 2,
+                       window_size: int = 512, **_):
+    """Turn every attention layer of a built model into native sparse attention: adds the gate projection
+    (three gates per query head), the pooling parameters of the key and value compression and the
+    intra-window position term, and records the settings on the config (reference:
+    src/lmms_engine/models/bagel/monkey_patch.py:160-253)."""
+    from ..ops import nsa as nsa_ops
+
+    params = nsa_ops.NSAParams(block_size, compress_type, kernel_size, kernel_stride, topk, init_blocks, local_blocks, window_size)
+    cfg = model.config
+    for layer in model.model.layers:
+        attn = layer.self_attn
+        ref = attn.q_proj.weight
+        attn.g_proj = nn.Linear(cfg.hidden_size, attn.n_q * 3, bias=False).to(device=ref.device, dtype=ref.dtype)
+        for name in ("compress_key", "compress_value"):
+            w = nsa_ops.compress_weight(compress_type, attn.n_kv, attn.head_dim, kernel_size)
+            if w is None:
+                setattr(attn, name, None)
+            else:
+                attn.register_parameter(name, nn.Parameter(w.to(device=ref.device, dtype=ref.dtype)))
+        attn.register_parameter("intra_block_pe", nn.Parameter(torch.zeros(attn.n_kv, kernel_size, attn.head_dim, device=ref.device, dtype=ref.dtype)))
+        attn.nsa = params
+    cfg.extra["nsa_config"] = {k: getattr(params, k) for k in params.__dataclass_fields__}
+    return model
+
+
+from .monkey_patch import MONKEY_PATCHER  # noqa: E402
+
+MONKEY_PATCHER.register("bagel", "nsa")(apply_nsa_to_bagel)

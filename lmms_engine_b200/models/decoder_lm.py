@@ -170,12 +170,25 @@ class Attention(nn.Module):
         if ctx.sp_size > 1 and fc_sp is None:
             # Ulysses: trade the sequence split for a head split around attention
             q, k, v = sp.seq_to_head_qkv(q, k, v, ctx.sp_group)
+        k_plain = k
         q = rope_ops.rope_apply(q, ctx.cos, ctx.sin)
         k = rope_ops.rope_apply(k, ctx.cos, ctx.sin)
-        o = attn_ops.varlen_attn(
-            q, k, v, ctx.cu_seqlens, ctx.cu_seqlens, ctx.max_seqlen, ctx.max_seqlen, causal=ctx.causal,
-            softmax_scale=1.0 / math.sqrt(D), window_size=self.window,
-        )
+        if getattr(self, "nsa", None) is not None:
+            # native sparse attention (added to a built model by the "nsa" patch of the bagel family)
+            assert ctx.sp_size == 1 and ctx.tp_size == 1, "native sparse attention runs without sequence / tensor parallelism"
+            from ..ops import nsa as nsa_ops
+
+            k_cmp, counts = nsa_ops.compress(k_plain, self.compress_key, ctx.cu_seqlens, self.nsa.kernel_size,
+                                             self.nsa.kernel_stride, self.intra_block_pe, self.nsa.compress_type)
+            v_cmp, _ = nsa_ops.compress(v, self.compress_value, ctx.cu_seqlens, self.nsa.kernel_size,
+                                        self.nsa.kernel_stride, None, self.nsa.compress_type)
+            gates = torch.sigmoid(gemm_ops.linear(x, _w(self.g_proj.weight), None)).view(x.shape[0], self.n_q, 3)
+            o = nsa_ops.nsa_attention(q, k, v, k_cmp, v_cmp, counts, gates, ctx.cu_seqlens, self.nsa, 1.0 / math.sqrt(D))
+        else:
+            o = attn_ops.varlen_attn(
+                q, k, v, ctx.cu_seqlens, ctx.cu_seqlens, ctx.max_seqlen, ctx.max_seqlen, causal=ctx.causal,
+                softmax_scale=1.0 / math.sqrt(D), window_size=self.window,
+            )
         if fc_sp is not None:
             return fused_ops.ulysses_out(o, _w(self.o_proj.weight), fc_sp, self.n_q, D, self.layer_idx)
         if ctx.sp_size > 1:

@@ -8,9 +8,11 @@ Gated delta rule per head (state ``S [d_k, d_v]``, decay ``exp(g_t) <= 1``, writ
     S_t = exp(g_t) S_{t-1} + beta_t k_t (v_t - (exp(g_t) S_{t-1})^T k_t)^T,    o_t = S_t^T q_t / sqrt(d_k)
 
 It is evaluated chunk-wise (64 tokens): inside a chunk through the inverse of a unit lower-triangular matrix,
-between chunks through the carried state.  Packed documents are processed one by one, so neither the short causal
-convolution nor the state ever crosses a document boundary.  The recurrence runs in fp32 PyTorch; projections,
-norms, the gated attention layers and the loss use the engine's kernels.  Full-attention heads wider than 128
+between chunks through the carried state.  All documents of a packed batch are padded to whole chunks and
+processed together (``ops/gdn.py``): the in-chunk algebra as batched fp32 ops, the chunk-to-chunk recurrence in one
+CUDA kernel per direction with the state reset at every document start, so neither the short causal convolution nor
+the state ever crosses a document boundary.  Projections, norms, the gated attention layers and the loss use the
+engine's kernels.  Full-attention heads wider than 128
 (the released models use 256) fall back to the reference attention path.
 """
 from __future__ import annotations
@@ -25,6 +27,7 @@ import torch.nn.functional as F
 
 from ..ops import attention as attn_ops
 from ..ops import gemm as gemm_ops
+from ..ops import gdn as gdn_ops
 from ..ops import norm as norm_ops
 from ..ops import rope as rope_ops
 from .decoder_lm import DecoderBackbone, DecoderConfig, DecoderLM, PackedContext, SwiGLUMLP, _w
@@ -159,20 +162,27 @@ class GatedDeltaNet(nn.Module):
         b, a = proj[:, c + self.value_dim:c + self.value_dim + self.hv], proj[:, c + self.value_dim + self.hv:c + self.value_dim + 2 * self.hv]
         beta = b.sigmoid()
         g = -self.A_log.float().exp() * F.softplus(a.float() + self.dt_bias)
-        bounds = ctx.cu_seqlens.tolist()
-        outs = []
-        for lo, hi in zip(bounds[:-1], bounds[1:]):
-            if hi <= lo:
-                continue
-            # causal depthwise convolution inside the document, then SiLU
-            seg = F.silu(self.conv1d(mixed[lo:hi].t()[None].to(self.conv1d.weight.dtype))[0, :, : hi - lo]).t()
-            q, k, v = torch.split(seg, [self.key_dim, self.key_dim, self.value_dim], -1)
-            q, k, v = q.reshape(-1, self.hk, self.dk), k.reshape(-1, self.hk, self.dk), v.reshape(-1, self.hv, self.dv)
-            if self.hv // self.hk > 1:
-                q, k = q.repeat_interleave(self.hv // self.hk, 1), k.repeat_interleave(self.hv // self.hk, 1)
-            outs.append(chunk_gated_delta_rule(q, k, v, g[lo:hi], beta[lo:hi]))
-        o = torch.cat(outs, 0) if outs else x.new_zeros((0, self.hv, self.dv))
-        if o.shape[0] < T:  # trailing padding tokens of a sequence-parallel split
+        plan = getattr(ctx, "gdn_plan", None)
+        if plan is None:
+            # one host read of the document boundaries per forward pass, shared by all layers
+            bounds = ctx.cu_seqlens.tolist()
+            lengths = [hi - lo for lo, hi in zip(bounds[:-1], bounds[1:]) if hi > lo]
+            pos = torch.cat([torch.arange(n) for n in lengths]) if lengths else torch.zeros(0, dtype=torch.long)
+            plan = (lengths, pos.to(x.device, non_blocking=True), gdn_ops.chunk_plan(lengths, x.device))
+            try:
+                ctx.gdn_plan = plan
+            except AttributeError:
+                pass
+        lengths, pos_in_doc, chunks = plan
+        live = int(pos_in_doc.numel())  # rows after it are the padding of a sequence-parallel split
+        # causal depthwise convolution inside every document, then SiLU
+        seg = gdn_ops.causal_conv_silu_packed(mixed[:live], self.conv1d.weight[:, 0], pos_in_doc)
+        q, k, v = torch.split(seg, [self.key_dim, self.key_dim, self.value_dim], -1)
+        q, k, v = q.reshape(-1, self.hk, self.dk), k.reshape(-1, self.hk, self.dk), v.reshape(-1, self.hv, self.dv)
+        if self.hv // self.hk > 1:
+            q, k = q.repeat_interleave(self.hv // self.hk, 1), k.repeat_interleave(self.hv // self.hk, 1)
+        o = gdn_ops.chunk_gated_delta_rule_packed(q, k, v, g[:live], beta[:live], lengths, chunks)
+        if o.shape[0] < T:
             o = torch.cat([o, o.new_zeros((T - o.shape[0], self.hv, self.dv))], 0)
         # RMSNorm over the head dim, gated by SiLU(z)
         o = norm_ops.rmsnorm(o.reshape(-1, self.dv).to(x.dtype), self.norm.weight, self.eps)

@@ -86,8 +86,21 @@ def test_llava_onevision_gpu():
                                           pixel_values=torch.randn(tiles, 3, 32, 32), image_sizes=torch.tensor([list(size)])))
 
 
-def test_qwen3_5_hybrid_gpu():
-    cfg = dict(TEXT, num_hidden_layers=4, head_dim=64, linear_conv_kernel_dim=4, linear_key_head_dim=32, linear_value_head_dim=32,
-               linear_num_key_heads=2, linear_num_value_heads=4, partial_rotary_factor=0.25)
+@pytest.mark.parametrize("linear_dim", [32, 128])  # 128: the state recurrence runs in its CUDA kernels
+def test_qwen3_5_hybrid_gpu(linear_dim):
+    cfg = dict(TEXT, num_hidden_layers=4, head_dim=64, linear_conv_kernel_dim=4, linear_key_head_dim=linear_dim,
+               linear_value_head_dim=linear_dim, linear_num_key_heads=2, linear_num_value_heads=4, partial_rotary_factor=0.25)
     ids = torch.randint(0, 250, (200,))
     _compare("qwen3_5_text", cfg, dict(input_ids=ids, labels=ids, cu_seqlens=torch.tensor([0, 70, 200], dtype=torch.int32)))
+
+
+def test_llava_onevision1_5_gpu():
+    cfg = dict(model_type="llavaonevision1_5", text_config=dict(TEXT, rms_norm_eps=1e-6),
+               vision_config=dict(depth=2, hidden_size=128, intermediate_size=256, num_heads=4, patch_size=8, text_hidden_size=128),
+               image_token_id=250, video_token_id=251)
+    ids = torch.randint(0, 240, (1, 64))
+    ids[0, 4:10], ids[0, 30:34] = 250, 251
+    grid_i, grid_v = torch.tensor([[1, 4, 6]]), torch.tensor([[2, 2, 4]])
+    _compare("llavaonevision1_5", cfg, dict(input_ids=ids, attention_mask=torch.ones_like(ids), labels=ids,
+                                            pixel_values=torch.randn(24, 3 * 8 * 8), image_grid_thw=grid_i,
+                                            pixel_values_videos=torch.randn(16, 3 * 8 * 8), video_grid_thw=grid_v))

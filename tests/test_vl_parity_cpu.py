@@ -581,3 +581,38 @@ def test_llava_onevision1_5_rice_tower_and_decoder_wiring():
         got = model(input_ids=ids, attention_mask=torch.ones_like(ids), labels=ids, pixel_values=patches[:24],
                     image_grid_thw=grid[:1], pixel_values_videos=patches[24:], video_grid_thw=grid[1:])["loss"]
     assert abs(float(ref) - float(got)) < 2e-5, (float(ref), float(got))
+
+
+def test_packed_gated_delta_rule_equals_per_document_rule_and_convolution():
+    """All documents at once (padded to whole chunks, state reset per document) == one document at a time;
+    the packed causal convolution == ``conv1d`` per document; gradients agree as well."""
+    from lmms_engine_b200.models.qwen3_5 import chunk_gated_delta_rule
+    from lmms_engine_b200.ops import gdn
+
+    torch.manual_seed(0)
+    lengths = [70, 5, 64, 130]
+    T, H, dk, dv = sum(lengths), 3, 16, 8
+    q, k, v = (torch.randn(T, H, d, requires_grad=True) for d in (dk, dk, dv))
+    g = (-torch.rand(T, H)).requires_grad_()
+    beta = torch.rand(T, H).requires_grad_()
+    got = gdn.chunk_gated_delta_rule_packed(q, k, v, g, beta, lengths)
+    want, at = [], 0
+    for L in lengths:
+        want.append(chunk_gated_delta_rule(q[at:at + L], k[at:at + L], v[at:at + L], g[at:at + L], beta[at:at + L]))
+        at += L
+    want = torch.cat(want)
+    assert (got - want).abs().max() < 1e-5
+    probe = torch.randn_like(got)
+    ga = torch.autograd.grad((got * probe).sum(), (q, k, v, g, beta))
+    gb = torch.autograd.grad((want * probe).sum(), (q, k, v, g, beta))
+    for a, b in zip(ga, gb):
+        assert (a - b).abs().max() < 1e-4 * max(1.0, float(b.abs().max()))
+    x = torch.randn(T, 6)
+    conv = torch.nn.Conv1d(6, 6, 4, groups=6, padding=3, bias=False)
+    pos = torch.cat([torch.arange(L) for L in lengths])
+    out = gdn.causal_conv_silu_packed(x, conv.weight[:, 0], pos)
+    ref, at = [], 0
+    for L in lengths:
+        ref.append(F.silu(conv(x[at:at + L].t()[None])[0, :, :L]).t())
+        at += L
+    assert (out - torch.cat(ref)).abs().max() < 1e-6
