@@ -297,3 +297,46 @@ def test_ema_filter_compute_tracker_and_formatting(tmp_path, monkeypatch):
     hf = TrainUtilities.convert_open_to_hf([{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "a.png"}},
                                                                            {"type": "text", "text": "hi"}]}])
     assert hf[0]["content"][0] == {"type": "image", "image": "a.png"}
+
+
+def test_prepare_init_weight_composes_parts_and_grows_vocabulary(tmp_path):
+    """A decoder checkpoint + an audio-encoder checkpoint -> an ``aero`` checkpoint with three more tokens."""
+    import torch
+
+    from lmms_engine_b200.mapping_func import create_model_from_config, create_model_from_pretrained
+    from lmms_engine_b200.models import hf_io
+    from lmms_engine_b200.tools import create_hf_dataset, prepare_init_weight, split_jsonl
+
+    torch.manual_seed(0)
+    text = dict(vocab_size=125, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, tie_word_embeddings=False)
+    audio = dict(d_model=32, encoder_layers=2, encoder_attention_heads=4, encoder_ffn_dim=64, num_mel_bins=16, max_source_positions=50)
+    lm = create_model_from_config("qwen2", dict(text, model_type="qwen2"))
+    hf_io.save_pretrained(lm, str(tmp_path / "lm"))
+    donor = create_model_from_config("qwen2_audio", dict(model_type="qwen2_audio", text_config=text, audio_config=audio))
+    hf_io.save_pretrained({"audio_tower." + k: v for k, v in donor.audio_tower.state_dict().items()}, str(tmp_path / "enc"), config={})
+    cfg_path = tmp_path / "aero.json"
+    cfg_path.write_text(json.dumps(dict(model_type="aero", text_config=text, audio_config=audio, audio_token_index=126)))
+    report = prepare_init_weight.main(["--model-type", "aero", "--config", str(cfg_path), "--part", f"language_model={tmp_path / 'lm'}",
+                                       "--part", f"audio_tower={tmp_path / 'enc'}", "--add-tokens", "3", "--pad-vocab-to", "64",
+                                       "--dtype", "float32", "--output", str(tmp_path / "out")])
+    assert report["language_model"]["placed"] == len(lm.state_dict()) and report["audio_tower"]["unused"] == 0
+    assert report["fresh"] >= 1  # the projector
+    model = create_model_from_pretrained(str(tmp_path / "out"))
+    emb = model.language_model.model.embed_tokens.weight
+    assert emb.shape[0] == 128
+    assert torch.equal(emb[:125], lm.model.embed_tokens.weight)
+    # new rows sit near the mean embedding
+    mu = lm.model.embed_tokens.weight.mean(0)
+    assert (emb[125:] - mu).abs().max() < 0.05
+    assert torch.equal(model.audio_tower.state_dict()["layers.0.self_attn.q_proj.weight"],
+                       donor.audio_tower.state_dict()["layers.0.self_attn.q_proj.weight"])
+    # conversation conversion and splitting
+    src = tmp_path / "llava.json"
+    src.write_text(json.dumps([{"id": "a", "image": "x.png", "conversations": [
+        {"from": "human", "value": "<image>\nwhat is it"}, {"from": "gpt", "value": "a cat"}]}] * 5))
+    assert create_hf_dataset.main(["--input", str(src), "--output", str(tmp_path / "ds")]) == 5
+    rows = [json.loads(l) for l in open(tmp_path / "ds" / "train.jsonl")]
+    assert rows[0]["messages"][0]["content"][0]["type"] == "image_url" and rows[0]["messages"][1]["role"] == "assistant"
+    parts = split_jsonl.main(["-i", str(tmp_path / "ds" / "train.jsonl"), "-s", "2"])
+    assert [sum(1 for _ in open(p)) for p in parts] == [3, 2]
