@@ -6,6 +6,11 @@
   (reference: src/lmms_engine/datasets/naive/sit_dataset.py).
 * ``rae`` (map-style): images resized to a fixed square for the autoencoder / discriminator trainer
   (reference: src/lmms_engine/datasets/naive/rae_dataset.py).
+* ``bagel_iterable`` + processor ``bagel``: interleaved text / image conversations for the unified
+  understanding + generation model: every text span is ``<|im_start|> ids <|im_end|>`` (assistant spans
+  supervised), every image is ``<|vision_start|> latent tokens <|vision_end|>`` sharing one rotary position;
+  assistant images are generation targets (random noise level), user images are clean conditions
+  (reference: src/lmms_engine/datasets/processor/bagel_processor.py:91-365, collator/bagel_collator.py:11-80).
 * processors ``sit``, ``rae_siglip``, ``wanvideo`` (tensor normalisation only) and ``nanovlm`` (ChatML text
   plus NaFlex patches: an image is resized so that it has at most ``max_num_patches`` patches of
   ``patch_size`` pixels and is flattened to ``[rows*cols, C*p*p]`` with its ``spatial_shapes`` row).
@@ -330,3 +335,137 @@ class RaeDataset(_RecordDataset):
         rec, folder = self.data_list[i], self.data_folder[i]
         img = self.load_image(os.path.join(folder or "", rec["image"]))
         return {"pixel_values": self.processor.image_to_tensor(img)}
+
+
+# ------------------------------------------------------------------------------- unified understanding + generation
+@register_processor("bagel")
+class BagelProcessor(ChatProcessor):
+    """Builds the packed stream of ``models/bagel.py`` from one conversation.
+
+    Images arrive as latents ``[C, h, w]`` (precomputed with the VAE: ``.pt`` / ``.npy`` files, the way the video
+    pipeline stores its latents) or, with ``latent_from_pixels: true``, as PIL images that are average-pooled by
+    ``vae_downsample`` into 3-channel pseudo-latents.  ``latent_patch_size`` x ``latent_patch_size`` latent cells form
+    one token.  Dropout of text / image conditions for classifier-free guidance follows the reference's
+    probabilities (``text_cond_dropout_prob``, ``vae_cond_dropout_prob``)."""
+
+    def build(self):
+        super().build()
+        kw = self.kwargs
+        self.p = int(kw.get("latent_patch_size", 2))
+        self.down = int(kw.get("vae_downsample", 8))
+        self.max_latent = int(kw.get("max_latent_size", 64))
+        self.from_pixels = bool(kw.get("latent_from_pixels", False))
+        self.text_drop = float(kw.get("text_cond_dropout_prob", 0.0))
+        self.vae_drop = float(kw.get("vae_cond_dropout_prob", 0.0))
+        self.rng = np.random.default_rng(int(kw.get("seed", 0)))
+        return self
+
+    def to_latent(self, img) -> torch.Tensor:
+        if torch.is_tensor(img):
+            return img.float()
+        if isinstance(img, np.ndarray) and img.ndim == 3 and img.dtype != np.uint8:
+            return torch.from_numpy(img).float()
+        if not self.from_pixels:
+            raise ValueError("bagel processor: image is not a latent tensor; precompute latents or set latent_from_pixels")
+        from PIL import Image
+
+        img = img.convert("RGB") if isinstance(img, Image.Image) else Image.fromarray(np.asarray(img).astype(np.uint8)).convert("RGB")
+        cell = self.down * self.p
+        w, h = img.size
+        side = self.max_latent * self.down
+        scale = min(1.0, side / max(w, h))
+        w, h = max(cell, int(w * scale) // cell * cell), max(cell, int(h * scale) // cell * cell)
+        x = torch.from_numpy(np.asarray(img.resize((w, h), Image.BICUBIC)).copy()).float().permute(2, 0, 1) / 127.5 - 1.0
+        return torch.nn.functional.avg_pool2d(x[None], self.down)[0]
+
+    def latent_tokens(self, lat: torch.Tensor):
+        """``[C, h, w]`` -> ``[h/p * w/p, C*p*p]`` tokens and their position ids on the ``max_latent`` grid."""
+        C, h, w = lat.shape
+        p = self.p
+        rows, cols = h // p, w // p
+        tok = lat[:, : rows * p, : cols * p].reshape(C, rows, p, cols, p).permute(1, 3, 0, 2, 4).reshape(rows * cols, C * p * p)
+        pos = (torch.arange(rows)[:, None] * self.max_latent + torch.arange(cols)[None, :]).flatten()
+        return tok, pos
+
+    def process(self, hf_messages=None, images=None, videos=None, audios=None, add_system_prompt: bool = True, **kw):
+        ids: List[int] = []
+        labels: List[int] = []
+        pos: List[int] = []
+        lat_tok, lat_pos, lat_idx, lat_t, lat_loss = [], [], [], [], []
+        rope, image_at = 0, 0
+        for msg in hf_messages:
+            role = msg["role"]
+            content = msg["content"] if isinstance(msg["content"], list) else [{"type": "text", "text": msg["content"]}]
+            for c in content:
+                kind = c.get("type")
+                if kind == "text":
+                    if role != "assistant" and self.text_drop > 0 and self.rng.random() < self.text_drop:
+                        continue
+                    body = self._enc(c["text"])
+                    span = [self.im_start] + body + [self.im_end]
+                    # the model shifts labels itself: a supervised position holds its own token
+                    labels += ([-100] + body + [self.im_end]) if role == "assistant" else [-100] * len(span)
+                    ids += span
+                    pos += list(range(rope, rope + len(span)))
+                    rope += len(span)
+                elif kind in ("image", "image_url"):
+                    img = images[image_at]
+                    image_at += 1
+                    target = role == "assistant"
+                    if not target and self.vae_drop > 0 and self.rng.random() < self.vae_drop:
+                        rope += 1  # a dropped condition image still advances the position
+                        continue
+                    tok, tpos = self.latent_tokens(self.to_latent(img))
+                    n = tok.shape[0]
+                    start = len(ids) + 1
+                    ids += [self.vision_start] + [self.image_token_id] * n + [self.vision_end]
+                    labels += [-100] * (n + 2)
+                    pos += [rope] * (n + 2)
+                    rope += 1
+                    lat_tok.append(tok)
+                    lat_pos.append(tpos)
+                    lat_idx.append(torch.arange(start, start + n))
+                    # generation targets get a logit-normal noise level, condition images stay clean
+                    t = float(1.0 / (1.0 + math.exp(-self.rng.standard_normal()))) if target else 0.0
+                    lat_t.append(torch.full((n,), t))
+                    lat_loss.append(torch.full((n,), target, dtype=torch.bool))
+        out = {"input_ids": torch.tensor(ids, dtype=torch.long), "labels": torch.tensor(labels, dtype=torch.long),
+               "position_ids": torch.tensor(pos, dtype=torch.long)}
+        if lat_tok:
+            out.update(latent_tokens=torch.cat(lat_tok), latent_pos=torch.cat(lat_pos), latent_index=torch.cat(lat_idx),
+                       timesteps=torch.cat(lat_t), latent_loss_mask=torch.cat(lat_loss))
+        return out
+
+
+class BagelCollator:
+    """Packed stream over several conversations: like the packed collator, with every ``*_index`` tensor moved by
+    the start of its conversation."""
+
+    def __call__(self, batch):
+        from .collator.packed_collator import PackedCollator, _flatten
+
+        samples, at, moved = _flatten(batch), 0, []
+        for s in samples:
+            s = dict(s)
+            for k in list(s):
+                if k.endswith("_index") and torch.is_tensor(s[k]):
+                    s[k] = s[k] + at
+            at += int(s["input_ids"].numel())
+            moved.append(s)
+        return PackedCollator()(moved)
+
+
+@register_dataset("bagel_iterable")
+class BagelIterableDataset(MultiModalIterableDataset):
+    """``dataset_type: bagel_iterable``: the vision iterable dataset whose images may be stored latents."""
+
+    def load_image(self, url, data_folder=None):
+        path = os.path.join(data_folder, url) if data_folder and not os.path.isabs(str(url)) else url
+        if str(path).endswith(".pt"):
+            return torch.load(path, map_location="cpu", weights_only=True)
+        if str(path).endswith(".npy"):
+            return torch.from_numpy(np.load(path))
+        return super().load_image(url, data_folder)
+
+    def get_collator(self):
+        return BagelCollator()

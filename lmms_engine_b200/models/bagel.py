@@ -83,7 +83,7 @@ class Bagel(DecoderLM):
         self.latent_pos_embed = nn.Embedding(cfg.max_latent_size ** 2, cfg.hidden_size)
 
     def forward(self, input_ids=None, labels=None, cu_seqlens=None, position_ids=None, latent_tokens=None,
-                latent_index=None, latent_pos=None, timesteps=None, **kw) -> Dict[str, Any]:
+                latent_index=None, latent_pos=None, timesteps=None, latent_loss_mask=None, **kw) -> Dict[str, Any]:
         """Packed stream of length T.  ``latent_tokens [G, C*p*p]`` are clean VAE patches that sit at
         stream positions ``latent_index [G]`` (their ``input_ids`` entries are ignored);
         ``timesteps [G]`` in (0,1) give each patch's noise level (same value within an image)."""
@@ -116,7 +116,12 @@ class Bagel(DecoderLM):
             ce = ce_ops.fused_linear_cross_entropy(hidden, _w(self.lm_head.weight), shifted, "mean")
         if G:
             pred = self.llm2vae(hidden.index_select(0, latent_index)).float()
-            mse = ((pred - target) ** 2).mean()
+            err = ((pred - target) ** 2).mean(-1)
+            if latent_loss_mask is not None:  # clean condition images carry no loss
+                keep = latent_loss_mask.to(err.dtype)
+                mse = (err * keep).sum() / keep.sum().clamp(min=1.0)
+            else:
+                mse = err.mean()
             out["velocity"] = pred
         loss = 0.0
         if ce is not None:

@@ -232,3 +232,62 @@ def test_log_mel_matches_whisper_extractor_and_audio_processor_counts():
     assert out["audio_values"].shape == (1, 128, 3000)
     assert int((out["input_ids"] == proc.audio_token_id).sum()) == 50  # 200 mel frames -> 100 -> 50 pooled rows
     assert (out["labels"][out["input_ids"] == proc.audio_token_id] == -100).all()
+
+
+def test_bagel_dataset_processor_collator_feed_the_model(tmp_path):
+    """Interleaved text / image conversations -> packed stream with latent tokens -> one training step of the model."""
+    import numpy as np
+    from PIL import Image
+
+    from lmms_engine_b200.datasets import registry  # noqa: F401
+    from lmms_engine_b200.datasets.config import DatasetConfig
+    from lmms_engine_b200.mapping_func import DATASET_MAPPING, create_model_from_config
+
+    torch.manual_seed(0)
+    torch.save(torch.randn(3, 8, 12), tmp_path / "gen.pt")
+    np.save(tmp_path / "cond.npy", np.random.randn(3, 4, 4).astype(np.float32))
+    Image.fromarray((np.random.rand(40, 64, 3) * 255).astype(np.uint8)).save(tmp_path / "photo.png")
+    records = [
+        {"messages": [{"role": "user", "content": [{"type": "text", "text": "draw a cat"}]},
+                      {"role": "assistant", "content": [{"type": "image_url", "image_url": {"url": "gen.pt"}}]}]},
+        {"messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "cond.npy"}},
+                                                   {"type": "text", "text": "what is it"}]},
+                      {"role": "assistant", "content": [{"type": "text", "text": "a dog"}]}]},
+        {"messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "photo.png"}},
+                                                   {"type": "text", "text": "same, at night"}]},
+                      {"role": "assistant", "content": [{"type": "image_url", "image_url": {"url": "gen.pt"}}]}]},
+    ]
+    path = tmp_path / "d.jsonl"
+    path.write_text("".join(json.dumps(r) + "\n" for r in records))
+    cfg = DatasetConfig(dataset_type="bagel_iterable", dataset_format="jsonl", dataset_path=str(path), shuffle=False, packing=False,
+                        processor_config={"processor_name": "byte", "processor_type": "bagel",
+                                          "extra_kwargs": {"latent_patch_size": 2, "vae_downsample": 8, "max_latent_size": 8,
+                                                           "latent_from_pixels": True}},
+                        extra_kwargs={"data_folder": str(tmp_path)})
+    ds = DATASET_MAPPING["bagel_iterable"](cfg).build()
+    ds.data_folder = [str(tmp_path)] * len(ds.data_list)
+    samples = [s for pack in ds for s in pack]
+    assert len(samples) == 3
+    a, b, c = samples
+    p = ds.processor
+    # generation target: 4 x 6 tokens of 3*2*2 values between the vision markers, one rotary position, noise level in (0, 1)
+    assert a["latent_tokens"].shape == (24, 12) and a["latent_loss_mask"].all() and 0 < float(a["timesteps"][0]) < 1
+    start = int(a["latent_index"][0])
+    assert a["input_ids"][start - 1] == p.vision_start and a["input_ids"][start + 24] == p.vision_end
+    assert a["position_ids"][start - 1] == a["position_ids"][start + 24] and (a["labels"] == -100).all()
+    assert a["latent_pos"][:7].tolist() == [0, 1, 2, 3, 4, 5, 8]
+    # understanding: clean condition image, assistant text supervised (own tokens, the model shifts)
+    assert not b["latent_loss_mask"].any() and float(b["timesteps"].max()) == 0.0
+    sup = b["labels"] != -100
+    assert p.tokenizer.decode(b["input_ids"][sup].tolist()) == "a dog<|im_end|>"
+    assert c["latent_tokens"].shape[0] == (40 // 16) * (64 // 16) + 24  # pooled photo + target
+    batch = ds.get_collator()([samples])
+    assert batch["cu_seqlens"].tolist() == [0, a["input_ids"].numel(), a["input_ids"].numel() + b["input_ids"].numel(),
+                                            sum(s["input_ids"].numel() for s in samples)]
+    assert int(batch["latent_index"][24]) == a["input_ids"].numel() + int(b["latent_index"][0])
+    model = create_model_from_config("bagel", dict(model_type="bagel", vocab_size=p.tokenizer.vocab_size + 64, hidden_size=32,
+                                                   intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                                                   num_key_value_heads=2, latent_channels=3, latent_patch_size=2, max_latent_size=8))
+    out = model(**batch)
+    out["loss"].backward()
+    assert torch.isfinite(out["loss"]) and out["ce"] is not None and out["mse"] is not None
