@@ -31,11 +31,19 @@ constexpr int THREADS = 256;
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
 
-// stage a [C, DK] fp32 block (contiguous in global memory) into padded shared memory
+__device__ __forceinline__ void cp_async16(float* dst_smem, const float* src) {
+  const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(dst_smem));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// stage a [C, DK] fp32 block (contiguous in global memory) into padded shared memory with asynchronous 16-byte
+// copies: the caller commits the group and waits for it before the block is read
 __device__ __forceinline__ void stage_ck(float* dst, const float* __restrict__ src) {
   for (int idx = threadIdx.x; idx < C * DK / 4; idx += THREADS) {
     const int r = idx / (DK / 4), c4 = idx - r * (DK / 4);
-    st4(dst + r * LDK + c4 * 4, ld4(src + r * DK + c4 * 4));
+    cp_async16(dst + r * LDK + c4 * 4, src + r * DK + c4 * 4);
   }
 }
 
@@ -55,6 +63,21 @@ __device__ __forceinline__ void rows_times_state(const float* A, const float* B,
     const float a0 = A[r0 * LDK + kk], a1 = A[(r0 + 1) * LDK + kk];
     acc[0][0] += a0 * b.x; acc[0][1] += a0 * b.y; acc[0][2] += a0 * b.z; acc[0][3] += a0 * b.w;
     acc[1][0] += a1 * b.x; acc[1][1] += a1 * b.y; acc[1][2] += a1 * b.z; acc[1][3] += a1 * b.w;
+  }
+}
+
+// the same for two left operands that share B (one pass over the state)
+__device__ __forceinline__ void rows_times_state2(const float* A1, const float* A2, const float* B, int r0, int c0,
+                                                  float acc1[2][4], float acc2[2][4]) {
+#pragma unroll 8
+  for (int kk = 0; kk < DK; ++kk) {
+    const float4 b = ld4(B + kk * LDV + c0);
+    const float a0 = A1[r0 * LDK + kk], a1 = A1[(r0 + 1) * LDK + kk];
+    const float q0 = A2[r0 * LDK + kk], q1 = A2[(r0 + 1) * LDK + kk];
+    acc1[0][0] += a0 * b.x; acc1[0][1] += a0 * b.y; acc1[0][2] += a0 * b.z; acc1[0][3] += a0 * b.w;
+    acc1[1][0] += a1 * b.x; acc1[1][1] += a1 * b.y; acc1[1][2] += a1 * b.z; acc1[1][3] += a1 * b.w;
+    acc2[0][0] += q0 * b.x; acc2[0][1] += q0 * b.y; acc2[0][2] += q0 * b.z; acc2[0][3] += q0 * b.w;
+    acc2[1][0] += q1 * b.x; acc2[1][1] += q1 * b.y; acc2[1][2] += q1 * b.z; acc2[1][3] += q1 * b.w;
   }
 }
 
@@ -87,28 +110,27 @@ gdn_scan_fwd_kernel(const float* __restrict__ w, const float* __restrict__ u, co
   const int ty = tid >> 3, tx = tid & 7;
   const int r0 = 2 * ty, k0 = 4 * ty, c0 = 4 * tx;
   for (int idx = tid; idx < DK * LDV; idx += THREADS) sS[idx] = 0.f;
+  // operands of chunk 0; inside the loop the next chunk's w / q~ load while the state update runs, and the
+  // chunk's k~ loads while the two products with the state run
+  stage_ck(sW, w + static_cast<long>(h) * n * C * DK);
+  stage_ck(sQ, qt + static_cast<long>(h) * n * C * DK);
+  cp_async_commit();
   for (int i = 0; i < n; ++i) {
     const long chunk = static_cast<long>(h) * n + i;
-    stage_ck(sW, w + chunk * C * DK);
-    stage_ck(sQ, qt + chunk * C * DK);
-    stage_ck(sK, kt + chunk * C * DK);
     if (reset[i]) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) st4(sS + (k0 + j) * LDV + c0, make_float4(0.f, 0.f, 0.f, 0.f));
     }
+    cp_async_wait_all();
     __syncthreads();
+    stage_ck(sK, kt + chunk * C * DK);
+    cp_async_commit();
     // state before this chunk, for the backward pass
     float* hrow = hist + chunk * DK * dv + static_cast<long>(slice) * DVT;
-    float s_old[4][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float4 s = ld4(sS + (k0 + j) * LDV + c0);
-      s_old[j][0] = s.x; s_old[j][1] = s.y; s_old[j][2] = s.z; s_old[j][3] = s.w;
-      st4(hrow + static_cast<long>(k0 + j) * dv + c0, s);
-    }
+    for (int j = 0; j < 4; ++j) st4(hrow + static_cast<long>(k0 + j) * dv + c0, ld4(sS + (k0 + j) * LDV + c0));
     float p[2][4] = {}, oo[2][4] = {};
-    rows_times_state(sW, sS, r0, c0, p);
-    rows_times_state(sQ, sS, r0, c0, oo);
+    rows_times_state2(sW, sQ, sS, r0, c0, p, oo);
     const long tok = chunk * C;
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
@@ -119,18 +141,26 @@ gdn_scan_fwd_kernel(const float* __restrict__ w, const float* __restrict__ u, co
       st4(o + off, make_float4(oo[j][0], oo[j][1], oo[j][2], oo[j][3]));
       st4(sV + (r0 + j) * LDV + c0, vn);
     }
-    __syncthreads();
+    cp_async_wait_all();
+    __syncthreads();   // k~ and v_new are in shared memory; nobody reads w / q~ of this chunk any more
+    if (i + 1 < n) {
+      stage_ck(sW, w + (chunk + 1) * C * DK);
+      stage_ck(sQ, qt + (chunk + 1) * C * DK);
+    }
+    cp_async_commit();
     const float g = gamma[chunk];
     float acc[4][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-#pragma unroll
-      for (int c = 0; c < 4; ++c) acc[j][c] = g * s_old[j][c];
+    for (int j = 0; j < 4; ++j) {
+      const float4 sv = ld4(sS + (k0 + j) * LDV + c0);   // own tile: only this thread rewrites it
+      acc[j][0] = g * sv.x; acc[j][1] = g * sv.y; acc[j][2] = g * sv.z; acc[j][3] = g * sv.w;
+    }
     transposed_times_rows(sK, sV, k0, c0, 1.f, acc);
 #pragma unroll
     for (int j = 0; j < 4; ++j) st4(sS + (k0 + j) * LDV + c0, make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]));
-    __syncthreads();
+    // the loop-top barrier orders these writes (and the reads of k~ / v_new) before the next chunk's use
   }
+  cp_async_wait_all();
 }
 
 // out[r][kk] = sign * sum_c A[r][c] * B[kk][c] for r in 4*ry..+3, kk = kx + 16 j (j < 8); A [C][LDV], B [DK][LDV]
@@ -180,12 +210,14 @@ gdn_scan_bwd_kernel(const float* __restrict__ w, const float* __restrict__ qt, c
     const long chunk = static_cast<long>(h) * n + i;
     const long tok = chunk * C;
     const long col = static_cast<long>(slice) * DVT;
-    stage_ck(sW, w + chunk * C * DK);
+    stage_ck(sW, w + chunk * C * DK);     // asynchronous copies, in flight while the slices below are loaded
     stage_ck(sQ, qt + chunk * C * DK);
     stage_ck(sK, kt + chunk * C * DK);
+    cp_async_commit();
     stage_slice(sS, hist + chunk * DK * dv + col, DK, dv);
     stage_slice(sV, vnew + tok * dv + col, C, dv);
     stage_slice(sO, d_o + tok * dv + col, C, dv);
+    cp_async_wait_all();
     __syncthreads();
     // total gradient of v_new: what the caller saw plus what the state update carried forward
     float t[2][4] = {};
