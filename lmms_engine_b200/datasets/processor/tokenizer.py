@@ -81,7 +81,12 @@ class ByteChatTokenizer:
             json.dump({"type": "byte_chat", "special_tokens": self.special}, f)
 
 
+REALTIME_TOKENS = ["<|audio_start|>", "<|audio_end|>", "<|audio_pad|>", "<|rt_start|>", "<|rt_pad|>", "<|rt_speak|>", "<|rt_end|>"]
+
+
 def load_tokenizer(name: Optional[str]):
+    if name == "byte_realtime":
+        return ByteChatTokenizer(REALTIME_TOKENS)
     if not name or name in ("byte", "none", "byte_chat"):
         return ByteChatTokenizer()
     marker = os.path.join(name, "byte_chat_tokenizer.json") if os.path.isdir(name) else None

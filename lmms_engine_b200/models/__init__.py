@@ -62,3 +62,7 @@ for _mt in ("qwen3_5_moe_text", "qwen3_5_moe"):
     register_model(_mt, Qwen35MoEConfig, Qwen35MoELM, "causal_lm")
 for _mt in ("qwen3_5", "qwen3_5_moe"):
     register_model(_mt, VLConfig, VLModel, "image_text_to_text")
+
+from .aero_realtime import AeroRealtimeConfig, AeroRealtimeModel  # noqa: E402
+
+register_model("aero_realtime", AeroRealtimeConfig, AeroRealtimeModel, "image_text_to_text")

@@ -474,7 +474,7 @@ class VoxtralRealtimeEncoder(nn.Module):
     """Streaming audio encoder (reference: src/lmms_engine/models/voxtral_realtime/voxtral_realtime_ops.py, a patch of the
     ``transformers`` class): causal convolutions, rotary causal attention inside a sliding window, RMSNorm, gated MLP.
     ``input_features [n, mel, T]`` with ``feature_attention_mask [n, T]`` (or full clips); every clip is one varlen
-    document of ``ceil(L / 2)`` frames.  Returns ``{"last_hidden_state": [sum(frames), hidden], "frame_lengths"}``."""
+    document of ``floor(L / 2)`` frames.  Returns ``{"last_hidden_state": [sum(frames), hidden], "frame_lengths"}``."""
 
     config_class = VoxtralRealtimeEncoderConfig
     _no_split_modules = ["VoxtralEncoderLayer"]
@@ -493,7 +493,7 @@ class VoxtralRealtimeEncoder(nn.Module):
         lens = feature_attention_mask.sum(-1).long() if feature_attention_mask is not None else torch.full((n,), T, device=input_features.device)
         x = F.gelu(self.embedder.conv1(input_features.to(self.embedder.conv1.weight.dtype)))
         x = F.gelu(self.embedder.conv2(x)).permute(0, 2, 1)  # causal: frame j covers mel frames <= 2j+1
-        frames = ((lens - 1) // 2 + 1).tolist()
+        frames = (lens // 2).clamp(min=1).tolist()  # the stride-2 causal convolution yields floor(L / 2) frames
         flat = torch.cat([x[i, :f] for i, f in enumerate(frames)], 0)
         cu = torch.cumsum(torch.tensor([0] + frames, device=x.device), 0).to(torch.int32)
         pos = torch.cat([torch.arange(f, device=x.device) for f in frames]).float()

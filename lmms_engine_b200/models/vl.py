@@ -169,10 +169,11 @@ class VLModel(nn.Module):
     def get_input_embeddings(self):
         return self.language_model.model.embed_tokens
 
-    def embed_multimodal(self, ids, pixel_values, image_grid_thw, pixel_values_videos, video_grid_thw):
-        """Token embeddings with image / video features written over their placeholders."""
+    def embed_multimodal(self, ids, pixel_values, image_grid_thw, pixel_values_videos, video_grid_thw, embed_ids=None):
+        """Token embeddings with image / video features written over their placeholders (``embed_ids``: a parallel
+        stream whose tokens are embedded instead, placeholders still found in ``ids``)."""
         cfg = self.config
-        emb = self.language_model.model.embed_tokens(ids)
+        emb = self.language_model.model.embed_tokens(ids if embed_ids is None else embed_ids)
         deep_all, index_all = None, None
         for pix, grid, tok in ((pixel_values, image_grid_thw, cfg.image_token_id),
                                (pixel_values_videos, video_grid_thw, cfg.video_token_id)):

@@ -291,3 +291,68 @@ def test_bagel_dataset_processor_collator_feed_the_model(tmp_path):
     out = model(**batch)
     out["loss"].backward()
     assert torch.isfinite(out["loss"]) and out["ce"] is not None and out["mse"] is not None
+
+
+def test_aero_realtime_processor_places_speech_on_the_audio_timeline(tmp_path):
+    """One slot per 80 ms; silence supervised as rt_pad, a speech segment written after its start time with an
+    unsupervised context slot; the collated batch drives the model."""
+    import numpy as np
+
+    from lmms_engine_b200.datasets import registry  # noqa: F401
+    from lmms_engine_b200.datasets.config import ProcessorConfig
+    from lmms_engine_b200.mapping_func import DATAPROCESSOR_MAPPING, DATASET_MAPPING, create_model_from_config
+
+    proc = DATAPROCESSOR_MAPPING["aero_realtime"](ProcessorConfig(processor_name="byte_realtime", processor_type="aero_realtime",
+                                                                   extra_kwargs={"num_mel_bins": 16, "downsample_factor": 4})).build()
+    wave = np.random.default_rng(0).standard_normal(16000 * 2).astype(np.float32)  # 2 s -> 200 mel frames -> 100 frames -> 25 slots
+    msgs = [{"role": "user", "content": [{"type": "audio", "audio": "clip"}]}]
+    segs = [{"role": "assistant", "time": 0.5, "text": "hi!"}, {"role": "user", "time": 0.1, "text": "ignored"}]
+    out = proc.process(msgs, audios=[wave], realtime_segments=segs)
+    ids, stream, labels = out["input_ids"], out["text_stream_ids"], out["labels"]
+    slots = torch.nonzero(ids == proc.audio_token_id).flatten()
+    assert slots.numel() == 25 and ids[slots[0] - 1] == proc.audio_start and ids[slots[-1] + 1] == proc.audio_end
+    assert out["input_features"].shape == (1, 16, 200) and int(out["feature_attention_mask"].sum()) == 200
+    first = 7  # 0.5 s / 0.08 s -> slot 7 (0.56 s) is the first at or after the start time
+    assert abs(proc.seconds_per_slot - 0.08) < 1e-9
+    assert stream[slots[first]] == proc.rt_pad and labels[slots[first]] == -100
+    said = stream[slots[first + 1:first + 4]].tolist()
+    assert bytes(said).decode() == "hi!" and labels[slots[first + 1:first + 4]].tolist() == said
+    others = [k for k in range(25) if not first <= k <= first + 3]
+    assert all(stream[slots[k]] == proc.rt_pad and labels[slots[k]] == proc.rt_pad for k in others)
+    assert torch.equal(stream[ids != proc.audio_token_id], ids[ids != proc.audio_token_id])
+    # dataset + collator + model
+    import wave as wavelib
+
+    from lmms_engine_b200.datasets.config import DatasetConfig
+
+    for name, seconds in (("a.wav", 1.0), ("b.wav", 0.5)):
+        with wavelib.open(str(tmp_path / name), "wb") as w:
+            w.setnchannels(1), w.setsampwidth(2), w.setframerate(16000)
+            w.writeframes((np.random.default_rng(1).standard_normal(int(16000 * seconds)) * 3000).astype(np.int16).tobytes())
+    records = [{"messages": [{"role": "user", "content": [{"type": "audio_url", "audio_url": {"url": "a.wav"}}]}],
+                "realtime_segments": [{"role": "assistant", "time": 0.2, "text": "ok"}]},
+               {"messages": [{"role": "user", "content": [{"type": "audio_url", "audio_url": {"url": "b.wav"}},
+                                                          {"type": "text", "text": "what was said"}]},
+                             {"role": "assistant", "content": [{"type": "text", "text": "nothing"}]}]}]
+    path = tmp_path / "rt.jsonl"
+    path.write_text("".join(json.dumps(r) + "\n" for r in records))
+    cfg = DatasetConfig(dataset_type="aero_realtime_iterable", dataset_format="jsonl", dataset_path=str(path), shuffle=False,
+                        packing=False, processor_config={"processor_name": "byte_realtime", "processor_type": "aero_realtime",
+                                                         "extra_kwargs": {"num_mel_bins": 16, "downsample_factor": 4}})
+    ds = DATASET_MAPPING["aero_realtime_iterable"](cfg).build()
+    ds.data_folder = [str(tmp_path)] * len(ds.data_list)
+    samples = [s for pack in ds for s in pack]
+    assert [int((s["input_ids"] == proc.audio_token_id).sum()) for s in samples] == [12, 6]
+    batch = ds.get_collator()([samples])
+    assert batch["input_features"].shape == (2, 16, 100) and batch["text_stream_ids"].shape == batch["input_ids"].shape
+    text = dict(vocab_size=len(proc.tokenizer) + 6, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, head_dim=8, rope_scaling={"mrope_section": [2, 1, 1], "mrope_interleaved": True})
+    vis = dict(depth=1, hidden_size=16, intermediate_size=32, num_heads=2, patch_size=4, out_hidden_size=32, num_position_embeddings=16,
+               deepstack_visual_indexes=[])
+    audio = dict(hidden_size=16, intermediate_size=32, num_hidden_layers=1, num_attention_heads=2, head_dim=8, num_mel_bins=16, sliding_window=8)
+    model = create_model_from_config("aero_realtime", dict(model_type="aero_realtime", backbone_family="qwen3_vl", text_config=text,
+                                                           vision_config=vis, audio_config=audio, downsample_factor=4,
+                                                           audio_token_index=proc.audio_token_id))
+    loss = model(**batch)["loss"]
+    loss.backward()
+    assert torch.isfinite(loss) and model.multi_modal_projector.linear_1.weight.grad.abs().sum() > 0

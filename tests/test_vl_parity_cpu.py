@@ -395,8 +395,8 @@ def test_voxtral_realtime_encoder_matches_upstream():
     mask[1, 41:] = 0
     with torch.no_grad():
         out = mine(x, mask)
-    assert out["frame_lengths"].tolist() == [30, 21]
-    assert torch.allclose(out["last_hidden_state"][30:], ref[1, :21], atol=1e-4)
+    assert out["frame_lengths"].tolist() == [30, 20]  # frame 20 would also cover mel frame 41, outside the clip
+    assert torch.allclose(out["last_hidden_state"][30:], ref[1, :20], atol=1e-4)
 
 
 def test_gated_delta_rule_chunked_equals_recurrent():
@@ -616,3 +616,73 @@ def test_packed_gated_delta_rule_equals_per_document_rule_and_convolution():
         ref.append(F.silu(conv(x[at:at + L].t()[None])[0, :, :L]).t())
         at += L
     assert (out - torch.cat(ref)).abs().max() < 1e-6
+
+
+@pytest.mark.parametrize("family", ["qwen3_vl", "qwen3_5"])
+def test_aero_realtime_adds_audio_rows_to_the_text_stream(family):
+    """Without audio and text stream the model IS its backbone; with them, the decoder sees the text-stream
+    embeddings plus the projected audio rows at the audio positions (checked against a hand-built embedding)."""
+    from lmms_engine_b200.mapping_func import create_model_from_config
+
+    torch.manual_seed(0)
+    text = dict(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=2 if family == "qwen3_vl" else 4,
+                num_attention_heads=4, num_key_value_heads=2, head_dim=16, tie_word_embeddings=False)
+    if family == "qwen3_5":
+        text.update(linear_conv_kernel_dim=4, linear_key_head_dim=16, linear_value_head_dim=16, linear_num_key_heads=2,
+                    linear_num_value_heads=4, rope_parameters={"rope_theta": 10000.0, "partial_rotary_factor": 0.5,
+                                                               "mrope_section": [2, 1, 1], "mrope_interleaved": True})
+    else:
+        text.update(rope_scaling={"mrope_section": [4, 2, 2], "mrope_interleaved": True})
+    vis = dict(depth=2, hidden_size=32, intermediate_size=64, num_heads=2, patch_size=4, temporal_patch_size=2, spatial_merge_size=2,
+               out_hidden_size=64, num_position_embeddings=16, in_channels=3, deepstack_visual_indexes=[0] if family == "qwen3_vl" else [])
+    audio = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2, head_dim=16, num_mel_bins=8,
+                 sliding_window=6)
+    cfg = dict(model_type="aero_realtime", backbone_family=family, text_config=text, vision_config=vis, audio_config=audio,
+               downsample_factor=2, image_token_index=290, video_token_index=291, audio_token_index=292,
+               vision_start_token_index=293)
+    model = create_model_from_config("aero_realtime", cfg).eval()
+    assert type(model).__name__ == "AeroRealtimeModel" and model.config.to_dict()["backbone_family"] == family
+    backbone = create_model_from_config(family, dict(model_type=family, text_config=text, vision_config=vis, image_token_id=290,
+                                                     video_token_id=291, vision_start_token_id=293)).eval()
+    missing, unexpected = backbone.load_state_dict(model.state_dict(), strict=False)
+    assert not missing and all(k.startswith(("audio_tower.", "multi_modal_projector.")) for k in unexpected)
+    ids = torch.randint(0, 280, (1, 48))
+    ids[0, 2], ids[0, 3:7] = 293, 290
+    ids[0, 20:25] = 292
+    pix, grid = torch.randn(16, 3 * 2 * 4 * 4), torch.tensor([[1, 4, 4]])
+    ones = torch.ones_like(ids)
+    common = dict(input_ids=ids, attention_mask=ones, labels=ids, pixel_values=pix, image_grid_thw=grid)
+    with torch.no_grad():
+        plain = model(**common)["loss"]
+        assert abs(float(plain) - float(backbone(**common)["loss"])) < 1e-6
+        # two clips: 13 and 8 mel frames -> 6 and 4 encoder frames -> 3 + 2 rows of two frames each
+        feats = torch.randn(2, 8, 13)
+        mel_mask = torch.zeros(2, 13, dtype=torch.long)
+        mel_mask[0, :13], mel_mask[1, :8] = 1, 1
+        stream = ids.clone()
+        stream[0, 20:25] = torch.tensor([281, 282, 283, 281, 281])
+        got = model(**common, text_stream_ids=stream, input_features=feats, feature_attention_mask=mel_mask)["loss"]
+        frame_mask = torch.zeros(2, 6, dtype=torch.long)
+        frame_mask[0, :6], frame_mask[1, :4] = 1, 1
+        again = model(**common, text_stream_ids=stream, input_features=feats, audio_attention_mask=frame_mask)["loss"]
+        enc = model.audio_tower(feats, mel_mask)
+        hidden = enc["last_hidden_state"]
+        assert enc["frame_lengths"].tolist() == [6, 4]
+        rows = torch.cat([hidden[0:6].reshape(3, -1), hidden[6:10].reshape(2, -1)])
+        rows = model.multi_modal_projector(rows)
+        emb, deep, deep_idx = VLModel_embed(model, ids[0], pix, grid, stream[0])
+        emb[20:25] += rows
+        lm = model.language_model
+        _, labels, pos, cu, _ = lm.prepare_packed(ids, ones, ids, None, None)
+        from lmms_engine_b200.models import mrope
+
+        pos = mrope.build_mrope_positions(ids[0], cu, (290, 291), grid.tolist(), [0.0], 2, 0.0)
+        want = lm(inputs_embeds=emb, labels=labels, position_ids=pos, cu_seqlens=cu, deepstack=deep, deepstack_index=deep_idx)["loss"]
+    assert abs(float(got) - float(want)) < 1e-5 and abs(float(got) - float(plain)) > 1e-4
+    assert abs(float(again) - float(got)) < 1e-6  # the same clips described by a frame-level mask
+
+
+def VLModel_embed(model, ids, pix, grid, stream):
+    from lmms_engine_b200.models.vl import VLModel
+
+    return VLModel.embed_multimodal(model, ids, pix, grid, None, None, embed_ids=stream)
