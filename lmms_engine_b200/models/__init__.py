@@ -66,3 +66,7 @@ for _mt in ("qwen3_5", "qwen3_5_moe"):
 from .aero_realtime import AeroRealtimeConfig, AeroRealtimeModel  # noqa: E402
 
 register_model("aero_realtime", AeroRealtimeConfig, AeroRealtimeModel, "image_text_to_text")
+
+from .gated_deltanet import GatedDeltaNetConfig, GatedDeltaNetLM  # noqa: E402
+
+register_model("gated_deltanet", GatedDeltaNetConfig, GatedDeltaNetLM, "causal_lm")

@@ -162,17 +162,7 @@ class GatedDeltaNet(nn.Module):
         b, a = proj[:, c + self.value_dim:c + self.value_dim + self.hv], proj[:, c + self.value_dim + self.hv:c + self.value_dim + 2 * self.hv]
         beta = b.sigmoid()
         g = -self.A_log.float().exp() * F.softplus(a.float() + self.dt_bias)
-        plan = getattr(ctx, "gdn_plan", None)
-        if plan is None:
-            # one host read of the document boundaries per forward pass, shared by all layers
-            bounds = ctx.cu_seqlens.tolist()
-            lengths = [hi - lo for lo, hi in zip(bounds[:-1], bounds[1:]) if hi > lo]
-            pos = torch.cat([torch.arange(n) for n in lengths]) if lengths else torch.zeros(0, dtype=torch.long)
-            plan = (lengths, pos.to(x.device, non_blocking=True), gdn_ops.chunk_plan(lengths, x.device))
-            try:
-                ctx.gdn_plan = plan
-            except AttributeError:
-                pass
+        plan = gdn_ops.plan_for(ctx, x.device)
         lengths, pos_in_doc, chunks = plan
         live = int(pos_in_doc.numel())  # rows after it are the padding of a sequence-parallel split
         # causal depthwise convolution inside every document, then SiLU

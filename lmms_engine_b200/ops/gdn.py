@@ -108,6 +108,22 @@ def chunk_plan(lengths: List[int], device) -> Tuple[torch.Tensor, torch.Tensor, 
     return (torch.tensor(src, dtype=torch.long, device=device), torch.tensor(back, dtype=torch.long, device=device), reset)
 
 
+def plan_for(ctx, device):
+    """``(lengths, pos_in_doc, chunk_plan)`` of a packed context: one host read of the document boundaries per
+    forward pass, cached on the context and shared by all layers."""
+    plan = getattr(ctx, "gdn_plan", None)
+    if plan is None:
+        bounds = ctx.cu_seqlens.tolist()
+        lengths = [hi - lo for lo, hi in zip(bounds[:-1], bounds[1:]) if hi > lo]
+        pos = torch.cat([torch.arange(n) for n in lengths]) if lengths else torch.zeros(0, dtype=torch.long)
+        plan = (lengths, pos.to(device, non_blocking=True), chunk_plan(lengths, device))
+        try:
+            ctx.gdn_plan = plan
+        except AttributeError:
+            pass
+    return plan
+
+
 def chunk_gated_delta_rule_packed(q, k, v, g, beta, lengths: List[int], plan=None):
     """``q, k [T, H, dk]``, ``v [T, H, dv]``, ``g, beta [T, H]`` for documents of ``lengths`` laid end to end ->
     ``o [T, H, dv]``.  Math in fp32; q and k are L2-normalised here, q is scaled by ``dk ** -0.5``."""

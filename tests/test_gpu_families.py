@@ -104,3 +104,31 @@ def test_llava_onevision1_5_gpu():
     _compare("llavaonevision1_5", cfg, dict(input_ids=ids, attention_mask=torch.ones_like(ids), labels=ids,
                                             pixel_values=torch.randn(24, 3 * 8 * 8), image_grid_thw=grid_i,
                                             pixel_values_videos=torch.randn(16, 3 * 8 * 8), video_grid_thw=grid_v))
+
+
+def test_gated_deltanet_matches_library_model_gpu():
+    """Same weights in the FLA library's model (its Triton kernels) and in the native one: equal loss."""
+    import warnings
+
+    try:
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            from fla.models import GatedDeltaNetConfig as FC, GatedDeltaNetForCausalLM as FM
+    except Exception as e:  # the library is an optional oracle
+        pytest.skip(f"fla not usable: {e}")
+    from lmms_engine_b200.mapping_func import create_model_from_config
+    from lmms_engine_b200.ops import _cuda
+
+    torch.manual_seed(0)
+    cfg = dict(vocab_size=256, hidden_size=256, num_hidden_layers=2, num_heads=2, num_v_heads=4, head_dim=128, expand_v=1.0, hidden_ratio=4)
+    lib = FM(FC(**cfg, fuse_norm=False, fuse_swiglu=False, fuse_cross_entropy=False)).to("cuda", torch.bfloat16).eval()
+    mine = create_model_from_config("gated_deltanet", cfg).to("cuda", torch.bfloat16).eval()
+    mine.load_state_dict(mine.convert_hf_state_dict(lib.state_dict()), strict=True)
+    ids = torch.randint(0, 256, (1, 300), device="cuda")
+    n0 = _cuda.launch_count
+    with torch.no_grad():
+        want = lib(input_ids=ids, labels=ids).loss
+        got = mine(input_ids=ids, attention_mask=torch.ones_like(ids), labels=ids)["loss"]
+    torch.cuda.synchronize()
+    assert _cuda.launch_count > n0
+    assert abs(float(got) - float(want)) < 0.03, (float(got), float(want))

@@ -686,3 +686,57 @@ def VLModel_embed(model, ids, pix, grid, stream):
     from lmms_engine_b200.models.vl import VLModel
 
     return VLModel.embed_multimodal(model, ids, pix, grid, None, None, embed_ids=stream)
+
+
+def test_gated_deltanet_lm_loads_library_checkpoints_and_matches_token_recurrence():
+    """``gated_deltanet``: parameter names / shapes of the FLA library's model load strictly; one linear-attention
+    layer equals a token-by-token restatement built from its weights (two documents, value heads = 2 x key heads)."""
+    from lmms_engine_b200.mapping_func import create_model_from_config
+    from lmms_engine_b200.models.decoder_lm import PackedContext
+    from lmms_engine_b200.models.qwen3_5 import recurrent_gated_delta_rule
+
+    torch.manual_seed(0)
+    cfg = dict(vocab_size=200, hidden_size=64, num_hidden_layers=2, num_heads=2, num_v_heads=4, head_dim=16, expand_v=2.0, hidden_ratio=4)
+    model = create_model_from_config("gated_deltanet", cfg).eval()
+    assert model.config.intermediate_size == 256
+    try:
+        import warnings
+
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            from fla.models import GatedDeltaNetConfig as FC, GatedDeltaNetForCausalLM as FM
+        lib = FM(FC(**cfg, fuse_norm=False, fuse_swiglu=False))
+        model.load_state_dict(model.convert_hf_state_dict(lib.state_dict()), strict=True)
+    except ImportError:
+        pass
+    layer = model.model.layers[0].attn
+    lens = [37, 70]
+    x = torch.randn(sum(lens), 64)
+    cu = torch.tensor([0, 37, 107], dtype=torch.int32)
+    ctx = PackedContext(cu, 70, None, None, True)
+    with torch.no_grad():
+        got = layer(x, ctx)
+        outs, at = [], 0
+        for L in lens:
+            seg = x[at:at + L]
+            at += L
+
+            def conv(t, w):  # causal depthwise convolution, last tap on the current token, then SiLU
+                pad = F.pad(t, (0, 0, w.shape[-1] - 1, 0))
+                return F.silu(sum(pad[j:j + L] * w[:, 0, j] for j in range(w.shape[-1])))
+
+            q = conv(seg @ layer.q_proj.weight.T, layer.q_conv1d.weight).view(L, 2, 16).repeat_interleave(2, 1)
+            k = conv(seg @ layer.k_proj.weight.T, layer.k_conv1d.weight).view(L, 2, 16).repeat_interleave(2, 1)
+            v = conv(seg @ layer.v_proj.weight.T, layer.v_conv1d.weight).view(L, 4, 32)
+            g = -layer.A_log.exp() * F.softplus(seg @ layer.a_proj.weight.T + layer.dt_bias)
+            beta = (seg @ layer.b_proj.weight.T).sigmoid()
+            o = recurrent_gated_delta_rule(q, k, v, g, beta)
+            o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + 1e-6) * layer.o_norm.weight
+            gate = (seg @ layer.g_proj.weight.T).view(L, 4, 32)
+            outs.append((o * F.silu(gate)).reshape(L, -1) @ layer.o_proj.weight.T)
+        want = torch.cat(outs)
+    assert (got - want).abs().max() < 2e-5 * max(1.0, float(want.abs().max()))
+    ids = torch.randint(0, 200, (107,))
+    out = model(input_ids=ids, labels=ids, cu_seqlens=cu)
+    out["loss"].backward()
+    assert torch.isfinite(out["loss"]) and model.model.layers[1].attn.A_log.grad is not None
