@@ -23,6 +23,8 @@ CHUNK = 64
 
 _cuda.register("b200_gdn_scan_fwd", "gdn_scan", "ppppppppp" + "iiii" + "s")
 _cuda.register("b200_gdn_scan_bwd", "gdn_scan", "pppppppppppppp" + "iiii" + "s")
+_cuda.register("b200_conv_silu_fwd", "gdn_conv", "pppp" + "l" + "iii" + "s")
+_cuda.register("b200_conv_silu_bwd", "gdn_conv", "pppppp" + "l" + "iii" + "s")
 
 
 def l2norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
@@ -161,9 +163,8 @@ def chunk_gated_delta_rule_packed(q, k, v, g, beta, lengths: List[int], plan=Non
     return out.index_select(0, back).to(dt)
 
 
-def causal_conv_silu_packed(x: torch.Tensor, weight: torch.Tensor, pos_in_doc: torch.Tensor) -> torch.Tensor:
-    """Depthwise causal convolution inside every document followed by SiLU.  ``x [T, Ch]``,
-    ``weight [Ch, K]`` (tap ``K-1`` multiplies the current token), ``pos_in_doc [T]``."""
+def causal_conv_silu_ref(x: torch.Tensor, weight: torch.Tensor, pos_in_doc: torch.Tensor) -> torch.Tensor:
+    """fp32 framework-op form (CPU path and oracle of the kernels)."""
     K = weight.shape[1]
     xf = x.float()
     acc = xf * weight[:, K - 1].float()
@@ -171,3 +172,34 @@ def causal_conv_silu_packed(x: torch.Tensor, weight: torch.Tensor, pos_in_doc: t
         shifted = F.pad(xf, (0, 0, j, 0))[: xf.shape[0]]
         acc = acc + torch.where((pos_in_doc >= j).unsqueeze(1), shifted, torch.zeros_like(shifted)) * weight[:, K - 1 - j].float()
     return F.silu(acc).to(x.dtype)
+
+
+class _ConvSilu(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, pos32):
+        x = x.contiguous()
+        w = weight.float().contiguous()
+        y = torch.empty_like(x)
+        _cuda.call("b200_conv_silu_fwd", x.data_ptr(), w.data_ptr(), pos32.data_ptr(), y.data_ptr(), x.shape[0], x.shape[1],
+                   w.shape[1], int(x.dtype == torch.bfloat16), _cuda.stream())
+        ctx.save_for_backward(x, w, pos32)
+        ctx.wdtype = weight.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, pos32 = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = torch.empty_like(x)
+        dw = torch.zeros_like(w)
+        _cuda.call("b200_conv_silu_bwd", x.data_ptr(), w.data_ptr(), pos32.data_ptr(), dy.data_ptr(), dx.data_ptr(), dw.data_ptr(),
+                   x.shape[0], x.shape[1], w.shape[1], int(x.dtype == torch.bfloat16), _cuda.stream())
+        return dx, dw.to(ctx.wdtype), None
+
+
+def causal_conv_silu_packed(x: torch.Tensor, weight: torch.Tensor, pos_in_doc: torch.Tensor) -> torch.Tensor:
+    """Depthwise causal convolution inside every document followed by SiLU.  ``x [T, Ch]``,
+    ``weight [Ch, K]`` (tap ``K-1`` multiplies the current token), ``pos_in_doc [T]``."""
+    if x.is_cuda and weight.shape[1] in (2, 3, 4) and x.dtype in (torch.bfloat16, torch.float32) and x.shape[0] > 0:
+        return _ConvSilu.apply(x, weight, pos_in_doc.to(torch.int32).contiguous())
+    return causal_conv_silu_ref(x, weight, pos_in_doc)

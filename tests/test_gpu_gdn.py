@@ -77,3 +77,27 @@ def test_packed_rule_matches_cpu_and_reports_time():
                 print(f"GDN_TIME {name}: {a.elapsed_time(b) / 2:.2f} ms per forward+backward, T={T} H={H}", flush=True)
             finally:
                 gdn.scan = keep
+
+
+@pytest.mark.parametrize("dtype,K", [(torch.float32, 4), (torch.bfloat16, 4), (torch.float32, 2)])
+def test_conv_silu_kernels_match_framework_ops(dtype, K):
+    from lmms_engine_b200.ops import _cuda, gdn
+
+    torch.manual_seed(0)
+    lengths = [70, 1, 33, 200, 2]
+    T, Ch = sum(lengths), 200
+    pos = torch.cat([torch.arange(n) for n in lengths]).cuda()
+    x = torch.randn(T, Ch, device="cuda", dtype=dtype).requires_grad_()
+    w = (0.5 * torch.randn(Ch, K, device="cuda")).requires_grad_()
+    n0 = _cuda.launch_count
+    y = gdn.causal_conv_silu_packed(x, w, pos)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    assert _cuda.launch_count == n0 + 2, "the convolution kernels did not run"
+    xr, wr = x.detach().float().requires_grad_(), w.detach().clone().requires_grad_()
+    yr = gdn.causal_conv_silu_ref(xr, wr, pos)
+    yr.backward(gy.float())
+    tol = 1e-5 if dtype == torch.float32 else 3e-2
+    assert (y.float() - yr).abs().max() < tol
+    assert (x.grad.float() - xr.grad).abs().max() < tol * 4
+    assert (w.grad - wr.grad).abs().max() < tol * max(1.0, float(wr.grad.abs().max()))
