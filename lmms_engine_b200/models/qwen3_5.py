@@ -12,7 +12,8 @@ between chunks through the carried state.  All documents of a packed batch are p
 processed together (``ops/gdn.py``): the in-chunk algebra as batched fp32 ops, the chunk-to-chunk recurrence in one
 CUDA kernel per direction with the state reset at every document start, so neither the short causal convolution nor
 the state ever crosses a document boundary.  Projections, norms, the gated attention layers and the loss use the
-engine's kernels.  Full-attention heads wider than 128
+engine's kernels.  Under Ulysses sequence parallelism the heads of both layer kinds are exchanged around the
+sequence-wide parts (convolution + rule, attention).  Full-attention heads wider than 128
 (the released models use 256) fall back to the reference attention path.
 """
 from __future__ import annotations
@@ -22,6 +23,7 @@ from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional
 
 import torch
+import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
 
@@ -30,6 +32,7 @@ from ..ops import gemm as gemm_ops
 from ..ops import gdn as gdn_ops
 from ..ops import norm as norm_ops
 from ..ops import rope as rope_ops
+from ..parallel.sequence_parallel import ulysses as sp
 from .decoder_lm import DecoderBackbone, DecoderConfig, DecoderLM, PackedContext, SwiGLUMLP, _w
 
 
@@ -160,20 +163,42 @@ class GatedDeltaNet(nn.Module):
         c = 2 * self.key_dim + self.value_dim
         mixed, z = proj[:, :c], proj[:, c:c + self.value_dim]
         b, a = proj[:, c + self.value_dim:c + self.value_dim + self.hv], proj[:, c + self.value_dim + self.hv:c + self.value_dim + 2 * self.hv]
+        A_log, dt_bias, conv_w = self.A_log, self.dt_bias, self.conv1d.weight[:, 0]
+        hk, hv = self.hk, self.hv
+        if ctx.sp_size > 1:
+            # Ulysses: the convolution and the rule run on whole sequences of this rank's heads.  Heads are
+            # independent (the convolution is depthwise), so one exchange in and one out carry the layer.
+            n, r = ctx.sp_size, dist.get_rank(ctx.sp_group)
+            assert hk % n == 0 and hv % n == 0, "linear-attention heads must divide the sequence-parallel size"
+            qh, kh, vh = torch.split(mixed, [self.key_dim, self.key_dim, self.value_dim], -1)
+            qh = sp.gather_seq_scatter_heads(qh.reshape(T, hk, self.dk), ctx.sp_group)
+            kh = sp.gather_seq_scatter_heads(kh.reshape(T, hk, self.dk), ctx.sp_group)
+            vh = sp.gather_seq_scatter_heads(vh.reshape(T, hv, self.dv), ctx.sp_group)
+            ab = sp.gather_seq_scatter_heads(torch.stack([a, b], -1).float(), ctx.sp_group)
+            a, b = ab[..., 0], ab[..., 1]
+            hk, hv = hk // n, hv // n
+            mixed = torch.cat([qh.flatten(1), kh.flatten(1), vh.flatten(1)], -1)
+            rows = torch.cat([torch.arange(r * hk * self.dk, (r + 1) * hk * self.dk),
+                              self.key_dim + torch.arange(r * hk * self.dk, (r + 1) * hk * self.dk),
+                              2 * self.key_dim + torch.arange(r * hv * self.dv, (r + 1) * hv * self.dv)]).to(conv_w.device)
+            conv_w = conv_w.index_select(0, rows)
+            A_log, dt_bias = A_log[r * hv:(r + 1) * hv], dt_bias[r * hv:(r + 1) * hv]
         beta = b.sigmoid()
-        g = -self.A_log.float().exp() * F.softplus(a.float() + self.dt_bias)
+        g = -A_log.float().exp() * F.softplus(a.float() + dt_bias)
         plan = gdn_ops.plan_for(ctx, x.device)
         lengths, pos_in_doc, chunks = plan
         live = int(pos_in_doc.numel())  # rows after it are the padding of a sequence-parallel split
         # causal depthwise convolution inside every document, then SiLU
-        seg = gdn_ops.causal_conv_silu_packed(mixed[:live], self.conv1d.weight[:, 0], pos_in_doc)
-        q, k, v = torch.split(seg, [self.key_dim, self.key_dim, self.value_dim], -1)
-        q, k, v = q.reshape(-1, self.hk, self.dk), k.reshape(-1, self.hk, self.dk), v.reshape(-1, self.hv, self.dv)
-        if self.hv // self.hk > 1:
-            q, k = q.repeat_interleave(self.hv // self.hk, 1), k.repeat_interleave(self.hv // self.hk, 1)
+        seg = gdn_ops.causal_conv_silu_packed(mixed[:live], conv_w, pos_in_doc)
+        q, k, v = torch.split(seg, [hk * self.dk, hk * self.dk, hv * self.dv], -1)
+        q, k, v = q.reshape(-1, hk, self.dk), k.reshape(-1, hk, self.dk), v.reshape(-1, hv, self.dv)
+        if hv // hk > 1:
+            q, k = q.repeat_interleave(hv // hk, 1), k.repeat_interleave(hv // hk, 1)
         o = gdn_ops.chunk_gated_delta_rule_packed(q, k, v, g[:live], beta[:live], lengths, chunks)
-        if o.shape[0] < T:
-            o = torch.cat([o, o.new_zeros((T - o.shape[0], self.hv, self.dv))], 0)
+        if o.shape[0] < mixed.shape[0]:
+            o = torch.cat([o, o.new_zeros((mixed.shape[0] - o.shape[0], hv, self.dv))], 0)
+        if ctx.sp_size > 1:
+            o = sp.gather_heads_scatter_seq(o, ctx.sp_group)
         # RMSNorm over the head dim, gated by SiLU(z)
         o = norm_ops.rmsnorm(o.reshape(-1, self.dv).to(x.dtype), self.norm.weight, self.eps)
         o = (o.float() * F.silu(z.reshape(-1, self.dv).float())).to(x.dtype).reshape(T, self.value_dim)
@@ -202,9 +227,13 @@ class GatedAttention(nn.Module):
         v = gemm_ops.linear(x, _w(self.v_proj.weight), _w(self.v_proj.bias)).view(T, self.n_kv, D)
         q = self.q_norm(q.reshape(-1, D)).view(T, self.n_q, D)
         k = self.k_norm(k.reshape(-1, D)).view(T, self.n_kv, D)
+        if ctx.sp_size > 1:  # Ulysses: trade the sequence split for a head split around attention
+            q, k, v = sp.seq_to_head_qkv(q, k, v, ctx.sp_group)
         q, k = rope_ops.rope_apply(q, ctx.cos, ctx.sin), rope_ops.rope_apply(k, ctx.cos, ctx.sin)
         o = attn_ops.varlen_attn(q, k, v, ctx.cu_seqlens, ctx.cu_seqlens, ctx.max_seqlen, ctx.max_seqlen, causal=ctx.causal,
                                  softmax_scale=1.0 / math.sqrt(D))
+        if ctx.sp_size > 1:
+            o = sp.head_to_seq(o, ctx.sp_group, self.n_q, self.n_kv)
         o = (o.reshape(T, -1).float() * torch.sigmoid(gate.float())).to(x.dtype)
         return gemm_ops.linear(o, _w(self.o_proj.weight), _w(self.o_proj.bias))
 
@@ -264,11 +293,6 @@ class Qwen35LM(DecoderLM):
         super()._init_weights(m)
         if isinstance(m, ZRMSNorm):
             nn.init.zeros_(m.weight)
-
-    def forward(self, *args, **kwargs):
-        if self.sp_group is not None:
-            raise NotImplementedError("sequence parallelism for the linear-attention layers (state hand-off between ranks) is not built")
-        return super().forward(*args, **kwargs)
 
     def convert_hf_state_dict(self, sd):
         out = {}

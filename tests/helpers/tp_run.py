@@ -19,10 +19,26 @@ def main(mode):
 
     cfg = DecoderConfig(model_type="qwen3", vocab_size=256, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
                         num_attention_heads=4, num_key_value_heads=2 if mode == "tp" else 1, head_dim=16)
+    build = DecoderLM
+    if mode == "ulysses_hybrid":
+        # Gated-DeltaNet + gated-attention hybrid: both layer kinds trade the sequence split for a head split
+        from lmms_engine_b200.models.qwen3_5 import Qwen35Config, Qwen35LM
+
+        cfg = Qwen35Config(vocab_size=256, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
+                           num_key_value_heads=2, head_dim=16, linear_conv_kernel_dim=4, linear_key_head_dim=16,
+                           linear_value_head_dim=16, linear_num_key_heads=2, linear_num_value_heads=4, partial_rotary_factor=0.5)
+        build = Qwen35LM
     torch.manual_seed(0)
-    full = DecoderLM(cfg)
+    full = build(cfg)
     torch.manual_seed(0)
-    model = DecoderLM(cfg)
+    model = build(cfg)
+    if mode == "ulysses_hybrid":
+        with torch.no_grad():  # zero-centred norm scales and unit decay parameters would hide mistakes
+            for m_ in (full, model):
+                g_ = torch.Generator().manual_seed(7)
+                for p_ in m_.parameters():
+                    if p_.dim() == 1:
+                        p_.copy_(0.5 * torch.rand(p_.shape, generator=g_))
     g = torch.Generator().manual_seed(3)
     ids = torch.randint(0, 256, (91,), generator=g)  # not a multiple of the group size: exercises padding
     cu = torch.tensor([0, 40, 91], dtype=torch.int32)

@@ -61,5 +61,11 @@ def test_ulysses_matches_unsharded(world):
     assert "ulysses ok" in torchrun("tp_run.py", world, "ulysses")
 
 
+def test_ulysses_hybrid_linear_attention_matches_unsharded():
+    """Qwen3.5 layers under Ulysses: the linear-attention heads (convolution + delta rule) and the gated-attention heads
+    are exchanged around their sequence-wide parts; loss and gradients equal the single-process model."""
+    assert "ulysses_hybrid ok" in torchrun("tp_run.py", 2, "ulysses_hybrid")
+
+
 def test_vit_frame_parallel_matches_local_tower():
     assert "vit frame parallel ok" in torchrun("vit_fp_run.py", 3)
