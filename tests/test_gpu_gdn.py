@@ -101,3 +101,35 @@ def test_conv_silu_kernels_match_framework_ops(dtype, K):
     assert (y.float() - yr).abs().max() < tol
     assert (x.grad.float() - xr.grad).abs().max() < tol * 4
     assert (w.grad - wr.grad).abs().max() < tol * max(1.0, float(wr.grad.abs().max()))
+
+
+def test_conv_silu_bandwidth_report():
+    """With ``GDN_TIME`` set: device time of the convolution kernels on the Qwen3.5-9B sized stream
+    (16 384 tokens x 8192 channels, bf16) against the bytes they must move."""
+    if not os.environ.get("GDN_TIME"):
+        pytest.skip("timing report only")
+    from lmms_engine_b200.ops import gdn
+
+    T, Ch, K = 16384, 8192, 4
+    pos = (torch.arange(T, device="cuda") % 2048)
+    x = torch.randn(T, Ch, device="cuda", dtype=torch.bfloat16).requires_grad_()
+    w = (0.5 * torch.randn(Ch, K, device="cuda")).requires_grad_()
+    gy = torch.randn(T, Ch, device="cuda", dtype=torch.bfloat16)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    times = {"fwd": [], "bwd": []}
+    for it in range(6):
+        flush.zero_()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        y = gdn.causal_conv_silu_packed(x, w, pos)
+        e[1].record()
+        y.backward(gy)
+        e[2].record()
+        torch.cuda.synchronize()
+        if it >= 3:
+            times["fwd"].append(e[0].elapsed_time(e[1]))
+            times["bwd"].append(e[1].elapsed_time(e[2]))
+    nbytes = T * Ch * 2
+    fwd, bwd = min(times["fwd"]), min(times["bwd"])
+    print(f"GDN_TIME conv fwd {fwd:.3f} ms = {2 * nbytes / fwd / 1e6:.0f} GB/s (x read + y written); "
+          f"bwd {bwd:.3f} ms = {3 * nbytes / bwd / 1e6:.0f} GB/s (x, dy read + dx written)", flush=True)
