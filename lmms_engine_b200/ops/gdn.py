@@ -177,7 +177,7 @@ def causal_conv_silu_ref(x: torch.Tensor, weight: torch.Tensor, pos_in_doc: torc
 class _ConvSilu(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, pos32):
-        x = x.contiguous()
+        x = _dense16(x)
         w = weight.float().contiguous()
         y = torch.empty_like(x)
         _cuda.call("b200_conv_silu_fwd", x.data_ptr(), w.data_ptr(), pos32.data_ptr(), y.data_ptr(), x.shape[0], x.shape[1],
@@ -189,7 +189,7 @@ class _ConvSilu(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x, w, pos32 = ctx.saved_tensors
-        dy = dy.contiguous()
+        dy = _dense16(dy)
         dx = torch.empty_like(x)
         dw = torch.zeros_like(w)
         _cuda.call("b200_conv_silu_bwd", x.data_ptr(), w.data_ptr(), pos32.data_ptr(), dy.data_ptr(), dx.data_ptr(), dw.data_ptr(),
@@ -200,6 +200,7 @@ class _ConvSilu(torch.autograd.Function):
 def causal_conv_silu_packed(x: torch.Tensor, weight: torch.Tensor, pos_in_doc: torch.Tensor) -> torch.Tensor:
     """Depthwise causal convolution inside every document followed by SiLU.  ``x [T, Ch]``,
     ``weight [Ch, K]`` (tap ``K-1`` multiplies the current token), ``pos_in_doc [T]``."""
-    if x.is_cuda and weight.shape[1] in (2, 3, 4) and x.dtype in (torch.bfloat16, torch.float32) and x.shape[0] > 0:
+    if (x.is_cuda and weight.shape[1] in (2, 3, 4) and x.dtype in (torch.bfloat16, torch.float32) and x.shape[0] > 0
+            and x.shape[1] % 2 == 0):
         return _ConvSilu.apply(x, weight, pos_in_doc.to(torch.int32).contiguous())
     return causal_conv_silu_ref(x, weight, pos_in_doc)
