@@ -10,9 +10,9 @@
 * **sliding**: causal attention over the last ``window_size`` tokens (the varlen tcgen05 kernel).
 
 Same call structure as the patched attention of src/lmms_engine/models/bagel/nsa_op.py:25-159, which
-drives an external Triton package; this file states the arithmetic in PyTorch.  The selected branch is
-evaluated as masked attention over query chunks (its cost is that of dense attention, its result that of
-the block-sparse one); no gradient flows through the block choice.
+drives an external Triton package; this file states the arithmetic in PyTorch.  The selected branch gathers the
+chosen blocks per query chunk when the document is long (work proportional to ``topk * block_size``) and runs as
+masked attention when it is short; no gradient flows through the block choice.
 """
 from __future__ import annotations
 
@@ -138,29 +138,56 @@ def compressed_attention(q, k_cmp, v_cmp, cu, counts, p: NSAParams, scale: float
     return out, topk_idx
 
 
-def topk_sparse_attention(q, k, v, topk_idx, block: int, cu, scale: float, q_chunk: int = 2048):
-    """Selected branch: every query attends causally to the tokens of its chosen blocks."""
+def _selected_dense(q, kf, vf, idx, block, s0, s1, G, scale):
+    """Queries ``s0:s1`` of one document against all its keys under the block mask (short documents)."""
+    L, Hkv = kf.shape[0], kf.shape[1]
+    nb = (L + block - 1) // block
+    dev = q.device
+    kblk = torch.arange(L, device=dev) // block
+    sel = torch.zeros((s1 - s0, Hkv, nb + 1), dtype=torch.bool, device=dev)
+    sel.scatter_(2, torch.where(idx >= 0, idx, torch.full_like(idx, nb)), True)
+    tok = sel[:, :, :nb].index_select(2, kblk)  # [c, Hkv, L]
+    tok &= (torch.arange(L, device=dev)[None, :] <= torch.arange(s0, s1, device=dev)[:, None]).unsqueeze(1)
+    tok = tok.permute(1, 0, 2).repeat_interleave(G, 0)  # [Hq, c, L]
+    s = torch.einsum("qhd,khd->hqk", q, kf.repeat_interleave(G, 1)) * scale
+    prob = torch.softmax(s.masked_fill(~tok, float("-inf")), -1)
+    return torch.einsum("hqk,khd->qhd", prob, vf.repeat_interleave(G, 1))
+
+
+def _selected_gathered(q, kf, vf, idx, block, s0, s1, G, scale):
+    """The same through a gather of the chosen blocks: work grows with ``topk * block``, not with the document."""
+    L, Hkv, D = kf.shape
+    dev = q.device
+    c, topk = s1 - s0, idx.shape[-1]
+    keys = idx.clamp(min=0).unsqueeze(-1) * block + torch.arange(block, device=dev)  # [c, Hkv, topk, block]
+    ok = (idx >= 0).unsqueeze(-1) & (keys <= torch.arange(s0, s1, device=dev)[:, None, None, None])
+    keys = keys.clamp(max=L - 1).view(c, Hkv, topk * block)
+    ok = ok.view(c, Hkv, topk * block)
+    heads = torch.arange(Hkv, device=dev)[None, :, None]
+    kg, vg = kf.transpose(0, 1)[heads, keys], vf.transpose(0, 1)[heads, keys]  # [c, Hkv, topk*block, D]
+    qg = q.view(c, Hkv, G, D)
+    s = torch.einsum("chgd,chkd->chgk", qg, kg) * scale
+    prob = torch.softmax(s.masked_fill(~ok.unsqueeze(2), float("-inf")), -1)
+    return torch.einsum("chgk,chkd->chgd", prob, vg).reshape(c, Hkv * G, D)
+
+
+def topk_sparse_attention(q, k, v, topk_idx, block: int, cu, scale: float, q_chunk: int = 2048, gather: Optional[bool] = None):
+    """Selected branch: every query attends causally to the tokens of its chosen blocks.  Documents longer than
+    twice the selected span gather their blocks (``gather`` forces a path)."""
     T, Hq, D = q.shape
     Hkv = k.shape[1]
     G = Hq // Hkv
+    span = topk_idx.shape[-1] * block
     outs = []
     at = 0
     for L in _doc_lens(cu):
-        nb = (L + block - 1) // block
-        kf = k[at:at + L].float().repeat_interleave(G, 1)
-        vf = v[at:at + L].float().repeat_interleave(G, 1)
-        kblk = torch.arange(L, device=q.device) // block
-        for s0 in range(0, L, q_chunk):
-            s1 = min(L, s0 + q_chunk)
-            idx = topk_idx[at + s0:at + s1]  # [c, Hkv, topk]
-            sel = torch.zeros((s1 - s0, Hkv, nb + 1), dtype=torch.bool, device=q.device)
-            sel.scatter_(2, torch.where(idx >= 0, idx, torch.full_like(idx, nb)), True)
-            tok = sel[:, :, :nb].index_select(2, kblk)  # [c, Hkv, L]
-            tok &= (torch.arange(L, device=q.device)[None, :] <= torch.arange(s0, s1, device=q.device)[:, None]).unsqueeze(1)
-            tok = tok.permute(1, 0, 2).repeat_interleave(G, 0)  # [Hq, c, L]
-            s = torch.einsum("qhd,khd->hqk", q[at + s0:at + s1].float(), kf) * scale
-            prob = torch.softmax(s.masked_fill(~tok, float("-inf")), -1)
-            outs.append(torch.einsum("hqk,khd->qhd", prob, vf).to(q.dtype))
+        kf, vf = k[at:at + L].float(), v[at:at + L].float()
+        use_gather = gather if gather is not None else L > 2 * span
+        step = max(1, min(q_chunk, (1 << 27) // max(1, Hkv * span * D))) if use_gather else q_chunk
+        for s0 in range(0, L, step):
+            s1 = min(L, s0 + step)
+            fn = _selected_gathered if use_gather else _selected_dense
+            outs.append(fn(q[at + s0:at + s1].float(), kf, vf, topk_idx[at + s0:at + s1], block, s0, s1, G, scale).to(q.dtype))
         at += L
     return torch.cat(outs) if outs else q.new_zeros((0, Hq, D))
 

@@ -81,6 +81,17 @@ def test_branches_match_token_by_token_restatement():
     _, idx = nsa.compressed_attention(q, k_cmp, v_cmp, cu, counts, p, scale)
     for (t, hk), sel in chosen.items():
         assert {int(b) for b in idx[t, hk] if b >= 0} == sel, (t, hk)
+    # gathered blocks == masked attention, values and gradients
+    qg, kg, vg = (t.clone().requires_grad_() for t in (q, k, v))
+    qd, kd, vd = (t.clone().requires_grad_() for t in (q, k, v))
+    a = nsa.topk_sparse_attention(qg, kg, vg, idx, p.block_size, cu, scale, q_chunk=16, gather=True)
+    b = nsa.topk_sparse_attention(qd, kd, vd, idx, p.block_size, cu, scale, gather=False)
+    assert (a - b).abs().max() < 1e-5
+    probe = torch.randn_like(a)
+    (a * probe).sum().backward()
+    (b * probe).sum().backward()
+    for x, y in ((qg, qd), (kg, kd), (vg, vd)):
+        assert (x.grad - y.grad).abs().max() < 1e-4
     # the linear compression starts as the window average
     wl = nsa.compress_weight("linear", Hkv, D, 4)
     k_lin, _ = nsa.compress(k, wl, cu, 4, 2, None, "linear")
