@@ -10,6 +10,7 @@ the Frobenius pre-normalisation follow the reference
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -68,6 +69,45 @@ def newton_schulz(X: torch.Tensor, steps: int = 5, work: Optional[dict] = None, 
             _gemm.gemm(B, cur, b_mn_major=True, beta=a, cin=cur, out=nxt, max_ctas=max_ctas)  # a X + B X
         cur, nxt = nxt, cur
     return cur
+
+
+GRAPH_MAX_DIM = int(os.environ.get("LMMS_B200_MUON_GRAPH_MAX_DIM", "2048"))
+
+
+def newton_schulz_graphed(X: torch.Tensor, steps: int, work: dict, max_ctas: int = 0) -> torch.Tensor:
+    """The same chain replayed from a CUDA graph: for small matrices the ``3 * steps`` products take a few
+    microseconds each and the chain is bound by launches; one graph launch replaces them.  The graph of a shape is
+    captured on first use (after one eager pass that allocates the work buffers) and owns its input and output
+    buffers: the result must be consumed before the next call with the same shape on the same ``work``."""
+    key = ("graph", tuple(X.shape), steps, max_ctas)
+    entry = work.get(key)
+    if entry is None:
+        inner: dict = {}
+        side = torch.cuda.Stream(device=X.device)
+        side.wait_stream(torch.cuda.current_stream(X.device))
+        with torch.cuda.stream(side):
+            newton_schulz(X.clone(), steps, inner, max_ctas)  # allocates A / B / Y, sets kernel attributes
+        torch.cuda.current_stream(X.device).wait_stream(side)
+        xin, xs = torch.empty_like(X), torch.empty_like(X)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            xs.copy_(xin)  # the chain overwrites its input (ping-pong buffer)
+            out = newton_schulz(xs, steps, inner, max_ctas)
+        entry = work[key] = (graph, xin, out, inner)
+    graph, xin, out, _ = entry
+    xin.copy_(X)
+    graph.replay()
+    return out
+
+
+def orthogonalize(X: torch.Tensor, steps: int = 5, work: Optional[dict] = None, max_ctas: int = 0) -> torch.Tensor:
+    """Newton-Schulz chain, from a captured graph when the matrix is small enough to be launch-bound
+    (both sides at most ``LMMS_B200_MUON_GRAPH_MAX_DIM``, default 2048; 0 turns graphs off)."""
+    small = max(X.shape) <= GRAPH_MAX_DIM
+    native = X.is_cuda and X.dtype == torch.bfloat16 and X.shape[0] % 8 == 0 and X.shape[1] % 8 == 0 and X.is_contiguous()
+    if small and native and work is not None and not torch.cuda.is_current_stream_capturing():
+        return newton_schulz_graphed(X, steps, work, max_ctas)
+    return newton_schulz(X, steps, work, max_ctas)
 
 
 def muon_scale(shape, rms_scale: bool = True) -> float:

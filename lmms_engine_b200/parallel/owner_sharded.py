@@ -317,7 +317,7 @@ class OwnerShardedRuntime:
                 x = torch.empty(s.shape, dtype=torch.bfloat16 if self.P.is_cuda else torch.float32, device=self.device)
                 optim_ops.muon_momentum(mom, self.G[a:b], x.view(-1), lane["sumsq"], beta=cfg["momentum"],
                                         nesterov=cfg["nesterov"], gscale=gscale)
-                o = muon_ops.newton_schulz(x, cfg["ns_steps"], lane["work"], max_ctas=lane["ctas"])
+                o = muon_ops.orthogonalize(x, cfg["ns_steps"], lane["work"], max_ctas=lane["ctas"])
                 optim_ops.muon_update(
                     self.mu_master[a - lo : b - lo], self.P[a:b] if self.needs_master else None, o.reshape(-1),
                     lr=lr, wd=self.weight_decay, scale=muon_ops.muon_scale(s.shape, cfg["rms_scale"]), skip=self._skip,

@@ -271,3 +271,39 @@ def test_plucker_rays_match_reference_formulation():
     assert torch.allclose(out.cpu(), ref, atol=1e-4, rtol=1e-4)
     cf = camera.plucker_rays(K, c2w, H, W, channels_first=True)
     assert torch.equal(cf, out.permute(0, 1, 4, 2, 3))
+
+
+def test_newton_schulz_graph_replay_equals_eager_and_reports_time():
+    """Small matrices run their Newton-Schulz chain from a captured CUDA graph: same result as the eager chain,
+    replay after replay; with ``MUON_GRAPH_TIME`` set the two are timed on a launch-bound size."""
+    import os
+
+    from lmms_engine_b200.ops import muon
+
+    torch.manual_seed(0)
+    work = {}
+    for shape in ((256, 512), (768, 256)):
+        for trial in range(3):
+            x = torch.randn(shape, device="cuda", dtype=torch.bfloat16)
+            x = x / x.float().norm()
+            want = muon.newton_schulz(x.clone(), 5, {}).clone()
+            got = muon.orthogonalize(x.clone(), 5, work)
+            assert ("graph", shape, 5, 0) in work
+            assert torch.equal(got, want), (shape, trial)
+    big = torch.randn(4096, 256, device="cuda", dtype=torch.bfloat16)
+    muon.orthogonalize(big / big.float().norm(), 5, work)
+    assert ("graph", (4096, 256), 5, 0) not in work  # large matrices stay eager
+    if os.environ.get("MUON_GRAPH_TIME"):
+        x = torch.randn(1152, 1152, device="cuda", dtype=torch.bfloat16)
+        x = x / x.float().norm()
+        for name, fn in (("eager", lambda: muon.newton_schulz(x.clone(), 5, work)), ("graph", lambda: muon.orthogonalize(x, 5, work))):
+            for it in range(3):
+                if it == 1:
+                    torch.cuda.synchronize()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                for _ in range(50):
+                    fn()
+            b.record()
+            torch.cuda.synchronize()
+            print(f"MUON_GRAPH_TIME {name}: {a.elapsed_time(b) / 100 * 1000:.1f} us per 1152 x 1152 chain (15 products)", flush=True)
