@@ -110,6 +110,39 @@ def chunk_plan(lengths: List[int], device) -> Tuple[torch.Tensor, torch.Tensor, 
     return (torch.tensor(src, dtype=torch.long, device=device), torch.tensor(back, dtype=torch.long, device=device), reset)
 
 
+class _PaddedGather(torch.autograd.Function):
+    """``cat([x, 0])[fwd]`` whose backward is the gather ``cat([g, 0])[bwd]`` instead of a scatter-add: every
+    real row of ``x`` appears exactly once in ``fwd`` (index ``len(x)`` = the zero row) and ``bwd`` is its inverse."""
+
+    @staticmethod
+    def forward(ctx, x, fwd, bwd):
+        ctx.save_for_backward(fwd, bwd)
+        return torch.cat([x, x.new_zeros((1,) + x.shape[1:])], 0).index_select(0, fwd)
+
+    @staticmethod
+    def backward(ctx, g):
+        fwd, bwd = ctx.saved_tensors
+        return torch.cat([g, g.new_zeros((1,) + g.shape[1:])], 0).index_select(0, bwd), None, None
+
+
+class _Unpad(torch.autograd.Function):
+    """``x[back]`` (drop the padding rows); backward places the rows back with the gather ``cat([g, 0])[src]``."""
+
+    @staticmethod
+    def forward(ctx, x, back, src):
+        ctx.save_for_backward(src)
+        return x.index_select(0, back)
+
+    @staticmethod
+    def backward(ctx, g):
+        (src,) = ctx.saved_tensors
+        return torch.cat([g, g.new_zeros((1,) + g.shape[1:])], 0).index_select(0, src), None, None
+
+
+def _unpad(x, back, src):
+    return _Unpad.apply(x, back, src)
+
+
 def plan_for(ctx, device):
     """``(lengths, pos_in_doc, chunk_plan)`` of a packed context: one host read of the document boundaries per
     forward pass, cached on the context and shared by all layers."""
@@ -137,11 +170,14 @@ def chunk_gated_delta_rule_packed(q, k, v, g, beta, lengths: List[int], plan=Non
     if n == 0:
         return v.new_zeros((T, H, dv))
 
-    def lay(x):  # [T, H, ...] -> [H, n, C, ...] with zero padding rows
-        x = torch.cat([x.float(), x.new_zeros((1,) + x.shape[1:], dtype=torch.float32)], 0).index_select(0, src)
-        return x.view(n, CHUNK, *x.shape[1:]).movedim(2, 0)
+    def lay(x):  # [T, H, ...] -> contiguous fp32 [H, n, C, ...] with zero padding rows
+        # gather in the input dtype (half the bytes for bf16 streams), then one strided copy that also casts
+        x = _PaddedGather.apply(x, src, back)
+        x = x.view(n, CHUNK, *x.shape[1:]).movedim(2, 0)
+        return torch.empty(x.shape, dtype=torch.float32, device=x.device).copy_(x)
 
-    q, k = lay(l2norm(q.float()) * dk ** -0.5), lay(l2norm(k.float()))
+    # padding rows are zero, so normalising after the layout change leaves them zero
+    q, k = l2norm(lay(q)) * dk ** -0.5, l2norm(lay(k))
     v, g, beta = lay(v), lay(g), lay(beta)          # g, beta: [H, n, C]
     vb, kb = v * beta[..., None], k * beta[..., None]
     g = g.cumsum(-1)
@@ -159,8 +195,10 @@ def chunk_gated_delta_rule_packed(q, k, v, g, beta, lengths: List[int], plan=Non
     v_new, o_state = scan(w, u, qt, kt, gamma, reset)
     attn = ((q @ k.transpose(-1, -2)) * decay).masked_fill(strict, 0)
     out = o_state + attn @ v_new                   # [H, n, C, dv]
-    out = out.movedim(0, 2).reshape(n * CHUNK, H, dv)
-    return out.index_select(0, back).to(dt)
+    # back to the stream: cast first (half the bytes for bf16 streams), one strided copy, one gather
+    out = out.to(dt).movedim(0, 2).reshape(n * CHUNK, H, dv)
+    # stream row t sits at padded row back[t]; the gradient of this gather is the gather by ``src`` of [g; 0]
+    return _unpad(out, back, src)
 
 
 def causal_conv_silu_ref(x: torch.Tensor, weight: torch.Tensor, pos_in_doc: torch.Tensor) -> torch.Tensor:
