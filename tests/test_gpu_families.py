@@ -125,3 +125,34 @@ def test_gated_deltanet_matches_library_model_gpu():
     out = json.loads(res.stdout.strip().splitlines()[-1])
     assert out["native_launches"] > 0, "the native kernels did not run"
     assert abs(out["native"] - out["library"]) < 0.03, out
+
+
+def test_qwen3_5_hybrid_step_time_report():
+    """With ``QWEN35_TIME`` set: forward + backward of a four-layer hybrid stack at production head sizes
+    (hidden 2048, 16 key / 32 value heads of 128, gated attention with 16 heads of 128) on 16 384 packed tokens."""
+    import os
+
+    if not os.environ.get("QWEN35_TIME"):
+        pytest.skip("timing report only")
+    from lmms_engine_b200.mapping_func import create_model_from_config
+
+    torch.manual_seed(0)
+    cfg = dict(vocab_size=32000, hidden_size=2048, intermediate_size=6144, num_hidden_layers=4, num_attention_heads=16,
+               num_key_value_heads=4, head_dim=128, linear_conv_kernel_dim=4, linear_key_head_dim=128, linear_value_head_dim=128,
+               linear_num_key_heads=16, linear_num_value_heads=32, partial_rotary_factor=0.25)
+    model = create_model_from_config("qwen3_5_text", cfg).to("cuda", torch.bfloat16)
+    lengths = [8192, 4096, 2048, 1024, 512, 256, 128, 128]
+    ids = torch.randint(0, 32000, (sum(lengths),), device="cuda")
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0).tolist()), dtype=torch.int32, device="cuda")
+    for it in range(3):
+        if it == 1:
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+        loss = model(input_ids=ids, labels=ids, cu_seqlens=cu)["loss"]
+        loss.backward()
+    b.record()
+    torch.cuda.synchronize()
+    assert torch.isfinite(loss)
+    print(f"QWEN35_TIME 4 layers (3 linear-attention + 1 gated-attention), 16384 tokens: {a.elapsed_time(b) / 2:.1f} ms per forward+backward, "
+          f"peak memory {torch.cuda.max_memory_allocated() / 2**30:.1f} GiB", flush=True)
