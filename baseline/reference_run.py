@@ -46,6 +46,51 @@ def _prepare_imports():
     sys.path.insert(0, os.path.join(HERE, "_ref"))
 
 
+def _assert_patched(model) -> None:
+    """The reference swallows every error of its monkey-patch step and carries on with the
+    plain ``transformers`` model on padded batches with full logits
+    (``train/runner.py:113-126``).  A number from that state is not the reference's
+    rmpad + Liger configuration, so this arm refuses to time it: the checks below look at the
+    reference's own objects after ``runner.build()``
+    (``models/qwen2/monkey_patch.py:62-93``)."""
+    from liger_kernel.transformers.rms_norm import LigerRMSNorm
+    from liger_kernel.transformers.swiglu import LigerSwiGLUMLP
+    from lmms_engine.models.qwen2 import qwen2_ops
+    from transformers.models.qwen2 import modeling_qwen2 as mq
+
+    problems = []
+    if mq.Qwen2Model.forward is not qwen2_ops.model_forward:
+        problems.append("Qwen2Model.forward is not the reference's rmpad model_forward")
+    if mq.Qwen2DecoderLayer.forward is not qwen2_ops.decoder_layer_forward:
+        problems.append("Qwen2DecoderLayer.forward is not the reference's rmpad decoder_layer_forward")
+    if mq.Qwen2Attention.forward is not qwen2_ops.attn_forward:
+        problems.append("Qwen2Attention.forward is not the reference's rmpad attn_forward")
+    fwd = mq.Qwen2ForCausalLM.forward
+    if getattr(getattr(fwd, "__wrapped__", fwd), "__name__", "") != "qwen2_lce_forward":
+        problems.append("Qwen2ForCausalLM.forward is not the reference's qwen2_lce_forward (fused linear + CE)")
+    layer = model.model.layers[0]
+    if layer.mlp.forward.__func__ is not LigerSwiGLUMLP.forward:
+        problems.append("decoder MLP instances do not run LigerSwiGLUMLP.forward")
+    if layer.input_layernorm.forward.__func__ is not LigerRMSNorm.forward:
+        problems.append("RMSNorm instances do not run LigerRMSNorm.forward")
+    if problems:
+        raise RuntimeError("reference rmpad/Liger patch did not apply: " + "; ".join(problems))
+
+
+def _transformers_compat(model) -> None:
+    """The reference's rmpad forward reads ``decoder_layer.attention_type``
+    (``models/qwen2/qwen2_ops.py:152``), an attribute that ``transformers`` 4.5x set on every
+    ``Qwen2DecoderLayer`` and that the installed 5.x no longer sets (it indexes
+    ``config.layer_types`` instead), although the reference declares ``transformers < 5.9`` as
+    supported.  The attribute is restored on the model instance, with the value the older
+    library gave it, so that the reference's own code runs unchanged."""
+    cfg = model.config
+    types = getattr(cfg, "layer_types", None) or ["full_attention"] * cfg.num_hidden_layers
+    for i, layer in enumerate(model.model.layers):
+        if not hasattr(layer, "attention_type"):
+            layer.attention_type = types[i]
+
+
 def main(args):
     import numpy as np
     import torch
@@ -138,7 +183,7 @@ def main(args):
     model_cfg = dict(MODEL_7B)
     if args.layers:
         model_cfg["num_hidden_layers"] = args.layers
-    out_dir = os.path.join(ROOT, "gpurun_out", "ref_out")
+    out_dir = os.path.join(args.out_dir, "reference")
     cfg = {
         "trainer_type": "fsdp2_trainer" if args.adamw else "fsdp2_trainer_muon_bench",
         "dataset_config": {"dataset_type": "synthetic_packed_bench", "dataset_format": "json", "processor_config": {"processor_name": "none", "processor_type": "pure_text"},
@@ -148,13 +193,15 @@ def main(args):
         "trainer_args": dict(
             output_dir=out_dir, max_steps=10**6, learning_rate=2e-4, weight_decay=0.01, per_device_train_batch_size=1,
             bf16=True, logging_steps=10**6, save_strategy="no", lr_scheduler_type="constant", max_grad_norm=1.0,
-            use_liger_kernel=True, use_rmpad=True, fsdp2=True, gradient_checkpointing=bool(args.ref_checkpointing),
+            use_liger_kernel=True, use_rmpad=True, fsdp2=True, gradient_checkpointing=bool(args.checkpointing),
             fsdp_config={"transformer_layer_cls_to_wrap": ["Qwen2DecoderLayer"], "reshard_after_forward": False},
             report_to="none", seed=0, dataloader_pin_memory=True, dataloader_num_workers=0,
         ),
     }
     runner = create_train_task(cfg)
     runner.build()
+    _assert_patched(runner.model)
+    _transformers_compat(runner.model)
     tr = runner.trainer
     tr.prepare_model()
     loader = tr.prepare_dataloader(tr.train_dataset, is_training=True)
@@ -223,7 +270,7 @@ def main(args):
             "config": {"model": "Qwen2.5-7B-style via transformers Qwen2ForCausalLM + reference rmpad/Liger patches",
                        "global_batch": tokens * world, "seq_len": tokens, "parallelism": f"dp{world} (reference fsdp2_trainer, FSDP2)",
                        "optimizer": "adamw" if args.adamw else "muon+adamw (reference Muon class)",
-                       "gradient_checkpointing": bool(args.ref_checkpointing), "layers": model_cfg["num_hidden_layers"]},
+                       "gradient_checkpointing": bool(args.checkpointing), "layers": model_cfg["num_hidden_layers"]},
             "clocks": clocks,
             "e2e": {"value": total / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},

@@ -48,8 +48,38 @@ class PermissiveModule(types.ModuleType):
         return cls
 
 
+class _SubmoduleFinder:
+    """Makes ``import pkg.any.sub.module`` succeed for every stand-in package, so that a
+    third-party library which probes one of them (Liger imports ``peft.utils.other`` when it
+    sees a ``peft`` module) does not fail on a submodule nobody listed."""
+
+    roots: set = set()
+
+    @classmethod
+    def find_spec(cls, fullname, path=None, target=None):
+        from importlib.machinery import ModuleSpec
+
+        if fullname.split(".", 1)[0] not in cls.roots or fullname in sys.modules:
+            return None
+        return ModuleSpec(fullname, cls, is_package=True)
+
+    @staticmethod
+    def create_module(spec):
+        m = PermissiveModule(spec.name)
+        m.__path__ = []
+        return m
+
+    @staticmethod
+    def exec_module(module):
+        pass
+
+
 def install(name, submodules=(), attrs=None):
     from importlib.machinery import ModuleSpec
+
+    _SubmoduleFinder.roots.add(name)
+    if _SubmoduleFinder not in sys.meta_path:
+        sys.meta_path.append(_SubmoduleFinder)
 
     mod = PermissiveModule(name)
     mod.__path__ = []  # behaves as a package

@@ -21,6 +21,7 @@ import os
 import statistics
 import subprocess
 import sys
+import tempfile
 import threading
 import time
 
@@ -107,7 +108,7 @@ def build_config(args, out_dir):
             output_dir=out_dir, max_steps=10**9, learning_rate=2e-4, weight_decay=0.01, per_device_train_batch_size=1,
             bf16=True, logging_steps=10**9, save_strategy="no", lr_scheduler_type="constant", use_muon=not args.adamw,
             max_grad_norm=1.0, sharding_runtime=args.runtime, seed=0, dataloader_pin_memory=True,
-            gradient_checkpointing=bool(args.checkpointing), sp_ulysses_degree=args.sp,
+            gradient_checkpointing=bool(args.checkpointing), sp_ulysses_degree=args.sp, ddp_timeout=300,
         ),
     }
 
@@ -128,7 +129,7 @@ def run_ours(args):
 
     if args.linear_backend:
         gemm_ops.LINEAR_BACKEND = args.linear_backend
-    runner = create_train_task(build_config(args, os.path.join(ROOT, "gpurun_out", "bench_out"))).build()
+    runner = create_train_task(build_config(args, os.path.join(args.out_dir, "ours"))).build()
     tr = runner.trainer
     with torch.device("cpu"):
         pass
@@ -209,7 +210,7 @@ def run_ours(args):
                                        f"dp{world // args.sp} x ulysses{args.sp} ({tr.runtime_kind} runtime; not the headline layout)"), "optimizer": "adamw" if args.adamw else "muon+adamw",
                        "l2": "inputs and weights larger than L2 every step (15 GB of parameters)",
                        "layers": build_config(args, "x")["model_config"]["load_from_config"]["config"]["num_hidden_layers"],
-                       "linear_backend": gemm_ops.LINEAR_BACKEND},
+                       "linear_backend": gemm_ops.LINEAR_BACKEND, "gradient_checkpointing": bool(args.checkpointing)},
             "clocks": clocks, "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
             "gpu_launches": launches, "tokens_per_gpu_per_s": value / world,
@@ -237,10 +238,11 @@ def main():
     ap.add_argument("--adamw", action="store_true", help="AdamW only (not the headline config)")
     ap.add_argument("--runtime", default="native", choices=["native", "torch_fsdp2", "auto"])
     ap.add_argument("--linear-backend", default=None, choices=[None, "tcgen05", "cublas"])
-    ap.add_argument("--checkpointing", type=int, default=0)
+    ap.add_argument("--checkpointing", type=int, default=0,
+                    help="gradient checkpointing, the same setting for both arms")
     ap.add_argument("--sp", type=int, default=1, help="Ulysses degree (not the headline layout; sequence = tokens * sp)")
-    ap.add_argument("--ref-checkpointing", type=int, default=1,
-                    help="reference arm: gradient checkpointing as in its examples/qwen2_5_llm config")
+    ap.add_argument("--out-dir", default=os.path.join(tempfile.gettempdir(), "lmms_engine_b200_bench"),
+                    help="trainer output directory (nothing is saved there during the timed steps)")
     args = ap.parse_args()
     sys.stdout.flush()
     os.environ["BENCH_JSON_FD"] = str(os.dup(1))

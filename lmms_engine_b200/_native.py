@@ -11,9 +11,12 @@ libraries), so there is nothing to cite here.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
+import fcntl
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import threading
@@ -57,10 +60,28 @@ def host_sources() -> List[Path]:
     return sorted((CSRC / "host").glob("*.cpp"))
 
 
+_INCLUDE = re.compile(r'^\s*#\s*include\s+"([^"]+)"', re.M)
+
+
+def _local_includes(path: Path, seen: set) -> None:
+    """Headers of this tree that ``path`` includes, transitively."""
+    for name in _INCLUDE.findall(path.read_text(errors="ignore")):
+        for base in (path.parent, CSRC):
+            hdr = (base / name).resolve()
+            if hdr.exists() and hdr not in seen:
+                seen.add(hdr)
+                _local_includes(hdr, seen)
+                break
+
+
 def _digest(src: Path) -> str:
+    """Hash of a source file and of the in-tree headers it pulls in: a library is rebuilt when one of them changes."""
     h = hashlib.sha1()
     h.update(src.read_bytes())
-    for hdr in sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")):
+    seen: set = set()
+    _local_includes(src, seen)
+    for hdr in sorted(seen):
+        h.update(hdr.name.encode())
         h.update(hdr.read_bytes())
     return h.hexdigest()
 
@@ -77,9 +98,26 @@ def _stale(src: Path) -> bool:
     return stamp.read_text().strip() != _digest(src)
 
 
-def _compile(src: Path, verbose: bool = False) -> str:
+@contextlib.contextmanager
+def _build_lock(name: str):
+    """Inter-process lock for one library: under ``torchrun`` every rank may find the same
+    library stale at the same moment; only one of them compiles, the others wait and then
+    see the fresh stamp."""
     LIBDIR.mkdir(exist_ok=True)
-    out = _lib_path(src.stem)
+    with open(LIBDIR / f".{name}.lock", "w") as fh:
+        fcntl.flock(fh, fcntl.LOCK_EX)
+        try:
+            yield
+        finally:
+            fcntl.flock(fh, fcntl.LOCK_UN)
+
+
+def _compile(src: Path, verbose: bool = False) -> str:
+    """Compile to a temporary file and rename it into place, so that a process that is
+    loading the library never sees a half-written file."""
+    LIBDIR.mkdir(exist_ok=True)
+    final = _lib_path(src.stem)
+    out = final.with_name(f".{final.name}.{os.getpid()}.tmp")
     if src.suffix == ".cu":
         nvcc = _nvcc()
         if nvcc is None:
@@ -92,9 +130,21 @@ def _compile(src: Path, verbose: bool = False) -> str:
         cmd = ["g++", *GXX_FLAGS, "-I", str(CSRC), "-o", str(out), str(src)]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
+        with contextlib.suppress(FileNotFoundError):
+            out.unlink()
         raise RuntimeError(f"build of {src.name} failed:\n{res.stdout}\n{res.stderr}")
-    out.with_suffix(".sha1").write_text(_digest(src))
+    os.replace(out, final)
+    stamp_tmp = final.with_name(f".{final.stem}.{os.getpid()}.sha1.tmp")
+    stamp_tmp.write_text(_digest(src))
+    os.replace(stamp_tmp, final.with_suffix(".sha1"))
     return res.stderr
+
+
+def _compile_if_stale(src: Path, force: bool = False, verbose: bool = False) -> Optional[str]:
+    with _build_lock(src.stem):
+        if force or _stale(src):
+            return _compile(src, verbose)
+    return None
 
 
 def build_all(force: bool = False, verbose: bool = False) -> List[str]:
@@ -103,10 +153,10 @@ def build_all(force: bool = False, verbose: bool = False) -> List[str]:
     if not todo:
         return []
     with ThreadPoolExecutor(max_workers=min(8, len(todo))) as ex:
-        logs = list(ex.map(lambda s: _compile(s, verbose), todo))
+        logs = list(ex.map(lambda s: _compile_if_stale(s, force, verbose), todo))
     if verbose:
         for s, log in zip(todo, logs):
-            print(f"== {s.name}\n{log}")
+            print(f"== {s.name}\n{log or ''}")
     return [s.stem for s in todo]
 
 
@@ -129,7 +179,7 @@ def lib(name: str) -> ctypes.CDLL:
             if src.suffix == ".cu" and _nvcc() is None and path.exists():
                 pass  # use the shipped binary
             else:
-                _compile(src)
+                _compile_if_stale(src)
         handle = ctypes.CDLL(str(path))
         _loaded[name] = handle
         return handle

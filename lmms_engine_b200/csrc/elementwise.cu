@@ -510,13 +510,17 @@ __global__ void sumsq_finish_kernel(const float* __restrict__ part, float* __res
   if (threadIdx.x == 0) out[0] = accumulate ? out[0] + acc : acc;
 }
 // From the global sum of squares: norm, clip coefficient min(1, max_norm/(norm+1e-6)),
-// and a skip flag when the norm is not finite.  No host round trip.
+// and a skip flag when the norm is not finite or a kernel of this device has raised the status
+// word (a bounded wait that ran out: the gradients of this step may be incomplete).  No host
+// round trip.
 __global__ void clip_coef_kernel(const float* __restrict__ sumsq, float* __restrict__ norm_out,
-                                 float* __restrict__ coef_out, int* __restrict__ skip_out, float max_norm) {
+                                 float* __restrict__ coef_out, int* __restrict__ skip_out, float max_norm,
+                                 const int* __restrict__ status) {
   const float norm = sqrtf(*sumsq);
   *norm_out = norm;
   const bool finite = isfinite(norm);
-  *skip_out = finite ? 0 : 1;
+  const bool faulted = status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0;
+  *skip_out = (finite && !faulted) ? 0 : 1;
   float c = 1.f;
   if (max_norm > 0.f && finite) c = fminf(1.f, max_norm / (norm + 1e-6f));
   *coef_out = c;
@@ -803,9 +807,9 @@ int b200_sumsq(const void* g, int g_is_fp32, long n, void* part, void* out, int 
   return CHECK_LAUNCH();
 }
 int b200_clip_coef(const void* sumsq, void* norm_out, void* coef_out, void* skip_out, float max_norm,
-                   cudaStream_t st) {
+                   const void* status, cudaStream_t st) {
   clip_coef_kernel<<<1, 1, 0, st>>>((const float*)sumsq, (float*)norm_out, (float*)coef_out, (int*)skip_out,
-                                    max_norm);
+                                    max_norm, (const int*)status);
   return CHECK_LAUNCH();
 }
 int b200_scale(void* g, int g_is_fp32, long n, const void* coef, cudaStream_t st) {

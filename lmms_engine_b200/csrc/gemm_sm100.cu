@@ -740,6 +740,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+}  // namespace b200
+
+#include "gemm2_sm100.cuh"
+
+namespace b200 {
+
 // ---------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -877,6 +883,60 @@ static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMa
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
+// 0: one-CTA tiles only; 1: CTA-pair tiles wherever the shape allows (default)
+static int g_pair_mode = 1;
+static int g_pair_clusters = -1;
+
+template <int EPI>
+static int max_pair_clusters() {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(2, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kSmem2Bytes;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, gemm2_bf16_kernel<EPI>, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+// One 256 x 256 tile per CTA pair; p.n_tiles_m counts 256-row blocks here.
+template <int EPI>
+static int launch2(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const CUtensorMap& tC,
+                   const CUtensorMap& tC2, const CUtensorMap& tC3, const GemmParams& p, int max_ctas,
+                   cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm2_bf16_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2Bytes);
+    if (e != cudaSuccess) return -3;
+    attr_set = true;
+  }
+  if (g_pair_clusters < 0) {
+    // the pairs are persistent: launch no more than can be resident at once
+    g_pair_clusters = max_pair_clusters<EPI>();
+    if (g_pair_clusters <= 0) return -5;
+  }
+  int pairs = g_pair_clusters;
+  if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
+  const int tiles = p.n_tiles_m * p.n_tiles_n;
+  if (tiles < pairs) pairs = tiles;
+  if (pairs <= 0) return 0;
+  GemmParams pp = p;
+  if (pp.group_m <= 0) pp.group_m = g_group_m;
+  gemm2_bf16_kernel<EPI><<<2 * pairs, kThreads, kSmem2Bytes, stream>>>(tA, tB, tB2, tC, tC2, tC3, pp);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+static bool pair_shape_ok(int M, int N) { return g_pair_mode != 0 && M > 128 && N >= 128; }
+
 }  // namespace b200
 
 using namespace b200;
@@ -895,6 +955,34 @@ int b200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, i
   int rc = 0;
   int a3d = a_mn_major && (M % 64 == 0) && (lda >= M);
   int b3d = b_mn_major && (N % 64 == 0) && (ldb >= N);
+  if (pair_shape_ok(M, N) && (!symmetric || M == N)) {
+    // CTA-pair tiles: every CTA stages 128 rows of each operand
+    if (a3d && make_map_mn3d(&tA, A, K, M, lda, 2) != 0) a3d = 0;
+    if (b3d && make_map_mn3d(&tB, B, K, N, ldb, 2) != 0) b3d = 0;
+    if (!a_mn_major) rc |= make_map(&tA, A, M, K, lda, BK, 128, true);
+    else if (!a3d) rc |= make_map(&tA, A, K, M, lda, 64, BK, true);
+    if (!b_mn_major) rc |= make_map(&tB, B, N, K, ldb, BK, 128, true);
+    else if (!b3d) rc |= make_map(&tB, B, K, N, ldb, 64, BK, true);
+    rc |= make_map(&tC, C, M, N, ldc, 64, 32, true);
+    if (rc != 0) return rc;
+    GemmParams p{};
+    p.M = M; p.N = N; p.K = K;
+    p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
+    p.a_mn3d = a3d; p.b_mn3d = b3d;
+    p.alpha = alpha; p.beta = beta;
+    p.bias = symmetric ? nullptr : static_cast<const __nv_bfloat16*>(bias);
+    p.cin = static_cast<const __nv_bfloat16*>(cin);
+    p.ldcin = ldcin;
+    p.n_tiles_m = (M + kTile2M - 1) / kTile2M;
+    p.n_tiles_n = (N + BN - 1) / BN;
+    p.status = status;
+    if (symmetric) {
+      p.cmirror = static_cast<__nv_bfloat16*>(C);
+      p.ldc = ldc;
+      return launch2<EPI_SYMM>(tA, tB, tB, tC, tC, tC, p, max_ctas, stream);
+    }
+    return launch2<EPI_PLAIN>(tA, tB, tB, tC, tC, tC, p, max_ctas, stream);
+  }
   // the one-box fetch is an optimisation: if the driver rejects the 3-D view, use 2-D boxes
   if (a3d && make_map_mn3d(&tA, A, K, M, lda, BM / 64) != 0) a3d = 0;
   if (b3d && make_map_mn3d(&tB, B, K, N, ldb, BN / 64) != 0) b3d = 0;
@@ -1052,6 +1140,7 @@ int b200_gemm_swiglu_bf16(const void* X, const void* Wg, const void* Wu, void* H
   if ((ldx | ldw | ldh) & 7) return -10;
   CUtensorMap tA, tB, tB2, tC, tC2, tC3;
   int rc = 0;
+  const bool pair = pair_shape_ok(M, I);
   rc |= make_map(&tA, X, M, K, ldx, BK, BM, true);
   rc |= make_map(&tB, Wg, I, K, ldw, BK, 128, true);
   rc |= make_map(&tB2, Wu, I, K, ldw, BK, 128, true);
@@ -1062,10 +1151,11 @@ int b200_gemm_swiglu_bf16(const void* X, const void* Wg, const void* Wu, void* H
   GemmParams p{};
   p.M = M; p.N = I; p.K = K;
   p.alpha = 1.f;
-  p.n_tiles_m = (M + BM - 1) / BM;
+  p.n_tiles_m = pair ? (M + kTile2M - 1) / kTile2M : (M + BM - 1) / BM;
   p.n_tiles_n = (I + 127) / 128;
   p.store_gu = store_gu;
   p.status = status;
+  if (pair) return launch2<EPI_SWIGLU>(tA, tB, tB2, tC, tC2, tC3, p, 0, stream);
   return launch<EPI_SWIGLU>(tA, tB, tB2, tC, tC2, tC3, p, 0, stream);
 }
 
@@ -1077,17 +1167,19 @@ int b200_gemm_stats_bf16(const void* X, const void* W, void* logits, void* stats
   if ((ldx | ldw | ldc) & 7) return -10;
   CUtensorMap tA, tB, tC;
   int rc = 0;
+  const bool pair = pair_shape_ok(M, N);
   rc |= make_map(&tA, X, M, K, ldx, BK, BM, true);
-  rc |= make_map(&tB, W, N, K, ldw, BK, BN, true);
+  rc |= make_map(&tB, W, N, K, ldw, BK, pair ? 128 : BN, true);
   rc |= make_map(&tC, logits, M, N, ldc, 64, 32, true);
   if (rc != 0) return rc;
   GemmParams p{};
   p.M = M; p.N = N; p.K = K;
   p.alpha = alpha;
   p.stats = static_cast<float2*>(stats);
-  p.n_tiles_m = (M + BM - 1) / BM;
+  p.n_tiles_m = pair ? (M + kTile2M - 1) / kTile2M : (M + BM - 1) / BM;
   p.n_tiles_n = (N + BN - 1) / BN;
   p.status = status;
+  if (pair) return launch2<EPI_STATS>(tA, tB, tB, tC, tC, tC, p, 0, stream);
   return launch<EPI_STATS>(tA, tB, tB, tC, tC, tC, p, 0, stream);
 }
 
@@ -1173,5 +1265,14 @@ int b200_gemm_set_group_m(int g) {
 }
 
 int b200_gemm_tile_n() { return BN; }
+
+// CTA pairs that a pair-kernel launch uses at most (-1 before the first such launch).
+int b200_gemm_pair_clusters() { return g_pair_clusters; }
+
+// 1 (default): 256 x 256 tiles on CTA pairs wherever the shape allows; 0: one-CTA 128 x 256 tiles only.
+int b200_gemm_set_pair_mode(int on) {
+  if (on == 0 || on == 1) g_pair_mode = on;
+  return g_pair_mode;
+}
 
 }  // extern "C"

@@ -82,6 +82,185 @@ __global__ void peer_barrier_kernel(PeerPtrs pads, int n, int self, unsigned int
   }
 }
 
+// ---------------------------------------------------------------- bucketed reduce-to-owner
+// The gradients of one bucket (the parameters of one decoder layer) are final on this rank as soon
+// as its backward has passed the layer.  One launch on a side stream then
+//   1. tells every peer so: pad_r[flag_off + self] = epoch                       (block 0)
+//   2. waits, bounded, until every peer has said the same about this bucket      (every block)
+//   3. pulls the ranges of the bucket that this rank owns from all peers, sums them in fp32 and
+//      writes the sum over its own copy.
+// The backward of the remaining layers keeps running on the main stream meanwhile, so only the
+// last bucket's transfer is exposed.  A rank that owns nothing in a bucket still launches (steps 1-2
+// with an empty range list).  A wait that runs out raises the status word and the kernel carries on
+// with what is there: the optimizer's skip flag reads the same word, so such a step changes nothing.
+constexpr int kMaxRanges = 8;
+struct RangeList {
+  long lo[kMaxRanges];    // first element of the range in the flat buffer
+  long nvec[kMaxRanges];  // 16-byte vectors in the range
+  int n;
+};
+
+template <typename T>
+struct Vec16;
+template <>
+struct Vec16<__nv_bfloat16> {
+  static constexpr int kElems = 8;
+  static __device__ __forceinline__ void add(const uint4& v, float* acc) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(w[j]);
+      acc[2 * j] += f.x;
+      acc[2 * j + 1] += f.y;
+    }
+  }
+  static __device__ __forceinline__ uint4 pack(const float* acc, float scale) {
+    return make_uint4(pack_bf16x2(acc[0] * scale, acc[1] * scale), pack_bf16x2(acc[2] * scale, acc[3] * scale),
+                      pack_bf16x2(acc[4] * scale, acc[5] * scale), pack_bf16x2(acc[6] * scale, acc[7] * scale));
+  }
+};
+template <>
+struct Vec16<float> {
+  static constexpr int kElems = 4;
+  static __device__ __forceinline__ void add(const uint4& v, float* acc) {
+    acc[0] += __uint_as_float(v.x);
+    acc[1] += __uint_as_float(v.y);
+    acc[2] += __uint_as_float(v.z);
+    acc[3] += __uint_as_float(v.w);
+  }
+  static __device__ __forceinline__ uint4 pack(const float* acc, float scale) {
+    return make_uint4(__float_as_uint(acc[0] * scale), __float_as_uint(acc[1] * scale), __float_as_uint(acc[2] * scale),
+                      __float_as_uint(acc[3] * scale));
+  }
+};
+
+template <typename T>
+__global__ void peer_bucket_reduce_kernel(PeerPtrs grads, PeerPtrs pads, int n, int self, int flag_off,
+                                          unsigned int epoch, RangeList rl, float scale, int* status,
+                                          long long cycle_limit) {
+  const int t = threadIdx.x;
+  if (blockIdx.x == 0 && t < n) {
+    __threadfence_system();
+    unsigned int* remote = static_cast<unsigned int*>(pads.p[t]) + flag_off + self;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  }
+  if (rl.n == 0) return;
+  if (t < n) {
+    const unsigned int* mine = static_cast<const unsigned int*>(pads.p[self]) + flag_off + t;
+    const long long t0 = clock64();
+    unsigned int v = 0;
+    for (;;) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if (static_cast<int>(v - epoch) >= 0) break;
+      if (clock64() - t0 > cycle_limit) {
+        if (status != nullptr) atomicExch(status, kStatusPeerTimeout);
+        break;
+      }
+      __nanosleep(500);
+    }
+  }
+  __syncthreads();
+  long total = 0;
+  for (int r = 0; r < rl.n; ++r) total += rl.nvec[r];
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + t; i < total; i += static_cast<long>(gridDim.x) * blockDim.x) {
+    long j = i;
+    int r = 0;
+    while (j >= rl.nvec[r]) {
+      j -= rl.nvec[r];
+      ++r;
+    }
+    const long off = rl.lo[r] + j * Vec16<T>::kElems;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    uint4 v[kMaxPeers > 8 ? 8 : kMaxPeers];
+    // issue the loads of up to eight peers before the first add: eight 16-byte requests in flight per thread
+    for (int r0 = 0; r0 < n; r0 += 8) {
+      const int m = min(8, n - r0);
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        if (q < m) {
+          const int src = (self + r0 + q) % n;  // a different first peer on every rank spreads the load over the links
+          v[q] = *reinterpret_cast<const uint4*>(static_cast<const T*>(grads.p[src]) + off);
+        }
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        if (q < m) Vec16<T>::add(v[q], acc);
+    }
+    *reinterpret_cast<uint4*>(static_cast<T*>(grads.p[self]) + off) = Vec16<T>::pack(acc, scale);
+  }
+}
+
+// ---------------------------------------------------------------- owner update + publish in one pass
+// AdamW on the slice of the flat buffers that this rank owns; the new bf16 value of every element is
+// stored into ALL replicas (this rank's included) from the same registers, so no separate publish
+// pass reads the parameters again.  `p32`, `m`, `v` are the owner's fp32 slices (element 0 = flat
+// element `lo`); `g` is the reduced gradient at flat element `lo`.  n % 8 == 0, lo % 8 == 0.
+template <typename GT>
+__global__ void peer_adamw_kernel(PeerPtrs params, int n_ranks, int self, long lo, float* __restrict__ p32,
+                                  float* __restrict__ m, float* __restrict__ v, const GT* __restrict__ g, long n8,
+                                  float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2,
+                                  const float* gscale, const int* skip) {
+  if (skip != nullptr && *skip) return;
+  const float gs = gscale != nullptr ? *gscale : 1.f;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    float gi[8], out[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) gi[j] = static_cast<float>(g[i * 8 + j]) * gs;
+    float4 pa = reinterpret_cast<float4*>(p32)[2 * i], pb = reinterpret_cast<float4*>(p32)[2 * i + 1];
+    float4 ma = reinterpret_cast<float4*>(m)[2 * i], mb = reinterpret_cast<float4*>(m)[2 * i + 1];
+    float4 va = reinterpret_cast<float4*>(v)[2 * i], vb = reinterpret_cast<float4*>(v)[2 * i + 1];
+    float pv[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
+    float mv[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w};
+    float vv[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      mv[j] = beta1 * mv[j] + (1.f - beta1) * gi[j];
+      vv[j] = beta2 * vv[j] + (1.f - beta2) * gi[j] * gi[j];
+      float pi = pv[j] * (1.f - lr * wd);
+      pi -= lr * (mv[j] / bc1) / (sqrtf(vv[j] / bc2) + eps);
+      pv[j] = pi;
+      out[j] = pi;
+    }
+    reinterpret_cast<float4*>(p32)[2 * i] = make_float4(pv[0], pv[1], pv[2], pv[3]);
+    reinterpret_cast<float4*>(p32)[2 * i + 1] = make_float4(pv[4], pv[5], pv[6], pv[7]);
+    reinterpret_cast<float4*>(m)[2 * i] = make_float4(mv[0], mv[1], mv[2], mv[3]);
+    reinterpret_cast<float4*>(m)[2 * i + 1] = make_float4(mv[4], mv[5], mv[6], mv[7]);
+    reinterpret_cast<float4*>(v)[2 * i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    reinterpret_cast<float4*>(v)[2 * i + 1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
+    const uint4 pk = make_uint4(pack_bf16x2(out[0], out[1]), pack_bf16x2(out[2], out[3]), pack_bf16x2(out[4], out[5]),
+                                pack_bf16x2(out[6], out[7]));
+    for (int r = 0; r < n_ranks; ++r) {
+      const int dst = (self + r) % n_ranks;
+      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[dst]) + lo + i * 8) = pk;
+    }
+  }
+}
+
+// Muon: p = p*(1 - lr*wd) - lr*scale*o on the owner's fp32 master, new bf16 value into all replicas.
+__global__ void peer_muon_update_kernel(PeerPtrs params, int n_ranks, int self, long lo, float* __restrict__ p32,
+                                        const __nv_bfloat16* __restrict__ o, long n8, float lr, float wd, float scale,
+                                        const int* skip) {
+  if (skip != nullptr && *skip) return;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const uint4 ov = reinterpret_cast<const uint4*>(o)[i];
+    const float2 o0 = unpack_bf16x2(ov.x), o1 = unpack_bf16x2(ov.y), o2 = unpack_bf16x2(ov.z), o3 = unpack_bf16x2(ov.w);
+    const float od[8] = {o0.x, o0.y, o1.x, o1.y, o2.x, o2.y, o3.x, o3.y};
+    float4 pa = reinterpret_cast<float4*>(p32)[2 * i], pb = reinterpret_cast<float4*>(p32)[2 * i + 1];
+    float pv[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) pv[j] = pv[j] * (1.f - lr * wd) - lr * scale * od[j];
+    reinterpret_cast<float4*>(p32)[2 * i] = make_float4(pv[0], pv[1], pv[2], pv[3]);
+    reinterpret_cast<float4*>(p32)[2 * i + 1] = make_float4(pv[4], pv[5], pv[6], pv[7]);
+    const uint4 pk = make_uint4(pack_bf16x2(pv[0], pv[1]), pack_bf16x2(pv[2], pv[3]), pack_bf16x2(pv[4], pv[5]),
+                                pack_bf16x2(pv[6], pv[7]));
+    for (int r = 0; r < n_ranks; ++r) {
+      const int dst = (self + r) % n_ranks;
+      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[dst]) + lo + i * 8) = pk;
+    }
+  }
+}
+
 // flags[i] += 1 with release semantics at system scope, one lane per flag: publishes what earlier
 // operations of the stream (copy-engine transfers included) wrote into the peers' memory
 __global__ void peer_signal_kernel(PeerPtrs flags, int n) {
@@ -120,6 +299,87 @@ int b200_peer_publish(const void* const* peer_ptrs, int n, int self, long lo_byt
   long blocks = (c16 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   peer_publish_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(pp, n, self, lo_bytes, c16);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// One bucket of the overlapped reduce-to-owner (see peer_bucket_reduce_kernel).  `ranges` holds n_ranges
+// pairs (first element, element count) of the flat buffer, each a multiple of 16 bytes; `max_blocks`
+// bounds the grid so that the transfer shares the GPU with the backward pass.
+int b200_peer_bucket_reduce(const void* const* grad_ptrs, const void* const* pad_ptrs, int n, int self, int is_fp32,
+                            int flag_off, unsigned int epoch, const long* ranges, int n_ranges, float scale, int* status,
+                            int timeout_ms, int max_blocks, cudaStream_t st) {
+  if (n <= 1) return 0;
+  if (n > kMaxPeers || n_ranges < 0) return -10;
+  PeerPtrs gp{}, pp{};
+  for (int i = 0; i < n; ++i) {
+    gp.p[i] = const_cast<void*>(grad_ptrs[i]);
+    pp.p[i] = const_cast<void*>(pad_ptrs[i]);
+  }
+  const long long limit = static_cast<long long>(timeout_ms) * 1900000LL;
+  const int epv = is_fp32 ? 4 : 8;
+  int done = 0;
+  bool first = true;
+  while (first || done < n_ranges) {
+    RangeList rl{};
+    long total = 0;
+    for (; done < n_ranges && rl.n < kMaxRanges; ++done) {
+      const long lo = ranges[2 * done], cnt = ranges[2 * done + 1];
+      if (cnt <= 0) continue;
+      if ((lo % epv) || (cnt % epv)) return -10;
+      rl.lo[rl.n] = lo;
+      rl.nvec[rl.n] = cnt / epv;
+      total += cnt / epv;
+      ++rl.n;
+    }
+    long blocks = (total + 255) / 256;
+    if (blocks < 1) blocks = 1;
+    if (max_blocks > 0 && blocks > max_blocks) blocks = max_blocks;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (is_fp32)
+      peer_bucket_reduce_kernel<float><<<static_cast<int>(blocks), 256, 0, st>>>(gp, pp, n, self, flag_off, epoch, rl, scale,
+                                                                                status, limit);
+    else
+      peer_bucket_reduce_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, st>>>(gp, pp, n, self, flag_off, epoch, rl,
+                                                                                        scale, status, limit);
+    first = false;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+int b200_peer_adamw(const void* const* param_ptrs, int n, int self, long lo, void* p32, void* m, void* v, const void* g,
+                    int g_is_fp32, long count, float lr, float beta1, float beta2, float eps, float wd, float bc1,
+                    float bc2, const void* gscale, const void* skip, int max_blocks, cudaStream_t st) {
+  if (count <= 0) return 0;
+  if (n > kMaxPeers || (lo % 8) || (count % 8)) return -10;
+  PeerPtrs pp{};
+  for (int i = 0; i < n; ++i) pp.p[i] = const_cast<void*>(param_ptrs[i]);
+  const long n8 = count / 8;
+  long blocks = (n8 + 255) / 256;
+  if (max_blocks > 0 && blocks > max_blocks) blocks = max_blocks;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (g_is_fp32)
+    peer_adamw_kernel<float><<<static_cast<int>(blocks), 256, 0, st>>>(pp, n, self, lo, (float*)p32, (float*)m, (float*)v,
+                                                                       (const float*)g, n8, lr, beta1, beta2, eps, wd, bc1,
+                                                                       bc2, (const float*)gscale, (const int*)skip);
+  else
+    peer_adamw_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, st>>>(
+        pp, n, self, lo, (float*)p32, (float*)m, (float*)v, (const __nv_bfloat16*)g, n8, lr, beta1, beta2, eps, wd, bc1, bc2,
+        (const float*)gscale, (const int*)skip);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+int b200_peer_muon_update(const void* const* param_ptrs, int n, int self, long lo, void* p32, const void* o, long count,
+                          float lr, float wd, float scale, const void* skip, int max_blocks, cudaStream_t st) {
+  if (count <= 0) return 0;
+  if (n > kMaxPeers || (lo % 8) || (count % 8)) return -10;
+  PeerPtrs pp{};
+  for (int i = 0; i < n; ++i) pp.p[i] = const_cast<void*>(param_ptrs[i]);
+  const long n8 = count / 8;
+  long blocks = (n8 + 255) / 256;
+  if (max_blocks > 0 && blocks > max_blocks) blocks = max_blocks;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  peer_muon_update_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(pp, n, self, lo, (float*)p32, (const __nv_bfloat16*)o, n8,
+                                                                    lr, wd, scale, (const int*)skip);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -21,6 +21,9 @@ class MultiModalIterableDataset(DatasetCore, IterableDataset):
     def __init__(self, config):
         super().__init__(config)
         self.cur_idx = 0
+        # set by load_state_dict and cleared by the next __iter__: that pass continues from the
+        # restored cursor, every other pass starts at the beginning of the shard
+        self._resuming = False
         self.dp_rank, self.dp_size = 0, 1
 
     def build(self):
@@ -44,15 +47,20 @@ class MultiModalIterableDataset(DatasetCore, IterableDataset):
 
     def load_state_dict(self, sd: Dict[str, Any]) -> None:
         self.cur_idx = int(sd.get("cur_idx", 0))
+        self._resuming = True
 
     def _my_indices(self) -> List[int]:
+        """Contiguous shard of the shuffled order for this data-parallel rank (the first
+        ``n % dp_size`` ranks hold one record more, so no record is dropped), then a contiguous
+        slice of ``ceil(len / workers)`` records per dataloader worker."""
         n = len(self.order)
-        per = n // self.dp_size
-        mine = self.order[self.dp_rank * per:(self.dp_rank + 1) * per] if self.dp_size > 1 else list(self.order)
+        base, extra = divmod(n, self.dp_size)
+        start = self.dp_rank * base + min(self.dp_rank, extra)
+        mine = self.order[start:start + base + (1 if self.dp_rank < extra else 0)]
         info = get_worker_info()
         if info is not None and info.num_workers > 1:
-            per_w = len(mine) // info.num_workers
-            mine = mine[info.id * per_w:(info.id + 1) * per_w]
+            per_w = -(-len(mine) // info.num_workers)
+            mine = mine[info.id * per_w:min((info.id + 1) * per_w, len(mine))]
         return mine
 
     def __iter__(self) -> Iterator[List[Dict[str, torch.Tensor]]]:
@@ -62,6 +70,9 @@ class MultiModalIterableDataset(DatasetCore, IterableDataset):
         if cfg.packing:
             kw = dict((cfg.extra_kwargs or {}).get("packing_kwargs", {}) or {})
             packer = build_online_packer(cfg.packing_strategy or "first_fit", cfg.packing_length, **kw)
+        if not self._resuming:
+            self.cur_idx = 0
+        self._resuming = False
         pos = self.cur_idx
         while pos < len(mine):
             i = mine[pos]
@@ -79,8 +90,13 @@ class MultiModalIterableDataset(DatasetCore, IterableDataset):
             if n > cfg.packing_length:
                 if cfg.filter_overlong:
                     continue
+                # oversize samples bypass the packer; what it holds goes out first, so the order of
+                # the stream is kept
+                for pack in packer.flush():
+                    self.cur_idx = pos - 1
+                    yield pack
                 self.cur_idx = pos
-                yield [sample]  # oversize samples bypass the packer
+                yield [sample]
                 continue
             for pack in packer.add(sample, n):
                 self.cur_idx = pos - 1 if (cfg.packing_strategy or "first_fit") == "first_fit" else pos

@@ -18,6 +18,8 @@ _SIG: Dict[str, Tuple[str, str]] = {
     "b200_gemm_swiglu_bf16": ("gemm_sm100", "ppppppiiiiiiips"),
     "b200_gemm_stats_bf16": ("gemm_sm100", "ppppiiiiiifps"),
     "b200_gemm_tile_n": ("gemm_sm100", ""),
+    "b200_gemm_set_pair_mode": ("gemm_sm100", "i"),
+    "b200_gemm_pair_clusters": ("gemm_sm100", ""),
     # elementwise
     "b200_num_partials": ("elementwise", ""),
     "b200_norm_fwd": ("elementwise", "ppppppppiiffis"),
@@ -31,7 +33,7 @@ _SIG: Dict[str, Tuple[str, str]] = {
     "b200_muon_update": ("elementwise", "ppplfffps"),
     "b200_ema": ("elementwise", "ppilfs"),
     "b200_sumsq": ("elementwise", "pilppis"),
-    "b200_clip_coef": ("elementwise", "ppppfs"),
+    "b200_clip_coef": ("elementwise", "ppppfps"),
     "b200_scale": ("elementwise", "pilps"),
     "b200_gather_rows": ("elementwise", "ppplis"),
     "b200_scatter_rows": ("elementwise", "ppplis" + ""),
@@ -79,6 +81,9 @@ def status_word(device: torch.device) -> torch.Tensor:
     return t
 
 
+STATUS_NAMES = {1: "a barrier wait timed out", 2: "bad shape", 3: "a wait for a peer GPU timed out", 4: "a receive buffer overflowed"}
+
+
 def check_status(device: Optional[torch.device] = None) -> None:
     """Synchronising check of the kernel status word; raises on a device-side timeout."""
     for idx, t in list(_status.items()):
@@ -87,7 +92,7 @@ def check_status(device: Optional[torch.device] = None) -> None:
         v = int(t.item())
         if v != 0:
             t.zero_()
-            raise RuntimeError(f"native kernel reported status {v} on cuda:{idx} (1 = barrier wait timed out)")
+            raise RuntimeError(f"native kernel reported status {v} on cuda:{idx} ({STATUS_NAMES.get(v, 'unknown')})")
 
 
 def call(name: str, *args) -> None:

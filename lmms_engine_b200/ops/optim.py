@@ -110,11 +110,13 @@ def sumsq_(g: torch.Tensor, out: torch.Tensor, accumulate: bool) -> None:
 
 
 def clip_coef(sumsq, norm_out, coef_out, skip_out, max_norm: float) -> None:
-    """norm = sqrt(sumsq); coef = min(1, max_norm/(norm+1e-6)); skip = !isfinite(norm)."""
+    """norm = sqrt(sumsq); coef = min(1, max_norm/(norm+1e-6)); skip = !isfinite(norm), or a kernel
+    of this device has raised the status word since it was last read (a bounded wait that ran out
+    leaves the step's gradients incomplete: such a step must not update the weights)."""
     if sumsq.is_cuda:
         _cuda.call(
             "b200_clip_coef", sumsq.data_ptr(), norm_out.data_ptr(), coef_out.data_ptr(), skip_out.data_ptr(),
-            float(max_norm), _cuda.stream(),
+            float(max_norm), _cuda.status_word(sumsq.device).data_ptr(), _cuda.stream(),
         )
         return
     norm = float(sumsq.item()) ** 0.5 if sumsq.item() >= 0 else float("nan")

@@ -6,20 +6,27 @@ parameters REPLICATED (no all-gather before forward, no re-gather in backward, n
 on the critical path of the step) and shards what is actually large: fp32 master weights,
 optimizer moments and the optimizer's compute.  One step is
 
-    forward/backward      gradients accumulate in a flat bf16 buffer, no communication
-    reduce-to-owner       every rank receives the mean gradient of the ranges it owns
+    forward/backward      gradients accumulate in a flat buffer (bf16, or fp32 on request)
+    reduce-to-owner       every rank receives the summed gradient of the ranges it owns; with the
+                          peer-memory implementation this happens bucket by bucket (one bucket per
+                          decoder layer) on a side stream WHILE the backward of the earlier layers
+                          is still running, so only the last bucket's transfer is exposed
     norm / clip           sum of squares over owned ranges, one scalar all-reduce
     owner update          AdamW on an even slice of the elementwise region; Muon on WHOLE
                           matrices, spread over ranks by Newton-Schulz cost (LPT)
-    publish               owners write the new bf16 values into every replica
+    publish               owners write the new bf16 values into every replica; with the
+                          peer-memory implementation the update kernels store them into all
+                          replicas themselves, matrix by matrix, next to the Newton-Schulz chains
+                          of the other matrices
 
 Whole-matrix ownership is what Muon needs (Newton-Schulz works on full matrices): the
 reference gathers FSDP shards to ``index % world`` owners and scatters them back with
 NCCL gather/scatter per parameter (src/lmms_engine/utils/muon_utils.py:206-275); here the
 ownership is the sharding itself.  The collective steps go through a ``Comm`` object: the
 default uses torch.distributed (NCCL or gloo); on NVLink systems the peer-memory
-implementation in ``parallel/peer_comm.py`` fuses reduce+momentum and update+publish into
-single kernels that read and write peer memory directly.
+implementation in ``parallel/peer_comm.py`` reads and writes peer memory directly from its own
+kernels (bucketed pull-reduce, update + publish in one kernel).  The Muon momentum is NOT folded
+into the reduce: it needs the clip coefficient, which exists only once every bucket is reduced.
 
 For models too large to replicate, the trainer falls back to stock FSDP2
 (``sharding_runtime: torch_fsdp2``), as the reference does everywhere
@@ -28,9 +35,9 @@ For models too large to replicate, the trainer falls back to stock FSDP2
 from __future__ import annotations
 
 import contextlib
-import os
-
 import math
+import os
+import re
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
@@ -72,6 +79,8 @@ def lpt_assign(costs: Sequence[float], n: int) -> List[int]:
 
 class TorchComm:
     """Collective steps of the runtime on torch.distributed (NCCL / gloo)."""
+
+    supports_overlap = False
 
     def __init__(self, group):
         self.group = group
@@ -205,6 +214,9 @@ class OwnerShardedRuntime:
         # ---- flat buffers and parameter views -------------------------------------------------
         self.P = self.comm.allocate(total, param_dtype, self.device)
         self.G = self.comm.allocate(total, self.grad_dtype, self.device)
+        # gradients accumulate straight into the flat buffer when it has the parameters' dtype; an fp32
+        # buffer under bf16 parameters is fed by a hook that adds each finished gradient and drops it
+        self.bind_grads = self.grad_dtype == param_dtype
         name_to_param = dict(params)
         with torch.no_grad():
             for s in segs:
@@ -212,8 +224,9 @@ class OwnerShardedRuntime:
                 view = self.P[s.offset : s.offset + s.numel].view(s.shape)
                 view.copy_(p.data)
                 p.data = view
-                p.grad = self.G[s.offset : s.offset + s.numel].view(s.shape)
+                p.grad = self.G[s.offset : s.offset + s.numel].view(s.shape) if self.bind_grads else None
         self.params = name_to_param
+        self._build_buckets()
         # replicas must start identical whatever each rank's initialisation did
         self.comm.broadcast_all(self.P, 0)
 
@@ -234,6 +247,108 @@ class OwnerShardedRuntime:
         self._ns_in = None
         self.my_matrices = [s for s in segs if s.kind == "muon" and s.owner == self.rank]
 
+    # ---- gradient buckets ---------------------------------------------------------------------
+    @staticmethod
+    def bucket_key(name: str) -> str:
+        """Parameters of one repeated block (``...layers.12.``) share a bucket; everything else is
+        grouped by its first two name components (embeddings, final norm, output head)."""
+        m = re.match(r"^(.*?\.\d+)\.", name)
+        if m:
+            return m.group(1)
+        return ".".join(name.split(".")[:2])
+
+    def _build_buckets(self) -> None:
+        """Buckets in parameter order; ``bucket_ranges[b][r]`` = ranges of bucket b that rank r owns."""
+        self.overlap = bool(getattr(self.comm, "supports_overlap", False)) and self.n > 1 and self.P.is_cuda \
+            and os.environ.get("LMMS_B200_OVERLAP_REDUCE", "1") != "0"
+        keys: Dict[str, int] = {}
+        self.bucket_of: Dict[str, int] = {}
+        for s in self.segments:
+            self.bucket_of[s.name] = keys.setdefault(self.bucket_key(s.name), len(keys))
+        nb = len(keys)
+        if self.overlap and nb > self.comm.max_buckets:
+            # fold the surplus into the last bucket rather than refuse the model
+            for k in self.bucket_of:
+                self.bucket_of[k] = min(self.bucket_of[k], self.comm.max_buckets - 1)
+            nb = self.comm.max_buckets
+        self.n_buckets = nb
+        self.bucket_size = [0] * nb
+        raw: List[List[List[Tuple[int, int]]]] = [[[] for _ in range(self.n)] for _ in range(nb)]
+        for s in self.segments:
+            b = self.bucket_of[s.name]
+            self.bucket_size[b] += 1
+            lo, hi = s.offset, _round_up(s.offset + s.numel, ALIGN)
+            if s.kind == "muon":
+                raw[b][s.owner].append((lo, hi))
+            else:
+                for r, (a0, a1) in enumerate(self.adam_ranges):
+                    x0, x1 = max(lo, a0), min(hi, a1)
+                    if x1 > x0:
+                        raw[b][r].append((x0, x1))
+        self.bucket_ranges = [[self._merge(rs) for rs in per_rank] for per_rank in raw]
+        self._armed = False
+        self._count = [0] * nb
+        self._fired = [False] * nb
+        self._side = torch.cuda.Stream(device=self.device) if self.overlap else None
+        if self.overlap or not self.bind_grads:
+            for s in self.segments:
+                self.params[s.name].register_post_accumulate_grad_hook(self._make_hook(s))
+
+    @staticmethod
+    def _merge(ranges: List[Tuple[int, int]]) -> List[Tuple[int, int]]:
+        out: List[Tuple[int, int]] = []
+        for lo, hi in sorted(ranges):
+            if out and lo <= out[-1][1]:
+                out[-1] = (out[-1][0], max(out[-1][1], hi))
+            else:
+                out.append((lo, hi))
+        return out
+
+    def _make_hook(self, seg: "Segment"):
+        b = self.bucket_of[seg.name]
+
+        def hook(p):
+            if not self.bind_grads and p.grad is not None:
+                self.G[seg.offset : seg.offset + seg.numel].add_(p.grad.reshape(-1))
+                p.grad = None
+            if self.overlap and self._armed:
+                self._count[b] += 1
+                if self._count[b] == self.bucket_size[b] and not self._fired[b]:
+                    self._fire(b, max_blocks=self.REDUCE_BLOCKS)
+
+        return hook
+
+    REDUCE_BLOCKS = int(os.environ.get("LMMS_B200_REDUCE_BLOCKS", "24"))
+
+    def arm(self) -> None:
+        """Call before the LAST backward of an optimizer step: from then on every bucket is reduced to
+        its owners as soon as its gradients are final, next to the rest of the backward pass."""
+        if self.overlap:
+            self._armed = True
+            self._count = [0] * self.n_buckets
+            self._fired = [False] * self.n_buckets
+
+    def _fire(self, b: int, max_blocks: int) -> None:
+        main = torch.cuda.current_stream(self.device)
+        ev = torch.cuda.Event()
+        ev.record(main)
+        self._side.wait_event(ev)
+        with torch.cuda.stream(self._side):
+            self.comm.bucket_reduce(self.G, b, self.bucket_ranges[b][self.rank], self.step_count + 1, max_blocks)
+        self._fired[b] = True
+
+    def _finish_reduce(self) -> None:
+        """Reduce whatever the backward hooks have not (parameters without a gradient this step, or a
+        step that was not armed) and make the main stream wait for all of it."""
+        for b in range(self.n_buckets):
+            if not self._fired[b]:
+                self._fire(b, max_blocks=0)
+        done = torch.cuda.Event()
+        done.record(self._side)
+        torch.cuda.current_stream(self.device).wait_event(done)
+        self._armed = False
+        self._fired = [False] * self.n_buckets
+
     # ------------------------------------------------------------------------------------
     @property
     def all_ranges(self) -> List[List[Tuple[int, int]]]:
@@ -244,6 +359,8 @@ class OwnerShardedRuntime:
 
     def rebind_grads(self) -> None:
         """Point every ``p.grad`` at its slice of the flat buffer again (after an external ``zero_grad(set_to_none)``)."""
+        if not self.bind_grads:
+            return
         for s in self.segments:
             self.params[s.name].grad = self.G[s.offset : s.offset + s.numel].view(s.shape)
 
@@ -251,8 +368,12 @@ class OwnerShardedRuntime:
     def step(self, lr_factor: float = 1.0) -> torch.Tensor:
         """Reduce, clip, update and publish.  Returns the global gradient norm (device scalar)."""
         comm = self.comm
-        self.step_count += 1
-        comm.reduce_to_owner(self.G, self.all_ranges)
+        if self.overlap:
+            self._finish_reduce()  # buckets were (mostly) reduced during the backward pass
+            self.step_count += 1
+        else:
+            self.step_count += 1
+            comm.reduce_to_owner(self.G, self.all_ranges)
         # gradient of the MEAN loss over ranks; folded into the clip coefficient below
         inv_n = 1.0 / self.n
         first = True
@@ -270,7 +391,10 @@ class OwnerShardedRuntime:
         lr = self.lr * lr_factor
         self._adam_update(lr, gscale)
         self._muon_update(lr, gscale)
-        comm.publish(self.P, self.all_ranges)
+        if self.overlap:
+            comm.barrier()  # every replica is complete, and every peer has finished reading my gradients
+        else:
+            comm.publish(self.P, self.all_ranges)
         self.G.zero_()
         return self._norm
 
@@ -283,11 +407,18 @@ class OwnerShardedRuntime:
             if b <= a:
                 continue
             s = slice(a - lo, b - lo)
+            if self.overlap and self.needs_master:
+                self.comm.adamw_publish(self.P, a, self.ad_master[s], self.ad_m[s], self.ad_v[s], self.G[a:b], lr=lr,
+                                        beta1=self.betas[0], beta2=self.betas[1], eps=self.eps, wd=wd, step=self.step_count,
+                                        gscale=gscale, skip=self._skip)
+                continue
             optim_ops.adamw_step(
                 self.ad_master[s], self.P[a:b] if self.needs_master else None, self.ad_m[s], self.ad_v[s], self.G[a:b],
                 lr=lr, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps, wd=wd, step=self.step_count,
                 gscale=gscale, skip=self._skip,
             )
+            if self.overlap:
+                self.comm.publish_range(self.P, a, b)
 
     def _muon_update(self, lr: float, gscale: torch.Tensor) -> None:
         """Momentum, Newton-Schulz and the update of every matrix this rank owns.
@@ -318,10 +449,20 @@ class OwnerShardedRuntime:
                 optim_ops.muon_momentum(mom, self.G[a:b], x.view(-1), lane["sumsq"], beta=cfg["momentum"],
                                         nesterov=cfg["nesterov"], gscale=gscale)
                 o = muon_ops.orthogonalize(x, cfg["ns_steps"], lane["work"], max_ctas=lane["ctas"])
+                if self.overlap and self.needs_master and s.numel % 8 == 0:
+                    # update + publish in one kernel, on this lane, next to the other lanes' chains
+                    self.comm.muon_update_publish(self.P, a, self.mu_master[a - lo : b - lo], o.reshape(-1), lr=lr,
+                                                  wd=self.weight_decay, scale=muon_ops.muon_scale(s.shape, cfg["rms_scale"]),
+                                                  skip=self._skip, max_blocks=self.PUBLISH_BLOCKS)
+                    if n_l > 1:
+                        x.record_stream(lane["stream"])
+                    continue
                 optim_ops.muon_update(
                     self.mu_master[a - lo : b - lo], self.P[a:b] if self.needs_master else None, o.reshape(-1),
                     lr=lr, wd=self.weight_decay, scale=muon_ops.muon_scale(s.shape, cfg["rms_scale"]), skip=self._skip,
                 )
+                if self.overlap:
+                    self.comm.publish_range(self.P, a, _round_up(b, ALIGN))
                 if n_l > 1:
                     x.record_stream(lane["stream"])
         if n_l > 1:
@@ -329,6 +470,8 @@ class OwnerShardedRuntime:
                 done = torch.cuda.Event()
                 done.record(lane["stream"])
                 main.wait_event(done)
+
+    PUBLISH_BLOCKS = int(os.environ.get("LMMS_B200_PUBLISH_BLOCKS", "32"))
 
     def _muon_lanes(self):
         if self._lanes is None:

@@ -83,6 +83,7 @@ class FSDP2SFTTrainer:
         self.tracking: Optional[Tracking] = None
         self.log_history: List[Dict[str, Any]] = []
         self.enable_perf_metrics = True
+        self._acc_tokens, self._acc_flops, self._acc_t0 = 0.0, 0.0, time.perf_counter()
 
     # ------------------------------------------------------------------ helpers
     @property
@@ -156,6 +157,12 @@ class FSDP2SFTTrainer:
                 fully_shard(module, **kw)
         fully_shard(self.model, **kw)
 
+    def native_grad_dtype(self) -> torch.dtype:
+        """Dtype of the native runtime's flat gradient buffer (accumulation across micro-batches and the
+        cross-rank sum): ``reduce_dtype`` when it asks for fp32, the compute dtype otherwise."""
+        want = str_to_dtype(self.args.reduce_dtype) if self.args.reduce_dtype else None
+        return torch.float32 if want == torch.float32 else self.compute_dtype()
+
     def build_param_groups(self):
         """AdamW groups, or the four Muon/Adam x decay/no-decay groups when ``use_muon``."""
         decay, no_decay, mu = [], [], []
@@ -176,17 +183,27 @@ class FSDP2SFTTrainer:
             group = self.pgm.dp_cp_group if (self.pgm is not None and self.world_size > 1) else None
             comm = None
             if self.device.type == "cuda" and self.world_size > 1 and os.environ.get("LMMS_B200_PEER_COMM", "1") != "0":
-                try:
-                    from ...parallel.peer_comm import PeerComm
+                from ...parallel.peer_comm import PeerComm
 
-                    comm = PeerComm(group, self.device)
-                except Exception as e:  # symmetric memory unavailable: NCCL path
+                # a device-side wait for a peer gives up after the job's collective timeout, like NCCL would
+                timeout_ms = int(max(float(args.ddp_timeout or 1800), 1.0) * 1000)
+                try:
+                    comm = PeerComm(group, self.device, barrier_timeout_ms=timeout_ms)
+                except Exception as e:
+                    # ranks on different hosts (no peer mapping) are a configuration the operator must choose
+                    # on purpose: the NCCL path is a different, slower runtime
+                    if os.environ.get("LMMS_B200_PEER_COMM", "1") != "auto":
+                        raise RuntimeError(
+                            "peer-memory communication could not be set up for the native runtime "
+                            f"({type(e).__name__}: {e}); set LMMS_B200_PEER_COMM=0 to run it on torch.distributed "
+                            "collectives, or LMMS_B200_PEER_COMM=auto to fall back with a warning") from e
                     logger.warning(f"peer-memory communication unavailable ({e}); using torch.distributed collectives")
             self.runtime = OwnerShardedRuntime(
                 self.model, group, lr=args.learning_rate, weight_decay=args.weight_decay,
                 betas=(args.adam_beta1, args.adam_beta2), eps=args.adam_epsilon, max_grad_norm=args.max_grad_norm,
                 use_muon=bool(args.use_muon), muon_momentum=args.muon_momentum, muon_nesterov=args.muon_nesterov,
                 muon_ns_steps=args.muon_ns_steps, param_dtype=self.compute_dtype(), device=self.device, comm=comm,
+                grad_dtype=self.native_grad_dtype(),
             )
             return
         decay, no_decay, mu = self.build_param_groups()
@@ -264,6 +281,8 @@ class FSDP2SFTTrainer:
         args = self.args
         self.model.train()
         loss = self.compute_loss(batch)
+        if do_step and self.runtime is not None:
+            self.runtime.arm()  # this backward finishes the step's gradients: reduce them bucket by bucket as they complete
         (loss / args.gradient_accumulation_steps).backward()
         self.accumulated_grad_steps += 1
         grad_norm = None
@@ -309,17 +328,22 @@ class FSDP2SFTTrainer:
         promised = TrainUtilities.get_device_flops("B")
         sp_tp = self.sp_size * (self.pgm.tp_size if self.pgm is not None else 1)
         mfu = flops / max(step_seconds, 1e-9) / sp_tp / promised if math.isfinite(promised) else 0.0
-        stats = torch.tensor([mfu, ntok, flops], dtype=torch.float64, device=self.device)
+        # tokens and FLOPs of the steps since the last logged one were counted on the host, step by step
+        # (count_step); only the exchange between ranks waits for a logged step
+        acc_tok, acc_flops, acc_s = self._acc_tokens, self._acc_flops, max(time.perf_counter() - self._acc_t0, step_seconds)
+        self._acc_tokens, self._acc_flops, self._acc_t0 = 0.0, 0.0, time.perf_counter()
+        stats = torch.tensor([mfu, ntok, flops, acc_tok, acc_flops], dtype=torch.float64, device=self.device)
         if self.world_size > 1:
-            gathered = torch.empty(self.world_size * 3, dtype=torch.float64, device=self.device)
+            gathered = torch.empty(self.world_size * 5, dtype=torch.float64, device=self.device)
             dist.all_gather_into_tensor(gathered, stats)
-            g = gathered.view(self.world_size, 3)
+            g = gathered.view(self.world_size, 5)
         else:
-            g = stats.view(1, 3)
+            g = stats.view(1, 5)
         toks = g[:, 1] / self.sp_size
         total = float(toks.sum())
-        self.total_tokens += int(total)
-        self.compute_tracker.update(float(g[:, 2].sum()) / sp_tp, int(total), step_seconds)
+        window_tokens = float(g[:, 3].sum()) / self.sp_size
+        self.total_tokens += int(window_tokens)
+        self.compute_tracker.update(float(g[:, 4].sum()) / sp_tp, int(window_tokens), acc_s)
         return {
             "train/mfu": float(g[:, 0].mean()),
             "perf/global_seq_len_avg": float(g[:, 1].mean()),
@@ -330,9 +354,30 @@ class FSDP2SFTTrainer:
             "train/tokens_per_gpu": total / max(step_seconds, 1e-9) / self.world_size,
         }
 
+    def count_step(self, seqlens: List[int]) -> None:
+        """Host-side token and FLOP counters, updated on EVERY optimizer step from lengths the host already
+        knows (no device sync), so that ``logging_steps > 1`` does not undercount what is persisted."""
+        self._acc_tokens += float(sum(seqlens))
+        self._acc_flops += float(self.flops_counter.flops_per_step(seqlens))
+
     def extra_metrics(self) -> Dict[str, Any]:
         """Trainer-specific values merged into every logged step."""
         return {}
+
+    def check_device_status(self, heartbeat=None) -> None:
+        """Read the status word that bounded device-side waits raise (a peer barrier that ran out, a
+        fused collective that gave up).  The step in which it was raised applied no update (the word
+        feeds the optimizer's skip flag), so the weights are intact; training must not go on."""
+        if self.device.type != "cuda":
+            return
+        from ...ops import _cuda
+
+        try:
+            _cuda.check_status(self.device)
+        except RuntimeError as e:
+            if heartbeat is not None:
+                heartbeat.report_error(self.global_step, f"device status: {e}")
+            raise
 
     # ------------------------------------------------------------------ checkpoints
     def _full_model_state(self) -> Dict[str, torch.Tensor]:
@@ -410,6 +455,9 @@ class FSDP2SFTTrainer:
             self.runtime.refresh_master_from_params()
             if saved_w == W and os.path.exists(os.path.join(path, "optimizer", ckpt.rank_file("optimizer", W, r))):
                 self.runtime.load_state_dict(ckpt.load_rank_state(path, "optimizer", "optimizer", W, r))
+            elif not self.args.save_only_model:
+                logger.warning(f"optimizer state of {path} was written by {saved_w} ranks and is not loaded into this "
+                               f"run of {W} ranks: AdamW moments and Muon momentum start from zero")
         else:
             if saved_w != W:
                 raise ValueError(f"torch_fsdp2 checkpoints resume only at the saved world size ({saved_w})")
@@ -553,6 +601,8 @@ class FSDP2SFTTrainer:
                 self.global_step += 1
                 prof.step()
                 mem_prof.step(self.global_step)
+                if self.enable_perf_metrics:
+                    self.count_step(seqlens_acc)
                 log_now = args.logging_steps and self.global_step % max(int(args.logging_steps), 1) == 0
                 if log_now or self.global_step == total_steps:
                     ev_prof.start("training_metrics")
@@ -568,6 +618,7 @@ class FSDP2SFTTrainer:
                         mean_loss = mean_loss.clone()
                         dist.all_reduce(mean_loss, op=dist.ReduceOp.SUM)
                         mean_loss = mean_loss / self.world_size
+                    self.check_device_status(heartbeat)  # the loss read below synchronises anyway
                     metrics = {"train/loss": float(mean_loss), "train/lr": args.learning_rate * self.lr_factor,
                                "train/grad_norm": float(grad_norm) if grad_norm is not None else 0.0}
                     if self.enable_perf_metrics:
@@ -583,6 +634,7 @@ class FSDP2SFTTrainer:
                 seqlens_acc = []
                 ev_prof.flush()
                 if args.save_strategy != "no" and args.save_steps and self.global_step % int(args.save_steps) == 0:
+                    self.check_device_status(heartbeat)  # never write a completion marker over a failed step
                     path = self.save_checkpoints()
                     self.validation_step(path)
                 self._check_eval_results()
@@ -595,10 +647,7 @@ class FSDP2SFTTrainer:
         prof.stop_and_save()
         mem_prof.stop()
         ev_prof.close()
-        if self.device.type == "cuda":
-            from ...ops import _cuda
-
-            _cuda.check_status()
+        self.check_device_status(heartbeat)
         if args.save_strategy != "no" and (not args.save_steps or self.global_step % int(args.save_steps) != 0):
             self.save_checkpoints()
         if self.rank == 0:

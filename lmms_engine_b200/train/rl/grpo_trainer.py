@@ -83,15 +83,28 @@ def grpo_token_loss(logp, old_logp, ref_logp, adv_tok, mask, clip_range: float, 
 
 @torch.no_grad()
 def sample_completions(model, prompts: Sequence[torch.Tensor], max_new_tokens: int, temperature: float,
-                       eos_token_id: Optional[int], generator=None) -> List[torch.Tensor]:
+                       eos_token_id: Optional[int], generator=None, sync_group=None, token_group=None) -> List[torch.Tensor]:
     """Ancestral sampling for a list of prompts, all sequences advanced together as one packed
-    batch per step (no KV cache: rollouts here are short; serving-grade generation is out of scope)."""
+    batch per step (no KV cache: rollouts here are short; serving-grade generation is out of scope).
+
+    ``sync_group``: ranks whose forward passes contain collectives (sharded parameters, sequence
+    parallelism).  They must run the same number of forwards, so the loop ends only when NO rank of
+    the group has an unfinished sequence, and a rank that is done keeps forwarding its (finished)
+    batch; tokens sampled for a finished sequence are dropped.
+    ``token_group``: ranks that hold the SAME prompts (a sequence-parallel group).  The tokens drawn
+    by its first rank are broadcast, so that all of them continue the same text."""
     dev = prompts[0].device
     seqs = [p.clone() for p in prompts]
     done = [False] * len(seqs)
     for _ in range(max_new_tokens):
         live = [i for i, d in enumerate(done) if not d]
-        if not live:
+        if sync_group is not None:
+            flag = torch.tensor([1 if live else 0], dtype=torch.int32, device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=sync_group)
+            if int(flag) == 0:
+                break
+            live = list(range(len(seqs)))  # same shapes of work on every rank
+        elif not live:
             break
         ids = torch.cat([seqs[i] for i in live])
         lens = torch.tensor([seqs[i].numel() for i in live], dtype=torch.int32, device=dev)
@@ -100,7 +113,11 @@ def sample_completions(model, prompts: Sequence[torch.Tensor], max_new_tokens: i
         last = hidden.index_select(0, (cu[1:] - 1).long())
         logits = F.linear(last, model.lm_head.weight).float() / max(temperature, 1e-5)
         nxt = torch.multinomial(torch.softmax(logits, -1), 1, generator=generator).flatten()
+        if token_group is not None:
+            dist.broadcast(nxt, src=dist.get_global_rank(token_group, 0), group=token_group)
         for j, i in enumerate(live):
+            if done[i]:
+                continue
             seqs[i] = torch.cat([seqs[i], nxt[j:j + 1]])
             if eos_token_id is not None and int(nxt[j]) == eos_token_id:
                 done[i] = True
@@ -138,6 +155,9 @@ class GRPOTrainer(FSDP2SFTTrainer):
         self.ref_model = None
         self.enable_perf_metrics = False
         self.rl_metrics: Dict[str, float] = {}
+        if self.num_iterations > 1 and max(int(self.args.gradient_accumulation_steps or 1), 1) > 1:
+            raise ValueError("rl_config.num_iterations > 1 updates the policy several times per batch and cannot be "
+                             "combined with gradient_accumulation_steps > 1")
 
     def prepare_model(self):
         super().prepare_model()
@@ -161,7 +181,15 @@ class GRPOTrainer(FSDP2SFTTrainer):
         model = self.model
         prompts = [p for p in self.prompts_of(batch) for _ in range(self.group_size)]
         model.eval()
-        completions = sample_completions(model, prompts, self.max_new_tokens, self.temperature, self.eos_token_id)
+        sync_group = token_group = None
+        if self.world_size > 1 and dist.is_initialized():
+            if self.sp_size > 1 and self.pgm is not None:
+                token_group = self.pgm.cp_group
+                sync_group = self.pgm.cp_group
+            if getattr(self, "runtime_kind", "native") != "native":
+                sync_group = dist.group.WORLD  # sharded parameters: every forward all-gathers
+        completions = sample_completions(model, prompts, self.max_new_tokens, self.temperature, self.eos_token_id,
+                                         sync_group=sync_group, token_group=token_group)
         rewards = torch.tensor([self.reward_fn(p, c) for p, c in zip(prompts, completions)], dtype=torch.float32, device=self.device)
         adv = group_advantages(rewards, self.group_size)
         ids = torch.cat([torch.cat([p, c]) for p, c in zip(prompts, completions)])
@@ -174,12 +202,19 @@ class GRPOTrainer(FSDP2SFTTrainer):
             ref_logp = packed_logprobs(self.ref_model, ids, cu) if self.ref_model is not None else None
         model.train()
         loss = None
+        grad_norm = None
+        ga = max(int(self.args.gradient_accumulation_steps or 1), 1)
         for _ in range(self.num_iterations):
             logp = packed_logprobs(model, ids, cu)
             loss, kl = grpo_token_loss(logp, old_logp, ref_logp, adv_tok, mask, self.clip_range, self.beta)
-            loss.backward()
-            self.lr_factor = self.current_lr_factor(self.global_step)
-            grad_norm = self.runtime.step(self.lr_factor) if self.runtime is not None else self._torch_step()
+            (loss / ga).backward()
+            self.accumulated_grad_steps += 1
+            # with accumulation the optimizer moves once per ``gradient_accumulation_steps`` batches, in step
+            # with ``global_step`` and the schedule; without it, once per policy iteration
+            if do_step:
+                self.lr_factor = self.current_lr_factor(self.global_step)
+                grad_norm = self.runtime.step(self.lr_factor) if self.runtime is not None else self._torch_step()
+                self.accumulated_grad_steps = 0
         self.rl_metrics = {"rl/reward_mean": float(rewards.mean()), "rl/reward_std": float(rewards.std(unbiased=False)),
                            "rl/completion_len": float(mask.sum() / max(len(prompts), 1)),
                            "rl/kl": float(kl) if kl is not None else 0.0}

@@ -113,6 +113,45 @@ def test_iterable_dataset_packs_shards_and_resumes(tmp_path):
     assert batch["position_ids"][batch["cu_seqlens"][1]] == 0
 
 
+def test_iterable_dataset_second_epoch_and_oversize_order(tmp_path):
+    """A second pass over the dataset (num_workers=0) yields the same packs as the first; a sample longer
+    than the packing length comes out alone, after whatever the packer held before it."""
+    from lmms_engine_b200.datasets.config import DatasetConfig
+    from lmms_engine_b200.datasets import registry  # noqa: F401
+    from lmms_engine_b200.mapping_func import DATASET_MAPPING
+
+    path = tmp_path / "d.jsonl"
+    _write_records(path)
+    cfg = DatasetConfig(dataset_type="vision_iterable", dataset_format="jsonl", dataset_path=str(path),
+                        processor_config={"processor_name": "byte", "processor_type": "qwen2"}, packing=True,
+                        packing_strategy="first_fit", packing_length=512, shuffle=False)
+    ds = DATASET_MAPPING["vision_iterable"](cfg).build()
+    first = [[s["input_ids"].tolist() for s in p] for p in ds]
+    second = [[s["input_ids"].tolist() for s in p] for p in ds]
+    assert len(first) > 0 and first == second
+    # a resumed pass continues from the cursor, the pass after it starts over
+    ds.load_state_dict({"cur_idx": 30})
+    assert sum(len(p) for p in ds) == 10
+    assert sum(len(p) for p in ds) == 40
+    # oversize: with a packing length below the longest record, stream order is preserved
+    lens = [int(s["input_ids"].numel()) for p in DATASET_MAPPING["vision_iterable"](cfg).build() for s in p]
+    cut = sorted(lens)[len(lens) // 2]
+    cfg2 = DatasetConfig(dataset_type="vision_iterable", dataset_format="jsonl", dataset_path=str(path),
+                         processor_config={"processor_name": "byte", "processor_type": "qwen2"}, packing=True,
+                         packing_strategy="first_fit", packing_length=cut, shuffle=False, filter_overlong=False)
+    ds2 = DATASET_MAPPING["vision_iterable"](cfg2).build()
+    out = [int(s["input_ids"].numel()) for p in ds2 for s in p]
+    assert out == lens
+    assert any(len(p) == 1 and p[0]["input_ids"].numel() > cut for p in ds2)
+    # ranks share every record: 40 records over 3 ranks -> 14 + 13 + 13
+    sizes = []
+    for r in range(3):
+        d = DATASET_MAPPING["vision_iterable"](cfg).build()
+        d.dp_rank, d.dp_size = r, 3
+        sizes.append(sum(len(p) for p in d))
+    assert sizes == [14, 13, 13]
+
+
 def test_map_dataset_offline_packing_and_padded_collator(tmp_path):
     from lmms_engine_b200.datasets.config import DatasetConfig
     from lmms_engine_b200.datasets import registry  # noqa: F401

@@ -15,7 +15,19 @@ def _check(out, ref, tol=2e-2):
     assert err / den < tol, f"rel err {err / den:.4f}"
 
 
-SHAPES = [(128, 256, 64), (256, 512, 128), (384, 768, 320), (200, 264, 72), (1024, 3584, 3584), (77, 40, 24)]
+SHAPES = [(128, 256, 64), (256, 512, 128), (384, 768, 320), (200, 264, 72), (1024, 3584, 3584), (4096, 2304, 512),
+          (77, 40, 24)]
+
+
+@pytest.fixture(autouse=True, params=["pair", "single"])
+def tile_mode(request):
+    """Every test runs with 256 x 256 tiles on CTA pairs (the default) and with one-CTA tiles only."""
+    from lmms_engine_b200.ops import _cuda
+
+    set_mode = _cuda.fn("b200_gemm_set_pair_mode")
+    set_mode(1 if request.param == "pair" else 0)
+    yield request.param
+    set_mode(1)
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)

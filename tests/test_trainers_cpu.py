@@ -78,6 +78,16 @@ def test_grpo_trainer_improves_reward_signal(tmp_path):
     assert "rl/reward_mean" in hist[0] and "rl/kl" in hist[0]
 
 
+def test_grpo_trainer_steps_once_per_accumulation_window(tmp_path):
+    """With gradient accumulation the optimizer moves once per window, together with global_step."""
+    hist, runner = _run(tmp_path, "grpo_trainer", "qwen2", TINY_LM, _packed(prompt_len=4), steps=2, gradient_accumulation_steps=2,
+                        rl_config={"group_size": 2, "max_new_tokens": 4, "reward": "length", "beta": 0.0})
+    assert runner.trainer.runtime.step_count == 2
+    with pytest.raises(ValueError, match="num_iterations"):
+        _run(tmp_path, "grpo_trainer", "qwen2", TINY_LM, _packed(prompt_len=4), steps=1, gradient_accumulation_steps=2,
+             rl_config={"group_size": 2, "max_new_tokens": 2, "num_iterations": 2})
+
+
 def test_grpo_math():
     from lmms_engine_b200.train.rl import group_advantages, grpo_token_loss
 
