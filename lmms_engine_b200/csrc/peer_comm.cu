@@ -189,6 +189,113 @@ __global__ void peer_bucket_reduce_kernel(PeerPtrs grads, PeerPtrs pads, int n, 
   }
 }
 
+// ---------------------------------------------------------------- gradient slots of the parameter-sharded runtime
+// Every rank has written the gradients of one block into the same peer-mapped slot.  The owner of a
+// parameter pulls it from all ranks' slots, sums in fp32 and ADDS the sum to its own gradient range
+// (fp32 or bf16).  Flags: `ready` (this rank's slot content is final: raised on every peer, waited for
+// before the pull) and `ack` (this rank no longer reads the peers' slots: raised on every peer by the
+// last block to finish; a rank rewrites a slot only after all acknowledgements of its previous use).
+constexpr int kMaxItems = 16;
+struct ItemList {
+  long slot_off[kMaxItems];  // first element in the slot
+  long own_off[kMaxItems];   // first element in the owner's gradient range
+  long nvec[kMaxItems];      // 16-byte vectors of the slot's dtype
+  int n;
+};
+__device__ unsigned int g_slot_done[64];
+
+template <typename ST, typename OT>
+__global__ void peer_slot_reduce_kernel(PeerPtrs slots, PeerPtrs pads, int n, int self, int ready_off, unsigned int epoch,
+                                        int do_signal, ItemList il, OT* __restrict__ g_own, int* status,
+                                        long long cycle_limit, int do_ack, int ack_off, unsigned int ack_value) {
+  const int t = threadIdx.x;
+  if (do_signal && blockIdx.x == 0 && t < n) {
+    __threadfence_system();
+    unsigned int* remote = static_cast<unsigned int*>(pads.p[t]) + ready_off + self;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  }
+  if (il.n > 0) {
+    if (t < n) {
+      const unsigned int* mine = static_cast<const unsigned int*>(pads.p[self]) + ready_off + t;
+      const long long t0 = clock64();
+      unsigned int v = 0;
+      for (;;) {
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        if (static_cast<int>(v - epoch) >= 0) break;
+        if (clock64() - t0 > cycle_limit) {
+          if (status != nullptr) atomicExch(status, kStatusPeerTimeout);
+          break;
+        }
+        __nanosleep(500);
+      }
+    }
+    __syncthreads();
+    long total = 0;
+    for (int r = 0; r < il.n; ++r) total += il.nvec[r];
+    constexpr int E = Vec16<ST>::kElems;
+    for (long i = blockIdx.x * static_cast<long>(blockDim.x) + t; i < total; i += static_cast<long>(gridDim.x) * blockDim.x) {
+      long j = i;
+      int r = 0;
+      while (j >= il.nvec[r]) {
+        j -= il.nvec[r];
+        ++r;
+      }
+      const long soff = il.slot_off[r] + j * E;
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      uint4 v[8];
+      for (int r0 = 0; r0 < n; r0 += 8) {
+        const int m = min(8, n - r0);
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          if (q < m) v[q] = *reinterpret_cast<const uint4*>(static_cast<const ST*>(slots.p[(self + r0 + q) % n]) + soff);
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          if (q < m) Vec16<ST>::add(v[q], acc);
+      }
+      OT* out = g_own + il.own_off[r] + j * E;
+#pragma unroll
+      for (int e = 0; e < E; ++e) out[e] = static_cast<OT>(static_cast<float>(out[e]) + acc[e]);
+    }
+  }
+  if (do_ack) {
+    // the last block to get here has seen every other block finish its loads
+    __shared__ unsigned int last;
+    __threadfence();
+    __syncthreads();
+    unsigned int* counter = &g_slot_done[(ack_off >> 5) & 63];
+    if (t == 0) last = (atomicAdd(counter, 1u) == gridDim.x - 1) ? 1u : 0u;
+    __syncthreads();
+    if (last) {
+      if (t == 0) *counter = 0;
+      if (t < n) {
+        __threadfence_system();
+        unsigned int* remote = static_cast<unsigned int*>(pads.p[t]) + ack_off + self;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(ack_value) : "memory");
+      }
+    }
+  }
+}
+
+// Wait (bounded) until the n flags pad_self[off .. off + n) have all reached `value`.
+__global__ void peer_wait_flags_kernel(PeerPtrs pads, int n, int self, int off, unsigned int value, int* status,
+                                       long long cycle_limit) {
+  const int t = threadIdx.x;
+  if (t < n) {
+    const unsigned int* mine = static_cast<const unsigned int*>(pads.p[self]) + off + t;
+    const long long t0 = clock64();
+    unsigned int v = 0;
+    for (;;) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if (static_cast<int>(v - value) >= 0) break;
+      if (clock64() - t0 > cycle_limit) {
+        if (status != nullptr) atomicExch(status, kStatusPeerTimeout);
+        break;
+      }
+      __nanosleep(500);
+    }
+  }
+}
+
 // ---------------------------------------------------------------- owner update + publish in one pass
 // AdamW on the slice of the flat buffers that this rank owns; the new bf16 value of every element is
 // stored into ALL replicas (this rank's included) from the same registers, so no separate publish
@@ -343,6 +450,66 @@ int b200_peer_bucket_reduce(const void* const* grad_ptrs, const void* const* pad
                                                                                         scale, status, limit);
     first = false;
   }
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Gradient slot of the parameter-sharded runtime (see peer_slot_reduce_kernel).  `items` holds n_items
+// triples (first element in the slot, first element in g_own, element count); counts are multiples of
+// 8 elements.  Always raises this rank's ready flag and, when done, its acknowledgement.
+int b200_peer_slot_reduce(const void* const* slot_ptrs, const void* const* pad_ptrs, int n, void* g_own, int self,
+                          int slot_is_fp32, int own_is_fp32, int ready_off, const long* items, int n_items,
+                          unsigned int epoch, int* status, int ack_off, unsigned int ack_value, int timeout_ms,
+                          cudaStream_t st) {
+  if (n <= 1) return 0;
+  if (n > kMaxPeers || n_items < 0) return -10;
+  PeerPtrs sp{}, pp{};
+  for (int i = 0; i < n; ++i) {
+    sp.p[i] = const_cast<void*>(slot_ptrs[i]);
+    pp.p[i] = const_cast<void*>(pad_ptrs[i]);
+  }
+  const long long limit = static_cast<long long>(timeout_ms) * 1900000LL;
+  const int epv = slot_is_fp32 ? 4 : 8;
+  int done = 0;
+  bool first = true;
+  while (first || done < n_items) {
+    ItemList il{};
+    long total = 0;
+    for (; done < n_items && il.n < kMaxItems; ++done) {
+      const long so = items[3 * done], oo = items[3 * done + 1], cnt = items[3 * done + 2];
+      if (cnt <= 0) continue;
+      if ((so % epv) || (oo % 4) || (cnt % epv)) return -10;
+      il.slot_off[il.n] = so;
+      il.own_off[il.n] = oo;
+      il.nvec[il.n] = cnt / epv;
+      total += cnt / epv;
+      ++il.n;
+    }
+    const int do_ack = done >= n_items;
+    long blocks = (total + 255) / 256;
+    if (blocks < 1) blocks = 1;
+    if (blocks > 148 * 4) blocks = 148 * 4;
+    const int sig = first ? 1 : 0;
+#define LAUNCH_SLOT(ST, OT)                                                                                             \
+  peer_slot_reduce_kernel<ST, OT><<<static_cast<int>(blocks), 256, 0, st>>>(sp, pp, n, self, ready_off, epoch, sig, il, \
+                                                                            static_cast<OT*>(g_own), status, limit,     \
+                                                                            do_ack, ack_off, ack_value)
+    if (slot_is_fp32 && own_is_fp32) LAUNCH_SLOT(float, float);
+    else if (!slot_is_fp32 && own_is_fp32) LAUNCH_SLOT(__nv_bfloat16, float);
+    else if (!slot_is_fp32 && !own_is_fp32) LAUNCH_SLOT(__nv_bfloat16, __nv_bfloat16);
+    else return -10;
+#undef LAUNCH_SLOT
+    first = false;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+int b200_peer_wait_flags(const void* const* pad_ptrs, int n, int self, int off, unsigned int value, int* status,
+                         int timeout_ms, cudaStream_t st) {
+  if (n <= 1) return 0;
+  if (n > kMaxPeers) return -10;
+  PeerPtrs pp{};
+  for (int i = 0; i < n; ++i) pp.p[i] = const_cast<void*>(pad_ptrs[i]);
+  peer_wait_flags_kernel<<<1, 32, 0, st>>>(pp, n, self, off, value, status, static_cast<long long>(timeout_ms) * 1900000LL);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -174,6 +174,18 @@ class OwnerShardedRuntime:
             params.append((name, p))
         self.device = device or params[0][1].device
 
+        self._plan_and_allocate(params, use_muon, muon_ns_steps, no_decay_patterns)
+        self._build_buckets()
+        self._init_owned_state()
+        f32 = dict(dtype=torch.float32, device=self.device)
+        self._sumsq = torch.zeros(1, **f32)
+        self._norm = torch.zeros(1, **f32)
+        self._coef = torch.ones(1, **f32)
+        self._skip = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def _plan_and_allocate(self, params, use_muon: bool, muon_ns_steps: int, no_decay_patterns) -> None:
+        """Ownership, the flat layout and the flat buffers; binds every parameter to its slice."""
+        param_dtype = self.param_dtype
         muon_idx = [i for i, (nm, p) in enumerate(params) if use_muon and muon_ops.is_muon_param(nm, p)]
         owners = lpt_assign([muon_ops.ns_flops(tuple(params[i][1].shape), muon_ns_steps) for i in muon_idx], self.n)
         owner_of = dict(zip(muon_idx, owners))
@@ -226,26 +238,21 @@ class OwnerShardedRuntime:
                 p.data = view
                 p.grad = self.G[s.offset : s.offset + s.numel].view(s.shape) if self.bind_grads else None
         self.params = name_to_param
-        self._build_buckets()
         # replicas must start identical whatever each rank's initialisation did
         self.comm.broadcast_all(self.P, 0)
 
-        # ---- owned state ------------------------------------------------------------------------
+    def _init_owned_state(self) -> None:
+        """fp32 master weights and optimizer moments of the ranges this rank owns."""
         my_mu, my_ad = self.muon_ranges[self.rank], self.adam_ranges[self.rank]
         self.own_ranges = [my_mu, my_ad]
         f32 = dict(dtype=torch.float32, device=self.device)
-        self.needs_master = param_dtype != torch.float32
+        self.needs_master = self.param_dtype != torch.float32
         self.mu_master = self.P[my_mu[0] : my_mu[1]].float() if self.needs_master else self.P[my_mu[0] : my_mu[1]]
         self.mu_mom = torch.zeros(my_mu[1] - my_mu[0], **f32)
         self.ad_master = self.P[my_ad[0] : my_ad[1]].float() if self.needs_master else self.P[my_ad[0] : my_ad[1]]
         self.ad_m = torch.zeros(my_ad[1] - my_ad[0], **f32)
         self.ad_v = torch.zeros(my_ad[1] - my_ad[0], **f32)
-        self._sumsq = torch.zeros(1, **f32)
-        self._norm = torch.zeros(1, **f32)
-        self._coef = torch.ones(1, **f32)
-        self._skip = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self._ns_in = None
-        self.my_matrices = [s for s in segs if s.kind == "muon" and s.owner == self.rank]
+        self.my_matrices = [s for s in self.segments if s.kind == "muon" and s.owner == self.rank]
 
     # ---- gradient buckets ---------------------------------------------------------------------
     @staticmethod
@@ -357,6 +364,9 @@ class OwnerShardedRuntime:
     def zero_grad(self) -> None:
         self.G.zero_()
 
+    def after_backward(self) -> None:
+        """Called by the trainer after every backward pass (nothing to do when parameters are replicated)."""
+
     def rebind_grads(self) -> None:
         """Point every ``p.grad`` at its slice of the flat buffer again (after an external ``zero_grad(set_to_none)``)."""
         if not self.bind_grads:
@@ -431,6 +441,34 @@ class OwnerShardedRuntime:
         parameters are published."""
         lo, _ = self.muon_ranges[self.rank]
         cfg = self.muon
+
+        def body(s: Segment, lane) -> None:
+            a, b = s.offset, s.offset + s.numel
+            mom = self.mu_mom[a - lo : b - lo]
+            x = torch.empty(s.shape, dtype=torch.bfloat16 if self.P.is_cuda else torch.float32, device=self.device)
+            optim_ops.muon_momentum(mom, self.G[a:b], x.view(-1), lane["sumsq"], beta=cfg["momentum"],
+                                    nesterov=cfg["nesterov"], gscale=gscale)
+            o = muon_ops.orthogonalize(x, cfg["ns_steps"], lane["work"], max_ctas=lane["ctas"])
+            if lane["stream"] is not None:
+                x.record_stream(lane["stream"])
+            if self.overlap and self.needs_master and s.numel % 8 == 0:
+                # update + publish in one kernel, on this lane, next to the other lanes' chains
+                self.comm.muon_update_publish(self.P, a, self.mu_master[a - lo : b - lo], o.reshape(-1), lr=lr,
+                                              wd=self.weight_decay, scale=muon_ops.muon_scale(s.shape, cfg["rms_scale"]),
+                                              skip=self._skip, max_blocks=self.PUBLISH_BLOCKS)
+                return
+            optim_ops.muon_update(
+                self.mu_master[a - lo : b - lo], self.P[a:b] if self.needs_master else None, o.reshape(-1),
+                lr=lr, wd=self.weight_decay, scale=muon_ops.muon_scale(s.shape, cfg["rms_scale"]), skip=self._skip,
+            )
+            if self.overlap:
+                self.comm.publish_range(self.P, a, _round_up(b, ALIGN))
+
+        self._on_lanes(self.my_matrices, body)
+
+    def _on_lanes(self, matrices, body) -> None:
+        """Run ``body(segment, lane)`` for every matrix, dealt round-robin to the lanes' streams; the
+        lanes start after what is queued on the current stream and the current stream waits for them."""
         lanes = self._muon_lanes()
         n_l = len(lanes)
         main = torch.cuda.current_stream() if n_l > 1 else None
@@ -439,32 +477,11 @@ class OwnerShardedRuntime:
             ready.record(main)
             for lane in lanes:
                 lane["stream"].wait_event(ready)
-        for i, s in enumerate(self.my_matrices):
+        for i, s in enumerate(matrices):
             lane = lanes[i % n_l]
-            a, b = s.offset, s.offset + s.numel
-            mom = self.mu_mom[a - lo : b - lo]
             ctx = torch.cuda.stream(lane["stream"]) if n_l > 1 else contextlib.nullcontext()
             with ctx:
-                x = torch.empty(s.shape, dtype=torch.bfloat16 if self.P.is_cuda else torch.float32, device=self.device)
-                optim_ops.muon_momentum(mom, self.G[a:b], x.view(-1), lane["sumsq"], beta=cfg["momentum"],
-                                        nesterov=cfg["nesterov"], gscale=gscale)
-                o = muon_ops.orthogonalize(x, cfg["ns_steps"], lane["work"], max_ctas=lane["ctas"])
-                if self.overlap and self.needs_master and s.numel % 8 == 0:
-                    # update + publish in one kernel, on this lane, next to the other lanes' chains
-                    self.comm.muon_update_publish(self.P, a, self.mu_master[a - lo : b - lo], o.reshape(-1), lr=lr,
-                                                  wd=self.weight_decay, scale=muon_ops.muon_scale(s.shape, cfg["rms_scale"]),
-                                                  skip=self._skip, max_blocks=self.PUBLISH_BLOCKS)
-                    if n_l > 1:
-                        x.record_stream(lane["stream"])
-                    continue
-                optim_ops.muon_update(
-                    self.mu_master[a - lo : b - lo], self.P[a:b] if self.needs_master else None, o.reshape(-1),
-                    lr=lr, wd=self.weight_decay, scale=muon_ops.muon_scale(s.shape, cfg["rms_scale"]), skip=self._skip,
-                )
-                if self.overlap:
-                    self.comm.publish_range(self.P, a, _round_up(b, ALIGN))
-                if n_l > 1:
-                    x.record_stream(lane["stream"])
+                body(s, lane)
         if n_l > 1:
             for lane in lanes:
                 done = torch.cuda.Event()

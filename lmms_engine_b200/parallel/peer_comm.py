@@ -41,9 +41,9 @@ def _ptr_array(ptrs: List[int]):
 
 class PeerComm:
     supports_overlap = True
-    PAD_WORDS = 16384       # [0, 64): barrier slots; then 16 words per bucket flag block
+    PAD_WORDS = 16384       # [0, 64): barrier slots; then 32 words per flag block (16 ready + 16 acknowledgement flags)
     BUCKET_FLAG_BASE = 64
-    BUCKET_FLAG_STRIDE = 16
+    BUCKET_FLAG_STRIDE = 32
     BARRIER_TIMEOUT_MS = 1800 * 1000  # default: the usual collective timeout of a training job
 
     def __init__(self, group, device: torch.device, barrier_timeout_ms: int = 0):

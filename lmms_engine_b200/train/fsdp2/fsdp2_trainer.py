@@ -11,8 +11,10 @@ checkpoint directory layout with rotation and auto-resume, profilers, async eval
 
 What is different by design:
 
-* two sharding runtimes: ``native`` (replicated bf16 weights + owner-sharded optimizer,
-  ``parallel/owner_sharded.py``) and ``torch_fsdp2`` (stock ``fully_shard``, ZeRO-3);
+* three sharding runtimes: ``native`` (replicated bf16 weights + owner-sharded optimizer,
+  ``parallel/owner_sharded.py``), ``native_sharded`` (parameters sharded by owner as well and
+  gathered block by block over peer memory, ``parallel/param_sharded.py``) and ``torch_fsdp2``
+  (stock ``fully_shard``);
 * AdamW **and Muon** are available here (the reference wires Muon only into its HF trainer);
 * the step makes no host round trip: loss, grad-norm, clip coefficient and the skip flag
   stay on the device and are read back only when a step is logged; step time is measured
@@ -98,6 +100,10 @@ class FSDP2SFTTrainer:
     def sp_size(self) -> int:
         return self.pgm.cp_size if self.pgm is not None else 1
 
+    @property
+    def is_native(self) -> bool:
+        return getattr(self, "runtime_kind", None) in ("native", "native_sharded")
+
     def compute_dtype(self) -> torch.dtype:
         if self.args.bf16:
             return torch.bfloat16
@@ -126,7 +132,7 @@ class FSDP2SFTTrainer:
             self.model.sp_group = self.pgm.cp_group
         if getattr(self.model, "vit_frame_parallel", False) and self.pgm is not None and self.world_size > 1:
             self.model.vit_group = self.pgm.dp_cp_group
-        if self.runtime_kind == "native":
+        if self.is_native:
             self.model.to(device=self.device, dtype=dtype)
             return
         # ---- stock FSDP2 (ZeRO-3), also the path for TP / EP / HSDP meshes ------------------
@@ -179,7 +185,7 @@ class FSDP2SFTTrainer:
 
     def prepare_optimizer(self):
         args = self.args
-        if self.runtime_kind == "native":
+        if self.is_native:
             group = self.pgm.dp_cp_group if (self.pgm is not None and self.world_size > 1) else None
             comm = None
             if self.device.type == "cuda" and self.world_size > 1 and os.environ.get("LMMS_B200_PEER_COMM", "1") != "0":
@@ -198,7 +204,10 @@ class FSDP2SFTTrainer:
                             f"({type(e).__name__}: {e}); set LMMS_B200_PEER_COMM=0 to run it on torch.distributed "
                             "collectives, or LMMS_B200_PEER_COMM=auto to fall back with a warning") from e
                     logger.warning(f"peer-memory communication unavailable ({e}); using torch.distributed collectives")
-            self.runtime = OwnerShardedRuntime(
+            runtime_cls = OwnerShardedRuntime
+            if self.runtime_kind == "native_sharded":
+                from ...parallel.param_sharded import ParamShardedRuntime as runtime_cls
+            self.runtime = runtime_cls(
                 self.model, group, lr=args.learning_rate, weight_decay=args.weight_decay,
                 betas=(args.adam_beta1, args.adam_beta2), eps=args.adam_epsilon, max_grad_norm=args.max_grad_norm,
                 use_muon=bool(args.use_muon), muon_momentum=args.muon_momentum, muon_nesterov=args.muon_nesterov,
@@ -266,7 +275,7 @@ class FSDP2SFTTrainer:
 
     # ------------------------------------------------------------------ step
     def compute_loss(self, batch: Dict[str, Any]) -> torch.Tensor:
-        if self.device.type == "cuda" and self.runtime_kind != "native" and self.compute_dtype() != torch.float32:
+        if self.device.type == "cuda" and not self.is_native and self.compute_dtype() != torch.float32:
             with torch.autocast("cuda", dtype=self.compute_dtype()):
                 out = self.model(**batch)
         else:
@@ -284,6 +293,8 @@ class FSDP2SFTTrainer:
         if do_step and self.runtime is not None:
             self.runtime.arm()  # this backward finishes the step's gradients: reduce them bucket by bucket as they complete
         (loss / args.gradient_accumulation_steps).backward()
+        if self.runtime is not None:
+            self.runtime.after_backward()
         self.accumulated_grad_steps += 1
         grad_norm = None
         if do_step:
@@ -383,6 +394,27 @@ class FSDP2SFTTrainer:
     def _full_model_state(self) -> Dict[str, torch.Tensor]:
         return {k: v for k, v in self.model.state_dict().items()}
 
+    def _iter_full_model_state(self):
+        """``(state-dict key, full tensor)`` pairs; tensors of a parameter-sharded runtime are valid only
+        until the next pair is requested."""
+        if hasattr(self.runtime, "full_state_items"):
+            by_param = {id(p): k for k, p in self.model.state_dict(keep_vars=True).items()}
+            aliases: Dict[str, List[str]] = {}
+            for k, p in self.model.state_dict(keep_vars=True).items():
+                aliases.setdefault(by_param[id(p)], []).append(k)
+            params = dict(self.model.named_parameters())
+            seen = set()
+            for name, full in self.runtime.full_state_items():
+                canon = by_param.get(id(params[name]), name)
+                for k in aliases.get(canon, [name]):  # tied weights appear under every one of their keys
+                    seen.add(k)
+                    yield k, full
+            for k, v in self.model.state_dict().items():  # persistent buffers
+                if k not in seen:
+                    yield k, v
+            return
+        yield from self._full_model_state().items()
+
     def save_checkpoints(self, output_dir: Optional[str] = None, step: Optional[int] = None) -> str:
         args = self.args
         step = self.global_step if step is None else step
@@ -390,11 +422,15 @@ class FSDP2SFTTrainer:
         os.makedirs(out, exist_ok=True)
         W, r = self.world_size, self.rank
         ckpt.barrier()
-        if self.runtime_kind == "native":
-            if self.pgm is not None:
-                model_sd = ckpt.shard0_dtensor_state(self._full_model_state(), self.pgm.device_mesh["fsdp"])
-            else:
-                model_sd = {k: v.detach().cpu() for k, v in self._full_model_state().items()}
+        if self.is_native:
+            mesh = self.pgm.device_mesh["fsdp"] if self.pgm is not None else None
+            model_sd = {}
+            # one tensor at a time: a sharded runtime materialises a block's parameters only while they are consumed
+            for name, full in self._iter_full_model_state():
+                if mesh is not None:
+                    model_sd.update(ckpt.shard0_dtensor_state({name: full}, mesh))
+                else:
+                    model_sd[name] = full.detach().cpu().clone()
             opt_sd = self.runtime.state_dict()
         else:
             model_sd = self.model.state_dict()
@@ -445,13 +481,16 @@ class FSDP2SFTTrainer:
     def load_checkpoints(self, path: str) -> None:
         W, r = self.world_size, self.rank
         saved_w = ckpt.saved_world_size(path)
-        if self.runtime_kind == "native":
+        if self.is_native:
             full = ckpt.load_full_model_state(path)
-            own = self.model.state_dict()
-            with torch.no_grad():
-                for k, v in full.items():
-                    if k in own:
-                        own[k].copy_(v.to(own[k].dtype))
+            if hasattr(self.runtime, "load_full_state"):
+                self.runtime.load_full_state(full)
+            else:
+                own = self.model.state_dict()
+                with torch.no_grad():
+                    for k, v in full.items():
+                        if k in own:
+                            own[k].copy_(v.to(own[k].dtype))
             self.runtime.refresh_master_from_params()
             if saved_w == W and os.path.exists(os.path.join(path, "optimizer", ckpt.rank_file("optimizer", W, r))):
                 self.runtime.load_state_dict(ckpt.load_rank_state(path, "optimizer", "optimizer", W, r))

@@ -187,7 +187,7 @@ class GRPOTrainer(FSDP2SFTTrainer):
                 token_group = self.pgm.cp_group
                 sync_group = self.pgm.cp_group
             if getattr(self, "runtime_kind", "native") != "native":
-                sync_group = dist.group.WORLD  # sharded parameters: every forward all-gathers
+                sync_group = dist.group.WORLD  # sharded parameters: every forward gathers them
         completions = sample_completions(model, prompts, self.max_new_tokens, self.temperature, self.eos_token_id,
                                          sync_group=sync_group, token_group=token_group)
         rewards = torch.tensor([self.reward_fn(p, c) for p, c in zip(prompts, completions)], dtype=torch.float32, device=self.device)

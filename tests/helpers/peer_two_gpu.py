@@ -1,8 +1,9 @@
 """Multi-rank check of the peer-memory runtime, one rank per GPU (launched by torchrun).
 
 1. PeerComm.reduce_to_owner / publish against NCCL reduce / broadcast on the same data.
-2. Three optimizer steps of a small decoder with the owner-sharded runtime on PeerComm and on
-   TorchComm: parameters must agree across ranks and across the two implementations.
+2. Three optimizer steps of a small decoder with the owner-sharded runtime on PeerComm (buckets
+   reduced during the backward pass; reduced only at the step; fp32 gradient buffer) and on
+   TorchComm: parameters must agree across ranks and across the implementations.
 NVLS is kept off (plain peer loads and stores only)."""
 import os
 import sys
@@ -52,17 +53,27 @@ def main():
     cfg = DecoderConfig(model_type="qwen2", vocab_size=4096, hidden_size=512, intermediate_size=1408,
                         num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=128)
     results = []
-    for make_comm in (lambda: comm, lambda: TorchComm(dist.group.WORLD)):
+    variants = [("peer, reduce during backward", lambda: comm, True, torch.bfloat16),
+                ("peer, reduce at the step", lambda: comm, False, torch.bfloat16),
+                ("peer, fp32 gradients", lambda: comm, True, torch.float32),
+                ("torch.distributed", lambda: TorchComm(dist.group.WORLD), False, torch.bfloat16)]
+    for label, make_comm, armed, grad_dtype in variants:
         torch.manual_seed(0)
         with torch.device(dev):
             model = DecoderLM(cfg).to(torch.bfloat16)
-        rt = OwnerShardedRuntime(model, dist.group.WORLD, lr=1e-3, weight_decay=0.01, use_muon=True, device=dev, comm=make_comm())
+        rt = OwnerShardedRuntime(model, dist.group.WORLD, lr=1e-3, weight_decay=0.01, use_muon=True, device=dev, comm=make_comm(),
+                                 grad_dtype=grad_dtype)
+        assert rt.overlap == (label.startswith("peer")), label
         torch.manual_seed(7 + rank)
         for step in range(3):
             ids = torch.randint(0, 4096, (1024,), device=dev)
             cu = torch.tensor([0, 300, 1024], dtype=torch.int32, device=dev)
             out = model(input_ids=ids, labels=ids, cu_seqlens=cu)
+            if armed:
+                rt.arm()
             out["loss"].backward()
+            if armed and step == 0:
+                assert all(rt._fired), "every bucket should have been reduced by its backward hook"
             rt.step()
         torch.cuda.synchronize()
         _cuda.check_status()
@@ -71,8 +82,9 @@ def main():
         dist.broadcast(other, src=0)
         assert torch.equal(mine, other), "replicas diverged"
         results.append(mine.float())
-    diff = (results[0] - results[1]).abs().max().item()
+    diff = max((r - results[-1]).abs().max().item() for r in results[:-1])
     assert diff < 2e-2, diff
+    assert torch.equal(results[0], results[1]), "reducing during the backward pass must not change the result"
     if rank == 0:
         print(f"peer runtime ok: world {world}, max param diff peer-vs-nccl {diff:.2e}")
     dist.barrier()

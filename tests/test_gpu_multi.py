@@ -40,6 +40,12 @@ def test_peer_runtime_four_gpus():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_param_sharded_runtime_two_gpus():
+    out = _torchrun("param_sharded_gpu.py", 2)
+    assert "param sharded ok" in out
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_fused_comm_gemms_two_gpus():
     out = _torchrun("fused_comm_run.py", 2)
     assert "fused comm ok" in out
