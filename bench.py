@@ -236,7 +236,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=TOKENS_PER_GPU)
     ap.add_argument("--layers", type=int, default=0, help="debug: fewer layers (invalidates the number)")
     ap.add_argument("--adamw", action="store_true", help="AdamW only (not the headline config)")
-    ap.add_argument("--runtime", default="native", choices=["native", "torch_fsdp2", "auto"])
+    ap.add_argument("--runtime", default="native", choices=["native", "native_sharded", "torch_fsdp2", "auto"])
     ap.add_argument("--linear-backend", default=None, choices=[None, "tcgen05", "cublas"])
     ap.add_argument("--checkpointing", type=int, default=0,
                     help="gradient checkpointing, the same setting for both arms")

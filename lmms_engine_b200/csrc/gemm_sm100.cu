@@ -840,7 +840,7 @@ static int make_map_e3(CUtensorMap* m, const void* ptr, uint64_t E, uint64_t R, 
 }
 
 static int g_num_sms = 0;
-static int g_group_m = 16;
+static int g_group_m = 8;
 
 template <int EPI, int COMM = 0>
 static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const CUtensorMap& tC,
@@ -1258,7 +1258,7 @@ int b200_gemm_grouped_wgrad_bf16(const void* A, const void* B, void* dW, const v
   return launch<EPI_PLAIN>(tA, tB, tB, tC, tC, tC, p, 0, stream);
 }
 
-// Tuning knob: how many m-blocks share a sweep over N (default 16).
+// Tuning knob: how many m-blocks share a sweep over N (default 8).
 int b200_gemm_set_group_m(int g) {
   if (g >= 1 && g <= 1024) g_group_m = g;
   return g_group_m;

@@ -215,6 +215,12 @@ class ParamShardedRuntime(OwnerShardedRuntime):
                     is_block = False
             if is_block:
                 block_of[i] = key
+        stray = [nm for i, (nm, p) in enumerate(params) if i not in block_of and use_muon and muon_ops.is_muon_param(nm, p)]
+        if stray and rank == 0:
+            from ..utils.logging_utils import logger
+
+            logger.warning(f"native_sharded: {len(stray)} Muon-eligible matrices lie outside a repeated block and are updated "
+                           f"with AdamW in the replicated region: {stray[:4]}{' ...' if len(stray) > 4 else ''}")
         sh_idx = [i for i in range(len(params)) if i in block_of]
         mu_idx = [i for i in sh_idx if use_muon and muon_ops.is_muon_param(*params[i])]
         ad_idx = [i for i in sh_idx if i not in set(mu_idx)]
@@ -364,7 +370,9 @@ class ParamShardedRuntime(OwnerShardedRuntime):
         if old is not None:
             self._unbind(old)
         my_lo = {r: self.own_span[r][0] for r in range(self.n)}
-        items = [(s.owner, s.offset - my_lo[s.owner], self._slot_off[s.name], s.numel) for s in self._block_segs[block]]
+        # parameters that this rank owns are used in place (ensure_block binds them to the own range)
+        items = [(s.owner, s.offset - my_lo[s.owner], self._slot_off[s.name], s.numel) for s in self._block_segs[block]
+                 if s.owner != self.rank or not self.sc.peer]
         if self._prefetch is not None:
             with torch.cuda.stream(self._prefetch):
                 if self._w_free[j] is not None:
@@ -399,9 +407,13 @@ class ParamShardedRuntime(OwnerShardedRuntime):
         if self._w_ready[j] is not None:
             torch.cuda.current_stream(self.device).wait_event(self._w_ready[j])
         slot = self._w_slots[j]
+        base = self.own_span[self.rank][0]
         for s in self._block_segs[block]:
-            o = self._slot_off[s.name]
-            self.params[s.name].data = slot[o : o + s.numel].view(s.shape)
+            if s.owner == self.rank and self.sc.peer:
+                self.params[s.name].data = self.P_own[s.offset - base : s.offset - base + s.numel].view(s.shape)
+            else:
+                o = self._slot_off[s.name]
+                self.params[s.name].data = slot[o : o + s.numel].view(s.shape)
         self._w_busy[j] = True
         self._clock += 1
         self._w_clock[j] = self._clock

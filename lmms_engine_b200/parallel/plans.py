@@ -1,10 +1,18 @@
 """Per-model parallel plans (expert parallel / tensor parallel composed with FSDP2).
 
-``qwen3_moe``: experts sharded over the ``ep`` mesh (``Shard(0)`` of the stacked parameters)
-and, when the data-parallel degree exceeds the expert-parallel degree, additionally
-FSDP-sharded on ``dp_shard_mod_ep`` with ``Shard(1)``; attention, embeddings and the rest are
-FSDP-sharded on the full ``fsdp`` mesh - the composition of the reference plan
-(src/lmms_engine/parallel/qwen3_moe/parallelize.py:26-151).
+Mixture-of-experts decoders, alone (``qwen3_moe``, ``qwen2_moe``, ``qwen3_5_moe`` text) or as the
+language model of a multimodal wrapper (``qwen3_vl_moe``, ``qwen3_omni_moe``, ``qwen3_5_moe``,
+``aero_realtime`` on a MoE backbone): experts sharded over the ``ep`` mesh (``Shard(0)`` of the
+stacked parameters) and, when the data-parallel degree exceeds the expert-parallel degree,
+additionally FSDP-sharded on ``dp_shard_mod_ep`` with ``Shard(1)``; attention, embeddings, the
+vision / audio towers and the rest are FSDP-sharded on the full ``fsdp`` mesh.  One plan function
+covers what the reference spells out per family
+(src/lmms_engine/parallel/qwen3_moe/parallelize.py:26-151,
+src/lmms_engine/parallel/qwen3_vl_moe/parallelize.py:34-128,
+src/lmms_engine/parallel/qwen3_omni_moe/parallelize.py:1-188,
+src/lmms_engine/parallel/qwen3_5_moe/parallelize.py:1-120,
+src/lmms_engine/parallel/aero_realtime/parallelize.py:55-253): the decoder is found under
+``language_model`` when the model is a wrapper, the towers by their attribute names.
 
 Dense decoders (``qwen2``/``qwen3`` and the text decoder of the VL wrappers) get the
 sequence-parallel tensor-parallel plan of ``parallel/tensor_parallel.py``.
@@ -34,8 +42,21 @@ def _fsdp_kwargs(args, mesh, mp):
     return kw
 
 
+TOWER_ATTRS = ("visual", "audio_tower", "projector", "audio_projector", "multi_modal_projector")
+
+
+def text_decoder(model):
+    """The causal decoder of a model: the model itself, or ``language_model`` of a multimodal wrapper."""
+    return getattr(model, "language_model", model)
+
+
 @register_parallel_plan("qwen3_moe")
 @register_parallel_plan("qwen2_moe")
+@register_parallel_plan("qwen3_vl_moe")
+@register_parallel_plan("qwen3_omni_moe")
+@register_parallel_plan("qwen3_omni_moe_thinker")
+@register_parallel_plan("qwen3_5_moe")
+@register_parallel_plan("qwen3_5_moe_text")
 def parallelize_moe(model, args, dtype=None, **_):
     from torch.distributed.fsdp import fully_shard
     from torch.distributed.tensor import Shard
@@ -50,19 +71,29 @@ def parallelize_moe(model, args, dtype=None, **_):
         apply_expert_parallel(model, pgm.ep_mesh, pgm.ep_group)
     mp = _mp_policy(args, dtype)
     fsdp_mesh = pgm.device_mesh["fsdp"]
-    for layer in model.model.layers:
+    text = text_decoder(model)
+    if text is not model:
+        # towers of a multimodal wrapper: one FSDP unit each, like the reference's ``fully_shard(model.visual)``
+        for attr in TOWER_ATTRS:
+            tower = getattr(model, attr, None)
+            if tower is not None and any(p.requires_grad for p in tower.parameters()):
+                fully_shard(tower, **_fsdp_kwargs(args, fsdp_mesh, mp))
+    for layer in text.model.layers:
         if isinstance(layer.mlp, SparseMoeBlock) and pgm.enable_ep and pgm.layout.dp_shard_mod_ep > 1:
             fully_shard(layer.mlp.experts, shard_placement_fn=lambda p: Shard(1),
                         **_fsdp_kwargs(args, pgm.device_mesh["dp_shard_mod_ep"], mp))
-        fully_shard(layer.self_attn, **_fsdp_kwargs(args, fsdp_mesh, mp))
+        for mixer_name in ("self_attn", "linear_attn"):  # hybrid decoders have one or the other per layer
+            mixer = getattr(layer, mixer_name, None)
+            if mixer is not None:
+                fully_shard(mixer, **_fsdp_kwargs(args, fsdp_mesh, mp))
         if pgm.enable_ep and isinstance(layer.mlp, SparseMoeBlock):
             # the experts are managed above (or are purely expert-parallel): keep them out of the layer group
             ignored = set(layer.mlp.experts.parameters())
             fully_shard(layer, ignored_params=ignored, **_fsdp_kwargs(args, fsdp_mesh, mp))
         else:
             fully_shard(layer, **_fsdp_kwargs(args, fsdp_mesh, mp))
-    if not model.config.tie_word_embeddings:
-        fully_shard(model.model.embed_tokens, **_fsdp_kwargs(args, fsdp_mesh, mp))
+    if not getattr(text.config, "tie_word_embeddings", False):
+        fully_shard(text.model.embed_tokens, **_fsdp_kwargs(args, fsdp_mesh, mp))
     ignored = set()
     if pgm.enable_ep:
         for m in model.modules():
@@ -70,6 +101,17 @@ def parallelize_moe(model, args, dtype=None, **_):
                 ignored |= set(m.experts.parameters())
     fully_shard(model, ignored_params=ignored or None, **_fsdp_kwargs(args, fsdp_mesh, mp))
     return model
+
+
+@register_parallel_plan("aero_realtime")
+def parallelize_aero_realtime(model, args, dtype=None, **kw):
+    """Streaming-audio wrapper: expert parallelism when its backbone is a MoE decoder, the dense
+    tensor-parallel plan otherwise (src/lmms_engine/parallel/aero_realtime/parallelize.py:55-253)."""
+    from ..models.moe_lm import SparseMoeBlock
+
+    if any(isinstance(m, SparseMoeBlock) for m in model.modules()):
+        return parallelize_moe(model, args, dtype, **kw)
+    return parallelize_dense_tp(model, args, dtype, **kw)
 
 
 @register_parallel_plan("qwen2")

@@ -31,6 +31,13 @@ def test_expert_parallel_matches_unsharded(world):
     assert "expert parallel ok" in torchrun("ep_run.py", world)
 
 
+def test_expert_parallel_plans_of_all_moe_families():
+    """qwen3_moe, qwen3_5_moe, qwen3_vl_moe, qwen3_omni_moe and aero_realtime (MoE backbone): the registered
+    plan shards the experts and the sharded model equals the unsharded one."""
+    out = torchrun("ep_plan_run.py", 2)
+    assert "expert parallel plans ok: qwen3_moe qwen3_5_moe_text qwen3_vl_moe qwen3_omni_moe_thinker aero_realtime" in out
+
+
 def test_rank_layout_arithmetic():
     from lmms_engine_b200.parallel.process_group_manager import RankLayout
 
