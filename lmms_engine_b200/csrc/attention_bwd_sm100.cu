@@ -38,7 +38,7 @@ struct BwdP {
   __nv_bfloat16* dK;     // [Tk, Hkv, D]
   __nv_bfloat16* dV;
   long lddq, lddk, lddv;
-  int Tq;
+  int Tq, Tk;
   int* status;
 };
 
@@ -63,7 +63,7 @@ __device__ __forceinline__ uint64_t desc_lbo(uint32_t addr, uint32_t lbo_bytes) 
 }
 
 __device__ __forceinline__ bool find_work(const int* cu_a, const int* cu_b, int n_docs, int block, int item,
-                                          int* work) {
+                                          int* work, int total_a, int total_b, int* status) {
   // work: doc, a0 (offset of the 128-block inside the doc), len_a, len_b, a_start, b_start
   int acc = 0;
   for (int d = 0; d < n_docs; ++d) {
@@ -76,6 +76,10 @@ __device__ __forceinline__ bool find_work(const int* cu_a, const int* cu_b, int 
       work[3] = cu_b[d + 1] - cu_b[d];
       work[4] = cu_a[d];
       work[5] = cu_b[d];
+      if (!doc_in_bounds(work[4], work[2], total_a, status) || !doc_in_bounds(work[5], work[3], total_b, status)) {
+        work[0] = -1;
+        return false;
+      }
       return true;
     }
     acc += nb;
@@ -104,7 +108,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     work[0] = -1;
-    find_work(p.cu_k, p.cu_q, p.n_docs, kKeys, blockIdx.x, work);
+    find_work(p.cu_k, p.cu_q, p.n_docs, kKeys, blockIdx.x, work, p.Tk, p.Tq, p.status);
     mbar_init(kv_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&q_full[i], 1);
@@ -357,7 +361,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     for (int d = 0; d < p.n_docs; ++d) total += (p.cu_q[d + 1] - p.cu_q[d] + kKeys - 1) / kKeys;
     work[0] = -1;
     const int item = total - 1 - static_cast<int>(blockIdx.x);
-    if (item >= 0) find_work(p.cu_q, p.cu_k, p.n_docs, kKeys, item, work);
+    if (item >= 0) find_work(p.cu_q, p.cu_k, p.n_docs, kKeys, item, work, p.Tq, p.Tk, p.status);
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&kv_full[i], 1);
@@ -654,6 +658,7 @@ extern "C" int b200_attn_bwd_v2(const void* q, const void* k, const void* v, con
   p.dV = static_cast<__nv_bfloat16*>(dv);
   p.lddq = lddq; p.lddk = lddk; p.lddv = lddv;
   p.Tq = Tq;
+  p.Tk = Tk;
   p.status = status;
   static bool set = false;
   if (!set) {

@@ -43,7 +43,7 @@ struct FwdParams {
   __nv_bfloat16* O;      // [T, Hq, D]
   long ldo;              // row stride of O in elements
   float* lse;            // [Hq, Tq]
-  int Tq;
+  int Tq, Tk;
   int* status;
 };
 
@@ -100,6 +100,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           work[3] = p.cu_k[d + 1] - p.cu_k[d];
           work[4] = p.cu_q[d];
           work[5] = p.cu_k[d];
+          if (!doc_in_bounds(work[4], work[2], p.Tq, p.status) || !doc_in_bounds(work[5], work[3], p.Tk, p.status)) work[0] = -1;
           break;
         }
         acc += nb;
@@ -406,7 +407,7 @@ struct BwdParams {
   __nv_bfloat16* dK;     // [Tk, Hkv, D]
   __nv_bfloat16* dV;
   long lddk, lddv;
-  int Tq;
+  int Tq, Tk;
   int* status;
 };
 
@@ -461,6 +462,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         work[3] = lk;
         work[4] = p.cu_q[d];
         work[5] = p.cu_k[d];
+        if (!doc_in_bounds(work[4], work[2], p.Tq, p.status) || !doc_in_bounds(work[5], work[3], p.Tk, p.status)) work[0] = -1;
         break;
       }
       acc += nb;
@@ -810,6 +812,7 @@ int b200_attn_fwd(const void* q, const void* k, const void* v, void* o, void* ls
   p.ldo = ldo;
   p.lse = static_cast<float*>(lse);
   p.Tq = Tq;
+  p.Tk = Tk;
   p.status = status;
   dim3 grid((Tq + kBlockQ - 1) / kBlockQ + n_docs, Hq);
   if (DP == 64) {
@@ -863,6 +866,7 @@ int b200_attn_bwd(const void* q, const void* k, const void* v, const void* o, co
   p.dV = static_cast<__nv_bfloat16*>(dv);
   p.lddk = lddk; p.lddv = lddv;
   p.Tq = Tq;
+  p.Tk = Tk;
   p.status = status;
   dim3 grid((Tk + kBlockK - 1) / kBlockK + n_docs, Hkv);
   {

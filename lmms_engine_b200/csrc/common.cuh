@@ -263,6 +263,17 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16_major(int m, int n, int a
   return umma_idesc_bf16(m, n) | (static_cast<uint32_t>(a_mn) << 15) | (static_cast<uint32_t>(b_mn) << 16);
 }
 
+// ---------------------------------------------------------------- packed-document bounds
+// A document [start, start + len) of a packed stream must lie inside the tensor it indexes.  Kernels
+// that derive row addresses from cu_seqlens call this for the document they were assigned; a table
+// that reaches past the tensor raises kStatusBadShape and the CTA does no work instead of writing
+// out of bounds.
+__device__ __forceinline__ bool doc_in_bounds(int start, int len, int total, int* status) {
+  if (start >= 0 && len >= 0 && start + len <= total) return true;
+  if (status != nullptr) atomicExch(status, kStatusBadShape);
+  return false;
+}
+
 // ---------------------------------------------------------------- misc numeric helpers
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);

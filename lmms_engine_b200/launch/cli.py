@@ -38,57 +38,59 @@ def filter_training_args(kwargs: Dict[str, Any]) -> Dict[str, Any]:
         else:
             dropped.append(k)
     if dropped:
-        logger.warning(f"Filtering out unsupported TrainingArguments parameters: {dropped}")
+        logger.warning(f"trainer_args entries that this engine does not know are ignored: {sorted(dropped)}")
     return kept
 
 
+def _init_distributed(raw_args: Dict[str, Any]) -> bool:
+    """Bring up ``torch.distributed`` (env:// rendezvous; a lone process gets a local one) and the
+    process-group manager for the degrees the trainer arguments ask for.  Returns ``use_cpu``."""
+    from ..parallel.process_group_manager import RankLayout
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    # all mesh arithmetic and its error messages live in RankLayout; this builds the layout once up front so a
+    # bad combination of degrees fails before any process group exists
+    layout = RankLayout.from_degrees(world, tp=raw_args.get("tp_degree"), cp=raw_args.get("sp_ulysses_degree"),
+                                     ep=raw_args.get("ep_degree"),
+                                     hsdp_shard=(raw_args.get("fsdp_config") or {}).get("hsdp_shard_size"))
+    cpu = bool(raw_args.get("use_cpu")) or not torch.cuda.is_available()
+    if not dist.is_initialized():
+        if world == 1 and "MASTER_ADDR" not in os.environ:
+            os.environ.update(MASTER_ADDR="127.0.0.1", RANK="0", WORLD_SIZE="1", LOCAL_RANK="0")
+            os.environ.setdefault("MASTER_PORT", "29500")
+        if not cpu:
+            torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        dist.init_process_group(backend="gloo" if cpu else "nccl", init_method="env://", world_size=world,
+                                rank=int(os.environ.get("RANK", "0")),
+                                timeout=datetime.timedelta(seconds=raw_args.get("ddp_timeout", 1800)))
+    setup_process_group_manager(tp_size=layout.tp, cp_size=layout.cp, pp_size=1, dp_size=layout.dp, ep_size=layout.ep,
+                                hsdp_shard_size=layout.hsdp_shard)
+    return cpu
+
+
 def create_train_task(config: Dict[str, Any]):
+    """Public entry point (``lmms_engine.launch.cli.create_train_task`` of the reference,
+    src/lmms_engine/launch/cli.py:24-94): a config dict with ``trainer_type``, ``dataset_config``,
+    ``model_config`` and ``trainer_args`` becomes a ``TrainRunner``; distributed state is set up on the way."""
     from ..train.runner import TrainRunner
 
-    dataset_config = DatasetConfig(**config.pop("dataset_config"))
-    model_config = ModelConfig(**config.pop("model_config"))
-    trainer_type = config.pop("trainer_type")
-    global_rank = int(os.environ.get("RANK", "0"))
-    world_size = int(os.environ.get("WORLD_SIZE", "1"))
-
-    trainer_args = config.get("trainer_args") or {}
-    sp_degree = trainer_args.get("sp_ulysses_degree", 1) or 1
-    tp_degree = trainer_args.get("tp_degree", 1) or 1
-    ep_degree = trainer_args.get("ep_degree", 1) or 1
-    if tp_degree < 1:
-        raise ValueError(f"tp_degree must be >= 1, got {tp_degree}")
-    if world_size % (sp_degree * tp_degree) != 0:
+    raw_args = dict(config.get("trainer_args") or {})
+    if raw_args.get("deepspeed"):
         raise ValueError(
-            f"World size ({world_size}) must be divisible by sp_ulysses_degree ({sp_degree}) * tp_degree ({tp_degree})"
-        )
-    dp_size = world_size // (sp_degree * tp_degree)
-    use_cpu = bool(trainer_args.get("use_cpu", False)) or not torch.cuda.is_available()
-    backend = "gloo" if use_cpu else "nccl"
-    ddp_timeout = trainer_args.get("ddp_timeout", 30 * 60)
-    if not dist.is_initialized():
-        if world_size == 1 and "MASTER_ADDR" not in os.environ:
-            os.environ["MASTER_ADDR"] = "127.0.0.1"
-            os.environ.setdefault("MASTER_PORT", "29500")
-            os.environ["RANK"] = "0"
-            os.environ["WORLD_SIZE"] = "1"
-            os.environ["LOCAL_RANK"] = "0"
-        if backend == "nccl":
-            torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
-        dist.init_process_group(rank=global_rank, world_size=world_size, backend=backend, init_method="env://",
-                                timeout=datetime.timedelta(seconds=ddp_timeout))
-    fsdp_config = trainer_args.get("fsdp_config", {}) or {}
-    hsdp_shard_size = fsdp_config.get("hsdp_shard_size", 0) or 0
-    setup_process_group_manager(tp_size=tp_degree, cp_size=sp_degree, pp_size=1, dp_size=dp_size, ep_size=ep_degree,
-                                hsdp_shard_size=hsdp_shard_size)
-    trainer_args = dict(config.pop("trainer_args"))
-    if use_cpu:
-        trainer_args["use_cpu"] = True
-    eval_cfg = trainer_args.pop("eval_config", None)
-    if eval_cfg is not None:
-        trainer_args["eval_config"] = EvalConfig(**eval_cfg).to_dict()
-    args = TrainingArguments(**filter_training_args(trainer_args))
-    train_config = TrainerConfig(dataset_config=dataset_config, model_config=model_config, trainer_type=trainer_type,
-                                 trainer_args=args, extra_kwargs=config.get("extra_kwargs"))
+            "trainer_args.deepspeed is set, but this engine has no DeepSpeed runtime: ZeRO-1/2 is what "
+            "sharding_runtime: native does (optimizer state and gradients held by owner ranks), ZeRO-3 is "
+            "sharding_runtime: native_sharded or torch_fsdp2.  Remove the deepspeed entry and pick one of those.")
+    if _init_distributed(raw_args):
+        raw_args["use_cpu"] = True
+    if raw_args.get("eval_config") is not None:
+        raw_args["eval_config"] = EvalConfig(**raw_args["eval_config"]).to_dict()
+    train_config = TrainerConfig(
+        dataset_config=DatasetConfig(**config["dataset_config"]),
+        model_config=ModelConfig(**config["model_config"]),
+        trainer_type=config["trainer_type"],
+        trainer_args=TrainingArguments(**filter_training_args(raw_args)),
+        extra_kwargs=config.get("extra_kwargs"),
+    )
     return TrainRunner(config=train_config)
 
 
@@ -112,7 +114,7 @@ def build_config(argv: List[str]) -> Dict[str, Any]:
     config = ov.apply_overrides(config, rest)
     config_yaml = config.pop("config_yaml", None)
     if config_yaml:
-        logger.info(f"Detected config yaml, merging with the default config. Will use the args in {config_yaml} to override current config.")
+        logger.info(f"config_yaml={config_yaml}: its entries are laid over the defaults, command-line overrides come last")
         with open(config_yaml) as f:
             loaded = yaml.safe_load(f)
         if isinstance(loaded, list):  # legacy form: a one-element list holding the config

@@ -135,6 +135,11 @@ def varlen_attn(
     D = q.shape[-1]
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
     window_left = int(window_size[0]) if window_size is not None else -1
+    window_right = int(window_size[1]) if window_size is not None and len(window_size) > 1 else -1
+    if window_right >= 0 and not causal:
+        # a causal mask already limits the right side to 0; a finite right window without it is a
+        # different mask, which neither the kernel nor the reference formulation below implements
+        raise NotImplementedError(f"window_size[1] = {window_right} (right window) is only supported together with causal=True")
     native = q.is_cuda and q.dtype == torch.bfloat16 and D % 8 == 0 and D <= 128 and backend != "reference"
     if native:
         cu_q = cu_seqlens_q.to(torch.int32).contiguous()

@@ -56,6 +56,17 @@ class RankLayout:
             if (self.dp * self.cp) % self.hsdp_shard != 0:
                 raise ValueError(f"dp*cp ({self.dp * self.cp}) must be divisible by hsdp_shard_size ({self.hsdp_shard})")
 
+    @classmethod
+    def from_degrees(cls, world_size: int, tp=None, cp=None, ep=None, hsdp_shard=None) -> "RankLayout":
+        """Layout for the degrees of a training configuration (``None`` / 0 mean 1); the data-parallel
+        degree is whatever of the world the model-parallel degrees leave."""
+        tp, cp, ep = int(tp or 1), int(cp or 1), int(ep or 1)
+        if tp < 1 or cp < 1 or ep < 1:
+            raise ValueError(f"parallel degrees must be positive: tp_degree={tp}, sp_ulysses_degree={cp}, ep_degree={ep}")
+        if world_size % (tp * cp):
+            raise ValueError(f"{world_size} ranks cannot be split into groups of sp_ulysses_degree x tp_degree = {cp} x {tp}")
+        return cls(world_size=world_size, tp=tp, cp=cp, pp=1, dp=world_size // (tp * cp), ep=ep, hsdp_shard=int(hsdp_shard or 0))
+
     def coords(self, rank: int):
         """(dp, pp, cp, tp) coordinates of ``rank``."""
         tp = rank % self.tp

@@ -65,3 +65,26 @@ def test_attn_strided_qkv_views():
     o = attention.varlen_attn(q, k, v, cu, cu, causal=True)
     ref = attention.varlen_attn_ref(q.float(), k.float(), v.float(), cu, cu, causal=True)
     assert (o.float() - ref).abs().max().item() < 3e-2
+
+
+def test_cu_seqlens_past_the_tensor_raise_status_not_a_fault():
+    """A cu_seqlens table that reaches past the packed tensor makes the kernel raise its status word and skip
+    the document; nothing is written out of bounds and the context stays usable."""
+    from lmms_engine_b200.ops import _cuda, attention
+
+    T, H, D = 256, 2, 64
+    q = torch.randn(T, H, D, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(T, H, D, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(T, H, D, device="cuda", dtype=torch.bfloat16)
+    bad = torch.tensor([0, 128, 384], dtype=torch.int32, device="cuda")  # the second document ends 128 rows past T
+    attention.varlen_attn(q, k, v, bad, bad, causal=True)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="bad shape"):
+        _cuda.check_status()
+    good = torch.tensor([0, 128, 256], dtype=torch.int32, device="cuda")
+    out = attention.varlen_attn(q, k, v, good, good, causal=True)
+    ref = attention.varlen_attn_ref(q, k, v, good, good, True, 1.0 / D ** 0.5, -1)
+    assert (out.float() - ref.float()).abs().max() < 3e-2
+    _cuda.check_status()
+    with pytest.raises(NotImplementedError):
+        attention.varlen_attn(q, k, v, good, good, causal=False, window_size=(-1, 16))

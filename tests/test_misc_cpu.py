@@ -340,3 +340,29 @@ def test_prepare_init_weight_composes_parts_and_grows_vocabulary(tmp_path):
     assert rows[0]["messages"][0]["content"][0]["type"] == "image_url" and rows[0]["messages"][1]["role"] == "assistant"
     parts = split_jsonl.main(["-i", str(tmp_path / "ds" / "train.jsonl"), "-s", "2"])
     assert [sum(1 for _ in open(p)) for p in parts] == [3, 2]
+
+
+def test_deepspeed_configs_are_rejected_with_directions():
+    """A ``deepspeed:`` entry is not silently dropped: the error names the runtimes that replace ZeRO."""
+    import pytest
+
+    from lmms_engine_b200.launch.cli import create_train_task
+
+    cfg = {"trainer_type": "fsdp2_trainer", "dataset_config": {"dataset_type": "synthetic_packed", "dataset_format": "synthetic"},
+           "model_config": {"load_from_config": {"model_type": "qwen2", "config": {}}},
+           "trainer_args": {"output_dir": "/tmp/x", "deepspeed": "examples/ds_config/zero2.json"}}
+    with pytest.raises(ValueError, match="native_sharded"):
+        create_train_task(cfg)
+
+
+def test_rank_layout_from_degrees_reports_bad_combinations():
+    import pytest
+
+    from lmms_engine_b200.parallel.process_group_manager import RankLayout
+
+    lay = RankLayout.from_degrees(8, tp=2, cp=2)
+    assert (lay.dp, lay.tp, lay.cp) == (2, 2, 2)
+    with pytest.raises(ValueError, match="cannot be split"):
+        RankLayout.from_degrees(8, tp=3)
+    with pytest.raises(ValueError, match="positive"):
+        RankLayout.from_degrees(8, tp=-1)
