@@ -256,8 +256,20 @@ class FSDP2SFTTrainer:
             kw["prefetch_factor"] = args.dataloader_prefetch_factor
         self.sampler = None
         if not isinstance(ds, IterableDataset):
-            self.sampler = DistributedSampler(ds, num_replicas=self.dp_size, rank=self.dp_rank, shuffle=True,
-                                              seed=args.seed, drop_last=args.dataloader_drop_last)
+            # samplers work on DATA-parallel ranks: the ranks of a sequence-/tensor-parallel group read the same samples
+            lengths = None
+            if args.group_by_length:
+                from ..samplers import LengthGroupedSampler, dataset_lengths
+
+                lengths = dataset_lengths(ds)
+                if lengths is None:
+                    logger.warning("group_by_length is set but the dataset exposes no modality_length / lengths; sampling uniformly")
+            if lengths is not None:
+                self.sampler = LengthGroupedSampler(lengths, args.per_device_train_batch_size, num_replicas=self.dp_size,
+                                                    rank=self.dp_rank, seed=args.seed, drop_last=args.dataloader_drop_last)
+            else:
+                self.sampler = DistributedSampler(ds, num_replicas=self.dp_size, rank=self.dp_rank, shuffle=True,
+                                                  seed=args.seed, drop_last=args.dataloader_drop_last)
             kw["sampler"] = self.sampler
         try:
             from torchdata.stateful_dataloader import StatefulDataLoader

@@ -366,3 +366,29 @@ def test_rank_layout_from_degrees_reports_bad_combinations():
         RankLayout.from_degrees(8, tp=3)
     with pytest.raises(ValueError, match="positive"):
         RankLayout.from_degrees(8, tp=-1)
+
+
+def test_length_grouped_sampler_groups_and_shards():
+    """Every sample once per epoch, the ranks of a step hold similar lengths, text-only and multimodal samples
+    are batched apart, epochs differ, ranks of one data-parallel index agree."""
+    import random
+
+    from lmms_engine_b200.train.samplers import LengthGroupedSampler
+
+    rnd = random.Random(0)
+    lengths = [rnd.randint(10, 2000) * (1 if rnd.random() < 0.7 else -1) for _ in range(960)]
+    R, B = 4, 2
+    per_rank = [list(LengthGroupedSampler(lengths, B, num_replicas=R, rank=r, seed=5)) for r in range(R)]
+    assert sorted(i for pr in per_rank for i in pr) == list(range(960))
+    spreads, mixed = [], 0
+    for step in range(len(per_rank[0]) // B):
+        idx = [i for pr in per_rank for i in pr[step * B:(step + 1) * B]]
+        ls = [abs(lengths[i]) for i in idx]
+        spreads.append(max(ls) - min(ls))
+        mixed += len({lengths[i] >= 0 for i in idx}) > 1
+    assert sum(spreads) / len(spreads) < 150, sum(spreads) / len(spreads)  # a random batch of 8 spreads over ~1500
+    assert mixed <= 3
+    again = LengthGroupedSampler(lengths, B, num_replicas=R, rank=0, seed=5)
+    assert list(again) == per_rank[0]
+    again.set_epoch(1)
+    assert list(again) != per_rank[0]
