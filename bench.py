@@ -200,7 +200,9 @@ def build_config(args, out_dir):
         "dataset_config": {"dataset_type": "synthetic_vl", "dataset_format": "synthetic", "packing": True,
                            "packing_length": tokens, "data_seed": 1234, "extra_kwargs": data},
         "model_config": {"load_from_config": {"model_type": mtype, "config": model},
-                         "monkey_patch_kwargs": {"vit_frame_parallel": args.gpus > 1}},
+                         # frames are balanced over the ranks of the native runtime; under tensor parallelism the tower is
+                         # an FSDP2 unit that every rank runs on its own sample (as in the reference)
+                         "monkey_patch_kwargs": {"vit_frame_parallel": args.gpus > 1 and args.config == "vl_sp8"}},
         "trainer_args": targs,
     }
 
@@ -288,6 +290,8 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, ms_e2e = float(t[0]), float(t[1])
     peak_gb = torch.cuda.max_memory_allocated() / 2**30
+    # peer-mapped (symmetric) buffers are allocated outside torch's caching allocator
+    symm_gb = getattr(getattr(tr.runtime, "comm", None), "allocated_bytes", 0) / 2**30 if tr.runtime is not None else 0.0
     if rank == 0:
         total_tokens = tokens_per_step * replicas * args.steps  # one packed sequence per model-parallel group
         value = total_tokens / (ms / 1e3)
@@ -322,7 +326,8 @@ def run_ours(args):
             "clocks": clocks, "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
             "gpu_launches": launches, "tokens_per_gpu_per_s": value / world,
-            "mfu_ref_formula": flops / (ms / args.steps / 1e3) / 2.25e15, "peak_mem_gb": peak_gb, "last_loss": last,
+            "mfu_ref_formula": flops / (ms / args.steps / 1e3) / 2.25e15, "peak_mem_gb": peak_gb + symm_gb, "peak_mem_allocator_gb": peak_gb,
+            "peer_mapped_mem_gb": symm_gb, "last_loss": last,
         }
         emit_json(out)
     if dist.is_initialized():

@@ -54,6 +54,9 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const LT* __restrict__ 
     for (int i = 0; i < 8; ++i) {
       v[i] *= inv;
       if (i < per) probs[static_cast<size_t>(t) * E + lane + 32 * i] = v[i];
+      // non-finite logits (an upstream overflow) must not derail the selection below: every round has to find an
+      // expert index inside [0, E), the histogram and the permutation index memory with it
+      if (!(v[i] >= 0.f)) v[i] = 0.f;
     }
     // k rounds of warp arg-max; ties go to the lower expert index (like torch.topk on CUDA
     // is not guaranteed to; the engine's own reference uses the same rule)
@@ -177,6 +180,7 @@ __global__ void moe_combine_kernel(const bf16* __restrict__ src, const int* __re
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int j = 0; j < k; ++j) {
       const int row = row_of[t * k + j];
+      if (row < 0) continue;
       const float wt = w != nullptr ? w[t * k + j] : 1.f;
       const V8 v = *reinterpret_cast<const V8*>(src + static_cast<size_t>(row) * H + c);
 #pragma unroll

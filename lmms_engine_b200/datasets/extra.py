@@ -183,11 +183,61 @@ class OmniProcessor(QwenVLProcessor):
 
     def build_ids_and_labels(self, messages, mm, add_system_prompt=True):
         mm = dict(mm, audio=list(self._audio_counts))
+        self._mm_now = mm
         return super().build_ids_and_labels(messages, mm, add_system_prompt)
 
-    def process(self, hf_messages=None, images=None, videos=None, audios=None, add_system_prompt: bool = True, **kw):
+    # ---- a video that carries its sound track ("use_audio_in_video") ------------------------------------
+    # The clip's audio placeholders are interleaved with its video placeholders in chunks of ``seconds_per_chunk``
+    # seconds, between <|vision_start|><|audio_bos|> and <|audio_eos|><|vision_end|>; the audio clip of the video is
+    # the next one in ``audios`` (datasets put it at the video's place in the list).
+    seconds_per_chunk = 2.0
+    use_audio_in_video = False
+
+    def render_video(self, counters, mm) -> List[int]:
+        if not self.use_audio_in_video:
+            return super().render_video(counters, mm)
+        from ..models.mrope import interleave_av
+
+        i = counters["video"]
+        counters["video"] += 1
+        n_audio = mm["audio"][counters["audio"]]
+        counters["audio"] += 1
+        t, h, w = mm["video_grids"][i]
+        per = (h // self.merge_size) * (w // self.merge_size)
+        sec = self._second_per_grid[i] if i < len(self._second_per_grid) else 1.0
+        vt = np.floor(np.repeat(np.arange(t), per) * sec * self.tokens_per_second).astype(np.int64)
+        ids = [self.vision_start] + ([self.audio_bos] if self.audio_bos is not None else [])
+        for kind, lo, hi in interleave_av(vt, n_audio, int(self.tokens_per_second * self.seconds_per_chunk)):
+            ids += [self.video_token_id if kind == "video" else self.audio_token_id] * (hi - lo)
+        ids += ([self.audio_eos] if self.audio_eos is not None else []) + [self.vision_end]
+        return ids + self._enc("\n")
+
+    def positions(self, out) -> torch.Tensor:
+        if not self.use_audio_in_video:
+            return super().positions(out)
+        from ..models.mrope import omni_positions_one
+
+        if self.audio_bos is None or self.audio_eos is None:
+            raise ValueError("use_audio_in_video needs a tokenizer with <|audio_bos|> / <|audio_eos|>")
+        img = out["image_grid_thw"].tolist() if "image_grid_thw" in out else []
+        vid = out["video_grid_thw"].tolist() if "video_grid_thw" in out else []
+        spg = out["second_per_grid_ts"].tolist() if "second_per_grid_ts" in out else None
+        pos = omni_positions_one(out["input_ids"].numpy(), self.image_token_id, self.video_token_id, self.audio_token_id, img, vid, spg,
+                                 self.merge_size, self.tokens_per_second, self.seconds_per_chunk)
+        return torch.from_numpy(pos)
+
+    def process(self, hf_messages=None, images=None, videos=None, audios=None, add_system_prompt: bool = True,
+                use_audio_in_video: bool = False, **kw):
         from .processor.audio_process import log_mel_spectrogram
 
+        tok = self.tokenizer
+        self.audio_bos = self._maybe_token("<|audio_bos|>")
+        self.audio_eos = self._maybe_token("<|audio_eos|>")
+        self.use_audio_in_video = bool(use_audio_in_video) and bool(videos) and bool(audios)
+        fps = kw.get("video_fps")
+        self._second_per_grid = [self.temporal_patch_size / float((fps[i] if fps and i < len(fps) else None) or getattr(self.config, "fps", 1) or 1)
+                                 for i in range(len(videos or []))]
+        del tok
         audio_out, self._audio_counts = {}, []
         if audios:
             feats, masks = [], []
@@ -201,8 +251,17 @@ class OmniProcessor(QwenVLProcessor):
             out = super().process(hf_messages, images=images, videos=videos, audios=None, add_system_prompt=add_system_prompt, **kw)
         finally:
             self._audio_counts = []
+            self.use_audio_in_video = False
         out.update(audio_out)
         return out
+
+    def _maybe_token(self, text: str):
+        try:
+            ix = self.tokenizer.convert_tokens_to_ids(text)
+        except Exception:
+            return None
+        unk = getattr(self.tokenizer, "unk_token_id", None)
+        return None if ix is None or (unk is not None and ix == unk) else int(ix)
 
 
 from .processor.chat import Qwen3VLProcessor  # noqa: E402

@@ -107,5 +107,7 @@ class MultiModalIterableDataset(DatasetCore, IterableDataset):
                 yield pack
 
 
-for _name in ("vision_iterable", "qwen3_vl_iterable", "qwen_omni_iterable", "llava_ov2_iterable", "text_iterable"):
+# generic record handling; ``qwen3_vl_iterable`` / ``qwen_omni_iterable`` are in ``datasets/families.py``,
+# ``llava_ov2_iterable`` (codec-stream videos) in ``datasets/codec_video.py``
+for _name in ("vision_iterable", "text_iterable"):
     register_dataset(_name)(type(f"{_name.title().replace('_', '')}Dataset", (MultiModalIterableDataset,), {"__doc__": f"``dataset_type: {_name}``"}))

@@ -83,6 +83,48 @@ class MultiModalDataLoadingMixin:
                 pass
         return self._load_cv2(full, video_start, video_end)
 
+    def load_video_with_metadata(self, path: str, data_folder: Optional[str] = None, video_start: Optional[float] = None,
+                                 video_end: Optional[float] = None) -> Tuple[np.ndarray, dict]:
+        """Frames plus what a processor needs to talk about time: ``video_time`` (seconds of the source), ``fps`` of
+        the source, ``frames_indices`` and ``frame_times`` of the sampled frames, ``total_num_frames`` and the
+        effective ``sample_fps``.  Decoded with decord when it is installed, with OpenCV otherwise."""
+        full = self._resolve(path, data_folder)
+        try:
+            import decord
+
+            vr = decord.VideoReader(full)
+            fps, total = float(vr.get_avg_fps()), len(vr)
+            read = lambda idx: vr.get_batch(idx).asnumpy()  # noqa: E731
+        except ImportError:
+            import cv2
+
+            cap = cv2.VideoCapture(full)
+            if not cap.isOpened():
+                raise FileNotFoundError(full)
+            fps = float(cap.get(cv2.CAP_PROP_FPS) or 25.0)
+            total = int(cap.get(cv2.CAP_PROP_FRAME_COUNT))
+
+            def read(idx):
+                out = []
+                for i in idx:
+                    cap.set(cv2.CAP_PROP_POS_FRAMES, i)
+                    ok, fr = cap.read()
+                    if not ok:
+                        break
+                    out.append(cv2.cvtColor(fr, cv2.COLOR_BGR2RGB))
+                cap.release()
+                if not out:
+                    raise RuntimeError(f"no frames decoded from {full}")
+                return np.stack(out)
+        lo = int((video_start or 0) * fps)
+        hi = min(total, int(video_end * fps)) if video_end else total
+        idx = (self.sample_indices(max(hi - lo, 1), fps) + lo).tolist()
+        frames = read(idx)
+        idx = idx[: len(frames)]
+        span = max((hi - lo) / fps, 1e-6)
+        return frames, {"video_time": total / fps, "fps": fps, "frames_indices": idx, "frame_times": [i / fps for i in idx],
+                        "total_num_frames": total, "sample_fps": len(idx) / span}
+
     def _load_decord(self, full, start, end):
         import decord
 

@@ -58,5 +58,7 @@ class MultiModalDataset(DatasetCore, Dataset):
         return [self.process_record(self.data_list[i], self.data_folder[i]) for i in self.groups[idx]]
 
 
-for _name in ("vision", "vision_audio", "qwen_omni", "qwen3_vl", "llava_video", "text"):
+# ``vision``, ``vision_audio`` and ``text`` differ in the reference only by which media their records hold, which the
+# generic record handling discovers by itself; datasets with behaviour of their own live in ``datasets/families.py``
+for _name in ("vision", "vision_audio", "text"):
     register_dataset(_name)(type(f"{_name.title().replace('_', '')}Dataset", (MultiModalDataset,), {"__doc__": f"``dataset_type: {_name}``"}))

@@ -196,15 +196,44 @@ class Qwen3VLProcessor(QwenVLProcessor):
     per_frame_video = True
     tokens_per_second = 0.0
 
+    def process(self, hf_messages=None, images=None, videos=None, audios=None, add_system_prompt: bool = True,
+                video_fps=None, video_metadata=None, **kw):
+        """``video_metadata``: one dict per video with ``frame_times`` (seconds of every sampled frame, what the
+        Qwen3-VL dataset reads from the decoder) or ``fps`` + ``frames_indices``; without it the timestamps assume
+        frames sampled at the configured (or ``video_fps``) rate."""
+        self._video_times = []
+        for i in range(len(videos or [])):
+            meta = (video_metadata[i] if video_metadata and i < len(video_metadata) else None) or {}
+            if meta.get("frame_times") is not None:
+                self._video_times.append([float(x) for x in meta["frame_times"]])
+            elif meta.get("frames_indices") is not None and meta.get("fps"):
+                self._video_times.append([float(ix) / float(meta["fps"]) for ix in meta["frames_indices"]])
+            else:
+                self._video_times.append(None)
+        self._video_fps = list(video_fps) if video_fps else []
+        try:
+            return super().process(hf_messages, images=images, videos=videos, audios=audios, add_system_prompt=add_system_prompt,
+                                   video_fps=video_fps, **kw)
+        finally:
+            self._video_times, self._video_fps = [], []
+
     def render_video(self, counters, mm) -> List[int]:
         i = counters["video"]
         counters["video"] += 1
         t, h, w = mm["video_grids"][i]
         per = (h * w) // (self.merge_size ** 2)
-        fps = float(getattr(self.config, "fps", 1) or 1)
+        times = getattr(self, "_video_times", None)
+        times = times[i] if times and i < len(times) else None
+        fps_list = getattr(self, "_video_fps", None) or []
+        fps = float((fps_list[i] if i < len(fps_list) else None) or getattr(self.config, "fps", 1) or 1)
         ids: List[int] = []
         for f in range(t):
-            stamp = (f * self.temporal_patch_size + (self.temporal_patch_size - 1) / 2.0) / fps
+            if times:
+                # mean time of the frames merged into this temporal step (the last frame repeats when the count is odd)
+                group = [times[min(f * self.temporal_patch_size + j, len(times) - 1)] for j in range(self.temporal_patch_size)]
+                stamp = sum(group) / len(group)
+            else:
+                stamp = (f * self.temporal_patch_size + (self.temporal_patch_size - 1) / 2.0) / fps
             ids += self._enc(f"<{stamp:.1f} seconds>")
             ids += [self.vision_start] + [self.video_token_id] * per + [self.vision_end]
         return ids + self._enc("\n")

@@ -4,3 +4,4 @@ an unknown ``dataset_type``."""
 from . import synthetic  # noqa: F401
 from . import iterable, naive, processor  # noqa: F401
 from . import extra  # noqa: F401
+from . import families  # noqa: F401

@@ -6,6 +6,7 @@ Each exported function is declared once with a compact signature string:
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -95,12 +96,26 @@ def check_status(device: Optional[torch.device] = None) -> None:
             raise RuntimeError(f"native kernel reported status {v} on cuda:{idx} ({STATUS_NAMES.get(v, 'unknown')})")
 
 
+# LMMS_B200_DEBUG_SYNC=1: synchronise after every native launch and name the launcher whose kernel failed
+# (asynchronous faults are otherwise reported by whatever call happens to synchronise next).
+DEBUG_SYNC = os.environ.get("LMMS_B200_DEBUG_SYNC", "0") == "1"
+
+
+def _debug_sync(name: str) -> None:
+    try:
+        torch.cuda.synchronize()
+    except Exception as e:  # noqa: BLE001
+        raise RuntimeError(f"device fault during or before {name}: {e}") from e
+
+
 def call(name: str, *args) -> None:
     global launch_count
     rc = fn(name)(*args)
     launch_count += 1
     if rc != 0:
         raise RuntimeError(f"{name} failed with code {rc}")
+    if DEBUG_SYNC:
+        _debug_sync(name)
 
 
 def call_raw(name: str, *args) -> int:
@@ -108,6 +123,8 @@ def call_raw(name: str, *args) -> int:
     global launch_count
     rc = fn(name)(*args)
     launch_count += 1
+    if DEBUG_SYNC:
+        _debug_sync(name)
     return rc
 
 

@@ -334,14 +334,17 @@ class OwnerShardedRuntime:
             self._armed = True
             self._count = [0] * self.n_buckets
             self._fired = [False] * self.n_buckets
+            self._epoch = None
 
     def _fire(self, b: int, max_blocks: int) -> None:
         main = torch.cuda.current_stream(self.device)
         ev = torch.cuda.Event()
         ev.record(main)
         self._side.wait_event(ev)
+        if getattr(self, "_epoch", None) is None:
+            self._epoch = self.comm.bump("bucket_epoch")  # one epoch per optimizer step, the same on every rank
         with torch.cuda.stream(self._side):
-            self.comm.bucket_reduce(self.G, b, self.bucket_ranges[b][self.rank], self.step_count + 1, max_blocks)
+            self.comm.bucket_reduce(self.G, b, self.bucket_ranges[b][self.rank], self._epoch, max_blocks)
         self._fired[b] = True
 
     def _finish_reduce(self) -> None:
@@ -355,6 +358,7 @@ class OwnerShardedRuntime:
         torch.cuda.current_stream(self.device).wait_event(done)
         self._armed = False
         self._fired = [False] * self.n_buckets
+        self._epoch = None
 
     # ------------------------------------------------------------------------------------
     @property

@@ -94,6 +94,11 @@ class TorchShardComm:
     def wait_acks(self, slot_index: int, use: int) -> None:
         return  # the reduce above is complete when it returns
 
+    def bump(self, key) -> int:
+        c = self.__dict__.setdefault("_counters", {})
+        c[key] = c.get(key, 0) + 1
+        return c[key]
+
     def all_reduce_sum(self, t: torch.Tensor) -> None:
         if self.n > 1:
             dist.all_reduce(t, group=self.group)
@@ -174,6 +179,9 @@ class PeerShardComm:
         _cuda.call("b200_peer_wait_flags", ctypes.addressof(pc._pad_ptrs), self.n, self.rank,
                    self.slot_flag_block(slot_index) + self.ACK_OFFSET, use & 0x7FFFFFFF, st.data_ptr(), pc.BARRIER_TIMEOUT_MS,
                    _cuda.stream())
+
+    def bump(self, key) -> int:
+        return self.pc.bump(key)
 
     def all_reduce_sum(self, t):
         self.pc.all_reduce_sum(t)
@@ -475,7 +483,7 @@ class ParamShardedRuntime(OwnerShardedRuntime):
         self._g_next = (j + 1) % self.GRAD_SLOTS
         if self._g_use[j] > 0:
             self.sc.wait_acks(self._slot_flag_index(j), self._g_use[j])  # every owner has read the slot's last content
-        self._g_use[j] += 1
+        self._g_use[j] = self.sc.bump(("slot", self._slot_flag_index(j)))
         slot = self._g_slots[j]
         slot.zero_()
         for s in self._block_segs[block]:
@@ -498,7 +506,7 @@ class ParamShardedRuntime(OwnerShardedRuntime):
     def _reduce_block(self, block: str) -> None:
         """All gradients of the block are final on this rank: hand them to their owners."""
         j, use = self._g_of.pop(block)
-        self._blk_round[block] += 1
+        self._blk_round[block] = self.sc.bump(("block", self._flag_block(block)))
         my_lo = {r: self.own_span[r][0] for r in range(self.n)}
         items = [(s.owner, self._slot_off[s.name], s.offset - my_lo[s.owner], _round_up(s.numel, 8)) for s in self._block_segs[block]]
         if self._side is not None:

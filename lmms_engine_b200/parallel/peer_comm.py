@@ -74,6 +74,8 @@ class PeerComm:
     def allocate(self, numel: int, dtype, device) -> torch.Tensor:
         t = self._symm.empty(numel, dtype=dtype, device=device)
         t.zero_()
+        # symmetric buffers bypass torch's caching allocator: memory reports add this counter
+        self.allocated_bytes = getattr(self, "allocated_bytes", 0) + t.numel() * t.element_size()
         hdl = self._symm.rendezvous(t, group=self.group)
         self._handles[t.data_ptr()] = (t, hdl, _ptr_array([int(p) for p in hdl.buffer_ptrs]))
         return t
@@ -88,6 +90,14 @@ class PeerComm:
         st = _cuda.status_word(self.device)
         _cuda.call("b200_peer_barrier", ctypes.addressof(self._pad_ptrs), self.n, self.rank, self._epoch, st.data_ptr(),
                    self.BARRIER_TIMEOUT_MS, _cuda.stream())
+
+    def bump(self, key) -> int:
+        """Next value of the monotonic counter ``key``.  Flag values on the pad only ever grow, so every protocol
+        that signals through the pad draws its epochs from here: a second runtime on the same communicator then
+        continues where the first one stopped instead of meeting flags that already read "ready"."""
+        c = self.__dict__.setdefault("_counters", {})
+        c[key] = c.get(key, 0) + 1
+        return c[key]
 
     @property
     def max_buckets(self) -> int:

@@ -47,6 +47,9 @@ def balanced_vit_forward(tower, patches: torch.Tensor, grid_thw: torch.Tensor, g
         # nothing assigned to this rank: still contribute (empty) rows so that the exchange and the
         # autograd graph have the same shape everywhere
         width = tower.cfg.out_hidden_size
+        if any(hasattr(p, "to_local") for p in tower.parameters()):
+            raise RuntimeError("ViT frame balancing found a rank without frames while the tower's parameters are sharded "
+                               "(FSDP2): a sharded tower must run on every rank; turn vit_frame_parallel off for this layout")
         feats = got.new_zeros((0, width)) + 0.0 * sum(p.sum() for p in tower.parameters() if p.requires_grad).to(got.dtype)
         deep = [feats for _ in range(n_deep)] if n_deep else None
     back_send = [c // unit for c in recv_p]

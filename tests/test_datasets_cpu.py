@@ -395,3 +395,140 @@ def test_aero_realtime_processor_places_speech_on_the_audio_timeline(tmp_path):
     loss = model(**batch)["loss"]
     loss.backward()
     assert torch.isfinite(loss) and model.multi_modal_projector.linear_1.weight.grad.abs().sum() > 0
+
+
+# ------------------------------------------------------------------------------------------------
+# datasets with record handling of their own (datasets/families.py)
+def _write_video(path, n_frames=24, fps=8.0, size=(64, 64)):
+    import cv2
+
+    wr = cv2.VideoWriter(str(path), cv2.VideoWriter_fourcc(*"mp4v"), fps, size)
+    assert wr.isOpened()
+    rng = np.random.default_rng(0)
+    for i in range(n_frames):
+        wr.write((rng.integers(0, 255, (size[1], size[0], 3)) * 0 + (i * 10) % 255).astype(np.uint8))
+    wr.release()
+
+
+def _write_wav(path, seconds, sr=16000):
+    import wave as wavelib
+
+    data = (np.sin(np.arange(int(seconds * sr)) * 0.05) * 8000).astype(np.int16)
+    with wavelib.open(str(path), "wb") as w:
+        w.setnchannels(1), w.setsampwidth(2), w.setframerate(sr)
+        w.writeframes(data.tobytes())
+
+
+def _family_dataset(tmp_path, name, processor_type, records, **cfg):
+    from lmms_engine_b200.datasets import registry  # noqa: F401
+    from lmms_engine_b200.datasets.config import DatasetConfig
+    from lmms_engine_b200.mapping_func import DATASET_MAPPING
+
+    path = tmp_path / f"{name}.jsonl"
+    with open(path, "w") as f:
+        for r in records:
+            f.write(json.dumps(r) + "\n")
+    extra = cfg.pop("extra_kwargs", {})
+    c = DatasetConfig(dataset_type=name, dataset_format="jsonl", dataset_path=str(path), shuffle=False, packing=False,
+                      processor_config={"processor_name": "byte", "processor_type": processor_type}, fps=2, extra_kwargs=extra, **cfg)
+    return DATASET_MAPPING[name](c).build()
+
+
+def test_qwen3_vl_dataset_stamps_videos_with_the_times_of_the_sampled_frames(tmp_path):
+    """The Qwen3-VL datasets decode a video together with its metadata; the ``<t seconds>`` stamps in front of
+    every temporal step are the mean times of the frames that were actually sampled (8 fps source, 2 fps sampling)."""
+    from lmms_engine_b200.datasets.families import Qwen3VLDataset, Qwen3VLIterableDataset
+
+    _write_video(tmp_path / "v.mp4", n_frames=24, fps=8.0)
+    rec = {"messages": [{"role": "user", "content": [{"type": "video_url", "video_url": {"url": str(tmp_path / "v.mp4")}},
+                                                     {"type": "text", "text": "what happens?"}]},
+                        {"role": "assistant", "content": [{"type": "text", "text": "colours change"}]}]}
+    ds = _family_dataset(tmp_path, "qwen3_vl", "qwen3_vl", [rec])
+    assert isinstance(ds, Qwen3VLDataset)
+    frames, meta = ds.load_video_with_metadata(str(tmp_path / "v.mp4"))
+    assert meta["fps"] == 8.0 and meta["total_num_frames"] == 24 and len(meta["frame_times"]) == frames.shape[0] == 6
+    out = ds[0][0]
+    text = ds.processor.tokenizer.decode([t for t in out["input_ids"].tolist() if t < 256])
+    times = meta["frame_times"]
+    want = [f"<{(times[2 * i] + times[2 * i + 1]) / 2:.1f} seconds>" for i in range(3)]
+    assert all(w in text for w in want), (want, text)
+    assert out["video_grid_thw"].tolist()[0][0] == 3 and out["position_ids"].shape == (3, out["input_ids"].numel())
+    it = _family_dataset(tmp_path, "qwen3_vl_iterable", "qwen3_vl", [rec])
+    assert isinstance(it, Qwen3VLIterableDataset)
+    assert torch.equal(next(iter(it))[0]["input_ids"], out["input_ids"])
+
+
+def test_qwen_omni_dataset_chunks_audio_and_interleaves_sound_tracks(tmp_path):
+    """A 70 s clip with a 30 s limit becomes three audio placeholders; with ``use_audio_in_video`` the sound track
+    found next to a video is interleaved with the video tokens in 2-second chunks and the positions follow the
+    audio-visual index."""
+    from lmms_engine_b200.models.mrope import omni_positions_one
+
+    _write_wav(tmp_path / "long.wav", 70)
+    _write_video(tmp_path / "clip.mp4", n_frames=48, fps=8.0)
+    _write_wav(tmp_path / "clip.wav", 6)
+    rec_audio = {"messages": [{"role": "user", "content": [{"type": "audio_url", "audio_url": {"url": str(tmp_path / "long.wav")}},
+                                                           {"type": "text", "text": "transcribe"}]},
+                              {"role": "assistant", "content": [{"type": "text", "text": "a tone"}]}]}
+    rec_av = {"messages": [{"role": "user", "content": [{"type": "video_url", "video_url": {"url": str(tmp_path / "clip.mp4")}},
+                                                        {"type": "text", "text": "describe"}]},
+                           {"role": "assistant", "content": [{"type": "text", "text": "a tone over colours"}]}]}
+    ds = _family_dataset(tmp_path, "qwen_omni", "qwen2_5_omni", [rec_audio, rec_av], extra_kwargs={"use_audio_in_video": True})
+    a = ds[0][0]
+    assert a["audio_values"].shape[0] == 3  # 30 + 30 + 10 seconds
+    proc = ds.processor
+    ids = a["input_ids"]
+    runs = int(((ids == proc.audio_token_id) & (torch.roll(ids, 1) != proc.audio_token_id)).sum())
+    assert runs == 3
+    b = ds[1][0]
+    ids = b["input_ids"]
+    lo = int((ids == proc.vision_start).nonzero()[0])
+    hi = int((ids == proc.vision_end).nonzero()[0])
+    assert ids[lo + 1] == proc.tokenizer.convert_tokens_to_ids("<|audio_bos|>") and ids[hi - 1] == proc.tokenizer.convert_tokens_to_ids("<|audio_eos|>")
+    block = ids[lo + 2:hi - 1]
+    is_v = block == proc.video_token_id
+    assert is_v.any() and (~is_v).any() and set(block.tolist()) == {proc.video_token_id, proc.audio_token_id}
+    switches = int((is_v[1:] != is_v[:-1]).sum())
+    assert switches >= 3  # several 2-second chunks of each kind alternate
+    t, h, w = b["video_grid_thw"].tolist()[0]
+    assert int(is_v.sum()) == t * (h // 2) * (w // 2) and b["audio_values"].shape[0] == 1
+    want = omni_positions_one(ids.numpy(), proc.image_token_id, proc.video_token_id, proc.audio_token_id, [], b["video_grid_thw"].tolist(),
+                              b["second_per_grid_ts"].tolist(), 2, 25.0, 2.0)
+    assert np.array_equal(b["position_ids"].numpy(), want)
+    # video and audio tokens of one moment share temporal positions
+    pos = b["position_ids"][0, lo + 2:hi - 1]
+    assert pos[is_v].min() == pos[~is_v].min()
+    # without the option the sound track is ignored
+    plain = _family_dataset(tmp_path, "qwen_omni_iterable", "qwen2_5_omni", [rec_av])
+    c = next(iter(plain))[0]
+    assert "audio_values" not in c and int((c["input_ids"] == proc.audio_token_id).sum()) == 0
+
+
+def test_llava_video_dataset_time_instruction_frame_directories_and_csv(tmp_path):
+    from PIL import Image
+
+    _write_video(tmp_path / "v.mp4", n_frames=40, fps=8.0)
+    frames_dir = tmp_path / "frames"
+    frames_dir.mkdir()
+    for i in range(6):
+        Image.fromarray(np.full((32, 32, 3), i * 30, dtype=np.uint8)).save(frames_dir / f"{i:04d}.jpg")
+    rec = {"messages": [{"role": "user", "content": [{"type": "video_url", "video_url": {"url": str(tmp_path / "v.mp4")}},
+                                                     {"type": "text", "text": "what is shown?"}]},
+                        {"role": "assistant", "content": [{"type": "text", "text": "grey frames"}]}]}
+    rec_dir = {"messages": [{"role": "user", "content": [{"type": "video_url", "video_url": {"url": str(frames_dir)}},
+                                                         {"type": "text", "text": "and here?"}]},
+                            {"role": "assistant", "content": [{"type": "text", "text": "six frames"}]}]}
+    rec_csv = {"video": str(tmp_path / "v.mp4"), "prompt": "caption this", "answer": "a caption"}
+    ds = _family_dataset(tmp_path, "llava_video", "llava_video", [rec, rec_dir, rec_csv],
+                         extra_kwargs={"frames_upbound": 4, "force_sample": True, "add_time_instruction": True})
+    frames, meta = ds.load_video_with_time(str(tmp_path / "v.mp4"), None)
+    assert frames.shape[0] == 4 and meta["num_frames"] == 4 and abs(meta["video_time"] - 5.0) < 1e-6
+    assert meta["frame_time"].count("s") == 4
+    tok = ds.processor.tokenizer
+    text = tok.decode([t for t in ds[0][0]["input_ids"].tolist() if t < 256])
+    assert "The video lasts for 5.00 seconds, and 4 frames are uniformly sampled from it." in text and meta["frame_time"] in text
+    text_dir = tok.decode([t for t in ds[1][0]["input_ids"].tolist() if t < 256])
+    assert "The video lasts for 6.00 seconds" in text_dir
+    out_csv = ds[2][0]
+    text_csv = tok.decode([t for t in out_csv["input_ids"].tolist() if t < 256])
+    assert "caption this" in text_csv and "a caption" in text_csv and (out_csv["labels"] != -100).any()

@@ -740,3 +740,47 @@ def test_gated_deltanet_lm_loads_library_checkpoints_and_matches_token_recurrenc
     out = model(input_ids=ids, labels=ids, cu_seqlens=cu)
     out["loss"].backward()
     assert torch.isfinite(out["loss"]) and model.model.layers[1].attn.A_log.grad is not None
+
+
+def test_omni_audio_in_video_positions_match_upstream():
+    """Interleaved audio-visual blocks (``use_audio_in_video``): token order and ``(t, h, w)`` positions equal the
+    upstream index of Qwen2.5-Omni, including stand-alone clips and images in the same stream."""
+    pytest.importorskip("transformers")
+    import numpy as np
+    from transformers.models.qwen2_5_omni.configuration_qwen2_5_omni import Qwen2_5OmniThinkerConfig
+    from transformers.models.qwen2_5_omni.modeling_qwen2_5_omni import Qwen2_5OmniThinkerForConditionalGeneration
+
+    from lmms_engine_b200.models.mrope import interleave_av, omni_positions_one
+
+    text = dict(vocab_size=200, hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=1,
+                rope_scaling={"mrope_section": [2, 3, 3], "rope_type": "default", "type": "default"})
+    vis = dict(depth=1, hidden_size=16, intermediate_size=32, num_heads=2, patch_size=4, temporal_patch_size=2, spatial_merge_size=2,
+               out_hidden_size=32, window_size=16, fullatt_block_indexes=[0])
+    aud = dict(num_mel_bins=8, d_model=16, encoder_layers=1, encoder_attention_heads=2, encoder_ffn_dim=32, max_source_positions=100,
+               n_window=10, output_dim=32)
+    IMG, VID, AUD, VS, VE, AS, AE = 150, 151, 152, 153, 154, 155, 156
+    hc = Qwen2_5OmniThinkerConfig(text_config=text, vision_config=vis, audio_config=aud, image_token_index=IMG, video_token_index=VID,
+                                  audio_token_index=AUD, vision_start_token_id=VS, vision_end_token_id=VE, audio_start_token_id=AS,
+                                  audio_end_token_id=AE, position_id_per_seconds=25, seconds_per_chunk=2)
+    upstream = Qwen2_5OmniThinkerForConditionalGeneration(hc)
+    rng = np.random.default_rng(0)
+    for trial in range(8):
+        grid_v = [(int(rng.integers(2, 6)), 4, int(rng.choice([4, 8])))]
+        spg = [float(rng.choice([1.0, 2.0, 0.5]))]
+        mel = int(rng.integers(100, 900))
+        n_a = ((mel - 1) // 2 + 1 - 2) // 2 + 1
+        t, h, w = grid_v[0]
+        vt = np.floor(np.repeat(np.arange(t), (h // 2) * (w // 2)) * spg[0] * 25).astype(np.int64)
+        block = []
+        for kind, lo, hi in interleave_av(vt, n_a, 50):
+            block += [VID if kind == "video" else AUD] * (hi - lo)
+        ids = [1, 2, 3, VS] + [IMG] * 4 + [VE, 5, 6, VS, AS] + block + [AE, VE, 7, 8, 9]
+        mels = [mel]
+        if trial % 2:
+            ids += [AS] + [AUD] * 37 + [AE, 10, 11]
+            mels.append(37 * 4)
+        ids_t = torch.tensor([ids])
+        ref, _ = upstream.get_rope_index(ids_t, torch.tensor([(1, 4, 4)]), torch.tensor(grid_v), torch.ones_like(ids_t), True,
+                                         torch.tensor(mels), torch.tensor(spg))
+        mine = omni_positions_one(np.array(ids), IMG, VID, AUD, [(1, 4, 4)], grid_v, spg, 2, 25.0, 2.0)
+        assert np.array_equal(ref[:, 0].numpy(), mine), trial
