@@ -20,7 +20,7 @@ class DatasetConfig(Args):
     shuffle: bool = True
     data_seed: Optional[int] = 42
     eval_dataset_path: Optional[str] = None
-    object_storage: Optional[Literal["azure", "gcs", "none"]] = "none"
+    object_storage: Optional[str] = "none"  # azure | gcs | none | a back end added with register_storage_backend
     bucket_name: Optional[str] = None
     packing: Optional[bool] = False
     packing_strategy: Optional[str] = None

@@ -23,21 +23,51 @@ class MultiModalDataLoadingMixin:
             return os.path.join(data_folder, path)
         return path
 
+    # ---- object storage ------------------------------------------------------------------------
+    def storage(self):
+        """Client for ``config.object_storage`` / ``config.bucket_name`` (``None`` for local files), built on first
+        use in the process that reads the data (dataloader workers each get their own)."""
+        kind = getattr(self.config, "object_storage", "none")
+        if kind in (None, "none", ""):
+            return None
+        cached = self.__dict__.get("_storage_client")
+        if cached is None or cached[0] != os.getpid():
+            from ..utils.object_storage import make_client
+
+            cached = (os.getpid(), make_client(kind, getattr(self.config, "bucket_name", None)))
+            self.__dict__["_storage_client"] = cached
+        return cached[1]
+
+    def open_object(self, blob: str) -> io.BytesIO:
+        """In-memory stream of a blob of the configured bucket."""
+        from ..utils.object_storage import fetch_stream
+
+        client = self.storage()
+        if client is None:
+            raise ValueError("open_object needs dataset_config.object_storage (gcs | azure | a registered back end)")
+        return fetch_stream(client, blob)
+
+    def local_copy(self, full: str) -> str:
+        """A path that decoders can open: the file itself, or a cached download of the blob."""
+        client = self.storage()
+        if client is None:
+            return full
+        from ..utils.object_storage import fetch_to_cache
+
+        return fetch_to_cache(client, full, (getattr(self.config, "extra_kwargs", None) or {}).get("object_cache_dir"))
+
     def load_image(self, path: str, data_folder: Optional[str] = None):
         from PIL import Image
 
         full = self._resolve(path, data_folder)
-        storage = getattr(self.config, "object_storage", "none")
-        if storage not in (None, "none") and "://" in full:
-            stream = self.open_object(full)
-            return Image.open(stream).convert("RGB")
+        if self.storage() is not None:
+            return Image.open(self.open_object(full)).convert("RGB")
         return Image.open(full).convert("RGB")
-
-    def open_object(self, url: str) -> io.BytesIO:
-        raise NotImplementedError("object storage clients (gcs / azure) are injected by the deployment")
 
     def load_audio(self, path: str, sr: int = 16000, data_folder: Optional[str] = None) -> Tuple[np.ndarray, int]:
         full = self._resolve(path, data_folder)
+        if self.storage() is not None:
+            full = self.local_copy(full)
         try:
             import soundfile as sf
 
@@ -69,7 +99,7 @@ class MultiModalDataLoadingMixin:
     def load_video(self, path: str, data_folder: Optional[str] = None, video_start: Optional[float] = None,
                    video_end: Optional[float] = None) -> Tuple[np.ndarray, float]:
         """Frames ``[n, H, W, 3] uint8`` and the sampled frames-per-second."""
-        full = self._resolve(path, data_folder)
+        full = self.local_copy(self._resolve(path, data_folder))
         backend = getattr(self.config, "video_backend", "qwen_vl_utils")
         if backend == "decord":
             try:
@@ -88,7 +118,7 @@ class MultiModalDataLoadingMixin:
         """Frames plus what a processor needs to talk about time: ``video_time`` (seconds of the source), ``fps`` of
         the source, ``frames_indices`` and ``frame_times`` of the sampled frames, ``total_num_frames`` and the
         effective ``sample_fps``.  Decoded with decord when it is installed, with OpenCV otherwise."""
-        full = self._resolve(path, data_folder)
+        full = self.local_copy(self._resolve(path, data_folder))
         try:
             import decord
 

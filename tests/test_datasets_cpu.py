@@ -532,3 +532,49 @@ def test_llava_video_dataset_time_instruction_frame_directories_and_csv(tmp_path
     out_csv = ds[2][0]
     text_csv = tok.decode([t for t in out_csv["input_ids"].tolist() if t < 256])
     assert "caption this" in text_csv and "a caption" in text_csv and (out_csv["labels"] != -100).any()
+
+
+def test_object_storage_serves_images_audio_and_videos(tmp_path):
+    """Media named by bucket + blob path go through a storage client: images from memory, audio and videos through a
+    cached local copy; a flaky back end is retried, a missing blob raises (so the record is skipped and logged)."""
+    from PIL import Image
+
+    from lmms_engine_b200.utils import object_storage as osto
+
+    bucket = tmp_path / "bucket"
+    (bucket / "media").mkdir(parents=True)
+    Image.fromarray(np.full((40, 40, 3), 90, dtype=np.uint8)).save(bucket / "media" / "a.png")
+    _write_wav(bucket / "media" / "a.wav", 1)
+    _write_video(bucket / "media" / "a.mp4", n_frames=16, fps=8.0)
+
+    class Flaky(osto.LocalDirectoryClient):
+        calls = 0
+
+        def read(self, blob):
+            Flaky.calls += 1
+            if Flaky.calls % 2:
+                raise ConnectionError("transient")
+            return super().read(blob)
+
+    osto.register_storage_backend("flaky_test", Flaky)
+    rec = {"messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "media/a.png"}},
+                                                     {"type": "video_url", "video_url": {"url": "media/a.mp4"}},
+                                                     {"type": "text", "text": "hi"}]},
+                        {"role": "assistant", "content": [{"type": "text", "text": "ok"}]}]}
+    ds = _family_dataset(tmp_path, "vision", "qwen2_5_vl", [rec], object_storage="flaky_test", bucket_name=str(bucket),
+                         extra_kwargs={"object_cache_dir": str(tmp_path / "cache")})
+    import lmms_engine_b200.utils.object_storage as mod
+
+    old = mod.time.sleep
+    mod.time.sleep = lambda s: None
+    try:
+        out = ds[0][0]
+        wav, sr = ds.load_audio("media/a.wav")
+        with pytest.raises(IOError):
+            ds.load_image("media/missing.png")
+    finally:
+        mod.time.sleep = old
+    assert "pixel_values" in out and "pixel_values_videos" in out and len(wav) == sr
+    assert len(os.listdir(tmp_path / "cache")) == 2  # the video and the audio clip
+    with pytest.raises(ValueError, match="bucket_name"):
+        osto.make_client("gcs", None)
