@@ -39,7 +39,8 @@ class PackedCollator:
         }
         if any("position_ids" in s for s in samples):  # multimodal (3, n) positions from a processor
             out["position_ids"] = torch.cat([s["position_ids"] for s in samples], dim=-1)
-        for key in samples[0].keys():
+        keys = list(dict.fromkeys(k for s in samples for k in s.keys()))  # a text-only first sample must not hide the others' media
+        for key in keys:
             if key in ("input_ids", "labels", "position_ids", "attention_mask"):
                 continue
             vals = [s[key] for s in samples if key in s and s[key] is not None]

@@ -5,3 +5,4 @@ from . import synthetic  # noqa: F401
 from . import iterable, naive, processor  # noqa: F401
 from . import extra  # noqa: F401
 from . import families  # noqa: F401
+from . import codec_video  # noqa: F401

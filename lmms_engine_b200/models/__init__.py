@@ -70,3 +70,7 @@ register_model("aero_realtime", AeroRealtimeConfig, AeroRealtimeModel, "image_te
 from .gated_deltanet import GatedDeltaNetConfig, GatedDeltaNetLM  # noqa: E402
 
 register_model("gated_deltanet", GatedDeltaNetConfig, GatedDeltaNetLM, "causal_lm")
+
+from .llava_ov2 import LlavaOnevision2  # noqa: E402
+
+register_model("llava_onevision2", VLConfig, LlavaOnevision2, "image_text_to_text")

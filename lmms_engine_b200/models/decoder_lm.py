@@ -271,6 +271,8 @@ class PackedContext:
     aux: List[Any] = field(default_factory=list)
     deepstack: Optional[List[torch.Tensor]] = None  # per-layer additive visual features
     deepstack_index: Optional[torch.Tensor] = None
+    split_group: Any = None  # group over which the token stream is split between blocks (None: not split)
+    split_total: int = 0  # padded length of the whole stream
 
 
 def unpad_batch(input_ids, attention_mask, labels=None, position_ids=None):
@@ -331,7 +333,13 @@ class DecoderBackbone(nn.Module):
                 h, residual = layer(h, residual, ctx)
             if ctx.deepstack is not None and i < len(ctx.deepstack):
                 # Qwen3-VL deepstack: add visual features to the stream at visual positions
-                h = h.index_add(0, ctx.deepstack_index, ctx.deepstack[i].to(h.dtype))
+                if ctx.split_group is None:
+                    h = h.index_add(0, ctx.deepstack_index, ctx.deepstack[i].to(h.dtype))
+                else:
+                    # the stream is split over a sequence- / tensor-parallel group while the indices address the whole
+                    # sequence: scatter into a full-length buffer and keep this rank's slice (no host round trip)
+                    full = h.new_zeros((ctx.split_total, h.shape[1])).index_add_(0, ctx.deepstack_index, ctx.deepstack[i].to(h.dtype))
+                    h = h + sp.slice_for_rank(full, ctx.split_group)
         out, _ = self.norm(h, residual)
         return out
 
@@ -442,6 +450,7 @@ class DecoderLM(nn.Module):
         elif sg_size > 1:
             inputs_embeds = sp.slice_for_rank(sp.pad_to_multiple(inputs_embeds, sg_size, 0), sg)
         if sg_size > 1:
+            ctx.split_group, ctx.split_total = sg, T_full + (-T_full) % sg_size
             # padded tail tokens form a trailing pseudo-document
             pad = (-T_full) % sg_size
             if pad:

@@ -44,6 +44,11 @@ class VLConfig:
         """LLaVA-OneVision-1.5: Rice tower, Qwen3 decoder, plain 1-D rotary positions."""
         return self.model_type.startswith("llavaonevision1_5")
 
+    @property
+    def is_ov2(self) -> bool:
+        """LLaVA-OneVision-2: position-carrying patch tower, Qwen3 decoder, plain 1-D rotary positions."""
+        return self.model_type.startswith("llava_onevision2")
+
     @classmethod
     def from_dict(cls, d: Dict[str, Any]) -> "VLConfig":
         d = dict(d)
@@ -54,8 +59,17 @@ class VLConfig:
         if not text:
             text = {k: v for k, v in d.items() if k in {f for f in DecoderConfig.__dataclass_fields__}}
         moe = "moe" in mt
-        rice = mt.startswith("llavaonevision1_5")
-        if rice:
+        rice = mt.startswith("llavaonevision1_5") or mt.startswith("llava_onevision2")
+        if mt.startswith("llava_onevision2"):
+            text["model_type"] = "qwen3"
+            text["mrope_section"] = None
+            vis["model_type"] = "onevision2_vit"
+            vis.setdefault("temporal_patch_size", 1)
+            vis.setdefault("hidden_act", "gelu")
+            vis.setdefault("hidden_size", 1024)
+            vis.setdefault("intermediate_size", 4096)
+            vis.setdefault("depth", 24)
+        elif rice:
             text["model_type"] = "qwen3"  # q/k RMSNorm on the head dimension, no attention bias
             text["mrope_section"] = None
             vis["model_type"] = "rice_vit"
@@ -110,6 +124,7 @@ class VLConfig:
              "vision_start_token_id": self.vision_start_token_id, "vision_end_token_id": self.vision_end_token_id,
              "tie_word_embeddings": self.tie_word_embeddings,
              "architectures": self.architectures or [
+                 "LlavaOnevision2ForConditionalGeneration" if self.is_ov2 else
                  "LLaVAOneVision1_5_ForConditionalGeneration" if self.is_rice else
                  "Qwen3VLForConditionalGeneration" if self.is_qwen3 else "Qwen2_5_VLForConditionalGeneration"]}
         d.update(self.extra)
@@ -131,7 +146,11 @@ class VLModel(nn.Module):
     def __init__(self, cfg: VLConfig):
         super().__init__()
         self.config = cfg
-        if cfg.is_rice:
+        if cfg.is_ov2:
+            from .llava_ov2 import OneVisionTower
+
+            self.visual = OneVisionTower(cfg.vision_config)
+        elif cfg.is_rice:
             from .rice import RiceVisionTower
 
             self.visual = RiceVisionTower(cfg.vision_config)
@@ -215,7 +234,7 @@ class VLModel(nn.Module):
         lm = self.language_model
         had_mrope = position_ids is not None and position_ids.dim() >= 2 and position_ids.shape[-2] == 3
         ids, labels, pos, cu, _ = lm.prepare_packed(input_ids, attention_mask, labels, position_ids if had_mrope else None, cu_seqlens)
-        if not had_mrope and not cfg.is_rice:
+        if not had_mrope and not cfg.is_rice and not cfg.is_ov2:
             grids, secs = [], []
             for g, is_video in ((image_grid_thw, False), (video_grid_thw, True)):
                 if g is None:

@@ -8,7 +8,49 @@ import torch
 import torch.distributed as dist
 
 
+def vl_deepstack(mode):
+    """Qwen3-VL style model (deepstack features added at visual positions) with the token stream split over a
+    Ulysses group or a tensor-parallel group: same loss as the unsharded model."""
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    from torch.distributed.device_mesh import init_device_mesh
+
+    from lmms_engine_b200.mapping_func import create_model_from_config
+    from lmms_engine_b200.parallel.tensor_parallel import shard_decoder_for_tp
+
+    text = dict(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                head_dim=16, tie_word_embeddings=False, rope_scaling={"mrope_section": [4, 2, 2], "mrope_interleaved": True})
+    vis = dict(depth=2, hidden_size=32, intermediate_size=64, num_heads=2, patch_size=4, temporal_patch_size=2, spatial_merge_size=2,
+               out_hidden_size=64, num_position_embeddings=16, deepstack_visual_indexes=[0, 1], in_channels=3)
+    cfg = dict(model_type="qwen3_vl", text_config=text, vision_config=vis, image_token_id=290, video_token_id=291, vision_start_token_id=293)
+    torch.manual_seed(0)
+    full = create_model_from_config("qwen3_vl", dict(cfg)).float()
+    torch.manual_seed(0)
+    model = create_model_from_config("qwen3_vl", dict(cfg)).float()
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, 280, (1, 61), generator=g)  # odd length: the split pads
+    ids[0, 2], ids[0, 3:7] = 293, 290
+    ids[0, 30], ids[0, 31:47] = 293, 290
+    pix = torch.randn(16 + 64, 3 * 2 * 4 * 4, generator=g)
+    grid = torch.tensor([[1, 4, 4], [1, 8, 8]])
+    batch = dict(input_ids=ids, attention_mask=torch.ones_like(ids), labels=ids, pixel_values=pix, image_grid_thw=grid)
+    ref = full(**batch)["loss"]
+    if mode == "vl_ulysses":
+        model.sp_group = dist.group.WORLD
+    else:
+        mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("tp",))
+        shard_decoder_for_tp(model.language_model, mesh, mesh.get_group())
+    loss = model(**batch)["loss"]
+    loss.backward()
+    assert abs(float(loss) - float(ref)) < 1e-4, (mode, float(loss), float(ref))
+    if rank == 0:
+        print(f"{mode} ok")
+    dist.destroy_process_group()
+
+
 def main(mode):
+    if mode.startswith("vl_"):
+        return vl_deepstack(mode)
     dist.init_process_group("gloo")
     rank, world = dist.get_rank(), dist.get_world_size()
     from torch.distributed.device_mesh import init_device_mesh

@@ -68,6 +68,13 @@ def test_ulysses_matches_unsharded(world):
     assert "ulysses ok" in torchrun("tp_run.py", world, "ulysses")
 
 
+@pytest.mark.parametrize("mode", ["vl_ulysses", "vl_tp"])
+def test_deepstack_features_follow_the_split_token_stream(mode):
+    """Deepstack visual features are indexed over the whole sequence; under Ulysses or sequence-parallel tensor
+    parallelism every rank adds the rows that fall into its slice."""
+    assert f"{mode} ok" in torchrun("tp_run.py", 2, mode)
+
+
 def test_ulysses_hybrid_linear_attention_matches_unsharded():
     """Qwen3.5 layers under Ulysses: the linear-attention heads (convolution + delta rule) and the gated-attention heads
     are exchanged around their sequence-wide parts; loss and gradients equal the single-process model."""
