@@ -255,24 +255,29 @@ class DecoderLayer(nn.Module):
         return out, residual
 
 
-@dataclass
 class PackedContext:
-    """Everything a layer needs to know about the packed token stream of this step."""
+    """Everything a layer needs to know about the packed token stream of this step.
 
-    cu_seqlens: torch.Tensor  # int32 [n_docs + 1] over the FULL (un-split) sequence
-    max_seqlen: int
-    cos: torch.Tensor  # fp32 [T_full, rot_dim]
-    sin: torch.Tensor
-    causal: bool = True
-    sp_group: Any = None
-    sp_size: int = 1
-    tp_group: Any = None
-    tp_size: int = 1
-    aux: List[Any] = field(default_factory=list)
-    deepstack: Optional[List[torch.Tensor]] = None  # per-layer additive visual features
-    deepstack_index: Optional[torch.Tensor] = None
-    split_group: Any = None  # group over which the token stream is split between blocks (None: not split)
-    split_total: int = 0  # padded length of the whole stream
+    Deliberately NOT a dataclass: FSDP2's ``cast_forward_inputs`` walks into dataclass arguments of every wrapped
+    module, rebuilds them and casts their floating-point tensors to the parameter dtype.  That would turn the fp32
+    rotary tables into bf16 behind kernels that read them as fp32, and hand every layer a copy of ``aux`` so that
+    router losses appended by the layers never reach the model.  A plain object is passed through untouched."""
+
+    def __init__(self, cu_seqlens: torch.Tensor, max_seqlen: int, cos: torch.Tensor, sin: torch.Tensor, causal: bool = True,
+                 sp_group: Any = None, sp_size: int = 1, tp_group: Any = None, tp_size: int = 1, aux: Optional[List[Any]] = None,
+                 deepstack: Optional[List[torch.Tensor]] = None, deepstack_index: Optional[torch.Tensor] = None,
+                 split_group: Any = None, split_total: int = 0):
+        self.cu_seqlens = cu_seqlens  # int32 [n_docs + 1] over the FULL (un-split) sequence
+        self.max_seqlen = max_seqlen
+        self.cos, self.sin = cos, sin  # fp32 [T_full, rot_dim]
+        self.causal = causal
+        self.sp_group, self.sp_size = sp_group, sp_size
+        self.tp_group, self.tp_size = tp_group, tp_size
+        self.aux = [] if aux is None else aux
+        self.deepstack = deepstack  # per-layer additive visual features
+        self.deepstack_index = deepstack_index
+        self.split_group = split_group  # group over which the token stream is split between blocks (None: not split)
+        self.split_total = split_total  # padded length of the whole stream
 
 
 def unpad_batch(input_ids, attention_mask, labels=None, position_ids=None):

@@ -55,6 +55,19 @@ class Experts(nn.Module):
         self.down_proj = nn.Parameter(torch.empty(n, hidden, inter))
         self.num_experts, self.hidden, self.inter = n, hidden, inter
 
+    def forward(self, xp: torch.Tensor, perm) -> torch.Tensor:
+        """Grouped SwiGLU MLP over expert-major rows.  Every caller (the local path and the expert-parallel
+        dispatchers) goes through ``forward`` so that a wrapper's hooks (FSDP2 unshard / mixed precision) run; under
+        expert parallelism the stacked parameters are DTensors on the ep mesh and the rows are this rank's experts'."""
+        gate_up, down = self.gate_up_proj, self.down_proj
+        if hasattr(gate_up, "to_local"):
+            gate_up, down = gate_up.to_local(), down.to_local()
+        if xp.shape[0] > 0:
+            return moe_ops.grouped_mlp(xp, gate_up, down, perm)
+        # no rows for this rank's experts in this step: keep the parameters in the graph (their gradient hooks and
+        # the collectives behind them must still run on every rank)
+        return xp.new_zeros((0, self.hidden)) + 0.0 * (gate_up.sum() + down.sum()).to(xp.dtype)
+
 
 class SparseMoeBlock(nn.Module):
     def __init__(self, cfg: MoEConfig):
@@ -76,7 +89,7 @@ class SparseMoeBlock(nn.Module):
         else:
             perm = moe_ops.build_permutation(idx, w, counts)
             xp = moe_ops.dispatch(x, perm)
-            yp = moe_ops.grouped_mlp(xp, self.experts.gate_up_proj, self.experts.down_proj, perm)
+            yp = self.experts(xp, perm)
             y = moe_ops.combine(yp, w, perm)
         if cfg.shared_expert_intermediate_size:
             s = self.shared_expert(x)

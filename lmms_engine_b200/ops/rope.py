@@ -107,6 +107,11 @@ class _RopeFn(torch.autograd.Function):
 def rope_apply(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
     """Rotate ``x [T, H, D]`` by the per-token table; differentiable."""
     if x.is_cuda and x.dtype == torch.bfloat16 and cos.shape[-1] % 16 == 0 and x.shape[-1] % 8 == 0:
+        if cos.dtype != torch.float32 or sin.dtype != torch.float32:
+            # the kernel reads the tables as fp32; a table that some wrapper cast down would be read past its end
+            raise TypeError(f"rotary tables must be float32, got {cos.dtype} / {sin.dtype}")
+        if cos.shape[0] < x.shape[0]:
+            raise ValueError(f"rotary table has {cos.shape[0]} rows for {x.shape[0]} tokens")
         return _RopeFn.apply(x, cos.contiguous(), sin.contiguous())
     return rope_apply_ref(x, cos, sin)
 

@@ -102,11 +102,7 @@ class ExpertParallel:
         used = sum(in_splits)
         recv = _AllToAllRows.apply(xp[:used], in_splits, out_splits, self.group)
         grouped = recv.index_select(0, regroup)
-        gate_up, down = _local_tensor(experts.gate_up_proj), _local_tensor(experts.down_proj)
-        if local.rows > 0:
-            yp = moe_ops.grouped_mlp(grouped, gate_up, down, local)
-        else:
-            yp = grouped.new_zeros((0, x.shape[1])) + 0.0 * (gate_up.sum() + down.sum()).to(grouped.dtype)
+        yp = experts(grouped, local)
         back = _AllToAllRows.apply(yp.index_select(0, inverse), out_splits, in_splits, self.group)
         if used < perm.rows:
             back = torch.cat([back, back.new_zeros((perm.rows - used, back.shape[1]))], 0)

@@ -28,7 +28,7 @@ import torch.distributed as dist
 
 from ..ops import _cuda
 from ..ops import moe as moe_ops
-from .expert_parallel import ExpertParallel, _local_tensor, _pad
+from .expert_parallel import ExpertParallel, _pad
 from .fused_comm import SymmPool
 
 TILE = moe_ops.TILE
@@ -152,11 +152,7 @@ class PeerExpertParallel(ExpertParallel):
         dest_rank, dest_row, local, cap = self.layout(counts, perm)
         self._stages(cap, x.shape[1])
         grouped = _PeerDispatch.apply(x.contiguous(), self, perm, dest_rank, dest_row, local.rows)
-        gate_up, down = _local_tensor(experts.gate_up_proj), _local_tensor(experts.down_proj)
-        if local.rows > 0:
-            yp = moe_ops.grouped_mlp(grouped, gate_up, down, local)
-        else:
-            yp = grouped.new_zeros((0, x.shape[1])) + 0.0 * (gate_up.sum() + down.sum()).to(grouped.dtype)
+        yp = experts(grouped, local)
         return _PeerCombine.apply(yp, w, self, perm, dest_rank, dest_row)
 
 

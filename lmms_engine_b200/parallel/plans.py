@@ -26,13 +26,21 @@ from . import process_group_manager as pgm_mod
 from .parallelize import register_parallel_plan
 
 
-def _mp_policy(args, dtype):
+def mixed_precision_policy(args, dtype, root: bool = False):
+    """FSDP2 policy of a wrapped module.  ``cast_forward_inputs`` is off: the models cast their own inputs (as they
+    must under the native runtimes, which have no such hook), and FSDP's cast walks into every tensor, container and
+    dataclass argument of every wrapped block - it would turn fp32 rotary tables, which the kernels read as fp32, into
+    bf16 ones.  ``output_dtype`` describes what the MODEL returns, so only the root module carries it; blocks hand
+    their activations on in the compute dtype."""
     from torch.distributed.fsdp import MixedPrecisionPolicy
 
     if dtype is None or dtype == torch.float32:
         return None
     return MixedPrecisionPolicy(param_dtype=dtype, reduce_dtype=str_to_dtype(args.reduce_dtype),
-                                output_dtype=str_to_dtype(args.output_dtype))
+                                output_dtype=str_to_dtype(args.output_dtype) if root else None, cast_forward_inputs=False)
+
+
+_mp_policy = mixed_precision_policy
 
 
 def _fsdp_kwargs(args, mesh, mp):
@@ -79,7 +87,9 @@ def parallelize_moe(model, args, dtype=None, **_):
             if tower is not None and any(p.requires_grad for p in tower.parameters()):
                 fully_shard(tower, **_fsdp_kwargs(args, fsdp_mesh, mp))
     for layer in text.model.layers:
-        if isinstance(layer.mlp, SparseMoeBlock) and pgm.enable_ep and pgm.layout.dp_shard_mod_ep > 1:
+        if isinstance(layer.mlp, SparseMoeBlock) and pgm.enable_ep:
+            # also when the experts are purely expert-parallel (a mesh of one rank): the wrap is what gives them the
+            # fp32 master / bf16 compute split of the mixed-precision policy
             fully_shard(layer.mlp.experts, shard_placement_fn=lambda p: Shard(1),
                         **_fsdp_kwargs(args, pgm.device_mesh["dp_shard_mod_ep"], mp))
         for mixer_name in ("self_attn", "linear_attn"):  # hybrid decoders have one or the other per layer
@@ -99,7 +109,7 @@ def parallelize_moe(model, args, dtype=None, **_):
         for m in model.modules():
             if isinstance(m, SparseMoeBlock):
                 ignored |= set(m.experts.parameters())
-    fully_shard(model, ignored_params=ignored or None, **_fsdp_kwargs(args, fsdp_mesh, mp))
+    fully_shard(model, ignored_params=ignored or None, **_fsdp_kwargs(args, fsdp_mesh, mixed_precision_policy(args, dtype, root=True)))
     return model
 
 

@@ -56,9 +56,7 @@ def shard_decoder_for_tp(decoder_lm, tp_mesh, tp_group) -> None:
 
 
 def apply_tensor_parallel(model, args, dtype=None):
-    from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
-
-    from ..utils.train_utils import str_to_dtype
+    from torch.distributed.fsdp import fully_shard
 
     pgm = pgm_mod.process_group_manager
     if pgm.enable_ep:
@@ -66,10 +64,9 @@ def apply_tensor_parallel(model, args, dtype=None):
     text = getattr(model, "language_model", model)  # VL wrappers keep the decoder here
     if pgm.enable_tp:
         shard_decoder_for_tp(text, pgm.tp_mesh, pgm.tp_group)
-    mp = None
-    if dtype is not None and dtype != torch.float32:
-        mp = MixedPrecisionPolicy(param_dtype=dtype, reduce_dtype=str_to_dtype(args.reduce_dtype),
-                                  output_dtype=str_to_dtype(args.output_dtype))
+    from .plans import mixed_precision_policy
+
+    mp = mixed_precision_policy(args, dtype)
     kw = dict(mesh=pgm.device_mesh["fsdp"], reshard_after_forward=bool((args.fsdp_config or {}).get("reshard_after_forward", True)))
     if mp is not None:
         kw["mp_policy"] = mp
@@ -80,5 +77,8 @@ def apply_tensor_parallel(model, args, dtype=None):
         for blk in getattr(vis, "blocks", []):
             fully_shard(blk, **kw)
         fully_shard(vis, **kw)
+    root_mp = mixed_precision_policy(args, dtype, root=True)
+    if root_mp is not None:
+        kw["mp_policy"] = root_mp
     fully_shard(model, **kw)
     return model

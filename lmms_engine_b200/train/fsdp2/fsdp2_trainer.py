@@ -136,7 +136,7 @@ class FSDP2SFTTrainer:
             self.model.to(device=self.device, dtype=dtype)
             return
         # ---- stock FSDP2 (ZeRO-3), also the path for TP / EP / HSDP meshes ------------------
-        from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
+        from torch.distributed.fsdp import fully_shard
 
         from ...parallel.parallelize import apply_parallelize, has_parallel_plan
 
@@ -148,10 +148,9 @@ class FSDP2SFTTrainer:
             apply_parallelize(self.model, model_type, args, dtype)
             return
         self.model.to(self.device)
-        mp = None
-        if dtype != torch.float32:
-            mp = MixedPrecisionPolicy(param_dtype=dtype, reduce_dtype=str_to_dtype(args.reduce_dtype),
-                                      output_dtype=str_to_dtype(args.output_dtype))
+        from ...parallel.plans import mixed_precision_policy
+
+        mp = mixed_precision_policy(args, dtype)
         mesh = self.pgm.fsdp_mesh
         fsdp_cfg = args.fsdp_config or {}
         kw = dict(mesh=mesh, reshard_after_forward=bool(fsdp_cfg.get("reshard_after_forward", True)))
@@ -161,6 +160,9 @@ class FSDP2SFTTrainer:
         for module in self.model.modules():
             if type(module).__name__ in wrap_names:
                 fully_shard(module, **kw)
+        root_mp = mixed_precision_policy(args, dtype, root=True)
+        if root_mp is not None:
+            kw["mp_policy"] = root_mp
         fully_shard(self.model, **kw)
 
     def native_grad_dtype(self) -> torch.dtype:

@@ -47,10 +47,13 @@ def main():
     from lmms_engine_b200.parallel.parallelize import apply_parallelize, has_parallel_plan
     from lmms_engine_b200.parallel.process_group_manager import setup_process_group_manager
 
-    setup_process_group_manager(tp_size=1, cp_size=1, pp_size=1, dp_size=world, ep_size=world, device_type="cpu")
+    ep = int(sys.argv[1]) if len(sys.argv) > 1 else world  # ep < world: the experts are also FSDP-sharded over the other ranks
+    setup_process_group_manager(tp_size=1, cp_size=1, pp_size=1, dp_size=world, ep_size=ep, device_type="cpu")
     args = types.SimpleNamespace(fsdp_config={"reshard_after_forward": True}, reduce_dtype="float32", output_dtype="float32")
     done = []
     for family, cfg in family_configs():
+        if ep < world and family not in ("qwen3_moe", "qwen3_vl_moe"):
+            continue
         assert has_parallel_plan(family), family
         torch.manual_seed(0)
         full = create_model_from_config(family, dict(cfg)).float().train()
@@ -61,7 +64,7 @@ def main():
         assert blocks and all(b.ep is not None for b in blocks), family
         for b in blocks:
             p = b.experts.gate_up_proj
-            assert isinstance(p, DTensor) and p.to_local().shape[0] == TEXT["num_experts"] // world, (family, type(p))
+            assert isinstance(p, DTensor) and p.to_local().shape[0] == TEXT["num_experts"] // ep, (family, type(p))
         g = torch.Generator().manual_seed(11 + rank)
         n = 60 + 9 * rank
         ids = torch.randint(0, 280, (1, n), generator=g)
@@ -75,6 +78,19 @@ def main():
         grads = [p.grad for p in model.parameters() if p.grad is not None]
         assert len(grads) > 10, family
         done.append(family)
+    # bf16 policy: FSDP must hand the step's context to every wrapped block untouched (fp32 rotary tables, ONE aux list)
+    torch.manual_seed(0)
+    cfg = dict(TEXT, router_aux_loss_coef=0.01)
+    model = create_model_from_config("qwen3_moe", cfg).train()
+    apply_parallelize(model, "qwen3_moe", args, torch.bfloat16)
+    seen = []
+    for layer in model.model.layers:
+        layer.self_attn.register_forward_pre_hook(lambda m, a: seen.append((a[1].cos.dtype, id(a[1].aux))))
+    ids = torch.randint(0, 280, (70,), generator=torch.Generator().manual_seed(3 + rank))
+    out = model(input_ids=ids, labels=ids, cu_seqlens=torch.tensor([0, 30, 70], dtype=torch.int32))
+    assert len(seen) == 2 and all(d == torch.float32 for d, _ in seen), seen
+    assert len({i for _, i in seen}) == 1 and len(out["aux"]) == 2, (seen, len(out["aux"]))
+    out["loss"].backward()
     if rank == 0:
         print("expert parallel plans ok: " + " ".join(done))
     dist.destroy_process_group()

@@ -38,6 +38,12 @@ def test_expert_parallel_plans_of_all_moe_families():
     assert "expert parallel plans ok: qwen3_moe qwen3_5_moe_text qwen3_vl_moe qwen3_omni_moe_thinker aero_realtime" in out
 
 
+def test_expert_parallel_plan_with_experts_also_sharded_by_fsdp():
+    """4 ranks, ep 2: the experts are split over the ep mesh (dim 0) AND FSDP-sharded over the two replicas (dim 1)."""
+    out = torchrun("ep_plan_run.py", 4, "2")
+    assert "expert parallel plans ok: qwen3_moe qwen3_vl_moe" in out
+
+
 def test_rank_layout_arithmetic():
     from lmms_engine_b200.parallel.process_group_manager import RankLayout
 
