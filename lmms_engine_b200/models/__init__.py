@@ -24,7 +24,10 @@ for _mt in ("qwen3_dllm", "dream_dllm", "llada_dllm"):
     register_model(_mt, DLLMConfig, DiffusionLM, "masked_lm")
 register_model("sit", SiTConfig, SiT, "general")
 register_model("wanvideo", WanConfig, WanDiT, "general")
-register_model("rae_siglip", RaeConfig, RaeAutoencoder, "general")
+from .rae import RaeSiglip, RaeSiglipConfig  # noqa: E402
+
+register_model("rae_siglip", RaeSiglipConfig, RaeSiglip, "general")
+register_model("rae_toy", RaeConfig, RaeAutoencoder, "general")
 register_model("bagel", BagelConfig, Bagel, "general")
 
 __all__ = ["ModelConfig", "DecoderConfig", "DecoderLM", "MoEConfig", "MoEDecoderLM", "VLConfig", "VLModel", "DLLMConfig",

@@ -105,6 +105,8 @@ class TrainingArguments:
     muon_nesterov: bool = True
     # RL (GRPO) trainer
     rl_config: Optional[Dict[str, Any]] = None
+    # RAE trainer: perceptual / adversarial recipe (keys and defaults: train/fsdp2/extra_trainers.py GAN_DEFAULTS)
+    gan_config: Optional[Dict[str, Any]] = None
     # engine runtime: "auto" picks the native sharded runtime on CUDA and stock FSDP2 on CPU
     sharding_runtime: str = "auto"
 

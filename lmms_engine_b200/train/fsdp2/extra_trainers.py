@@ -99,22 +99,62 @@ def diff_augment(x: torch.Tensor, policy=("color", "translation", "cutout")) -> 
     return x
 
 
+GAN_DEFAULTS: Dict[str, Any] = {
+    # the stage-1 recipe of the reference (src/lmms_engine/train/fsdp2/rae_trainer.py:28-56); schedule entries are in
+    # epochs unless the ``*_step`` form is given
+    "disc_weight": 0.75, "perceptual_weight": 1.0, "disc_updates": 1, "max_d_weight": 1e4, "disc_loss": "hinge",
+    "gen_loss": "vanilla", "discriminator_start": 6, "discriminator_loss_start": 8, "lpips_start": 0,
+    "discriminator_lr": 2e-4, "discriminator_weight_decay": 0.0, "discriminator": "dino", "dino_ckpt_path": None, "ks": 9,
+    "key_depths": (2, 5, 8, 11), "norm_type": "bn", "using_spec_norm": True, "norm_eps": 1e-6, "recipe": "S_8",
+    "lpips_vgg_path": None, "lpips_lin_path": None, "allow_random_critics": False, "augment": {"prob": 1.0, "cutout": 0.0},
+}
+
+
 @TRAINER_REGISTER.register("rae_trainer")
 class RaeTrainer(FSDP2SFTTrainer):
-    """Expects a model with ``encode``, ``decode``, ``discriminator`` and ``last_layer()``."""
+    """Expects a model with ``encode`` / ``decode`` (or a forward returning ``out_pixels``) and ``last_layer()``.
+
+    Generator loss = L1 + ``perceptual_weight`` x LPIPS + ``disc_weight`` x adaptive weight x adversarial term; the
+    adaptive weight balances the gradient norms of the reconstruction and adversarial terms at the decoder's last
+    layer.  The critics (LPIPS, DINO discriminator) live in the trainer, not in the model: the autoencoder's checkpoint
+    holds the autoencoder only.  Options come from ``trainer_args.gan_config`` over ``GAN_DEFAULTS``."""
 
     def __init__(self, *a, **k):
         super().__init__(*a, **k)
         self.enable_perf_metrics = False
-        cfg = dict((self.args.rl_config or {}).get("gan", {})) if self.args.rl_config else {}
-        self.disc_start = int(cfg.get("disc_start", 0))
-        self.disc_weight = float(cfg.get("disc_weight", 0.75))
-        self.disc_steps = int(cfg.get("disc_steps", 1))
-        self.perceptual_weight = float(cfg.get("perceptual_weight", 0.0))
+        cfg = dict(GAN_DEFAULTS)
+        cfg.update(dict(getattr(self.args, "gan_config", None) or {}))
+        self.gan = cfg
+        self.disc_weight, self.perceptual_weight = float(cfg["disc_weight"]), float(cfg["perceptual_weight"])
+        self.disc_updates, self.max_d_weight = int(cfg["disc_updates"]), float(cfg["max_d_weight"])
         self.ema_state: Dict[str, torch.Tensor] = {}
+        self.discriminator = self.lpips = None
+        self.loss_parts: Dict[str, float] = {}
 
     def resolve_runtime(self) -> str:
         return "torch_fsdp2" if self.world_size > 1 else "plain"
+
+    # ---- set-up -------------------------------------------------------------------------------------------
+    def build_critics(self):
+        from ...models.rae import DinoDiscriminator, Lpips
+
+        cfg = self.gan
+        rand = bool(cfg["allow_random_critics"])
+        if self.disc_weight > 0:
+            if cfg["discriminator"] == "dino":
+                self.discriminator = DinoDiscriminator(cfg["dino_ckpt_path"], ks=int(cfg["ks"]), key_depths=tuple(cfg["key_depths"]),
+                                                       norm_type=cfg["norm_type"], using_spec_norm=bool(cfg["using_spec_norm"]),
+                                                       norm_eps=float(cfg["norm_eps"]), recipe=cfg["recipe"], allow_random=rand,
+                                                       backbone=cfg.get("backbone"))
+            elif cfg["discriminator"] == "patch":
+                from ...models.diffusion import PatchDiscriminator
+
+                self.discriminator = PatchDiscriminator(3, int(cfg.get("disc_dim", 256)))
+            else:
+                raise ValueError(f"unknown discriminator '{cfg['discriminator']}' (dino | patch)")
+            self.discriminator.to(self.device).train()
+        if self.perceptual_weight > 0:
+            self.lpips = Lpips(cfg["lpips_vgg_path"], cfg["lpips_lin_path"], allow_random=rand).to(self.device)
 
     def prepare_model(self):
         if self.world_size > 1:
@@ -122,58 +162,110 @@ class RaeTrainer(FSDP2SFTTrainer):
         else:
             self.runtime_kind = "plain"
             self.model.to(self.device)
+        self.build_critics()
 
     def prepare_optimizer(self):
         a = self.args
-        gen = [p for n, p in self.model.named_parameters() if p.requires_grad and "discriminator" not in n]
-        disc = [p for n, p in self.model.named_parameters() if p.requires_grad and "discriminator" in n]
-        kw = dict(lr=a.learning_rate, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon, weight_decay=a.weight_decay)
-        self.optimizer = torch.optim.AdamW(gen, **kw)
-        self.disc_optimizer = torch.optim.AdamW(disc, **kw)
-        for o in (self.optimizer, self.disc_optimizer):
+        gen = [p for p in self.model.parameters() if p.requires_grad]
+        kw = dict(betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon)
+        self.optimizer = torch.optim.AdamW(gen, lr=a.learning_rate, weight_decay=a.weight_decay, **kw)
+        opts = [self.optimizer]
+        self.disc_optimizer = None
+        if self.discriminator is not None:
+            disc = [p for p in self.discriminator.parameters() if p.requires_grad]
+            self.disc_optimizer = torch.optim.AdamW(disc, lr=float(self.gan["discriminator_lr"]),
+                                                    weight_decay=float(self.gan["discriminator_weight_decay"]), **kw)
+            opts.append(self.disc_optimizer)
+        for o in opts:
             for g in o.param_groups:
                 g.setdefault("initial_lr", g["lr"])
+
+    def _start_step(self, name: str) -> int:
+        if f"{name}_step" in self.gan:
+            return int(self.gan[f"{name}_step"])
+        return int(float(self.gan[name]) * (self.steps_per_epoch() or 0))
+
+    # ---- losses -------------------------------------------------------------------------------------------
+    def augment(self, x):
+        aug = self.gan.get("augment") or {}
+        if float(aug.get("prob", 1.0)) <= 0 or torch.rand(()) > float(aug.get("prob", 1.0)):
+            return x
+        policy = ("color", "translation") + (("cutout",) if float(aug.get("cutout", 0.0)) > 0 else ())
+        return diff_augment(x, policy)
 
     def adaptive_weight(self, rec_loss, g_loss):
         last = self.model.last_layer()
         g_rec = torch.autograd.grad(rec_loss, last, retain_graph=True)[0]
         g_gan = torch.autograd.grad(g_loss, last, retain_graph=True)[0]
-        return (g_rec.norm() / (g_gan.norm() + 1e-4)).clamp(0, 1e4).detach() * self.disc_weight
+        return (g_rec.norm() / (g_gan.norm() + 1e-6)).clamp(0, self.max_d_weight).detach()
+
+    def gen_loss(self, logits_fake):
+        if self.gan["gen_loss"] == "hinge":
+            return -logits_fake.mean()
+        return F.softplus(-logits_fake).mean()  # "vanilla": non-saturating
+
+    def disc_loss(self, real, fake):
+        if self.gan["disc_loss"] == "hinge":
+            return 0.5 * (F.relu(1 - real).mean() + F.relu(1 + fake).mean())
+        return 0.5 * (F.softplus(-real).mean() + F.softplus(fake).mean())
+
+    def reconstruct(self, x):
+        m = self.model
+        out = m(pixel_values=x)
+        return out["out_pixels"] if "out_pixels" in out else out["reconstruction"]
 
     def training_step(self, batch, do_step):
         m = self.model
         m.train()
         x = batch["pixel_values"].float()
-        z, hw = m.encode(x)
-        rec = m.decode(z, x.shape[0], hw)
+        rec = self.reconstruct(x).float()
         rec_loss = (rec - x).abs().mean()
-        use_gan = self.global_step >= self.disc_start
-        loss = rec_loss
-        if use_gan:
-            g_loss = -m.discriminator(diff_augment(rec)).mean()
-            loss = rec_loss + self.adaptive_weight(rec_loss, g_loss) * g_loss
+        lp = rec_loss.new_zeros(())
+        if self.lpips is not None and self.global_step >= self._start_step("lpips_start"):
+            lp = self.lpips(rec * 2 - 1, x * 2 - 1)
+        loss = rec_loss + self.perceptual_weight * lp
+        g_loss = aw = rec_loss.new_zeros(())
+        if self.discriminator is not None and self.global_step >= self._start_step("discriminator_loss_start"):
+            self.discriminator.eval()
+            g_loss = self.gen_loss(self.discriminator(self.augment(rec * 2 - 1)))
+            aw = self.adaptive_weight(loss, g_loss)
+            loss = loss + self.disc_weight * aw * g_loss
         self.lr_factor = self.current_lr_factor(self.global_step)
         for o in (self.optimizer, self.disc_optimizer):
-            for g in o.param_groups:
+            for g in (o.param_groups if o is not None else ()):
                 g["lr"] = g["initial_lr"] * self.lr_factor
         self.optimizer.zero_grad(set_to_none=True)
         loss.backward()
         gn = torch.nn.utils.clip_grad_norm_([p for g in self.optimizer.param_groups for p in g["params"]], self.args.max_grad_norm)
         self.optimizer.step()
-        if use_gan:
-            for _ in range(self.disc_steps):
-                real = m.discriminator(diff_augment(x))
-                fake = m.discriminator(diff_augment(rec.detach()))
-                d_loss = 0.5 * (F.relu(1 - real).mean() + F.relu(1 + fake).mean())  # hinge
+        d_total = 0.0
+        if self.discriminator is not None and self.global_step >= self._start_step("discriminator_start"):
+            self.discriminator.train()
+            fake = (rec.detach() * 2 - 1).clamp(-1, 1)
+            fake = torch.round((fake + 1) * 127.5) / 127.5 - 1  # what an 8-bit image of the reconstruction would hold
+            for _ in range(max(self.disc_updates, 1)):
+                d_loss = self.disc_loss(self.discriminator(self.augment(x * 2 - 1)), self.discriminator(self.augment(fake)))
                 self.disc_optimizer.zero_grad(set_to_none=True)
                 d_loss.backward()
+                if self.world_size > 1:  # the critic is replicated: average its gradients
+                    for p in self.discriminator.parameters():
+                        if p.grad is not None:
+                            dist.all_reduce(p.grad, op=dist.ReduceOp.AVG)
                 self.disc_optimizer.step()
-        decay = self.args.ema_decay or 0.9999
+                d_total += float(d_loss.detach())
+        self.loss_parts = {"l1_loss": float(rec_loss.detach()), "lpips_loss": float(lp.detach()), "gan_loss": float(g_loss.detach()),
+                           "adaptive_weight": float(aw), "disc_loss": d_total / max(self.disc_updates, 1)}
+        decay = self.args.ema_decay or 0.9978
         with torch.no_grad():
             for n, p in m.named_parameters():
-                if p.requires_grad and "discriminator" not in n:
+                if p.requires_grad:
                     self.ema_state.setdefault(n, p.detach().float().clone()).lerp_(p.detach().float(), 1 - decay)
         return loss.detach(), gn
+
+    def calculate_training_metrics(self, seqlens, step_seconds):
+        out = super().calculate_training_metrics(seqlens, step_seconds)
+        out.update({f"train/{k}": v for k, v in self.loss_parts.items()})
+        return out
 
     def save_checkpoints(self, output_dir=None, step=None):
         step = self.global_step if step is None else step
@@ -182,4 +274,7 @@ class RaeTrainer(FSDP2SFTTrainer):
         if self.rank == 0:
             torch.save({k: v.cpu() for k, v in self.model.state_dict().items()}, os.path.join(out, "model.pt"))
             torch.save({k: v.cpu() for k, v in self.ema_state.items()}, os.path.join(out, "ema_state.pt"))
+            if self.discriminator is not None:
+                heads = {k: v.cpu() for k, v in self.discriminator.state_dict().items() if not k.startswith("dino.")}
+                torch.save({"discriminator": heads, "optimizer": self.disc_optimizer.state_dict()}, os.path.join(out, "discriminator.pt"))
         return out

@@ -68,8 +68,10 @@ def test_rae_trainer_gan_steps(tmp_path):
     spec = {"pixel_values": {"shape": [3, 32, 32]}}
     _, runner = _run(tmp_path, "rae_trainer", "rae_siglip",
                      dict(image_size=32, patch_size=8, encoder_dim=32, encoder_depth=1, encoder_heads=2, decoder_dim=32,
-                          decoder_depth=1, decoder_heads=2, disc_dim=32), _tensors(spec), per_device_train_batch_size=2)
-    assert runner.trainer.ema_state
+                          decoder_depth=1, decoder_heads=2), _tensors(spec), per_device_train_batch_size=2,
+                     gan_config=dict(discriminator="patch", disc_dim=32, perceptual_weight=0.0, discriminator_start_step=0,
+                                     discriminator_loss_start_step=0))
+    assert runner.trainer.ema_state and runner.trainer.loss_parts["disc_loss"] > 0
 
 
 def test_grpo_trainer_improves_reward_signal(tmp_path):
