@@ -12,6 +12,8 @@ from .packed_collator import _flatten
 
 
 class VisionCollator:
+    STACKED = ("video",)
+
     def __init__(self, processor=None, pad_token_id: int = 0, padding_side: str = "right", ignore_index: int = -100):
         self.processor = processor
         tok = getattr(processor, "tokenizer", None)
@@ -33,8 +35,9 @@ class VisionCollator:
     def __call__(self, batch: Sequence[Any]) -> Dict[str, torch.Tensor]:
         samples = _flatten(batch)
         ids = self._pad([s["input_ids"].view(-1) for s in samples], self.pad)
-        labels = self._pad([s["labels"].view(-1) for s in samples], self.ignore)
-        out: Dict[str, torch.Tensor] = {"input_ids": ids, "labels": labels}
+        out: Dict[str, torch.Tensor] = {"input_ids": ids}
+        if all("labels" in s for s in samples):  # generative families carry prompts without labels
+            out["labels"] = self._pad([s["labels"].view(-1) for s in samples], self.ignore)
         lens = torch.tensor([s["input_ids"].numel() for s in samples])
         ar = torch.arange(ids.shape[1]).unsqueeze(0)
         if self.side == "left":
@@ -46,5 +49,6 @@ class VisionCollator:
                 continue
             vals = [s[key] for s in samples if key in s and s[key] is not None]
             if vals and all(torch.is_tensor(v) for v in vals):
-                out[key] = torch.cat(vals, dim=0)
+                # a clip is one item of the batch (its first axis is time), everything else is a list of rows
+                out[key] = torch.stack(vals, 0) if key in self.STACKED else torch.cat(vals, dim=0)
         return out

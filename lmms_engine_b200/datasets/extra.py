@@ -93,8 +93,7 @@ class TensorProcessor:
         return {"pixel_values": self.image_to_tensor(image)} if image is not None else {}
 
 
-for _name in ("sit", "rae_siglip", "wanvideo"):
-    register_processor(_name)(TensorProcessor)
+register_processor("tensor")(TensorProcessor)  # family processors: datasets/processor/generative_processors.py
 
 
 @register_processor("nanovlm")
@@ -380,10 +379,12 @@ class _RecordDataset(DatasetCore, Dataset):
 
 @register_dataset("sit")
 class SitDataset(_RecordDataset):
-    """Rows ``{"latent": path (.pt / .npy) | nested list, "label": int}``."""
+    """Rows ``{"latent": path (.pt / .npy) | nested list, "label": int}`` or ``{"image": path, "label": int}``."""
 
     def __getitem__(self, i) -> Dict[str, Any]:
         rec, folder = self.data_list[i], self.data_folder[i]
+        if "image" in rec:
+            return self.processor.process(image=self.load_image(os.path.join(folder or "", rec["image"])), label=rec.get("label", 0))
         lat = rec["latent"]
         if isinstance(lat, str):
             path = os.path.join(folder or "", lat)

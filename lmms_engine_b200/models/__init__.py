@@ -23,7 +23,10 @@ from .dllm import DiffusionLM, DLLMConfig
 for _mt in ("qwen3_dllm", "dream_dllm", "llada_dllm"):
     register_model(_mt, DLLMConfig, DiffusionLM, "masked_lm")
 register_model("sit", SiTConfig, SiT, "general")
-register_model("wanvideo", WanConfig, WanDiT, "general")
+from .wan import WanVideoConfig, WanVideoModel  # noqa: E402
+
+register_model("wanvideo", WanVideoConfig, WanVideoModel, "general")
+register_model("wan_dit_lite", WanConfig, WanDiT, "general")
 from .rae import RaeSiglip, RaeSiglipConfig  # noqa: E402
 
 register_model("rae_siglip", RaeSiglipConfig, RaeSiglip, "general")

@@ -132,14 +132,15 @@ class DLLMTrainer(Trainer):
 
 @TRAINER_REGISTER.register("wan_trainer")
 class WanVideoTrainer(Trainer):
-    trainable_prefixes = ("blocks", "patch_embedding", "head", "time_embedding", "text_embedding", "camera_adapter", "head_ada")
+    """Flow-matching training of the video diffusion family.  The model freezes everything outside
+    ``config.trainable_modules`` itself (``freeze_except``); models without that method (a bare diffusion
+    transformer) train whole."""
 
     def __init__(self, *a, **k):
         super().__init__(*a, **k)
         self.enable_perf_metrics = False
 
     def prepare_model(self):
-        for n, p in self.model.named_parameters():
-            if not n.startswith(self.trainable_prefixes):
-                p.requires_grad_(False)  # VAE / text / image encoders stay frozen
+        if hasattr(self.model, "freeze_except"):
+            self.model.freeze_except()  # autoencoder / text / image encoders stay frozen and in eval mode
         super().prepare_model()
