@@ -448,7 +448,8 @@ class BagelProcessor(ChatProcessor):
         C, h, w = lat.shape
         p = self.p
         rows, cols = h // p, w // p
-        tok = lat[:, : rows * p, : cols * p].reshape(C, rows, p, cols, p).permute(1, 3, 0, 2, 4).reshape(rows * cols, C * p * p)
+        # inside a patch: (pixel row, pixel column, channel), the order of the released input / output projections
+        tok = lat[:, : rows * p, : cols * p].reshape(C, rows, p, cols, p).permute(1, 3, 2, 4, 0).reshape(rows * cols, p * p * C)
         pos = (torch.arange(rows)[:, None] * self.max_latent + torch.arange(cols)[None, :]).flatten()
         return tok, pos
 
@@ -457,6 +458,7 @@ class BagelProcessor(ChatProcessor):
         labels: List[int] = []
         pos: List[int] = []
         lat_tok, lat_pos, lat_idx, lat_t, lat_loss = [], [], [], [], []
+        splits: List[List[int]] = []  # [length, mode]: 0 causal text, 1 full (clean image), 2 noise (noised target image)
         rope, image_at = 0, 0
         for msg in hf_messages:
             role = msg["role"]
@@ -473,6 +475,10 @@ class BagelProcessor(ChatProcessor):
                     ids += span
                     pos += list(range(rope, rope + len(span)))
                     rope += len(span)
+                    if splits and splits[-1][1] == 0:
+                        splits[-1][0] += len(span)
+                    else:
+                        splits.append([len(span), 0])
                 elif kind in ("image", "image_url"):
                     img = images[image_at]
                     image_at += 1
@@ -494,8 +500,12 @@ class BagelProcessor(ChatProcessor):
                     t = float(1.0 / (1.0 + math.exp(-self.rng.standard_normal()))) if target else 0.0
                     lat_t.append(torch.full((n,), t))
                     lat_loss.append(torch.full((n,), target, dtype=torch.bool))
+                    splits.append([n + 2, 2 if target else 1])
         out = {"input_ids": torch.tensor(ids, dtype=torch.long), "labels": torch.tensor(labels, dtype=torch.long),
                "position_ids": torch.tensor(pos, dtype=torch.long)}
+        if self.kwargs.get("attention_modes", True) and splits:
+            out["split_lens"] = torch.tensor([s[0] for s in splits], dtype=torch.long)
+            out["attn_modes"] = torch.tensor([s[1] for s in splits], dtype=torch.long)
         if lat_tok:
             out.update(latent_tokens=torch.cat(lat_tok), latent_pos=torch.cat(lat_pos), latent_index=torch.cat(lat_idx),
                        timesteps=torch.cat(lat_t), latent_loss_mask=torch.cat(lat_loss))
