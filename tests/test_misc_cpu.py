@@ -331,6 +331,22 @@ def test_prepare_init_weight_composes_parts_and_grows_vocabulary(tmp_path):
     assert (emb[125:] - mu).abs().max() < 0.05
     assert torch.equal(model.audio_tower.state_dict()["layers.0.self_attn.q_proj.weight"],
                        donor.audio_tower.state_dict()["layers.0.self_attn.q_proj.weight"])
+    # the same composition as a family recipe: configs read from the parts' directories, ids continue the vocabulary
+    hf_io.save_pretrained({"audio_tower." + k: v for k, v in donor.audio_tower.state_dict().items()}, str(tmp_path / "enc2"),
+                          config={"audio_config": audio})
+    report = prepare_init_weight.main(["--recipe", "aero", "--language-model", str(tmp_path / "lm"), "--audio-model", str(tmp_path / "enc2"),
+                                       "--dtype", "float32", "--output", str(tmp_path / "out_recipe")])
+    assert report["language_model"]["placed"] == len(lm.state_dict()) and report["audio_tower"]["unused"] == 0
+    again = create_model_from_pretrained(str(tmp_path / "out_recipe"))
+    assert again.language_model.model.embed_tokens.weight.shape[0] == 128 and again.config.audio_token_index == 127
+    # an autoencoder from a SigLIP checkpoint, configuration only
+    enc_cfg = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=4, image_size=32, patch_size=8)
+    (tmp_path / "siglip").mkdir()
+    (tmp_path / "siglip" / "config.json").write_text(json.dumps({"vision_config": enc_cfg}))
+    prepare_init_weight.main(["--recipe", "rae_siglip2", "--vision-model", str(tmp_path / "siglip"), "--skip-weights", "--noise-tau", "0.5",
+                              "--output", str(tmp_path / "rae")])
+    rae = json.load(open(tmp_path / "rae" / "config.json"))
+    assert rae["model_type"] == "rae_siglip" and rae["encoder_config"]["hidden_size"] == 32 and rae["decoder_config"]["decoder_hidden_size"] == 1152
     # conversation conversion and splitting
     src = tmp_path / "llava.json"
     src.write_text(json.dumps([{"id": "a", "image": "x.png", "conversations": [
@@ -392,3 +408,52 @@ def test_length_grouped_sampler_groups_and_shards():
     assert list(again) == per_rank[0]
     again.set_epoch(1)
     assert list(again) != per_rank[0]
+
+
+def test_check_data_subcommands_measure_media_and_write_precomputed_tokens(tmp_path, capsys):
+    """exists / tokens / precompute / summary over a YAML of sources, from folders and through an object-storage client."""
+    import wave
+
+    import numpy as np
+    import yaml
+    from PIL import Image
+
+    from lmms_engine_b200.tools import check_data
+
+    media = tmp_path / "media"
+    media.mkdir()
+    Image.fromarray(np.zeros((280, 560, 3), dtype=np.uint8)).save(media / "a.png")
+    with wave.open(str(media / "s.wav"), "wb") as w:
+        w.setnchannels(1), w.setsampwidth(2), w.setframerate(16000)
+        w.writeframes(np.zeros(16000 * 2, dtype=np.int16).tobytes())
+    rows = [{"id": "r0", "messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "a.png"}},
+                                                                   {"type": "audio_url", "audio_url": {"url": "s.wav"}},
+                                                                   {"type": "text", "text": "what is it"}]}]},
+            {"messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "gone.png"}}]}]}]
+    data = tmp_path / "d.jsonl"
+    data.write_text("".join(json.dumps(r) + "\n" for r in rows))
+    spec = tmp_path / "d.yaml"
+    spec.write_text(yaml.safe_dump({"datasets": [{"path": str(data), "data_folder": str(media), "data_type": "jsonl"}]}))
+    assert check_data.main(["exists", "--dataset", str(spec), "--out", str(tmp_path / "missing.txt")]) == 1
+    assert (tmp_path / "missing.txt").read_text().strip().endswith("gone.png")
+    assert check_data.main(["tokens", "--dataset", str(spec), "--out", str(tmp_path / "tokens.txt")]) == 0
+    image_tokens, audio_tokens, default_image = 280 * 560 // (14 * 14 * 4), 50, 500 * 500 // (14 * 14 * 4)
+    assert f"({image_tokens + audio_tokens + default_image})" in (tmp_path / "tokens.txt").read_text()
+    assert check_data.main(["precompute", "--dataset", str(spec), "--out-dir", str(tmp_path / "out")]) == 0
+    got = [json.loads(l) for l in open(tmp_path / "out" / "d.jsonl")]
+    parts = got[0]["messages"][0]["content"]
+    assert parts[0]["precomputed_tokens"] == image_tokens and parts[1]["precomputed_tokens"] == audio_tokens
+    assert parts[2]["precomputed_tokens"] == 3 * 1.25 and got[1]["id"] == "Unknown_ID"
+    assert got[1]["messages"][0]["content"][0]["precomputed_tokens"] == default_image  # unreadable: the default, and reported
+    assert "unreadable_media" in capsys.readouterr().out
+    assert check_data.estimate_tokens(got[0]) == int(image_tokens + audio_tokens + 3.75)
+    # the same through a storage client ("local" = a directory standing in for a bucket), and the single-table form
+    cloud = tmp_path / "cloud.yaml"
+    cloud.write_text(yaml.safe_dump({"datasets": [{"path": str(data), "data_folder": "", "data_type": "jsonl"}]}))
+    assert check_data.main(["precompute", "--dataset", str(cloud), "--parquet", str(tmp_path / "all.parquet"),
+                            "--object-storage", "local", "--bucket", str(media)]) == 0
+    import pyarrow.parquet as pq
+
+    table = pq.read_table(tmp_path / "all.parquet").to_pylist()
+    assert json.loads(table[0]["messages"])[0]["content"][0]["precomputed_tokens"] == image_tokens
+    assert check_data.main(["summary", "--dataset", str(spec)]) == 1
