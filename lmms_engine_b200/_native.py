@@ -26,7 +26,12 @@ from typing import Dict, List, Optional
 
 _PKG = Path(__file__).resolve().parent
 CSRC = _PKG / "csrc"
-LIBDIR = _PKG / "_lib"
+# LMMS_B200_DEBUG_BOUNDS=1 selects the debug build of every CUDA library: compiled with -DB200_DEBUG_BOUNDS (the
+# per-element index checks behind B200_DBG_INDEX in csrc/common.cuh) into its own directory, so that the release
+# objects stay in place.  Failed checks raise the per-device status word that ``ops._cuda.check_status`` turns into
+# an exception.
+DEBUG_BOUNDS = os.environ.get("LMMS_B200_DEBUG_BOUNDS", "0") == "1"
+LIBDIR = _PKG / ("_lib_dbg" if DEBUG_BOUNDS else "_lib")
 
 NVCC_FLAGS = [
     "-gencode",
@@ -39,6 +44,8 @@ NVCC_FLAGS = [
     "-Xcompiler",
     "-fPIC",
 ]
+if DEBUG_BOUNDS:
+    NVCC_FLAGS.append("-DB200_DEBUG_BOUNDS=1")
 GXX_FLAGS = ["-O3", "-std=c++17", "-shared", "-fPIC", "-march=x86-64-v3", "-pthread"]
 
 _lock = threading.Lock()

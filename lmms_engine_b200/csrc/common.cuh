@@ -21,6 +21,7 @@ enum KernelStatus : int {
   kStatusBadShape = 2,
   kStatusPeerTimeout = 3,
   kStatusOverflow = 4,
+  kStatusBadIndex = 5,
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -273,6 +274,22 @@ __device__ __forceinline__ bool doc_in_bounds(int start, int len, int total, int
   if (status != nullptr) atomicExch(status, kStatusBadShape);
   return false;
 }
+
+// ---------------------------------------------------------------- index bounds
+// Rows addressed through an index table (routing tables, gather / scatter maps) are checked against the tensor they
+// index: an index past the end raises kStatusBadIndex and the access is skipped.  The check is one compare per row and
+// stays on in every build.  B200_DEBUG_BOUNDS (the debug build of the native libraries) switches on the checks that cost
+// a compare per ELEMENT or an extra load, through B200_DBG_INDEX.
+__device__ __forceinline__ bool index_in_bounds(long idx, long limit, int* status) {
+  if (idx < limit) return true;
+  if (status != nullptr) atomicExch(status, kStatusBadIndex);
+  return false;
+}
+#ifdef B200_DEBUG_BOUNDS
+#define B200_DBG_INDEX(idx, limit, status) index_in_bounds((idx), (limit), (status))
+#else
+#define B200_DBG_INDEX(idx, limit, status) true
+#endif
 
 // ---------------------------------------------------------------- misc numeric helpers
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {

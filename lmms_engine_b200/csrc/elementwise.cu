@@ -537,7 +537,7 @@ __global__ void scale_kernel(GT* __restrict__ g, long n, const float* __restrict
 // ------------------------------------------------------------------ packed-sequence index kernels
 // out[i, :] = src[idx[i], :]  (idx < 0 writes zeros) and the scatter inverse (optionally adding).
 __global__ void gather_rows_kernel(const bf16* __restrict__ src, const int64_t* __restrict__ idx,
-                                   bf16* __restrict__ out, long n_out, int H) {
+                                   bf16* __restrict__ out, long n_out, int H, long n_src, int* status) {
   const int vec = H / 8;
   const long total = n_out * vec;
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
@@ -547,12 +547,12 @@ __global__ void gather_rows_kernel(const bf16* __restrict__ src, const int64_t* 
     const int64_t s = idx[r];
     bf16x8 v;
     v.w[0] = v.w[1] = v.w[2] = v.w[3] = 0u;
-    if (s >= 0) v = *reinterpret_cast<const bf16x8*>(src + s * H + c);
+    if (s >= 0 && index_in_bounds(s, n_src, status)) v = *reinterpret_cast<const bf16x8*>(src + s * H + c);
     *reinterpret_cast<bf16x8*>(out + r * H + c) = v;
   }
 }
 __global__ void scatter_rows_kernel(const bf16* __restrict__ src, const int64_t* __restrict__ idx,
-                                    bf16* __restrict__ out, long n_src, int H, int add) {
+                                    bf16* __restrict__ out, long n_src, int H, int add, long n_out, int* status) {
   const int vec = H / 8;
   const long total = n_src * vec;
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
@@ -560,7 +560,7 @@ __global__ void scatter_rows_kernel(const bf16* __restrict__ src, const int64_t*
     const long r = i / vec;
     const int c = (i - r * vec) * 8;
     const int64_t d = idx[r];
-    if (d < 0) continue;
+    if (d < 0 || !index_in_bounds(d, n_out, status)) continue;
     float v[8];
     load8(src + r * H + c, v);
     if (add) {
@@ -819,18 +819,21 @@ int b200_scale(void* g, int g_is_fp32, long n, const void* coef, cudaStream_t st
   return CHECK_LAUNCH();
 }
 
-int b200_gather_rows(const void* src, const void* idx, void* out, long n_out, int H, cudaStream_t st) {
+// n_src / n_out: rows of the indexed tensor; an index beyond it raises kStatusBadIndex in *status and is skipped.
+int b200_gather_rows(const void* src, const void* idx, void* out, long n_out, int H, long n_src, void* status,
+                     cudaStream_t st) {
   if (n_out <= 0) return 0;
   if (H % 8) return -10;
   gather_rows_kernel<<<grid_for(n_out * (H / 8), 256), 256, 0, st>>>((const bf16*)src, (const int64_t*)idx, (bf16*)out,
-                                                                     n_out, H);
+                                                                     n_out, H, n_src, (int*)status);
   return CHECK_LAUNCH();
 }
-int b200_scatter_rows(const void* src, const void* idx, void* out, long n_src, int H, int add, cudaStream_t st) {
+int b200_scatter_rows(const void* src, const void* idx, void* out, long n_src, int H, int add, long n_out, void* status,
+                      cudaStream_t st) {
   if (n_src <= 0) return 0;
   if (H % 8) return -10;
   scatter_rows_kernel<<<grid_for(n_src * (H / 8), 256), 256, 0, st>>>((const bf16*)src, (const int64_t*)idx,
-                                                                      (bf16*)out, n_src, H, add);
+                                                                      (bf16*)out, n_src, H, add, n_out, (int*)status);
   return CHECK_LAUNCH();
 }
 

@@ -129,11 +129,20 @@ __global__ void moe_offsets_kernel(const int* __restrict__ counts, int* __restri
   }
 }
 
+// Debug build: rows computed from the counts are checked against the size of the row tables (counts that do not belong
+// to these top-k indices would otherwise write past them); the flag is read and cleared by b200_moe_debug_bad_index().
+#ifdef B200_DEBUG_BOUNDS
+__device__ int g_debug_bad_index = 0;
+#define MOE_DBG_STATUS (&g_debug_bad_index)
+#else
+#define MOE_DBG_STATUS nullptr
+#endif
+
 // One CTA per expert: destination rows in token order (stable, deterministic).
 __global__ void __launch_bounds__(256) moe_rows_kernel(const int* __restrict__ topk_idx, const float* __restrict__ topk_w,
                                                        const int* __restrict__ expert_start, int* __restrict__ row_of,
                                                        int64_t* __restrict__ token_of_row, float* __restrict__ weight_of_row,
-                                                       int T, int k) {
+                                                       int T, int k, long max_rows) {
   __shared__ int warp_tot[8];
   __shared__ int base;
   const int e = blockIdx.x;
@@ -155,7 +164,7 @@ __global__ void __launch_bounds__(256) moe_rows_kernel(const int* __restrict__ t
     for (int w = 0; w < warp; ++w) wbase += warp_tot[w];
     int total = 0;
     for (int w = 0; w < (blockDim.x >> 5); ++w) total += warp_tot[w];
-    if (slot >= 0) {
+    if (slot >= 0 && B200_DBG_INDEX(base + wbase + before, max_rows, MOE_DBG_STATUS)) {
       const int row = base + wbase + before;
       row_of[static_cast<size_t>(t) * k + slot] = row;
       token_of_row[row] = t;
@@ -170,7 +179,8 @@ __global__ void __launch_bounds__(256) moe_rows_kernel(const int* __restrict__ t
 // ---------------------------------------------------------------------------- combine & friends
 // out[t, :] = sum_j (w ? w[t,j] : 1) * src[row_of[t,j], :]
 __global__ void moe_combine_kernel(const bf16* __restrict__ src, const int* __restrict__ row_of,
-                                   const float* __restrict__ w, bf16* __restrict__ out, int T, int k, int H) {
+                                   const float* __restrict__ w, bf16* __restrict__ out, int T, int k, int H,
+                                   long n_src, int* status) {
   const int vec = H / 8;
   const long total = static_cast<long>(T) * vec;
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
@@ -180,7 +190,7 @@ __global__ void moe_combine_kernel(const bf16* __restrict__ src, const int* __re
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int j = 0; j < k; ++j) {
       const int row = row_of[t * k + j];
-      if (row < 0) continue;
+      if (row < 0 || !index_in_bounds(row, n_src, status)) continue;
       const float wt = w != nullptr ? w[t * k + j] : 1.f;
       const V8 v = *reinterpret_cast<const V8*>(src + static_cast<size_t>(row) * H + c);
 #pragma unroll
@@ -200,7 +210,7 @@ __global__ void moe_combine_kernel(const bf16* __restrict__ src, const int* __re
 // dsrc[row, :] = weight_of_row[row] * dout[token_of_row[row], :]   (zero for padding rows)
 __global__ void moe_combine_bwd_src_kernel(const bf16* __restrict__ dout, const int64_t* __restrict__ token_of_row,
                                            const float* __restrict__ weight_of_row, bf16* __restrict__ dsrc,
-                                           long rows, int H) {
+                                           long rows, int H, long n_tok, int* status) {
   const int vec = H / 8;
   const long total = rows * vec;
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
@@ -210,7 +220,7 @@ __global__ void moe_combine_bwd_src_kernel(const bf16* __restrict__ dout, const 
     const int64_t t = token_of_row[r];
     V8 o;
     o.w[0] = o.w[1] = o.w[2] = o.w[3] = 0u;
-    if (t >= 0) {
+    if (t >= 0 && index_in_bounds(t, n_tok, status)) {
       const float wt = weight_of_row != nullptr ? weight_of_row[r] : 1.f;
       const V8 v = *reinterpret_cast<const V8*>(dout + t * H + c);
 #pragma unroll
@@ -226,7 +236,7 @@ __global__ void moe_combine_bwd_src_kernel(const bf16* __restrict__ dout, const 
 // dw[t, j] = <dout[t, :], src[row_of[t, j], :]>   (one warp per (t, j))
 __global__ void moe_combine_bwd_w_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ src,
                                          const int* __restrict__ row_of, float* __restrict__ dw, long pairs, int k,
-                                         int H) {
+                                         int H, long n_src, int* status) {
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   for (long p = blockIdx.x * static_cast<long>(wpb) + (threadIdx.x >> 5); p < pairs;
@@ -234,7 +244,8 @@ __global__ void moe_combine_bwd_w_kernel(const bf16* __restrict__ dout, const bf
     const long t = p / k;
     const int row = row_of[p];
     float acc = 0.f;
-    for (int c = lane * 8; c < H; c += 256) {
+    const bool ok = row >= 0 && index_in_bounds(row, n_src, status);  // uniform over the warp
+    for (int c = lane * 8; ok && c < H; c += 256) {
       const V8 a = *reinterpret_cast<const V8*>(dout + t * H + c);
       const V8 b = *reinterpret_cast<const V8*>(src + static_cast<size_t>(row) * H + c);
 #pragma unroll
@@ -336,32 +347,48 @@ int b200_moe_permute(const void* topk_idx, const void* topk_w, const void* count
   cudaMemsetAsync(weight_of_row, 0, sizeof(float) * max_rows, st);
   moe_offsets_kernel<<<1, 256, 0, st>>>((const int*)counts, (int*)expert_start, (int*)tile_expert, E, max_tiles);
   moe_rows_kernel<<<E, 256, 0, st>>>((const int*)topk_idx, (const float*)topk_w, (const int*)expert_start, (int*)row_of,
-                                     (int64_t*)token_of_row, (float*)weight_of_row, T, k);
+                                     (int64_t*)token_of_row, (float*)weight_of_row, T, k, max_rows);
   return CHECK_LAUNCH();
 }
 
-int b200_moe_combine(const void* src, const void* row_of, const void* w, void* out, int T, int k, int H,
-                     cudaStream_t st) {
+// Debug build: 1 if a computed row left its table since the last call (and clears the flag); -1 in the release build.
+int b200_moe_debug_bad_index() {
+#ifdef B200_DEBUG_BOUNDS
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_debug_bad_index, sizeof(int)) != cudaSuccess) return -2;
+  cudaMemcpyToSymbol(g_debug_bad_index, &zero, sizeof(int));
+  return v != 0;
+#else
+  return -1;
+#endif
+}
+
+// n_src / n_tok: rows of the tensor that the routing table indexes; entries beyond it raise kStatusBadIndex in *status
+// and contribute nothing.
+int b200_moe_combine(const void* src, const void* row_of, const void* w, void* out, int T, int k, int H, long n_src,
+                     void* status, cudaStream_t st) {
   if (T <= 0) return 0;
   if (H % 8) return -10;
   moe_combine_kernel<<<grid_for(static_cast<long>(T) * (H / 8), 256), 256, 0, st>>>(
-      (const bf16*)src, (const int*)row_of, (const float*)w, (bf16*)out, T, k, H);
+      (const bf16*)src, (const int*)row_of, (const float*)w, (bf16*)out, T, k, H, n_src, (int*)status);
   return CHECK_LAUNCH();
 }
 int b200_moe_combine_bwd_src(const void* dout, const void* token_of_row, const void* weight_of_row, void* dsrc, long rows,
-                             int H, cudaStream_t st) {
+                             int H, long n_tok, void* status, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (H % 8) return -10;
   moe_combine_bwd_src_kernel<<<grid_for(rows * (H / 8), 256), 256, 0, st>>>(
-      (const bf16*)dout, (const int64_t*)token_of_row, (const float*)weight_of_row, (bf16*)dsrc, rows, H);
+      (const bf16*)dout, (const int64_t*)token_of_row, (const float*)weight_of_row, (bf16*)dsrc, rows, H, n_tok,
+      (int*)status);
   return CHECK_LAUNCH();
 }
 int b200_moe_combine_bwd_w(const void* dout, const void* src, const void* row_of, void* dw, long pairs, int k, int H,
-                           cudaStream_t st) {
+                           long n_src, void* status, cudaStream_t st) {
   if (pairs <= 0) return 0;
   if (H % 8) return -10;
   moe_combine_bwd_w_kernel<<<grid_for(pairs * 32, 256), 256, 0, st>>>((const bf16*)dout, (const bf16*)src,
-                                                                      (const int*)row_of, (float*)dw, pairs, k, H);
+                                                                      (const int*)row_of, (float*)dw, pairs, k, H, n_src,
+                                                                      (int*)status);
   return CHECK_LAUNCH();
 }
 int b200_swiglu_cat_fwd(const void* gu, void* h, long rows, int I, cudaStream_t st) {

@@ -36,12 +36,12 @@ _SIG: Dict[str, Tuple[str, str]] = {
     "b200_sumsq": ("elementwise", "pilppis"),
     "b200_clip_coef": ("elementwise", "ppppfps"),
     "b200_scale": ("elementwise", "pilps"),
-    "b200_gather_rows": ("elementwise", "ppplis"),
+    "b200_gather_rows": ("elementwise", "pppli" + "lps"),
     "b200_scatter_rows": ("elementwise", "ppplis" + ""),
     "b200_ce_finalize": ("elementwise", "pppppiiliis"),
     "b200_ce_dlogits": ("elementwise", "ppppiliis"),
 }
-_SIG["b200_scatter_rows"] = ("elementwise", "pppliis")
+_SIG["b200_scatter_rows"] = ("elementwise", "pppliilps")
 
 _CT = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_long, "f": ctypes.c_float, "s": ctypes.c_void_p}
 _fn_cache: Dict[str, ctypes._CFuncPtr] = {}
@@ -82,7 +82,8 @@ def status_word(device: torch.device) -> torch.Tensor:
     return t
 
 
-STATUS_NAMES = {1: "a barrier wait timed out", 2: "bad shape", 3: "a wait for a peer GPU timed out", 4: "a receive buffer overflowed"}
+STATUS_NAMES = {1: "a barrier wait timed out", 2: "bad shape", 3: "a wait for a peer GPU timed out", 4: "a receive buffer overflowed",
+                5: "an index table addressed a row outside its tensor (the access was skipped)"}
 
 
 def check_status(device: Optional[torch.device] = None) -> None:
@@ -94,6 +95,8 @@ def check_status(device: Optional[torch.device] = None) -> None:
         if v != 0:
             t.zero_()
             raise RuntimeError(f"native kernel reported status {v} on cuda:{idx} ({STATUS_NAMES.get(v, 'unknown')})")
+    if _native.DEBUG_BOUNDS and "b200_moe_debug_bad_index" in _SIG and fn("b200_moe_debug_bad_index")() > 0:
+        raise RuntimeError("debug build: the expert permutation computed a row outside its tables (counts and top-k indices disagree)")
 
 
 # LMMS_B200_DEBUG_SYNC=1: synchronise after every native launch and name the launcher whose kernel failed

@@ -20,7 +20,8 @@ class _GatherFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, src, idx):
         out = torch.empty((idx.numel(), src.shape[1]), dtype=src.dtype, device=src.device)
-        _cuda.call("b200_gather_rows", src.data_ptr(), idx.data_ptr(), out.data_ptr(), idx.numel(), src.shape[1], _cuda.stream())
+        _cuda.call("b200_gather_rows", src.data_ptr(), idx.data_ptr(), out.data_ptr(), idx.numel(), src.shape[1], src.shape[0],
+                   _cuda.status_word(src.device).data_ptr(), _cuda.stream())
         ctx.save_for_backward(idx)
         ctx.n_src = src.shape[0]
         return out
@@ -31,7 +32,8 @@ class _GatherFn(torch.autograd.Function):
         dsrc = torch.zeros((ctx.n_src, dout.shape[1]), dtype=dout.dtype, device=dout.device)
         dout = dout.contiguous()
         # indices are unique in every use of this op (a permutation or a subset)
-        _cuda.call("b200_scatter_rows", dout.data_ptr(), idx.data_ptr(), dsrc.data_ptr(), idx.numel(), dout.shape[1], 0, _cuda.stream())
+        _cuda.call("b200_scatter_rows", dout.data_ptr(), idx.data_ptr(), dsrc.data_ptr(), idx.numel(), dout.shape[1], 0, ctx.n_src,
+                   _cuda.status_word(dout.device).data_ptr(), _cuda.stream())
         return dsrc, None
 
 
@@ -49,7 +51,8 @@ class _ScatterFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, base, src, idx, add):
         out = base.clone()
-        _cuda.call("b200_scatter_rows", src.data_ptr(), idx.data_ptr(), out.data_ptr(), idx.numel(), src.shape[1], int(add), _cuda.stream())
+        _cuda.call("b200_scatter_rows", src.data_ptr(), idx.data_ptr(), out.data_ptr(), idx.numel(), src.shape[1], int(add), out.shape[0],
+                   _cuda.status_word(src.device).data_ptr(), _cuda.stream())
         ctx.save_for_backward(idx)
         ctx.add = add
         return out
@@ -59,7 +62,8 @@ class _ScatterFn(torch.autograd.Function):
         (idx,) = ctx.saved_tensors
         dout = dout.contiguous()
         dsrc = torch.empty((idx.numel(), dout.shape[1]), dtype=dout.dtype, device=dout.device)
-        _cuda.call("b200_gather_rows", dout.data_ptr(), idx.data_ptr(), dsrc.data_ptr(), idx.numel(), dout.shape[1], _cuda.stream())
+        _cuda.call("b200_gather_rows", dout.data_ptr(), idx.data_ptr(), dsrc.data_ptr(), idx.numel(), dout.shape[1], dout.shape[0],
+                   _cuda.status_word(dout.device).data_ptr(), _cuda.stream())
         if ctx.add:
             dbase = dout
         else:

@@ -26,9 +26,10 @@ from . import _cuda
 
 _cuda.register("b200_moe_router", "moe", "pippppiiiiis")
 _cuda.register("b200_moe_permute", "moe", "ppppppppiiils")
-_cuda.register("b200_moe_combine", "moe", "ppppiiis")
-_cuda.register("b200_moe_combine_bwd_src", "moe", "pppplis")
-_cuda.register("b200_moe_combine_bwd_w", "moe", "pppplii" + "s")
+_cuda.register("b200_moe_debug_bad_index", "moe", "")
+_cuda.register("b200_moe_combine", "moe", "ppppiii" + "lps")
+_cuda.register("b200_moe_combine_bwd_src", "moe", "pppplilps")
+_cuda.register("b200_moe_combine_bwd_w", "moe", "pppplii" + "lps")
 _cuda.register("b200_swiglu_cat_fwd", "moe", "pplis")
 _cuda.register("b200_swiglu_cat_bwd", "moe", "pplis")
 _cuda.register("b200_gemm_grouped_bf16", "gemm_sm100", "ppppiiiiiiips")
@@ -150,7 +151,8 @@ class _DispatchFn(torch.autograd.Function):
     def forward(ctx, x, perm: Permutation):
         H = x.shape[1]
         out = torch.empty((perm.rows, H), dtype=x.dtype, device=x.device)
-        _cuda.call("b200_gather_rows", x.data_ptr(), perm.token_of_row.data_ptr(), out.data_ptr(), perm.rows, H, _cuda.stream())
+        _cuda.call("b200_gather_rows", x.data_ptr(), perm.token_of_row.data_ptr(), out.data_ptr(), perm.rows, H, x.shape[0],
+                   _cuda.status_word(x.device).data_ptr(), _cuda.stream())
         ctx.perm = perm
         ctx.T = x.shape[0]
         return out
@@ -162,7 +164,8 @@ class _DispatchFn(torch.autograd.Function):
         H = dout.shape[1]
         k = perm.row_of.shape[1]
         dx = torch.empty((ctx.T, H), dtype=dout.dtype, device=dout.device)
-        _cuda.call("b200_moe_combine", dout.data_ptr(), perm.row_of.data_ptr(), None, dx.data_ptr(), ctx.T, k, H, _cuda.stream())
+        _cuda.call("b200_moe_combine", dout.data_ptr(), perm.row_of.data_ptr(), None, dx.data_ptr(), ctx.T, k, H, dout.shape[0],
+                   _cuda.status_word(dout.device).data_ptr(), _cuda.stream())
         return dx, None
 
 
@@ -182,7 +185,8 @@ class _CombineFn(torch.autograd.Function):
         H = src.shape[1]
         wf = w.float().contiguous()
         out = torch.empty((T, H), dtype=src.dtype, device=src.device)
-        _cuda.call("b200_moe_combine", src.data_ptr(), perm.row_of.data_ptr(), wf.data_ptr(), out.data_ptr(), T, k, H, _cuda.stream())
+        _cuda.call("b200_moe_combine", src.data_ptr(), perm.row_of.data_ptr(), wf.data_ptr(), out.data_ptr(), T, k, H, src.shape[0],
+                   _cuda.status_word(src.device).data_ptr(), _cuda.stream())
         ctx.save_for_backward(src, wf)
         ctx.perm = perm
         ctx.wdtype = w.dtype
@@ -195,11 +199,12 @@ class _CombineFn(torch.autograd.Function):
         dout = dout.contiguous()
         T, k = perm.row_of.shape
         H = src.shape[1]
-        dsrc = torch.empty_like(src)
+        dsrc = torch.empty_like(src) if src.shape[0] == perm.rows else torch.zeros_like(src)
         _cuda.call("b200_moe_combine_bwd_src", dout.data_ptr(), perm.token_of_row.data_ptr(), perm.weight_of_row.data_ptr(),
-                   dsrc.data_ptr(), perm.rows, H, _cuda.stream())
+                   dsrc.data_ptr(), min(perm.rows, src.shape[0]), H, dout.shape[0], _cuda.status_word(src.device).data_ptr(), _cuda.stream())
         dw = torch.empty((T, k), dtype=torch.float32, device=src.device)
-        _cuda.call("b200_moe_combine_bwd_w", dout.data_ptr(), src.data_ptr(), perm.row_of.data_ptr(), dw.data_ptr(), T * k, k, H, _cuda.stream())
+        _cuda.call("b200_moe_combine_bwd_w", dout.data_ptr(), src.data_ptr(), perm.row_of.data_ptr(), dw.data_ptr(), T * k, k, H, src.shape[0],
+                   _cuda.status_word(src.device).data_ptr(), _cuda.stream())
         return dsrc, dw.to(ctx.wdtype), None
 
 
