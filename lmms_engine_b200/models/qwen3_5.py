@@ -45,6 +45,7 @@ class Qwen35Config(DecoderConfig):
     linear_value_head_dim: int = 128
     linear_num_key_heads: int = 16
     linear_num_value_heads: int = 32
+    linear_attn_cp: str = "auto"  # under sequence parallelism: heads | state | auto (see GatedDeltaNet.cp_mode)
     layer_types: Optional[List[str]] = None
     full_attention_interval: int = 4
 
@@ -152,6 +153,7 @@ class GatedDeltaNet(nn.Module):
         self.in_proj_z = nn.Linear(cfg.hidden_size, self.value_dim, bias=False)
         self.in_proj_b = nn.Linear(cfg.hidden_size, self.hv, bias=False)
         self.in_proj_a = nn.Linear(cfg.hidden_size, self.hv, bias=False)
+        self.linear_attn_cp = getattr(cfg, "linear_attn_cp", "auto")
 
     def forward(self, x: torch.Tensor, ctx: PackedContext) -> torch.Tensor:
         T = x.shape[0]
@@ -165,6 +167,9 @@ class GatedDeltaNet(nn.Module):
         b, a = proj[:, c + self.value_dim:c + self.value_dim + self.hv], proj[:, c + self.value_dim + self.hv:c + self.value_dim + 2 * self.hv]
         A_log, dt_bias, conv_w = self.A_log, self.dt_bias, self.conv1d.weight[:, 0]
         hk, hv = self.hk, self.hv
+        by_state = ctx.sp_size > 1 and self.cp_mode(ctx.sp_size) == "state"
+        if by_state:
+            return self._finish(self._forward_state_cp(mixed, a, b, conv_w, ctx, x.device), z, x, T)
         if ctx.sp_size > 1:
             # Ulysses: the convolution and the rule run on whole sequences of this rank's heads.  Heads are
             # independent (the convolution is depthwise), so one exchange in and one out carry the layer.
@@ -199,6 +204,41 @@ class GatedDeltaNet(nn.Module):
             o = torch.cat([o, o.new_zeros((mixed.shape[0] - o.shape[0], hv, self.dv))], 0)
         if ctx.sp_size > 1:
             o = sp.gather_heads_scatter_seq(o, ctx.sp_group)
+        return self._finish(o, z, x, T)
+
+    def cp_mode(self, sp_size: int) -> str:
+        """How the layer runs under sequence parallelism: ``heads`` trades the token split for a head split (needs the
+        head counts to divide the group), ``state`` keeps the tokens where they are and hands the recurrent state from
+        rank to rank.  ``linear_attn_cp`` in the config picks one; ``auto`` takes ``heads`` when it divides."""
+        mode = getattr(self, "linear_attn_cp", "auto")
+        if mode == "auto":
+            return "heads" if (self.hk % sp_size == 0 and self.hv % sp_size == 0) else "state"
+        return mode
+
+    def _forward_state_cp(self, mixed, a, b, conv_w, ctx, device):
+        """All heads, this rank's tokens: convolution with a halo of ``kernel - 1`` rows from the previous rank, the
+        rule with the state handed over between ranks."""
+        lengths, pos_in_doc, chunks, first_continues, live = gdn_ops.cp_plan_for(ctx, device, ctx.sp_group)
+        K = self.kernel
+        halo = gdn_ops.conv_halo(mixed[:max(live, 0)] if live else mixed[:0], K - 1, ctx.sp_group)
+        beta = b.sigmoid()
+        g = -self.A_log.float().exp() * F.softplus(a.float() + self.dt_bias)
+        if live:
+            first = int(pos_in_doc[0]) if first_continues else 0
+            halo_pos = torch.arange(first - (K - 1), first, device=device).clamp(min=0)
+            seg = gdn_ops.causal_conv_silu_packed(torch.cat([halo, mixed[:live]], 0), conv_w, torch.cat([halo_pos, pos_in_doc]))[K - 1:]
+        else:
+            seg = mixed[:0] + 0.0 * halo.sum()
+        q, k, v = torch.split(seg, [self.key_dim, self.key_dim, self.value_dim], -1)
+        q, k, v = q.reshape(-1, self.hk, self.dk), k.reshape(-1, self.hk, self.dk), v.reshape(-1, self.hv, self.dv)
+        if self.hv // self.hk > 1:
+            q, k = q.repeat_interleave(self.hv // self.hk, 1), k.repeat_interleave(self.hv // self.hk, 1)
+        o = gdn_ops.chunk_gated_delta_rule_cp(q, k, v, g[:live], beta[:live], lengths, first_continues, ctx.sp_group, chunks)
+        if o.shape[0] < mixed.shape[0]:
+            o = torch.cat([o, o.new_zeros((mixed.shape[0] - o.shape[0], self.hv, self.dv))], 0)
+        return o
+
+    def _finish(self, o, z, x, T):
         # RMSNorm over the head dim, gated by SiLU(z)
         o = norm_ops.rmsnorm(o.reshape(-1, self.dv).to(x.dtype), self.norm.weight, self.eps)
         o = (o.float() * F.silu(z.reshape(-1, self.dv).float())).to(x.dtype).reshape(T, self.value_dim)

@@ -159,16 +159,9 @@ def plan_for(ctx, device):
     return plan
 
 
-def chunk_gated_delta_rule_packed(q, k, v, g, beta, lengths: List[int], plan=None):
-    """``q, k [T, H, dk]``, ``v [T, H, dv]``, ``g, beta [T, H]`` for documents of ``lengths`` laid end to end ->
-    ``o [T, H, dv]``.  Math in fp32; q and k are L2-normalised here, q is scaled by ``dk ** -0.5``."""
-    dt = q.dtype
-    T, H, dk = k.shape
-    dv = v.shape[-1]
-    src, back, reset = plan if plan is not None else chunk_plan(lengths, q.device)
-    n = len(reset)
-    if n == 0:
-        return v.new_zeros((T, H, dv))
+def _chunk_terms(q, k, v, g, beta, src, back, n):
+    """Per-chunk quantities of the rule from packed inputs: what the scan consumes and what finishes the output."""
+    dk = k.shape[-1]
 
     def lay(x):  # [T, H, ...] -> contiguous fp32 [H, n, C, ...] with zero padding rows
         # gather in the input dtype (half the bytes for bf16 streams), then one strided copy that also casts
@@ -192,13 +185,147 @@ def chunk_gated_delta_rule_packed(q, k, v, g, beta, lengths: List[int], plan=Non
     qt = q * g.exp()[..., None]
     kt = k * (g[..., -1:] - g).exp()[..., None]
     gamma = g[..., -1].exp()
-    v_new, o_state = scan(w, u, qt, kt, gamma, reset)
     attn = ((q @ k.transpose(-1, -2)) * decay).masked_fill(strict, 0)
+    return w, u, qt, kt, gamma, attn
+
+
+def cp_plan_for(ctx, device, group):
+    """Like ``plan_for`` for this rank's contiguous slice of the (padded) stream: ``(piece lengths, position of every
+    local token inside its document, chunk plan, first_continues, live)``; ``live`` = local rows that are real tokens."""
+    import torch.distributed as dist
+
+    plan = getattr(ctx, "gdn_cp_plan", None)
+    if plan is None:
+        bounds = [int(b) for b in ctx.cu_seqlens.tolist()]
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        total = ctx.split_total or bounds[-1] + (-bounds[-1]) % world
+        per = total // world
+        lo, hi = rank * per, min((rank + 1) * per, bounds[-1])
+        lengths, pos, first_continues = [], [], False
+        for a, b in zip(bounds[:-1], bounds[1:]):
+            s, e = max(a, lo), min(b, hi)
+            if e > s:
+                if not lengths and s > a:
+                    first_continues = True
+                lengths.append(e - s)
+                pos.append(torch.arange(s - a, e - a))
+        pos_t = torch.cat(pos) if pos else torch.zeros(0, dtype=torch.long)
+        plan = (lengths, pos_t.to(device, non_blocking=True), chunk_plan(lengths, device), first_continues, max(hi - lo, 0))
+        try:
+            ctx.gdn_cp_plan = plan
+        except AttributeError:
+            pass
+    return plan
+
+
+def chunk_gated_delta_rule_packed(q, k, v, g, beta, lengths: List[int], plan=None):
+    """``q, k [T, H, dk]``, ``v [T, H, dv]``, ``g, beta [T, H]`` for documents of ``lengths`` laid end to end ->
+    ``o [T, H, dv]``.  Math in fp32; q and k are L2-normalised here, q is scaled by ``dk ** -0.5``."""
+    dt = q.dtype
+    T, H, dk = k.shape
+    dv = v.shape[-1]
+    src, back, reset = plan if plan is not None else chunk_plan(lengths, q.device)
+    n = len(reset)
+    if n == 0:
+        return v.new_zeros((T, H, dv))
+    w, u, qt, kt, gamma, attn = _chunk_terms(q, k, v, g, beta, src, back, n)
+    v_new, o_state = scan(w, u, qt, kt, gamma, reset)
     out = o_state + attn @ v_new                   # [H, n, C, dv]
     # back to the stream: cast first (half the bytes for bf16 streams), one strided copy, one gather
     out = out.to(dt).movedim(0, 2).reshape(n * CHUNK, H, dv)
     # stream row t sits at padded row back[t]; the gradient of this gather is the gather by ``src`` of [g; 0]
     return _unpad(out, back, src)
+
+
+# ------------------------------------------------------------------------------ state hand-off between ranks
+def scan_with_state(w, u, qt, kt, gamma, reset: List[bool], init=None, read_final: bool = False):
+    """The chunk recurrence with a given state before the first chunk and / or the state after the last chunk read
+    out, on the unchanged scan (kernel or loop).  Both are expressed as extra chunks: ``init [H, dk, dvv]`` enters
+    through chunks whose keys are rows of the identity and whose values are the rows of ``init`` (no decay, no
+    correction, no output), the final state leaves through chunks whose queries are rows of the identity.  Gradients
+    with respect to ``init`` and of the final state follow from the scan's own backward."""
+    H, n, C, dk = w.shape
+    dvv = u.shape[-1]
+    nf = (dk + C - 1) // C
+    eye = torch.zeros((nf * C, dk), dtype=w.dtype, device=w.device)
+    eye[:dk] = torch.eye(dk, dtype=w.dtype, device=w.device)
+    eye = eye.view(nf, C, dk)[None].expand(H, -1, -1, -1)
+    zk, zv, one = w.new_zeros((H, nf, C, dk)), u.new_zeros((H, nf, C, dvv)), gamma.new_ones((H, nf))
+    reset = list(reset)
+    pre = post = 0
+    if init is not None:
+        rows = torch.cat([init.to(u.dtype), u.new_zeros((H, nf * C - dk, dvv))], 1).view(H, nf, C, dvv)
+        w, u, qt, kt, gamma = torch.cat([zk, w], 1), torch.cat([rows, u], 1), torch.cat([zk, qt], 1), torch.cat([eye, kt], 1), torch.cat([one, gamma], 1)
+        reset = [True] + [False] * (nf - 1) + [False] + reset[1:]
+        pre = nf
+    if read_final:
+        w, u, qt, kt, gamma = torch.cat([w, zk], 1), torch.cat([u, zv], 1), torch.cat([qt, eye], 1), torch.cat([kt, zk], 1), torch.cat([gamma, one], 1)
+        reset = reset + [False] * nf
+        post = nf
+    v_new, o = scan(w.contiguous(), u.contiguous(), qt.contiguous(), kt.contiguous(), gamma.contiguous(), reset)
+    final = o[:, pre + n:].reshape(H, nf * C, dvv)[:, :dk] if read_final else None
+    return v_new[:, pre:pre + n], o[:, pre:pre + n], final
+
+
+def chunk_gated_delta_rule_cp(q, k, v, g, beta, lengths: List[int], first_continues: bool, group, plan=None):
+    """The rule when the packed stream is split into contiguous token slices over the ranks of ``group`` (all heads on
+    every rank).  ``lengths``: the pieces of documents inside this rank's slice; ``first_continues``: the first piece
+    continues a document that began on an earlier rank.
+
+    The state recurrence is affine in the state, so a slice acts on an incoming state ``S`` as ``A S + B``: ``B`` is the
+    slice's own final state from zero, ``A`` its final state from the identity with zero values, and the outputs are
+    ``out(0) + outA S``.  Every rank runs those two scans on its own slice at once (the second only when its first piece
+    continues), ``A`` and ``B`` of all ranks are gathered (``[H, dk, dk]`` and ``[H, dk, dv]`` per rank) and every rank folds
+    the earlier ranks' maps into its incoming state.  A document boundary inside a slice resets the state, which makes
+    that slice's ``A`` zero by construction.  The reference delegates this to the FLA library's context-parallel path
+    (src/lmms_engine/models/qwen3_5/qwen3_5_ops.py:183-200, 266-279)."""
+    import torch.distributed as dist
+    import torch.distributed.nn.functional as dist_fn
+
+    dt = q.dtype
+    T, H, dk = k.shape
+    dv = v.shape[-1]
+    src, back, reset = plan if plan is not None else chunk_plan(lengths, q.device)
+    n = len(reset)
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    dev = q.device
+    if n:
+        w, u, qt, kt, gamma, attn = _chunk_terms(q, k, v, g, beta, src, back, n)
+        v0, o0, B = scan_with_state(w, u, qt, kt, gamma, reset, None, True)
+        out0 = o0 + attn @ v0
+        if first_continues:
+            ident = torch.eye(dk, dtype=torch.float32, device=dev)[None].expand(H, -1, -1)
+            vA, oA, A = scan_with_state(w, torch.zeros_like(w), qt, kt, gamma, reset, ident, True)
+            outA = oA + attn @ vA                     # [H, n, C, dk]: how the outputs read the incoming state
+        else:
+            A, outA = torch.zeros((H, dk, dk), dtype=torch.float32, device=dev), None
+    else:  # an empty slice (only padding of the split) passes the state on unchanged
+        B = torch.zeros((H, dk, dv), dtype=torch.float32, device=dev) + 0.0 * (q.sum() + k.sum() + v.sum() + g.sum() + beta.sum()).float()
+        A = torch.eye(dk, dtype=torch.float32, device=dev)[None].expand(H, -1, -1).contiguous() if first_continues else torch.zeros((H, dk, dk), dtype=torch.float32, device=dev)
+        outA = out0 = None
+    packed = torch.cat([A.reshape(H, -1), B.reshape(H, -1)], 1).contiguous()
+    everyone = dist_fn.all_gather(packed, group=group)
+    # every rank must run the gather's backward (a collective), also the ranks that use none of its outputs
+    S = torch.zeros((H, dk, dv), dtype=torch.float32, device=dev) + 0.0 * sum(e.sum() for e in everyone)
+    for j in range(rank):
+        Aj, Bj = everyone[j][:, : dk * dk].view(H, dk, dk), everyone[j][:, dk * dk:].view(H, dk, dv)
+        S = Aj @ S + Bj
+    if not n:
+        return v.new_zeros((T, H, dv)) + 0.0 * S.sum().to(dt)
+    out = out0 + 0.0 * S.sum() if outA is None else out0 + outA @ S[:, None]
+    out = out.to(dt).movedim(0, 2).reshape(n * CHUNK, H, dv)
+    return _unpad(out, back, src)
+
+
+def conv_halo(x: torch.Tensor, rows: int, group):
+    """The last ``rows`` rows of the previous rank's slice (zeros on the first rank), differentiably."""
+    import torch.distributed as dist
+    import torch.distributed.nn.functional as dist_fn
+
+    rank = dist.get_rank(group)
+    tail = x[-rows:] if x.shape[0] >= rows else torch.cat([x.new_zeros((rows - x.shape[0],) + x.shape[1:]), x], 0)
+    tails = dist_fn.all_gather(tail.contiguous(), group=group)
+    return tails[rank - 1] if rank > 0 else torch.zeros_like(tail) + 0.0 * tails[0]
 
 
 def causal_conv_silu_ref(x: torch.Tensor, weight: torch.Tensor, pos_in_doc: torch.Tensor) -> torch.Tensor:

@@ -62,19 +62,23 @@ def main(mode):
     cfg = DecoderConfig(model_type="qwen3", vocab_size=256, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
                         num_attention_heads=4, num_key_value_heads=2 if mode == "tp" else 1, head_dim=16)
     build = DecoderLM
-    if mode == "ulysses_hybrid":
-        # Gated-DeltaNet + gated-attention hybrid: both layer kinds trade the sequence split for a head split
+    if mode.startswith("ulysses_hybrid"):
+        # Gated-DeltaNet + gated-attention hybrid: both layer kinds trade the sequence split for a head split; in the
+        # "_state" variant the linear-attention layers keep their tokens and hand the recurrent state from rank to rank
+        # (3 key heads / 3 value heads: no head split over 2 or 4 ranks exists)
         from lmms_engine_b200.models.qwen3_5 import Qwen35Config, Qwen35LM
 
+        state = mode.endswith("_state")
         cfg = Qwen35Config(vocab_size=256, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
-                           num_key_value_heads=2, head_dim=16, linear_conv_kernel_dim=4, linear_key_head_dim=16,
-                           linear_value_head_dim=16, linear_num_key_heads=2, linear_num_value_heads=4, partial_rotary_factor=0.5)
+                           num_key_value_heads=2 if not state else 4, head_dim=16, linear_conv_kernel_dim=4, linear_key_head_dim=16,
+                           linear_value_head_dim=16, linear_num_key_heads=3 if state else 2, linear_num_value_heads=3 if state else 4,
+                           partial_rotary_factor=0.5, linear_attn_cp="state" if state else "auto")
         build = Qwen35LM
     torch.manual_seed(0)
     full = build(cfg)
     torch.manual_seed(0)
     model = build(cfg)
-    if mode == "ulysses_hybrid":
+    if mode.startswith("ulysses_hybrid"):
         with torch.no_grad():  # zero-centred norm scales and unit decay parameters would hide mistakes
             for m_ in (full, model):
                 g_ = torch.Generator().manual_seed(7)
@@ -84,6 +88,9 @@ def main(mode):
     g = torch.Generator().manual_seed(3)
     ids = torch.randint(0, 256, (91,), generator=g)  # not a multiple of the group size: exercises padding
     cu = torch.tensor([0, 40, 91], dtype=torch.int32)
+    if mode.endswith("_state"):  # a document that spans three ranks' slices, then two short ones
+        ids = torch.randint(0, 256, (203,), generator=g)
+        cu = torch.tensor([0, 150, 170, 203], dtype=torch.int32)
     ref = full(input_ids=ids, labels=ids, cu_seqlens=cu)["loss"]
     ref.backward()
     if mode == "tp":

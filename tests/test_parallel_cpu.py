@@ -87,5 +87,13 @@ def test_ulysses_hybrid_linear_attention_matches_unsharded():
     assert "ulysses_hybrid ok" in torchrun("tp_run.py", 2, "ulysses_hybrid")
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_linear_attention_state_hand_off_between_ranks(world):
+    """Gated-DeltaNet layers under sequence parallelism WITHOUT a head split: every rank keeps its tokens, the recurrent
+    state (and the convolution's last rows) pass from rank to rank; loss and gradients equal the unsharded model's, with
+    head counts that do not divide the group."""
+    assert "ulysses_hybrid_state ok" in torchrun("tp_run.py", world, "ulysses_hybrid_state")
+
+
 def test_vit_frame_parallel_matches_local_tower():
     assert "vit frame parallel ok" in torchrun("vit_fp_run.py", 3)
