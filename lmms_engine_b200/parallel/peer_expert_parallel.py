@@ -5,7 +5,8 @@ Per layer:
 
 1. the count matrix is all-gathered and read on the host once (like the reference,
    src/lmms_engine/parallel/expert_parallel/utils.py:11-77) to size the expert-major layout of every
-   rank; from it every local row gets its destination ``(rank, row)``;
+   rank; from it every local row gets its destination ``(rank, row)``.  With ``LMMS_B200_EP_DEVICE_LAYOUT=1`` the
+   same layout is computed on the device for receive areas of a fixed capacity, and nothing is read back;
 2. **push**: one kernel gathers token rows through the local permutation and stores them directly at
    their final expert-major row on the owning rank (no send buffer, no receive-side regroup);
 3. grouped tcgen05 GEMMs on the owner (``ops.moe.grouped_mlp``);
@@ -21,6 +22,7 @@ every rank's arrival, a pull starts with every rank's readiness).
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import List, Optional
 
 import torch
@@ -69,6 +71,10 @@ class PeerExpertParallel(ExpertParallel):
         self.x_stage: Optional[_Stage] = None  # peers push into it
         self.y_stage: Optional[_Stage] = None  # peers pull from it
         self.launches = 0
+        # LMMS_B200_EP_DEVICE_LAYOUT=1: no host read of the count matrix per layer (fixed-capacity receive areas,
+        # overflow reported through the status word); costs activation memory in proportion to the capacity factor
+        self.device_layout = os.environ.get("LMMS_B200_EP_DEVICE_LAYOUT", "0") == "1"
+        self.capacity_factor = float(os.environ.get("LMMS_B200_EP_CAPACITY", "1.5"))
 
     # ------------------------------------------------------------------ layout
     def _stages(self, rows_needed: int, H: int):
@@ -112,6 +118,52 @@ class PeerExpertParallel(ExpertParallel):
                                     expert_start=expert_start.to(dev), rows=my_rows, n_experts=El)
         return dest_rank, dest_row, local, int(rows_per_rank.max())
 
+    def capacity(self, T: int, k: int) -> int:
+        """Rows reserved per rank when the layout is computed on the device: ``capacity_factor`` x the balanced share
+        (``T * k`` rows when every rank brings ``T`` tokens) plus the worst-case tile padding."""
+        rows = int(self.capacity_factor * T * k) + self.ep * self.El * TILE
+        return (rows + 4095) // 4096 * 4096
+
+    def layout_device(self, counts: torch.Tensor, perm: moe_ops.Permutation, cap: int):
+        """``layout`` without the host: the same destinations and expert-major layout as tensors computed on the device
+        from the gathered count matrix, for a receive area of ``cap`` rows known before the counts are.  Rows that would
+        land beyond ``cap`` are not sent (destination rank -1) and raise the overflow status word, which the next status
+        check turns into an exception: raise ``capacity_factor`` (or use the host layout) for such routing."""
+        all_counts = torch.empty(self.ep * self.E, dtype=counts.dtype, device=counts.device)
+        dist.all_gather_into_tensor(all_counts, counts.contiguous(), group=self.group)
+        return self.layout_from_counts(all_counts.view(self.ep, self.E), perm, cap, self.rank, self.El,
+                                       _cuda.status_word(self.device) if counts.is_cuda else None)
+
+    @staticmethod
+    def layout_from_counts(C: torch.Tensor, perm: moe_ops.Permutation, cap: int, me: int, El: int, status: Optional[torch.Tensor] = None):
+        ep, E = C.shape
+        dev = C.device
+        P = (C.long() + TILE - 1) // TILE * TILE             # padded segment sizes, [source, expert]
+        per_expert = P.sum(0)                                # rows of expert e on its owner
+        seg = per_expert.view(ep, El)
+        start_on_owner = (seg.cumsum(1) - seg).flatten()     # owner lays out expert e as [source 0 | source 1 | ...]
+        before_me = P[:me].sum(0)
+        send_base = start_on_owner + before_me
+        e_row = perm.tile_expert.long().repeat_interleave(TILE)
+        live = e_row >= 0
+        e_safe = e_row.clamp(min=0)
+        pos = torch.arange(e_row.numel(), device=dev) - perm.expert_start.long()[e_safe]
+        dest_row = torch.where(live, send_base[e_safe] + pos, torch.zeros_like(pos))
+        fits = dest_row < cap
+        dest_rank = torch.where(live & fits, e_safe // El, torch.full_like(e_safe, -1)).to(torch.int32)
+        dest_row = torch.where(fits, dest_row, torch.zeros_like(dest_row)).to(torch.int32)
+        if status is not None:  # any rank's area too small: every rank learns of it from the same count matrix
+            over = (seg.sum(1) > cap).any()
+            status.copy_(torch.where(over, torch.full_like(status, 4), status))
+        mine = per_expert[me * El:(me + 1) * El]
+        expert_start = torch.cat([mine.new_zeros(1), mine.cumsum(0)]).clamp(max=cap).to(torch.int32)
+        tile_row = torch.arange(cap // TILE, device=dev) * TILE
+        tile_expert = torch.searchsorted(expert_start[1:].long(), tile_row, right=True)
+        tile_expert = torch.where(tile_row < expert_start[-1].long(), tile_expert, torch.full_like(tile_expert, -1)).to(torch.int32)
+        local = moe_ops.Permutation(row_of=None, token_of_row=None, weight_of_row=None, tile_expert=tile_expert,
+                                    expert_start=expert_start, rows=cap, n_experts=El)
+        return dest_rank, dest_row, local, cap
+
     # ------------------------------------------------------------------ kernels
     def push(self, x, perm, dest_rank, dest_row, scalar=None):
         self.push_epoch += 1
@@ -149,7 +201,10 @@ class PeerExpertParallel(ExpertParallel):
     # ------------------------------------------------------------------ layer
     def __call__(self, x, idx, w, counts, experts) -> torch.Tensor:
         perm = moe_ops.build_permutation(idx, w, counts)  # by global expert id
-        dest_rank, dest_row, local, cap = self.layout(counts, perm)
+        if self.device_layout:
+            dest_rank, dest_row, local, cap = self.layout_device(counts, perm, self.capacity(*idx.shape))
+        else:
+            dest_rank, dest_row, local, cap = self.layout(counts, perm)
         self._stages(cap, x.shape[1])
         grouped = _PeerDispatch.apply(x.contiguous(), self, perm, dest_rank, dest_row, local.rows)
         yp = experts(grouped, local)

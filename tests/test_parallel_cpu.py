@@ -97,3 +97,43 @@ def test_linear_attention_state_hand_off_between_ranks(world):
 
 def test_vit_frame_parallel_matches_local_tower():
     assert "vit frame parallel ok" in torchrun("vit_fp_run.py", 3)
+
+
+def test_expert_layout_computed_on_the_device_equals_the_host_layout():
+    """The fixed-capacity layout (no read-back of the count matrix) gives the same destinations and expert-major
+    tables as the host layout; an area that is too small withholds the rows that do not fit and raises the status word."""
+    import torch
+
+    from lmms_engine_b200.ops import moe as moe_ops
+    from lmms_engine_b200.parallel.peer_expert_parallel import PeerExpertParallel
+
+    torch.manual_seed(0)
+    ep, E, T, k = 4, 8, 50, 2
+    El, TILE = E // ep, moe_ops.TILE
+    idx_all = [torch.stack([torch.randperm(E)[:k] for _ in range(T)]) for _ in range(ep)]
+    counts_all = torch.stack([torch.bincount(i.flatten(), minlength=E) for i in idx_all]).int()
+    for me in range(ep):
+        idx = idx_all[me]
+        perm = moe_ops.build_permutation(idx.int(), torch.rand(T, k), counts_all[me])
+        # host layout, restated: owner r holds its experts in order, each as [source 0 | source 1 | ...] padded to tiles
+        P = (counts_all.long() + TILE - 1) // TILE * TILE
+        per_expert = P.sum(0)
+        rows_per_rank = per_expert.view(ep, El).sum(1)
+        cap = int(rows_per_rank.max())
+        dest_rank, dest_row, local, _ = PeerExpertParallel.layout_from_counts(counts_all, perm, cap, me, El)
+        for t in range(T):
+            for j in range(k):
+                e = int(idx[t, j])
+                row = int(perm.row_of[t, j])
+                owner = e // El
+                base = int(per_expert[owner * El:e].sum() + P[:me, e].sum())
+                assert int(dest_rank[row]) == owner and int(dest_row[row]) == base + (row - int(perm.expert_start[e]))
+        assert local.expert_start.tolist() == [0] + per_expert[me * El:(me + 1) * El].cumsum(0).tolist()
+        assert local.tile_expert.numel() == cap // TILE
+        want_tiles = sum(([i] * int(per_expert[me * El + i] // TILE) for i in range(El)), [])
+        assert local.tile_expert.tolist()[: len(want_tiles)] == want_tiles and all(v == -1 for v in local.tile_expert.tolist()[len(want_tiles):])
+        # an area one tile too small for the fullest rank
+        status = torch.zeros(1, dtype=torch.int32)
+        small = cap - TILE
+        d_rank, d_row, loc, _ = PeerExpertParallel.layout_from_counts(counts_all, perm, small, me, El, status)
+        assert int(status) == 4 and int(d_row.max()) < small and int(loc.expert_start.max()) <= small
