@@ -87,20 +87,45 @@ class DataUtilities:
         return DataUtilities.load_inline_datasets(spec["datasets"])
 
     @staticmethod
-    def load_inline_datasets(specs: List[dict], workers: int = 8) -> Tuple[List[dict], List[str]]:
-        """Every source is loaded in parallel; returns the concatenated records and, per record,
-        the ``data_folder`` of the source it came from."""
-        def _load(spec):
-            recs = DataUtilities.load_one(spec["path"], spec.get("data_type", "json"))
-            return recs, [spec.get("data_folder", "") or ""] * len(recs)
+    def _load_spec(spec: dict):
+        return DataUtilities.load_one(spec["path"], spec.get("data_type", "json"))
 
-        with ThreadPoolExecutor(max_workers=max(1, min(workers, len(specs)))) as ex:
-            parts = list(ex.map(_load, specs))
+    @staticmethod
+    def load_inline_datasets(specs: List[dict], workers: int = 8, processes: Optional[bool] = None) -> Tuple[List[dict], List[str]]:
+        """Every source is loaded in parallel; returns the concatenated records and, per record, the ``data_folder`` of
+        the source it came from.  Parsing JSON holds the interpreter lock, so with several large sources the loads run
+        in worker PROCESSES (like the reference's pool, src/lmms_engine/utils/data_utils.py:129-153, 235-272);
+        ``processes=None`` chooses that when the sources total more than 64 MB, threads otherwise (no fork for small
+        data, and tests stay cheap).  ``LMMS_B200_DATA_LOAD_PROCESSES=0|1`` overrides."""
+        if not specs:
+            return [], []
+        env = os.environ.get("LMMS_B200_DATA_LOAD_PROCESSES")
+        if env is not None:
+            processes = env == "1"
+        if processes is None:
+            size = sum(os.path.getsize(s["path"]) for s in specs if os.path.isfile(s.get("path", "")))
+            processes = len(specs) > 1 and size > 64 * 2 ** 20
+        n = max(1, min(workers, len(specs)))
+        if processes:
+            import torch
+
+            # forked workers are cheap and need no importable main module, but a process that already holds a CUDA
+            # context must not fork: fall back to threads there
+            processes = not (torch.cuda.is_available() and torch.cuda.is_initialized())
+        if processes:
+            import multiprocessing as mp
+            from concurrent.futures import ProcessPoolExecutor
+
+            with ProcessPoolExecutor(max_workers=n, mp_context=mp.get_context("fork")) as ex:
+                parts = list(ex.map(DataUtilities._load_spec, specs))
+        else:
+            with ThreadPoolExecutor(max_workers=n) as ex:
+                parts = list(ex.map(DataUtilities._load_spec, specs))
         data, folders = [], []
-        for recs, f in parts:
+        for spec, recs in zip(specs, parts):
             data.extend(recs)
-            folders.extend(f)
-        logger.info(f"loaded {len(data)} records from {len(specs)} source(s)")
+            folders.extend([spec.get("data_folder", "") or ""] * len(recs))
+        logger.info(f"loaded {len(data)} records from {len(specs)} source(s) ({'processes' if processes else 'threads'})")
         return data, folders
 
     @staticmethod

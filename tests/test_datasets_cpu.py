@@ -578,3 +578,16 @@ def test_object_storage_serves_images_audio_and_videos(tmp_path):
     assert len(os.listdir(tmp_path / "cache")) == 2  # the video and the audio clip
     with pytest.raises(ValueError, match="bucket_name"):
         osto.make_client("gcs", None)
+
+
+def test_dataset_sources_load_in_worker_processes_or_threads(tmp_path):
+    from lmms_engine_b200.utils.data_utils import DataUtilities
+
+    specs = []
+    for i in range(3):
+        path = tmp_path / f"s{i}.jsonl"
+        path.write_text("".join(json.dumps({"id": f"{i}-{j}"}) + "\n" for j in range(5)))
+        specs.append({"path": str(path), "data_type": "jsonl", "data_folder": f"f{i}"})
+    threads = DataUtilities.load_inline_datasets(specs, processes=False)
+    procs = DataUtilities.load_inline_datasets(specs, processes=True)
+    assert threads == procs and [r["id"] for r in procs[0]][::5] == ["0-0", "1-0", "2-0"] and procs[1][::5] == ["f0", "f1", "f2"]
