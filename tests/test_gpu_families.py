@@ -156,3 +156,52 @@ def test_qwen3_5_hybrid_step_time_report():
     assert torch.isfinite(loss)
     print(f"QWEN35_TIME 4 layers (3 linear-attention + 1 gated-attention), 16384 tokens: {a.elapsed_time(b) / 2:.1f} ms per forward+backward, "
           f"peak memory {torch.cuda.max_memory_allocated() / 2**30:.1f} GiB", flush=True)
+
+
+def test_llava_onevision2_gpu():
+    from lmms_engine_b200.models.llava_ov2 import build_patch_positions
+
+    cfg = dict(model_type="llava_onevision2", text_config=dict(TEXT, rms_norm_eps=1e-6),
+               vision_config=dict(depth=2, hidden_size=128, intermediate_size=256, num_heads=4, patch_size=8, spatial_merge_size=2,
+                                  text_hidden_size=128, hidden_act="gelu"), image_token_id=250, video_token_id=251)
+    ids = torch.randint(0, 240, (1, 64))
+    ids[0, 4:10], ids[0, 30:33] = 250, 250
+    grid = torch.tensor([[1, 4, 6], [3, 2, 2]])  # an image and three kept codec blocks
+    import numpy as np
+
+    pos = torch.from_numpy(np.concatenate([build_patch_positions([(1, 4, 6)], 2),
+                                           np.array([[t, h, w] for t in (1, 4, 6) for h in (2, 3) for w in (0, 1)])]))
+    _compare("llava_onevision2", cfg, dict(input_ids=ids, attention_mask=torch.ones_like(ids), labels=ids, pixel_values=torch.randn(36, 3 * 8 * 8),
+                                           image_grid_thw=grid, patch_positions=pos))
+
+
+def test_wanvideo_transformer_gpu():
+    cfg = dict(dit_hidden_size=128, dit_num_layers=2, dit_num_heads=4, dit_intermediate_size=256, dit_in_channels=8, dit_out_channels=8,
+               dit_text_dim=64, vace=dict(vace_layers=[0], vace_in_dim=6), motion_controller=True, trainable_modules="dit,vace,motion_controller")
+    torch.manual_seed(1)
+    lat = torch.randn(2, 8, 3, 8, 8)
+    _compare("wanvideo", cfg, dict(latents=lat, context=torch.randn(2, 7, 64), timestep_index=torch.tensor([200, 800]),
+                                   noise=torch.randn(2, 8, 3, 8, 8), vace_context=torch.randn(2, 6, 3, 8, 8),
+                                   motion_bucket_id=torch.tensor([2.0, 5.0])), tol=0.2)
+
+
+def test_rae_siglip_gpu():
+    cfg = dict(noise_tau=0.0, encoder_config=dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                                                  image_size=32, patch_size=8),
+               decoder_config=dict(decoder_hidden_size=128, decoder_num_hidden_layers=2, decoder_num_attention_heads=4, decoder_intermediate_size=256))
+    _compare("rae_siglip", cfg, dict(pixel_values=torch.rand(3, 3, 32, 32)))
+
+
+def test_bagel_mixture_of_transformers_gpu():
+    cfg = dict(TEXT, model_type="bagel", layer_module="Qwen2MoTDecoderLayer", qk_norm=True, attention_bias=True, latent_channels=4,
+               latent_patch_size=2, max_latent_size=8, visual_und=True, vit_rope=False, vit_select_layer=-1, vit_max_num_patch_per_side=4,
+               vit_config=dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4, image_size=32, patch_size=8))
+    from lmms_engine_b200.models.bagel_parts import flattened_position_ids
+
+    ids = torch.randint(0, 250, (60,))
+    batch = dict(input_ids=ids, labels=ids, cu_seqlens=torch.tensor([0, 36, 60], dtype=torch.int32), vit_tokens=torch.randn(8, 3 * 8 * 8),
+                 vit_index=torch.arange(2, 10), vit_position_ids=flattened_position_ids(16, 32, 8, 4), vit_seqlens=torch.tensor([8]),
+                 latent_tokens=torch.randn(6, 16), latent_index=torch.arange(20, 26), latent_pos=torch.tensor([0, 1, 2, 8, 9, 10]),
+                 timesteps=torch.full((6,), 0.4), noise=torch.randn(6, 16),
+                 split_lens=[2, 8, 10, 6, 10, 24], attn_modes=["causal", "full", "causal", "noise", "causal", "causal"])
+    _compare("bagel", cfg, batch, tol=0.2)
