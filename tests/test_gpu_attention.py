@@ -88,3 +88,29 @@ def test_cu_seqlens_past_the_tensor_raise_status_not_a_fault():
     _cuda.check_status()
     with pytest.raises(NotImplementedError):
         attention.varlen_attn(q, k, v, good, good, causal=False, window_size=(-1, 16))
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_queries_shorter_than_keys_bottom_right_aligned(causal):
+    """Documents whose keys are a visible prefix followed by the queries' own tokens (the attention splits of the
+    unified model): the causal mask is aligned to the END of the keys."""
+    from lmms_engine_b200.ops import attention, _cuda
+
+    torch.manual_seed(0)
+    lq, lk = [5, 130, 64, 1], [40, 130, 300, 129]
+    cu_q = torch.tensor([0] + list(torch.tensor(lq).cumsum(0)), dtype=torch.int32, device="cuda")
+    cu_k = torch.tensor([0] + list(torch.tensor(lk).cumsum(0)), dtype=torch.int32, device="cuda")
+    q = torch.randn(sum(lq), 4, 64, device="cuda").to(torch.bfloat16).requires_grad_()
+    k = torch.randn(sum(lk), 2, 64, device="cuda").to(torch.bfloat16).requires_grad_()
+    v = torch.randn(sum(lk), 2, 64, device="cuda").to(torch.bfloat16).requires_grad_()
+    o = attention.varlen_attn(q, k, v, cu_q, cu_k, causal=causal)
+    do = torch.randn_like(o)
+    o.backward(do)
+    _cuda.check_status()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    orf = attention.varlen_attn_ref(qr, kr, vr, cu_q, cu_k, causal=causal)
+    orf.backward(do.float())
+    assert (o.float() - orf).abs().max().item() < 3e-2
+    for name, a, b in (("dq", q.grad, qr.grad), ("dk", k.grad, kr.grad), ("dv", v.grad, vr.grad)):
+        err = (a.float() - b).abs().max().item() / (b.abs().max().item() + 1e-6)
+        assert err < 3e-2, (name, err)
