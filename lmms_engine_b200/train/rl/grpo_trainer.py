@@ -147,7 +147,8 @@ class GRPOTrainer(FSDP2SFTTrainer):
         self.group_size = int(cfg.get("group_size", 8))
         self.max_new_tokens = int(cfg.get("max_new_tokens", 64))
         self.temperature = float(cfg.get("temperature", 1.0))
-        self.clip_range = float(cfg.get("clip_range", 0.2))
+        clip = cfg.get("clip_range", 0.2)
+        self.clip_range = float(clip[0] if isinstance(clip, (list, tuple)) else clip)
         self.beta = float(cfg.get("beta", 0.04))
         self.num_iterations = int(cfg.get("num_iterations", 1))
         self.eos_token_id = cfg.get("eos_token_id")

@@ -110,3 +110,15 @@ def test_transformers_fallback_family_trains(tmp_path):
     hist, runner = _run(tmp_path, "fsdp2_trainer", "mistral", cfg, _packed(collator_type="padded"), steps=4)
     assert type(runner.model).__module__.startswith("transformers")
     assert hist[-1]["train/loss"] < hist[0]["train/loss"] + 0.5
+
+
+def test_flow_grpo_trainer_samples_scores_and_replays_image_generation(tmp_path):
+    """Unified model: groups of images sampled per prompt with recorded SDE steps, rewards normalised per group, the
+    policy replays every recorded step and the optimizer moves after each."""
+    cfg = dict(model_type="bagel", vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=8, latent_channels=4, latent_patch_size=2, max_latent_size=8, layer_module="Qwen2MoTDecoderLayer")
+    hist, runner = _run(tmp_path, "flow_grpo_trainer", "bagel", cfg, _packed(prompt_len=4), steps=2,
+                        rl_config={"group_size": 3, "image_hw": [2, 2], "num_timesteps": 5, "sde_window": [1, 2], "noise_level": 0.7,
+                                   "reward": "latent_brightness", "boi_token_id": 126, "eoi_token_id": 127, "beta": 0.01, "clip_range": [1e-3, 1e-3]})
+    assert "rl/reward_mean" in hist[0] and hist[0]["rl/recorded_steps"] > 0 and "rl/policy_loss" in hist[0]
+    assert runner.trainer.ref_model is not None
