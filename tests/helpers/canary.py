@@ -2,7 +2,7 @@
 it hold a poison pattern; ``check`` fails when a kernel wrote outside the tensor it was given."""
 import torch
 
-POISON = 12345.0
+POISON = 12288.0  # exactly representable in bf16
 
 
 class Canary:
