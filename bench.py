@@ -285,6 +285,17 @@ def run_ours(args):
     sync_all()
     ms_e2e = t0.elapsed_time(t1)
 
+    # LMMS_B200_STEP_BREAKDOWN=1: exposed device time of every phase of one more step (max over ranks)
+    breakdown = None
+    if tr.runtime is not None and getattr(tr.runtime, "breakdown", False):
+        tr.training_step({k: v.to(dev) for k, v in host_batches[0].items()}, True)
+        phases = tr.runtime.phase_times()
+        names = sorted(phases)
+        pt = torch.tensor([phases[n] for n in names], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(pt, op=dist.ReduceOp.MAX)
+        breakdown = {n: round(float(v), 3) for n, v in zip(names, pt)}
+
     t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -329,6 +340,8 @@ def run_ours(args):
             "mfu_ref_formula": flops / (ms / args.steps / 1e3) / 2.25e15, "peak_mem_gb": peak_gb + symm_gb, "peak_mem_allocator_gb": peak_gb,
             "peer_mapped_mem_gb": symm_gb, "last_loss": last,
         }
+        if breakdown is not None:
+            out["step_breakdown_ms"] = breakdown
         emit_json(out)
     if dist.is_initialized():
         dist.destroy_process_group()

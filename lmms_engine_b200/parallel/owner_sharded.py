@@ -162,6 +162,8 @@ class OwnerShardedRuntime:
         self.param_dtype = param_dtype
         self.grad_dtype = grad_dtype or param_dtype
         self.step_count = 0
+        self.breakdown = os.environ.get("LMMS_B200_STEP_BREAKDOWN", "0") == "1"
+        self.phase_events: List[Tuple[str, Any]] = []
         self._ns_work: Dict[Any, torch.Tensor] = {}
         self._lanes = None
 
@@ -379,15 +381,35 @@ class OwnerShardedRuntime:
             self.params[s.name].grad = self.G[s.offset : s.offset + s.numel].view(s.shape)
 
     @torch.no_grad()
+    def _mark(self, name: str) -> None:
+        """Phase marker on the current stream (``LMMS_B200_STEP_BREAKDOWN=1``): the device time between two markers is the
+        phase's exposed time.  Collected per step in ``phase_events``; ``phase_times()`` turns them into milliseconds."""
+        if self.breakdown and self.P.is_cuda:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.phase_events.append((name, ev))
+
+    def phase_times(self) -> Dict[str, float]:
+        """Milliseconds of every phase of the last step (synchronises)."""
+        if not self.phase_events:
+            return {}
+        torch.cuda.synchronize()
+        out: Dict[str, float] = {}
+        for (_, a), (name, b) in zip(self.phase_events[:-1], self.phase_events[1:]):
+            out[name] = out.get(name, 0.0) + a.elapsed_time(b)
+        return out
+
     def step(self, lr_factor: float = 1.0) -> torch.Tensor:
         """Reduce, clip, update and publish.  Returns the global gradient norm (device scalar)."""
         comm = self.comm
+        self._mark("backward")  # everything since the step's first marker (set by the trainer) up to here
         if self.overlap:
             self._finish_reduce()  # buckets were (mostly) reduced during the backward pass
             self.step_count += 1
         else:
             self.step_count += 1
             comm.reduce_to_owner(self.G, self.all_ranges)
+        self._mark("reduce_exposed")
         # gradient of the MEAN loss over ranks; folded into the clip coefficient below
         inv_n = 1.0 / self.n
         first = True
@@ -401,15 +423,20 @@ class OwnerShardedRuntime:
         if inv_n != 1.0:
             self._sumsq.mul_(inv_n * inv_n)
         optim_ops.clip_coef(self._sumsq, self._norm, self._coef, self._skip, float(self.max_grad_norm or 0.0))
+        self._mark("grad_norm")
         gscale = self._coef * inv_n if inv_n != 1.0 else self._coef
         lr = self.lr * lr_factor
         self._adam_update(lr, gscale)
+        self._mark("adamw_publish" if self.overlap else "adamw")
         self._muon_update(lr, gscale)
+        self._mark("muon_publish" if self.overlap else "muon")
         if self.overlap:
             comm.barrier()  # every replica is complete, and every peer has finished reading my gradients
         else:
             comm.publish(self.P, self.all_ranges)
+        self._mark("final_barrier" if self.overlap else "publish")
         self.G.zero_()
+        self._mark("zero_grads")
         return self._norm
 
     def _adam_update(self, lr: float, gscale: torch.Tensor) -> None:

@@ -303,7 +303,13 @@ class FSDP2SFTTrainer:
         Returns device scalars ``(loss, grad_norm or None)``."""
         args = self.args
         self.model.train()
+        rt = self.runtime
+        if rt is not None and getattr(rt, "breakdown", False):
+            rt.phase_events = []
+            rt._mark("start")
         loss = self.compute_loss(batch)
+        if rt is not None and getattr(rt, "breakdown", False):
+            rt._mark("forward")
         if do_step and self.runtime is not None:
             self.runtime.arm()  # this backward finishes the step's gradients: reduce them bucket by bucket as they complete
         (loss / args.gradient_accumulation_steps).backward()
