@@ -11,11 +11,6 @@
   supervised), every image is ``<|vision_start|> latent tokens <|vision_end|>`` sharing one rotary position;
   assistant images are generation targets (random noise level), user images are clean conditions
   (reference: src/lmms_engine/datasets/processor/bagel_processor.py:91-365, collator/bagel_collator.py:11-80).
-* ``aero_realtime_iterable`` + processor ``aero_realtime``: an audio timeline of ``<|audio_pad|>`` slots (one per
-  ``downsample_factor`` encoder frames) with a parallel text stream: silence slots hold ``<|rt_pad|>``, assistant
-  speech segments are written into the slots that follow their start time (reference:
-  src/lmms_engine/datasets/processor/aero_realtime_processor.py:540-650; the video-chunk interleaving of the reference
-  is not built: clips are audio).
 * processors ``sit``, ``rae_siglip``, ``wanvideo`` (tensor normalisation only) and ``nanovlm`` (ChatML text
   plus NaFlex patches: an image is resized so that it has at most ``max_num_patches`` patches of
   ``patch_size`` pixels and is flattened to ``[rows*cols, C*p*p]`` with its ``spatial_shapes`` row).
@@ -544,130 +539,3 @@ class BagelIterableDataset(MultiModalIterableDataset):
 
     def get_collator(self):
         return BagelCollator()
-
-
-# ------------------------------------------------------------------------------- realtime audio stream
-@register_processor("aero_realtime")
-class AeroRealtimeProcessor(ChatProcessor):
-    """``input_ids`` / ``text_stream_ids`` / ``labels`` of the realtime design.
-
-    The user turn holds ``<|audio_start|> <|audio_pad|> x N <|audio_end|>`` per clip, ``N = (mel frames // 2) //
-    downsample_factor`` (the encoder halves the mel rate; the projector groups ``downsample_factor`` frames), i.e. one
-    slot per ``2 * downsample_factor`` mel hops of 10 ms.  ``text_stream_ids`` mirrors ``input_ids`` except on the
-    audio slots: ``<|rt_pad|>`` by default (supervised as silence unless masked by ``rt_pad_label_mask_ratio``); every
-    assistant segment ``{"role": "assistant", "time": seconds, "text": ...}`` of ``realtime_segments`` takes the free
-    slots from its start time on: the first keeps ``<|rt_pad|>`` unsupervised, the following carry the speech tokens in
-    both the stream and the labels.  Ordinary assistant turns after the clip are supervised as usual."""
-
-    def build(self):
-        super().build()
-        t, kw = self.tokenizer, self.kwargs
-        ids = {name: t.convert_tokens_to_ids(name) for name in ("<|audio_pad|>", "<|audio_start|>", "<|audio_end|>", "<|rt_pad|>")}
-        missing = [k for k, v in ids.items() if v is None]
-        if missing:
-            raise ValueError(f"tokenizer lacks the realtime tokens {missing} (use a realtime checkpoint's tokenizer or 'byte_realtime')")
-        self.audio_token_id, self.audio_start, self.audio_end, self.rt_pad = (ids[k] for k in ("<|audio_pad|>", "<|audio_start|>", "<|audio_end|>", "<|rt_pad|>"))
-        self.n_mels = int(kw.get("num_mel_bins", 128))
-        self.max_frames = int(kw.get("max_frames", 3000))
-        self.df = int(kw.get("downsample_factor", 4))
-        self.pad_mask_ratio = float(kw.get("rt_pad_label_mask_ratio", 0.0))
-        self.rng = np.random.default_rng(int(kw.get("seed", 0)))
-        return self
-
-    @property
-    def seconds_per_slot(self) -> float:
-        return 2 * self.df * 160 / 16000.0
-
-    def process(self, hf_messages=None, images=None, videos=None, audios=None, add_system_prompt: bool = True,
-                realtime_segments=None, **kw):
-        from .processor.audio_process import log_mel_spectrogram
-
-        out: Dict[str, torch.Tensor] = {}
-        mm = {"image": [], "video": [], "audio": []}
-        if audios:
-            feats, masks = [], []
-            for wav in audios:
-                f, m, valid = log_mel_spectrogram(wav, self.n_mels, self.max_frames)
-                feats.append(f), masks.append(m)
-                mm["audio"].append(max((valid // 2) // self.df, 1))
-            longest = max(int(m.sum()) for m in masks)
-            longest += longest % 2
-            out["input_features"] = torch.stack(feats)[..., :longest]
-            out["feature_attention_mask"] = torch.stack(masks)[..., :longest]
-        built = self.build_ids_and_labels(hf_messages, mm, add_system_prompt)
-        ids, labels = built["input_ids"], built["labels"]
-        stream = ids.clone()
-        slots = torch.nonzero(ids == self.audio_token_id, as_tuple=False).flatten().tolist()
-        for pos in slots:
-            stream[pos] = self.rt_pad
-            labels[pos] = -100 if (self.pad_mask_ratio > 0 and self.rng.random() < self.pad_mask_ratio) else self.rt_pad
-        times = [k * self.seconds_per_slot for k in range(len(slots))]
-        taken = set()
-        for seg in sorted((s for s in (realtime_segments or []) if s.get("role") == "assistant" and s.get("text")),
-                          key=lambda s: float(s["time"])):
-            first = next((k for k, t in enumerate(times) if t >= float(seg["time"])), len(slots))
-            free = [k for k in range(first, len(slots)) if k not in taken]
-            if len(free) < 2:
-                continue
-            head = slots[free[0]]
-            stream[head], labels[head] = self.rt_pad, -100  # context slot: the model is not asked to decide to start here
-            taken.add(free[0])
-            for k, tok in zip(free[1:], self._enc(seg["text"])):
-                stream[slots[k]] = labels[slots[k]] = tok
-                taken.add(k)
-        out.update(input_ids=ids, labels=labels, text_stream_ids=stream)
-        return out
-
-    def render_message(self, msg, counters, mm):
-        """ChatML turn; audio clips are wrapped in their start / end markers."""
-        ids = self._enc(f"<|im_start|>{msg['role']}\n")
-        content = msg["content"] if isinstance(msg["content"], list) else [{"type": "text", "text": msg["content"]}]
-        for c in content:
-            kind = c.get("type")
-            if kind == "text":
-                ids += self._enc(c["text"])
-            elif kind in ("audio", "audio_url"):
-                n = mm["audio"][counters["audio"]]
-                counters["audio"] += 1
-                ids += [self.audio_start] + [self.audio_token_id] * n + [self.audio_end]
-            else:
-                raise ValueError(f"the realtime processor takes text and audio content, got {kind}")
-        return ids + [self.im_end] + self._enc("\n")
-
-
-class _RealtimeCollator:
-    """Packed collator that also concatenates the text stream along the token axis and pads the clips of all
-    samples to one mel length."""
-
-    def __call__(self, batch):
-        from .collator.packed_collator import PackedCollator, _flatten
-
-        samples = _flatten(batch)
-        clips = [s for s in samples if "input_features" in s]
-        width = max((s["input_features"].shape[-1] for s in clips), default=0)
-        padded = []
-        for s in samples:
-            s = dict(s)
-            if "input_features" in s:
-                extra = width - s["input_features"].shape[-1]
-                s["input_features"] = torch.nn.functional.pad(s["input_features"], (0, extra))
-                s["feature_attention_mask"] = torch.nn.functional.pad(s["feature_attention_mask"], (0, extra))
-            padded.append(s)
-        return PackedCollator()(padded)
-
-
-@register_dataset("aero_realtime_iterable")
-class AeroRealtimeIterableDataset(MultiModalIterableDataset):
-    """``dataset_type: aero_realtime_iterable``: records may carry ``realtime_segments`` next to ``messages``."""
-
-    def process_record(self, record: dict, data_folder=""):
-        from ..utils.train_utils import TrainUtilities
-
-        messages = self.messages_of(record)
-        images, videos, audios, fps = self.load_media(messages, data_folder)
-        hf_messages = TrainUtilities.convert_open_to_hf(messages)
-        return self.processor.process(hf_messages, images=images or None, audios=audios or None,
-                                      realtime_segments=record.get("realtime_segments"))
-
-    def get_collator(self):
-        return _RealtimeCollator()

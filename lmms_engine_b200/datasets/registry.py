@@ -6,3 +6,4 @@ from . import iterable, naive, processor  # noqa: F401
 from . import extra  # noqa: F401
 from . import families  # noqa: F401
 from . import codec_video  # noqa: F401
+from . import realtime  # noqa: F401

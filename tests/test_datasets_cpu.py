@@ -397,6 +397,144 @@ def test_aero_realtime_processor_places_speech_on_the_audio_timeline(tmp_path):
     assert torch.isfinite(loss) and model.multi_modal_projector.linear_1.weight.grad.abs().sum() > 0
 
 
+def _realtime_processor(**extra):
+    from lmms_engine_b200.datasets import registry  # noqa: F401
+    from lmms_engine_b200.datasets.config import ProcessorConfig
+    from lmms_engine_b200.mapping_func import DATAPROCESSOR_MAPPING
+
+    kw = {"num_mel_bins": 16, "downsample_factor": 4, "patch_size": 4, "min_pixels": 64, "max_pixels": 256}
+    kw.update(extra)
+    return DATAPROCESSOR_MAPPING["aero_realtime"](ProcessorConfig(processor_name="byte_realtime", processor_type="aero_realtime",
+                                                                   extra_kwargs=kw)).build()
+
+
+def test_aero_realtime_interleaves_video_chunks_with_their_audio_slots():
+    """A 2 s video of 8 frames at 4 fps with its 2 s track: 4 temporal patches stamped 0.1 / 0.6 / 1.1 / 1.6 s; the 25
+    slots of 80 ms are split at those stamps; typed text goes in front of the first patch at or after its time; speech
+    goes into the slots from its start time on, across envelope boundaries."""
+    from lmms_engine_b200.datasets.realtime import split_slots_over_chunks
+
+    assert split_slots_over_chunks(25, [0.125, 0.625, 1.125, 1.625], 12.5) == [8, 7, 6, 4]
+    assert split_slots_over_chunks(3, [], 12.5) == [] and split_slots_over_chunks(0, [0.0, 1.0], 12.5) == [0, 0]
+    proc = _realtime_processor()
+    frames = np.random.default_rng(0).integers(0, 255, (8, 16, 16, 3)).astype(np.uint8)
+    wave = np.random.default_rng(1).standard_normal(32000).astype(np.float32)
+    meta = [{"fps": 4.0, "frames_indices": list(range(8))}]
+    msgs = [{"role": "user", "content": [{"type": "video", "video": "clip.mp4"}]}]
+    segs = [{"role": "assistant", "time": 0.5, "text": "a cat walks by"}, {"role": "user", "time": 1.0, "text": "what now?"}]
+    out = proc.process(msgs, videos=[frames], audios=[wave], realtime_segments=segs, video_metadata=meta)
+    ids, stream, labels = out["input_ids"].tolist(), out["text_stream_ids"].tolist(), out["labels"].tolist()
+    t, h, w = out["video_grid_thw"][0].tolist()
+    assert t == 4 and out["pixel_values_videos"].shape[0] == t * h * w
+    per_patch = h * w // 4
+    starts = [i for i, x in enumerate(ids) if x == proc.audio_start]
+    ends = [i for i, x in enumerate(ids) if x == proc.audio_end]
+    assert [e - s - 1 for s, e in zip(starts, ends)] == [8, 7, 6, 4]
+    text = proc.tokenizer.decode(ids)
+    for stamp in ("<0.1 seconds>", "<0.6 seconds>", "<1.1 seconds>", "<1.6 seconds>"):
+        assert stamp in text
+    assert text.index("what now?") < text.index("<1.1 seconds>") and text.index("what now?") > text.index("<0.6 seconds>")
+    for s in starts:  # every audio envelope directly follows its video envelope
+        assert ids[s - 1] == proc.vision_end and ids[s - 1 - per_patch:s - 1] == [proc.video_token_id] * per_patch
+    slots = [i for i, x in enumerate(ids) if x == proc.audio_token_id]
+    assert len(slots) == 25 and out["input_features"].shape == (1, 16, 200)
+    # slots carry their patch's stamp: the first slot at or after 0.5 s is the first of the second envelope (index 8)
+    said = list(b"a cat walks by")
+    assert stream[slots[8]] == proc.rt_pad and labels[slots[8]] == -100
+    assert [stream[slots[k]] for k in range(9, 9 + len(said))] == said == [labels[slots[k]] for k in range(9, 9 + len(said))]
+    quiet = [k for k in range(25) if not 8 <= k < 9 + len(said)]
+    assert all(stream[slots[k]] == proc.rt_pad == labels[slots[k]] for k in quiet)
+    off = [i for i in range(len(ids)) if i not in slots]
+    assert all(labels[i] == -100 and stream[i] == ids[i] for i in off)
+    assert out["position_ids"].shape == (3, len(ids))
+
+
+def test_aero_realtime_answers_questions_in_silent_slots_after_the_video():
+    """Without timed segments a (question, answer) pair becomes ``question <audio_start> pad x n <audio_end>`` inside
+    the user turn: the stream carries the answer, the labels supervise it, and n slots of silence join the features;
+    the sample runs through the model in both audio layouts."""
+    from lmms_engine_b200.datasets.realtime import RealtimeCollator
+    from lmms_engine_b200.mapping_func import create_model_from_config
+
+    frames = np.random.default_rng(0).integers(0, 255, (4, 16, 16, 3)).astype(np.uint8)
+    wave = np.random.default_rng(1).standard_normal(16000).astype(np.float32)
+    msgs = [{"role": "user", "content": [{"type": "video", "video": "clip.mp4"}, {"type": "text", "text": "what is it?"}]},
+            {"role": "assistant", "content": [{"type": "text", "text": "a cat"}]}]
+    for chunked in (False, True):
+        proc = _realtime_processor(chunk_audio=chunked)
+        out = proc.process(msgs, videos=[frames], audios=[wave], video_fps=[4.0])
+        ids, stream, labels = out["input_ids"].tolist(), out["text_stream_ids"].tolist(), out["labels"].tolist()
+        answer, n_track = list(b"a cat"), 12  # 1 s -> 100 mel frames -> 12 slots
+        slots = [i for i, x in enumerate(ids) if x == proc.audio_token_id]
+        assert len(slots) == n_track + len(answer)
+        tail = slots[n_track:]
+        assert [stream[i] for i in tail] == answer == [labels[i] for i in tail]
+        assert ids[tail[0] - 1] == proc.audio_start and ids[tail[-1] + 1] == proc.audio_end
+        question = list(b"what is it?")
+        assert ids[tail[0] - 1 - len(question):tail[0] - 1] == question
+        assert ids[-2] == proc.im_end and sum(1 for x in ids if x == proc.im_end) == 2  # system + the one user turn
+        assert all(labels[i] == proc.rt_pad for i in slots[:n_track])
+        if chunked:
+            assert out["input_features"].shape == (n_track + len(answer), 16, 8)
+            assert out["feature_attention_mask"].shape == (n_track + len(answer), 4)
+            assert float(out["input_features"][n_track:].abs().sum()) == 0.0
+        else:
+            assert out["input_features"].shape == (2, 16, 100) and out["feature_attention_mask"].sum(-1).tolist() == [100, 40]
+        batch = RealtimeCollator()([[out]])
+        text = dict(vocab_size=len(proc.tokenizer) + 6, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                    num_key_value_heads=2, head_dim=8, rope_scaling={"mrope_section": [2, 1, 1], "mrope_interleaved": True})
+        vis = dict(depth=1, hidden_size=16, intermediate_size=32, num_heads=2, patch_size=4, out_hidden_size=32,
+                   num_position_embeddings=16, deepstack_visual_indexes=[])
+        audio = dict(hidden_size=16, intermediate_size=32, num_hidden_layers=1, num_attention_heads=2, head_dim=8, num_mel_bins=16,
+                     sliding_window=8)
+        model = create_model_from_config("aero_realtime", dict(
+            model_type="aero_realtime", backbone_family="qwen3_vl", text_config=text, vision_config=vis, audio_config=audio,
+            downsample_factor=4, audio_token_index=proc.audio_token_id, video_token_id=proc.video_token_id,
+            image_token_id=proc.image_token_id, vision_start_token_id=proc.vision_start))
+        rows = model.audio_rows(batch["input_features"].float(), batch["feature_attention_mask"])
+        assert rows.shape[0] == len(slots)
+        loss = model(**batch)["loss"]
+        loss.backward()
+        assert torch.isfinite(loss) and model.visual.patch_embed.proj.weight.grad is not None
+
+
+def test_aero_realtime_dataset_reads_timed_messages_and_the_sound_track(tmp_path):
+    """``"realtime": true`` records: messages with a ``time`` become segments, the video brings the ``.wav`` next to it,
+    ``user_audio`` is mixed onto it."""
+    from lmms_engine_b200.datasets import registry  # noqa: F401
+    from lmms_engine_b200.datasets.config import DatasetConfig
+    from lmms_engine_b200.datasets.realtime import mix_onto_track
+    from lmms_engine_b200.mapping_func import DATASET_MAPPING
+
+    mixed = mix_onto_track(np.zeros(10, np.float32), np.ones(4, np.float32) * 0.5, 0.5, 16)
+    assert mixed.shape == (12,) and mixed[8:].tolist() == [0.5] * 4 and float(mixed[:8].sum()) == 0.0
+    _write_video(tmp_path / "v.mp4", n_frames=16, fps=8.0)
+    _write_wav(tmp_path / "v.wav", 2.0)
+    _write_wav(tmp_path / "q.wav", 0.25)
+    record = {"realtime": True, "user_audio": [{"path": "q.wav", "start_time": 0.5}],
+              "messages": [{"role": "user", "content": [{"type": "video_url", "video_url": {"url": "v.mp4"}}]},
+                           {"role": "user", "time": 0.4, "content": [{"type": "text", "text": "tell me"}]},
+                           {"role": "assistant", "time": 1.0, "content": [{"type": "text", "text": "ok"}]}]}
+    path = tmp_path / "rt.jsonl"
+    path.write_text(json.dumps(record) + "\n")
+    cfg = DatasetConfig(dataset_type="aero_realtime_iterable", dataset_format="jsonl", dataset_path=str(path), shuffle=False,
+                        packing=False, fps=4, processor_config={"processor_name": "byte_realtime", "processor_type": "aero_realtime",
+                                                                 "extra_kwargs": {"num_mel_bins": 16, "patch_size": 4, "min_pixels": 64,
+                                                                                  "max_pixels": 256}})
+    ds = DATASET_MAPPING["aero_realtime_iterable"](cfg).build()
+    ds.data_folder = [str(tmp_path)] * len(ds.data_list)
+    (sample,) = [s for pack in ds for s in pack]
+    proc = ds.processor
+    ids, stream, labels = sample["input_ids"], sample["text_stream_ids"], sample["labels"]
+    text = proc.tokenizer.decode(ids.tolist())
+    assert "tell me" in text and "ok" not in text.replace("tokens", "")
+    slots = torch.nonzero(ids == proc.audio_token_id).flatten()
+    assert slots.numel() == 25
+    spoken = [i for i in slots.tolist() if labels[i] not in (-100, proc.rt_pad)]
+    assert bytes(stream[spoken].tolist()) == b"ok" and labels[spoken].tolist() == stream[spoken].tolist()
+    assert int((ids == proc.audio_start).sum()) == int(sample["video_grid_thw"][0, 0])
+
+
 # ------------------------------------------------------------------------------------------------
 # datasets with record handling of their own (datasets/families.py)
 def _write_video(path, n_frames=24, fps=8.0, size=(64, 64)):
