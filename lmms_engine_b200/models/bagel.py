@@ -110,12 +110,32 @@ class MoTAttention(Attention):
             q = _by_type(q, und, gen, lambda t: self.q_norm(t.reshape(-1, D)).view(t.shape), lambda t: self.q_norm_moe_gen(t.reshape(-1, D)).view(t.shape))
             k = _by_type(k, und, gen, lambda t: self.k_norm(t.reshape(-1, D)).view(t.shape), lambda t: self.k_norm_moe_gen(t.reshape(-1, D)).view(t.shape))
         q, k = rope_ops.rope_apply(q.contiguous(), ctx.cos, ctx.sin), rope_ops.rope_apply(k.contiguous(), ctx.cos, ctx.sin)
-        o = split_attention(q, k, v.contiguous(), ctx, 1.0 / math.sqrt(D)).reshape(T, nq)
+        o = split_attention(q, k, v.contiguous(), ctx, 1.0 / math.sqrt(D), self.layer_idx).reshape(T, nq)
         return _by_type(o, und, gen, lambda t: gemm_ops.linear(t, self.o_proj.weight, None), lambda t: gemm_ops.linear(t, self.o_proj_moe_gen.weight, None))
 
 
-def split_attention(q, k, v, ctx: PackedContext, scale: float):
-    """Attention under the per-split rules when the context carries them, plain packed causal attention otherwise."""
+def _own_attention_path(ctx) -> bool:
+    """Per-split rules, a recorded prefix or a recording pass: all are served by ``split_attention``."""
+    return any(getattr(ctx, name, None) is not None for name in ("split_plan", "kv_prefix", "kv_capture"))
+
+
+def split_attention(q, k, v, ctx: PackedContext, scale: float, layer_idx: int = 0):
+    """Attention under the per-split rules when the context carries them, plain packed causal attention otherwise.
+
+    Two hooks serve sampling (the roles of ``NaiveCache`` in src/lmms_engine/models/bagel/modeling_utils.py and of the
+    ``forward_cache_update_*`` passes of bagel.py): with ``ctx.kv_capture`` (a list) the rotated keys and the values of
+    this layer are recorded; with ``ctx.kv_prefix`` (one ``(k, v)`` per layer) the stream is ONE block that attends
+    fully to itself and to that recorded prefix."""
+    capture = getattr(ctx, "kv_capture", None)
+    if capture is not None:
+        capture.append((k.detach(), v.detach()))
+    prefix = getattr(ctx, "kv_prefix", None)
+    if prefix is not None:
+        pk, pv = prefix[layer_idx]
+        kk, vv = torch.cat([pk.to(k.dtype), k], 0), torch.cat([pv.to(v.dtype), v], 0)
+        cu_q = torch.tensor([0, q.shape[0]], dtype=torch.int32, device=q.device)
+        cu_k = torch.tensor([0, kk.shape[0]], dtype=torch.int32, device=q.device)
+        return attn_ops.varlen_attn(q, kk, vv, cu_q, cu_k, causal=False, softmax_scale=scale)
     plan = getattr(ctx, "split_plan", None)
     if plan is None:
         return attn_ops.varlen_attn(q, k, v, ctx.cu_seqlens, ctx.cu_seqlens, ctx.max_seqlen, ctx.max_seqlen, causal=True, softmax_scale=scale)
@@ -185,7 +205,7 @@ class MoTLayer(DecoderLayer):
     def forward(self, h, residual, ctx: PackedContext):
         gen = getattr(ctx, "gen_index", None)
         if gen is None or not self.parts:
-            if getattr(ctx, "split_plan", None) is None:
+            if not _own_attention_path(ctx):
                 return super().forward(h, residual, ctx)
         stream = h if residual is None else h + residual
         und = ctx.und_index if gen is not None else None
@@ -207,7 +227,7 @@ class MoTLayer(DecoderLayer):
 
     def _shared_attention(self, x, ctx):
         at, D = self.self_attn, self.self_attn.head_dim
-        if getattr(ctx, "split_plan", None) is None:
+        if not _own_attention_path(ctx):
             return at(x, ctx)
         w = torch.cat([_w(at.q_proj.weight), _w(at.k_proj.weight), _w(at.v_proj.weight)], 0)
         b = torch.cat([_w(at.q_proj.bias), _w(at.k_proj.bias), _w(at.v_proj.bias)], 0) if at.q_proj.bias is not None else None
@@ -217,7 +237,7 @@ class MoTLayer(DecoderLayer):
         if at.cfg.qk_norm:
             q, k = at.q_norm(q.reshape(-1, D)).view(q.shape), at.k_norm(k.reshape(-1, D)).view(k.shape)
         q, k = rope_ops.rope_apply(q.contiguous(), ctx.cos, ctx.sin), rope_ops.rope_apply(k.contiguous(), ctx.cos, ctx.sin)
-        o = split_attention(q, k, v.contiguous(), ctx, 1.0 / math.sqrt(D))
+        o = split_attention(q, k, v.contiguous(), ctx, 1.0 / math.sqrt(D), at.layer_idx)
         return gemm_ops.linear(o.reshape(T, nq), _w(at.o_proj.weight), None)
 
 
@@ -280,6 +300,44 @@ class _Connector(nn.Module):
         h = gemm_ops.linear(x, self.fc1.weight, self.fc1.bias)
         h = F.gelu(h, approximate="tanh") if "tanh" in self.act else F.gelu(h)
         return gemm_ops.linear(h, self.fc2.weight, self.fc2.bias)
+
+
+class TaylorForecaster:
+    """Skips decoder passes during sampling by extrapolating the predicted velocity over the step index.
+
+    The first ``first_enhance`` steps are computed; afterwards every ``interval``-th step is, and the steps between are
+    forecast from a Taylor expansion whose derivatives (up to ``max_order``) are finite differences of the computed
+    steps.  This is the schedule and the expansion of the reference's TaylorSeer option
+    (src/lmms_engine/models/bagel/cache_utils.py:12-128, qwen2_navit.py:839-908), applied to the velocity of the latent
+    tokens - the quantity the sampler consumes - instead of to every layer's output, of which only the last one reaches
+    the result; one forecaster serves one guidance branch."""
+
+    def __init__(self, interval: int = 3, max_order: int = 6, first_enhance: int = 5):
+        self.interval, self.max_order, self.first_enhance = max(int(interval), 1), int(max_order), int(first_enhance)
+        self.factors: List[torch.Tensor] = []
+        self.computed: List[int] = []
+        self.counter = 0
+
+    def wants_model(self, step: int) -> bool:
+        """Whether ``step`` must run the model; otherwise ``forecast`` serves it.  Call once per step, in order."""
+        if step < self.first_enhance or self.counter == self.interval - 1 or not self.factors:
+            self.counter = 0
+            return True
+        self.counter += 1
+        return False
+
+    def update(self, step: int, value: torch.Tensor) -> None:
+        new = [value]
+        if self.computed and step > self.first_enhance - 2:
+            distance = step - self.computed[-1]
+            for i in range(min(self.max_order, len(self.factors))):
+                new.append((new[i] - self.factors[i]) / distance)
+        self.factors = new
+        self.computed.append(step)
+
+    def forecast(self, step: int) -> torch.Tensor:
+        x = step - self.computed[-1]
+        return sum(f * (x ** i / math.factorial(i)) for i, f in enumerate(self.factors))
 
 
 class Bagel(DecoderLM):
@@ -356,9 +414,13 @@ class Bagel(DecoderLM):
             emb = emb.index_copy(0, latent_index, g)
         return emb, noise, target, t
 
-    def run_decoder(self, emb, pos, cu, gen_index, split_lens=None, attn_modes=None):
+    def run_decoder(self, emb, pos, cu, gen_index, split_lens=None, attn_modes=None, kv_capture=None, kv_prefix=None):
         cos, sin = self.model.rope_tables(pos)
         ctx = PackedContext(cu, int(pos.shape[-1]), cos, sin, True)
+        if kv_capture is not None:
+            ctx.kv_capture = kv_capture
+        if kv_prefix is not None:
+            ctx.kv_prefix = kv_prefix
         T = emb.shape[0]
         if gen_index is not None and gen_index.numel() and self.config.gen_parts():
             mask = torch.zeros(T, dtype=torch.bool, device=emb.device)
@@ -438,23 +500,59 @@ class Bagel(DecoderLM):
         return dict(ids=ids, pos=pos, cu=torch.tensor([0, n + G + 2], dtype=torch.int32, device=dev), latent_index=torch.arange(n + 1, n + 1 + G, device=dev),
                     latent_pos=lat_pos, split_lens=[n, G + 2] if n else [G + 2], attn_modes=["causal", "full"] if n else ["full"])
 
-    def flow_velocity(self, stream: Dict[str, Any], x_t: torch.Tensor, t: float) -> torch.Tensor:
-        """Velocity prediction ``[G, C*p*p]`` for the noised latent patches ``x_t`` of ``stream`` at time ``t`` in (0, 1]."""
-        emb = self.model.embed_tokens(stream["ids"])
+    @torch.no_grad()
+    def cache_prompt(self, stream: Dict[str, Any]) -> Dict[str, Any]:
+        """Run the prompt of ``stream`` once and keep every layer's rotated keys and values, so that the sampling steps
+        only run the image block against them.  Exact: the prompt is causal text in front of the block, so nothing in
+        it depends on the block.  Returns ``stream`` with ``prefix`` (one ``(k, v)`` per layer) and ``block`` (the
+        stream reduced to the image block); a stream without a prompt is returned unchanged."""
+        n = int(stream["latent_index"][0]) - 1  # tokens in front of the begin-of-image marker
+        if n <= 0 or "prefix" in stream:
+            return stream
+        captured: List[Any] = []
+        emb = self.model.embed_tokens(stream["ids"][:n])
+        cu = torch.tensor([0, n], dtype=torch.int32, device=emb.device)
+        self.run_decoder(emb, stream["pos"][:n], cu, None, [n], ["causal"], kv_capture=captured)
+        if len(captured) != len(self.model.layers):
+            raise RuntimeError(f"{len(captured)} layers recorded their keys, the decoder has {len(self.model.layers)}")
+        block = dict(ids=stream["ids"][n:], pos=stream["pos"][n:], latent_index=stream["latent_index"] - n, latent_pos=stream["latent_pos"],
+                     cu=torch.tensor([0, stream["ids"].numel() - n], dtype=torch.int32, device=emb.device))
+        return dict(stream, prefix=captured, block=block)
+
+    def flow_velocity(self, stream: Dict[str, Any], x_t: torch.Tensor, t: float, cached: bool = False) -> torch.Tensor:
+        """Velocity prediction ``[G, C*p*p]`` for the noised latent patches ``x_t`` of ``stream`` at time ``t`` in (0, 1].
+        ``cached``: use the prompt keys / values recorded by ``cache_prompt`` (sampling only: they carry no gradient)."""
+        prefix = stream.get("prefix") if cached else None
+        part = stream["block"] if prefix is not None else stream
+        emb = self.model.embed_tokens(part["ids"])
         tt = torch.full((x_t.shape[0],), float(t), device=x_t.device)
-        g = self.vae2llm(x_t.to(emb.dtype)) + self.time_embedder(tt).to(emb.dtype) + self.latent_pos_embed(stream["latent_pos"]).to(emb.dtype)
-        emb = emb.index_copy(0, stream["latent_index"], g)
-        hidden = self.run_decoder(emb, stream["pos"], stream["cu"], stream["latent_index"], stream["split_lens"], stream["attn_modes"])
-        return self.llm2vae(hidden.index_select(0, stream["latent_index"])).float()
+        g = self.vae2llm(x_t.to(emb.dtype)) + self.time_embedder(tt).to(emb.dtype) + self.latent_pos_embed(part["latent_pos"]).to(emb.dtype)
+        emb = emb.index_copy(0, part["latent_index"], g)
+        if prefix is not None:
+            hidden = self.run_decoder(emb, part["pos"], part["cu"], part["latent_index"], kv_prefix=prefix)
+        else:
+            hidden = self.run_decoder(emb, part["pos"], part["cu"], part["latent_index"], part["split_lens"], part["attn_modes"])
+        return self.llm2vae(hidden.index_select(0, part["latent_index"])).float()
 
     def guided_velocity(self, stream, x_t, t, uncond_stream=None, cfg_text_scale: float = 1.0, cfg_renorm_min: float = 0.0,
-                        cfg_renorm_type: str = "global"):
+                        cfg_renorm_type: str = "global", cached: bool = False, forecast=None):
         """Classifier-free guidance on the text condition with the guided field rescaled down to the conditional one's
-        norm (over everything: "global"; per token: "channel")."""
-        v = self.flow_velocity(stream, x_t, t)
+        norm (over everything: "global"; per token: "channel").  ``forecast = (step, forecaster of the conditional
+        branch, forecaster of the unconditional branch)`` lets the forecasters serve the steps they can."""
+
+        def branch(st, fc):
+            if fc is None:
+                return self.flow_velocity(st, x_t, t, cached)
+            if fc.wants_model(forecast[0]):
+                v = self.flow_velocity(st, x_t, t, cached)
+                fc.update(forecast[0], v)
+                return v
+            return fc.forecast(forecast[0])
+
+        v = branch(stream, forecast[1] if forecast else None)
         if uncond_stream is None or cfg_text_scale <= 1.0:
             return v
-        v_un = self.flow_velocity(uncond_stream, x_t, t)
+        v_un = branch(uncond_stream, forecast[2] if forecast else None)
         v_g = v_un + cfg_text_scale * (v - v_un)
         if cfg_renorm_type == "global":
             scale = (v.norm() / (v_g.norm() + 1e-8)).clamp(min=cfg_renorm_min, max=1.0)
@@ -472,22 +570,31 @@ class Bagel(DecoderLM):
     @torch.no_grad()
     def generate_image(self, prompt_ids, hw, boi_id: int, eoi_id: int, num_timesteps: int = 24, timestep_shift: Optional[float] = None,
                        noise_level: float = 0.7, sde_window=None, uncond_ids=None, cfg_text_scale: float = 1.0, cfg_interval=(0.0, 1.0),
-                       cfg_renorm_min: float = 0.0, cfg_renorm_type: str = "global", generator=None) -> Dict[str, Any]:
+                       cfg_renorm_min: float = 0.0, cfg_renorm_type: str = "global", generator=None, use_cache: bool = True,
+                       taylor: Optional[Dict[str, int]] = None) -> Dict[str, Any]:
         """Sample one image's latent patches from noise.  Steps inside ``sde_window = (first, count)`` (default: all) are
         stochastic and recorded - the state before the step, the state after it, its time and its log-probability - for
-        the policy-gradient pass; the other steps are plain Euler steps of the flow."""
+        the policy-gradient pass; the other steps are plain Euler steps of the flow.  ``use_cache``: run the prompt once
+        and every step on the image block only (same result; the recorded streams stay complete for the learning pass).
+        ``taylor`` (``{"interval", "max_order", "first_enhance"}``, any subset): forecast the velocity of the steps between
+        computed ones (``TaylorForecaster``; approximate, meant for previews and evaluation, not for recorded rollouts)."""
         dev = prompt_ids.device
         stream = self.image_stream(prompt_ids, hw, boi_id, eoi_id)
         un = self.image_stream(uncond_ids, hw, boi_id, eoi_id) if uncond_ids is not None else None
+        if use_cache:
+            stream = self.cache_prompt(stream)
+            un = self.cache_prompt(un) if un is not None else None
         ts = self.flow_schedule(num_timesteps, dev, timestep_shift)
         pd = self.config.latent_channels * self.config.latent_patch_size ** 2
         x = torch.randn((int(hw[0]) * int(hw[1]), pd), device=dev, generator=generator)
         first, count = sde_window if sde_window is not None else (0, num_timesteps - 1)
         rec: Dict[str, List] = {"latents": [], "prev_latents": [], "timesteps": [], "next_timesteps": [], "log_probs": []}
+        seers = (TaylorForecaster(**taylor), TaylorForecaster(**taylor)) if taylor is not None else None
         for i in range(num_timesteps - 1):
             t, t_next = float(ts[i]), float(ts[i + 1])
             scale = cfg_text_scale if cfg_interval[0] < t <= cfg_interval[1] else 1.0
-            v = self.guided_velocity(stream, x, t, un, scale, cfg_renorm_min, cfg_renorm_type)
+            v = self.guided_velocity(stream, x, t, un, scale, cfg_renorm_min, cfg_renorm_type, cached=use_cache,
+                                     forecast=(i,) + seers if seers else None)
             if first <= i < first + count and noise_level > 0:
                 nxt, logp, _, _ = self.sde_step_with_logprob(v[None], x[None], torch.tensor([t], device=dev), t_next - t, noise_level,
                                                              generator=generator, sigma_max=float(ts[1]))
@@ -500,7 +607,8 @@ class Bagel(DecoderLM):
             else:
                 x = x + v * (t_next - t)
         rec["image_latent"] = x
-        rec["stream"], rec["uncond_stream"] = stream, un
+        plain = lambda st: None if st is None else {k: v for k, v in st.items() if k not in ("prefix", "block")}  # noqa: E731
+        rec["stream"], rec["uncond_stream"] = plain(stream), plain(un)
         return rec
 
     def unpatchify_latent(self, tokens: torch.Tensor, hw) -> torch.Tensor:

@@ -178,3 +178,69 @@ def test_rollout_records_steps_and_the_policy_pass_reproduces_their_log_probabil
     # without noise the sampler is the deterministic Euler solver and records nothing
     det = model.generate_image(prompt, (2, 3), boi_id=101, eoi_id=102, num_timesteps=4, noise_level=0.0)
     assert det["latents"] == [] and torch.isfinite(det["image_latent"]).all()
+
+
+@pytest.mark.parametrize("layer_module", ["Qwen2DecoderLayer", "Qwen2MoEDecoderLayer", "Qwen2MoTDecoderLayer"])
+def test_sampling_on_recorded_prompt_keys_equals_the_full_stream(layer_module):
+    """Running the prompt once and every step on the image block against its keys / values gives the image of the
+    full-stream sampler, with and without guidance; the record handed to the learning pass stays complete."""
+    from lmms_engine_b200.mapping_func import create_model_from_config
+
+    torch.manual_seed(1)
+    model = create_model_from_config("bagel", dict(BASE, layer_module=layer_module)).eval()
+    with torch.no_grad():
+        model.llm2vae.weight.normal_(0, 0.05)
+    prompt, uncond = torch.randint(0, 100, (9,)), torch.randint(0, 100, (3,))
+    for kw in (dict(), dict(uncond_ids=uncond, cfg_text_scale=3.0)):
+        runs = [model.generate_image(prompt, (3, 2), boi_id=101, eoi_id=102, num_timesteps=5, noise_level=0.5, use_cache=flag,
+                                     generator=torch.Generator().manual_seed(7), **kw) for flag in (True, False)]
+        assert torch.allclose(runs[0]["image_latent"], runs[1]["image_latent"], atol=2e-5)
+        assert torch.allclose(torch.stack(runs[0]["log_probs"]), torch.stack(runs[1]["log_probs"]), atol=1e-3)
+        assert set(runs[0]["stream"]) == set(runs[1]["stream"]) and "prefix" not in runs[0]["stream"]
+    cached = model.cache_prompt(model.image_stream(prompt, (3, 2), 101, 102))
+    assert len(cached["prefix"]) == 2 and cached["prefix"][0][0].shape == (9, 2, 8) and cached["block"]["ids"].numel() == 8
+    bare = model.image_stream(prompt[:0], (3, 2), 101, 102)
+    assert model.cache_prompt(bare) is bare  # nothing in front of the image: nothing to record
+
+
+def test_taylor_forecaster_schedule_and_expansion():
+    """Computed steps: the first ``first_enhance``, then every ``interval``-th; a quadratic in the step index is forecast
+    exactly once two derivatives exist; sampling with forecasts runs the decoder less often and stays close."""
+    from lmms_engine_b200.mapping_func import create_model_from_config
+    from lmms_engine_b200.models.bagel import TaylorForecaster
+
+    fc = TaylorForecaster(interval=3, max_order=2, first_enhance=5)
+    f = lambda s: torch.tensor([1.0 + 0.5 * s + 0.25 * s * s, -2.0 * s])  # noqa: E731
+    ran, worst = [], 0.0
+    for step in range(14):
+        if fc.wants_model(step):
+            fc.update(step, f(step))
+            ran.append(step)
+        elif len(fc.factors) == 3 and step > 9:
+            worst = max(worst, float((fc.forecast(step) - f(step)).abs().max()))
+    assert ran == [0, 1, 2, 3, 4, 7, 10, 13]
+    # backward differences of a quadratic over uneven spacing: first derivative lags by half a spacing -> small, bounded error
+    assert worst < 3.0
+    lin = TaylorForecaster(interval=4, max_order=1, first_enhance=2)
+    for step in range(9):
+        if lin.wants_model(step):
+            lin.update(step, torch.tensor([3.0 * step]))
+        else:
+            assert abs(float(lin.forecast(step)) - 3.0 * step) < 1e-6  # a line is forecast exactly
+    torch.manual_seed(2)
+    model = create_model_from_config("bagel", dict(BASE, layer_module="Qwen2MoTDecoderLayer")).eval()
+    with torch.no_grad():
+        model.llm2vae.weight.normal_(0, 0.05)
+    calls = []
+    handle = model.llm2vae.register_forward_hook(lambda *a: calls.append(1))
+    prompt = torch.randint(0, 100, (5,))
+    kw = dict(boi_id=101, eoi_id=102, num_timesteps=16, noise_level=0.0)
+    plain = model.generate_image(prompt, (2, 2), generator=torch.Generator().manual_seed(5), **kw)
+    n_plain = len(calls)
+    fast = model.generate_image(prompt, (2, 2), generator=torch.Generator().manual_seed(5), taylor={"interval": 3, "max_order": 2}, **kw)
+    handle.remove()
+    assert n_plain == 15 and len(calls) - n_plain == 8  # steps 0-4, 7, 10 and 13 of the 15
+    scale = float(plain["image_latent"].abs().mean())
+    assert float((fast["image_latent"] - plain["image_latent"]).abs().mean()) < 0.05 * scale
+    every = model.generate_image(prompt, (2, 2), generator=torch.Generator().manual_seed(5), taylor={"interval": 1}, **kw)
+    assert torch.equal(every["image_latent"], plain["image_latent"])
