@@ -341,6 +341,7 @@ class TaylorForecaster:
 
 
 class Bagel(DecoderLM):
+    supports_kv_cache = False
     config_class = BagelConfig
     backbone_cls = BagelBackbone
     _no_split_modules = ["MoTLayer"]

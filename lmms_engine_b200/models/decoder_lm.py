@@ -184,6 +184,12 @@ class Attention(nn.Module):
                                         self.nsa.kernel_stride, None, self.nsa.compress_type)
             gates = torch.sigmoid(gemm_ops.linear(x, _w(self.g_proj.weight), None)).view(x.shape[0], self.n_q, 3)
             o = nsa_ops.nsa_attention(q, k, v, k_cmp, v_cmp, counts, gates, ctx.cu_seqlens, self.nsa, 1.0 / math.sqrt(D))
+        elif getattr(ctx, "kv_cache", None) is not None:
+            # generation: the new tokens attend to the cached rows of their sequence and to themselves
+            assert ctx.sp_size == 1 and ctx.tp_size == 1, "the key / value cache runs without sequence / tensor parallelism"
+            k_all, v_all, cu_k, max_k = ctx.kv_cache.extend(self.layer_idx, k, v)
+            o = attn_ops.varlen_attn(q, k_all, v_all, ctx.cu_seqlens, cu_k, ctx.max_seqlen, max_k, causal=ctx.causal,
+                                     softmax_scale=1.0 / math.sqrt(D), window_size=self.window)
         else:
             o = attn_ops.varlen_attn(
                 q, k, v, ctx.cu_seqlens, ctx.cu_seqlens, ctx.max_seqlen, ctx.max_seqlen, causal=ctx.causal,
@@ -355,6 +361,7 @@ class DecoderLM(nn.Module):
     config_class = DecoderConfig
     backbone_cls = DecoderBackbone
     _no_split_modules = ["DecoderLayer"]
+    supports_kv_cache = True  # generation on cached keys / values (models/kv_cache.py); families with other mixers say False
 
     def __init__(self, cfg: DecoderConfig):
         super().__init__()
@@ -423,8 +430,11 @@ class DecoderLM(nn.Module):
         return_logits: bool = False,
         deepstack: Optional[List[torch.Tensor]] = None,
         deepstack_index: Optional[torch.Tensor] = None,
+        kv_cache: Any = None,
         **unused,
     ) -> Dict[str, Any]:
+        if kv_cache is not None and not self.supports_kv_cache:
+            raise NotImplementedError(f"{type(self).__name__} has no key / value cache path")
         if inputs_embeds is None:
             ids, labels, pos, cu, _ = self.prepare_packed(input_ids, attention_mask, labels, position_ids, cu_seqlens)
         else:
@@ -448,6 +458,8 @@ class DecoderLM(nn.Module):
         sg, sg_size = (tp_group, tp_size) if tp_size > 1 else (sp_group, sp_size)
         ctx = PackedContext(cu, int(max_seqlen), cos, sin, self.causal, sp_group, sp_size, tp_group, tp_size,
                             deepstack=deepstack, deepstack_index=deepstack_index)
+        if kv_cache is not None:
+            ctx.kv_cache = kv_cache  # positions of the new tokens come from ``kv_cache.advance`` through ``position_ids``
         if inputs_embeds is None:
             if sg_size > 1:
                 ids = sp.slice_for_rank(sp.pad_to_multiple(ids, sg_size, 0), sg)

@@ -28,6 +28,7 @@ class DLLMConfig(DecoderConfig):
 
 
 class DiffusionLM(DecoderLM):
+    supports_kv_cache = False
     config_class = DLLMConfig
 
     def __init__(self, cfg: DLLMConfig):

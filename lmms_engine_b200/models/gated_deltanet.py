@@ -150,6 +150,7 @@ class GatedDeltaNetBackbone(DecoderBackbone):
 
 
 class GatedDeltaNetLM(DecoderLM):
+    supports_kv_cache = False
     config_class = GatedDeltaNetConfig
     backbone_cls = GatedDeltaNetBackbone
     _no_split_modules = ["GatedDeltaNetBlock"]

@@ -325,6 +325,7 @@ class Qwen35Backbone(DecoderBackbone):
 
 
 class Qwen35LM(DecoderLM):
+    supports_kv_cache = False
     config_class = Qwen35Config
     backbone_cls = Qwen35Backbone
     _no_split_modules = ["Qwen35Layer"]

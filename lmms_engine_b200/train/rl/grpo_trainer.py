@@ -83,19 +83,32 @@ def grpo_token_loss(logp, old_logp, ref_logp, adv_tok, mask, clip_range: float, 
 
 @torch.no_grad()
 def sample_completions(model, prompts: Sequence[torch.Tensor], max_new_tokens: int, temperature: float,
-                       eos_token_id: Optional[int], generator=None, sync_group=None, token_group=None) -> List[torch.Tensor]:
-    """Ancestral sampling for a list of prompts, all sequences advanced together as one packed
-    batch per step (no KV cache: rollouts here are short; serving-grade generation is out of scope).
+                       eos_token_id: Optional[int], generator=None, sync_group=None, token_group=None,
+                       use_cache: Optional[bool] = None) -> List[torch.Tensor]:
+    """Ancestral sampling for a list of prompts, all sequences advanced together as one packed batch per step.
 
+    ``use_cache`` (default: when the model supports it and is not sequence-parallel): the prompts are run once and
+    every later step feeds ONE token per sequence against the cached keys / values (``models/kv_cache.py``); otherwise
+    every step re-runs the whole sequences.  Both draw the same tokens from the same generator state.
     ``sync_group``: ranks whose forward passes contain collectives (sharded parameters, sequence
     parallelism).  They must run the same number of forwards, so the loop ends only when NO rank of
     the group has an unfinished sequence, and a rank that is done keeps forwarding its (finished)
     batch; tokens sampled for a finished sequence are dropped.
     ``token_group``: ranks that hold the SAME prompts (a sequence-parallel group).  The tokens drawn
     by its first rank are broadcast, so that all of them continue the same text."""
+    from ...models.kv_cache import PackedKVCache
+
     dev = prompts[0].device
     seqs = [p.clone() for p in prompts]
     done = [False] * len(seqs)
+    inner = getattr(model, "module", model)
+    if use_cache is None:
+        use_cache = bool(getattr(inner, "supports_kv_cache", False)) and token_group is None and getattr(inner, "sp_group", None) is None
+    cache = None
+    if use_cache:
+        n_layers = len(inner.model.layers)
+        cache = PackedKVCache(n_layers, [p.numel() + max_new_tokens for p in prompts], device=dev)
+    fed = [0] * len(seqs)  # tokens of every sequence that the cache holds
     for _ in range(max_new_tokens):
         live = [i for i, d in enumerate(done) if not d]
         if sync_group is not None:
@@ -106,10 +119,28 @@ def sample_completions(model, prompts: Sequence[torch.Tensor], max_new_tokens: i
             live = list(range(len(seqs)))  # same shapes of work on every rank
         elif not live:
             break
-        ids = torch.cat([seqs[i] for i in live])
-        lens = torch.tensor([seqs[i].numel() for i in live], dtype=torch.int32, device=dev)
-        cu = F.pad(torch.cumsum(lens, 0, dtype=torch.int32), (1, 0))
-        hidden = model(input_ids=ids, cu_seqlens=cu)["hidden_states"]
+        if cache is not None:
+            # a finished sequence that must keep running (sync_group) re-feeds its last token without growing
+            new = [seqs[i][fed[i]:] if seqs[i].numel() > fed[i] else seqs[i][-1:] for i in live]
+            counts = [0] * len(seqs)
+            for i, t in zip(live, new):
+                counts[i] = t.numel()
+            for i in live:
+                if seqs[i].numel() == fed[i]:  # nothing new: overwrite the last row instead of appending
+                    cache.lens[i] -= 1
+                    fed[i] -= 1
+            pos = cache.advance(counts)
+            for i in live:
+                fed[i] += counts[i]
+            ids = torch.cat(new)
+            lens = torch.tensor([t.numel() for t in new], dtype=torch.int32, device=dev)
+            cu = F.pad(torch.cumsum(lens, 0, dtype=torch.int32), (1, 0))
+            hidden = model(input_ids=ids, cu_seqlens=cu, position_ids=pos, kv_cache=cache)["hidden_states"]
+        else:
+            ids = torch.cat([seqs[i] for i in live])
+            lens = torch.tensor([seqs[i].numel() for i in live], dtype=torch.int32, device=dev)
+            cu = F.pad(torch.cumsum(lens, 0, dtype=torch.int32), (1, 0))
+            hidden = model(input_ids=ids, cu_seqlens=cu)["hidden_states"]
         last = hidden.index_select(0, (cu[1:] - 1).long())
         logits = F.linear(last, model.lm_head.weight).float() / max(temperature, 1e-5)
         nxt = torch.multinomial(torch.softmax(logits, -1), 1, generator=generator).flatten()

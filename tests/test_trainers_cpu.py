@@ -101,6 +101,46 @@ def test_grpo_math():
     assert torch.allclose(logp.grad, torch.tensor([-0.5, 0.5])) and float(kl) == 0.0
 
 
+@pytest.mark.parametrize("family", ["qwen3", "qwen3_moe"])
+def test_generation_on_cached_keys_matches_rerunning_the_sequences(family):
+    """Prefill + one token per step against the key / value cache gives the hidden states of the full pass and the
+    same sampled completions (EOS at different steps, a rank kept running by its group)."""
+    from lmms_engine_b200.mapping_func import create_model_from_config
+    from lmms_engine_b200.models.kv_cache import PackedKVCache
+    from lmms_engine_b200.train.rl.grpo_trainer import sample_completions
+
+    torch.manual_seed(0)
+    cfg = dict(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+               head_dim=8, max_position_embeddings=128)
+    if family == "qwen3_moe":
+        cfg.update(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, norm_topk_prob=True)
+    model = create_model_from_config(family, dict(cfg, model_type=family)).eval()
+    seqs = [torch.randint(0, 64, (n,)) for n in (9, 5, 12)]
+    with torch.no_grad():
+        cu = torch.tensor([0, 9, 14, 26], dtype=torch.int32)
+        full = model(input_ids=torch.cat(seqs), cu_seqlens=cu)["hidden_states"]
+        cache = PackedKVCache(2, [16, 16, 16])
+        heads = [6, 5, 7]  # prefill lengths; the rest arrives in two uneven passes, the second sequence sits one out
+        pos = cache.advance(heads)
+        ids = torch.cat([s[:h] for s, h in zip(seqs, heads)])
+        first = model(input_ids=ids, cu_seqlens=torch.tensor([0, 6, 11, 18], dtype=torch.int32), position_ids=pos, kv_cache=cache)["hidden_states"]
+        pos = cache.advance([3, 0, 2])
+        assert pos.tolist() == [6, 7, 8, 7, 8]
+        second = model(input_ids=torch.cat([seqs[0][6:9], seqs[2][7:9]]), cu_seqlens=torch.tensor([0, 3, 5], dtype=torch.int32),
+                       position_ids=pos, kv_cache=cache)["hidden_states"]
+        pos = cache.advance([0, 0, 3])
+        third = model(input_ids=seqs[2][9:], cu_seqlens=torch.tensor([0, 3], dtype=torch.int32), position_ids=pos, kv_cache=cache)["hidden_states"]
+    pieces = torch.cat([first[:6], second[:3], first[6:11], first[11:18], second[3:5], third])
+    assert torch.allclose(pieces, full, atol=2e-5), float((pieces - full).abs().max())
+    with pytest.raises(ValueError):
+        cache.advance([8, 0, 0])  # 9 held + 8 > 16
+    prompts = [torch.randint(0, 64, (n,)) for n in (4, 7, 3)]
+    runs = [sample_completions(model, prompts, 12, 1.0, eos_token_id=5, generator=torch.Generator().manual_seed(11), use_cache=flag)
+            for flag in (True, False)]
+    assert all(torch.equal(a, b) for a, b in zip(*runs)) and any(r.numel() < 12 for r in runs[0])
+    assert model.supports_kv_cache
+
+
 def test_transformers_fallback_family_trains(tmp_path):
     """A model family without a native implementation is built from the transformers library and
     trained by the same trainer on padded batches."""
