@@ -457,3 +457,36 @@ def test_check_data_subcommands_measure_media_and_write_precomputed_tokens(tmp_p
     table = pq.read_table(tmp_path / "all.parquet").to_pylist()
     assert json.loads(table[0]["messages"])[0]["content"][0]["precomputed_tokens"] == image_tokens
     assert check_data.main(["summary", "--dataset", str(spec)]) == 1
+
+
+def test_sharegpt_conversations_become_messages(tmp_path):
+    """``<image>`` in a record that carries a video becomes a video item in front of the turn's text; the parquet holds
+    the messages as a JSON string that the map-style dataset reads back."""
+    from lmms_engine_b200.tools import convert_sharegpt as cs
+
+    entries = [{"id": 7, "video": "clips/a.mp4", "conversations": [{"from": "human", "value": "<image>\nWhat happens?"},
+                                                                   {"from": "gpt", "value": "A cat jumps."},
+                                                                   {"from": "human", "value": "And then?"}, {"from": "gpt", "value": "It lands."}]},
+               {"id": "b", "image": ["x.png", "y.png"], "conversations": [{"from": "human", "value": "Compare <image> and <image> <image>"},
+                                                                          {"from": "gpt", "value": "Same."}]},
+               {"id": "bad", "conversations": [{"from": "alien", "value": "?"}]}]
+    src = tmp_path / "0_30_s_academic" / "x_oe_processed.json"
+    src.parent.mkdir()
+    src.write_text(json.dumps(entries))
+    (tmp_path / "0_30_s_academic" / "x_mc_processed.json").write_text(json.dumps(entries[:1]))
+    out = tmp_path / "out" / "v.parquet"
+    cs.main(["--input-dir", str(tmp_path), "--glob", "0_30_s*/*_processed.json", "--contains", "_oe_", "--system", "Watch in silence.",
+             "--output", str(out)])
+    import pyarrow.parquet as pq
+
+    table = pq.read_table(out).to_pydict()
+    assert table["id"] == ["7", "b"]
+    first, second = (json.loads(m) for m in table["messages"])
+    assert first[0] == {"role": "system", "content": [{"type": "text", "text": "Watch in silence."}]}
+    assert first[1]["content"] == [{"type": "video_url", "video_url": {"url": "clips/a.mp4"}}, {"type": "text", "text": "What happens?"}]
+    assert [m["role"] for m in first] == ["system", "user", "assistant", "user", "assistant"] and first[3]["content"][0]["text"] == "And then?"
+    kinds = [c["type"] for c in second[1]["content"]]
+    assert kinds == ["image_url", "image_url", "text"] and second[1]["content"][2]["text"] == "Compare\nand"  # third marker: no media left
+    jl = tmp_path / "v.jsonl"
+    cs.main(["--input", str(src), "--output", str(jl), "--max-per-file", "1"])
+    assert len(jl.read_text().splitlines()) == 1
