@@ -162,7 +162,7 @@ def test_example_configs_parse_into_config_objects():
     import lmms_engine_b200.train  # noqa: F401  (registers the trainers)
 
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    files = sorted(glob.glob(os.path.join(root, "examples", "*", "*.yaml")))
+    files = sorted(glob.glob(os.path.join(root, "examples", "*", "*.yaml")) + glob.glob(os.path.join(root, "examples", "*.yaml")))
     files = [f for f in files if os.sep + "data" + os.sep not in f]
     assert len(files) >= 5
     known = set(TrainingArguments.field_names())
