@@ -205,3 +205,48 @@ def test_bagel_mixture_of_transformers_gpu():
                  timesteps=torch.full((6,), 0.4), noise=torch.randn(6, 16),
                  split_lens=[2, 8, 10, 6, 10, 24], attn_modes=["causal", "full", "causal", "noise", "causal", "causal"])
     _compare("bagel", cfg, batch, tol=0.2)
+
+
+def test_generation_on_cached_keys_gpu():
+    """Prefill, then single-token steps against the key / value cache on the varlen kernel (one query row per sequence,
+    keys of different lengths): hidden states of the full pass, within bf16 noise; the Bagel sampler on recorded prompt
+    keys gives the image of the full-stream sampler."""
+    from lmms_engine_b200.mapping_func import create_model_from_config
+    from lmms_engine_b200.models.kv_cache import PackedKVCache
+    from lmms_engine_b200.ops import _cuda
+
+    torch.manual_seed(0)
+    model = create_model_from_config("qwen3", dict(TEXT, model_type="qwen3", max_position_embeddings=512)).to("cuda", torch.bfloat16).eval()
+    lens = [70, 33, 130]
+    seqs = [torch.randint(0, 256, (n,), device="cuda") for n in lens]
+    with torch.no_grad():
+        cu = torch.tensor([0, 70, 103, 233], dtype=torch.int32, device="cuda")
+        full = model(input_ids=torch.cat(seqs), cu_seqlens=cu)["hidden_states"].float()
+        cache = PackedKVCache(2, [n + 4 for n in lens], device="cuda")
+        heads = [n - 3 for n in lens]
+        pos = cache.advance(heads)
+        cu_h = torch.tensor([0, 67, 97, 224], dtype=torch.int32, device="cuda")
+        out = [model(input_ids=torch.cat([s[:h] for s, h in zip(seqs, heads)]), cu_seqlens=cu_h, position_ids=pos, kv_cache=cache)["hidden_states"].float()]
+        for step in range(3):
+            pos = cache.advance([1, 1, 1])
+            ids = torch.stack([s[h + step] for s, h in zip(seqs, heads)])
+            out.append(model(input_ids=ids, cu_seqlens=torch.tensor([0, 1, 2, 3], dtype=torch.int32, device="cuda"), position_ids=pos,
+                             kv_cache=cache)["hidden_states"].float())
+    torch.cuda.synchronize()
+    _cuda.check_status()
+    at = 0
+    for i, (n, h) in enumerate(zip(lens, heads)):
+        start = [0, 67, 97][i]
+        got = torch.cat([out[0][start:start + h]] + [out[1 + s][i:i + 1] for s in range(3)])
+        ref = full[at:at + n]
+        assert (got - ref).abs().max() < 0.06 * ref.abs().max(), (i, float((got - ref).abs().max()), float(ref.abs().max()))
+        at += n
+    bagel = create_model_from_config("bagel", dict(TEXT, model_type="bagel", latent_channels=4, latent_patch_size=2, max_latent_size=8,
+                                                   attention_bias=True, layer_module="Qwen2MoTDecoderLayer")).to("cuda", torch.bfloat16).eval()
+    prompt = torch.randint(0, 200, (40,), device="cuda")
+    runs = [bagel.generate_image(prompt, (4, 4), boi_id=201, eoi_id=202, num_timesteps=4, noise_level=0.0, use_cache=flag,
+                                 generator=torch.Generator("cuda").manual_seed(3)) for flag in (True, False)]
+    torch.cuda.synchronize()
+    _cuda.check_status()
+    a, b = runs[0]["image_latent"].float(), runs[1]["image_latent"].float()
+    assert torch.isfinite(a).all() and (a - b).abs().max() < 0.05 * b.abs().max() + 0.05
