@@ -23,6 +23,7 @@ from ..eval.config import EvalConfig
 from ..models.config import ModelConfig
 from ..parallel.process_group_manager import setup_process_group_manager
 from ..train.config import TrainerConfig, TrainingArguments
+from ..utils.config_loader import load_config
 from ..utils.logging_utils import logger, setup_distributed_logging
 from . import overrides as ov
 
@@ -111,17 +112,22 @@ def save_config(config: Dict[str, Any]) -> None:
 def build_config(argv: List[str]) -> Dict[str, Any]:
     cp, cn, rest = ov.split_argv(argv)
     config = ov.load_config_file(cp, cn, DEFAULT_CONFIG)
+    defaults = deepcopy(config)
     config = ov.apply_overrides(config, rest)
     config_yaml = config.pop("config_yaml", None)
     if config_yaml:
         logger.info(f"config_yaml={config_yaml}: its entries are laid over the defaults, command-line overrides come last")
-        with open(config_yaml) as f:
-            loaded = yaml.safe_load(f)
+        loaded = load_config(config_yaml)  # .yaml / .yml / .json, also relative to the project root
         if isinstance(loaded, list):  # legacy form: a one-element list holding the config
             loaded = loaded[0]
             if "config" in loaded and "type" in loaded:
                 loaded = loaded["config"]
+        # the file replaces whole top-level sections of the defaults (as in the reference, src/lmms_engine/launch/cli.py:147-154);
+        # the command line is then applied to the result, so `config_yaml=x.yaml trainer_args.max_steps=10` does what it says
+        config = defaults
         config.update(loaded)
+        config = ov.apply_overrides(config, rest)
+        config.pop("config_yaml", None)
     return config
 
 

@@ -490,3 +490,33 @@ def test_sharegpt_conversations_become_messages(tmp_path):
     jl = tmp_path / "v.jsonl"
     cs.main(["--input", str(src), "--output", str(jl), "--max-per-file", "1"])
     assert len(jl.read_text().splitlines()) == 1
+
+
+def test_config_files_and_capability_probes(tmp_path, monkeypatch):
+    """JSON and YAML configurations load alike (also by a path relative to the project root) and drive the launcher;
+    the capability probes answer without importing anything heavy."""
+    from lmms_engine_b200.launch import cli
+    from lmms_engine_b200.utils import config_loader as cl
+    from lmms_engine_b200.utils import import_utils as iu
+
+    cfg = {"trainer_type": "fsdp2_trainer", "dataset_config": {"dataset_type": "vision", "dataset_format": "json"},
+           "model_config": {"load_from_pretrained_path": "x"}, "trainer_args": {"output_dir": "out", "learning_rate": 1e-5}}
+    for name in ("a.json", "b.yaml", "c.yml"):
+        cl.save_config(cfg, str(tmp_path / "conf" / name))
+        assert cl.load_config(str(tmp_path / "conf" / name)) == cfg
+    with pytest.raises(ValueError):
+        cl.load_config(str(tmp_path / "conf" / "a.json").replace("a.json", "a.txt")) if (tmp_path / "conf" / "a.txt").write_text("x") else None
+    with pytest.raises(FileNotFoundError):
+        cl.load_config("no/such/file.yaml")
+    (tmp_path / "pyproject.toml").write_text("")
+    (tmp_path / "deep" / "er").mkdir(parents=True)
+    monkeypatch.chdir(tmp_path / "deep" / "er")
+    assert cl.load_config("conf/b.yaml") == cfg  # found from the project root
+    built = cli.build_config([f"config_yaml={tmp_path / 'conf' / 'a.json'}", "trainer_args.learning_rate=2e-5"])
+    assert built["trainer_type"] == "fsdp2_trainer" and built["trainer_args"]["output_dir"] == "out"
+    assert built["trainer_args"]["learning_rate"] == 2e-5 and "config_yaml" not in built  # the command line has the last word
+    assert iu.is_package_available("torch") and not iu.is_package_available("surely_not_a_package")
+    assert iu.is_torch_version_greater_than("1.0") and iu.is_transformers_version_greater_or_equal_to("4.0")
+    assert iu.is_torch_npu_available() is False and isinstance(iu.is_video_audio_available(), bool)
+    if not torch.cuda.is_available():
+        assert not iu.is_flash_attn_2_available() and not iu.is_liger_kernel_available() and not iu.is_fused_moe_available()
