@@ -233,6 +233,9 @@ class VLModel(nn.Module):
         cfg = self.config
         lm = self.language_model
         had_mrope = position_ids is not None and position_ids.dim() >= 2 and position_ids.shape[-2] == 3
+        # a generation step (key / value cache present) states the positions of its new tokens, whatever their form;
+        # otherwise one-dimensional positions are the collator's per-document counters, which images and videos replace
+        had_mrope = had_mrope or (position_ids is not None and kw.get("kv_cache") is not None)
         ids, labels, pos, cu, _ = lm.prepare_packed(input_ids, attention_mask, labels, position_ids if had_mrope else None, cu_seqlens)
         if not had_mrope and not cfg.is_rice and not cfg.is_ov2:
             grids, secs = [], []

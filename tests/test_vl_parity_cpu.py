@@ -784,3 +784,75 @@ def test_omni_audio_in_video_positions_match_upstream():
                                          torch.tensor(mels), torch.tensor(spg))
         mine = omni_positions_one(np.array(ids), IMG, VID, AUD, [(1, 4, 4)], grid_v, spg, 2, 25.0, 2.0)
         assert np.array_equal(ref[:, 0].numpy(), mine), trial
+
+
+def _tiny_realtime(family="qwen3_vl"):
+    from lmms_engine_b200.mapping_func import create_model_from_config
+
+    text = dict(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                head_dim=16, tie_word_embeddings=False, rope_scaling={"mrope_section": [4, 2, 2], "mrope_interleaved": True})
+    vis = dict(depth=2, hidden_size=32, intermediate_size=64, num_heads=2, patch_size=4, temporal_patch_size=2, spatial_merge_size=2,
+               out_hidden_size=64, num_position_embeddings=16, in_channels=3, deepstack_visual_indexes=[0])
+    audio = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2, head_dim=16, num_mel_bins=8, sliding_window=6)
+    cfg = dict(model_type="aero_realtime", backbone_family=family, text_config=text, vision_config=vis, audio_config=audio,
+               downsample_factor=2, image_token_index=290, video_token_index=291, audio_token_index=292, vision_start_token_index=293)
+    return create_model_from_config("aero_realtime", cfg).eval(), text, vis
+
+
+def test_generation_with_an_image_prompt_matches_rerunning_the_sequence():
+    """Greedy continuation of an image + text prompt on the key / value cache (rotary positions continue after the
+    prompt's largest multimodal position) equals re-running the growing sequence through the plain forward pass."""
+    from lmms_engine_b200.mapping_func import create_model_from_config
+    from lmms_engine_b200.models.generation import generate
+
+    torch.manual_seed(0)
+    _, text, vis = _tiny_realtime()
+    model = create_model_from_config("qwen3_vl", dict(model_type="qwen3_vl", text_config=text, vision_config=vis, image_token_id=290,
+                                                      video_token_id=291, vision_start_token_id=293)).eval()
+    ids = torch.randint(0, 280, (30,))
+    ids[2], ids[3:7] = 293, 290
+    pix, grid = torch.randn(16, 3 * 2 * 4 * 4), torch.tensor([[1, 4, 4]])
+    new = generate(model, ids, 6, pixel_values=pix, image_grid_thw=grid)
+    seq = ids.clone()
+    with torch.no_grad():
+        for _ in range(6):
+            cu = torch.tensor([0, seq.numel()], dtype=torch.int32)
+            hidden = model(input_ids=seq, cu_seqlens=cu, pixel_values=pix, image_grid_thw=grid)["hidden_states"]
+            nxt = F.linear(hidden[-1:], model.language_model.lm_head.weight).argmax(-1)
+            seq = torch.cat([seq, nxt])
+    assert new.tolist() == seq[30:].tolist()
+    text_only = create_model_from_config("qwen3", dict(text, model_type="qwen3", rope_scaling=None)).eval()
+    a = generate(text_only, ids[:12], 5, temperature=0.8, generator=torch.Generator().manual_seed(1))
+    b = generate(text_only, ids[:12], 5, temperature=0.8, generator=torch.Generator().manual_seed(1))
+    assert a.tolist() == b.tolist() and a.numel() == 5
+    from lmms_engine_b200.models.dllm import DiffusionLM
+
+    masked = create_model_from_config("qwen3_dllm", dict(text, model_type="qwen3_dllm", rope_scaling=None)).eval()
+    assert isinstance(masked, DiffusionLM)
+    with pytest.raises(NotImplementedError):  # bidirectional masked-token models do not generate left to right
+        generate(masked, ids[:12], 2)
+
+
+def test_realtime_session_streams_slot_by_slot_like_the_full_pass():
+    """One audio slot per call: the tokens the session emits are those the full forward pass predicts at the same
+    slots when it is given the whole stream at once (chunked audio: every slot is encoded by itself)."""
+    from lmms_engine_b200.models.generation import RealtimeSession
+
+    torch.manual_seed(0)
+    model, _, _ = _tiny_realtime()
+    AS, AE, PAD_TOK = 294, 295, 281
+    prompt = torch.cat([torch.randint(0, 280, (10,)), torch.tensor([AS])])
+    K = 7
+    feats = torch.randn(K, 8, 4)  # one [mel, 2 * downsample_factor] piece per slot
+    session = RealtimeSession(model, rt_pad_id=PAD_TOK)
+    session.start(prompt)
+    first = int(session.last)
+    emitted = [session.listen(feats[k]) for k in range(K)]
+    ids = torch.cat([prompt, torch.full((K,), 292)])
+    stream = torch.cat([prompt, torch.tensor([first] + emitted[:-1])])
+    with torch.no_grad():
+        cu = torch.tensor([0, ids.numel()], dtype=torch.int32)
+        hidden = model(input_ids=ids, cu_seqlens=cu, text_stream_ids=stream, input_features=feats,
+                       audio_attention_mask=torch.ones(K, 2, dtype=torch.long))["hidden_states"]
+        want = F.linear(hidden, model.language_model.lm_head.weight).argmax(-1)
+    assert int(want[10]) == first and want[11:].tolist() == emitted
