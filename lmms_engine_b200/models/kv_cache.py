@@ -28,6 +28,11 @@ class PackedKVCache:
         self.device = device
         self._write = self._read = self._cu_k = None
         self._max_k = 0
+        # layers that carry a recurrent state instead of keys / values (linear attention) keep it here:
+        # ``state[layer][sequence]`` is whatever that layer stores (convolution tail, state matrix)
+        self.state: dict = {}
+        self.new_lens: List[int] = []
+        self.had: List[int] = []
 
     def advance(self, new_lens: Sequence[int]) -> torch.Tensor:
         """Declare the next forward pass: ``new_lens[i]`` new tokens for sequence ``i`` (0 = none).  Returns the rotary
@@ -36,6 +41,7 @@ class PackedKVCache:
         if len(new_lens) != len(self.lens):
             raise ValueError(f"{len(new_lens)} lengths for a cache of {len(self.lens)} sequences")
         write, read, pos, cu = [], [], [], [0]
+        self.new_lens, self.had = new_lens, list(self.lens)
         for i, n in enumerate(new_lens):
             have = self.lens[i]
             if have + n > self.capacities[i]:

@@ -137,6 +137,7 @@ def recurrent_gated_delta_rule(q, k, v, g, beta):
 class GatedDeltaNet(nn.Module):
     def __init__(self, cfg: Qwen35Config, layer_idx: int):
         super().__init__()
+        self.layer_idx = layer_idx
         self.hk, self.hv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
         self.dk, self.dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
         self.key_dim, self.value_dim = self.hk * self.dk, self.hv * self.dv
@@ -167,6 +168,9 @@ class GatedDeltaNet(nn.Module):
         b, a = proj[:, c + self.value_dim:c + self.value_dim + self.hv], proj[:, c + self.value_dim + self.hv:c + self.value_dim + 2 * self.hv]
         A_log, dt_bias, conv_w = self.A_log, self.dt_bias, self.conv1d.weight[:, 0]
         hk, hv = self.hk, self.hv
+        if getattr(ctx, "kv_cache", None) is not None:
+            assert ctx.sp_size == 1, "generation runs without sequence parallelism"
+            return self._finish(self._forward_cached(mixed, a, b, conv_w, ctx.kv_cache), z, x, T)
         by_state = ctx.sp_size > 1 and self.cp_mode(ctx.sp_size) == "state"
         if by_state:
             return self._finish(self._forward_state_cp(mixed, a, b, conv_w, ctx, x.device), z, x, T)
@@ -238,6 +242,34 @@ class GatedDeltaNet(nn.Module):
             o = torch.cat([o, o.new_zeros((mixed.shape[0] - o.shape[0], self.hv, self.dv))], 0)
         return o
 
+    def _forward_cached(self, mixed, a, b, conv_w, cache):
+        """Generation: every sequence continues from its stored convolution tail (the last ``kernel - 1`` rows that went
+        into the convolution) and its state matrix; both are replaced by their values after this pass' tokens.  The rule
+        runs on the unchanged chunk scan with the state entering and leaving through ``scan_with_state``."""
+        K, dev = self.kernel, mixed.device
+        store = cache.state.setdefault(self.layer_idx, {})
+        beta = b.sigmoid()
+        g = -self.A_log.float().exp() * F.softplus(a.float() + self.dt_bias)
+        rep = self.hv // self.hk
+        outs, at = [], 0
+        for i, n in enumerate(cache.new_lens):
+            if n == 0:
+                continue
+            have = cache.had[i]
+            tail, S = store.get(i, (mixed.new_zeros((K - 1, mixed.shape[1])), None))
+            rows = torch.cat([tail, mixed[at:at + n]], 0)
+            pos = torch.arange(have - (K - 1), have + n, device=dev).clamp(min=0)
+            seg = gdn_ops.causal_conv_silu_packed(rows, conv_w, pos)[K - 1:]
+            q, k, v = torch.split(seg, [self.key_dim, self.key_dim, self.value_dim], -1)
+            q, k, v = q.reshape(n, self.hk, self.dk), k.reshape(n, self.hk, self.dk), v.reshape(n, self.hv, self.dv)
+            if rep > 1:
+                q, k = q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1)
+            o, S = gdn_ops.chunk_gated_delta_rule_stateful(q, k, v, g[at:at + n], beta[at:at + n], S)
+            store[i] = (rows[-(K - 1):].detach(), S.detach())
+            outs.append(o)
+            at += n
+        return torch.cat(outs, 0)
+
     def _finish(self, o, z, x, T):
         # RMSNorm over the head dim, gated by SiLU(z)
         o = norm_ops.rmsnorm(o.reshape(-1, self.dv).to(x.dtype), self.norm.weight, self.eps)
@@ -270,8 +302,14 @@ class GatedAttention(nn.Module):
         if ctx.sp_size > 1:  # Ulysses: trade the sequence split for a head split around attention
             q, k, v = sp.seq_to_head_qkv(q, k, v, ctx.sp_group)
         q, k = rope_ops.rope_apply(q, ctx.cos, ctx.sin), rope_ops.rope_apply(k, ctx.cos, ctx.sin)
-        o = attn_ops.varlen_attn(q, k, v, ctx.cu_seqlens, ctx.cu_seqlens, ctx.max_seqlen, ctx.max_seqlen, causal=ctx.causal,
-                                 softmax_scale=1.0 / math.sqrt(D))
+        if getattr(ctx, "kv_cache", None) is not None:  # generation: new tokens against the cached rows of their sequence
+            assert ctx.sp_size == 1, "generation runs without sequence parallelism"
+            k_all, v_all, cu_k, max_k = ctx.kv_cache.extend(self.layer_idx, k, v.contiguous())
+            o = attn_ops.varlen_attn(q, k_all, v_all, ctx.cu_seqlens, cu_k, ctx.max_seqlen, max_k, causal=ctx.causal,
+                                     softmax_scale=1.0 / math.sqrt(D))
+        else:
+            o = attn_ops.varlen_attn(q, k, v, ctx.cu_seqlens, ctx.cu_seqlens, ctx.max_seqlen, ctx.max_seqlen, causal=ctx.causal,
+                                     softmax_scale=1.0 / math.sqrt(D))
         if ctx.sp_size > 1:
             o = sp.head_to_seq(o, ctx.sp_group, self.n_q, self.n_kv)
         o = (o.reshape(T, -1).float() * torch.sigmoid(gate.float())).to(x.dtype)
@@ -325,7 +363,7 @@ class Qwen35Backbone(DecoderBackbone):
 
 
 class Qwen35LM(DecoderLM):
-    supports_kv_cache = False
+    supports_kv_cache = True  # attention layers cache keys / values, linear-attention layers their convolution tail and state
     config_class = Qwen35Config
     backbone_cls = Qwen35Backbone
     _no_split_modules = ["Qwen35Layer"]

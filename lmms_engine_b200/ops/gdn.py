@@ -267,6 +267,19 @@ def scan_with_state(w, u, qt, kt, gamma, reset: List[bool], init=None, read_fina
     return v_new[:, pre:pre + n], o[:, pre:pre + n], final
 
 
+def chunk_gated_delta_rule_stateful(q, k, v, g, beta, state=None):
+    """ONE sequence piece continued from ``state [H, dk, dv]`` (``None``: from zero): returns the outputs ``[T, H, dv]``
+    and the state after the piece.  Generation uses it for the prompt and for every later token."""
+    dt = q.dtype
+    T, H, dk = k.shape
+    src, back, reset = chunk_plan([T], q.device)
+    n = len(reset)
+    w, u, qt, kt, gamma, attn = _chunk_terms(q, k, v, g, beta, src, back, n)
+    v_new, o_state, final = scan_with_state(w, u, qt, kt, gamma, reset, state, True)
+    out = (o_state + attn @ v_new).to(dt).movedim(0, 2).reshape(n * CHUNK, H, v.shape[-1])
+    return _unpad(out, back, src), final
+
+
 def chunk_gated_delta_rule_cp(q, k, v, g, beta, lengths: List[int], first_continues: bool, group, plan=None):
     """The rule when the packed stream is split into contiguous token slices over the ranks of ``group`` (all heads on
     every rank).  ``lengths``: the pieces of documents inside this rank's slice; ``first_continues``: the first piece

@@ -101,7 +101,7 @@ def test_grpo_math():
     assert torch.allclose(logp.grad, torch.tensor([-0.5, 0.5])) and float(kl) == 0.0
 
 
-@pytest.mark.parametrize("family", ["qwen3", "qwen3_moe"])
+@pytest.mark.parametrize("family", ["qwen3", "qwen3_moe", "qwen3_5_text"])
 def test_generation_on_cached_keys_matches_rerunning_the_sequences(family):
     """Prefill + one token per step against the key / value cache gives the hidden states of the full pass and the
     same sampled completions (EOS at different steps, a rank kept running by its group)."""
@@ -114,12 +114,15 @@ def test_generation_on_cached_keys_matches_rerunning_the_sequences(family):
                head_dim=8, max_position_embeddings=128)
     if family == "qwen3_moe":
         cfg.update(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, norm_topk_prob=True)
+    if family == "qwen3_5_text":  # hybrid: linear-attention layers keep a convolution tail and a state matrix per sequence
+        cfg.update(num_hidden_layers=4, linear_conv_kernel_dim=4, linear_key_head_dim=8, linear_value_head_dim=8, linear_num_key_heads=2,
+                   linear_num_value_heads=4, rope_parameters={"rope_theta": 10000.0, "partial_rotary_factor": 0.5})
     model = create_model_from_config(family, dict(cfg, model_type=family)).eval()
     seqs = [torch.randint(0, 64, (n,)) for n in (9, 5, 12)]
     with torch.no_grad():
         cu = torch.tensor([0, 9, 14, 26], dtype=torch.int32)
         full = model(input_ids=torch.cat(seqs), cu_seqlens=cu)["hidden_states"]
-        cache = PackedKVCache(2, [16, 16, 16])
+        cache = PackedKVCache(cfg["num_hidden_layers"], [16, 16, 16])
         heads = [6, 5, 7]  # prefill lengths; the rest arrives in two uneven passes, the second sequence sits one out
         pos = cache.advance(heads)
         ids = torch.cat([s[:h] for s, h in zip(seqs, heads)])
