@@ -240,34 +240,73 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t ph = (it >> 1) & 1;
       const int hq = kvh * group + it / n_qt;
       const int qb0 = (ib_lo + it % n_qt) * kTile + half * 32;
-      const float* lse_p = p.lse + static_cast<size_t>(hq) * p.Tq + q_start + qb0;
-      const float* dl_p = p.delta + static_cast<size_t>(hq) * p.Tq + q_start + qb0;
+      // the 32 queries of this warp's columns: lane l fetches the statistics of query l before the wait (one coalesced
+      // load each, latency hidden behind the score products); the loop below reads them by shuffle
+      const bool q_ok = qb0 + lane < len_q;
+      const size_t stat = static_cast<size_t>(hq) * p.Tq + q_start + qb0 + lane;
+      const float lane_lse = q_ok ? p.lse[stat] * kLog2eB : 0.f;
+      const float lane_dl = q_ok ? p.delta[stat] * p.scale : 0.f;  // pre-scaled: dS = P * (dP * scale - delta * scale)
+      // visibility of the warp's 32 keys x 32 queries as a whole: interior tiles skip the per-element tests
+      const int key_first = k0 + q * 32, key_last = key_first + 31;
+      bool full = (qb0 + 31 < len_q) && (key_last < len_k);
+      bool none = (qb0 >= len_q) || (key_first >= len_k);
+      if (p.causal) {
+        full = full && (key_last <= qb0 + offset);
+        none = none || (key_first > qb0 + 31 + offset);
+      }
+      if (p.window_left >= 0) {
+        full = full && (key_first >= qb0 + 31 + offset - p.window_left);
+        none = none || (key_last < qb0 + offset - p.window_left);
+      }
       if (!mbar_wait(&s_full[s], ph, abort_word)) { ok = false; break; }
       tc_fence_after();
-      uint32_t rs[32], rd[32];
-      tmem_ld_32x32b_x32(tm_ST + s * 64 + lane_sel + half * 32, rs);
-      tmem_ld_32x32b_x32(tm_dPT + s * 64 + lane_sel + half * 32, rd);
-      tmem_ld_wait();
       uint32_t ppk[16], dpk[16];
+      if (none) {
 #pragma unroll
-      for (int j = 0; j < 32; j += 2) {
-        float pv[2], dsv[2];
+        for (int j = 0; j < 16; ++j) ppk[j] = dpk[j] = 0u;
+      } else {
+        uint32_t rs[32], rd[32];
+        tmem_ld_32x32b_x32(tm_ST + s * 64 + lane_sel + half * 32, rs);
+        tmem_ld_32x32b_x32(tm_dPT + s * 64 + lane_sel + half * 32, rd);
+        tmem_ld_wait();
+        if (full) {
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int qi = qb0 + j + e;
-          bool vis = (qi < len_q) && (kj < len_k);
-          if (p.causal) vis = vis && (kj <= qi + offset);
-          if (p.window_left >= 0) vis = vis && (kj >= qi + offset - p.window_left);
-          float pe = 0.f, dse = 0.f;
-          if (vis) {
-            pe = exp2f(__uint_as_float(rs[j + e]) * p.scale_log2 - lse_p[j + e] * kLog2eB);
-            dse = pe * (__uint_as_float(rd[j + e]) - dl_p[j + e]) * p.scale;
+          for (int j = 0; j < 32; j += 2) {
+            float pv[2], dsv[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const float l2 = __shfl_sync(0xffffffffu, lane_lse, j + e);
+              const float dl = __shfl_sync(0xffffffffu, lane_dl, j + e);
+              pv[e] = exp2f(__uint_as_float(rs[j + e]) * p.scale_log2 - l2);
+              dsv[e] = pv[e] * fmaf(__uint_as_float(rd[j + e]), p.scale, -dl);
+            }
+            ppk[j / 2] = pack_bf16x2(pv[0], pv[1]);
+            dpk[j / 2] = pack_bf16x2(dsv[0], dsv[1]);
           }
-          pv[e] = pe;
-          dsv[e] = dse;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float pv[2], dsv[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int qi = qb0 + j + e;
+              const float l2 = __shfl_sync(0xffffffffu, lane_lse, j + e);
+              const float dl = __shfl_sync(0xffffffffu, lane_dl, j + e);
+              bool vis = (qi < len_q) && (kj < len_k);
+              if (p.causal) vis = vis && (kj <= qi + offset);
+              if (p.window_left >= 0) vis = vis && (kj >= qi + offset - p.window_left);
+              float pe = 0.f, dse = 0.f;
+              if (vis) {
+                pe = exp2f(__uint_as_float(rs[j + e]) * p.scale_log2 - l2);
+                dse = pe * fmaf(__uint_as_float(rd[j + e]), p.scale, -dl);
+              }
+              pv[e] = pe;
+              dsv[e] = dse;
+            }
+            ppk[j / 2] = pack_bf16x2(pv[0], pv[1]);
+            dpk[j / 2] = pack_bf16x2(dsv[0], dsv[1]);
+          }
         }
-        ppk[j / 2] = pack_bf16x2(pv[0], pv[1]);
-        dpk[j / 2] = pack_bf16x2(dsv[0], dsv[1]);
       }
       if (it >= 2 && !mbar_wait(&pd_free[s], ph ^ 1, abort_word)) { ok = false; break; }
       uint8_t* rp = smem + Smem::kP + s * Smem::kProb + r * 128;
@@ -481,36 +520,67 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
     const bool row_valid = qi < len_q;
     const float my_lse = row_valid ? p.lse[static_cast<size_t>(head) * p.Tq + q_start + qi] * kLog2eB : 0.f;
-    const float my_delta = row_valid ? p.delta[static_cast<size_t>(head) * p.Tq + q_start + qi] : 0.f;
+    const float my_delta = row_valid ? p.delta[static_cast<size_t>(head) * p.Tq + q_start + qi] * p.scale : 0.f;  // pre-scaled
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
       const int s = it & 1;
       const uint32_t ph = (it >> 1) & 1;
       const int kb0 = (jb_lo + it) * kTile + half * 32;
+      // visibility of the warp's 32 queries x 32 keys as a whole: interior tiles skip the per-element tests,
+      // tiles above the diagonal skip the exponentials
+      const int row_first = q0 + q * 32, row_last = row_first + 31;
+      bool full = (row_last < len_q) && (kb0 + 31 < len_k);
+      bool none = (row_first >= len_q) || (kb0 >= len_k);
+      if (p.causal) {
+        full = full && (kb0 + 31 <= row_first + offset);
+        none = none || (kb0 > row_last + offset);
+      }
+      if (p.window_left >= 0) {
+        full = full && (kb0 >= row_last + offset - p.window_left);
+        none = none || (kb0 + 31 < row_first + offset - p.window_left);
+      }
       if (!mbar_wait(&s_full[s], ph, abort_word)) { ok = false; break; }
       tc_fence_after();
-      uint32_t rs[32], rd[32];
-      tmem_ld_32x32b_x32(tm_S + s * 64 + lane_sel + half * 32, rs);
-      tmem_ld_32x32b_x32(tm_dP + s * 64 + lane_sel + half * 32, rd);
-      tmem_ld_wait();
       uint32_t dpk[16];
+      if (none) {
 #pragma unroll
-      for (int j = 0; j < 32; j += 2) {
-        float dsv[2];
+        for (int j = 0; j < 16; ++j) dpk[j] = 0u;
+      } else {
+        uint32_t rs[32], rd[32];
+        tmem_ld_32x32b_x32(tm_S + s * 64 + lane_sel + half * 32, rs);
+        tmem_ld_32x32b_x32(tm_dP + s * 64 + lane_sel + half * 32, rd);
+        tmem_ld_wait();
+        if (full) {
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int kj = kb0 + j + e;
-          bool vis = row_valid && (kj < len_k);
-          if (p.causal) vis = vis && (kj <= qi + offset);
-          if (p.window_left >= 0) vis = vis && (kj >= qi + offset - p.window_left);
-          float dse = 0.f;
-          if (vis) {
-            const float pe = exp2f(__uint_as_float(rs[j + e]) * p.scale_log2 - my_lse);
-            dse = pe * (__uint_as_float(rd[j + e]) - my_delta) * p.scale;
+          for (int j = 0; j < 32; j += 2) {
+            float dsv[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const float pe = exp2f(__uint_as_float(rs[j + e]) * p.scale_log2 - my_lse);
+              dsv[e] = pe * fmaf(__uint_as_float(rd[j + e]), p.scale, -my_delta);
+            }
+            dpk[j / 2] = pack_bf16x2(dsv[0], dsv[1]);
           }
-          dsv[e] = dse;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float dsv[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int kj = kb0 + j + e;
+              bool vis = row_valid && (kj < len_k);
+              if (p.causal) vis = vis && (kj <= qi + offset);
+              if (p.window_left >= 0) vis = vis && (kj >= qi + offset - p.window_left);
+              float dse = 0.f;
+              if (vis) {
+                const float pe = exp2f(__uint_as_float(rs[j + e]) * p.scale_log2 - my_lse);
+                dse = pe * fmaf(__uint_as_float(rd[j + e]), p.scale, -my_delta);
+              }
+              dsv[e] = dse;
+            }
+            dpk[j / 2] = pack_bf16x2(dsv[0], dsv[1]);
+          }
         }
-        dpk[j / 2] = pack_bf16x2(dsv[0], dsv[1]);
       }
       if (it >= 2 && !mbar_wait(&ds_free[s], ph ^ 1, abort_word)) { ok = false; break; }
       uint8_t* rdst = smem + Smem::kDS + s * Smem::kProb + r * 128;
