@@ -42,20 +42,34 @@ struct BwdP {
   int* status;
 };
 
+// Shared memory.  The inner tiles (Q_i, dO_i in the dkdv kernel; K_j, V_j in the dq kernel) go through kStages stages:
+// a stage is released only when the accumulating products that read it have retired, and the refill then pays the whole
+// TMA latency, so with S stages a tile's period is about (latency + MMA time) / (S - 1).  The dq kernel needs no P
+// buffers and spends that room on a fourth stage.
 struct Smem {
+  static constexpr int kStages = 3;
   static constexpr int kBig = kKeys * DP * 2;     // 32 KB: a 128-row tile
   static constexpr int kSmall = kTile * DP * 2;   // 16 KB: a 64-row tile
   static constexpr int kProb = kKeys * kTile * 2; // 16 KB: a 128 x 64 probability tile
-  // dkdv: K, V | 2 x (Q_i, dO_i) | 2 x P^T | 2 x dS^T
-  // dq  : Q, dO | 2 x (K_j, V_j) | 2 x dS
+  // dkdv: K, V | kStages x (Q_i, dO_i) | 2 x P^T | 2 x dS^T
   static constexpr int kA0 = 0;
   static constexpr int kA1 = kBig;
-  static constexpr int kStage = 2 * kBig;                 // 2 stages of 2 small tiles
-  static constexpr int kP = kStage + 2 * 2 * kSmall;      // 2 buffers
-  static constexpr int kDS = kP + 2 * kProb;              // 2 buffers
+  static constexpr int kStage = 2 * kBig;
+  static constexpr int kP = kStage + kStages * 2 * kSmall;
+  static constexpr int kDS = kP + 2 * kProb;
   static constexpr int kBars = kDS + 2 * kProb;
   static constexpr int kTotal = kBars + 256 + 1024;
 };
+
+struct SmemQ {
+  static constexpr int kStages = 4;
+  // dq: Q, dO | kStages x (K_j, V_j) | 2 x dS
+  static constexpr int kStage = 2 * Smem::kBig;
+  static constexpr int kDS = kStage + kStages * 2 * Smem::kSmall;
+  static constexpr int kBars = kDS + 2 * Smem::kProb;
+  static constexpr int kTotal = kBars + 256 + 1024;
+};
+static_assert(Smem::kTotal <= 227 * 1024 && SmemQ::kTotal <= 227 * 1024, "shared memory of the backward kernels");
 
 __device__ __forceinline__ uint64_t desc_lbo(uint32_t addr, uint32_t lbo_bytes) {
   uint64_t d = umma_desc_sw128(addr);
@@ -94,14 +108,15 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::kBars);
-  uint64_t* kv_full = bars;          // 1
-  uint64_t* q_full = bars + 1;       // 2
-  uint64_t* q_empty = bars + 3;      // 2
-  uint64_t* s_full = bars + 5;       // 2   S^T and dP^T of a buffer are in TMEM
-  uint64_t* ds_full = bars + 7;      // 2   P^T / dS^T of a buffer are in shared memory
-  uint64_t* pd_free = bars + 9;      // 2   the dV / dK products that read a smem buffer retired
-  uint64_t* all_done = bars + 11;    // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  constexpr int S = Smem::kStages;
+  uint64_t* kv_full = bars;                  // 1
+  uint64_t* q_full = bars + 1;               // S   a stage holds Q_i and dO_i
+  uint64_t* q_empty = bars + 1 + S;          // S   the products that read a stage retired
+  uint64_t* s_full = bars + 1 + 2 * S;       // 2   S^T and dP^T of a buffer are in TMEM
+  uint64_t* ds_full = bars + 3 + 2 * S;      // 2   P^T / dS^T of a buffer are in shared memory
+  uint64_t* pd_free = bars + 5 + 2 * S;      // 2   the dV / dK products that read a smem buffer retired
+  uint64_t* all_done = bars + 7 + 2 * S;     // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8 + 2 * S);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* work = reinterpret_cast<int*>(tmem_slot + 2);
 
@@ -110,9 +125,11 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     work[0] = -1;
     find_work(p.cu_k, p.cu_q, p.n_docs, kKeys, blockIdx.x, work, p.Tk, p.Tq, p.status);
     mbar_init(kv_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < S; ++i) {
       mbar_init(&q_full[i], 1);
       mbar_init(&q_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
       mbar_init(&ds_full[i], 8);
       mbar_init(&pd_free[i], 1);
@@ -162,8 +179,8 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       bool ok = true;
       for (int it = 0; it < n_iter && ok; ++it) {
-        const int s = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
+        const int s = it % S;
+        const uint32_t ph = (it / S) & 1;
         const int hq = kvh * group + it / n_qt;
         const int qrow = q_start + (ib_lo + it % n_qt) * kTile;
         if (!mbar_wait(&q_empty[s], ph ^ 1, abort_word)) { ok = false; break; }
@@ -183,11 +200,11 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t sK = smem_u32(smem + Smem::kA0), sV = smem_u32(smem + Smem::kA1);
       bool ok = mbar_wait(kv_full, 0, abort_word);
       auto issue_scores = [&](int it) -> bool {
-        const int s = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait(&q_full[s], ph, abort_word)) return false;
+        const int s = it & 1;            // TMEM buffer of the scores
+        const int stg = it % S;          // shared-memory stage of Q_i / dO_i
+        if (!mbar_wait(&q_full[stg], (it / S) & 1, abort_word)) return false;
         tc_fence_after();
-        const uint32_t sQ = smem_u32(smem + Smem::kStage + s * 2 * Smem::kSmall);
+        const uint32_t sQ = smem_u32(smem + Smem::kStage + stg * 2 * Smem::kSmall);
         const uint32_t sdO = sQ + Smem::kSmall;
 #pragma unroll
         for (int kk = 0; kk < DP / 16; ++kk) {
@@ -211,7 +228,8 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t ph = (it >> 1) & 1;
         if (!mbar_wait(&ds_full[s], ph, abort_word)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t sQ = smem_u32(smem + Smem::kStage + s * 2 * Smem::kSmall);
+        const int stg = it % S;
+        const uint32_t sQ = smem_u32(smem + Smem::kStage + stg * 2 * Smem::kSmall);
         const uint32_t sdO = sQ + Smem::kSmall;
         const uint32_t sPT = smem_u32(smem + Smem::kP + s * Smem::kProb);
         const uint32_t sDST = smem_u32(smem + Smem::kDS + s * Smem::kProb);
@@ -223,7 +241,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           umma_bf16_ss(tm_dK, umma_desc_sw128(sDST + kk * 32), desc_lbo(sQ + kk * 2048, kTile * 128), idesc_acc,
                        (it | kk) != 0);
         }
-        umma_commit(&q_empty[s]);
+        umma_commit(&q_empty[stg]);
         umma_commit(&pd_free[s]);
       }
       if (ok) umma_commit(all_done);
@@ -381,15 +399,16 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, const BwdP p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::kBars);
-  uint64_t* q_full = bars;           // 1   Q and dO
-  uint64_t* kv_full = bars + 1;      // 2
-  uint64_t* kv_empty = bars + 3;     // 2
-  uint64_t* s_full = bars + 5;       // 2
-  uint64_t* ds_full = bars + 7;      // 2
-  uint64_t* ds_free = bars + 9;      // 2
-  uint64_t* all_done = bars + 11;    // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SmemQ::kBars);
+  constexpr int S = SmemQ::kStages;
+  uint64_t* q_full = bars;                   // 1   Q and dO
+  uint64_t* kv_full = bars + 1;              // S   a stage holds K_j and V_j
+  uint64_t* kv_empty = bars + 1 + S;         // S
+  uint64_t* s_full = bars + 1 + 2 * S;       // 2
+  uint64_t* ds_full = bars + 3 + 2 * S;      // 2
+  uint64_t* ds_free = bars + 5 + 2 * S;      // 2
+  uint64_t* all_done = bars + 7 + 2 * S;     // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8 + 2 * S);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* work = reinterpret_cast<int*>(tmem_slot + 2);
 
@@ -402,9 +421,11 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const int item = total - 1 - static_cast<int>(blockIdx.x);
     if (item >= 0) find_work(p.cu_q, p.cu_k, p.n_docs, kKeys, item, work, p.Tq, p.Tk, p.status);
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < S; ++i) {
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
       mbar_init(&ds_full[i], 8);
       mbar_init(&ds_free[i], 1);
@@ -451,12 +472,12 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       bool ok = true;
       for (int it = 0; it < n_iter && ok; ++it) {
-        const int s = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
+        const int s = it % S;
+        const uint32_t ph = (it / S) & 1;
         const int krow = k_start + (jb_lo + it) * kTile;
         if (!mbar_wait(&kv_empty[s], ph ^ 1, abort_word)) { ok = false; break; }
         mbar_expect_tx(&kv_full[s], 2 * Smem::kSmall);
-        uint8_t* dst = smem + Smem::kStage + s * 2 * Smem::kSmall;
+        uint8_t* dst = smem + SmemQ::kStage + s * 2 * Smem::kSmall;
 #pragma unroll
         for (int c = 0; c < DP / 64; ++c) {
           tma_load_3d(dst + c * (kTile * 128), &tmK, &kv_full[s], c * 64, kvh, krow);
@@ -471,11 +492,11 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       const uint32_t sQ = smem_u32(smem + Smem::kA0), sdO = smem_u32(smem + Smem::kA1);
       bool ok = mbar_wait(q_full, 0, abort_word);
       auto issue_scores = [&](int it) -> bool {
-        const int s = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait(&kv_full[s], ph, abort_word)) return false;
+        const int s = it & 1;            // TMEM buffer of the scores
+        const int stg = it % S;          // shared-memory stage of K_j / V_j
+        if (!mbar_wait(&kv_full[stg], (it / S) & 1, abort_word)) return false;
         tc_fence_after();
-        const uint32_t sK = smem_u32(smem + Smem::kStage + s * 2 * Smem::kSmall);
+        const uint32_t sK = smem_u32(smem + SmemQ::kStage + stg * 2 * Smem::kSmall);
         const uint32_t sV = sK + Smem::kSmall;
 #pragma unroll
         for (int kk = 0; kk < DP / 16; ++kk) {
@@ -499,15 +520,16 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const uint32_t ph = (it >> 1) & 1;
         if (!mbar_wait(&ds_full[s], ph, abort_word)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t sK = smem_u32(smem + Smem::kStage + s * 2 * Smem::kSmall);
-        const uint32_t sDS = smem_u32(smem + Smem::kDS + s * Smem::kProb);
+        const int stg = it % S;
+        const uint32_t sK = smem_u32(smem + SmemQ::kStage + stg * 2 * Smem::kSmall);
+        const uint32_t sDS = smem_u32(smem + SmemQ::kDS + s * Smem::kProb);
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk) {
           // A = dS [128 q x 64 keys] K-major; B = K_j [keys, d] MN-major (64-wide d chunks 8 KB apart)
           umma_bf16_ss(tm_dQ, umma_desc_sw128(sDS + kk * 32), desc_lbo(sK + kk * 2048, kTile * 128), idesc_dq,
                        (it | kk) != 0);
         }
-        umma_commit(&kv_empty[s]);
+        umma_commit(&kv_empty[stg]);
         umma_commit(&ds_free[s]);
       }
       if (ok) umma_commit(all_done);
@@ -583,7 +605,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       if (it >= 2 && !mbar_wait(&ds_free[s], ph ^ 1, abort_word)) { ok = false; break; }
-      uint8_t* rdst = smem + Smem::kDS + s * Smem::kProb + r * 128;
+      uint8_t* rdst = smem + SmemQ::kDS + s * Smem::kProb + r * 128;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int chunk = (half * 4 + c) ^ (r & 7);
@@ -733,13 +755,13 @@ extern "C" int b200_attn_bwd_v2(const void* q, const void* k, const void* v, con
   static bool set = false;
   if (!set) {
     cudaFuncSetAttribute(attn_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal);
-    cudaFuncSetAttribute(attn_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal);
+    cudaFuncSetAttribute(attn_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemQ::kTotal);
     set = true;
   }
   dim3 grid_kv((Tk + kKeys - 1) / kKeys + n_docs, Hkv);
   attn_dkdv_kernel<<<grid_kv, 384, Smem::kTotal, st>>>(tq64, tk128, tv128, tdo64, p);
   if (cudaGetLastError() != cudaSuccess) return -4;
   dim3 grid_q((Tq + kKeys - 1) / kKeys + n_docs, Hq);
-  attn_dq_kernel<<<grid_q, 384, Smem::kTotal, st>>>(tq128, tk64, tv64, tdo128, p);
+  attn_dq_kernel<<<grid_q, 384, SmemQ::kTotal, st>>>(tq128, tk64, tv64, tdo128, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
