@@ -487,6 +487,127 @@ __global__ void ema_kernel(float* __restrict__ ema, const PT* __restrict__ p, lo
     ema[i] = decay * ema[i] + (1.f - decay) * static_cast<float>(p[i]);
 }
 
+// ---- 16-byte versions of the optimizer passes ---------------------------------------------------------------
+// The passes above move 2 or 4 bytes per thread and iteration, which keeps too few bytes in flight to fill HBM
+// (1.3 - 3.5 TB/s measured).  These take four elements per thread and iteration (float4 / 4 x bf16); the launchers use
+// them when every pointer is 16-byte aligned (8 for the bf16 arrays) and hand the last n % 4 elements to the scalar
+// kernels.  Element-wise results are bit-identical to the scalar kernels; the sums of squares add in another order.
+struct alignas(8) bf16x4 {
+  uint32_t lo, hi;
+};
+__device__ __forceinline__ bf16x4 to_bf16x4(float a, float b, float c, float d) {
+  bf16x4 r;
+  r.lo = pack_bf16x2(a, b);
+  r.hi = pack_bf16x2(c, d);
+  return r;
+}
+
+__global__ void adamw_vec_kernel(float4* __restrict__ p32, bf16x4* __restrict__ p16, float4* __restrict__ m,
+                                 float4* __restrict__ v, const float4* __restrict__ g, long nv, float lr, float beta1,
+                                 float beta2, float eps, float wd, float bc1, float bc2, const float* gscale,
+                                 const int* skip) {
+  if (skip != nullptr && *skip) return;
+  const float gs = gscale != nullptr ? *gscale : 1.f;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < nv;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const float4 g4 = g[i];
+    float4 p4 = p32[i], m4 = m[i], v4 = v[i];
+    const float gi[4] = {g4.x * gs, g4.y * gs, g4.z * gs, g4.w * gs};
+    float pi[4] = {p4.x, p4.y, p4.z, p4.w}, mi[4] = {m4.x, m4.y, m4.z, m4.w}, vi[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      mi[e] = beta1 * mi[e] + (1.f - beta1) * gi[e];
+      vi[e] = beta2 * vi[e] + (1.f - beta2) * gi[e] * gi[e];
+      pi[e] *= (1.f - lr * wd);
+      pi[e] -= lr * (mi[e] / bc1) / (sqrtf(vi[e] / bc2) + eps);
+    }
+    m[i] = make_float4(mi[0], mi[1], mi[2], mi[3]);
+    v[i] = make_float4(vi[0], vi[1], vi[2], vi[3]);
+    p32[i] = make_float4(pi[0], pi[1], pi[2], pi[3]);
+    if (p16 != nullptr) p16[i] = to_bf16x4(pi[0], pi[1], pi[2], pi[3]);
+  }
+}
+
+__global__ void muon_momentum_vec_kernel(float4* __restrict__ mom, const float4* __restrict__ g, bf16x4* __restrict__ out,
+                                         float* __restrict__ sumsq, long nv, float beta, int nesterov,
+                                         const float* gscale) {
+  __shared__ float red[32];
+  const float gs = gscale != nullptr ? *gscale : 1.f;
+  float acc = 0.f;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < nv;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const float4 g4 = g[i];
+    const float4 m4 = mom[i];
+    const float gi[4] = {g4.x * gs, g4.y * gs, g4.z * gs, g4.w * gs};
+    float mi[4] = {m4.x, m4.y, m4.z, m4.w}, u[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      mi[e] = beta * mi[e] + (1.f - beta) * gi[e];
+      u[e] = nesterov ? gi[e] + beta * (mi[e] - gi[e]) : mi[e];
+      acc += u[e] * u[e];
+    }
+    mom[i] = make_float4(mi[0], mi[1], mi[2], mi[3]);
+    out[i] = to_bf16x4(u[0], u[1], u[2], u[3]);
+  }
+  acc = block_sum<256>(acc, red);
+  if (threadIdx.x == 0) atomicAdd(sumsq, acc);
+}
+
+__global__ void scale_by_norm_vec_kernel(uint4* __restrict__ x, const float* __restrict__ sumsq, long nv8, float eps) {
+  const float s = 1.f / (sqrtf(*sumsq) + eps);
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < nv8;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    uint4 w = x[i];
+    float2 a = unpack_bf16x2(w.x), b = unpack_bf16x2(w.y), c = unpack_bf16x2(w.z), d = unpack_bf16x2(w.w);
+    // the same rounding as the scalar kernel: bf16(float(x) * s)
+    w.x = pack_bf16x2(a.x * s, a.y * s);
+    w.y = pack_bf16x2(b.x * s, b.y * s);
+    w.z = pack_bf16x2(c.x * s, c.y * s);
+    w.w = pack_bf16x2(d.x * s, d.y * s);
+    x[i] = w;
+  }
+}
+
+__global__ void muon_update_vec_kernel(float4* __restrict__ p32, bf16x4* __restrict__ p16, const bf16x4* __restrict__ o,
+                                       long nv, float lr, float wd, float scale, const int* skip) {
+  if (skip != nullptr && *skip) return;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < nv;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const float4 p4 = p32[i];
+    const bf16x4 o4 = o[i];
+    const float2 oa = unpack_bf16x2(o4.lo), ob = unpack_bf16x2(o4.hi);
+    const float r0 = p4.x * (1.f - lr * wd) - lr * scale * oa.x;
+    const float r1 = p4.y * (1.f - lr * wd) - lr * scale * oa.y;
+    const float r2 = p4.z * (1.f - lr * wd) - lr * scale * ob.x;
+    const float r3 = p4.w * (1.f - lr * wd) - lr * scale * ob.y;
+    p32[i] = make_float4(r0, r1, r2, r3);
+    if (p16 != nullptr) p16[i] = to_bf16x4(r0, r1, r2, r3);
+  }
+}
+
+__global__ void sumsq_part_vec_kernel(const float4* __restrict__ g, float* __restrict__ part, long nv, const float* tail,
+                                      int n_tail) {
+  __shared__ float red[32];
+  float acc = 0.f;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x;
+  // four independent 16-byte loads per thread and iteration: the grid is capped at the size of the partials scratch
+  for (; i + 3 * stride < nv; i += 4 * stride) {
+    const float4 a = g[i], b = g[i + stride], c = g[i + 2 * stride], d = g[i + 3 * stride];
+    acc += (a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w) + (b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w) +
+           (c.x * c.x + c.y * c.y + c.z * c.z + c.w * c.w) + (d.x * d.x + d.y * d.y + d.z * d.z + d.w * d.w);
+  }
+  for (; i < nv; i += stride) {
+    const float4 v = g[i];
+    acc += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  if (blockIdx.x == 0 && threadIdx.x < n_tail) acc += tail[threadIdx.x] * tail[threadIdx.x];
+  acc = block_sum<256>(acc, red);
+  if (threadIdx.x == 0) part[blockIdx.x] = acc;
+}
+
+static inline bool aligned_to(const void* p, uintptr_t a) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
 // Deterministic two-stage sum of squares: part[blockIdx.x] then a single-CTA finish.
 template <typename GT>
 __global__ void sumsq_part_kernel(const GT* __restrict__ g, float* __restrict__ part, long n) {
@@ -757,6 +878,16 @@ int b200_adamw(void* p32, void* p16, void* m, void* v, const void* g, int g_is_f
                float beta2, float eps, float wd, float bc1, float bc2, const void* gscale, const void* skip,
                cudaStream_t st) {
   if (n <= 0) return 0;
+  if (g_is_fp32 && n >= 4 && aligned_to(p32, 16) && aligned_to(p16, 8) && aligned_to(m, 16) && aligned_to(v, 16) && aligned_to(g, 16)) {
+    const long nv = n / 4, done = nv * 4;
+    adamw_vec_kernel<<<grid_for(nv, 256), 256, 0, st>>>((float4*)p32, (bf16x4*)p16, (float4*)m, (float4*)v, (const float4*)g, nv, lr,
+                                                        beta1, beta2, eps, wd, bc1, bc2, (const float*)gscale, (const int*)skip);
+    if (done < n)
+      adamw_kernel<float><<<1, 32, 0, st>>>((float*)p32 + done, p16 ? (bf16*)p16 + done : nullptr, (float*)m + done, (float*)v + done,
+                                            (const float*)g + done, n - done, lr, beta1, beta2, eps, wd, bc1, bc2,
+                                            (const float*)gscale, (const int*)skip);
+    return CHECK_LAUNCH();
+  }
   int blocks = grid_for(n, 256);
   if (g_is_fp32)
     adamw_kernel<float><<<blocks, 256, 0, st>>>((float*)p32, (bf16*)p16, (float*)m, (float*)v, (const float*)g, n, lr,
@@ -772,6 +903,13 @@ int b200_muon_momentum(void* mom, const void* g, int g_is_fp32, void* out, void*
                        int nesterov, const void* gscale, float eps, cudaStream_t st) {
   if (n <= 0) return 0;
   cudaMemsetAsync(sumsq, 0, sizeof(float), st);
+  if (g_is_fp32 && n % 8 == 0 && aligned_to(mom, 16) && aligned_to(g, 16) && aligned_to(out, 16)) {
+    // whole matrices: their element counts are multiples of 8 in every supported layout
+    muon_momentum_vec_kernel<<<grid_for(n / 4, 256, 4), 256, 0, st>>>((float4*)mom, (const float4*)g, (bf16x4*)out, (float*)sumsq,
+                                                                     n / 4, beta, nesterov, (const float*)gscale);
+    scale_by_norm_vec_kernel<<<grid_for(n / 8, 256, 4), 256, 0, st>>>((uint4*)out, (const float*)sumsq, n / 8, eps);
+    return CHECK_LAUNCH();
+  }
   int blocks = grid_for(n, 256, 4);
   if (g_is_fp32)
     muon_momentum_kernel<float><<<blocks, 256, 0, st>>>((float*)mom, (const float*)g, (bf16*)out, (float*)sumsq, n,
@@ -786,6 +924,11 @@ int b200_muon_momentum(void* mom, const void* g, int g_is_fp32, void* out, void*
 int b200_muon_update(void* p32, void* p16, const void* o, long n, float lr, float wd, float scale, const void* skip,
                      cudaStream_t st) {
   if (n <= 0) return 0;
+  if (n % 4 == 0 && aligned_to(p32, 16) && aligned_to(p16, 8) && aligned_to(o, 8)) {
+    muon_update_vec_kernel<<<grid_for(n / 4, 256), 256, 0, st>>>((float4*)p32, (bf16x4*)p16, (const bf16x4*)o, n / 4, lr, wd, scale,
+                                                                 (const int*)skip);
+    return CHECK_LAUNCH();
+  }
   muon_update_kernel<<<grid_for(n, 256), 256, 0, st>>>((float*)p32, (bf16*)p16, (const bf16*)o, n, lr, wd, scale,
                                                        (const int*)skip);
   return CHECK_LAUNCH();
@@ -801,6 +944,14 @@ int b200_ema(void* ema, const void* p, int p_is_fp32, long n, float decay, cudaS
 // part: fp32 scratch of b200_num_partials() floats.  out[0] (+)= sum g^2.
 int b200_sumsq(const void* g, int g_is_fp32, long n, void* part, void* out, int accumulate, cudaStream_t st) {
   int blocks = grid_for(n > 0 ? n : 1, 256, 2);
+  if (g_is_fp32 && n >= 4 && aligned_to(g, 16)) {
+    const long nv = n / 4;
+    blocks = grid_for(nv, 256, 2);  // the partials scratch holds b200_num_partials() = 2 per SM
+    sumsq_part_vec_kernel<<<blocks, 256, 0, st>>>((const float4*)g, (float*)part, nv, (const float*)g + nv * 4,
+                                                  static_cast<int>(n - nv * 4));
+    sumsq_finish_kernel<<<1, 256, 0, st>>>((const float*)part, (float*)out, blocks, accumulate);
+    return CHECK_LAUNCH();
+  }
   if (g_is_fp32) sumsq_part_kernel<float><<<blocks, 256, 0, st>>>((const float*)g, (float*)part, n);
   else sumsq_part_kernel<bf16><<<blocks, 256, 0, st>>>((const bf16*)g, (float*)part, n);
   sumsq_finish_kernel<<<1, 256, 0, st>>>((const float*)part, (float*)out, blocks, accumulate);

@@ -211,6 +211,35 @@ def test_muon_kernels_and_ema():
     assert torch.allclose(ema, 0.1 * p16.float(), atol=1e-6)
 
 
+def test_muon_momentum_fp32_gradient_vector_and_scalar_paths():
+    """fp32 gradients (what the native runtimes hold): whole matrices take the 16-byte kernels, an odd length or an
+    unaligned view the scalar ones; both agree with the formula and with each other element for element."""
+    from lmms_engine_b200.ops import optim
+
+    torch.manual_seed(0)
+    for n, shift in ((384 * 256, 0), (384 * 256 + 3, 0), (384 * 256, 1)):
+        big_g = torch.randn(n + 8, device="cuda")
+        g = big_g[shift:shift + n]
+        mom = torch.zeros(n + 8, device="cuda")[shift:shift + n]
+        out = torch.empty(n + 8, device="cuda", dtype=torch.bfloat16)[shift:shift + n]
+        ss = torch.zeros(1, device="cuda")
+        optim.muon_momentum(mom, g, out, ss, beta=0.9, nesterov=True)
+        mref = 0.1 * g
+        u = g + 0.9 * (mref - g)
+        assert torch.allclose(mom, mref, atol=1e-6)
+        want = (u.to(torch.bfloat16).float() / (u.norm() + 1e-7)).to(torch.bfloat16)
+        assert (out.float() - want.float()).abs().max() <= 2 ** -8 * want.float().abs().max()
+        assert abs(float(ss) - float(u.double().pow(2).sum())) < 1e-3 * float(ss)
+        p = torch.randn(n + 8, device="cuda")[shift:shift + n]
+        p0 = p.clone()
+        p16 = torch.empty(n + 8, device="cuda", dtype=torch.bfloat16)[shift:shift + n]
+        optim.muon_update(p, p16, out, lr=0.02, wd=0.1, scale=3.0)
+        assert torch.allclose(p, p0 * (1 - 0.002) - 0.06 * out.float(), atol=1e-6) and torch.equal(p16, p.to(torch.bfloat16))
+        ss2 = torch.zeros(1, device="cuda")
+        optim.sumsq_(g, ss2, False)
+        assert abs(float(ss2) - float(g.double().pow(2).sum())) < 1e-5 * float(ss2)
+
+
 def test_gather_scatter_rows():
     from lmms_engine_b200.ops import index
 
