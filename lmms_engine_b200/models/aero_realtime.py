@@ -11,8 +11,8 @@
   multimodal rotary positions (audio positions advance like text).
 
 Reference: src/lmms_engine/models/aero_realtime/modeling_aero_realtime.py:110-148 (projector), :380-440 (audio features),
-:460-676 (forward), configuration_aero_realtime.py:187-300, backbone_registry.py.  Of the reference encoder's variants only
-the causal / RMSNorm / gated-MLP form is built (the released configuration).
+:460-676 (forward), configuration_aero_realtime.py:187-300, backbone_registry.py.  The reference encoder's variants (LayerNorm, GELU MLP, symmetric
+convolution padding, attention without causality) are configuration fields of the audio encoder (``models/audio.py``).
 """
 from __future__ import annotations
 
@@ -46,9 +46,6 @@ class AeroRealtimeConfig(VLConfig):
         if family not in FAMILIES:
             raise ValueError(f"unknown backbone_family={family}; expected one of {FAMILIES}")
         audio = dict(d.pop("audio_config", None) or {})
-        for variant, default in (("norm_type", "rms_norm"), ("mlp_type", "swiglu"), ("conv_padding", "causal")):
-            if audio.get(variant, default) != default:
-                raise NotImplementedError(f"audio encoder variant {variant}={audio[variant]} is not built")
         own = {k: d.pop(k) for k in ("projector_hidden_act", "downsample_factor", "audio_length_per_tok") if k in d}
         for a, b in (("image_token_index", "image_token_id"), ("video_token_index", "video_token_id"),
                      ("vision_start_token_index", "vision_start_token_id"), ("audio_token_index", "audio_token_id")):

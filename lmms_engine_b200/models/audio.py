@@ -385,7 +385,27 @@ class VoxtralRealtimeEncoderConfig:
     rope_theta: float = 10000.0
     sliding_window: Optional[int] = 750
     max_position_embeddings: int = 1500
+    # variants of the realtime model's own encoder (src/lmms_engine/models/aero_realtime/configuration_aero_realtime.py:41-114);
+    # the defaults are the released streaming encoder
+    norm_type: str = "rms_norm"            # rms_norm | layer_norm
+    mlp_type: str = "swiglu"               # swiglu | gelu (fc1 / fc2 with biases)
+    conv_padding: str = "causal"           # causal | symmetric (every chunk is encoded by itself)
+    activation_function: str = "gelu"
+    attention_window_left: Optional[int] = None   # None: sliding_window - 1 (or unlimited)
+    attention_window_right: int = 0                # 0: causal; negative: frames also see what follows
     extra: Dict[str, Any] = field(default_factory=dict)
+
+    def __post_init__(self):
+        if self.norm_type not in ("rms_norm", "layer_norm"):
+            raise ValueError(f"norm_type must be 'rms_norm' or 'layer_norm', got {self.norm_type}")
+        if self.mlp_type not in ("swiglu", "gelu"):
+            raise ValueError(f"mlp_type must be 'swiglu' or 'gelu', got {self.mlp_type}")
+        if self.conv_padding not in ("causal", "symmetric"):
+            raise ValueError(f"conv_padding must be 'causal' or 'symmetric', got {self.conv_padding}")
+        if self.attention_window_left is None:
+            self.attention_window_left = (self.sliding_window - 1) if self.sliding_window else -1
+        if self.attention_window_right > 0:
+            raise NotImplementedError("a bounded look-ahead (attention_window_right > 0) is not built: use 0 (causal) or -1 (unlimited)")
 
     @classmethod
     def from_dict(cls, d):
@@ -405,11 +425,17 @@ class VoxtralRealtimeEncoderConfig:
 
 
 class _CausalConv1d(nn.Conv1d):
-    """Left-padded so that frame t never sees later frames (kernel 3: pad 2 at stride 1, pad 1 at stride 2)."""
+    """Left-padded so that frame t never sees later frames (kernel 3: pad 2 at stride 1, pad 1 at stride 2); with
+    ``symmetric = True`` the same total padding is split between both ends (the left half rounded down), which gives the
+    same number of frames and lets a chunk be encoded without its neighbours."""
+
+    symmetric = False
 
     def forward(self, x):
         k = (self.kernel_size[0] - 1) * self.dilation[0] + 1
-        return super().forward(F.pad(x, (k - self.stride[0], 0)))
+        total = k - self.stride[0]
+        left = total // 2 if self.symmetric else total
+        return super().forward(F.pad(x, (left, total - left)))
 
 
 class _VoxtralEmbedder(nn.Module):
@@ -417,6 +443,7 @@ class _VoxtralEmbedder(nn.Module):
         super().__init__()
         self.conv1 = _CausalConv1d(c.num_mel_bins, c.hidden_size, kernel_size=3)
         self.conv2 = _CausalConv1d(c.hidden_size, c.hidden_size, kernel_size=3, stride=2)
+        self.conv1.symmetric = self.conv2.symmetric = getattr(c, "conv_padding", "causal") == "symmetric"
 
 
 class _VoxtralAttention(nn.Module):
@@ -428,7 +455,12 @@ class _VoxtralAttention(nn.Module):
         self.k_proj = nn.Linear(d, self.heads * hd, bias=False)
         self.v_proj = nn.Linear(d, self.heads * hd, bias=True)
         self.o_proj = nn.Linear(self.heads * hd, d, bias=True)
-        self.window = (c.sliding_window - 1, -1) if c.sliding_window else (-1, -1)
+        left = getattr(c, "attention_window_left", None)
+        left = ((c.sliding_window - 1) if c.sliding_window else -1) if left is None else left
+        self.causal = getattr(c, "attention_window_right", 0) == 0
+        if not self.causal and left >= 0:
+            raise NotImplementedError("a left window without causality is not built: use attention_window_left = -1 with attention_window_right = -1")
+        self.window = (left, -1) if left >= 0 else (-1, -1)
 
     def forward(self, x, cu, cos, sin):
         from ..ops import rope as rope_ops
@@ -438,7 +470,7 @@ class _VoxtralAttention(nn.Module):
         b = torch.cat([self.q_proj.bias, torch.zeros_like(self.q_proj.bias), self.v_proj.bias], 0)
         qkv = gemm_ops.linear(x, w, b).view(P, 3, self.heads, self.head_dim)
         q, k = rope_ops.rope_apply(qkv[:, 0], cos, sin), rope_ops.rope_apply(qkv[:, 1], cos, sin)
-        o = attn_ops.varlen_attn(q, k, qkv[:, 2], cu, cu, causal=True, softmax_scale=self.head_dim ** -0.5, window_size=self.window)
+        o = attn_ops.varlen_attn(q, k, qkv[:, 2], cu, cu, causal=self.causal, softmax_scale=self.head_dim ** -0.5, window_size=self.window)
         return gemm_ops.linear(o.reshape(P, -1), self.o_proj.weight, self.o_proj.bias)
 
 
@@ -456,14 +488,35 @@ class _VoxtralMLP(nn.Module):
         return gemm_ops.linear(h, self.down_proj.weight, self.down_proj.bias)
 
 
+class _VoxtralGeluMLP(nn.Module):
+    """``fc2(act(fc1(x)))`` with biases: the ``mlp_type: gelu`` variant."""
+
+    def __init__(self, c):
+        super().__init__()
+        self.fc1 = nn.Linear(c.hidden_size, c.intermediate_size)
+        self.fc2 = nn.Linear(c.intermediate_size, c.hidden_size)
+        self.act = getattr(c, "activation_function", "gelu")
+
+    def forward(self, x):
+        h = gemm_ops.linear(x, self.fc1.weight, self.fc1.bias)
+        h = F.silu(h) if self.act in ("silu", "swish") else F.gelu(h, approximate="tanh" if "tanh" in self.act or self.act == "gelu_new" else "none")
+        return gemm_ops.linear(h, self.fc2.weight, self.fc2.bias)
+
+
+def _encoder_norm(c):
+    from .decoder_lm import RMSNorm
+
+    if getattr(c, "norm_type", "rms_norm") == "layer_norm":
+        return nn.LayerNorm(c.hidden_size, eps=c.rms_norm_eps)
+    return RMSNorm(c.hidden_size, c.rms_norm_eps)
+
+
 class VoxtralEncoderLayer(nn.Module):
     def __init__(self, c):
         super().__init__()
-        from .decoder_lm import RMSNorm
-
         self.self_attn = _VoxtralAttention(c)
-        self.self_attn_layer_norm, self.final_layer_norm = RMSNorm(c.hidden_size, c.rms_norm_eps), RMSNorm(c.hidden_size, c.rms_norm_eps)
-        self.mlp = _VoxtralMLP(c)
+        self.self_attn_layer_norm, self.final_layer_norm = _encoder_norm(c), _encoder_norm(c)
+        self.mlp = _VoxtralGeluMLP(c) if getattr(c, "mlp_type", "swiglu") == "gelu" else _VoxtralMLP(c)
 
     def forward(self, x, cu, cos, sin):
         x = x + self.self_attn(self.self_attn_layer_norm(x), cu, cos, sin)
@@ -486,7 +539,7 @@ class VoxtralRealtimeEncoder(nn.Module):
         self.config = c
         self.embedder = _VoxtralEmbedder(c)
         self.layers = nn.ModuleList([VoxtralEncoderLayer(c) for _ in range(c.num_hidden_layers)])
-        self.norm = RMSNorm(c.hidden_size, c.rms_norm_eps)
+        self.norm = _encoder_norm(c)
 
     def forward(self, input_features, feature_attention_mask=None, **kw):
         n, _, T = input_features.shape

@@ -856,3 +856,55 @@ def test_realtime_session_streams_slot_by_slot_like_the_full_pass():
                        audio_attention_mask=torch.ones(K, 2, dtype=torch.long))["hidden_states"]
         want = F.linear(hidden, model.language_model.lm_head.weight).argmax(-1)
     assert int(want[10]) == first and want[11:].tolist() == emitted
+
+
+def test_streaming_audio_encoder_variants_against_plain_torch():
+    """LayerNorm + GELU MLP + symmetric convolution padding + attention without causality: the encoder equals a direct
+    restatement with library ops; the default stays causal (a change in the last mel frame moves only the last frame)."""
+    from lmms_engine_b200.models.audio import VoxtralRealtimeEncoder, VoxtralRealtimeEncoderConfig
+
+    torch.manual_seed(0)
+    base = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2, head_dim=16, num_mel_bins=8, sliding_window=6)
+    c = VoxtralRealtimeEncoderConfig.from_dict(dict(base, norm_type="layer_norm", mlp_type="gelu", conv_padding="symmetric",
+                                                    attention_window_left=-1, attention_window_right=-1))
+    m = VoxtralRealtimeEncoder(c).eval()
+    with torch.no_grad():
+        for p in m.parameters():
+            p.normal_(0, 0.2)
+    x = torch.randn(2, 8, 12)
+    sd = m.state_dict()
+
+    def plain(feats):
+        h = F.gelu(F.conv1d(F.pad(feats, (1, 1)), sd["embedder.conv1.weight"], sd["embedder.conv1.bias"]))
+        h = F.gelu(F.conv1d(F.pad(h, (0, 1)), sd["embedder.conv2.weight"], sd["embedder.conv2.bias"], stride=2)).transpose(1, 2)  # [n, 6, 32]
+        n, T, _ = h.shape
+        inv = 1.0 / (10000.0 ** (torch.arange(0, 16, 2).float() / 16))
+        ang = torch.arange(T).float()[:, None] * inv[None]
+        cos, sin = torch.cat([ang.cos(), ang.cos()], -1), torch.cat([ang.sin(), ang.sin()], -1)
+        rot = lambda t: torch.cat([-t[..., 8:], t[..., :8]], -1)  # noqa: E731
+        for i in range(2):
+            pre = f"layers.{i}."
+            y = F.layer_norm(h, (32,), sd[pre + "self_attn_layer_norm.weight"], sd[pre + "self_attn_layer_norm.bias"], 1e-5)
+            q = F.linear(y, sd[pre + "self_attn.q_proj.weight"], sd[pre + "self_attn.q_proj.bias"]).view(n, T, 2, 16)
+            k = F.linear(y, sd[pre + "self_attn.k_proj.weight"]).view(n, T, 2, 16)
+            v = F.linear(y, sd[pre + "self_attn.v_proj.weight"], sd[pre + "self_attn.v_proj.bias"]).view(n, T, 2, 16)
+            q, k = q * cos[None, :, None] + rot(q) * sin[None, :, None], k * cos[None, :, None] + rot(k) * sin[None, :, None]
+            a = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)).transpose(1, 2).reshape(n, T, 32)
+            h = h + F.linear(a, sd[pre + "self_attn.o_proj.weight"], sd[pre + "self_attn.o_proj.bias"])
+            y = F.layer_norm(h, (32,), sd[pre + "final_layer_norm.weight"], sd[pre + "final_layer_norm.bias"], 1e-5)
+            h = h + F.linear(F.gelu(F.linear(y, sd[pre + "mlp.fc1.weight"], sd[pre + "mlp.fc1.bias"])), sd[pre + "mlp.fc2.weight"], sd[pre + "mlp.fc2.bias"])
+        return F.layer_norm(h, (32,), sd["norm.weight"], sd["norm.bias"], 1e-5).reshape(n * T, 32)
+
+    with torch.no_grad():
+        got = m(x)
+        assert got["frame_lengths"].tolist() == [6, 6]
+        assert (got["last_hidden_state"] - plain(x)).abs().max() < 2e-5
+        causal = VoxtralRealtimeEncoder(VoxtralRealtimeEncoderConfig.from_dict(base)).eval()
+        x2 = x.clone()
+        x2[:, :, -1] += 1.0
+        moved = (causal(x)["last_hidden_state"] - causal(x2)["last_hidden_state"]).abs().reshape(2, 6, -1).amax(-1) > 1e-6
+        assert moved.sum(1).tolist() == [1, 1] and moved[:, -1].all()
+    with pytest.raises(ValueError):
+        VoxtralRealtimeEncoderConfig.from_dict(dict(base, norm_type="batch_norm"))
+    with pytest.raises(NotImplementedError):
+        VoxtralRealtimeEncoderConfig.from_dict(dict(base, attention_window_right=2))
