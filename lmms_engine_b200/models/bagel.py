@@ -135,7 +135,8 @@ def split_attention(q, k, v, ctx: PackedContext, scale: float, layer_idx: int = 
         kk, vv = torch.cat([pk.to(k.dtype), k], 0), torch.cat([pv.to(v.dtype), v], 0)
         cu_q = torch.tensor([0, q.shape[0]], dtype=torch.int32, device=q.device)
         cu_k = torch.tensor([0, kk.shape[0]], dtype=torch.int32, device=q.device)
-        return attn_ops.varlen_attn(q, kk, vv, cu_q, cu_k, causal=False, softmax_scale=scale)
+        # an image block sees itself fully; appended text is causal inside itself (the kernel aligns the mask bottom-right)
+        return attn_ops.varlen_attn(q, kk, vv, cu_q, cu_k, causal=bool(getattr(ctx, "kv_prefix_causal", False)), softmax_scale=scale)
     plan = getattr(ctx, "split_plan", None)
     if plan is None:
         return attn_ops.varlen_attn(q, k, v, ctx.cu_seqlens, ctx.cu_seqlens, ctx.max_seqlen, ctx.max_seqlen, causal=True, softmax_scale=scale)
@@ -302,6 +303,16 @@ class _Connector(nn.Module):
         return gemm_ops.linear(h, self.fc2.weight, self.fc2.bias)
 
 
+class BagelContext:
+    """What has been said so far, as every layer's rotated keys and values, with the next rotary position."""
+
+    def __init__(self):
+        self.layers: Optional[List[Any]] = None
+        self.next_pos = 0
+        self.length = 0
+        self.last_hidden: Optional[torch.Tensor] = None
+
+
 class TaylorForecaster:
     """Skips decoder passes during sampling by extrapolating the predicted velocity over the step index.
 
@@ -415,13 +426,14 @@ class Bagel(DecoderLM):
             emb = emb.index_copy(0, latent_index, g)
         return emb, noise, target, t
 
-    def run_decoder(self, emb, pos, cu, gen_index, split_lens=None, attn_modes=None, kv_capture=None, kv_prefix=None):
+    def run_decoder(self, emb, pos, cu, gen_index, split_lens=None, attn_modes=None, kv_capture=None, kv_prefix=None,
+                    prefix_causal: bool = False):
         cos, sin = self.model.rope_tables(pos)
         ctx = PackedContext(cu, int(pos.shape[-1]), cos, sin, True)
         if kv_capture is not None:
             ctx.kv_capture = kv_capture
         if kv_prefix is not None:
-            ctx.kv_prefix = kv_prefix
+            ctx.kv_prefix, ctx.kv_prefix_causal = kv_prefix, prefix_causal
         T = emb.shape[0]
         if gen_index is not None and gen_index.numel() and self.config.gen_parts():
             mask = torch.zeros(T, dtype=torch.bool, device=emb.device)
@@ -501,6 +513,59 @@ class Bagel(DecoderLM):
         return dict(ids=ids, pos=pos, cu=torch.tensor([0, n + G + 2], dtype=torch.int32, device=dev), latent_index=torch.arange(n + 1, n + 1 + G, device=dev),
                     latent_pos=lat_pos, split_lens=[n, G + 2] if n else [G + 2], attn_modes=["causal", "full"] if n else ["full"])
 
+    # ---- a conversation kept as keys / values: text, understood images and condition images appended turn by turn ----
+    @torch.no_grad()
+    def extend_context(self, context: Optional["BagelContext"], emb, pos, gen_index=None, causal: bool = True):
+        """Append one chunk (already embedded) to ``context``: it attends to everything appended before and to itself
+        (``causal``: text; otherwise fully: an image block).  Returns the chunk's hidden states.  The role of the
+        reference's ``forward_cache_update_text / _vit / _vae`` (src/lmms_engine/models/bagel/bagel.py:396-700)."""
+        context = context if context is not None else BagelContext()
+        T = emb.shape[0]
+        cu = torch.tensor([0, T], dtype=torch.int32, device=emb.device)
+        captured: List[Any] = []
+        if context.layers is None:
+            hidden = self.run_decoder(emb, pos, cu, gen_index, [T], ["causal" if causal else "full"], kv_capture=captured)
+            context.layers = captured
+        else:
+            hidden = self.run_decoder(emb, pos, cu, gen_index, kv_capture=captured, kv_prefix=context.layers, prefix_causal=causal)
+            context.layers = [(torch.cat([pk, k], 0), torch.cat([pv, v], 0)) for (pk, pv), (k, v) in zip(context.layers, captured)]
+        if len(context.layers) != len(self.model.layers):
+            raise RuntimeError(f"{len(context.layers)} layers recorded their keys, the decoder has {len(self.model.layers)}")
+        context.length += T
+        context.last_hidden = hidden
+        return context
+
+    @torch.no_grad()
+    def add_text(self, context, ids: torch.Tensor):
+        context = context if context is not None else BagelContext()
+        n = ids.numel()
+        pos = torch.arange(context.next_pos, context.next_pos + n, device=ids.device)
+        context = self.extend_context(context, self.model.embed_tokens(ids.reshape(-1)), pos, None, causal=True)
+        context.next_pos += n
+        return context
+
+    @torch.no_grad()
+    def add_image(self, context, boi_id: int, eoi_id: int, latent_tokens=None, latent_pos=None, vit_tokens=None, vit_position_ids=None):
+        """Append one image block ``begin marker, image rows, end marker`` at ONE rotary position: ``vit_tokens`` (an image to
+        understand: packed SigLIP patches of that image) or ``latent_tokens`` (a clean condition image: autoencoder patches at
+        noise level 0, handled by the generation parameters)."""
+        context = context if context is not None else BagelContext()
+        dev = (latent_tokens if latent_tokens is not None else vit_tokens).device
+        rows = (latent_tokens if latent_tokens is not None else vit_tokens).shape[0]
+        ids = torch.tensor([boi_id] + [0] * rows + [eoi_id], device=dev)
+        inner = torch.arange(1, rows + 1, device=dev)
+        if latent_tokens is not None:
+            emb, _, _, _ = self.embed_stream(ids, latent_tokens, inner, latent_pos, torch.zeros(rows, device=dev), noise=torch.zeros_like(latent_tokens.float()))
+            gen = inner
+        else:
+            emb, _, _, _ = self.embed_stream(ids, vit_tokens=vit_tokens, vit_index=inner, vit_position_ids=vit_position_ids,
+                                             vit_seqlens=torch.tensor([rows], device=dev))
+            gen = None
+        pos = torch.full((rows + 2,), context.next_pos, device=dev)
+        context = self.extend_context(context, emb, pos, gen, causal=False)
+        context.next_pos += 1
+        return context
+
     @torch.no_grad()
     def cache_prompt(self, stream: Dict[str, Any]) -> Dict[str, Any]:
         """Run the prompt of ``stream`` once and keep every layer's rotated keys and values, so that the sampling steps
@@ -519,6 +584,12 @@ class Bagel(DecoderLM):
         block = dict(ids=stream["ids"][n:], pos=stream["pos"][n:], latent_index=stream["latent_index"] - n, latent_pos=stream["latent_pos"],
                      cu=torch.tensor([0, stream["ids"].numel() - n], dtype=torch.int32, device=emb.device))
         return dict(stream, prefix=captured, block=block)
+
+    def _block_after(self, context: "BagelContext", hw, boi_id: int, eoi_id: int, dev) -> Dict[str, Any]:
+        """The image block that follows ``context``, in the form ``flow_velocity`` runs against recorded keys / values."""
+        bare = self.image_stream(torch.zeros(0, dtype=torch.long, device=dev), hw, boi_id, eoi_id)
+        block = dict(ids=bare["ids"], pos=bare["pos"] + context.next_pos, latent_index=bare["latent_index"], latent_pos=bare["latent_pos"], cu=bare["cu"])
+        return dict(bare, prefix=context.layers, block=block)
 
     def flow_velocity(self, stream: Dict[str, Any], x_t: torch.Tensor, t: float, cached: bool = False) -> torch.Tensor:
         """Velocity prediction ``[G, C*p*p]`` for the noised latent patches ``x_t`` of ``stream`` at time ``t`` in (0, 1].
@@ -572,19 +643,28 @@ class Bagel(DecoderLM):
     def generate_image(self, prompt_ids, hw, boi_id: int, eoi_id: int, num_timesteps: int = 24, timestep_shift: Optional[float] = None,
                        noise_level: float = 0.7, sde_window=None, uncond_ids=None, cfg_text_scale: float = 1.0, cfg_interval=(0.0, 1.0),
                        cfg_renorm_min: float = 0.0, cfg_renorm_type: str = "global", generator=None, use_cache: bool = True,
-                       taylor: Optional[Dict[str, int]] = None) -> Dict[str, Any]:
+                       taylor: Optional[Dict[str, int]] = None, context: Optional["BagelContext"] = None,
+                       uncond_context: Optional["BagelContext"] = None) -> Dict[str, Any]:
         """Sample one image's latent patches from noise.  Steps inside ``sde_window = (first, count)`` (default: all) are
         stochastic and recorded - the state before the step, the state after it, its time and its log-probability - for
         the policy-gradient pass; the other steps are plain Euler steps of the flow.  ``use_cache``: run the prompt once
         and every step on the image block only (same result; the recorded streams stay complete for the learning pass).
         ``taylor`` (``{"interval", "max_order", "first_enhance"}``, any subset): forecast the velocity of the steps between
         computed ones (``TaylorForecaster``; approximate, meant for previews and evaluation, not for recorded rollouts)."""
-        dev = prompt_ids.device
-        stream = self.image_stream(prompt_ids, hw, boi_id, eoi_id)
-        un = self.image_stream(uncond_ids, hw, boi_id, eoi_id) if uncond_ids is not None else None
-        if use_cache:
-            stream = self.cache_prompt(stream)
-            un = self.cache_prompt(un) if un is not None else None
+        if context is not None:
+            # the image follows a conversation held as keys / values (``add_text`` / ``add_image``): the recorded streams
+            # are blocks only, so such a rollout cannot feed ``grpo_learn``
+            dev = context.layers[0][0].device
+            stream = self._block_after(context, hw, boi_id, eoi_id, dev)
+            un = self._block_after(uncond_context, hw, boi_id, eoi_id, dev) if uncond_context is not None else None
+            use_cache = True
+        else:
+            dev = prompt_ids.device
+            stream = self.image_stream(prompt_ids, hw, boi_id, eoi_id)
+            un = self.image_stream(uncond_ids, hw, boi_id, eoi_id) if uncond_ids is not None else None
+            if use_cache:
+                stream = self.cache_prompt(stream)
+                un = self.cache_prompt(un) if un is not None else None
         ts = self.flow_schedule(num_timesteps, dev, timestep_shift)
         pd = self.config.latent_channels * self.config.latent_patch_size ** 2
         x = torch.randn((int(hw[0]) * int(hw[1]), pd), device=dev, generator=generator)

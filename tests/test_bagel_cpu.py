@@ -244,3 +244,40 @@ def test_taylor_forecaster_schedule_and_expansion():
     assert float((fast["image_latent"] - plain["image_latent"]).abs().mean()) < 0.05 * scale
     every = model.generate_image(prompt, (2, 2), generator=torch.Generator().manual_seed(5), taylor={"interval": 1}, **kw)
     assert torch.equal(every["image_latent"], plain["image_latent"])
+
+
+def test_conversation_kept_as_keys_and_values_matches_the_packed_stream():
+    """Text, a clean condition image and more text appended turn by turn give the hidden states of one packed pass under
+    the split rules; an image sampled after that conversation equals the one sampled from the same stream as a prompt."""
+    from lmms_engine_b200.mapping_func import create_model_from_config
+    from lmms_engine_b200.models.bagel import BagelContext
+
+    torch.manual_seed(3)
+    model = create_model_from_config("bagel", dict(BASE, layer_module="Qwen2MoTDecoderLayer")).eval()
+    with torch.no_grad():
+        model.llm2vae.weight.normal_(0, 0.05)
+    t1, t2 = torch.randint(0, 100, (6,)), torch.randint(0, 100, (5,))
+    lat = torch.randn(4, 16)
+    side = model.config.max_latent_size
+    lat_pos = (torch.arange(2)[:, None] * side + torch.arange(2)[None]).flatten()
+    ctx = model.add_text(None, t1)
+    ctx = model.add_image(ctx, 101, 102, latent_tokens=lat, latent_pos=lat_pos)
+    ctx = model.add_text(ctx, t2)
+    assert isinstance(ctx, BagelContext) and ctx.length == 6 + 6 + 5 and ctx.next_pos == 6 + 1 + 5
+    ids = torch.cat([t1, torch.tensor([101, 0, 0, 0, 0, 102]), t2])
+    pos = torch.cat([torch.arange(6), torch.full((6,), 6), torch.arange(7, 12)])
+    with torch.no_grad():
+        emb, _, _, _ = model.embed_stream(ids, lat, torch.arange(7, 11), lat_pos, torch.zeros(4), noise=torch.zeros(4, 16))
+        cu = torch.tensor([0, 17], dtype=torch.int32)
+        full = model.run_decoder(emb, pos, cu, torch.arange(7, 11), [6, 6, 5], ["causal", "full", "causal"])
+    assert torch.allclose(ctx.last_hidden, full[12:], atol=2e-5), float((ctx.last_hidden - full[12:]).abs().max())
+    after = model.generate_image(None, (2, 2), boi_id=101, eoi_id=102, num_timesteps=4, noise_level=0.0, context=ctx,
+                                 generator=torch.Generator().manual_seed(9))
+    # the same conversation as a plain text prompt (no image in between) must differ, the same text-only context must not
+    text_ctx = model.add_text(None, torch.cat([t1, t2]))
+    a = model.generate_image(None, (2, 2), boi_id=101, eoi_id=102, num_timesteps=4, noise_level=0.0, context=text_ctx,
+                             generator=torch.Generator().manual_seed(9))
+    b = model.generate_image(torch.cat([t1, t2]), (2, 2), boi_id=101, eoi_id=102, num_timesteps=4, noise_level=0.0,
+                             generator=torch.Generator().manual_seed(9))
+    assert torch.allclose(a["image_latent"], b["image_latent"], atol=2e-5)
+    assert not torch.allclose(after["image_latent"], b["image_latent"], atol=1e-5)  # the condition image is seen
