@@ -14,6 +14,8 @@
 // (src/lmms_engine/utils/fsdp2_utils.py:250-289).
 #include "common.cuh"
 
+#include <cstdlib>
+
 namespace b200 {
 
 typedef __nv_bfloat16 bf16;
@@ -606,7 +608,14 @@ __global__ void sumsq_part_vec_kernel(const float4* __restrict__ g, float* __res
   if (threadIdx.x == 0) part[blockIdx.x] = acc;
 }
 
-static inline bool aligned_to(const void* p, uintptr_t a) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+// LMMS_B200_SCALAR_OPTIM=1 keeps the scalar passes (the A/B of profiles/optimizer_passes_microbench.md)
+static inline bool aligned_to(const void* p, uintptr_t a) {
+  static const bool scalar_only = [] {
+    const char* e = getenv("LMMS_B200_SCALAR_OPTIM");
+    return e != nullptr && e[0] == '1';
+  }();
+  return !scalar_only && (p == nullptr || (reinterpret_cast<uintptr_t>(p) % a) == 0);
+}
 
 // Deterministic two-stage sum of squares: part[blockIdx.x] then a single-CTA finish.
 template <typename GT>

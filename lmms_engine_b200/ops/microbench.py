@@ -84,6 +84,27 @@ def main():
                      "lib_tflops": fl / t2 / 1e9})
         print(rows[-1], flush=True)
         del a, b
+    if args.only == "optim":
+        # optimizer passes on one 18944 x 3584 fp32 matrix: the 16-byte kernels against the scalar ones (reached through
+        # views that start one element off a 16-byte boundary)
+        from . import optim
+
+        n = 18944 * 3584
+        for shift, name in ((0, "16-byte"), (1, "scalar")):
+            cut = lambda t: t[shift:shift + n]  # noqa: E731
+            g, mom, p = cut(torch.randn(n + 8, device=dev)), cut(torch.zeros(n + 8, device=dev)), cut(torch.randn(n + 8, device=dev))
+            out, p16 = cut(torch.empty(n + 8, device=dev, dtype=torch.bfloat16)), cut(torch.empty(n + 8, device=dev, dtype=torch.bfloat16))
+            m, v, ss = cut(torch.zeros(n + 8, device=dev)), cut(torch.zeros(n + 8, device=dev)), torch.zeros(1, device=dev)
+            res = {"op": f"optimizer passes, {name} kernels, {n} elements",
+                   "muon_momentum_scale_ms": timeit(lambda: optim.muon_momentum(mom, g, out, ss, beta=0.95, nesterov=True), iters=args.iters, flush=flush),
+                   "muon_update_ms": timeit(lambda: optim.muon_update(p, p16, out, lr=0.02, wd=0.1, scale=3.0), iters=args.iters, flush=flush),
+                   "sumsq_ms": timeit(lambda: optim.sumsq_(g, ss, False), iters=args.iters, flush=flush),
+                   "adamw_ms": timeit(lambda: optim.adamw_step(p, p16, m, v, g, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, step=1),
+                                      iters=args.iters, flush=flush)}
+            rows.append(res)
+            print(res, flush=True)
+        _cuda.check_status()
+        return
     if args.only and args.only != "attn":
         _cuda.check_status()
         return
