@@ -171,6 +171,8 @@ class VLModel(nn.Module):
     # ViT frame balancing over the flattened dp x cp ranks (set by the trainer / monkey_patch_kwargs)
     vit_frame_parallel = False
     vit_group = None
+    # under sequence parallelism every rank of a group runs the tower on its share of the sample's frames
+    sp_split_vit = True
 
     # the trainer toggles these on whatever model it gets
     @property
@@ -199,6 +201,10 @@ class VLModel(nn.Module):
             balanced = self.vit_frame_parallel and self.vit_group is not None
             if (pix is None or pix.numel() == 0) and not balanced:
                 continue
+            from ..parallel.sequence_parallel import ulysses as sp_mod
+
+            sp_n = sp_mod.group_size(self.language_model.sp_group)
+            split_sp = sp_n > 1 and self.sp_split_vit and not (cfg.is_rice or cfg.is_ov2)
             if balanced:
                 # every rank takes part in the exchange, also one whose batch has no frames of this kind
                 from ..parallel.vit_parallel import balanced_vit_forward
@@ -207,11 +213,19 @@ class VLModel(nn.Module):
                 if pix is None:
                     pix = emb.new_zeros((0, vc.in_channels * vc.temporal_patch_size * vc.patch_size ** 2))
                     grid = torch.zeros((0, 3), dtype=torch.long, device=emb.device)
-                out = balanced_vit_forward(self.visual, pix.to(emb.dtype), grid, self.vit_group)
-                if pix.shape[0] == 0:
-                    continue
+                run = lambda p_, g_: balanced_vit_forward(self.visual, p_, g_, self.vit_group)  # noqa: E731
             else:
-                out = self.visual(pix.to(emb.dtype), grid)
+                run = self.visual
+            if split_sp:
+                # the ranks of a sequence-parallel group hold the same sample: each runs the tower on its share of the
+                # frames (and only that share enters the balancing), the features are gathered back
+                from ..parallel.vit_parallel.frame_parallel import sp_sharded_vit_forward
+
+                out = sp_sharded_vit_forward(self.visual, pix.to(emb.dtype), grid, self.language_model.sp_group, run, always_run=balanced)
+            else:
+                out = run(pix.to(emb.dtype), grid)
+            if pix.shape[0] == 0:
+                continue
             feats, deep = out if isinstance(out, tuple) else (out, None)
             mask = ids == tok
             # the k-th placeholder takes the k-th feature row: prefix count, no host round trip

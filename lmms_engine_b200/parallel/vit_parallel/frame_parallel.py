@@ -71,3 +71,96 @@ def balanced_vit_forward(tower, patches: torch.Tensor, grid_thw: torch.Tensor, g
         deep = [go_home(d) for d in deep]
         return feats, deep
     return feats
+
+
+# ------------------------------------------------------------------ a sequence-parallel group shares one sample
+class _GatherRows(torch.autograd.Function):
+    """All-gather of row blocks of different heights (``counts[r]`` rows from rank r), rank after rank.  Backward sums
+    every rank's gradient of this rank's rows (reduce-scatter; an all-reduce on back ends without one)."""
+
+    @staticmethod
+    def forward(ctx, x, counts, group):
+        n, me = dist.get_world_size(group), dist.get_rank(group)
+        mx = max(max(counts), 1)
+        pad = x.new_zeros((mx,) + tuple(x.shape[1:]))
+        pad[: x.shape[0]] = x
+        out = x.new_empty((n * mx,) + tuple(x.shape[1:]))
+        dist.all_gather_into_tensor(out, pad.contiguous(), group=group)
+        ctx.meta = (list(counts), group, n, me, mx)
+        return torch.cat([out[r * mx: r * mx + counts[r]] for r in range(n)], 0)
+
+    @staticmethod
+    def backward(ctx, g):
+        counts, group, n, me, mx = ctx.meta
+        buf = g.new_zeros((n * mx,) + tuple(g.shape[1:]))
+        at = 0
+        for r in range(n):
+            buf[r * mx: r * mx + counts[r]] = g[at: at + counts[r]]
+            at += counts[r]
+        if dist.get_backend(group) == "nccl":
+            mine = g.new_empty((mx,) + tuple(g.shape[1:]))
+            dist.reduce_scatter_tensor(mine, buf, group=group)
+        else:
+            dist.all_reduce(buf, group=group)
+            mine = buf[me * mx: (me + 1) * mx]
+        return mine[: counts[me]], None, None
+
+
+def deal_frames(sizes: List[int], n: int) -> List[int]:
+    """Owner rank of every frame: largest first onto the least loaded rank (ties: lowest rank), the same on every rank."""
+    load, owner = [0] * n, [0] * len(sizes)
+    for i in sorted(range(len(sizes)), key=lambda j: (-sizes[j], j)):
+        r = min(range(n), key=lambda q: (load[q], q))
+        owner[i] = r
+        load[r] += sizes[i]
+    return owner
+
+
+def sp_sharded_vit_forward(tower, patches: torch.Tensor, grid_thw: torch.Tensor, sp_group, run=None, always_run: bool = False):
+    """The ranks of a sequence-parallel group hold the SAME sample, so running the tower on every rank repeats the work
+    ``sp`` times and keeps ``sp`` copies of its activations.  Here every rank runs the tower on its share of the frames
+    (dealt by size) and the merged features are all-gathered back into frame order; the gather's backward sums the
+    ranks' gradients of a frame's features, which the owner back-propagates.  ``run(patches, grid)`` replaces the plain
+    tower call (the frame balancing across the data-parallel ranks, with ``always_run``).  The reference splits the deepstack features
+    per sequence-parallel rank but runs its tower on every rank (src/lmms_engine/models/qwen3_vl/qwen3_vl_ops.py:47-142)."""
+    n, me = dist.get_world_size(sp_group), dist.get_rank(sp_group)
+    run = run if run is not None else tower
+    frames = [(1, int(h), int(w)) for t, h, w in grid_thw.tolist() for _ in range(int(t))]
+    sizes = [h * w for _, h, w in frames]
+    owner = deal_frames(sizes, n)
+    starts = [0]
+    for c in sizes:
+        starts.append(starts[-1] + c)
+    mine = [i for i in range(len(frames)) if owner[i] == me]
+    unit = tower.cfg.spatial_merge_size ** 2
+    n_deep = len(getattr(tower, "deepstack_merger_list", []) or [])
+    if mine or always_run:  # ``always_run``: ``run`` holds collectives of its own that every rank must enter
+        rows = (torch.cat([torch.arange(starts[i], starts[i + 1]) for i in mine]) if mine else torch.zeros(0, dtype=torch.long)).to(patches.device)
+        sub_grid = torch.tensor([frames[i] for i in mine], dtype=torch.long, device=patches.device).reshape(-1, 3)
+        out = run(patches.index_select(0, rows), sub_grid)
+        feats, deep = out if isinstance(out, tuple) else (out, None)
+    else:
+        if any(hasattr(p, "to_local") for p in tower.parameters()):
+            raise RuntimeError("a sequence-parallel rank received no frame while the tower's parameters are sharded (FSDP2): "
+                               "a sharded tower must run on every rank")
+        feats = patches.new_zeros((0, tower.cfg.out_hidden_size)) + 0.0 * sum(p.sum() for p in tower.parameters() if p.requires_grad).to(patches.dtype)
+        deep = [feats for _ in range(n_deep)] if n_deep else None
+    counts = [sum(sizes[i] for i in range(len(frames)) if owner[i] == r) // unit for r in range(n)]
+    # rank-major order of the gathered rows -> frame order
+    merged = [c // unit for c in sizes]
+    at, where = 0, [0] * len(frames)
+    for r in range(n):
+        for i in range(len(frames)):
+            if owner[i] == r:
+                where[i] = at
+                at += merged[i]
+    back = torch.cat([torch.arange(where[i], where[i] + merged[i]) for i in range(len(frames))]).to(patches.device) if frames else None
+
+    def home(t):
+        full = _GatherRows.apply(t, counts, sp_group)
+        return full.index_select(0, back) if back is not None else full
+
+    feats = home(feats)
+    if deep is not None:
+        return feats, [home(d) for d in deep]
+    return feats

@@ -43,6 +43,19 @@ def vl_deepstack(mode):
     loss = model(**batch)["loss"]
     loss.backward()
     assert abs(float(loss) - float(ref)) < 1e-4, (mode, float(loss), float(ref))
+    if mode == "vl_ulysses":
+        # every rank ran the tower on its share of the images (two images, two ranks); the mean of the ranks' gradients
+        # (what the data-parallel reduction computes) is the full model's gradient, for the tower and for the decoder
+        ref.backward()
+        for (name, p), (_, q) in zip(model.named_parameters(), full.named_parameters()):
+            g = (p.grad if p.grad is not None else torch.zeros_like(p)).clone()
+            dist.all_reduce(g)
+            g /= world
+            want = q.grad if q.grad is not None else torch.zeros_like(q)
+            assert (g - want).abs().max() < 2e-4 * max(1.0, float(want.abs().max())), (name, float((g - want).abs().max()))
+        model.sp_split_vit = False  # every rank runs the whole tower: same loss
+        again = model(**batch)["loss"]
+        assert abs(float(again) - float(ref)) < 1e-4
     if rank == 0:
         print(f"{mode} ok")
     dist.destroy_process_group()

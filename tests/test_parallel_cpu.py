@@ -81,6 +81,12 @@ def test_deepstack_features_follow_the_split_token_stream(mode):
     assert f"{mode} ok" in torchrun("tp_run.py", 2, mode)
 
 
+def test_vision_tower_is_shared_out_over_a_sequence_parallel_group():
+    """Four ranks, two images: two ranks run the tower on one image each, two on nothing; features are gathered back and the
+    mean of the ranks' gradients is the full model's gradient."""
+    assert "vl_ulysses ok" in torchrun("tp_run.py", 4, "vl_ulysses")
+
+
 def test_ulysses_hybrid_linear_attention_matches_unsharded():
     """Qwen3.5 layers under Ulysses: the linear-attention heads (convolution + delta rule) and the gated-attention heads
     are exchanged around their sequence-wide parts; loss and gradients equal the single-process model."""
