@@ -259,6 +259,35 @@ __global__ void moe_combine_bwd_w_kernel(const bf16* __restrict__ dout, const bf
   }
 }
 
+// The expert side of the combine's backward on rows that are already in place (expert parallelism: the gradient rows
+// arrived in the staging area together with their router weight):
+//   d_y[r, :] = w[r] * g[r, :]      dot[r] = <g[r, :], y[r, :]>      (one warp per row, one pass over g and y)
+__global__ void moe_row_scale_dot_kernel(const bf16* __restrict__ g, long ldg, const bf16* __restrict__ y,
+                                         const float* __restrict__ w, bf16* __restrict__ d_y, float* __restrict__ dot,
+                                         long rows, int H) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  for (long r = blockIdx.x * static_cast<long>(wpb) + (threadIdx.x >> 5); r < rows;
+       r += static_cast<long>(gridDim.x) * wpb) {
+    const float wt = w[r];
+    float acc = 0.f;
+    for (int c = lane * 8; c < H; c += 256) {
+      const V8 a = *reinterpret_cast<const V8*>(g + r * ldg + c);
+      const V8 b = *reinterpret_cast<const V8*>(y + r * static_cast<long>(H) + c);
+      V8 o;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 fa = unpack_bf16x2(a.w[q]), fb = unpack_bf16x2(b.w[q]);
+        acc += fa.x * fb.x + fa.y * fb.y;
+        o.w[q] = pack_bf16x2(wt * fa.x, wt * fa.y);
+      }
+      *reinterpret_cast<V8*>(d_y + r * static_cast<long>(H) + c) = o;
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) dot[r] = acc;
+  }
+}
+
 // SwiGLU on the concatenated layout gu[rows, 2I] = [gate | up]:
 // forward h = silu(g) * u; backward overwrites gu with [dg | du] given dh.
 __global__ void swiglu_cat_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict__ h, long rows, int I) {
@@ -389,6 +418,14 @@ int b200_moe_combine_bwd_w(const void* dout, const void* src, const void* row_of
   moe_combine_bwd_w_kernel<<<grid_for(pairs * 32, 256), 256, 0, st>>>((const bf16*)dout, (const bf16*)src,
                                                                       (const int*)row_of, (float*)dw, pairs, k, H, n_src,
                                                                       (int*)status);
+  return CHECK_LAUNCH();
+}
+int b200_moe_row_scale_dot(const void* g, long ldg, const void* y, const void* w, void* d_y, void* dot, long rows, int H,
+                           cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (H % 8 || ldg % 8) return -10;
+  moe_row_scale_dot_kernel<<<grid_for(rows * 32, 256), 256, 0, st>>>((const bf16*)g, ldg, (const bf16*)y, (const float*)w,
+                                                                     (bf16*)d_y, (float*)dot, rows, H);
   return CHECK_LAUNCH();
 }
 int b200_swiglu_cat_fwd(const void* gu, void* h, long rows, int I, cudaStream_t st) {

@@ -48,7 +48,26 @@ class MoEConfig(DecoderConfig):
         return i not in self.mlp_only_layers and self.num_experts > 0 and (i + 1) % self.decoder_sparse_step == 0
 
 
+class _ScaleGrad(torch.autograd.Function):
+    """Identity whose backward multiplies the gradient by ``factor``."""
+
+    @staticmethod
+    def forward(ctx, x, factor):
+        ctx.factor = factor
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g * ctx.factor, None
+
+
 class Experts(nn.Module):
+    # set by the expert-parallel plan when the experts are NOT wrapped by a sharding wrapper (every expert lives on exactly
+    # one rank): the dtype the grouped products run in (the parameters stay fp32 masters) and the factor that turns the
+    # sum of the ranks' loss gradients, which the token exchange produces, into the gradient of their mean
+    compute_dtype = None
+    grad_scale = 1.0
+
     def __init__(self, n: int, hidden: int, inter: int):
         super().__init__()
         self.gate_up_proj = nn.Parameter(torch.empty(n, 2 * inter, hidden))
@@ -62,6 +81,10 @@ class Experts(nn.Module):
         gate_up, down = self.gate_up_proj, self.down_proj
         if hasattr(gate_up, "to_local"):
             gate_up, down = gate_up.to_local(), down.to_local()
+        if self.grad_scale != 1.0 and torch.is_grad_enabled():
+            gate_up, down = _ScaleGrad.apply(gate_up, self.grad_scale), _ScaleGrad.apply(down, self.grad_scale)
+        if self.compute_dtype is not None and gate_up.dtype != self.compute_dtype:
+            gate_up, down = gate_up.to(self.compute_dtype), down.to(self.compute_dtype)
         if xp.shape[0] > 0:
             return moe_ops.grouped_mlp(xp, gate_up, down, perm)
         # no rows for this rank's experts in this step: keep the parameters in the graph (their gradient hooks and

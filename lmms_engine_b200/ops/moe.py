@@ -30,6 +30,7 @@ _cuda.register("b200_moe_debug_bad_index", "moe", "")
 _cuda.register("b200_moe_combine", "moe", "ppppiii" + "lps")
 _cuda.register("b200_moe_combine_bwd_src", "moe", "pppplilps")
 _cuda.register("b200_moe_combine_bwd_w", "moe", "pppplii" + "lps")
+_cuda.register("b200_moe_row_scale_dot", "moe", "plpppplis")
 _cuda.register("b200_swiglu_cat_fwd", "moe", "pplis")
 _cuda.register("b200_swiglu_cat_bwd", "moe", "pplis")
 _cuda.register("b200_gemm_grouped_bf16", "gemm_sm100", "ppppiiiiiiips")
@@ -301,3 +302,17 @@ def load_balancing_loss(probs: torch.Tensor, counts: torch.Tensor, k: int) -> to
     T, E = probs.shape
     f = counts.to(torch.float32) / max(T, 1)
     return E * (f * probs.mean(0)).sum()
+
+
+def row_scale_dot(g: torch.Tensor, y: torch.Tensor, w: torch.Tensor, dot_out: torch.Tensor) -> torch.Tensor:
+    """``d_y = w[:, None] * g`` (in ``y``'s dtype) and ``dot_out[r] = <g[r], y[r]>`` in one pass over ``g`` and ``y``: the
+    expert side of the combine's backward when the gradient rows already sit next to their router weights."""
+    rows, H = y.shape
+    if g.is_cuda and g.dtype == torch.bfloat16 and y.dtype == torch.bfloat16 and H % 8 == 0 and g.stride(1) == 1 and g.stride(0) % 8 == 0:
+        d_y = torch.empty_like(y)
+        _cuda.call("b200_moe_row_scale_dot", g.data_ptr(), g.stride(0), y.contiguous().data_ptr(), w.data_ptr(), d_y.data_ptr(),
+                   dot_out.data_ptr(), rows, H, _cuda.stream())
+        return d_y
+    gf = g.float()
+    dot_out.copy_((gf * y.float()).sum(1))
+    return (gf * w.unsqueeze(1)).to(y.dtype)

@@ -249,7 +249,6 @@ class _PeerCombine(torch.autograd.Function):
         ep.push(dout.contiguous(), perm, dest_rank, dest_row, scalar=perm.weight_of_row)
         g = ep.x_stage.t[:rows]
         wrow = ep.x_stage.s[:rows]
-        d_yp = (g.float() * wrow.unsqueeze(1)).to(yp.dtype)
-        ep.y_stage.s[:rows].copy_((g.float() * yp.float()).sum(1))
+        d_yp = moe_ops.row_scale_dot(g, yp, wrow, ep.y_stage.s[:rows])
         dw = ep.pull_scalar(ep.y_stage, perm.row_of, dest_rank, dest_row).to(w.dtype)
         return d_yp, dw, None, None, None, None

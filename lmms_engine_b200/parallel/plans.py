@@ -86,12 +86,23 @@ def parallelize_moe(model, args, dtype=None, **_):
             tower = getattr(model, attr, None)
             if tower is not None and any(p.requires_grad for p in tower.parameters()):
                 fully_shard(tower, **_fsdp_kwargs(args, fsdp_mesh, mp))
+    expert_mesh = pgm.device_mesh["dp_shard_mod_ep"] if pgm.enable_ep else None
+    # the token exchange hands an expert the tokens of every data-parallel rank, so its gradient is the SUM of the ranks'
+    # loss gradients while every other parameter gets their mean: bring the experts to the same scale (the global norm
+    # clip compares them).  The reference leaves the sum (src/lmms_engine/parallel/qwen3_moe/parallelize.py).
+    dp_ranks = float(fsdp_mesh.size())
     for layer in text.model.layers:
         if isinstance(layer.mlp, SparseMoeBlock) and pgm.enable_ep:
-            # also when the experts are purely expert-parallel (a mesh of one rank): the wrap is what gives them the
-            # fp32 master / bf16 compute split of the mixed-precision policy
-            fully_shard(layer.mlp.experts, shard_placement_fn=lambda p: Shard(1),
-                        **_fsdp_kwargs(args, pgm.device_mesh["dp_shard_mod_ep"], mp))
+            if expert_mesh.size() > 1:
+                fully_shard(layer.mlp.experts, shard_placement_fn=lambda p: Shard(1), **_fsdp_kwargs(args, expert_mesh, mp))
+                # the wrapper averages over its own mesh; the rest of the factor is applied in the experts' forward
+                layer.mlp.experts.grad_scale = float(expert_mesh.size()) / dp_ranks
+            else:
+                # every expert lives on exactly one rank: a sharding wrapper over a mesh of one rank would only add its
+                # copies, casts and gradient passes per layer (about 40 % of the step of the 30B-A3B configuration).
+                # The parameters stay fp32 masters; the grouped products run in the compute dtype.
+                layer.mlp.experts.compute_dtype = dtype
+                layer.mlp.experts.grad_scale = 1.0 / dp_ranks
         for mixer_name in ("self_attn", "linear_attn"):  # hybrid decoders have one or the other per layer
             mixer = getattr(layer, mixer_name, None)
             if mixer is not None:

@@ -77,6 +77,23 @@ def main():
         assert abs(float(loss) - float(ref)) < 2e-4, (family, float(loss), float(ref))
         grads = [p.grad for p in model.parameters() if p.grad is not None]
         assert len(grads) > 10, family
+        # the gradient of the MEAN of the ranks' losses, for expert and non-expert parameters alike
+        ref.backward()
+        want = {}
+        for name, q in full.named_parameters():
+            gq = (q.grad if q.grad is not None else torch.zeros_like(q)).clone()
+            dist.all_reduce(gq)
+            want[name] = gq / world
+        checked = 0
+        for name, p in model.named_parameters():
+            if "experts." not in name or p.grad is None:
+                continue
+            got = p.grad.full_tensor() if hasattr(p.grad, "full_tensor") else p.grad
+            assert got.shape == want[name].shape, (family, name, got.shape, want[name].shape)
+            err = float((got - want[name]).abs().max())
+            assert err < 2e-4 * max(1.0, float(want[name].abs().max())), (family, name, err)
+            checked += 1
+        assert checked >= 2, family
         done.append(family)
     # bf16 policy: FSDP must hand the step's context to every wrapped block untouched (fp32 rotary tables, ONE aux list)
     torch.manual_seed(0)
