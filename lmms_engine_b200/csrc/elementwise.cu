@@ -299,6 +299,72 @@ __global__ void norm_bwd_warp_kernel(const bf16* __restrict__ dy, const bf16* __
   }
 }
 
+// RMSNorm backward for narrow rows (per-head norms: H = 64 / 128 / 256): LPR = H / 8 lanes hold a row, a warp works on
+// 32 / LPR rows at once, a block of sixteen warps leaves ONE row of dw partials (summed over its warps in shared memory),
+// so the grid can fill the machine within the same partials scratch.
+template <int LPR>
+__global__ void norm_bwd_narrow_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                       const float* __restrict__ rstd_in, bf16* __restrict__ dx,
+                                       float* __restrict__ dw_part, int rows, float w_offset) {
+  constexpr int H = LPR * 8;
+  constexpr int RPW = 32 / LPR;  // rows per warp and iteration
+  __shared__ float red[16][H];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane / LPR, col = (lane % LPR) * 8;
+  const int wpb = blockDim.x >> 5;
+  float wv[8], dw[8];
+  load8(w + col, wv);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    wv[j] += w_offset;
+    dw[j] = 0.f;
+  }
+  for (long row0 = (static_cast<long>(blockIdx.x) * wpb + warp) * RPW; row0 < rows;
+       row0 += static_cast<long>(gridDim.x) * wpb * RPW) {
+    const long row = row0 + sub;
+    const bool live = row < rows;
+    float dyv[8], xv[8], g[8], xh[8];
+    float dot = 0.f, rstd = 0.f;
+    if (live) {
+      const size_t base = static_cast<size_t>(row) * H + col;
+      rstd = rstd_in[row];
+      load8(dy + base, dyv);
+      load8(x + base, xv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        xh[j] = xv[j] * rstd;
+        g[j] = dyv[j] * wv[j];
+        dw[j] += dyv[j] * xh[j];
+        dot += g[j] * xh[j];
+      }
+    }
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    dot /= H;
+    if (live) {
+      float o8[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o8[j] = rstd * (g[j] - xh[j] * dot);
+      store8(dx + static_cast<size_t>(row) * H + col, o8);
+    }
+  }
+  // lanes that hold the same columns (one per row of the warp's group), then the block's warps
+#pragma unroll
+  for (int o = LPR; o < 32; o <<= 1)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw[j] += __shfl_xor_sync(0xffffffffu, dw[j], o);
+  if (sub == 0) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) red[warp][col + j] = dw[j];
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float acc = 0.f;
+    for (int q = 0; q < wpb; ++q) acc += red[q][c];
+    dw_part[static_cast<size_t>(blockIdx.x) * H + c] = acc;
+  }
+}
+
 // out[c] = sum_p part[p, c]  (fp32 -> fp32, optionally accumulating into out)
 __global__ void colsum_kernel(const float* __restrict__ part, float* __restrict__ out, int parts, int H,
                               int accumulate) {
@@ -823,6 +889,24 @@ int b200_norm_bwd(const void* dy, const void* x, const void* w, const void* rstd
   if (H % 8) return -10;
   int parts;
   if (H <= 512 && !ln && dres_in == nullptr) {
+    if (H == 64 || H == 128 || H == 256) {
+      const int lpr = H / 8, rows_per_block = 16 * (32 / lpr);
+      long want = (static_cast<long>(rows) + rows_per_block - 1) / rows_per_block;
+      parts = static_cast<int>(want < num_sms() * 2 ? want : num_sms() * 2);  // one partials row per block
+      if (parts < 1) parts = 1;
+      if (H == 64)
+        norm_bwd_narrow_kernel<8><<<parts, 512, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)rstd,
+                                                         (bf16*)dx, (float*)dw_part, rows, w_offset);
+      else if (H == 128)
+        norm_bwd_narrow_kernel<16><<<parts, 512, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)rstd,
+                                                          (bf16*)dx, (float*)dw_part, rows, w_offset);
+      else
+        norm_bwd_narrow_kernel<32><<<parts, 512, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)rstd,
+                                                          (bf16*)dx, (float*)dw_part, rows, w_offset);
+      if (cudaGetLastError() != cudaSuccess) return -4;
+      colsum_kernel<<<(H + 255) / 256, 256, 0, st>>>((const float*)dw_part, (float*)dw, parts, H, accumulate);
+      return CHECK_LAUNCH();
+    }
     int blocks = num_sms() * 2 / 8;
     if (blocks < 1) blocks = 1;
     parts = blocks * 8;

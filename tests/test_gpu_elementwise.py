@@ -13,7 +13,7 @@ def _close(a, b, atol=2e-2, rtol=2e-2):
     assert torch.allclose(a.float(), b.float(), atol=atol, rtol=rtol), (a.float() - b.float()).abs().max().item()
 
 
-@pytest.mark.parametrize("rows,H", [(37, 256), (513, 1024), (300, 3584), (64, 4096), (9, 8192), (1000, 128)])
+@pytest.mark.parametrize("rows,H", [(37, 256), (513, 1024), (300, 3584), (64, 4096), (9, 8192), (1000, 128), (70001, 128), (333, 64), (5003, 256)])
 def test_rmsnorm_fwd_bwd(rows, H):
     from lmms_engine_b200.ops import norm
 
