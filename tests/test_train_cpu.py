@@ -206,3 +206,25 @@ def test_hsdp_matches_plain_sharding_and_merges(tmp_path):
     assert m1.keys() == m2.keys()
     for k in m1:
         assert torch.allclose(m1[k].float(), m2[k].float(), atol=2e-3), k
+
+
+def test_expert_parallel_training_matches_plain_sharding_and_merges(tmp_path):
+    """Two ranks, tiny MoE decoder: experts split over the ranks (each expert on one rank, no sharding wrapper around them)
+    train like the plainly sharded model - the experts' gradients are those of the mean loss - and the checkpoint
+    consolidates to the same full-size weights."""
+    from lmms_engine_b200.merger.fsdp2 import FSDP2Merger
+    from lmms_engine_b200.models import hf_io
+
+    save = {"save_strategy": "steps", "save_steps": 4, "max_grad_norm": 1.0}
+    plain = run_tiny(tmp_path / "plain", nproc=2, steps=4, model="moe", runtime="torch_fsdp2", extra=save)
+    ep = run_tiny(tmp_path / "ep", nproc=2, steps=4, model="moe", extra={"ep_degree": 2, **save})
+    for a, b in zip(plain["loss"], ep["loss"]):
+        assert abs(a - b) < 2e-3, (plain["loss"], ep["loss"])
+    for a, b in zip(plain["grad_norm"], ep["grad_norm"]):
+        assert abs(a - b) < 2e-2 * max(1.0, a), (plain["grad_norm"], ep["grad_norm"])
+    m1 = hf_io.read_state_dict(str(FSDP2Merger(str(tmp_path / "plain" / "checkpoint-4")).merge()))
+    m2 = hf_io.read_state_dict(str(FSDP2Merger(str(tmp_path / "ep" / "checkpoint-4")).merge()))
+    assert m1.keys() == m2.keys() and any("experts" in k for k in m1)
+    for k in m1:
+        assert m1[k].shape == m2[k].shape, k
+        assert torch.allclose(m1[k].float(), m2[k].float(), atol=5e-3), (k, float((m1[k].float() - m2[k].float()).abs().max()))
