@@ -196,7 +196,6 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   } else if (warp == 1) {
     if (lane == 0 && n_iter > 0) {
       const uint32_t idesc_s = umma_idesc_bf16(kKeys, kTile);                    // M = keys, N = q, K = d
-      const uint32_t idesc_acc = umma_idesc_bf16_major(kKeys, DP, 0, 1);          // M = keys, N = d, K = q
       const uint32_t sK = smem_u32(smem + Smem::kA0), sV = smem_u32(smem + Smem::kA1);
       bool ok = mbar_wait(kv_full, 0, abort_word);
       auto issue_scores = [&](int it) -> bool {
@@ -221,9 +220,20 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         umma_commit(&s_full[s]);
         return true;
       };
-      if (ok) ok = issue_scores(0);
+      // the score products of tile it reuse the TMEM buffers of tile it - 2: wait until the softmax warps have read them
       for (int it = 0; it < n_iter && ok; ++it) {
-        if (it + 1 < n_iter && !issue_scores(it + 1)) { ok = false; break; }
+        if (it >= 2 && !mbar_wait(&ds_full[it & 1], ((it - 2) >> 1) & 1, abort_word)) { ok = false; break; }
+        if (!issue_scores(it)) { ok = false; break; }
+      }
+    }
+  } else if (warp == 3) {
+    // A second issuing thread for the accumulating products: a thread blocks while it issues and pays every commit,
+    // fence and barrier hand-off in sequence, so one thread for both kinds left the tensor pipe idle for about a
+    // third of a tile's time.
+    if (lane == 0 && n_iter > 0) {
+      const uint32_t idesc_acc = umma_idesc_bf16_major(kKeys, DP, 0, 1);          // M = keys, N = d, K = q
+      bool ok = true;
+      for (int it = 0; it < n_iter && ok; ++it) {
         const int s = it & 1;
         const uint32_t ph = (it >> 1) & 1;
         if (!mbar_wait(&ds_full[s], ph, abort_word)) { ok = false; break; }
@@ -408,7 +418,8 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   uint64_t* ds_full = bars + 3 + 2 * S;      // 2
   uint64_t* ds_free = bars + 5 + 2 * S;      // 2
   uint64_t* all_done = bars + 7 + 2 * S;     // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8 + 2 * S);
+  uint64_t* a_ready = bars + 8 + 2 * S;      // 1   Q and dO sit in TMEM (written by the eight softmax warps)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9 + 2 * S);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* work = reinterpret_cast<int*>(tmem_slot + 2);
 
@@ -431,6 +442,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       mbar_init(&ds_free[i], 1);
     }
     mbar_init(all_done, 1);
+    mbar_init(a_ready, 8);
     *abort_word = 0;
     fence_barrier_init();
   }
@@ -447,6 +459,11 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const uint32_t tm_S = tmem_base;          // 2 x 64
   const uint32_t tm_dP = tmem_base + 128;   // 2 x 64
   const uint32_t tm_dQ = tmem_base + 256;   // 128
+  // The A operands of the score products, Q and dO, are the same for every key tile.  From shared memory an
+  // M = 128, K = 16 instruction pays about 64 cycles for its 4 KB A slice whatever its N, which halves the rate of the
+  // 64-column score products; from TMEM (two bf16 per 32-bit column, row m in lane m) it does not.
+  const uint32_t tm_Q = tmem_base + 384;    // 64 columns: Q  [128 rows x 128 d] as bf16 pairs
+  const uint32_t tm_dO = tmem_base + 448;   // 64 columns: dO
 
   const int q0 = work[1], len_q = work[2], len_k = work[3], q_start = work[4], k_start = work[5];
   const int head = blockIdx.y;
@@ -488,9 +505,9 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   } else if (warp == 1) {
     if (lane == 0 && n_iter > 0) {
       const uint32_t idesc_s = umma_idesc_bf16(kKeys, kTile);                 // M = q, N = keys, K = d
-      const uint32_t idesc_dq = umma_idesc_bf16_major(kKeys, DP, 0, 1);        // M = q, N = d, K = keys
       const uint32_t sQ = smem_u32(smem + Smem::kA0), sdO = smem_u32(smem + Smem::kA1);
-      bool ok = mbar_wait(q_full, 0, abort_word);
+      bool ok = mbar_wait(a_ready, 0, abort_word);
+      tc_fence_after();
       auto issue_scores = [&](int it) -> bool {
         const int s = it & 1;            // TMEM buffer of the scores
         const int stg = it % S;          // shared-memory stage of K_j / V_j
@@ -500,22 +517,28 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const uint32_t sV = sK + Smem::kSmall;
 #pragma unroll
         for (int kk = 0; kk < DP / 16; ++kk) {
-          const uint32_t offA = (kk / 4) * (kKeys * 128) + (kk % 4) * 32;
           const uint32_t offB = (kk / 4) * (kTile * 128) + (kk % 4) * 32;
-          umma_bf16_ss(tm_S + s * 64, umma_desc_sw128(sQ + offA), umma_desc_sw128(sK + offB), idesc_s, kk != 0);
+          umma_bf16_ts(tm_S + s * 64, tm_Q + kk * 8, umma_desc_sw128(sK + offB), idesc_s, kk != 0);
         }
 #pragma unroll
         for (int kk = 0; kk < DP / 16; ++kk) {
-          const uint32_t offA = (kk / 4) * (kKeys * 128) + (kk % 4) * 32;
           const uint32_t offB = (kk / 4) * (kTile * 128) + (kk % 4) * 32;
-          umma_bf16_ss(tm_dP + s * 64, umma_desc_sw128(sdO + offA), umma_desc_sw128(sV + offB), idesc_s, kk != 0);
+          umma_bf16_ts(tm_dP + s * 64, tm_dO + kk * 8, umma_desc_sw128(sV + offB), idesc_s, kk != 0);
         }
         umma_commit(&s_full[s]);
         return true;
       };
-      if (ok) ok = issue_scores(0);
       for (int it = 0; it < n_iter && ok; ++it) {
-        if (it + 1 < n_iter && !issue_scores(it + 1)) { ok = false; break; }
+        if (it >= 2 && !mbar_wait(&ds_full[it & 1], ((it - 2) >> 1) & 1, abort_word)) { ok = false; break; }
+        if (!issue_scores(it)) { ok = false; break; }
+      }
+    }
+  } else if (warp == 3) {
+    // second issuing thread: the dQ products (see the dK / dV kernel)
+    if (lane == 0 && n_iter > 0) {
+      const uint32_t idesc_dq = umma_idesc_bf16_major(kKeys, DP, 0, 1);        // M = q, N = d, K = keys
+      bool ok = true;
+      for (int it = 0; it < n_iter && ok; ++it) {
         const int s = it & 1;
         const uint32_t ph = (it >> 1) & 1;
         if (!mbar_wait(&ds_full[s], ph, abort_word)) { ok = false; break; }
@@ -541,6 +564,32 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const int qi = q0 + r;
     const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
     const bool row_valid = qi < len_q;
+    // ---- Q (warps 4-7) and dO (warps 8-11) from shared memory (128-byte swizzle) into TMEM, one row per thread ----
+    if (n_iter > 0) {
+      bool okq = mbar_wait(q_full, 0, abort_word);
+      if (okq) {
+        const uint8_t* src = smem + (half == 0 ? Smem::kA0 : Smem::kA1);
+        const uint32_t dst = (half == 0 ? tm_Q : tm_dO) + lane_sel;
+#pragma unroll
+        for (int c64 = 0; c64 < DP / 64; ++c64) {       // two 64-column (128-byte) chunks of the row
+#pragma unroll
+          for (int h16 = 0; h16 < 2; ++h16) {           // 16 TMEM columns (64 bytes of the row) per store
+            uint32_t wds[16];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const int chunk = (h16 * 4 + c) ^ (r & 7);
+              const uint4 v = *reinterpret_cast<const uint4*>(src + c64 * (kKeys * 128) + r * 128 + chunk * 16);
+              wds[c * 4 + 0] = v.x; wds[c * 4 + 1] = v.y; wds[c * 4 + 2] = v.z; wds[c * 4 + 3] = v.w;
+            }
+            tmem_st_32x32b_x16(dst + c64 * 32 + h16 * 16, wds);
+          }
+        }
+        tmem_st_wait();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(a_ready);
+    }
     const float my_lse = row_valid ? p.lse[static_cast<size_t>(head) * p.Tq + q_start + qi] * kLog2eB : 0.f;
     const float my_delta = row_valid ? p.delta[static_cast<size_t>(head) * p.Tq + q_start + qi] * p.scale : 0.f;  // pre-scaled
     bool ok = true;
