@@ -175,9 +175,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   } else if (warp == 1) {
     if (lane == 0 && n_iter > 0) {
       const uint32_t idesc_qk = umma_idesc_bf16(kBlockQ, kBlockK);
-      const uint32_t idesc_pv = umma_idesc_bf16_major(kBlockQ, DP, 0, 1);
       const uint32_t sQ = smem_u32(smem + L::kQ);
-      const uint32_t sP = smem_u32(smem + L::kP);
       bool ok = mbar_wait(q_full, 0, abort_word);
       auto issue_qk = [&](int it) -> bool {
         const int s = it & 1;
@@ -195,11 +193,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         umma_commit(&s_full[s]);
         return true;
       };
-      if (ok) ok = issue_qk(0);
+      for (int it = 0; it < n_iter && ok; ++it) ok = issue_qk(it);
+    }
+  } else if (warp == 3) {
+    // A second issuing thread for the P V products: a thread blocks while it issues and pays every commit, fence and
+    // barrier hand-off in sequence; with one thread for both products the tensor pipe idled during those.
+    if (lane == 0 && n_iter > 0) {
+      const uint32_t idesc_pv = umma_idesc_bf16_major(kBlockQ, DP, 0, 1);
+      const uint32_t sP = smem_u32(smem + L::kP);
+      bool ok = true;
       for (int it = 0; it < n_iter && ok; ++it) {
-        if (it + 1 < n_iter) {
-          if (!issue_qk(it + 1)) { ok = false; break; }
-        }
         const int s = it & 1;
         const uint32_t ph = (it >> 1) & 1;
         if (!mbar_wait(p_full, it & 1, abort_word)) { ok = false; break; }
