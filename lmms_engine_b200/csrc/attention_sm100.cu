@@ -56,11 +56,12 @@ struct FwdSmem {
   static constexpr int kV = kK + 2 * kTile;        // 2 stages
   static constexpr int kP = kV + 2 * kTile;        // 128 x 128 bf16
   static constexpr int kBars = kP + kBlockQ * kBlockK * 2;
-  static constexpr int kTotal = kBars + 256 + 1024;
+  static constexpr int kX = kBars + 256;           // row maxima (2 tiles x 2 halves x 128 rows) and row sums (2 x 128), fp32
+  static constexpr int kTotal = kX + 3072 + 1024;
 };
 
 template <int DP>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(384, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
   using L = FwdSmem<DP>;
@@ -76,7 +77,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* s_empty = bars + 11;      // 2
   uint64_t* p_full = bars + 13;       // 1
   uint64_t* pv_done = bars + 14;      // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* pair_bar = bars + 15;     // 4   the two softmax warps of a TMEM lane quadrant exchange their row maxima
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* work = reinterpret_cast<int*>(tmem_slot + 2);  // doc, q0, len_q, len_k, q_start, k_start
 
@@ -113,9 +115,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 4);
+      mbar_init(&s_empty[i], 8);
     }
-    mbar_init(p_full, 4);
+    for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 2);
+    mbar_init(p_full, 8);
     mbar_init(pv_done, 1);
     *abort_word = 0;
     fence_barrier_init();
@@ -222,13 +225,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
   } else if (warp >= 4) {
-    const int q = warp - 4;
+    // Eight softmax warps: the two warps of a TMEM lane quadrant (warp, warp + 4) share the quadrant's 32 rows and
+    // take 64 of a tile's 128 key columns each.  Four warps - one per scheduler, 128 exponentials per thread and
+    // tile - were the limit of this kernel; the halves only exchange their row maxima (shared memory + a two-warp
+    // barrier per tile) and, once at the end, their row sums.
+    const int q = warp & 3;
+    const int half = (warp - 4) >> 2;
+    constexpr int kHalf = kBlockK / 2;      // key columns of a tile per thread
+    constexpr int kOC = DP / 2;             // accumulator columns per thread
     const int r = q * 32 + lane;            // row within the query block
     const int qi = q0 + r;                  // row within the document
     const bool row_valid = qi < len_q;
     const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
+    float* xmax = reinterpret_cast<float*>(smem + L::kX);            // [2 tiles][2 halves][128 rows]
+    float* xsum = xmax + 2 * 2 * kBlockQ;                            // [2 halves][128 rows]
     float m_used = -INFINITY;               // max the accumulator is currently scaled by
-    float l_run = 0.f;
+    float l_run = 0.f;                      // sum over this thread's columns only
     bool ok = true;
     uint8_t* sP = smem + L::kP;
     for (int it = 0; it < n_iter && ok; ++it) {
@@ -237,13 +249,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!mbar_wait(&s_full[s], ph, abort_word)) { ok = false; break; }
       tc_fence_after();
       const int kb0 = (jb_lo + it) * kBlockK;
+      const int kc0 = kb0 + half * kHalf;   // first key column of this thread
       const bool need_mask = (kb0 + kBlockK > len_k) || (p.causal && kb0 + kBlockK - 1 > q0 + offset) ||
                              (p.window_left >= 0 && kb0 < q0 + kBlockQ - 1 + offset - p.window_left);
-      float sv[kBlockK];
+      float sv[kHalf];
 #pragma unroll
-      for (int c = 0; c < kBlockK / 32; ++c) {
+      for (int c = 0; c < kHalf / 32; ++c) {
         uint32_t rr[32];
-        tmem_ld_32x32b_x32(tmem_S0 + s * 128 + lane_sel + c * 32, rr);
+        tmem_ld_32x32b_x32(tmem_S0 + s * 128 + lane_sel + half * kHalf + c * 32, rr);
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) sv[c * 32 + j] = __uint_as_float(rr[j]) * p.scale_log2;
@@ -253,8 +266,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (lane == 0) mbar_arrive(&s_empty[s]);
       if (need_mask) {
 #pragma unroll
-        for (int j = 0; j < kBlockK; ++j) {
-          const int kj = kb0 + j;
+        for (int j = 0; j < kHalf; ++j) {
+          const int kj = kc0 + j;
           bool vis = kj < len_k;
           if (p.causal) vis = vis && (kj <= qi + offset);
           if (p.window_left >= 0) vis = vis && (kj >= qi + offset - p.window_left);
@@ -263,8 +276,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       float mx = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < kBlockK; ++j) mx = fmaxf(mx, sv[j]);
-      // lazy rescale: keep the old reference max unless it is stale by more than 2^8
+      for (int j = 0; j < kHalf; ++j) mx = fmaxf(mx, sv[j]);
+      // the row's maximum over both halves
+      xmax[(s * 2 + half) * kBlockQ + r] = mx;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&pair_bar[q]);
+      if (!mbar_wait(&pair_bar[q], it & 1, abort_word)) { ok = false; break; }
+      mx = fmaxf(mx, xmax[(s * 2 + (half ^ 1)) * kBlockQ + r]);
+      // lazy rescale: keep the old reference max unless it is stale by more than 2^8 (the same decision in both halves)
       const bool grow = mx > m_used + 8.f;
       const bool any_grow = __any_sync(0xffffffffu, grow);
       float alpha = 1.f;
@@ -275,9 +294,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       const float m_ref = (m_new == -INFINITY) ? 0.f : m_new;
       float rs = 0.f;
-      uint32_t pk[kBlockK / 2];
+      uint32_t pk[kHalf / 2];
 #pragma unroll
-      for (int j = 0; j < kBlockK; j += 2) {
+      for (int j = 0; j < kHalf; j += 2) {
         const float p0 = exp2f(sv[j] - m_ref), p1 = exp2f(sv[j + 1] - m_ref);
         pk[j / 2] = pack_bf16x2(p0, p1);
         const float2 back = unpack_bf16x2(pk[j / 2]);
@@ -289,31 +308,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (it > 0) {
         if (!mbar_wait(pv_done, (it - 1) & 1, abort_word)) { ok = false; break; }
         tc_fence_after();
-        if (any_grow) {
+        if (any_grow) {  // this thread rescales its half of the accumulator's columns
 #pragma unroll
-          for (int c = 0; c < DP / 32; ++c) {
+          for (int c = 0; c < kOC / 32; ++c) {
             uint32_t rr[32];
-            tmem_ld_32x32b_x32(tmem_O + lane_sel + c * 32, rr);
+            tmem_ld_32x32b_x32(tmem_O + lane_sel + half * kOC + c * 32, rr);
             tmem_ld_wait();
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
+            for (int h2 = 0; h2 < 2; ++h2) {
               uint32_t w[16];
 #pragma unroll
-              for (int j = 0; j < 16; ++j) w[j] = __float_as_uint(__uint_as_float(rr[half * 16 + j]) * alpha);
-              tmem_st_32x32b_x16(tmem_O + lane_sel + c * 32 + half * 16, w);
+              for (int j = 0; j < 16; ++j) w[j] = __float_as_uint(__uint_as_float(rr[h2 * 16 + j]) * alpha);
+              tmem_st_32x32b_x16(tmem_O + lane_sel + half * kOC + c * 32 + h2 * 16, w);
             }
           }
           tmem_st_wait();
         }
       }
-      // P -> shared memory, 128B-swizzled K-major halves of 64 keys
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      // P -> shared memory: this thread's 64 keys are one 128B-swizzled K-major half of the tile
+      {
         uint8_t* rowp = sP + half * (kBlockQ * 128) + r * 128;
 #pragma unroll
         for (int c16 = 0; c16 < 8; ++c16) {
           const int chunk = c16 ^ (r & 7);
-          const int b = half * 32 + c16 * 4;
+          const int b = c16 * 4;
           *reinterpret_cast<uint4*>(rowp + chunk * 16) = make_uint4(pk[b], pk[b + 1], pk[b + 2], pk[b + 3]);
         }
       }
@@ -325,17 +343,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // ---- epilogue: O / l, LSE -------------------------------------------------------
     if (ok && n_iter > 0) ok = mbar_wait(pv_done, (n_iter - 1) & 1, abort_word);
     tc_fence_after();
-    const float inv_l = (l_run > 0.f) ? 1.f / l_run : 0.f;
-    if (row_valid && ok) {
+    // the row sum over both halves
+    xsum[half * kBlockQ + r] = l_run;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&pair_bar[q]);
+    if (ok) ok = mbar_wait(&pair_bar[q], n_iter & 1, abort_word);
+    const float l_all = l_run + xsum[(half ^ 1) * kBlockQ + r];
+    const float inv_l = (l_all > 0.f) ? 1.f / l_all : 0.f;
+    if (row_valid && ok && half == 0) {
       p.lse[static_cast<size_t>(head) * p.Tq + q_start + qi] =
-          (l_run > 0.f) ? (m_used + log2f(l_run)) * kLn2 : -INFINITY;
+          (l_all > 0.f) ? (m_used + log2f(l_all)) * kLn2 : -INFINITY;
     }
     __nv_bfloat16* orow = p.O + static_cast<size_t>(q_start + qi) * p.ldo + static_cast<size_t>(head) * p.D;
 #pragma unroll
-    for (int c = 0; c < DP / 32; ++c) {
+    for (int c = 0; c < kOC / 32; ++c) {
+      const int col0 = half * kOC + c * 32;
       uint32_t rr[32];
       if (n_iter > 0 && ok) {
-        tmem_ld_32x32b_x32(tmem_O + lane_sel + c * 32, rr);
+        tmem_ld_32x32b_x32(tmem_O + lane_sel + col0, rr);
         tmem_ld_wait();
       } else {
 #pragma unroll
@@ -344,7 +369,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (row_valid && ok) {
 #pragma unroll
         for (int j8 = 0; j8 < 4; ++j8) {
-          const int col = c * 32 + j8 * 8;
+          const int col = col0 + j8 * 8;
           if (col < p.D) {  // D is a multiple of 8
             uint4 o;
             o.x = pack_bf16x2(__uint_as_float(rr[j8 * 8 + 0]) * inv_l, __uint_as_float(rr[j8 * 8 + 1]) * inv_l);
@@ -821,11 +846,11 @@ int b200_attn_fwd(const void* q, const void* k, const void* v, void* o, void* ls
   if (DP == 64) {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<64>::kTotal); set = true; }
-    attn_fwd_kernel<64><<<grid, 256, FwdSmem<64>::kTotal, st>>>(tq, tk, tv, p);
+    attn_fwd_kernel<64><<<grid, 384, FwdSmem<64>::kTotal, st>>>(tq, tk, tv, p);
   } else {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<128>::kTotal); set = true; }
-    attn_fwd_kernel<128><<<grid, 256, FwdSmem<128>::kTotal, st>>>(tq, tk, tv, p);
+    attn_fwd_kernel<128><<<grid, 384, FwdSmem<128>::kTotal, st>>>(tq, tk, tv, p);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
