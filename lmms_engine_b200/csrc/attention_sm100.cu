@@ -23,6 +23,8 @@
 // (src/lmms_engine/kernels/attention.py:20-182).
 #include "common.cuh"
 
+#include <cuda_fp16.h>
+
 #include <stdio.h>
 
 namespace b200 {
@@ -50,14 +52,20 @@ struct FwdParams {
 // ---- shared memory plan (DP = padded head dim: 64 or 128) ------------------------------
 template <int DP>
 struct FwdSmem {
+  // A K or V stage is released only when the product that read it has retired, and its refill then pays the whole TMA
+  // latency (about 2 400 cycles), so with S stages a tile's period is at least that latency / (S - 1): three stages each.
+  // The room comes from Q, which is copied once into TMEM (the A operand of every Q K^T product) and only lands in
+  // shared memory, in the buffer that the probabilities use afterwards.
+  static constexpr int kStages = 3;
   static constexpr int kTile = kBlockQ * DP * 2;  // bytes of one Q / K / V tile
-  static constexpr int kQ = 0;
-  static constexpr int kK = kQ + kTile;            // 2 stages
-  static constexpr int kV = kK + 2 * kTile;        // 2 stages
-  static constexpr int kP = kV + 2 * kTile;        // 128 x 128 bf16
+  static constexpr int kK = 0;                     // kStages stages
+  static constexpr int kV = kK + kStages * kTile;  // kStages stages
+  static constexpr int kP = kV + kStages * kTile;  // 128 x 128 bf16
+  static constexpr int kQ = kP;                    // landing area of Q: every thread later writes P only where it read Q
   static constexpr int kBars = kP + kBlockQ * kBlockK * 2;
-  static constexpr int kX = kBars + 256;           // row maxima (2 tiles x 2 halves x 128 rows) and row sums (2 x 128), fp32
-  static constexpr int kTotal = kX + 3072 + 1024;
+  static constexpr int kX = kBars + 256;           // 1 KB: row maxima (2 tiles x 2 halves x 128 rows, fp16), then row sums (2 x 128, fp32)
+  static constexpr int kTotal = kX + 1024 + 1024;
+  static_assert(kTotal <= 227 * 1024, "shared memory of the forward kernel");
 };
 
 template <int DP>
@@ -68,17 +76,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
-  uint64_t* q_full = bars;            // 1
-  uint64_t* k_full = bars + 1;        // 2
-  uint64_t* k_empty = bars + 3;       // 2
-  uint64_t* v_full = bars + 5;        // 2
-  uint64_t* v_empty = bars + 7;       // 2
-  uint64_t* s_full = bars + 9;        // 2
-  uint64_t* s_empty = bars + 11;      // 2
-  uint64_t* p_full = bars + 13;       // 1
-  uint64_t* pv_done = bars + 14;      // 1
-  uint64_t* pair_bar = bars + 15;     // 4   the two softmax warps of a TMEM lane quadrant exchange their row maxima
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
+  constexpr int S = L::kStages;
+  uint64_t* q_full = bars;                  // 1
+  uint64_t* k_full = bars + 1;              // S
+  uint64_t* k_empty = bars + 1 + S;         // S
+  uint64_t* v_full = bars + 1 + 2 * S;      // S
+  uint64_t* v_empty = bars + 1 + 3 * S;     // S
+  uint64_t* s_full = bars + 1 + 4 * S;      // 2
+  uint64_t* s_empty = bars + 3 + 4 * S;     // 2
+  uint64_t* p_full = bars + 5 + 4 * S;      // 1
+  uint64_t* pv_done = bars + 6 + 4 * S;     // 1
+  uint64_t* pair_bar = bars + 7 + 4 * S;    // 4   the two softmax warps of a TMEM lane quadrant exchange their row maxima
+  uint64_t* a_ready = bars + 11 + 4 * S;    // 1   Q sits in TMEM
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12 + 4 * S);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* work = reinterpret_cast<int*>(tmem_slot + 2);  // doc, q0, len_q, len_k, q_start, k_start
 
@@ -109,14 +119,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < S; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
       mbar_init(&s_empty[i], 8);
     }
+    mbar_init(a_ready, 8);
     for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 2);
     mbar_init(p_full, 8);
     mbar_init(pv_done, 1);
@@ -135,6 +148,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_O = tmem_base;            // 128 columns
   const uint32_t tmem_S0 = tmem_base + 128;     // 2 x 128 columns
+  const uint32_t tmem_Q = tmem_base + 384;      // DP / 2 columns: Q as bf16 pairs, row m in lane m
 
   const int q0 = work[1], len_q = work[2], len_k = work[3], q_start = work[4], k_start = work[5];
   const int head = blockIdx.y;
@@ -160,8 +174,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tma_load_3d(smem + L::kQ + c * (kBlockQ * 128), &tmQ, q_full, c * 64, head, q_start + q0);
       bool ok = true;
       for (int it = 0; it < n_iter && ok; ++it) {
-        const int s = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
+        const int s = it % S;
+        const uint32_t ph = (it / S) & 1;
         const int krow = k_start + (jb_lo + it) * kBlockK;
         if (!mbar_wait(&k_empty[s], ph ^ 1, abort_word)) { ok = false; break; }
         mbar_expect_tx(&k_full[s], L::kTile);
@@ -178,21 +192,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   } else if (warp == 1) {
     if (lane == 0 && n_iter > 0) {
       const uint32_t idesc_qk = umma_idesc_bf16(kBlockQ, kBlockK);
-      const uint32_t sQ = smem_u32(smem + L::kQ);
-      bool ok = mbar_wait(q_full, 0, abort_word);
+      bool ok = mbar_wait(a_ready, 0, abort_word);
       auto issue_qk = [&](int it) -> bool {
-        const int s = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait(&k_full[s], ph, abort_word)) return false;
-        if (!mbar_wait(&s_empty[s], ph ^ 1, abort_word)) return false;
+        const int s = it & 1;            // TMEM buffer of the scores
+        const int stg = it % S;          // shared-memory stage of K
+        if (!mbar_wait(&k_full[stg], (it / S) & 1, abort_word)) return false;
+        if (!mbar_wait(&s_empty[s], ((it >> 1) & 1) ^ 1, abort_word)) return false;
         tc_fence_after();
-        const uint32_t sK = smem_u32(smem + L::kK + s * L::kTile);
+        const uint32_t sK = smem_u32(smem + L::kK + stg * L::kTile);
 #pragma unroll
         for (int kk = 0; kk < DP / 16; ++kk) {
           const uint32_t off = (kk / 4) * (kBlockQ * 128) + (kk % 4) * 32;
-          umma_bf16_ss(tmem_S0 + s * 128, umma_desc_sw128(sQ + off), umma_desc_sw128(sK + off), idesc_qk, kk != 0);
+          umma_bf16_ts(tmem_S0 + s * 128, tmem_Q + kk * 8, umma_desc_sw128(sK + off), idesc_qk, kk != 0);
         }
-        umma_commit(&k_empty[s]);
+        umma_commit(&k_empty[stg]);
         umma_commit(&s_full[s]);
         return true;
       };
@@ -206,12 +219,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t sP = smem_u32(smem + L::kP);
       bool ok = true;
       for (int it = 0; it < n_iter && ok; ++it) {
-        const int s = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
+        const int stg = it % S;
         if (!mbar_wait(p_full, it & 1, abort_word)) { ok = false; break; }
-        if (!mbar_wait(&v_full[s], ph, abort_word)) { ok = false; break; }
+        if (!mbar_wait(&v_full[stg], (it / S) & 1, abort_word)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t sV = smem_u32(smem + L::kV + s * L::kTile);
+        const uint32_t sV = smem_u32(smem + L::kV + stg * L::kTile);
 #pragma unroll
         for (int kk = 0; kk < kBlockK / 16; ++kk) {
           // A = P [128 q x 128 keys], K-major, two 64-key halves; B = V [keys x d], MN-major
@@ -220,7 +232,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           bd = (bd & ~(uint64_t(0x3FFF) << 16)) | (uint64_t((kBlockK * 128) >> 4) << 16);
           umma_bf16_ss(tmem_O, ad, bd, idesc_pv, (it | kk) != 0);
         }
-        umma_commit(&v_empty[s]);
+        umma_commit(&v_empty[stg]);
         umma_commit(pv_done);
       }
     }
@@ -237,12 +249,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int qi = q0 + r;                  // row within the document
     const bool row_valid = qi < len_q;
     const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
-    float* xmax = reinterpret_cast<float*>(smem + L::kX);            // [2 tiles][2 halves][128 rows]
-    float* xsum = xmax + 2 * 2 * kBlockQ;                            // [2 halves][128 rows]
+    // exchanged maxima are rounded to fp16 on both sides, so that both halves arrive at the same reference value (any
+    // common value near the maximum serves; the row sum and the log-sum-exp stay exact)
+    __half* xmax = reinterpret_cast<__half*>(smem + L::kX);          // [2 tiles][2 halves][128 rows]
+    float* xsum = reinterpret_cast<float*>(smem + L::kX);            // [2 halves][128 rows], after the loop
     float m_used = -INFINITY;               // max the accumulator is currently scaled by
     float l_run = 0.f;                      // sum over this thread's columns only
     bool ok = true;
     uint8_t* sP = smem + L::kP;
+    // ---- Q from its landing area (128-byte swizzle) into TMEM: thread (row r, half h) copies the 64-column chunk h of
+    // its row - the bytes it alone overwrites with probabilities later ----
+    if (n_iter > 0) {
+      const bool okq = mbar_wait(q_full, 0, abort_word);
+      if (okq && half < DP / 64) {
+        const uint8_t* src = smem + L::kQ + half * (kBlockQ * 128) + r * 128;
+#pragma unroll
+        for (int h16 = 0; h16 < 2; ++h16) {
+          uint32_t wds[16];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int chunk = (h16 * 4 + c) ^ (r & 7);
+            const uint4 v = *reinterpret_cast<const uint4*>(src + chunk * 16);
+            wds[c * 4 + 0] = v.x; wds[c * 4 + 1] = v.y; wds[c * 4 + 2] = v.z; wds[c * 4 + 3] = v.w;
+          }
+          tmem_st_32x32b_x16(tmem_Q + lane_sel + half * 32 + h16 * 16, wds);
+        }
+        tmem_st_wait();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(a_ready);
+    }
     for (int it = 0; it < n_iter && ok; ++it) {
       const int s = it & 1;
       const uint32_t ph = (it >> 1) & 1;
@@ -278,11 +315,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
       for (int j = 0; j < kHalf; ++j) mx = fmaxf(mx, sv[j]);
       // the row's maximum over both halves
-      xmax[(s * 2 + half) * kBlockQ + r] = mx;
+      const __half mx_h = __float2half_rn(fmaxf(mx, -60000.f));
+      xmax[(s * 2 + half) * kBlockQ + r] = mx_h;
       __syncwarp();
       if (lane == 0) mbar_arrive(&pair_bar[q]);
       if (!mbar_wait(&pair_bar[q], it & 1, abort_word)) { ok = false; break; }
-      mx = fmaxf(mx, xmax[(s * 2 + (half ^ 1)) * kBlockQ + r]);
+      mx = fmaxf(__half2float(mx_h), __half2float(xmax[(s * 2 + (half ^ 1)) * kBlockQ + r]));
+      if (mx <= -60000.f) mx = -INFINITY;  // a row that sees nothing in this tile
       // lazy rescale: keep the old reference max unless it is stale by more than 2^8 (the same decision in both halves)
       const bool grow = mx > m_used + 8.f;
       const bool any_grow = __any_sync(0xffffffffu, grow);
@@ -343,11 +382,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // ---- epilogue: O / l, LSE -------------------------------------------------------
     if (ok && n_iter > 0) ok = mbar_wait(pv_done, (n_iter - 1) & 1, abort_word);
     tc_fence_after();
-    // the row sum over both halves
-    xsum[half * kBlockQ + r] = l_run;
+    // the row sum over both halves; the area held the maxima: first make sure the partner has read its last one
     __syncwarp();
     if (lane == 0) mbar_arrive(&pair_bar[q]);
     if (ok) ok = mbar_wait(&pair_bar[q], n_iter & 1, abort_word);
+    xsum[half * kBlockQ + r] = l_run;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&pair_bar[q]);
+    if (ok) ok = mbar_wait(&pair_bar[q], (n_iter + 1) & 1, abort_word);
     const float l_all = l_run + xsum[(half ^ 1) * kBlockQ + r];
     const float inv_l = (l_all > 0.f) ? 1.f / l_all : 0.f;
     if (row_valid && ok && half == 0) {
