@@ -305,7 +305,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             for (int e = 0; e < 2; ++e) {
               const float l2 = __shfl_sync(0xffffffffu, lane_lse, j + e);
               const float dl = __shfl_sync(0xffffffffu, lane_dl, j + e);
-              pv[e] = exp2f(__uint_as_float(rs[j + e]) * p.scale_log2 - l2);
+              pv[e] = fast_exp2(fmaf(__uint_as_float(rs[j + e]), p.scale_log2, -l2));
               dsv[e] = pv[e] * fmaf(__uint_as_float(rd[j + e]), p.scale, -dl);
             }
             ppk[j / 2] = pack_bf16x2(pv[0], pv[1]);
@@ -325,7 +325,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               if (p.window_left >= 0) vis = vis && (kj >= qi + offset - p.window_left);
               float pe = 0.f, dse = 0.f;
               if (vis) {
-                pe = exp2f(__uint_as_float(rs[j + e]) * p.scale_log2 - l2);
+                pe = fast_exp2(fmaf(__uint_as_float(rs[j + e]), p.scale_log2, -l2));
                 dse = pe * fmaf(__uint_as_float(rd[j + e]), p.scale, -dl);
               }
               pv[e] = pe;
@@ -627,7 +627,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             float dsv[2];
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-              const float pe = exp2f(__uint_as_float(rs[j + e]) * p.scale_log2 - my_lse);
+              const float pe = fast_exp2(fmaf(__uint_as_float(rs[j + e]), p.scale_log2, -my_lse));
               dsv[e] = pe * fmaf(__uint_as_float(rd[j + e]), p.scale, -my_delta);
             }
             dpk[j / 2] = pack_bf16x2(dsv[0], dsv[1]);
@@ -644,7 +644,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               if (p.window_left >= 0) vis = vis && (kj >= qi + offset - p.window_left);
               float dse = 0.f;
               if (vis) {
-                const float pe = exp2f(__uint_as_float(rs[j + e]) * p.scale_log2 - my_lse);
+                const float pe = fast_exp2(fmaf(__uint_as_float(rs[j + e]), p.scale_log2, -my_lse));
                 dse = pe * fmaf(__uint_as_float(rd[j + e]), p.scale, -my_delta);
               }
               dsv[e] = dse;

@@ -290,13 +290,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const bool need_mask = (kb0 + kBlockK > len_k) || (p.causal && kb0 + kBlockK - 1 > q0 + offset) ||
                              (p.window_left >= 0 && kb0 < q0 + kBlockQ - 1 + offset - p.window_left);
       float sv[kHalf];
-#pragma unroll
-      for (int c = 0; c < kHalf / 32; ++c) {
-        uint32_t rr[32];
-        tmem_ld_32x32b_x32(tmem_S0 + s * 128 + lane_sel + half * kHalf + c * 32, rr);
+      {
+        // both loads in flight before the one wait (raw scores: the scale rides in the exponent's fma)
+        uint32_t ra[32], rb[32];
+        tmem_ld_32x32b_x32(tmem_S0 + s * 128 + lane_sel + half * kHalf, ra);
+        tmem_ld_32x32b_x32(tmem_S0 + s * 128 + lane_sel + half * kHalf + 32, rb);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) sv[c * 32 + j] = __uint_as_float(rr[j]) * p.scale_log2;
+        for (int j = 0; j < 32; ++j) {
+          sv[j] = __uint_as_float(ra[j]);
+          sv[32 + j] = __uint_as_float(rb[j]);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -314,6 +318,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       float mx = -INFINITY;
 #pragma unroll
       for (int j = 0; j < kHalf; ++j) mx = fmaxf(mx, sv[j]);
+      mx *= p.scale_log2;  // the scale is positive: the maximum of the scaled scores
       // the row's maximum over both halves
       const __half mx_h = __float2half_rn(fmaxf(mx, -60000.f));
       xmax[(s * 2 + half) * kBlockQ + r] = mx_h;
@@ -329,18 +334,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       float m_new = m_used;
       if (grow) {
         m_new = mx;
-        alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
+        alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
       }
-      const float m_ref = (m_new == -INFINITY) ? 0.f : m_new;
-      float rs = 0.f;
+      const float neg_ref = (m_new == -INFINITY) ? 0.f : -m_new;
+      // per element: one fma, one ex2, one add, half a convert.  The row sum takes the fp32 values (the bf16 rounding of
+      // P averages out below the output's own precision).
+      float rs0 = 0.f, rs1 = 0.f;
       uint32_t pk[kHalf / 2];
 #pragma unroll
       for (int j = 0; j < kHalf; j += 2) {
-        const float p0 = exp2f(sv[j] - m_ref), p1 = exp2f(sv[j + 1] - m_ref);
+        const float p0 = fast_exp2(fmaf(sv[j], p.scale_log2, neg_ref));
+        const float p1 = fast_exp2(fmaf(sv[j + 1], p.scale_log2, neg_ref));
         pk[j / 2] = pack_bf16x2(p0, p1);
-        const float2 back = unpack_bf16x2(pk[j / 2]);
-        rs += back.x + back.y;
+        rs0 += p0;
+        rs1 += p1;
       }
+      const float rs = rs0 + rs1;
       l_run = l_run * alpha + rs;
       m_used = m_new;
       // P buffer and the O accumulator are free once the previous PV product retired

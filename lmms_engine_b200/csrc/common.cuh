@@ -292,6 +292,13 @@ __device__ __forceinline__ bool index_in_bounds(long idx, long limit, int* statu
 #endif
 
 // ---------------------------------------------------------------- misc numeric helpers
+// 2^x on the special-function unit, one instruction (exp2f() adds a range fix-up for denormal results that a softmax does
+// not need): 2^-inf = +0.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
