@@ -102,9 +102,15 @@ class AeroRealtimeModel(VLModel):
         self.multi_modal_projector = AeroRealtimeProjector(cfg)
         self._rt = None
 
-    def audio_rows(self, input_features, mask):
-        """Projected audio rows of all clips, clip after clip: ``frames // downsample_factor`` rows per clip."""
+    def audio_rows(self, input_features, mask, stream_cache=None):
+        """Projected audio rows of all clips, clip after clip: ``frames // downsample_factor`` rows per clip.  With
+        ``stream_cache`` (``audio_tower.new_stream()``) the features are the NEXT piece of one running clip and the
+        encoder continues from the cache instead of starting a clip."""
         df = self.config.downsample_factor
+        if stream_cache is not None:
+            hidden = self.audio_tower.stream(input_features.reshape(input_features.shape[-2], input_features.shape[-1]), stream_cache)
+            keep = hidden.shape[0] // df * df
+            return self.multi_modal_projector(hidden[:keep].reshape(keep // df, -1))
         T = input_features.shape[-1]
         if mask is not None and mask.shape[-1] != T:
             # frame-level mask (after the stride-2 convolution): f frames cover 2 f mel frames
@@ -120,11 +126,11 @@ class AeroRealtimeModel(VLModel):
         return self.multi_modal_projector(torch.cat(rows, 0))
 
     def embed_multimodal(self, ids, pixel_values, image_grid_thw, pixel_values_videos, video_grid_thw, embed_ids=None):
-        stream, feats, mask = self._rt or (None, None, None)
+        stream, feats, mask, audio_cache = self._rt or (None, None, None, None)
         emb, deep, idx = super().embed_multimodal(ids, pixel_values, image_grid_thw, pixel_values_videos, video_grid_thw,
                                                   embed_ids=stream)
         if feats is not None:
-            rows = self.audio_rows(feats.to(emb.dtype), mask)
+            rows = self.audio_rows(feats.to(emb.dtype), mask, audio_cache)
             m = ids == self.config.audio_token_id
             # the k-th audio position receives the k-th row, added to the text-stream embedding
             src = (torch.cumsum(m, 0) - 1).clamp(min=0, max=max(rows.shape[0] - 1, 0))
@@ -132,7 +138,7 @@ class AeroRealtimeModel(VLModel):
         return emb, deep, idx
 
     def forward(self, input_ids=None, attention_mask=None, text_stream_ids=None, input_features=None,
-                audio_attention_mask=None, feature_attention_mask=None, **kw):
+                audio_attention_mask=None, feature_attention_mask=None, audio_stream_cache=None, **kw):
         stream = None
         if text_stream_ids is not None:
             if text_stream_ids.dim() == 2 and attention_mask is not None and kw.get("cu_seqlens") is None:
@@ -141,7 +147,7 @@ class AeroRealtimeModel(VLModel):
                 stream = text_stream_ids.reshape(-1)
         mask = audio_attention_mask if audio_attention_mask is not None else feature_attention_mask
         feats = input_features if input_features is not None and input_features.numel() > 0 else None
-        self._rt = (stream, feats, mask)
+        self._rt = (stream, feats, mask, audio_stream_cache)
         try:
             return super().forward(input_ids=input_ids, attention_mask=attention_mask, **kw)
         finally:

@@ -16,7 +16,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass, field, fields
-from typing import Any, Dict, Optional
+from typing import Any, Dict, List, Optional
 
 import torch
 import torch.nn as nn
@@ -391,8 +391,8 @@ class VoxtralRealtimeEncoderConfig:
     mlp_type: str = "swiglu"               # swiglu | gelu (fc1 / fc2 with biases)
     conv_padding: str = "causal"           # causal | symmetric (every chunk is encoded by itself)
     activation_function: str = "gelu"
-    attention_window_left: Optional[int] = None   # None: sliding_window - 1 (or unlimited)
-    attention_window_right: int = 0                # 0: causal; negative: frames also see what follows
+    attention_window_left: Optional[int] = None   # None: sliding_window - 1 (or unlimited); negative: unlimited
+    attention_window_right: int = 0                # 0: causal; n > 0: a frame also sees the next n; negative: all that follow
     extra: Dict[str, Any] = field(default_factory=dict)
 
     def __post_init__(self):
@@ -404,8 +404,6 @@ class VoxtralRealtimeEncoderConfig:
             raise ValueError(f"conv_padding must be 'causal' or 'symmetric', got {self.conv_padding}")
         if self.attention_window_left is None:
             self.attention_window_left = (self.sliding_window - 1) if self.sliding_window else -1
-        if self.attention_window_right > 0:
-            raise NotImplementedError("a bounded look-ahead (attention_window_right > 0) is not built: use 0 (causal) or -1 (unlimited)")
 
     @classmethod
     def from_dict(cls, d):
@@ -438,12 +436,45 @@ class _CausalConv1d(nn.Conv1d):
         return super().forward(F.pad(x, (left, total - left)))
 
 
+    def left_pad(self) -> int:
+        return (self.kernel_size[0] - 1) * self.dilation[0] + 1 - self.stride[0]
+
+    def continue_from(self, x, tail):
+        """The convolution of a stream that arrives in pieces: ``tail`` holds the last ``left_pad`` input frames of what
+        came before (zeros at the start, which is the padding of the one-piece form).  Returns the output frames of this
+        piece and the tail for the next one.  A piece must hold a whole number of strides."""
+        if x.shape[-1] % self.stride[0]:
+            raise ValueError(f"a piece of {x.shape[-1]} frames is not a multiple of the stride {self.stride[0]}")
+        full = torch.cat([tail.to(x.dtype), x], -1)
+        return nn.Conv1d.forward(self, full), full[..., full.shape[-1] - self.left_pad():]
+
+
 class _VoxtralEmbedder(nn.Module):
     def __init__(self, c):
         super().__init__()
         self.conv1 = _CausalConv1d(c.num_mel_bins, c.hidden_size, kernel_size=3)
         self.conv2 = _CausalConv1d(c.hidden_size, c.hidden_size, kernel_size=3, stride=2)
         self.conv1.symmetric = self.conv2.symmetric = getattr(c, "conv_padding", "causal") == "symmetric"
+
+
+def local_window_attention(q, k, v, cu, left: int, right: int, scale: float):
+    """Attention of packed documents in which frame i sees frames ``i - left .. i + right`` (a negative bound is no bound).
+    The dense form of the masks the varlen kernel does not cover - a bounded look-ahead, or a left bound without
+    causality (src/lmms_engine/models/aero_realtime/modeling_aero_realtime.py:914-935); the audio encoder's documents are
+    a few thousand frames at most.  ``q / k / v [P, heads, head_dim]``."""
+    out = torch.empty_like(q)
+    bounds = cu.tolist()
+    for a, b in zip(bounds[:-1], bounds[1:]):
+        i = torch.arange(b - a, device=q.device)
+        delta = i[None, :] - i[:, None]
+        allow = torch.ones_like(delta, dtype=torch.bool)
+        if left >= 0:
+            allow &= delta >= -left
+        if right >= 0:
+            allow &= delta <= right
+        o = F.scaled_dot_product_attention(q[a:b].transpose(0, 1), k[a:b].transpose(0, 1), v[a:b].transpose(0, 1), attn_mask=allow, scale=scale)
+        out[a:b] = o.transpose(0, 1)
+    return out
 
 
 class _VoxtralAttention(nn.Module):
@@ -457,12 +488,16 @@ class _VoxtralAttention(nn.Module):
         self.o_proj = nn.Linear(self.heads * hd, d, bias=True)
         left = getattr(c, "attention_window_left", None)
         left = ((c.sliding_window - 1) if c.sliding_window else -1) if left is None else left
-        self.causal = getattr(c, "attention_window_right", 0) == 0
-        if not self.causal and left >= 0:
-            raise NotImplementedError("a left window without causality is not built: use attention_window_left = -1 with attention_window_right = -1")
+        right = getattr(c, "attention_window_right", 0)
+        self.causal = right == 0
+        self.left, self.right = (left if left >= 0 else -1), (right if right >= 0 else -1)
+        # the varlen kernel covers causal masks (with or without a left bound) and the full mask
+        self.kernel_mask = self.causal or (self.left < 0 and self.right < 0)
         self.window = (left, -1) if left >= 0 else (-1, -1)
 
-    def forward(self, x, cu, cos, sin):
+    def forward(self, x, cu, cos, sin, past=None):
+        """``past``: ``None``, or a two-entry list ``[keys, values]`` of the frames that came before (rotated keys), which
+        is extended in place by this piece and trimmed to the left window: the streaming form, causal masks only."""
         from ..ops import rope as rope_ops
 
         P = x.shape[0]
@@ -470,7 +505,21 @@ class _VoxtralAttention(nn.Module):
         b = torch.cat([self.q_proj.bias, torch.zeros_like(self.q_proj.bias), self.v_proj.bias], 0)
         qkv = gemm_ops.linear(x, w, b).view(P, 3, self.heads, self.head_dim)
         q, k = rope_ops.rope_apply(qkv[:, 0], cos, sin), rope_ops.rope_apply(qkv[:, 1], cos, sin)
-        o = attn_ops.varlen_attn(q, k, qkv[:, 2], cu, cu, causal=self.causal, softmax_scale=self.head_dim ** -0.5, window_size=self.window)
+        v = qkv[:, 2]
+        scale = self.head_dim ** -0.5
+        if past is not None:
+            if not self.causal:
+                raise ValueError("an encoder whose frames see what follows cannot run on a stream")
+            if past[0] is not None:
+                k, v = torch.cat([past[0], k], 0), torch.cat([past[1], v], 0)
+            keep = k.shape[0] if self.left < 0 else min(k.shape[0], self.left)
+            past[0], past[1] = k[k.shape[0] - keep:].detach(), v[v.shape[0] - keep:].detach()
+            cu_k = torch.tensor([0, k.shape[0]], dtype=torch.int32, device=x.device)
+            o = attn_ops.varlen_attn(q, k.contiguous(), v.contiguous(), cu, cu_k, causal=True, softmax_scale=scale, window_size=self.window)
+        elif self.kernel_mask:
+            o = attn_ops.varlen_attn(q, k, v, cu, cu, causal=self.causal, softmax_scale=scale, window_size=self.window)
+        else:
+            o = local_window_attention(q, k, v, cu, self.left, self.right, scale)
         return gemm_ops.linear(o.reshape(P, -1), self.o_proj.weight, self.o_proj.bias)
 
 
@@ -518,9 +567,21 @@ class VoxtralEncoderLayer(nn.Module):
         self.self_attn_layer_norm, self.final_layer_norm = _encoder_norm(c), _encoder_norm(c)
         self.mlp = _VoxtralGeluMLP(c) if getattr(c, "mlp_type", "swiglu") == "gelu" else _VoxtralMLP(c)
 
-    def forward(self, x, cu, cos, sin):
-        x = x + self.self_attn(self.self_attn_layer_norm(x), cu, cos, sin)
+    def forward(self, x, cu, cos, sin, past=None):
+        x = x + self.self_attn(self.self_attn_layer_norm(x), cu, cos, sin, past)
         return x + self.mlp(self.final_layer_norm(x))
+
+
+class VoxtralStreamCache:
+    """What the streaming encoder carries from one piece of a clip to the next: the last input frames of both
+    convolutions (the reference's padding cache, src/lmms_engine/models/aero_realtime/modeling_aero_realtime.py:678-736),
+    every layer's rotated keys and values inside the left window, and the number of frames encoded so far (the rotary
+    position of the next one)."""
+
+    def __init__(self, n_layers: int):
+        self.conv_tails: List[Optional[torch.Tensor]] = [None, None]
+        self.layers: List[List[Optional[torch.Tensor]]] = [[None, None] for _ in range(n_layers)]
+        self.frames = 0
 
 
 class VoxtralRealtimeEncoder(nn.Module):
@@ -557,3 +618,37 @@ class VoxtralRealtimeEncoder(nn.Module):
         for layer in self.layers:
             flat = layer(flat, cu, cos, sin)
         return {"last_hidden_state": self.norm(flat), "frame_lengths": torch.tensor(frames, device=x.device)}
+
+    def _rotary(self, pos):
+        hd = self.config.head_dim
+        inv = 1.0 / (self.config.rope_theta ** (torch.arange(0, hd, 2, device=pos.device).float() / hd))
+        ang = pos[:, None] * inv[None, :]
+        return torch.cat([ang.cos(), ang.cos()], -1), torch.cat([ang.sin(), ang.sin()], -1)
+
+    def new_stream(self) -> VoxtralStreamCache:
+        c = self.config
+        if getattr(c, "conv_padding", "causal") != "causal" or getattr(c, "attention_window_right", 0) != 0:
+            raise ValueError("only the causal encoder (causal convolution padding, no look-ahead) encodes a stream piece by piece; "
+                             "the other variants encode every chunk by itself")
+        return VoxtralStreamCache(len(self.layers))
+
+    def stream(self, piece: torch.Tensor, cache: VoxtralStreamCache) -> torch.Tensor:
+        """Encode the next ``piece [mel, 2 m]`` (an even number of mel frames) of ONE clip and return its ``m`` frames
+        ``[m, hidden]``: the same rows the one-piece ``forward`` gives for these frames, because the convolutions continue
+        from the cached input tails and attention runs against the cached keys of the left window."""
+        x = piece.reshape(1, piece.shape[-2], piece.shape[-1]).to(self.embedder.conv1.weight.dtype)
+        e = self.embedder
+        tails = cache.conv_tails
+        if tails[0] is None:
+            tails[0] = x.new_zeros((1, x.shape[1], e.conv1.left_pad()))
+            tails[1] = x.new_zeros((1, e.conv2.in_channels, e.conv2.left_pad()))
+        h, tails[0] = e.conv1.continue_from(x, tails[0])
+        h, tails[1] = e.conv2.continue_from(F.gelu(h), tails[1])
+        flat = F.gelu(h)[0].transpose(0, 1).contiguous()
+        m = flat.shape[0]
+        cos, sin = self._rotary(torch.arange(cache.frames, cache.frames + m, device=x.device).float())
+        cu = torch.tensor([0, m], dtype=torch.int32, device=x.device)
+        for layer, past in zip(self.layers, cache.layers):
+            flat = layer(flat, cu, cos, sin, past)
+        cache.frames += m
+        return self.norm(flat)

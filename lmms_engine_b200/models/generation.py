@@ -112,13 +112,21 @@ def generate(model, input_ids: torch.Tensor, max_new_tokens: int, eos_token_id: 
 
 class RealtimeSession:
     """Streaming inference of the realtime model: after the prompt, every call of ``listen`` brings the mel features of
-    one audio slot (``[n_mels, 2 * downsample_factor]``, the ``chunk_audio`` layout of the processor, in which every slot
-    is encoded by itself) and returns the token the model emits for that slot - ``<|rt_pad|>`` while it stays silent,
-    speech tokens otherwise.  The emitted token is what the text stream carries at the NEXT slot, as in training, where
-    the stream at a slot holds the token spoken there and the label of a slot is the stream's next entry."""
+    one audio slot (``[n_mels, 2 * downsample_factor]``) and returns the token the model emits for that slot -
+    ``<|rt_pad|>`` while it stays silent, speech tokens otherwise.  The emitted token is what the text stream carries at
+    the NEXT slot, as in training, where the stream at a slot holds the token spoken there and the label of a slot is the
+    stream's next entry.
 
-    def __init__(self, model, rt_pad_id: int, audio_start_id: Optional[int] = None, max_slots: int = 4096):
+    ``continuous_audio = False``: every slot is encoded by itself (a model trained on the ``chunk_audio`` layout of the
+    processor).  ``True``: the slots are pieces of one clip - the audio encoder continues from its convolution tails and
+    its keys / values of the earlier slots, so slot t is encoded exactly as inside the whole clip (a model trained on whole
+    clips; the reference's padding cache plus encoder cache)."""
+
+    def __init__(self, model, rt_pad_id: int, audio_start_id: Optional[int] = None, max_slots: int = 4096,
+                 continuous_audio: bool = False):
         self.model, self.rt_pad = model, int(rt_pad_id)
+        self.continuous_audio = continuous_audio
+        self.audio_cache = None
         self.audio_start = audio_start_id
         self.max_slots = max_slots
         self.state: Optional[GenerationState] = None
@@ -131,6 +139,7 @@ class RealtimeSession:
         ids = prompt_ids.reshape(-1)
         self.state = GenerationState(self.model, ids.numel() + self.max_slots, ids.device)
         self.hidden = self.state.prefill(ids, **inputs)
+        self.audio_cache = self.model.audio_tower.new_stream() if self.continuous_audio else None
         self.last = _next_token(self.model, self.hidden, 0.0, None)  # what the stream carries at the first slot
 
     @torch.no_grad()
@@ -140,6 +149,7 @@ class RealtimeSession:
         feats = slot_features.reshape(1, slot_features.shape[-2], slot_features.shape[-1]).to(dev)
         mask = torch.ones((1, feats.shape[-1] // 2), dtype=torch.long, device=dev)
         slot = torch.tensor([cfg.audio_token_id], device=dev)
-        self.hidden = self.state.step(slot, text_stream_ids=self.last, input_features=feats, audio_attention_mask=mask)
+        extra = {"audio_stream_cache": self.audio_cache} if self.audio_cache is not None else {}
+        self.hidden = self.state.step(slot, text_stream_ids=self.last, input_features=feats, audio_attention_mask=mask, **extra)
         self.last = _next_token(self.model, self.hidden, temperature, generator)
         return int(self.last)

@@ -906,5 +906,59 @@ def test_streaming_audio_encoder_variants_against_plain_torch():
         assert moved.sum(1).tolist() == [1, 1] and moved[:, -1].all()
     with pytest.raises(ValueError):
         VoxtralRealtimeEncoderConfig.from_dict(dict(base, norm_type="batch_norm"))
-    with pytest.raises(NotImplementedError):
-        VoxtralRealtimeEncoderConfig.from_dict(dict(base, attention_window_right=2))
+
+
+def test_audio_encoder_stream_equals_the_whole_clip_and_look_ahead_is_bounded():
+    """(1) A clip encoded piece by piece on the stream cache (convolution tails, keys / values inside the left window)
+    gives the rows of the one-piece pass.  (2) With a look-ahead of two frames, a change in frame j moves frames
+    j - 2 ... j + left of a one-layer encoder and nothing else.  (3) The realtime session on continuous audio emits what
+    the full pass over the whole clip predicts."""
+    from lmms_engine_b200.models.audio import VoxtralRealtimeEncoder, VoxtralRealtimeEncoderConfig
+    from lmms_engine_b200.models.generation import RealtimeSession
+
+    torch.manual_seed(0)
+    base = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2, head_dim=16, num_mel_bins=8, sliding_window=5)
+    enc = VoxtralRealtimeEncoder(VoxtralRealtimeEncoderConfig.from_dict(base)).eval()
+    with torch.no_grad():
+        for p in enc.parameters():
+            p.normal_(0, 0.2)
+        clip = torch.randn(1, 8, 40)
+        whole = enc(clip)["last_hidden_state"]
+        cache = enc.new_stream()
+        rows = torch.cat([enc.stream(clip[0, :, a:b], cache) for a, b in ((0, 4), (4, 8), (8, 20), (20, 22), (22, 40))])
+        assert rows.shape == whole.shape and (rows - whole).abs().max() < 2e-5
+        assert cache.frames == 20 and cache.layers[0][0].shape[0] == 4  # sliding_window 5: the frame itself and 4 before it
+        with pytest.raises(ValueError):
+            enc.stream(clip[0, :, :3], enc.new_stream())
+
+        ahead = VoxtralRealtimeEncoder(VoxtralRealtimeEncoderConfig.from_dict(
+            dict(base, num_hidden_layers=1, attention_window_left=3, attention_window_right=2))).eval()
+        for p in ahead.parameters():
+            p.normal_(0, 0.2)
+        with pytest.raises(ValueError):
+            ahead.new_stream()
+        h = torch.randn(16, 32)
+        cu = torch.tensor([0, 16], dtype=torch.int32)
+        cos, sin = ahead._rotary(torch.arange(16).float())
+        h2 = h.clone()
+        h2[9] += 1.0
+        layer = ahead.layers[0].self_attn
+        moved = ((layer(h, cu, cos, sin) - layer(h2, cu, cos, sin)).abs().amax(-1) > 1e-7).nonzero().flatten().tolist()
+        assert moved == list(range(7, 13))  # frame i sees i - 3 ... i + 2, so frame 9 is seen by frames 7 ... 12
+
+    model, _, _ = _tiny_realtime()
+    AS, PAD_TOK, K = 294, 281, 6
+    prompt = torch.cat([torch.randint(0, 280, (10,)), torch.tensor([AS])])
+    feats = torch.randn(8, 4 * K)
+    session = RealtimeSession(model, rt_pad_id=PAD_TOK, continuous_audio=True)
+    session.start(prompt)
+    first = int(session.last)
+    emitted = [session.listen(feats[:, 4 * k:4 * k + 4]) for k in range(K)]
+    ids = torch.cat([prompt, torch.full((K,), 292)])
+    stream = torch.cat([prompt, torch.tensor([first] + emitted[:-1])])
+    with torch.no_grad():
+        cu = torch.tensor([0, ids.numel()], dtype=torch.int32)
+        hidden = model(input_ids=ids, cu_seqlens=cu, text_stream_ids=stream, input_features=feats[None],
+                       audio_attention_mask=torch.ones(1, 2 * K, dtype=torch.long))["hidden_states"]
+        want = F.linear(hidden, model.language_model.lm_head.weight).argmax(-1)
+    assert int(want[10]) == first and want[11:].tolist() == emitted
