@@ -50,5 +50,23 @@ class VisionCollator:
             vals = [s[key] for s in samples if key in s and s[key] is not None]
             if vals and all(torch.is_tensor(v) for v in vals):
                 # a clip is one item of the batch (its first axis is time), everything else is a list of rows
-                out[key] = torch.stack(vals, 0) if key in self.STACKED else torch.cat(vals, dim=0)
+                out[key] = torch.stack(vals, 0) if key in self.STACKED else self.join(key, vals)
+            elif vals and isinstance(vals[0], (bool, int, float)):
+                out[key] = vals[0]  # a flag of the whole batch (``use_audio_in_video``)
         return out
+
+    def join(self, key: str, vals):
+        return torch.cat(vals, dim=0)
+
+
+class LLaVACollator(VisionCollator):
+    """The padded collator for processors that give every image as ``[1, tiles, C, H, W]`` with its own number of tiles
+    (src/lmms_engine/datasets/collator/llava_collator.py:14-89): ``pixel_values`` are zero-padded on the tile axis to the
+    largest count of the batch before they are concatenated; rows that already agree pass unchanged."""
+
+    def join(self, key: str, vals):
+        if key == "pixel_values" and vals[0].dim() >= 3 and len({v.shape[1] for v in vals}) > 1:
+            most = max(v.shape[1] for v in vals)
+            vals = [torch.cat([v, v.new_zeros((v.shape[0], most - v.shape[1]) + tuple(v.shape[2:]))], 1) if v.shape[1] < most else v
+                    for v in vals]
+        return torch.cat(vals, dim=0)

@@ -80,3 +80,39 @@ register_model("gated_deltanet", GatedDeltaNetConfig, GatedDeltaNetLM, "causal_l
 from .llava_ov2 import LlavaOnevision2  # noqa: E402
 
 register_model("llava_onevision2", VLConfig, LlavaOnevision2, "image_text_to_text")
+
+
+# ---- the class names the reference exports from its ``models`` package (src/lmms_engine/models/__init__.py) -----------------
+_REFERENCE_NAMES = {
+    "AeroForConditionalGeneration": ("audio", "AeroModel"), "AeroConfig": ("audio", "AeroModel.config_class"),
+    "AeroProcessor": ("..datasets.extra", "Qwen2AudioProcessor"),
+    "AeroRealtimeForConditionalGeneration": ("aero_realtime", "AeroRealtimeModel"),
+    "AeroRealtimeProcessor": ("..datasets.realtime", "AeroRealtimeProcessor"),
+    "NanovlmForConditionalGeneration": ("nanovlm", "Nanovlm"),
+    "Qwen2_5OmniThinkerConfig": ("omni", "OmniThinkerConfig"), "Qwen2_5OmniThinkerForConditionalGeneration": ("omni", "OmniThinker"),
+    "Qwen3OmniMoeThinkerConfig": ("omni", "Omni3ThinkerConfig"), "Qwen3OmniMoeThinkerForConditionalGeneration": ("omni", "Omni3Thinker"),
+    "RaeSiglipModel": ("rae", "RaeSiglip"), "SiTModel": ("diffusion", "SiT"),
+    "WanVideoForConditionalGeneration": ("wan", "WanVideoModel"),
+    "WanVideoProcessor": ("..datasets.processor.generative_processors", "WanVideoProcessor"),
+    "Qwen3DLLMConfig": ("dllm", "DLLMConfig"), "DreamDLLMConfig": ("dllm", "DLLMConfig"), "LLaDADLLMConfig": ("dllm", "DLLMConfig"),
+    "Qwen3DLLMForMaskedLM": ("dllm", "DiffusionLM"), "DreamDLLMForMaskedLM": ("dllm", "DiffusionLM"), "LLaDADLLMForMaskedLM": ("dllm", "DiffusionLM"),
+    "Llavaonevision1_5Config": ("vl", "VLConfig"), "LLaVAOneVision1_5_ForConditionalGeneration": ("vl", "VLModel"),
+    "MONKEY_PATCHER": ("monkey_patch", "MONKEY_PATCHER"),
+}
+
+
+def __getattr__(name):
+    import importlib
+
+    if name in _REFERENCE_NAMES:
+        module, attr = _REFERENCE_NAMES[name]
+        package = __name__ if not module.startswith("..") else __name__.rsplit(".", 1)[0]
+        obj = importlib.import_module("." + module.lstrip("."), package)
+        for part in attr.split("."):
+            obj = getattr(obj, part)
+        return obj
+    if name.startswith("apply_liger_kernel_to_"):
+        from .monkey_patch import native_kernels_apply
+
+        return native_kernels_apply(name[len("apply_liger_kernel_to_"):])
+    raise AttributeError(name)

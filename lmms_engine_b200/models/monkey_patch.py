@@ -39,3 +39,17 @@ class MonkeyPatcher:
 
 
 MONKEY_PATCHER = MonkeyPatcher()
+
+
+def native_kernels_apply(family: str) -> Callable:
+    """What ``apply_liger_kernel_to_<family>`` is here.  The reference swaps library modules for Liger / unpadded ones
+    with these functions (src/lmms_engine/models/<family>/monkey_patch.py); the native models run the fused kernels
+    from the start, so the function has nothing to swap: it accepts the reference's arguments and runs the patches a
+    user registered for the family, if a model is given."""
+
+    def apply(model=None, **kwargs) -> int:
+        return MONKEY_PATCHER.apply(model, family, ["liger"], **kwargs) if model is not None else 0
+
+    apply.__name__ = f"apply_liger_kernel_to_{family}"
+    apply.__doc__ = native_kernels_apply.__doc__
+    return apply

@@ -61,3 +61,33 @@ def setup_distributed_logging(all_ranks: bool = False) -> None:
 def rank0_print(*args) -> None:
     if _rank() == 0:
         print(*args, flush=True)
+
+
+class Logging:
+    """The reference's older logging surface (src/lmms_engine/utils/logging_utils.py:52-95): static methods that print
+    on rank 0 only.  Kept for code written against it; new code uses ``logger``."""
+
+    @staticmethod
+    def _emit(level: str, msg: str) -> None:
+        if _rank() == 0:
+            getattr(logger, level)(msg)
+
+    @staticmethod
+    def info(msg: str) -> None:
+        Logging._emit("info", msg)
+
+    @staticmethod
+    def warning(msg: str) -> None:
+        Logging._emit("warning", msg)
+
+    @staticmethod
+    def error(msg: str) -> None:
+        Logging._emit("error", msg)
+
+    @staticmethod
+    def debug(msg: str) -> None:
+        Logging._emit("debug", msg)
+
+    @staticmethod
+    def null_logging(msg: str) -> None:
+        return None

@@ -520,3 +520,67 @@ def test_config_files_and_capability_probes(tmp_path, monkeypatch):
     assert iu.is_torch_npu_available() is False and isinstance(iu.is_video_audio_available(), bool)
     if not torch.cuda.is_available():
         assert not iu.is_flash_attn_2_available() and not iu.is_liger_kernel_available() and not iu.is_fused_moe_available()
+
+
+def test_public_class_names_of_the_reference_resolve():
+    """``from lmms_engine.<package> import <Name>`` works for the names the reference exports from its datasets, models,
+    train and utils packages; a custom dataset can subclass ``BaseDataset`` and register itself."""
+    import importlib
+
+    import torch
+
+    exported = {
+        "lmms_engine.datasets": ["DatasetConfig", "MultiModalDataset", "VisionSFTDataset", "VisionAudioSFTDataset", "FinewebEduDataset",
+                                 "MultiModalIterableDataset", "VisionSFTIterableDataset"],
+        "lmms_engine.datasets.naive": ["BaseDataset", "QwenOmniSFTDataset", "Qwen3VLDataset", "RaeDataset", "SitDataset", "LLaVAVideoDataset"],
+        "lmms_engine.datasets.iterable": ["AeroRealtimeIterableDataset", "BaseIterableDataset", "BagelIterableDataset", "LlavaOv2IterableDataset",
+                                          "Qwen3VLIterableDataset", "QwenOmniIterableDataset"],
+        "lmms_engine.datasets.collator": ["AeroRealtimeCollator", "VisionCollator", "BagelCollator", "LLaVACollator"],
+        "lmms_engine.datasets.processor": ["ProcessorConfig", "AeroDataProcessor", "AeroRealtimeDataProcessor", "BaseQwen2_5_DataProcessor",
+                                           "LLaVADataProcessor", "LLaVAVideoDataProcessor", "NanovlmDataProcessor", "Qwen2_5OmniDataProcessor",
+                                           "Qwen3OmniMoeDataProcessor", "Qwen2_5_VLDataProcessor", "Qwen2VLDataProcessor", "WanVideoDataProcessor",
+                                           "PureTextDataProcessor", "Qwen2DataProcessor", "BagelDataProcessor", "RaeSiglipDataProcessor",
+                                           "SitDataProcessor", "Qwen3_VLDataProcessor", "LlavaOnevision2DataProcessor"],
+        "lmms_engine.models": ["AeroForConditionalGeneration", "AeroConfig", "AeroRealtimeConfig", "AeroRealtimeForConditionalGeneration",
+                               "AeroRealtimeProcessor", "Bagel", "BagelConfig", "ModelConfig", "AeroProcessor", "MONKEY_PATCHER",
+                               "Qwen2_5OmniThinkerConfig", "Qwen2_5OmniThinkerForConditionalGeneration", "Qwen3OmniMoeThinkerConfig",
+                               "Qwen3OmniMoeThinkerForConditionalGeneration", "WanVideoConfig", "WanVideoForConditionalGeneration",
+                               "WanVideoProcessor", "NanovlmConfig", "NanovlmForConditionalGeneration", "RaeSiglipConfig", "RaeSiglipModel",
+                               "SiTModel", "SiTConfig", "SiT", "Qwen3DLLMForMaskedLM", "DreamDLLMConfig", "LLaDADLLMForMaskedLM",
+                               "Llavaonevision1_5Config", "LLaVAOneVision1_5_ForConditionalGeneration", "apply_liger_kernel_to_qwen3",
+                               "apply_liger_kernel_to_qwen3_vl_moe", "apply_liger_kernel_to_aero_realtime"],
+        "lmms_engine.train": ["TrainerConfig", "Trainer", "TrainingArguments", "TrainRunner", "TRAINER_REGISTER", "FSDP2SFTTrainer", "DLLMTrainer",
+                              "WanVideoTrainer"],
+        "lmms_engine.utils": ["Logging", "DataUtilities", "TrainUtilities", "StepProfiler", "ComputeTracker"],
+        "lmms_engine.protocol": ["Runnable", "Processable", "SFTChatData", "Args"],
+        "lmms_engine.merger": ["CheckpointMerger", "FSDP2Merger"],
+    }
+    for module, names in exported.items():
+        mod = importlib.import_module(module)
+        for name in names:
+            assert getattr(mod, name) is not None, (module, name)
+    with pytest.raises(AttributeError):
+        importlib.import_module("lmms_engine.datasets.naive").NoSuchDataset
+
+    from lmms_engine.datasets.collator import LLaVACollator
+    from lmms_engine.datasets.naive import BaseDataset
+    from lmms_engine.mapping_func import DATASET_MAPPING, register_dataset
+    from lmms_engine.models import MONKEY_PATCHER, apply_liger_kernel_to_qwen3
+
+    @register_dataset("my_custom_records")
+    class Mine(BaseDataset):
+        pass
+
+    assert DATASET_MAPPING.pop("my_custom_records") is Mine and hasattr(Mine, "get_collator") and hasattr(Mine, "build")
+    seen = []
+    MONKEY_PATCHER.register("qwen3", "liger")(lambda model, **kw: seen.append((model, kw)))
+    try:
+        assert apply_liger_kernel_to_qwen3() == 0 and apply_liger_kernel_to_qwen3(model="m", rope=True) == 1
+        assert seen == [("m", {"rope": True})]
+    finally:
+        MONKEY_PATCHER._patches.pop(("qwen3", "liger"))
+    batch = LLaVACollator(pad_token_id=0)([
+        {"input_ids": torch.arange(1, 4), "labels": torch.arange(1, 4), "pixel_values": torch.ones(1, 3, 2, 2, 2), "use_audio_in_video": False},
+        {"input_ids": torch.arange(1, 6), "labels": torch.arange(1, 6), "pixel_values": torch.ones(1, 5, 2, 2, 2), "use_audio_in_video": False}])
+    assert batch["pixel_values"].shape == (2, 5, 2, 2, 2) and batch["pixel_values"][0, 3:].abs().sum() == 0
+    assert batch["use_audio_in_video"] is False and batch["attention_mask"].sum(1).tolist() == [3, 5]
