@@ -250,3 +250,25 @@ def test_generation_on_cached_keys_gpu():
     _cuda.check_status()
     a, b = runs[0]["image_latent"].float(), runs[1]["image_latent"].float()
     assert torch.isfinite(a).all() and (a - b).abs().max() < 0.05 * b.abs().max() + 0.05
+
+
+def test_audio_encoder_stream_gpu():
+    """The streaming audio encoder on the varlen kernel: a few query frames against the cached keys of the left window
+    (bottom-right aligned causal mask plus sliding window) gives the rows of the one-piece pass, within bf16 noise."""
+    from lmms_engine_b200.models.audio import VoxtralRealtimeEncoder, VoxtralRealtimeEncoderConfig
+    from lmms_engine_b200.ops import _cuda
+
+    torch.manual_seed(0)
+    cfg = VoxtralRealtimeEncoderConfig.from_dict(dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=2,
+                                                      head_dim=64, num_mel_bins=16, sliding_window=24))
+    enc = VoxtralRealtimeEncoder(cfg).to("cuda", torch.bfloat16).eval()
+    clip = torch.randn(1, 16, 400, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        whole = enc(clip)["last_hidden_state"].float()
+        cache = enc.new_stream()
+        cuts = [0, 8, 16, 64, 72, 200, 208, 400]
+        rows = torch.cat([enc.stream(clip[0, :, a:b], cache) for a, b in zip(cuts[:-1], cuts[1:])]).float()
+    torch.cuda.synchronize()
+    _cuda.check_status()
+    assert rows.shape == whole.shape == (200, 128)
+    assert (rows - whole).abs().max() < 0.06 * whole.abs().max(), float((rows - whole).abs().max())
