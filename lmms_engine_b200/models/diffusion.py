@@ -465,6 +465,9 @@ class RaeAutoencoder(nn.Module):
     def last_layer(self):
         return self.to_pixels.weight
 
+    def last_layer_io(self):
+        return getattr(self, "_last_io", None)
+
     def patchify(self, x):
         B, C, H, W = x.shape
         p = self.config.patch_size
@@ -480,7 +483,10 @@ class RaeAutoencoder(nn.Module):
 
     def decode(self, z, B, hw):
         p = self.config.patch_size
-        out = self.to_pixels(self.decoder(z, B, hw)).float()
+        h = self.decoder(z, B, hw)
+        out = self.to_pixels(h)
+        self._last_io = (h, out) if out.requires_grad else None
+        out = out.float()
         return out.view(B, hw[0], hw[1], 3, p, p).permute(0, 3, 1, 4, 2, 5).reshape(B, 3, hw[0] * p, hw[1] * p)
 
     def forward(self, pixel_values=None, **kw):

@@ -45,7 +45,10 @@ def _prompt_positions(model, run) -> torch.Tensor:
 
 
 def _next_token(model, hidden_last: torch.Tensor, temperature: float, generator) -> torch.Tensor:
-    logits = F.linear(hidden_last, _decoder(model).lm_head.weight).float()
+    head = _decoder(model).lm_head.weight
+    if hasattr(head, "full_tensor"):  # held in shards by a wrapper outside the forward pass
+        head = head.full_tensor()
+    logits = F.linear(hidden_last, head).float()
     if temperature and temperature > 0:
         return torch.multinomial(torch.softmax(logits / temperature, -1), 1, generator=generator).flatten()
     return logits.argmax(-1)

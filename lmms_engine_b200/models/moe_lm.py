@@ -152,7 +152,8 @@ class MoEDecoderLM(DecoderLM):
         if aux:
             aux_loss = torch.stack([a.float() for a in aux]).mean()
             out["aux_loss"] = aux_loss
-            if out.get("loss") is not None and self.config.router_aux_loss_coef:
+            # per-token losses (``loss_reduction = "none"``, the log-probabilities of policy-gradient trainers) stay what they are
+            if out.get("loss") is not None and out["loss"].dim() == 0 and self.config.router_aux_loss_coef:
                 out["lm_loss"] = out["loss"].detach()
                 out["loss"] = out["loss"] + self.config.router_aux_loss_coef * aux_loss.to(out["loss"].dtype)
         return out

@@ -187,6 +187,7 @@ class MaeDecoder(nn.Module):
                 x = layer(x, cu)
         h = self.decoder_norm(x)
         logits = gemm_ops.linear(h, self.decoder_pred.weight, self.decoder_pred.bias)
+        self.last_layer_io = (h, logits) if logits.requires_grad else None
         return logits.view(B, N + 1, -1)[:, 1:], h.view(B, N + 1, -1)[:, 1:]
 
     def unpatchify(self, patches: torch.Tensor, size: Optional[Tuple[int, int]] = None) -> torch.Tensor:
@@ -241,6 +242,11 @@ class RaeSiglip(nn.Module):
     def last_layer(self) -> torch.Tensor:
         """Weight on which the adversarial term is balanced against the reconstruction term."""
         return self.decoder.decoder_pred.weight
+
+    def last_layer_io(self):
+        """Input rows and output of the last layer in the most recent training pass: the gradient of a loss with respect
+        to the last layer's weight is ``d_output^T @ input``, whatever wrapper holds the weight itself in shards."""
+        return getattr(self.decoder, "last_layer_io", None)
 
     def gradient_checkpointing_enable(self, **_):
         self.decoder.gradient_checkpointing = True

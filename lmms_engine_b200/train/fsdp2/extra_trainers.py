@@ -49,6 +49,14 @@ class BagelFSDP2Trainer(FSDP2SFTTrainer):
         return m
 
 
+def local_shard(t: torch.Tensor) -> torch.Tensor:
+    return t.to_local() if hasattr(t, "to_local") else t
+
+
+def whole_tensor(t: torch.Tensor) -> torch.Tensor:
+    return t.full_tensor() if hasattr(t, "full_tensor") else t
+
+
 @TRAINER_REGISTER.register("sit_trainer")
 class SitTrainer(FSDP2SFTTrainer):
     def __init__(self, *a, **k):
@@ -57,8 +65,9 @@ class SitTrainer(FSDP2SFTTrainer):
         self.ema_model = None
 
     def prepare_model(self):
+        twin = copy.deepcopy(self.model)  # before a sharding wrapper is applied: a wrapped model cannot be copied
         super().prepare_model()
-        self.ema_model = copy.deepcopy(self.model).requires_grad_(False).eval()
+        self.ema_model = self.prepare_frozen_twin(twin)
 
     def training_step(self, batch, do_step):
         out = super().training_step(batch, do_step)
@@ -66,13 +75,16 @@ class SitTrainer(FSDP2SFTTrainer):
             decay = self.args.ema_decay or 0.9999
             with torch.no_grad():
                 for pe, p in zip(self.ema_model.parameters(), self.model.parameters()):
+                    pe, p = local_shard(pe), local_shard(p)  # the twin is sharded like the model: shard meets shard
                     pe.lerp_(p.detach().to(pe.dtype), 1 - decay)
         return out
 
     def save_checkpoints(self, output_dir=None, step=None):
         path = super().save_checkpoints(output_dir, step)
-        if self.rank == 0 and self.ema_model is not None:
-            torch.save({k: v.cpu() for k, v in self.ema_model.state_dict().items()}, os.path.join(path, "ema.pt"))
+        if self.ema_model is not None:
+            full = {k: whole_tensor(v).cpu() for k, v in self.ema_model.state_dict().items()}  # a collective under sharding
+            if self.rank == 0:
+                torch.save(full, os.path.join(path, "ema.pt"))
         return path
 
 
@@ -194,9 +206,20 @@ class RaeTrainer(FSDP2SFTTrainer):
         return diff_augment(x, policy)
 
     def adaptive_weight(self, rec_loss, g_loss):
-        last = self.model.last_layer()
-        g_rec = torch.autograd.grad(rec_loss, last, retain_graph=True)[0]
-        g_gan = torch.autograd.grad(g_loss, last, retain_graph=True)[0]
+        """Ratio of the two terms' gradient norms at the last layer's weight.  The gradient is formed from the layer's
+        recorded input and output (``d_output^T @ input``): under a sharding wrapper the weight that took part in the
+        pass is a gathered temporary, so differentiating with respect to the module's (sharded) parameter finds nothing
+        (the reference differentiates the parameter with ``allow_unused``, src/lmms_engine/train/fsdp2/rae_trainer.py:446-472)."""
+        io = self.model.last_layer_io() if hasattr(self.model, "last_layer_io") else None
+        if io is None:
+            last = self.model.last_layer()
+            g_rec = torch.autograd.grad(rec_loss, last, retain_graph=True)[0]
+            g_gan = torch.autograd.grad(g_loss, last, retain_graph=True)[0]
+        else:
+            x, y = io
+            rows = x.detach().reshape(-1, x.shape[-1]).float()
+            g_rec, g_gan = (torch.autograd.grad(loss, y, retain_graph=True)[0].reshape(-1, y.shape[-1]).float().t() @ rows
+                            for loss in (rec_loss, g_loss))
         return (g_rec.norm() / (g_gan.norm() + 1e-6)).clamp(0, self.max_d_weight).detach()
 
     def gen_loss(self, logits_fake):
@@ -259,8 +282,18 @@ class RaeTrainer(FSDP2SFTTrainer):
         with torch.no_grad():
             for n, p in m.named_parameters():
                 if p.requires_grad:
-                    self.ema_state.setdefault(n, p.detach().float().clone()).lerp_(p.detach().float(), 1 - decay)
+                    q = local_shard(p.detach()).float()  # every rank averages the shard it holds
+                    self.ema_state.setdefault(n, q.clone()).lerp_(q, 1 - decay)
         return loss.detach(), gn
+
+    @staticmethod
+    def _whole_like(param, shard):
+        """The whole tensor of which ``shard`` is this rank's part, laid out like ``param``."""
+        if not hasattr(param, "to_local"):
+            return shard
+        from torch.distributed.tensor import DTensor
+
+        return DTensor.from_local(shard, param.device_mesh, param.placements, run_check=False).full_tensor()
 
     def calculate_training_metrics(self, seqlens, step_seconds):
         out = super().calculate_training_metrics(seqlens, step_seconds)
@@ -271,9 +304,12 @@ class RaeTrainer(FSDP2SFTTrainer):
         step = self.global_step if step is None else step
         out = os.path.join(output_dir or self.args.output_dir, f"checkpoint-{step}")
         os.makedirs(out, exist_ok=True)
+        weights = {k: whole_tensor(v).cpu() for k, v in self.model.state_dict().items()}  # collectives under sharding: every rank
+        params = dict(self.model.named_parameters())
+        ema = {k: self._whole_like(params[k], v).cpu() for k, v in self.ema_state.items()}
         if self.rank == 0:
-            torch.save({k: v.cpu() for k, v in self.model.state_dict().items()}, os.path.join(out, "model.pt"))
-            torch.save({k: v.cpu() for k, v in self.ema_state.items()}, os.path.join(out, "ema_state.pt"))
+            torch.save(weights, os.path.join(out, "model.pt"))
+            torch.save(ema, os.path.join(out, "ema_state.pt"))
             if self.discriminator is not None:
                 heads = {k: v.cpu() for k, v in self.discriminator.state_dict().items() if not k.startswith("dino.")}
                 torch.save({"discriminator": heads, "optimizer": self.disc_optimizer.state_dict()}, os.path.join(out, "discriminator.pt"))

@@ -165,6 +165,17 @@ class FSDP2SFTTrainer:
             kw["mp_policy"] = root_mp
         fully_shard(self.model, **kw)
 
+    def prepare_frozen_twin(self, twin):
+        """Give ``twin`` (a copy of the model taken BEFORE ``prepare_model``) the model's placement - device, dtype, and
+        under torch FSDP2 the same sharding wrappers - and freeze it: EMA weights, the reference policy of GRPO."""
+        keep = self.model
+        self.model = twin
+        try:
+            FSDP2SFTTrainer.prepare_model(self)
+        finally:
+            self.model = keep
+        return twin.requires_grad_(False).eval()
+
     def native_grad_dtype(self) -> torch.dtype:
         """Dtype of the native runtime's flat gradient buffer (accumulation across micro-batches and the
         cross-rank sum): ``reduce_dtype`` when it asks for fp32, the compute dtype otherwise."""

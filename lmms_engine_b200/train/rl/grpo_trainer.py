@@ -109,6 +109,9 @@ def sample_completions(model, prompts: Sequence[torch.Tensor], max_new_tokens: i
         n_layers = len(inner.model.layers)
         cache = PackedKVCache(n_layers, [p.numel() + max_new_tokens for p in prompts], device=dev)
     fed = [0] * len(seqs)  # tokens of every sequence that the cache holds
+    head = inner.lm_head.weight.detach()
+    if hasattr(head, "full_tensor"):  # held in shards by a wrapper outside the forward pass: gather once per rollout
+        head = head.full_tensor()
     for _ in range(max_new_tokens):
         live = [i for i, d in enumerate(done) if not d]
         if sync_group is not None:
@@ -142,7 +145,7 @@ def sample_completions(model, prompts: Sequence[torch.Tensor], max_new_tokens: i
             cu = F.pad(torch.cumsum(lens, 0, dtype=torch.int32), (1, 0))
             hidden = model(input_ids=ids, cu_seqlens=cu)["hidden_states"]
         last = hidden.index_select(0, (cu[1:] - 1).long())
-        logits = F.linear(last, model.lm_head.weight).float() / max(temperature, 1e-5)
+        logits = F.linear(last, head).float() / max(temperature, 1e-5)
         nxt = torch.multinomial(torch.softmax(logits, -1), 1, generator=generator).flatten()
         if token_group is not None:
             dist.broadcast(nxt, src=dist.get_global_rank(token_group, 0), group=token_group)
@@ -159,9 +162,18 @@ def packed_logprobs(model, ids: torch.Tensor, cu: torch.Tensor) -> torch.Tensor:
     """log p(token_t | prefix) for every position (0 at each document's first token)."""
     from ...models.decoder_lm import IGNORE_INDEX, shift_labels_per_document
 
-    hidden = model(input_ids=ids, cu_seqlens=cu)["hidden_states"]
     shifted = shift_labels_per_document(ids, cu)
-    nll = ce_ops.fused_linear_cross_entropy(hidden, model.lm_head.weight, shifted, "none")
+    inner = getattr(model, "module", model)
+    if getattr(inner, "sp_group", None) is None and getattr(inner, "tp_group", None) is None and hasattr(inner, "loss_reduction"):
+        # the head runs inside the forward pass, where a sharding wrapper has gathered its weight and will reduce its gradient
+        keep, inner.loss_reduction = inner.loss_reduction, "none"
+        try:
+            nll = model(input_ids=ids, labels=ids, cu_seqlens=cu)["loss"]
+        finally:
+            inner.loss_reduction = keep
+    else:
+        hidden = model(input_ids=ids, cu_seqlens=cu)["hidden_states"]
+        nll = ce_ops.fused_linear_cross_entropy(hidden, model.lm_head.weight, shifted, "none")
     # position t holds -log p(ids[t+1]); move it onto the token it scores
     out = torch.zeros_like(nll)
     out[1:] = -nll[:-1]
@@ -192,9 +204,10 @@ class GRPOTrainer(FSDP2SFTTrainer):
                              "combined with gradient_accumulation_steps > 1")
 
     def prepare_model(self):
+        twin = copy.deepcopy(self.model) if self.beta > 0 else None  # before a sharding wrapper is applied
         super().prepare_model()
-        if self.beta > 0:
-            self.ref_model = copy.deepcopy(self.model).requires_grad_(False).eval()
+        if twin is not None:
+            self.ref_model = self.prepare_frozen_twin(twin)
 
     def prompts_of(self, batch) -> List[torch.Tensor]:
         ids, cu = batch["input_ids"], batch["cu_seqlens"].tolist()

@@ -199,3 +199,25 @@ def test_rae_trainer_runs_the_full_recipe(tmp_path):
     # without critic weights the trainer refuses instead of training on noise
     with pytest.raises(FileNotFoundError):
         _run(tmp_path, "rae_trainer", "rae_siglip", dict(encoder_config=ENC, decoder_config=DEC), _tensors(spec), per_device_train_batch_size=2, steps=1)
+
+
+def test_adaptive_weight_from_the_last_layers_input_and_output_equals_the_weight_gradient():
+    """``d_output^T @ input`` is the gradient with respect to the last layer's weight: the trainer's sharding-proof form of
+    the GAN weight equals differentiating the parameter itself."""
+    import types
+
+    from lmms_engine_b200.mapping_func import create_model_from_config
+    from lmms_engine_b200.train.fsdp2.extra_trainers import RaeTrainer
+
+    torch.manual_seed(0)
+    model = create_model_from_config("rae_siglip", dict(image_size=32, patch_size=8, encoder_dim=32, encoder_depth=1, encoder_heads=2,
+                                                        decoder_dim=32, decoder_depth=1, decoder_heads=2)).train()
+    x = torch.rand(2, 3, 32, 32)
+    fake = types.SimpleNamespace(model=model, max_d_weight=1e4)
+    rec = RaeTrainer.reconstruct(fake, x).float() if hasattr(RaeTrainer, "reconstruct") else model(pixel_values=x)["out_pixels"]
+    rec_loss, g_loss = (rec - x).abs().mean(), (rec ** 2).mean() * 3.0
+    assert model.last_layer_io() is not None
+    got = RaeTrainer.adaptive_weight(fake, rec_loss, g_loss)
+    last = model.last_layer()
+    want = torch.autograd.grad(rec_loss, last, retain_graph=True)[0].norm() / (torch.autograd.grad(g_loss, last, retain_graph=True)[0].norm() + 1e-6)
+    assert abs(float(got) - float(want)) < 1e-4 * float(want)

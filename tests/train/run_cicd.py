@@ -47,6 +47,10 @@ def _vision(media: str = "image") -> dict:
                              "pixel_dtype": "float32"}}
 
 
+def _tensors(spec: dict) -> dict:
+    return {"dataset_type": "synthetic_tensors", "dataset_format": "synthetic", "extra_kwargs": {"spec": spec}}
+
+
 def _vl(model_type: str, text: dict) -> dict:
     return dict(model_type=model_type, text_config=dict(text), vision_config=dict(VISION), image_token_id=501, video_token_id=502,
                 vision_start_token_id=503)
@@ -67,7 +71,28 @@ FAMILIES: Dict[str, tuple] = {
     "qwen3_vl_moe": ("qwen3_vl_moe", _vl("qwen3_vl_moe", dict(VL_TEXT, **{k: MOE[k] for k in ("num_experts", "num_experts_per_tok",
                                                                                            "moe_intermediate_size", "norm_topk_prob")})),
                      _vision("image"), {}),
-    "qwen3_dllm": ("qwen3_dllm", LM, _packed(), {"trainer_type": "dllm_trainer"}),
+    "qwen2_5_vl": ("qwen2_5_vl", dict(model_type="qwen2_5_vl", text_config=dict(LM, rope_scaling={"mrope_section": [8, 4, 4]}),
+                                      vision_config=dict(depth=2, hidden_size=128, intermediate_size=256, num_heads=4, patch_size=8,
+                                                         temporal_patch_size=2, spatial_merge_size=2, out_hidden_size=128, window_size=32,
+                                                         fullatt_block_indexes=[1], in_channels=3),
+                                      image_token_id=501, video_token_id=502, vision_start_token_id=503), _vision("image"), {}),
+    "qwen3_dllm": ("qwen3_dllm", dict(LM, mask_token_id=511), _packed() | {"extra_kwargs": {"vocab_size": 500, "min_len": 16, "max_len": 128,
+                                                                                           "collator_type": "dllm", "mask_token_id": 511}},
+                   {"trainer_type": "dllm_trainer"}),
+    "hf_trainer": ("qwen2", LM, _packed(), {"trainer_type": "hf_trainer", "average_tokens_across_devices": True}),
+    "grpo": ("qwen2", LM, _packed() | {"extra_kwargs": {"vocab_size": 512, "min_len": 16, "max_len": 64, "prompt_len": 4}},
+             {"trainer_type": "grpo_trainer", "rl_config": {"group_size": 4, "max_new_tokens": 6, "reward": "repeat_last_prompt_token", "beta": 0.01}}),
+    "sit": ("sit", dict(input_size=8, hidden_size=128, depth=2, num_heads=4, num_classes=10),
+            _tensors({"pixel_values": {"shape": [4, 8, 8]}, "labels": {"shape": [], "kind": "randint", "high": 10}}),
+            {"trainer_type": "sit_trainer", "per_device_train_batch_size": 2}),
+    "wanvideo": ("wanvideo", dict(dim=128, ffn_dim=256, num_heads=4, num_layers=2, text_dim=64, in_dim=4, out_dim=4),
+                 _tensors({"latents": {"shape": [4, 2, 8, 8]}, "context": {"shape": [5, 64]}}),
+                 {"trainer_type": "wan_trainer", "per_device_train_batch_size": 2}),
+    "rae_siglip": ("rae_siglip", dict(image_size=32, patch_size=8, encoder_dim=128, encoder_depth=1, encoder_heads=2, decoder_dim=128,
+                                      decoder_depth=1, decoder_heads=2), _tensors({"pixel_values": {"shape": [3, 32, 32]}}),
+                   {"trainer_type": "rae_trainer", "per_device_train_batch_size": 2,
+                    "gan_config": dict(discriminator="patch", disc_dim=32, perceptual_weight=0.0, discriminator_start_step=0,
+                                       discriminator_loss_start_step=0)}),
 }
 
 
@@ -84,7 +109,8 @@ def write_config(name: str, out: str, steps: int, cpu: bool) -> str:
     extra = dict(extra)
     trainer_type = extra.pop("trainer_type", "fsdp2_trainer")
     targs = dict(output_dir=out, max_steps=steps, learning_rate=1e-3, per_device_train_batch_size=1, logging_steps=1, save_strategy="no",
-                 lr_scheduler_type="constant", seed=0, use_cpu=cpu, bf16=not cpu, ddp_timeout=120, report_to="none", **extra)
+                 lr_scheduler_type="constant", seed=0, use_cpu=cpu, bf16=not cpu, ddp_timeout=120, report_to="none")
+    targs.update(extra)
     cfg = [{"type": "trainer", "config": {"trainer_type": trainer_type, "dataset_config": dataset,
                                           "model_config": {"load_from_config": {"model_type": model_type, "config": model_cfg}},
                                           "trainer_args": targs}}]
