@@ -76,6 +76,12 @@ FAMILIES: Dict[str, tuple] = {
                                                          temporal_patch_size=2, spatial_merge_size=2, out_hidden_size=128, window_size=32,
                                                          fullatt_block_indexes=[1], in_channels=3),
                                       image_token_id=501, video_token_id=502, vision_start_token_id=503), _vision("image"), {}),
+    "llavaonevision1_5": ("llavaonevision1_5", dict(model_type="llavaonevision1_5", text_config=dict(LM, rope_theta=10000.0),
+                                                    vision_config=dict(depth=2, hidden_size=128, intermediate_size=256, num_heads=4, patch_size=8,
+                                                                       spatial_merge_size=2, text_hidden_size=128, hidden_act="gelu",
+                                                                       layer_norm_eps=1e-5),
+                                                    image_token_id=501, video_token_id=502),
+                          _vision("image") | {"extra_kwargs": dict(_vision("image")["extra_kwargs"], temporal_patch_size=1)}, {}),
     "qwen3_dllm": ("qwen3_dllm", dict(LM, mask_token_id=511), _packed() | {"extra_kwargs": {"vocab_size": 500, "min_len": 16, "max_len": 128,
                                                                                            "collator_type": "dllm", "mask_token_id": 511}},
                    {"trainer_type": "dllm_trainer"}),
