@@ -139,10 +139,16 @@ def sp_sharded_vit_forward(tower, patches: torch.Tensor, grid_thw: torch.Tensor,
         sub_grid = torch.tensor([frames[i] for i in mine], dtype=torch.long, device=patches.device).reshape(-1, 3)
         out = run(patches.index_select(0, rows), sub_grid)
         feats, deep = out if isinstance(out, tuple) else (out, None)
+    elif frames and any(hasattr(p, "to_local") for p in tower.parameters()):
+        # the tower's parameters are held in shards (FSDP2): its gathers and gradient reductions are collectives that every
+        # rank must enter, so a rank without a frame runs the smallest frame of the sample and keeps none of its rows
+        # (the empty slices stay in the graph, which sends zero gradients through the wrapper's reductions)
+        i = min(range(len(frames)), key=lambda j: (sizes[j], j))
+        rows = torch.arange(starts[i], starts[i + 1], device=patches.device)
+        out = run(patches.index_select(0, rows), torch.tensor([frames[i]], dtype=torch.long, device=patches.device))
+        feats, deep = out if isinstance(out, tuple) else (out, None)
+        feats, deep = feats[:0], ([d[:0] for d in deep] if deep is not None else None)
     else:
-        if any(hasattr(p, "to_local") for p in tower.parameters()):
-            raise RuntimeError("a sequence-parallel rank received no frame while the tower's parameters are sharded (FSDP2): "
-                               "a sharded tower must run on every rank")
         feats = patches.new_zeros((0, tower.cfg.out_hidden_size)) + 0.0 * sum(p.sum() for p in tower.parameters() if p.requires_grad).to(patches.dtype)
         deep = [feats for _ in range(n_deep)] if n_deep else None
     counts = [sum(sizes[i] for i in range(len(frames)) if owner[i] == r) // unit for r in range(n)]

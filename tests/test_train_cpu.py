@@ -240,7 +240,8 @@ def test_training_smoke_suite_runs_a_family_through_the_command_line():
     spec.loader.exec_module(suite)
     assert suite.main(["--cpu", "--gpu-count", "2", "--model-name", "qwen3_moe_ep", "--no-verbose", "--steps", "2"]) == 0
     # trainers that keep a frozen twin of the model (EMA weights, the GRPO reference policy) or differentiate at the last layer
-    # (the GAN weight of the autoencoder trainer) under the sharding wrapper of two ranks
-    assert suite.main(["--cpu", "--gpu-count", "2", "--model-name", "grpo,sit,rae_siglip", "--no-verbose", "--steps", "2"]) == 0
+    # (the GAN weight of the autoencoder trainer) under the sharding wrapper of two ranks; a sharded vision tower on a
+    # sequence-parallel rank that received no frame of the sample
+    assert suite.main(["--cpu", "--gpu-count", "2", "--model-name", "grpo,sit,rae_siglip,qwen3_vl_sp", "--no-verbose", "--steps", "3"]) == 0
     assert suite.main(["--cpu", "--model-name", "no_such_family"]) == 2
     assert suite.main(["--cpu", "--gpu-count", "1", "--model-name", "qwen3_sp", "--no-verbose"]) == 0  # skipped: needs 2 ranks

@@ -71,6 +71,16 @@ FAMILIES: Dict[str, tuple] = {
     "qwen3_vl_moe": ("qwen3_vl_moe", _vl("qwen3_vl_moe", dict(VL_TEXT, **{k: MOE[k] for k in ("num_experts", "num_experts_per_tok",
                                                                                            "moe_intermediate_size", "norm_topk_prob")})),
                      _vision("image"), {}),
+    "qwen3_tp": ("qwen3", LM, _packed(), {"tp_degree": 2}),
+    "qwen3_vl_sp": ("qwen3_vl", _vl("qwen3_vl", VL_TEXT), _vision("video"), {"sp_ulysses_degree": 2}),
+    "qwen3_vl_tp": ("qwen3_vl", _vl("qwen3_vl", VL_TEXT), _vision("image"), {"tp_degree": 2}),
+    "qwen3_vl_moe_ep": ("qwen3_vl_moe", _vl("qwen3_vl_moe", dict(VL_TEXT, **{k: MOE[k] for k in ("num_experts", "num_experts_per_tok",
+                                                                                              "moe_intermediate_size", "norm_topk_prob")})),
+                        _vision("image"), {"ep_degree": 2}),
+    "qwen3_5_moe_ep": ("qwen3_5_moe_text", dict(HYBRID, **{k: MOE[k] for k in ("num_experts", "num_experts_per_tok", "moe_intermediate_size",
+                                                                             "norm_topk_prob", "router_aux_loss_coef")}), _packed(),
+                       {"ep_degree": 2}),
+    "qwen3_5_sp": ("qwen3_5_text", HYBRID, _packed(), {"sp_ulysses_degree": 2}),
     "qwen2_5_vl": ("qwen2_5_vl", dict(model_type="qwen2_5_vl", text_config=dict(LM, rope_scaling={"mrope_section": [8, 4, 4]}),
                                       vision_config=dict(depth=2, hidden_size=128, intermediate_size=256, num_heads=4, patch_size=8,
                                                          temporal_patch_size=2, spatial_merge_size=2, out_hidden_size=128, window_size=32,
